@@ -1,0 +1,360 @@
+// Kronecker-factor construction: out = alpha * X^T X + beta * out where X is a
+// dense matrix, the im2col patch matrix of an NCHW input or an NCHW output
+// gradient viewed as (n*ho*wo, c).  X is gathered tile by tile and never
+// written to memory.  Only tiles on or below the diagonal are computed; the
+// epilogue mirrors them.  Long contractions are split across CTAs; partial
+// tiles go through a workspace and are summed in a fixed order.
+#include "gemm_simt.cuh"
+
+namespace kfac {
+
+struct FactorSplit {
+  int nt;          // tiles per side
+  int tiles;       // nt (nt + 1) / 2
+  int splits;      // CTAs along the contraction
+  long long rows_per_split;
+};
+
+static FactorSplit factor_split(long long rows, int d) {
+  FactorSplit s;
+  s.nt = (d + TM - 1) / TM;
+  s.tiles = s.nt * (s.nt + 1) / 2;
+  long long target = 4LL * sm_count();             // ~2 waves of 2 CTAs / SM
+  long long by_tiles = (target + s.tiles - 1) / s.tiles;
+  long long by_rows = (rows + 1023) / 1024;        // >= 64 k-stages per CTA
+  long long sp = by_tiles < by_rows ? by_tiles : by_rows;
+  if (sp < 1) sp = 1;
+  long long rps = (rows + sp - 1) / sp;
+  rps = (rps + TK - 1) / TK * TK;
+  if (rps < TK) rps = TK;
+  s.splits = (int)((rows + rps - 1) / rps);
+  if (s.splits < 1) s.splits = 1;
+  s.rows_per_split = rps;
+  return s;
+}
+
+__global__ void __launch_bounds__(NT, 2)
+factor_kernel(Operand X, long long rows, int d, int tiles,
+              long long rows_per_split, int splits, float alpha, float beta,
+              float* __restrict__ out, float* __restrict__ partial) {
+  __shared__ TileSmem sm;
+  int bi, bj;
+  tri_tile(blockIdx.x, bi, bj);
+  const int m0 = bi * TM, n0 = bj * TN;
+  const long long kbeg = (long long)blockIdx.y * rows_per_split;
+  const long long kend = min(rows, kbeg + rows_per_split);
+
+  float acc[8][8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+
+  tile_mainloop(X, X, m0, n0, kbeg, kend, sm, acc);
+
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  if (splits > 1) {
+    float* p = partial + ((long long)blockIdx.y * tiles + blockIdx.x) * (TM * TN);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      int lr = tile_row(ty, i);
+      *reinterpret_cast<float4*>(p + lr * TN + tx * 4) =
+          make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+      *reinterpret_cast<float4*>(p + lr * TN + 64 + tx * 4) =
+          make_float4(acc[i][4], acc[i][5], acc[i][6], acc[i][7]);
+    }
+    return;
+  }
+  const bool mirror = bi != bj;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    int r = m0 + tile_row(ty, i);
+    if (r >= d) continue;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      int c = n0 + tile_row(tx, j);
+      if (c >= d) continue;
+      float* q = out + (long long)r * d + c;
+      float v = alpha * acc[i][j];
+      if (beta != 0.f) v += beta * (*q);
+      *q = v;
+      if (mirror) out[(long long)c * d + r] = v;
+    }
+  }
+}
+
+// Sum the partial tiles of every split (ascending split order), scale, blend
+// with the previous contents and write both triangles.
+__global__ void __launch_bounds__(NT)
+factor_reduce_kernel(const float* __restrict__ partial, int tiles, int splits,
+                     int d, float alpha, float beta, float* __restrict__ out) {
+  int bi, bj;
+  tri_tile(blockIdx.x, bi, bj);
+  const int m0 = bi * TM, n0 = bj * TN;
+  const int tid = threadIdx.x;
+  const int lr = blockIdx.y * 8 + (tid >> 5);
+  const int lc = (tid & 31) * 4;
+  const int r = m0 + lr;
+  if (r >= d) return;
+  const float* p = partial + (long long)blockIdx.x * (TM * TN) + lr * TN + lc;
+  float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int sp = 0; sp < splits; ++sp) {
+    float4 v = *reinterpret_cast<const float4*>(p + (long long)sp * tiles * (TM * TN));
+    s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+  }
+  const float vals[4] = {s.x, s.y, s.z, s.w};
+  const bool mirror = bi != bj;
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    int c = n0 + lc + e;
+    if (c >= d) continue;
+    float* q = out + (long long)r * d + c;
+    float v = alpha * vals[e];
+    if (beta != 0.f) v += beta * (*q);
+    *q = v;
+    if (mirror) out[(long long)c * d + r] = v;
+  }
+}
+
+static int run_factor(const Operand& X, long long rows, int d, float alpha,
+                      float beta, float* out, void* workspace,
+                      size_t workspace_bytes, cudaStream_t stream) {
+  KFAC_REQUIRE(out != nullptr && X.base != nullptr, "factor: null pointer");
+  KFAC_REQUIRE(rows > 0 && d > 0, "factor: rows=%lld d=%d must be positive",
+               rows, d);
+  FactorSplit s = factor_split(rows, d);
+  float* partial = nullptr;
+  if (s.splits > 1) {
+    size_t need = (size_t)s.splits * s.tiles * TM * TN * sizeof(float);
+    if (workspace == nullptr || workspace_bytes < need)
+      return fail(KFAC_ERR_WORKSPACE,
+                  "factor: workspace of %zu bytes needed, %zu given", need,
+                  workspace_bytes);
+    partial = static_cast<float*>(workspace);
+  }
+  dim3 grid(s.tiles, s.splits);
+  factor_kernel<<<grid, NT, 0, stream>>>(X, rows, d, s.tiles,
+                                         s.rows_per_split, s.splits, alpha,
+                                         beta, out, partial);
+  KFAC_LAUNCH_CHECK("factor_kernel");
+  if (s.splits > 1) {
+    dim3 rgrid(s.tiles, TM / 8);
+    factor_reduce_kernel<<<rgrid, NT, 0, stream>>>(partial, s.tiles, s.splits,
+                                                   d, alpha, beta, out);
+    KFAC_LAUNCH_CHECK("factor_reduce_kernel");
+  }
+  return KFAC_OK;
+}
+
+// ------------------------------------------------------------ BN sample grads
+// Pass 1: per-channel batch mean and 1/sqrt(var + eps) over (n, hw).
+__global__ void bn_stats_kernel(const float* __restrict__ x, int n, int c,
+                                int hw, float eps, float* __restrict__ stats) {
+  const int ch = blockIdx.x;
+  double s = 0.0, ss = 0.0;
+  const long long per = (long long)n * hw;
+  for (long long i = threadIdx.x; i < per; i += blockDim.x) {
+    long long smp = i / hw;
+    long long off = (smp * c + ch) * hw + (i - smp * hw);
+    double v = x[off];
+    s += v;
+    ss += v * v;
+  }
+  __shared__ double sh[2][32];
+  for (int o = 16; o > 0; o >>= 1) {
+    s += __shfl_down_sync(0xffffffffu, s, o);
+    ss += __shfl_down_sync(0xffffffffu, ss, o);
+  }
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  if (l == 0) { sh[0][w] = s; sh[1][w] = ss; }
+  __syncthreads();
+  if (w == 0) {
+    const int nw = blockDim.x >> 5;
+    s = l < nw ? sh[0][l] : 0.0;
+    ss = l < nw ? sh[1][l] : 0.0;
+    for (int o = 16; o > 0; o >>= 1) {
+      s += __shfl_down_sync(0xffffffffu, s, o);
+      ss += __shfl_down_sync(0xffffffffu, ss, o);
+    }
+    if (l == 0) {
+      double mean = s / (double)per;
+      double var = ss / (double)per - mean * mean;
+      if (var < 0.0) var = 0.0;
+      stats[ch] = (float)mean;
+      stats[c + ch] = (float)(1.0 / sqrt(var + (double)eps));
+    }
+  }
+}
+
+// Pass 2: one warp per (sample, channel): sum_hw gy*xhat and sum_hw gy.
+__global__ void bn_sample_grads_kernel(const float* __restrict__ x,
+                                       const float* __restrict__ gy, int n,
+                                       int c, int hw, float scale,
+                                       const float* __restrict__ stats,
+                                       float* __restrict__ out) {
+  const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= (long long)n * c) return;
+  const int smp = (int)(warp / c), ch = (int)(warp - (long long)smp * c);
+  const float mean = stats[ch], istd = stats[c + ch];
+  const float* px = x + warp * hw;
+  const float* pg = gy + warp * hw;
+  float a = 0.f, b = 0.f;
+  for (int i = lane; i < hw; i += 32) {
+    float g = pg[i] * scale;
+    a += g * ((px[i] - mean) * istd);
+    b += g;
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    a += __shfl_down_sync(0xffffffffu, a, o);
+    b += __shfl_down_sync(0xffffffffu, b, o);
+  }
+  if (lane == 0) {
+    out[(long long)smp * 2 * c + ch] = a;
+    out[(long long)smp * 2 * c + c + ch] = b;
+  }
+}
+
+__global__ void axpby_kernel(long long count, float a,
+                             const float* __restrict__ x, float b,
+                             const float* y, float* out) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (; i < count; i += stride) {
+    float v = a * x[i];
+    if (b != 0.f) v += b * y[i];
+    out[i] = v;
+  }
+}
+
+__global__ void momentum_kernel(long long count, const float* __restrict__ grad,
+                                float* param, float* v, float lr,
+                                float momentum) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (; i < count; i += stride) {
+    float nv = momentum * v[i] - lr * grad[i];
+    v[i] = nv;
+    param[i] += nv;
+  }
+}
+
+}  // namespace kfac
+
+using namespace kfac;
+
+extern "C" size_t kfac_factor_workspace_bytes(int64_t rows, int d) {
+  if (rows <= 0 || d <= 0) return 0;
+  FactorSplit s = factor_split(rows, d);
+  if (s.splits <= 1) return 0;
+  return (size_t)s.splits * s.tiles * TM * TN * sizeof(float);
+}
+
+extern "C" int kfac_factor_dense(const float* x, int64_t rows, int d_in,
+                                 int64_t ld, int add_ones_col, float alpha,
+                                 float beta, float* out, void* workspace,
+                                 size_t workspace_bytes, void* stream) {
+  KFAC_REQUIRE(ld >= d_in, "factor_dense: ld=%lld < d_in=%d", (long long)ld,
+               d_in);
+  Operand X = strided_operand(x, ld, 1, d_in);
+  if (add_ones_col) X.extra_idx = d_in;
+  return run_factor(X, rows, d_in + (add_ones_col ? 1 : 0), alpha, beta, out,
+                    workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+extern "C" int kfac_factor_conv_input(const float* x, int n, int c, int h,
+                                      int w, int ksize, int stride, int pad,
+                                      int add_ones_col, float alpha, float beta,
+                                      float* out, void* workspace,
+                                      size_t workspace_bytes, void* stream) {
+  KFAC_REQUIRE(n > 0 && c > 0 && h > 0 && w > 0 && ksize > 0 && stride > 0 &&
+                   pad >= 0,
+               "factor_conv_input: bad geometry n=%d c=%d h=%d w=%d k=%d s=%d "
+               "p=%d", n, c, h, w, ksize, stride, pad);
+  KFAC_REQUIRE((long long)n * c * h * w < (1LL << 31),
+               "factor_conv_input: input has more than 2^31 elements");
+  int ho = (h + 2 * pad - ksize) / stride + 1;
+  int wo = (w + 2 * pad - ksize) / stride + 1;
+  KFAC_REQUIRE(ho > 0 && wo > 0, "factor_conv_input: empty output");
+  Operand X = {};
+  X.base = x;
+  X.ncols = c * ksize * ksize;
+  X.extra_idx = add_ones_col ? X.ncols : -1;
+  X.kfast = 1;
+  X.mode = 1;
+  X.period = 1;
+  X.C = c; X.H = h; X.W = w; X.ks = ksize; X.st = stride; X.pd = pad;
+  X.Ho = ho; X.Wo = wo;
+  if (ksize == 1 && pad == 0 && stride == 1) {
+    // 1x1 convolution: the patch matrix is the NCHW tensor viewed as
+    // (n*h*w, c); no gather needed.
+    X = strided_operand(x, 0, (long long)h * w, c);
+    X.period = h * w;
+    X.s_outer = (long long)c * h * w;
+    X.s_inner = 1;
+    X.kfast = 1;
+    X.extra_idx = add_ones_col ? c : -1;
+  }
+  int d = c * ksize * ksize + (add_ones_col ? 1 : 0);
+  return run_factor(X, (long long)n * ho * wo, d, alpha, beta, out, workspace,
+                    workspace_bytes, (cudaStream_t)stream);
+}
+
+extern "C" int kfac_factor_conv_grad(const float* gy, int n, int c, int ho,
+                                     int wo, float alpha, float beta,
+                                     float* out, void* workspace,
+                                     size_t workspace_bytes, void* stream) {
+  KFAC_REQUIRE(n > 0 && c > 0 && ho > 0 && wo > 0,
+               "factor_conv_grad: bad geometry n=%d c=%d ho=%d wo=%d", n, c, ho,
+               wo);
+  Operand X = strided_operand(gy, 0, (long long)ho * wo, c);
+  X.period = ho * wo;
+  X.s_outer = (long long)c * ho * wo;
+  X.s_inner = 1;
+  X.kfast = 1;
+  return run_factor(X, (long long)n * ho * wo, c, alpha, beta, out, workspace,
+                    workspace_bytes, (cudaStream_t)stream);
+}
+
+extern "C" int kfac_bn_sample_grads(const float* x, const float* gy, int n,
+                                    int c, int hw, float eps, float scale,
+                                    float* out, float* stats, void* stream) {
+  KFAC_REQUIRE(x && gy && out && stats, "bn_sample_grads: null pointer");
+  KFAC_REQUIRE(n > 0 && c > 0 && hw > 0, "bn_sample_grads: bad shape");
+  cudaStream_t st = (cudaStream_t)stream;
+  bn_stats_kernel<<<c, 256, 0, st>>>(x, n, c, hw, eps, stats);
+  KFAC_LAUNCH_CHECK("bn_stats_kernel");
+  long long warps = (long long)n * c;
+  int blocks = ceil_div(warps * 32, 256);
+  bn_sample_grads_kernel<<<blocks, 256, 0, st>>>(x, gy, n, c, hw, scale, stats,
+                                                 out);
+  KFAC_LAUNCH_CHECK("bn_sample_grads_kernel");
+  return KFAC_OK;
+}
+
+extern "C" int kfac_axpby(int64_t count, float a, const float* x, float b,
+                          const float* y, float* out, void* stream) {
+  if (count <= 0) return KFAC_OK;
+  KFAC_REQUIRE(x && out && (b == 0.f || y), "axpby: null pointer");
+  int blocks = ceil_div(count, 256 * 4);
+  int cap = sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  axpby_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(count, a, x, b, y,
+                                                         out);
+  KFAC_LAUNCH_CHECK("axpby_kernel");
+  return KFAC_OK;
+}
+
+extern "C" int kfac_momentum_update(int64_t count, const float* grad,
+                                    float* param, float* v, float lr,
+                                    float momentum, void* stream) {
+  if (count <= 0) return KFAC_OK;
+  KFAC_REQUIRE(grad && param && v, "momentum_update: null pointer");
+  int blocks = ceil_div(count, 256 * 4);
+  int cap = sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  momentum_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(count, grad, param,
+                                                            v, lr, momentum);
+  KFAC_LAUNCH_CHECK("momentum_kernel");
+  return KFAC_OK;
+}

@@ -1,0 +1,483 @@
+// Batched damped inverse of symmetric positive definite factors.
+//
+//   W = F + add * I                     (copy; the running average F is kept)
+//   W = L L^T                           blocked right-looking Cholesky, NB = 128
+//   X = L^-1                            diagonal blocks in the factor kernel,
+//                                       off-diagonal blocks by recursive doubling
+//   inv = X^T X                         symmetric product, lower tiles mirrored
+//
+// A plan precomputes, for a fixed set of matrices, the descriptor lists of
+// every grouped-GEMM launch; running it replays ~3 launches per 128-column
+// panel of the largest matrix plus 2 per doubling level, each launch covering
+// all matrices that are still active.
+#include <vector>
+#include <algorithm>
+
+#include "gemm_simt.cuh"
+
+namespace kfac {
+
+constexpr int DB = 128;        // diagonal block
+constexpr int DLD = DB + 1;    // shared-memory pitch
+
+struct MatInfo {
+  const float* F;
+  float* inv;
+  float* W;
+  float* X;
+  int d;
+  int partner;
+  int role;
+  float l2;
+  float scale;
+  int pad_;
+};
+
+__global__ void trace_kernel(const MatInfo* __restrict__ mats,
+                             float* __restrict__ trace, int* __restrict__ info) {
+  const MatInfo mi = mats[blockIdx.x];
+  float s = 0.f;
+  for (int i = threadIdx.x; i < mi.d; i += blockDim.x)
+    s += mi.F[(long long)i * mi.d + i];
+  __shared__ float sh[32];
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_down_sync(0xffffffffu, s, o);
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    s = threadIdx.x < (blockDim.x >> 5) ? sh[threadIdx.x] : 0.f;
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_down_sync(0xffffffffu, s, o);
+    if (threadIdx.x == 0) {
+      trace[blockIdx.x] = s;
+      info[blockIdx.x] = 0;
+    }
+  }
+}
+
+__global__ void damping_kernel(const MatInfo* __restrict__ mats, int count,
+                               const float* __restrict__ trace, float damping,
+                               int use_pi, float* __restrict__ add,
+                               float* __restrict__ add_out) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= count) return;
+  const MatInfo mi = mats[i];
+  float g = fmaxf(mi.l2, damping);
+  float v;
+  if (mi.role == 2) {
+    v = g * mi.scale;
+  } else {
+    float r = sqrtf(g);
+    float pi = 1.f;
+    if (use_pi && mi.partner >= 0) {
+      const MatInfo mp = mats[mi.partner];
+      // pi = sqrt(tr(A) dim(G) / (tr(G) dim(A))) with A the forward factor
+      float tA = mi.role == 0 ? trace[i] : trace[mi.partner];
+      float tG = mi.role == 0 ? trace[mi.partner] : trace[i];
+      float dA = (float)(mi.role == 0 ? mi.d : mp.d);
+      float dG = (float)(mi.role == 0 ? mp.d : mi.d);
+      pi = sqrtf((tA * dG) / (tG * dA));
+    }
+    v = mi.role == 0 ? pi * r : (1.f / pi) * r;
+  }
+  add[i] = v;
+  if (add_out) add_out[i] = v;
+}
+
+// W = F + add * I, blockIdx.y = matrix.
+__global__ void damp_copy_kernel(const MatInfo* __restrict__ mats,
+                                 const float* __restrict__ add) {
+  const MatInfo mi = mats[blockIdx.y];
+  const float a = add[blockIdx.y];
+  const long long total = (long long)mi.d * mi.d;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+       i < total; i += stride) {
+    int r = (int)(i / mi.d);
+    int c = (int)(i - (long long)r * mi.d);
+    float v = mi.F[i];
+    if (r == c) v += a;
+    mi.W[i] = v;
+  }
+}
+
+// Factor one diagonal block (<= 128 x 128) of W in shared memory and invert
+// the resulting triangle: W_jj <- L_jj (lower), X_jj <- L_jj^-1 (lower, upper
+// part zero).  One CTA per matrix that still has a block at `step`.
+__global__ void __launch_bounds__(256)
+chol_diag_kernel(const MatInfo* __restrict__ mats, const int* __restrict__ ids,
+                 int step, int* __restrict__ info) {
+  extern __shared__ float dsm[];
+  float (*S)[DLD] = reinterpret_cast<float (*)[DLD]>(dsm);
+  float (*X)[DLD] = reinterpret_cast<float (*)[DLD]>(dsm + DB * DLD);
+  float* dg = dsm + 2 * DB * DLD;
+  const int id = ids[blockIdx.x];
+  const MatInfo mi = mats[id];
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const int o = step * DB;
+  const int bs = min(DB, mi.d - o);
+  const int pb = (bs + 15) & ~15;
+  const long long ld = mi.d;
+  float* Wd = mi.W + (long long)o * ld + o;
+  float* Xd = mi.X + (long long)o * ld + o;
+
+  for (int idx = tid; idx < pb * pb; idx += 256) {
+    int i = idx / pb, j = idx - i * pb;
+    float v = 0.f;
+    if (i < bs && j <= i) v = Wd[i * ld + j];
+    else if (i == j) v = 1.f;
+    S[i][j] = v;
+    X[i][j] = 0.f;
+  }
+
+  for (int k = 0; k < pb; ++k) {
+    __syncthreads();
+    float akk = S[k][k];
+    if (!(akk > 0.f)) {
+      if (tid == 0) atomicCAS(&info[id], 0, o + k + 1);
+      akk = 1.f;
+    }
+    const float l = sqrtf(akk);
+    const float rl = 1.f / l;
+    if (tid == 0) dg[k] = l;
+    for (int i = k + 1 + tid; i < pb; i += 256) S[i][k] *= rl;
+    __syncthreads();
+    const int n = pb - k - 1;
+    for (int ii = ty; ii < n; ii += 16) {
+      const int i = k + 1 + ii;
+      const float lik = S[i][k];
+      for (int jj = tx; jj <= ii; jj += 16) {
+        const int j = k + 1 + jj;
+        S[i][j] -= lik * S[j][k];
+      }
+    }
+  }
+  __syncthreads();
+  if (tid < pb) S[tid][tid] = dg[tid];
+  __syncthreads();
+
+  for (int idx = tid; idx < bs * bs; idx += 256) {
+    int i = idx / bs, j = idx - i * bs;
+    if (j <= i) Wd[i * ld + j] = S[i][j];
+  }
+
+  // inverse of the 16x16 diagonal blocks, one thread per column
+  if (tid < pb) {
+    const int base = tid & ~15, c = tid & 15;
+    X[base + c][base + c] = 1.f / S[base + c][base + c];
+    for (int i = c + 1; i < 16; ++i) {
+      float s = 0.f;
+      for (int k = c; k < i; ++k) s += S[base + i][base + k] * X[base + k][base + c];
+      X[base + i][base + c] = -s / S[base + i][base + i];
+    }
+  }
+  __syncthreads();
+
+  // recursive doubling: X21 = -X22 * (L21 * X11)
+  for (int b = 16; b < pb; b <<= 1) {
+    const int nch = (pb + 2 * b - 1) / (2 * b);
+    const int total = nch * b * b;
+    for (int idx = tid; idx < total; idx += 256) {
+      int ch = idx / (b * b);
+      int rem = idx - ch * b * b;
+      int m = rem / b, n = rem - m * b;
+      int s = ch * 2 * b;
+      if (s + b >= pb) continue;
+      int r = min(b, pb - s - b);
+      if (m >= r) continue;
+      float t = 0.f;
+      for (int k = n; k < b; ++k) t += S[s + b + m][s + k] * X[s + k][s + n];
+      X[s + n][s + b + m] = t;  // parked in the unused upper block
+    }
+    __syncthreads();
+    for (int idx = tid; idx < total; idx += 256) {
+      int ch = idx / (b * b);
+      int rem = idx - ch * b * b;
+      int m = rem / b, n = rem - m * b;
+      int s = ch * 2 * b;
+      if (s + b >= pb) continue;
+      int r = min(b, pb - s - b);
+      if (m >= r) continue;
+      float t = 0.f;
+      for (int k = 0; k <= m; ++k) t += X[s + b + m][s + b + k] * X[s + n][s + b + k];
+      X[s + b + m][s + n] = -t;
+    }
+    __syncthreads();
+  }
+
+  for (int idx = tid; idx < bs * bs; idx += 256) {
+    int i = idx / bs, j = idx - i * bs;
+    Xd[i * ld + j] = (j <= i) ? X[i][j] : 0.f;
+  }
+}
+
+struct Launch {
+  int kind;      // 0 diag kernel, 1 grouped gemm
+  int off;       // offset into ids / descs
+  int n;         // number of ids / descs
+  int tiles;     // grouped gemm: total tiles
+  int step;      // diag kernel: panel index
+};
+
+}  // namespace kfac
+
+using namespace kfac;
+
+struct kfac_inverse_plan {
+  int count;
+  int device;
+  MatInfo* mats_dev;
+  float* trace_dev;
+  float* add_dev;
+  int* info_dev;
+  int* ids_dev;
+  GemmDesc* descs_dev;
+  std::vector<Launch> launches;
+  long long total_elems;
+};
+
+static size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
+
+extern "C" size_t kfac_inverse_workspace_bytes(int count, const int* dims) {
+  size_t total = 0;
+  for (int i = 0; i < count; ++i) {
+    if (dims[i] <= 0) return 0;
+    total += 2 * align256((size_t)dims[i] * dims[i] * sizeof(float));
+  }
+  return total;
+}
+
+extern "C" int kfac_inverse_plan_create(
+    int count, const int* dims, const float* const* factors,
+    float* const* inverses, const int* partner, const int* role,
+    const float* l2_coef, const float* scale, void* workspace,
+    size_t workspace_bytes, kfac_inverse_plan** out) {
+  KFAC_REQUIRE(out != nullptr, "inverse_plan_create: null plan pointer");
+  *out = nullptr;
+  KFAC_REQUIRE(count > 0 && dims && factors && inverses && role,
+               "inverse_plan_create: null argument or count=%d", count);
+  for (int i = 0; i < count; ++i) {
+    KFAC_REQUIRE(dims[i] > 0 && dims[i] <= 32768,
+                 "inverse_plan_create: dims[%d]=%d out of range", i, dims[i]);
+    KFAC_REQUIRE(factors[i] && inverses[i],
+                 "inverse_plan_create: null matrix pointer at %d", i);
+    KFAC_REQUIRE(role[i] >= 0 && role[i] <= 2,
+                 "inverse_plan_create: role[%d]=%d", i, role[i]);
+    if (role[i] != 2 && partner && partner[i] >= 0)
+      KFAC_REQUIRE(partner[i] < count && role[partner[i]] == 1 - role[i],
+                   "inverse_plan_create: partner[%d]=%d is not the other "
+                   "factor of a pair", i, partner[i]);
+  }
+  size_t need = kfac_inverse_workspace_bytes(count, dims);
+  if (workspace == nullptr || workspace_bytes < need)
+    return fail(KFAC_ERR_WORKSPACE,
+                "inverse_plan_create: workspace of %zu bytes needed, %zu given",
+                need, workspace_bytes);
+
+  std::vector<MatInfo> mats(count);
+  char* ws = static_cast<char*>(workspace);
+  int dmax = 0;
+  long long total_elems = 0;
+  for (int i = 0; i < count; ++i) {
+    MatInfo& m = mats[i];
+    size_t bytes = align256((size_t)dims[i] * dims[i] * sizeof(float));
+    m.F = factors[i];
+    m.inv = inverses[i];
+    m.W = reinterpret_cast<float*>(ws); ws += bytes;
+    m.X = reinterpret_cast<float*>(ws); ws += bytes;
+    m.d = dims[i];
+    m.partner = partner ? partner[i] : -1;
+    m.role = role[i];
+    m.l2 = l2_coef ? l2_coef[i] : 0.f;
+    m.scale = scale ? scale[i] : 1.f;
+    m.pad_ = 0;
+    dmax = std::max(dmax, dims[i]);
+    total_elems += (long long)dims[i] * dims[i];
+  }
+  // large matrices first: their tiles are scheduled first
+  std::vector<int> order(count);
+  for (int i = 0; i < count; ++i) order[i] = i;
+  std::stable_sort(order.begin(), order.end(),
+                   [&](int a, int b) { return dims[a] > dims[b]; });
+
+  std::vector<GemmDesc> descs;
+  std::vector<int> ids;
+  std::vector<Launch> launches;
+
+  auto begin_gemm = [&]() {
+    Launch l = {1, (int)descs.size(), 0, 0, 0};
+    return l;
+  };
+  auto push_desc = [&](Launch& l, GemmDesc g) {
+    g.tile_begin = l.tiles;
+    l.tiles += gemm_desc_tiles(g);
+    g.kfW = g.kfb = g.pW = g.pb = g.vW = g.vb = nullptr;
+    g.dW = 0;
+    g.pad_ = 0;
+    descs.push_back(g);
+    l.n += 1;
+  };
+  auto end_gemm = [&](Launch& l) {
+    if (l.n > 0) launches.push_back(l);
+  };
+
+  const int nsteps = (dmax + DB - 1) / DB;
+  for (int j = 0; j < nsteps; ++j) {
+    const int o = j * DB;
+    Launch dl = {0, (int)ids.size(), 0, 0, j};
+    for (int i : order)
+      if (dims[i] > o) { ids.push_back(i); dl.n += 1; }
+    launches.push_back(dl);
+
+    Launch trsm = begin_gemm();
+    for (int i : order) {
+      const int d = dims[i];
+      const int M = d - o - DB;
+      if (M <= 0) continue;
+      const MatInfo& m = mats[i];
+      GemmDesc g = {};
+      float* panel = m.W + (long long)(o + DB) * d + o;
+      g.A = strided_operand(panel, 1, d, M);
+      g.B = strided_operand(m.X + (long long)o * d + o, 1, d, DB);
+      g.C = panel; g.ldc = d; g.M = M; g.N = DB; g.K = DB;
+      g.alpha = 1.f; g.beta = 0.f; g.flags = 0;
+      push_desc(trsm, g);
+    }
+    end_gemm(trsm);
+
+    Launch trail = begin_gemm();
+    for (int i : order) {
+      const int d = dims[i];
+      const int M = d - o - DB;
+      if (M <= 0) continue;
+      const MatInfo& m = mats[i];
+      GemmDesc g = {};
+      float* panel = m.W + (long long)(o + DB) * d + o;
+      g.A = strided_operand(panel, 1, d, M);
+      g.B = g.A;
+      g.C = m.W + (long long)(o + DB) * d + (o + DB);
+      g.ldc = d; g.M = M; g.N = M; g.K = DB;
+      g.alpha = -1.f; g.beta = 1.f; g.flags = G_LOWER;
+      push_desc(trail, g);
+    }
+    end_gemm(trail);
+  }
+
+  for (long long b = DB; b < dmax; b *= 2) {
+    Launch g1 = begin_gemm(), g2 = begin_gemm();
+    std::vector<GemmDesc> second;
+    for (int i : order) {
+      const int d = dims[i];
+      if (d <= b) continue;
+      const MatInfo& m = mats[i];
+      for (long long s = 0; s + b < d; s += 2 * b) {
+        const int r = (int)std::min<long long>(b, d - s - b);
+        GemmDesc g = {};
+        // T = L21 * X11, parked in the output matrix
+        g.A = strided_operand(m.W + (s + b) * d + s, 1, d, r);
+        g.B = strided_operand(m.X + s * d + s, d, 1, (int)b);
+        g.C = m.inv + (s + b) * d + s;
+        g.ldc = d; g.M = r; g.N = (int)b; g.K = b;
+        g.alpha = 1.f; g.beta = 0.f; g.flags = G_KBEG_N0;
+        push_desc(g1, g);
+        // X21 = -X22 * T
+        GemmDesc h = {};
+        h.A = strided_operand(m.X + (s + b) * d + s + b, 1, d, r);
+        h.B = strided_operand(m.inv + (s + b) * d + s, d, 1, (int)b);
+        h.C = m.X + (s + b) * d + s;
+        h.ldc = d; h.M = r; h.N = (int)b; h.K = r;
+        h.alpha = -1.f; h.beta = 0.f; h.flags = G_KEND_M0;
+        second.push_back(h);
+      }
+    }
+    end_gemm(g1);
+    g2.off = (int)descs.size();
+    for (auto& h : second) push_desc(g2, h);
+    end_gemm(g2);
+  }
+
+  {
+    Launch prod = begin_gemm();
+    for (int i : order) {
+      const int d = dims[i];
+      const MatInfo& m = mats[i];
+      GemmDesc g = {};
+      g.A = strided_operand(m.X, d, 1, d);
+      g.B = g.A;
+      g.C = m.inv; g.ldc = d; g.M = d; g.N = d; g.K = d;
+      g.alpha = 1.f; g.beta = 0.f;
+      g.flags = G_LOWER | G_MIRROR | G_KBEG_M0;
+      push_desc(prod, g);
+    }
+    end_gemm(prod);
+  }
+
+  kfac_inverse_plan* p = new kfac_inverse_plan();
+  p->count = count;
+  p->total_elems = total_elems;
+  p->launches = launches;
+  p->mats_dev = nullptr; p->trace_dev = nullptr; p->add_dev = nullptr;
+  p->info_dev = nullptr; p->ids_dev = nullptr; p->descs_dev = nullptr;
+  cudaError_t e = cudaGetDevice(&p->device);
+  if (e == cudaSuccess) e = cudaMalloc(&p->mats_dev, sizeof(MatInfo) * count);
+  if (e == cudaSuccess) e = cudaMalloc(&p->trace_dev, sizeof(float) * count);
+  if (e == cudaSuccess) e = cudaMalloc(&p->add_dev, sizeof(float) * count);
+  if (e == cudaSuccess) e = cudaMalloc(&p->info_dev, sizeof(int) * count);
+  if (e == cudaSuccess) e = cudaMalloc(&p->ids_dev, sizeof(int) * std::max<size_t>(ids.size(), 1));
+  if (e == cudaSuccess) e = cudaMalloc(&p->descs_dev, sizeof(GemmDesc) * std::max<size_t>(descs.size(), 1));
+  if (e == cudaSuccess) e = cudaMemcpy(p->mats_dev, mats.data(), sizeof(MatInfo) * count, cudaMemcpyHostToDevice);
+  if (e == cudaSuccess && !ids.empty()) e = cudaMemcpy(p->ids_dev, ids.data(), sizeof(int) * ids.size(), cudaMemcpyHostToDevice);
+  if (e == cudaSuccess && !descs.empty()) e = cudaMemcpy(p->descs_dev, descs.data(), sizeof(GemmDesc) * descs.size(), cudaMemcpyHostToDevice);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(chol_diag_kernel,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)((2 * DB * DLD + DB) * sizeof(float)));
+  if (e != cudaSuccess) {
+    kfac_inverse_plan_destroy(p);
+    return fail(KFAC_ERR_CUDA, "inverse_plan_create: %s", cudaGetErrorString(e));
+  }
+  *out = p;
+  return KFAC_OK;
+}
+
+extern "C" int kfac_inverse_plan_run(kfac_inverse_plan* p, float damping,
+                                     int use_pi, int* info_dev,
+                                     float* diag_dev, void* stream) {
+  KFAC_REQUIRE(p != nullptr, "inverse_plan_run: null plan");
+  cudaStream_t st = (cudaStream_t)stream;
+  int* info = info_dev ? info_dev : p->info_dev;
+  trace_kernel<<<p->count, 256, 0, st>>>(p->mats_dev, p->trace_dev, info);
+  KFAC_LAUNCH_CHECK("trace_kernel");
+  damping_kernel<<<ceil_div(p->count, 128), 128, 0, st>>>(
+      p->mats_dev, p->count, p->trace_dev, damping, use_pi, p->add_dev,
+      diag_dev);
+  KFAC_LAUNCH_CHECK("damping_kernel");
+  {
+    dim3 grid(64, p->count);
+    damp_copy_kernel<<<grid, 256, 0, st>>>(p->mats_dev, p->add_dev);
+    KFAC_LAUNCH_CHECK("damp_copy_kernel");
+  }
+  const size_t dsm = (2 * DB * DLD + DB) * sizeof(float);
+  for (const Launch& l : p->launches) {
+    if (l.kind == 0) {
+      chol_diag_kernel<<<l.n, 256, dsm, st>>>(p->mats_dev, p->ids_dev + l.off,
+                                              l.step, info);
+      KFAC_LAUNCH_CHECK("chol_diag_kernel");
+    } else {
+      int rc = launch_grouped_gemm(p->descs_dev + l.off, l.n, l.tiles, 0.f, 0.f,
+                                   st);
+      if (rc != KFAC_OK) return rc;
+    }
+  }
+  return KFAC_OK;
+}
+
+extern "C" int kfac_inverse_plan_destroy(kfac_inverse_plan* p) {
+  if (p == nullptr) return KFAC_OK;
+  cudaFree(p->mats_dev);
+  cudaFree(p->trace_dev);
+  cudaFree(p->add_dev);
+  cudaFree(p->info_dev);
+  cudaFree(p->ids_dev);
+  cudaFree(p->descs_dev);
+  delete p;
+  return KFAC_OK;
+}

@@ -1,0 +1,268 @@
+"""Thin torch-tensor front end of the C ABI.
+
+Every function takes CUDA fp32 tensors, passes their raw device pointers and
+the current CUDA stream to ``libkfac_b200.so`` and returns torch tensors that
+own the outputs.  Tensors are plumbing only: all arithmetic happens in the
+library's kernels.
+"""
+
+import ctypes
+
+import torch
+
+from . import _lib
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _p(t):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _chk(t, name):
+    if t is None:
+        return
+    if not t.is_cuda:
+        raise _lib.KfacLibraryError(
+            '%s must be a CUDA tensor: this package has no CPU path' % name)
+    if t.dtype != torch.float32:
+        raise TypeError('%s must be float32, got %s' % (name, t.dtype))
+    if not t.is_contiguous():
+        raise ValueError('%s must be contiguous' % name)
+
+
+class Workspace(object):
+    """Grow-only device scratch buffer."""
+
+    def __init__(self):
+        self.buf = None
+
+    def get(self, nbytes, device):
+        nbytes = max(int(nbytes), 256)
+        if self.buf is None or self.buf.numel() < nbytes or \
+                self.buf.device != torch.device(device):
+            self.buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        return self.buf
+
+
+_factor_ws = Workspace()
+
+
+def _factor_out(d, out, beta, device):
+    if out is None:
+        if beta != 0.0:
+            raise ValueError('beta != 0 needs an existing `out`')
+        out = torch.empty((d, d), dtype=torch.float32, device=device)
+    _chk(out, 'out')
+    if tuple(out.shape) != (d, d):
+        raise ValueError('out must be %dx%d' % (d, d))
+    return out
+
+
+def factor_dense(x, add_ones_col=False, alpha=1.0, beta=0.0, out=None):
+    """out = alpha * [x,1]^T [x,1] + beta * out for a 2-D ``x``."""
+    lib = _lib.load()
+    _chk(x, 'x')
+    rows, d_in = x.shape
+    d = d_in + int(bool(add_ones_col))
+    out = _factor_out(d, out, beta, x.device)
+    nbytes = lib.kfac_factor_workspace_bytes(rows, d)
+    ws = _factor_ws.get(nbytes, x.device)
+    _lib.check(lib.kfac_factor_dense(
+        _p(x), rows, d_in, x.stride(0), int(bool(add_ones_col)), alpha, beta,
+        _p(out), _p(ws), ws.numel(), _stream()), 'kfac_factor_dense')
+    return out
+
+
+def factor_conv_input(x, ksize, stride, pad, add_ones_col=False, alpha=1.0,
+                      beta=0.0, out=None):
+    """out = alpha * P^T P + beta * out, P the im2col patches of NCHW ``x``."""
+    lib = _lib.load()
+    _chk(x, 'x')
+    n, c, h, w = x.shape
+    ho = (h + 2 * pad - ksize) // stride + 1
+    wo = (w + 2 * pad - ksize) // stride + 1
+    d = c * ksize * ksize + int(bool(add_ones_col))
+    out = _factor_out(d, out, beta, x.device)
+    nbytes = lib.kfac_factor_workspace_bytes(n * ho * wo, d)
+    ws = _factor_ws.get(nbytes, x.device)
+    _lib.check(lib.kfac_factor_conv_input(
+        _p(x), n, c, h, w, ksize, stride, pad, int(bool(add_ones_col)), alpha,
+        beta, _p(out), _p(ws), ws.numel(), _stream()),
+        'kfac_factor_conv_input')
+    return out
+
+
+def factor_conv_grad(gy, alpha=1.0, beta=0.0, out=None):
+    """out = alpha * g^T g + beta * out, g = NCHW ``gy`` as (n*ho*wo, c)."""
+    lib = _lib.load()
+    _chk(gy, 'gy')
+    n, c, ho, wo = gy.shape
+    out = _factor_out(c, out, beta, gy.device)
+    nbytes = lib.kfac_factor_workspace_bytes(n * ho * wo, c)
+    ws = _factor_ws.get(nbytes, gy.device)
+    _lib.check(lib.kfac_factor_conv_grad(
+        _p(gy), n, c, ho, wo, alpha, beta, _p(out), _p(ws), ws.numel(),
+        _stream()), 'kfac_factor_conv_grad')
+    return out
+
+
+def bn_sample_grads(x, gy, eps, scale):
+    """(n, 2c) per-sample gradients of the BatchNormalization scale/shift."""
+    lib = _lib.load()
+    _chk(x, 'x')
+    _chk(gy, 'gy')
+    n, c = x.shape[0], x.shape[1]
+    hw = 1
+    for s in x.shape[2:]:
+        hw *= s
+    out = torch.empty((n, 2 * c), dtype=torch.float32, device=x.device)
+    stats = torch.empty(2 * c, dtype=torch.float32, device=x.device)
+    _lib.check(lib.kfac_bn_sample_grads(
+        _p(x), _p(gy), n, c, hw, eps, scale, _p(out), _p(stats), _stream()),
+        'kfac_bn_sample_grads')
+    return out
+
+
+def axpby(a, x, b, y, out):
+    """out = a*x + b*y (out may be y)."""
+    lib = _lib.load()
+    for t, nm in ((x, 'x'), (y, 'y'), (out, 'out')):
+        _chk(t, nm)
+    _lib.check(lib.kfac_axpby(x.numel(), a, _p(x), b, _p(y), _p(out),
+                              _stream()), 'kfac_axpby')
+    return out
+
+
+class InversePlan(object):
+    """Batched damped inverse of a fixed set of factor buffers."""
+
+    def __init__(self, factors, inverses, partner, role, l2_coef=None,
+                 scale=None):
+        lib = _lib.load()
+        self._lib = lib
+        self.count = len(factors)
+        for t in list(factors) + list(inverses):
+            _chk(t, 'factor/inverse')
+        dims = [int(f.shape[0]) for f in factors]
+        self.dims = dims
+        self.factors, self.inverses = list(factors), list(inverses)
+        device = factors[0].device
+        dims_c = _lib.int_array(dims)
+        nbytes = lib.kfac_inverse_workspace_bytes(self.count, dims_c)
+        self.workspace = torch.empty(max(nbytes, 256), dtype=torch.uint8,
+                                     device=device)
+        self.info = torch.zeros(self.count, dtype=torch.int32, device=device)
+        self.diag = torch.zeros(self.count, dtype=torch.float32, device=device)
+        handle = ctypes.c_void_p()
+        _lib.check(lib.kfac_inverse_plan_create(
+            self.count, dims_c,
+            _lib.ptr_array([f.data_ptr() for f in factors]),
+            _lib.ptr_array([f.data_ptr() for f in inverses]),
+            _lib.int_array(partner), _lib.int_array(role),
+            _lib.float_array(l2_coef if l2_coef is not None
+                             else [0.0] * self.count),
+            _lib.float_array(scale if scale is not None
+                             else [1.0] * self.count),
+            _p(self.workspace), self.workspace.numel(),
+            ctypes.byref(handle)), 'kfac_inverse_plan_create')
+        self._handle = handle
+
+    def run(self, damping, use_pi=True):
+        _lib.check(self._lib.kfac_inverse_plan_run(
+            self._handle, damping, int(bool(use_pi)),
+            ctypes.c_void_p(self.info.data_ptr()),
+            ctypes.c_void_p(self.diag.data_ptr()), _stream()),
+            'kfac_inverse_plan_run')
+
+    def close(self):
+        if getattr(self, '_handle', None) is not None and self._handle:
+            self._lib.kfac_inverse_plan_destroy(self._handle)
+            self._handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+_precond_ws = Workspace()
+
+
+def precondition(G_inv, A_inv, grad_W, grad_b, kf_W=None, kf_b=None,
+                 param_W=None, param_b=None, mom_W=None, mom_b=None, lr=0.0,
+                 momentum=0.0):
+    """Grouped kf = G_inv [grad_W, grad_b] A_inv over lists of layers, with
+    the optional fused momentum update (see include/kfac_b200.h)."""
+    lib = _lib.load()
+    count = len(G_inv)
+    dG = [int(g.shape[0]) for g in G_inv]
+    dW = [int(w.numel() // w.shape[0]) for w in grad_W]
+    hb = [0 if b is None else 1 for b in grad_b]
+
+    def ptrs(lst):
+        if lst is None:
+            return None
+        for t in lst:
+            _chk(t, 'precondition argument')
+        return _lib.ptr_array([None if t is None else t.data_ptr()
+                               for t in lst])
+    nbytes = lib.kfac_precond_workspace_bytes(
+        count, _lib.int_array(dG), _lib.int_array(dW), _lib.int_array(hb))
+    ws = _precond_ws.get(nbytes, G_inv[0].device)
+    _lib.check(lib.kfac_precondition(
+        count, _lib.int_array(dG), _lib.int_array(dW), ptrs(G_inv),
+        ptrs(A_inv), ptrs(grad_W), ptrs(grad_b), ptrs(kf_W), ptrs(kf_b),
+        ptrs(param_W), ptrs(param_b), ptrs(mom_W), ptrs(mom_b), lr, momentum,
+        _p(ws), ws.numel(), _stream()), 'kfac_precondition')
+
+
+def symv_split(m, x0, x1, y0, y1, nan_flag=None):
+    lib = _lib.load()
+    d = int(m.shape[0])
+    _lib.check(lib.kfac_symv_split(
+        _p(m), d, x0.numel(), _p(x0), _p(x1), _p(y0), _p(y1),
+        None if nan_flag is None else ctypes.c_void_p(nan_flag.data_ptr()),
+        _stream()), 'kfac_symv_split')
+
+
+def momentum_update(grad, param, v, lr, momentum):
+    lib = _lib.load()
+    for t, nm in ((grad, 'grad'), (param, 'param'), (v, 'v')):
+        _chk(t, nm)
+    _lib.check(lib.kfac_momentum_update(param.numel(), _p(grad), _p(param),
+                                        _p(v), lr, momentum, _stream()),
+               'kfac_momentum_update')
+
+
+def _wire_args(arrays, tri, select):
+    nelems = [int(a.numel()) for a in arrays]
+    tri_dim = [int(a.shape[0]) if t else 0 for a, t in zip(arrays, tri)]
+    sel = None if select is None else _lib.int_array(select)
+    return (len(arrays), _lib.ptr_array([a.data_ptr() for a in arrays]),
+            _lib.i64_array(nelems), _lib.int_array(tri_dim), sel)
+
+
+def wire_nelems(arrays, tri):
+    lib = _lib.load()
+    n, _, nelems, tri_dim, _ = _wire_args(arrays, tri, None)
+    return int(lib.kfac_wire_nelems(n, nelems, tri_dim))
+
+
+def wire_pack(arrays, tri, wire, select=None, zero_skipped=False):
+    lib = _lib.load()
+    n, ptrs, nelems, tri_dim, sel = _wire_args(arrays, tri, select)
+    _lib.check(lib.kfac_wire_pack(n, ptrs, nelems, tri_dim, sel,
+                                  int(bool(zero_skipped)), _p(wire),
+                                  _stream()), 'kfac_wire_pack')
+
+
+def wire_unpack(arrays, tri, wire, select=None, scale=1.0, ema_r=-1.0):
+    lib = _lib.load()
+    n, ptrs, nelems, tri_dim, sel = _wire_args(arrays, tri, select)
+    _lib.check(lib.kfac_wire_unpack(n, ptrs, nelems, tri_dim, sel, scale,
+                                    ema_r, _p(wire), _stream()),
+               'kfac_wire_unpack')

@@ -1,0 +1,209 @@
+/*
+ * kfac_b200 -- C ABI of the B200 (sm_100a) K-FAC curvature kernels.
+ *
+ * Every pointer named *_dev / documented "device" is a raw device pointer on
+ * the current CUDA device; matrices are fp32, row-major, dense unless stated.
+ * `stream` is a cudaStream_t passed as void* (NULL = legacy default stream).
+ * Every function returns 0 on success and a non-zero code otherwise; the
+ * message for the calling thread's last failure is kfac_last_error().  No
+ * function synchronises the device or the stream unless it says so.  There is
+ * no CPU implementation behind this interface.
+ *
+ * The reference (chainerkfac) has no native boundary: each entry point names
+ * the Python function(s) of the reference whose arithmetic it replaces, by
+ * path inside the chainerkfac project.
+ */
+#ifndef KFAC_B200_H_
+#define KFAC_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define KFAC_OK 0
+#define KFAC_ERR_INVALID 1   /* bad argument                              */
+#define KFAC_ERR_CUDA 2      /* a CUDA runtime call or launch failed      */
+#define KFAC_ERR_WORKSPACE 3 /* workspace missing or too small            */
+
+/* Version of this interface (bumped on incompatible change). */
+int kfac_abi_version(void);
+/* Message of the calling thread's most recent failure ("" if none). */
+const char* kfac_last_error(void);
+
+/* ------------------------------------------------------------------ factors
+ * out(d x d) = alpha * X^T X + beta * out, X a (rows x d) matrix that is never
+ * materialised.  Only one triangle of tiles is computed; both triangles of
+ * `out` are written, bit-identical mirror images.  beta == 0 never reads
+ * `out`.  alpha carries the reference's scale (1/n, n, n/(ho*wo)); beta != 0
+ * fuses the running average (alpha = r*scale, beta = 1-r) or the accumulation
+ * over micro-steps.  Work is split along `rows`; partial tiles go to
+ * `workspace` (device, at least kfac_factor_workspace_bytes(rows, d) bytes,
+ * contents undefined on return).
+ */
+size_t kfac_factor_workspace_bytes(int64_t rows, int d);
+
+/* X = [x, 1]: x is (rows x d_in) with leading dimension ld; a column of ones
+ * is appended when add_ones_col != 0 (bias folded into the factor).
+ * Replaces FisherBlockLinear.compute_A / compute_G,
+ * optimizers/fisher_blocks/connections/linear.py:14-46. */
+int kfac_factor_dense(const float* x, int64_t rows, int d_in, int64_t ld,
+                      int add_ones_col, float alpha, float beta, float* out,
+                      void* workspace, size_t workspace_bytes, void* stream);
+
+/* X = im2col patches of an NCHW input: rows = n*ho*wo, columns ordered
+ * (c, ky, kx) with c slowest, zero padding, square kernel, then the optional
+ * ones column.  Replaces FisherBlockConvolution2D.compute_A,
+ * optimizers/fisher_blocks/connections/convolution_2d.py:19-41 (including the
+ * chainer.functions.im2col call, the NHWC transpose and column_stack). */
+int kfac_factor_conv_input(const float* x, int n, int c, int h, int w,
+                           int ksize, int stride, int pad, int add_ones_col,
+                           float alpha, float beta, float* out,
+                           void* workspace, size_t workspace_bytes,
+                           void* stream);
+
+/* X = output gradient viewed as (n*ho*wo, c) from NCHW storage.
+ * Replaces FisherBlockConvolution2D.compute_G,
+ * optimizers/fisher_blocks/connections/convolution_2d.py:43-72. */
+int kfac_factor_conv_grad(const float* gy, int n, int c, int ho, int wo,
+                          float alpha, float beta, float* out,
+                          void* workspace, size_t workspace_bytes,
+                          void* stream);
+
+/* Per-sample BatchNormalization gradients: out is (n x 2c),
+ * out[s, j] = scale * sum_hw gy[s,j,:] * xhat[s,j,:] and
+ * out[s, c+j] = scale * sum_hw gy[s,j,:], xhat = x normalised with the batch
+ * mean and biased variance (+eps).  hw = 1 for 2-D inputs.  `stats` is a
+ * device scratch of 2*c floats.  Followed by kfac_factor_dense(out, n, 2c, ..)
+ * it replaces FisherBlockBatchNormalization.compute_F,
+ * optimizers/fisher_blocks/normalizations/batch_normalization.py:78-131. */
+int kfac_bn_sample_grads(const float* x, const float* gy, int n, int c, int hw,
+                         float eps, float scale, float* out, float* stats,
+                         void* stream);
+
+/* out = a * x + b * y elementwise over `count` floats (out may alias y).
+ * Replaces the running-average expression of FisherBlock.update_cov_emas,
+ * optimizers/fisher_block.py:155-163, and KFAC.accumulate_grads /
+ * accumulate_covs, optimizers/kfac.py:286-304. */
+int kfac_axpby(int64_t count, float a, const float* x, float b, const float* y,
+               float* out, void* stream);
+
+/* ------------------------------------------------------------------ inverse
+ * Batched damped inverse of `count` symmetric positive definite factors:
+ * inverses[i] = (factors[i] + add_i * I)^-1, dense symmetric, by blocked
+ * Cholesky, triangular inverse and symmetric product (d^3 flops per factor).
+ * The factors are read-only: the running average stays undamped.
+ *
+ * role[i] selects add_i with g_i = max(l2_coef[i], damping):
+ *   0  forward factor A of a connection:  pi * sqrt(g_i)
+ *   1  backward factor G of a connection: sqrt(g_i) / pi
+ *   2  full block (BatchNormalization):   g_i * scale[i]
+ * pi = sqrt(tr(A) dim(G) / (tr(G) dim(A))) from the factor and its
+ * partner[i] (index of the other factor of the pair) when use_pi != 0, else 1.
+ * Replaces FisherBlock.update_invs, compute_pi_tracenorm and get_diagval
+ * (optimizers/fisher_block.py:14-49,165-179), FisherBlockConnection.
+ * get_diagvals (optimizers/fisher_blocks/connection.py:66-77),
+ * FisherBlockBatchNormalization.get_diagvals
+ * (optimizers/fisher_blocks/normalizations/batch_normalization.py:133-157)
+ * and inverse() (optimizers/cholesky_inverse.py:16-102).
+ *
+ * The plan records device pointers, so the factor and inverse buffers must
+ * stay where they are for the plan's lifetime.  `workspace` (device,
+ * kfac_inverse_workspace_bytes bytes) is owned by the caller and must outlive
+ * the plan; plans that run concurrently need distinct workspaces.
+ */
+typedef struct kfac_inverse_plan kfac_inverse_plan;
+
+size_t kfac_inverse_workspace_bytes(int count, const int* dims);
+
+int kfac_inverse_plan_create(int count, const int* dims,
+                             const float* const* factors,
+                             float* const* inverses, const int* partner,
+                             const int* role, const float* l2_coef,
+                             const float* scale, void* workspace,
+                             size_t workspace_bytes,
+                             kfac_inverse_plan** plan);
+
+/* info_dev: `count` ints on the device, 0 where the factorisation succeeded,
+ * else 1 + index of the first non-positive pivot (the reference never reads
+ * cuSOLVER's dev_info; here it is always produced).  diag_dev: `count` floats
+ * on the device receiving add_i (the reference's diag_val_forward/backward).
+ * Either may be NULL. */
+int kfac_inverse_plan_run(kfac_inverse_plan* plan, float damping, int use_pi,
+                          int* info_dev, float* diag_dev, void* stream);
+
+int kfac_inverse_plan_destroy(kfac_inverse_plan* plan);
+
+/* ------------------------------------------------------------ precondition
+ * For `count` layers: kf = G_inv * [grad_W, grad_b] * A_inv with grad_W viewed
+ * as (dG x dW); the first dW columns go to kf_W, the last to kf_b (layers with
+ * grad_b[i] == NULL have no bias column and A_inv is dW x dW).  When
+ * param_W[i] != NULL the momentum rule is fused into the same epilogue:
+ * v = momentum * v - lr * kf; param += v (mom_W / mom_b are the velocity
+ * buffers).  Replaces compute_kfgrads (connections/linear.py:48-61,
+ * connections/convolution_2d.py:74-90), FisherBlockConnection.update_kfgrads
+ * (fisher_blocks/connection.py:51-61) and, when fused, KFACUpdateRule.
+ * update_core (optimizers/kfac.py:87-116).
+ *
+ * All pointer arrays are host arrays of device pointers, read during the
+ * call.  `workspace`: device, kfac_precond_workspace_bytes bytes.
+ */
+size_t kfac_precond_workspace_bytes(int count, const int* dG, const int* dW,
+                                    const int* has_bias);
+
+int kfac_precondition(int count, const int* dG, const int* dW,
+                      const float* const* G_inv, const float* const* A_inv,
+                      const float* const* grad_W, const float* const* grad_b,
+                      float* const* kf_W, float* const* kf_b,
+                      float* const* param_W, float* const* param_b,
+                      float* const* mom_W, float* const* mom_b, float lr,
+                      float momentum, void* workspace, size_t workspace_bytes,
+                      void* stream);
+
+/* y = M x for a (d x d) matrix, one launch per call: the BatchNormalization
+ * preconditioning F_inv * [grad_gamma; grad_beta]
+ * (normalizations/batch_normalization.py:175-191). x is given in two pieces
+ * (x0 of length d0, then x1 of length d - d0; x1 may be NULL when d0 == d);
+ * y likewise.  nan_flag_dev (device int, may be NULL) is set to 1 when any
+ * output is NaN, which is the condition of the reference's raw-gradient
+ * fallback. */
+int kfac_symv_split(const float* m, int d, int d0, const float* x0,
+                    const float* x1, float* y0, float* y1, int* nan_flag_dev,
+                    void* stream);
+
+/* v = momentum * v - lr * grad; param += v over `count` floats.
+ * Replaces KFACUpdateRule.update_core_gpu, optimizers/kfac.py:101-116. */
+int kfac_momentum_update(int64_t count, const float* grad, float* param,
+                         float* v, float lr, float momentum, void* stream);
+
+/* ------------------------------------------------------- wire pack / unpack
+ * Wire format of the reference's collectives: the arrays concatenated in the
+ * given order, a square factor (tri_dim[i] > 0) as its packed row-major lower
+ * triangle incl. diagonal (dst[r(r+1)/2 + c] = a[r][c], c <= r), anything else
+ * (tri_dim[i] == 0) as its `nelems[i]` elements.  Arrays with select[i] == 0
+ * are skipped (pack leaves their slot untouched; zero_skipped != 0 clears it).
+ * unpack mirrors triangles back to full symmetric matrices and multiplies by
+ * `scale` (1/size for the mean); with ema_r >= 0 the unpacked value is blended
+ * into the destination as ema_r * value + (1 - ema_r) * dst.
+ * Replaces _pack_arrays_to_buffer / _unpack_arrays_from_buffer and the three
+ * NVRTC kernels of communicators/pure_nccl_communicator.py:110-147,300-471.
+ * Pointer/size arrays are host arrays read during the call.
+ */
+int64_t kfac_wire_nelems(int n_arrays, const int64_t* nelems,
+                         const int* tri_dim);
+
+int kfac_wire_pack(int n_arrays, const float* const* arrays,
+                   const int64_t* nelems, const int* tri_dim,
+                   const int* select, int zero_skipped, float* wire,
+                   void* stream);
+
+int kfac_wire_unpack(int n_arrays, float* const* arrays, const int64_t* nelems,
+                     const int* tri_dim, const int* select, float scale,
+                     float ema_r, const float* wire, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KFAC_B200_H_ */

@@ -1,0 +1,380 @@
+"""Parity of the CUDA kernels (called through the C ABI) with the oracle.
+
+Tolerances are the ones the project states for this path: relative Frobenius
+error <= 1e-4 on factors and inverses, <= 1e-3 on preconditioned gradients.
+Pack/unpack is bit-exact.
+"""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import kfac_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+FACTOR_TOL = 1e-4
+INVERSE_TOL = 1e-4
+KFGRAD_TOL = 1e-3
+
+
+@pytest.fixture(scope='module')
+def ops():
+    from chainerkfac_b200 import ops as _ops
+    return _ops
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def host(t):
+    return t.detach().cpu().numpy()
+
+
+def rel(a, b):
+    a = np.asarray(a, dtype=np.float64)
+    b = np.asarray(b, dtype=np.float64)
+    return np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30)
+
+
+def check_symmetric(m):
+    assert np.array_equal(m, m.T), 'factor is not bit-symmetric'
+
+
+# ------------------------------------------------------------------ factors
+@pytest.mark.parametrize('name', ['linear_bias', 'linear_nobias', 'linear_odd'])
+def test_factor_linear_golden(ops, golden, name):
+    g = golden(name)
+    bias = 'b' in g
+    x, gy = g['x0'], g['gy0']
+    n = x.shape[0]
+    A = host(ops.factor_dense(dev(x), bias, alpha=1.0 / n))
+    G = host(ops.factor_dense(dev(gy), False, alpha=float(n)))
+    assert rel(A, g['A0']) < FACTOR_TOL
+    assert rel(G, g['G0']) < FACTOR_TOL
+    check_symmetric(A)
+    check_symmetric(G)
+
+
+@pytest.mark.parametrize('name', ['conv3x3_bias', 'conv3x3_s2', 'conv1x1_s2',
+                                  'conv7x7_s2'])
+def test_factor_conv_golden(ops, golden, name):
+    g = golden(name)
+    bias = 'b' in g
+    x, gy = g['x0'], g['gy0']
+    n, _, ho, wo = gy.shape
+    A = host(ops.factor_conv_input(dev(x), int(g['ksize']), int(g['stride']),
+                                   int(g['pad']), bias, alpha=1.0 / n))
+    G = host(ops.factor_conv_grad(dev(gy), alpha=n / float(ho * wo)))
+    assert rel(A, g['A0']) < FACTOR_TOL
+    assert rel(G, g['G0']) < FACTOR_TOL
+    check_symmetric(A)
+
+
+@pytest.mark.parametrize('rows,d,bias', [
+    (32, 10, False), (128, 27, True), (128, 784, True), (128, 1000, True),
+    (5000, 64, False), (40000, 147, True), (3000, 513, False), (1, 5, True),
+    (17, 129, True), (2049, 300, False)])
+def test_factor_dense_sweep(ops, rows, d, bias):
+    rng = np.random.default_rng(rows * 131 + d)
+    x = np.maximum(rng.standard_normal((rows, d)), 0).astype(np.float32)
+    want = orc.linear_A(x.astype(np.float64), bias) * rows / 7.0
+    got = host(ops.factor_dense(dev(x), bias, alpha=1.0 / 7.0))
+    assert got.shape == want.shape
+    assert rel(got, want) < FACTOR_TOL
+    check_symmetric(got)
+
+
+def test_factor_dense_strided_rows(ops):
+    rng = np.random.default_rng(5)
+    big = dev(rng.standard_normal((300, 96)).astype(np.float32))
+    x = big[:, :50]                      # leading dimension 96
+    from chainerkfac_b200 import _lib
+    import ctypes
+    lib = _lib.load()
+    out = torch.empty((50, 50), device='cuda')
+    ws = torch.empty(max(lib.kfac_factor_workspace_bytes(300, 50), 256),
+                     dtype=torch.uint8, device='cuda')
+    _lib.check(lib.kfac_factor_dense(
+        ctypes.c_void_p(x.data_ptr()), 300, 50, 96, 0, 1.0, 0.0,
+        ctypes.c_void_p(out.data_ptr()), ctypes.c_void_p(ws.data_ptr()),
+        ws.numel(), None), 'strided')
+    torch.cuda.synchronize()
+    xs = host(big)[:, :50].astype(np.float64)
+    assert rel(host(out), xs.T @ xs) < FACTOR_TOL
+
+
+def test_factor_running_average_and_accumulation(ops):
+    rng = np.random.default_rng(9)
+    x1 = rng.random((64, 33)).astype(np.float32)
+    x2 = rng.random((64, 33)).astype(np.float32)
+    r = 0.9
+    ema = ops.factor_dense(dev(x1), True, alpha=1.0 / 64)
+    ops.factor_dense(dev(x2), True, alpha=r / 64, beta=1 - r, out=ema)
+    want = orc.update_cov_ema(orc.linear_A(x2, True), orc.linear_A(x1, True), r)
+    assert rel(host(ema), want) < FACTOR_TOL
+    check_symmetric(host(ema))
+    # long contraction (split across CTAs) with beta
+    x3 = rng.random((9000, 33)).astype(np.float32)
+    acc = ops.factor_dense(dev(x1), True, alpha=0.5 / 64)
+    ops.factor_dense(dev(x3), True, alpha=0.5 / 9000, beta=1.0, out=acc)
+    want = 0.5 * orc.linear_A(x1, True) + 0.5 * orc.linear_A(x3, True)
+    assert rel(host(acc), want) < FACTOR_TOL
+
+
+@pytest.mark.parametrize('n,c,h,k,s,p,bias', [
+    (2, 3, 32, 7, 2, 3, True),      # stem-like
+    (2, 64, 14, 3, 1, 1, False),    # 3x3, 576 columns
+    (3, 16, 15, 3, 2, 1, False),    # strided 3x3, odd extent
+    (2, 40, 9, 1, 1, 0, False),     # 1x1 (strided view path)
+    (2, 24, 10, 1, 2, 0, True),     # 1x1 stride 2 (gather path)
+    (1, 5, 6, 5, 1, 0, True),       # no padding
+    (4, 512, 7, 3, 1, 1, False)])   # 4608 columns
+def test_factor_conv_input_sweep(ops, n, c, h, k, s, p, bias):
+    rng = np.random.default_rng(n * 7 + c + h + k)
+    x = rng.standard_normal((n, c, h, h)).astype(np.float32)
+    want = orc.conv_A(x.astype(np.float64), k, s, p, bias)
+    got = host(ops.factor_conv_input(dev(x), k, s, p, bias, alpha=1.0 / n))
+    assert got.shape == want.shape
+    assert rel(got, want) < FACTOR_TOL
+    check_symmetric(got)
+
+
+@pytest.mark.parametrize('n,c,hw', [(2, 5, 3), (4, 64, 28), (3, 130, 7),
+                                    (32, 256, 14), (2, 2048, 7)])
+def test_factor_conv_grad_sweep(ops, n, c, hw):
+    rng = np.random.default_rng(n + c + hw)
+    gy = (rng.standard_normal((n, c, hw, hw)) / n).astype(np.float32)
+    want = orc.conv_G(gy.astype(np.float64))
+    got = host(ops.factor_conv_grad(dev(gy), alpha=n / float(hw * hw)))
+    assert rel(got, want) < FACTOR_TOL
+    check_symmetric(got)
+
+
+@pytest.mark.parametrize('name', ['bn_4d', 'bn_2d'])
+def test_bn_factor_golden(ops, golden, name):
+    g = golden(name)
+    x, gy = g['x'], g['gy']
+    n = x.shape[0]
+    grads = ops.bn_sample_grads(dev(x), dev(gy), float(g['eps']), float(n))
+    want = orc.bn_sample_grads(x, gy, float(g['eps']))
+    assert rel(host(grads), want) < FACTOR_TOL
+    F = host(ops.factor_dense(grads, False, alpha=1.0 / n))
+    assert rel(F, g['F']) < FACTOR_TOL
+
+
+# ------------------------------------------------------------------ inverse
+def spd(rng, d, m=None):
+    m = m or max(2 * d, 64)
+    X = rng.standard_normal((m, d)).astype(np.float32)
+    return (X.T @ X / m + 1e-3 * np.eye(d)).astype(np.float32)
+
+
+def run_pairs(ops, dimsA, dimsG, damping, use_pi=True, seed=0):
+    rng = np.random.default_rng(seed)
+    mats, partner, role = [], [], []
+    for i, (da, dg) in enumerate(zip(dimsA, dimsG)):
+        mats += [spd(rng, da), spd(rng, dg)]
+        partner += [2 * i + 1, 2 * i]
+        role += [0, 1]
+    F = [dev(m) for m in mats]
+    inv = [torch.empty_like(f) for f in F]
+    plan = ops.InversePlan(F, inv, partner, role)
+    plan.run(damping, use_pi)
+    torch.cuda.synchronize()
+    assert host(plan.info).tolist() == [0] * len(mats)
+    diag = host(plan.diag)
+    for i in range(len(dimsA)):
+        A, G = mats[2 * i], mats[2 * i + 1]
+        pi, dA, dG = orc.connection_damping(
+            A, G, damping, 0.0, 'tracenorm' if use_pi else 'none')
+        assert abs(diag[2 * i] - dA) <= 1e-5 * dA
+        assert abs(diag[2 * i + 1] - dG) <= 1e-5 * dG
+        for m, add, got in ((A, dA, inv[2 * i]), (G, dG, inv[2 * i + 1])):
+            want = orc.damped_inverse(m, np.float32(add))
+            truth = np.linalg.inv(m.astype(np.float64) +
+                                  float(add) * np.eye(m.shape[0]))
+            got = host(got)
+            assert rel(got, want) < INVERSE_TOL, (m.shape, rel(got, want))
+            assert rel(got, truth) < INVERSE_TOL
+            assert np.array_equal(got, got.T)
+        # the factors themselves stay undamped
+        assert np.array_equal(host(F[2 * i]), A)
+    plan.close()
+
+
+def test_inverse_small_batch(ops):
+    run_pairs(ops, [10, 27, 65, 148, 300], [7, 64, 128, 129, 257], 1e-3)
+
+
+def test_inverse_no_pi(ops):
+    run_pairs(ops, [33, 200], [16, 130], 2.5e-4, use_pi=False, seed=3)
+
+
+def test_inverse_mlp_shapes(ops):
+    run_pairs(ops, [785, 1001], [1000, 10], 1e-3, seed=1)
+
+
+def test_inverse_large(ops):
+    run_pairs(ops, [1152, 2304], [128, 513], 2.5e-4, seed=2)
+
+
+@pytest.mark.parametrize('d', [10, 65])
+def test_inverse_golden(ops, golden, d):
+    g = golden('inverse_%d' % d)
+    F = [dev(g['a'])]
+    inv = [torch.empty_like(F[0])]
+    plan = ops.InversePlan(F, inv, [-1], [2], l2_coef=[0.0], scale=[0.0])
+    plan.run(0.0)
+    assert rel(host(inv[0]), g['inv']) < INVERSE_TOL
+    plan.close()
+
+
+def test_inverse_bn_role_and_repeat(ops, golden):
+    g = golden('bn_4d')
+    F = [dev(g['F'])]
+    inv = [torch.empty_like(F[0])]
+    plan = ops.InversePlan(F, inv, [-1], [2], scale=[float(g['stab_coeff'])])
+    for _ in range(2):          # a plan is reusable
+        plan.run(float(g['damping']))
+        assert abs(host(plan.diag)[0] - g['diag']) < 1e-6 * g['diag']
+        assert rel(host(inv[0]), g['F_inv']) < INVERSE_TOL
+    plan.close()
+
+
+def test_inverse_reports_non_spd(ops):
+    a = np.eye(40, dtype=np.float32)
+    a[17, 17] = -1.0
+    F = [dev(a), dev(np.eye(6, dtype=np.float32))]
+    inv = [torch.empty_like(f) for f in F]
+    plan = ops.InversePlan(F, inv, [-1, -1], [2, 2], scale=[0.0, 0.0])
+    plan.run(0.0)
+    assert host(plan.info).tolist() == [18, 0]
+    assert rel(host(inv[1]), np.eye(6)) < 1e-6
+    plan.close()
+
+
+# ------------------------------------------------------------- precondition
+def precond_case(rng, dG, dW, bias):
+    dA = dW + int(bias)
+    Gi = spd(rng, dG)
+    Ai = spd(rng, dA)
+    gW = rng.standard_normal((dG, dW)).astype(np.float32)
+    gb = rng.standard_normal(dG).astype(np.float32) if bias else None
+    return Gi, Ai, gW, gb
+
+
+def test_precondition_matches_oracle(ops):
+    rng = np.random.default_rng(11)
+    shapes = [(10, 1000, True), (64, 147, True), (300, 129, False),
+              (1000, 784, True), (7, 5, False), (256, 2304, False)]
+    cases = [precond_case(rng, *s) for s in shapes]
+    Gi = [dev(c[0]) for c in cases]
+    Ai = [dev(c[1]) for c in cases]
+    gW = [dev(c[2]) for c in cases]
+    gb = [None if c[3] is None else dev(c[3]) for c in cases]
+    kW = [torch.empty_like(t) for t in gW]
+    kb = [None if t is None else torch.empty_like(t) for t in gb]
+    ops.precondition(Gi, Ai, gW, gb, kW, kb)
+    for c, w, b in zip(cases, kW, kb):
+        wantW, wantb = orc.connection_kfgrads(c[1], c[0], c[2], c[3])
+        assert rel(host(w), wantW) < KFGRAD_TOL
+        if b is not None:
+            assert rel(host(b), wantb) < KFGRAD_TOL
+
+
+def test_precondition_conv_shape_and_fused_update(ops):
+    rng = np.random.default_rng(12)
+    Gi, Ai, gW2, gb = precond_case(rng, 20, 3 * 3 * 6, True)
+    gW = gW2.reshape(20, 6, 3, 3)
+    W = rng.standard_normal(gW.shape).astype(np.float32)
+    b = rng.standard_normal(20).astype(np.float32)
+    vW = rng.standard_normal(gW.shape).astype(np.float32)
+    vb = rng.standard_normal(20).astype(np.float32)
+    dW_, db_, dvW, dvb = dev(W), dev(b), dev(vW), dev(vb)
+    kW, kb = torch.empty_like(dW_), torch.empty_like(db_)
+    ops.precondition([dev(Gi)], [dev(Ai)], [dev(gW)], [dev(gb)], [kW], [kb],
+                     [dW_], [db_], [dvW], [dvb], lr=0.05, momentum=0.9)
+    wantW, wantb = orc.connection_kfgrads(Ai, Gi, gW, gb)
+    assert rel(host(kW), wantW) < KFGRAD_TOL
+    assert rel(host(kb), wantb) < KFGRAD_TOL
+    orc.momentum_update(W, vW, wantW, 0.05, 0.9)
+    orc.momentum_update(b, vb, wantb, 0.05, 0.9)
+    assert rel(host(dW_), W) < 1e-5
+    assert rel(host(db_), b) < 1e-5
+    assert rel(host(dvW), vW) < KFGRAD_TOL
+
+
+def test_momentum_update_and_axpby(ops):
+    rng = np.random.default_rng(13)
+    p = rng.standard_normal(100003).astype(np.float32)
+    v = rng.standard_normal(100003).astype(np.float32)
+    g = rng.standard_normal(100003).astype(np.float32)
+    dp, dv = dev(p), dev(v)
+    ops.momentum_update(dev(g), dp, dv, 0.01, 0.9)
+    orc.momentum_update(p, v, g, 0.01, 0.9)
+    assert rel(host(dp), p) < 1e-6 and rel(host(dv), v) < 1e-6
+    y = dev(g)
+    ops.axpby(0.25, dev(p), 0.75, y, y)
+    assert rel(host(y), 0.25 * p + 0.75 * g) < 1e-6
+
+
+def test_bn_kfgrad(ops, golden):
+    g = golden('bn_4d')
+    c = g['g_gamma'].shape[0]
+    y0 = torch.empty(c, device='cuda')
+    y1 = torch.empty(c, device='cuda')
+    flag = torch.zeros(1, dtype=torch.int32, device='cuda')
+    ops.symv_split(dev(g['F_inv']), dev(g['g_gamma']), dev(g['g_beta']), y0, y1,
+                   flag)
+    assert rel(host(y0), g['kf_gamma']) < KFGRAD_TOL
+    assert rel(host(y1), g['kf_beta']) < KFGRAD_TOL
+    assert int(flag.item()) == 0
+    bad = g['F_inv'].copy()
+    bad[2, 3] = np.nan
+    ops.symv_split(dev(bad), dev(g['g_gamma']), dev(g['g_beta']), y0, y1, flag)
+    assert int(flag.item()) == 1
+
+
+# -------------------------------------------------------------- wire format
+def test_wire_pack_unpack_bit_exact(ops):
+    rng = np.random.default_rng(14)
+    shapes = [((37, 37), True), ((11,), False), ((1, 1), True),
+              ((300, 300), True), ((4, 9), False)]
+    arrs = []
+    for shp, tri in shapes:
+        a = rng.standard_normal(shp).astype(np.float32)
+        if tri:
+            a = (a + a.T).astype(np.float32)
+        arrs.append(a)
+    tri = [t for _, t in shapes]
+    d_arrs = [dev(a) for a in arrs]
+    n = ops.wire_nelems(d_arrs, tri)
+    nested = [[(a, t) for a, t in zip(arrs, tri)]]
+    assert n == orc.wire_nelems(nested)
+    wire = torch.full((n,), 7.0, device='cuda')
+    ops.wire_pack(d_arrs, tri, wire)
+    assert np.array_equal(host(wire), orc.pack_arrays(nested))
+    # selective pack with zero fill (all-gather send side)
+    sel = [1, 0, 1, 0, 1]
+    ops.wire_pack(d_arrs, tri, wire, select=sel, zero_skipped=True)
+    want = orc.pack_arrays(nested)
+    off = 0
+    for a, t, s in zip(arrs, tri, sel):
+        m = a.shape[0] * (a.shape[0] + 1) // 2 if t else a.size
+        if not s:
+            want[off:off + m] = 0
+        off += m
+    assert np.array_equal(host(wire), want)
+    # unpack with mean scaling mirrors the triangles
+    ops.wire_pack(d_arrs, tri, wire)
+    outs = [torch.zeros_like(t) for t in d_arrs]
+    ops.wire_unpack(outs, tri, wire, scale=0.25)
+    for a, o in zip(arrs, outs):
+        assert np.array_equal(host(o), a * np.float32(0.25))
+    # fused running average on unpack
+    prev = [dev(np.ones_like(a)) for a in arrs]
+    ops.wire_unpack(prev, tri, wire, scale=1.0, ema_r=0.5)
+    for a, o in zip(arrs, prev):
+        assert rel(host(o), 0.5 * a + 0.5) < 1e-6
