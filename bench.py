@@ -1,0 +1,475 @@
+#!/usr/bin/env python
+"""Benchmark of the K-FAC curvature hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (``config.workload``): one K-FAC step of a vanilla ResNet-50 at batch
+32 per GPU, 224x224 inputs -- for each of its 54 convolution / fully-connected
+layers the two Kronecker factors are built from the layer's input activations
+and output gradients with the running average fused in (decay 0.9), all 108
+factors are inverted with pi-split damping 2.5e-4, and the gradients are
+preconditioned and applied with momentum.  Activations and gradients are
+synthetic (seeded) tensors of the real shapes; ImageNet is not used.
+
+``value`` is images/sec with activations/gradients resident in HBM; ``e2e`` is
+images/sec of the optimizer's public ``update(lossfun, x, t)`` call with the
+image batch coming from pinned host memory and the loss read back.  Rank 0
+prints one JSON line.  ``--impl reference`` times the reference's CPU (NumPy)
+arithmetic for the same stages through the oracle restatement on the host
+cores, on one layer per distinct layer shape (times multiplied by the number of
+layers of that shape).
+"""
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+BATCH = 32
+DECAY = 0.9
+DAMPING = 2.5e-4
+LR = 0.01
+MOMENTUM = 0.9
+WORKLOAD = 'resnet50_kfac_step_b32_224'
+
+
+def layer_table():
+    from oracle import kfac_oracle as orc
+    layers = orc.resnet50_layers(batch=BATCH)
+    return layers, [orc.layer_dims(l) for l in layers]
+
+
+def algorithmic_flops(dims):
+    """Flops per step per GPU: one triangle of each factor, d^3 per inverse,
+    two products per preconditioned gradient."""
+    factor = sum(rA * dA * (dA + 1) + rG * dG * (dG + 1)
+                 for dA, dG, rA, rG in dims)
+    inverse = sum(dA ** 3 + dG ** 3 for dA, dG, _, _ in dims)
+    precond = sum(2 * dG * dG * dA + 2 * dG * dA * dA for dA, dG, _, _ in dims)
+    return dict(factor=float(factor), inverse=float(inverse),
+                precondition=float(precond))
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, 'MEASURED_PEAKS.json')
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(hbm_gbs=p['hbm_gbs'], tflops=p['bf16_tflops_sustained'],
+                    tflops_burst=p['bf16_tflops'], source='measured')
+    return dict(hbm_gbs=6650.0, tflops=1400.0, tflops_burst=1590.0,
+                source='fallback')
+
+
+# ---------------------------------------------------------------- clocks
+class ClockSampler(object):
+    """nvidia-smi clock / throttle-reason samples during the timed region."""
+
+    QUERY = ('clocks.sm,clocks.max.sm,power.draw,'
+             'clocks_event_reasons.hw_slowdown,'
+             'clocks_event_reasons.hw_thermal_slowdown,'
+             'clocks_event_reasons.sw_thermal_slowdown,'
+             'clocks_event_reasons.sw_power_cap')
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ['nvidia-smi', '-i', str(self.index),
+                 '--query-gpu=' + self.QUERY, '--format=csv,noheader,nounits',
+                 '-lms', '100'], stdout=subprocess.PIPE,
+                stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=['unsampled'])
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        sm, smax, reasons = [], [], set()
+        names = ['hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown',
+                 'sw_power_cap']
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(',')]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                smax.append(float(parts[1]))
+            except ValueError:
+                continue
+            for nm, val in zip(names, parts[3:7]):
+                if val.lower().startswith('active'):
+                    reasons.add(nm)
+        if not sm:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=['unsampled'])
+        return dict(sm_mhz=float(np.median(sm)), sm_max_mhz=float(max(smax)),
+                    samples=len(sm), reasons=sorted(reasons))
+
+
+# ------------------------------------------------------------- GPU workload
+class DeviceWorkload(object):
+    """Synthetic per-layer activations, output gradients, weights and K-FAC
+    state of ResNet-50 at batch 32, resident on one GPU."""
+
+    def __init__(self, device, seed):
+        import torch
+        from chainerkfac_b200 import ops
+        self.torch, self.ops = torch, ops
+        self.layers, self.dims = layer_table()
+        g = torch.Generator(device=device)
+        g.manual_seed(seed)
+        self.x, self.gy, self.W, self.b = [], [], [], []
+        self.gW, self.gb, self.vW, self.vb = [], [], [], []
+        self.ema, self.inv = [], []
+        for i, (l, (dA, dG, _, _)) in enumerate(zip(self.layers, self.dims)):
+            n = l['n']
+            if l['kind'] == 'conv':
+                xs = (n, l['cin'], l['hin'], l['hin'])
+                gs = (n, l['cout'], l['hout'], l['hout'])
+                ws = (l['cout'], l['cin'], l['k'], l['k'])
+            else:
+                xs, gs, ws = (n, l['cin']), (n, l['cout']), (l['cout'], l['cin'])
+            x = torch.randn(xs, device=device, generator=g)
+            if i > 0:
+                x.clamp_(min=0)          # post-ReLU activations
+            self.x.append(x)
+            self.gy.append(torch.randn(gs, device=device, generator=g) / n)
+            fan = ws[1] * (ws[2] * ws[3] if len(ws) == 4 else 1)
+            self.W.append(torch.randn(ws, device=device, generator=g) / fan ** 0.5)
+            self.gW.append(torch.randn(ws, device=device, generator=g) * 1e-2)
+            self.vW.append(torch.zeros(ws, device=device))
+            if l['bias']:
+                self.b.append(torch.zeros(ws[0], device=device))
+                self.gb.append(torch.randn(ws[0], device=device, generator=g) * 1e-2)
+                self.vb.append(torch.zeros(ws[0], device=device))
+            else:
+                self.b.append(None)
+                self.gb.append(None)
+                self.vb.append(None)
+            self.ema += [torch.zeros((dA, dA), device=device),
+                         torch.zeros((dG, dG), device=device)]
+            self.inv += [torch.empty((dA, dA), device=device),
+                         torch.empty((dG, dG), device=device)]
+        cnt = len(self.layers)
+        partner = [j ^ 1 for j in range(2 * cnt)]
+        role = [j & 1 for j in range(2 * cnt)]
+        self.plan = ops.InversePlan(self.ema, self.inv, partner, role)
+        self.first = True
+        self.input_bytes = sum(t.numel() * 4 for t in self.x + self.gy)
+
+    def factors(self):
+        ops = self.ops
+        r, rest = (1.0, 0.0) if self.first else (DECAY, 1.0 - DECAY)
+        for i, l in enumerate(self.layers):
+            n = l['n']
+            A, G = self.ema[2 * i], self.ema[2 * i + 1]
+            if l['kind'] == 'conv':
+                ops.factor_conv_input(self.x[i], l['k'], l['stride'], l['pad'],
+                                      l['bias'], alpha=r / n, beta=rest, out=A)
+                ops.factor_conv_grad(self.gy[i],
+                                     alpha=r * n / float(l['hout'] ** 2),
+                                     beta=rest, out=G)
+            else:
+                ops.factor_dense(self.x[i], l['bias'], alpha=r / n, beta=rest,
+                                 out=A)
+                ops.factor_dense(self.gy[i], False, alpha=r * n, beta=rest,
+                                 out=G)
+        self.first = False
+
+    def inverses(self):
+        self.plan.run(DAMPING, True)
+
+    def precondition(self):
+        cnt = len(self.layers)
+        self.ops.precondition(
+            [self.inv[2 * i + 1] for i in range(cnt)],
+            [self.inv[2 * i] for i in range(cnt)], self.gW, self.gb,
+            None, None, self.W, self.b, self.vW, self.vb, lr=LR,
+            momentum=MOMENTUM)
+
+    def step(self, events=None):
+        self.factors()
+        if events is not None:
+            events[1].record()
+        self.inverses()
+        if events is not None:
+            events[2].record()
+        self.precondition()
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from chainerkfac_b200 import _lib
+
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    rank = int(os.environ.get('RANK', '0'))
+    local_rank = int(os.environ.get('LOCAL_RANK', '0'))
+    if not torch.cuda.is_available():
+        raise SystemExit('bench.py needs a CUDA device (no CPU fallback)')
+    torch.cuda.set_device(local_rank)
+    device = torch.device('cuda', local_rank)
+    if world > 1:
+        dist.init_process_group('nccl', device_id=device)
+    lib = _lib.load()
+
+    wl = DeviceWorkload(device, seed=1234 + rank)
+    flops = algorithmic_flops(wl.dims)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        wl.step()
+    barrier()
+
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)]
+          for _ in range(args.steps)]
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = lib.kfac_launch_count()
+    barrier()
+    for s in range(args.steps):
+        ev[s][0].record()
+        wl.step(ev[s])
+        ev[s][3].record()
+    barrier()
+    launches = lib.kfac_launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+
+    total_ms = ev[0][0].elapsed_time(ev[-1][3])
+    phase = np.zeros(3)
+    for s in range(args.steps):
+        for j in range(3):
+            phase[j] += ev[s][j].elapsed_time(ev[s][j + 1])
+    phase /= args.steps
+    t = torch.tensor([total_ms], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms = float(t.item())
+    ms_per_step = total_ms / args.steps
+    value = BATCH * world / (ms_per_step * 1e-3)
+
+    info_bad = int((wl.plan.info != 0).sum().item())
+
+    e2e = None
+    if not args.no_e2e:
+        try:
+            e2e = run_e2e(args, device, world, rank)
+        except ImportError as exc:     # API layer not built yet
+            e2e = dict(value=None, unit='images/sec', error=str(exc))
+
+    if rank == 0:
+        peaks = measured_peaks()
+        names = ['factor', 'inverse', 'precondition']
+        dom = int(np.argmax(phase))
+        achieved = flops[names[dom]] / (phase[dom] * 1e-3) / 1e12
+        stage = {nm: dict(ms=float(ms), tflops=float(flops[nm] / (ms * 1e-3) / 1e12))
+                 for nm, ms in zip(names, phase)}
+        cpu = None if args.no_cpu_baseline else cpu_baseline_sample(steps=1, warmup=0)
+        line = {
+            'metric': 'ResNet-50 K-FAC images/sec (factor+inverse+precondition step)',
+            'value': value, 'unit': 'images/sec', 'n_gpus': world,
+            'steps': args.steps, 'warmup': max(args.warmup, 3),
+            'ms_per_step': ms_per_step, 'higher_is_better': True,
+            'scaling': 'weak', 'vs_baseline': None, 'dtype': 'f32',
+            'data': 'synthetic',
+            'config': {'workload': WORKLOAD, 'batch_per_gpu': BATCH,
+                       'layers': len(wl.layers), 'cov_ema_decay': DECAY,
+                       'damping': DAMPING,
+                       'l2_flush': 'inputs larger than L2 (%.1f GB of '
+                                   'activations and gradients per step)'
+                                   % (wl.input_bytes / 1e9),
+                       'parallelism': 'dp%d' % world},
+            'stages': stage,
+            'factor_inverse_ms': float(phase[0] + phase[1]),
+            'roofline': {
+                'bound': 'tensor', 'kernel': names[dom] + ' stage',
+                'achieved': achieved, 'peak': peaks['tflops'],
+                'unit': 'TFLOP/s', 'frac': achieved / peaks['tflops'],
+                'peak_source': '%s dense bf16 sustained (no tf32 figure in '
+                               'the file); fp32 data' % peaks['source'],
+                'traffic': None},
+            'cpu_baseline': cpu,
+            'gpu_launches': int(launches),
+            'clocks': clocks,
+            'e2e': e2e,
+            'nonpositive_pivots': info_bad,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_e2e(args, device, world, rank):
+    """images/sec of KFAC.update(lossfun, x, t) on a torch ResNet-50 with the
+    batch copied from pinned host memory and the loss read back every step."""
+    import torch
+    from chainerkfac_b200.bench_model import build_training_step
+    step, h2d, d2h = build_training_step(device, BATCH, world, rank,
+                                         cov_ema_decay=DECAY, damping=DAMPING,
+                                         lr=LR, momentum=MOMENTUM)
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        torch.distributed.barrier()
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(args.steps):
+        step()
+    t1.record()
+    torch.cuda.synchronize()
+    ms = torch.tensor([t0.elapsed_time(t1)], device=device, dtype=torch.float64)
+    if world > 1:
+        torch.distributed.all_reduce(ms, op=torch.distributed.ReduceOp.MAX)
+    per = float(ms.item()) / args.steps
+    return dict(value=BATCH * world / (per * 1e-3), unit='images/sec',
+                ms_per_step=per, h2d_bytes_per_step=h2d,
+                d2h_bytes_per_step=d2h)
+
+
+# ------------------------------------------------------------- CPU baseline
+def cpu_layer_inputs(l, rng):
+    n = l['n']
+    if l['kind'] == 'conv':
+        x = rng.standard_normal((n, l['cin'], l['hin'], l['hin']), dtype=np.float32)
+        gy = rng.standard_normal((n, l['cout'], l['hout'], l['hout']), dtype=np.float32) / np.float32(n)
+        gW = rng.standard_normal((l['cout'], l['cin'], l['k'], l['k']), dtype=np.float32)
+    else:
+        x = rng.standard_normal((n, l['cin']), dtype=np.float32)
+        gy = rng.standard_normal((n, l['cout']), dtype=np.float32) / np.float32(n)
+        gW = rng.standard_normal((l['cout'], l['cin']), dtype=np.float32)
+    gb = rng.standard_normal(l['cout'], dtype=np.float32) if l['bias'] else None
+    return x, gy, gW, gb
+
+
+def cpu_layer_pass(orc, l, inputs):
+    """The reference's --no_cuda stages for one layer, via the oracle."""
+    x, gy, gW, gb = inputs
+    W, v = np.zeros_like(gW), np.zeros_like(gW)
+    t0 = time.perf_counter()
+    if l['kind'] == 'conv':
+        A = orc.conv_A(x, l['k'], l['stride'], l['pad'], l['bias'])
+        G = orc.conv_G(gy)
+    else:
+        A = orc.linear_A(x, l['bias'])
+        G = orc.linear_G(gy)
+    t1 = time.perf_counter()
+    out = orc.connection_step(A, G, gW, gb, DAMPING, None, None, DECAY)
+    orc.momentum_update(W, v, out['kfgrad_W'], LR, MOMENTUM)
+    t2 = time.perf_counter()
+    return t1 - t0, t2 - t1
+
+
+def cpu_baseline_sample(steps=1, warmup=0, budget_s=150.0):
+    """Time the oracle on one layer per distinct shape; scale by multiplicity.
+    Stops early (and says so) once `budget_s` seconds of passes have run."""
+    from oracle import kfac_oracle as orc
+    layers, dims = layer_table()
+    groups = {}
+    for l, d in zip(layers, dims):
+        key = (l['kind'], l.get('k'), l.get('stride'), l['cin'], l['cout'],
+               l.get('hin'), l['bias'])
+        groups.setdefault(key, [l, 0])[1] += 1
+    rng = np.random.default_rng(7)
+    inputs = [cpu_layer_inputs(l, rng) for l, _ in groups.values()]
+    times, t_start, done = [], time.perf_counter(), 0
+    for it in range(warmup + steps):
+        tf = ti = 0.0
+        for (l, mult), inp in zip(groups.values(), inputs):
+            a, b = cpu_layer_pass(orc, l, inp)
+            tf += a * mult
+            ti += b * mult
+        done += 1
+        if it >= warmup:
+            times.append((tf, ti))
+        if time.perf_counter() - t_start > budget_s and times:
+            break
+    tf = float(np.mean([t[0] for t in times]))
+    ti = float(np.mean([t[1] for t in times]))
+    return dict(value=BATCH / (tf + ti), unit='images/sec',
+                cores=os.cpu_count(), kind='port',
+                factor_s=tf, inverse_precondition_s=ti,
+                passes_timed=len(times), passes_run=done,
+                sample='NumPy oracle (reference --no_cuda arithmetic, all '
+                       'host cores through the BLAS threads) on one layer of '
+                       'each of the %d distinct ResNet-50 layer shapes, batch '
+                       '32; each time multiplied by the number of layers of '
+                       'that shape (54 layers in total)' % len(groups))
+
+
+def run_reference(args):
+    rank = int(os.environ.get('RANK', '0'))
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    if rank != 0:
+        return
+    t0 = time.perf_counter()
+    cpu = cpu_baseline_sample(steps=max(args.steps, 1), warmup=args.warmup)
+    wall = time.perf_counter() - t0
+    value = cpu['value']
+    line = {
+        'impl': 'reference',
+        'metric': 'ResNet-50 K-FAC images/sec (factor+inverse+precondition step)',
+        'value': value, 'unit': 'images/sec', 'n_gpus': world,
+        'steps': args.steps, 'warmup': args.warmup,
+        'ms_per_step': 1e3 * BATCH / value, 'higher_is_better': True,
+        'scaling': 'weak', 'vs_baseline': None, 'dtype': 'f32',
+        'data': 'synthetic',
+        'config': {'workload': WORKLOAD, 'batch_per_gpu': BATCH,
+                   'layers': 54, 'cov_ema_decay': DECAY, 'damping': DAMPING,
+                   'parallelism': 'cpu (rank 0 only)'},
+        'cpu_baseline': cpu,
+        'e2e': {'value': value, 'unit': 'images/sec',
+                'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
+        'gpu_launches': 0, 'wall_s': wall,
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--gpus', type=int, default=1)
+    ap.add_argument('--steps', type=int, default=10)
+    ap.add_argument('--warmup', type=int, default=3)
+    ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
+    ap.add_argument('--no-e2e', action='store_true')
+    ap.add_argument('--no-cpu-baseline', action='store_true')
+    args = ap.parse_args()
+    if args.impl == 'reference':
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == '__main__':
+    main()

@@ -25,6 +25,7 @@ SZ = ctypes.c_size_t
 SIGNATURES = {
     'kfac_abi_version': (I, []),
     'kfac_last_error': (ctypes.c_char_p, []),
+    'kfac_launch_count': (I64, []),
     'kfac_factor_workspace_bytes': (SZ, [I64, I]),
     'kfac_factor_dense': (I, [VP, I64, I, I64, I, F, F, VP, VP, SZ, VP]),
     'kfac_factor_conv_input': (I, [VP, I, I, I, I, I, I, I, I, F, F, VP, VP,

@@ -31,6 +31,7 @@ inline int fail(int code, const char* fmt, ...) {
 
 #define KFAC_LAUNCH_CHECK(name)                                             \
   do {                                                                      \
+    ::kfac::count_launch();                                                 \
     cudaError_t e__ = cudaGetLastError();                                   \
     if (e__ != cudaSuccess)                                                 \
       return ::kfac::fail(KFAC_ERR_CUDA, "launch of %s failed: %s", name,   \
@@ -43,6 +44,9 @@ inline int fail(int code, const char* fmt, ...) {
   } while (0)
 
 inline int ceil_div(int64_t a, int64_t b) { return (int)((a + b - 1) / b); }
+
+// Counter behind kfac_launch_count().
+void count_launch();
 
 // Number of streaming multiprocessors of the current device (cached).
 int sm_count();

@@ -1,12 +1,17 @@
 // Grouped fp32 tile GEMM: one launch covers the tiles of many independent
 // problems (all layers of a stage).  Used by the inverse and the
 // precondition stages.
+#include <atomic>
+
 #include "gemm_simt.cuh"
 
 namespace kfac {
 
 static __thread char g_err[512];
 char* error_buffer() { return g_err; }
+
+static std::atomic<long long> g_launches(0);
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 int sm_count() {
   static int cached[64] = {0};
@@ -130,3 +135,6 @@ int launch_grouped_gemm(const GemmDesc* descs_dev, int ndesc, int total_tiles,
 
 extern "C" int kfac_abi_version(void) { return 1; }
 extern "C" const char* kfac_last_error(void) { return kfac::error_buffer(); }
+extern "C" int64_t kfac_launch_count(void) {
+  return kfac::g_launches.load(std::memory_order_relaxed);
+}

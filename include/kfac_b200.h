@@ -32,6 +32,8 @@ extern "C" {
 int kfac_abi_version(void);
 /* Message of the calling thread's most recent failure ("" if none). */
 const char* kfac_last_error(void);
+/* Number of kernels this library has launched in this process so far. */
+int64_t kfac_launch_count(void);
 
 /* ------------------------------------------------------------------ factors
  * out(d x d) = alpha * X^T X + beta * out, X a (rows x d) matrix that is never
