@@ -28,6 +28,8 @@ SIGNATURES = {
     'kfac_launch_count': (I64, []),
     'kfac_factor_workspace_bytes': (SZ, [I64, I]),
     'kfac_factor_dense': (I, [VP, I64, I, I64, I, F, F, VP, VP, SZ, VP]),
+    'kfac_factor_noalloc_max_bytes': (SZ, []),
+    'kfac_factor_dense_noalloc': (I, [VP, I64, I, I64, I, F, F, VP, VP]),
     'kfac_factor_conv_input': (I, [VP, I, I, I, I, I, I, I, I, F, F, VP, VP,
                                    SZ, VP]),
     'kfac_factor_conv_grad': (I, [VP, I, I, I, I, F, F, VP, VP, SZ, VP]),

@@ -4,6 +4,8 @@
 // written to memory.  Only tiles on or below the diagonal are computed; the
 // epilogue mirrors them.  Long contractions are split across CTAs; partial
 // tiles go through a workspace and are summed in a fixed order.
+#include <mutex>
+
 #include "gemm_simt.cuh"
 
 namespace kfac {
@@ -114,6 +116,34 @@ factor_reduce_kernel(const float* __restrict__ partial, int tiles, int splits,
     *q = v;
     if (mirror) out[(long long)c * d + r] = v;
   }
+}
+
+// Built-in scratch for kfac_factor_dense_noalloc: room for
+// kNoAllocTiles partial 128x128 tiles.  Lives in every context that loads the
+// library, from load until exit.
+constexpr int kNoAllocTiles = 512;
+constexpr size_t kNoAllocBytes =
+    (size_t)kNoAllocTiles * TM * TN * sizeof(float);  // 32 MiB
+static __device__ __align__(256) float g_noalloc_scratch[kNoAllocTiles * TM * TN];
+
+// Device address of g_noalloc_scratch on the current device.  In host code the
+// array's name is only a handle, so the address is looked up once per device
+// (with that device current) and cached.
+static int noalloc_scratch_address(float** out) {
+  static std::mutex mu;
+  static float* cached[64] = {nullptr};
+  int dev = 0;
+  KFAC_CUDA(cudaGetDevice(&dev));
+  KFAC_REQUIRE(dev >= 0 && dev < 64, "device index %d unsupported", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (cached[dev] == nullptr) {
+    float* ptr = nullptr;
+    KFAC_CUDA(cudaGetSymbolAddress((void**)&ptr, g_noalloc_scratch));
+    KFAC_REQUIRE(ptr != nullptr, "built-in scratch has no device address");
+    cached[dev] = ptr;
+  }
+  *out = cached[dev];
+  return KFAC_OK;
 }
 
 static int run_factor(const Operand& X, long long rows, int d, float alpha,
@@ -357,4 +387,32 @@ extern "C" int kfac_momentum_update(int64_t count, const float* grad,
                                                             v, lr, momentum);
   KFAC_LAUNCH_CHECK("momentum_kernel");
   return KFAC_OK;
+}
+
+extern "C" size_t kfac_factor_noalloc_max_bytes(void) { return kNoAllocBytes; }
+
+extern "C" int kfac_factor_dense_noalloc(const float* x, int64_t rows,
+                                         int d_in, int64_t ld,
+                                         int add_ones_col, float alpha,
+                                         float beta, float* out,
+                                         void* stream) {
+  KFAC_REQUIRE(ld >= d_in, "factor_dense_noalloc: ld=%lld < d_in=%d",
+               (long long)ld, d_in);
+  const int d = d_in + (add_ones_col ? 1 : 0);
+  size_t need = kfac_factor_workspace_bytes(rows, d);
+  if (need > kNoAllocBytes)
+    return fail(KFAC_ERR_WORKSPACE,
+                "factor_dense_noalloc: rows=%lld d=%d needs %zu bytes of "
+                "scratch, the built-in scratch holds %zu; use "
+                "kfac_factor_dense with a caller workspace",
+                (long long)rows, d, need, kNoAllocBytes);
+  float* scratch = nullptr;
+  int rc = noalloc_scratch_address(&scratch);
+  if (rc != KFAC_OK) return rc;
+  Operand X = strided_operand(x, ld, 1, d_in);
+  if (add_ones_col) X.extra_idx = d_in;
+  // Every partial tile is written in full before it is read, so nothing in
+  // the shared scratch has to be cleared between calls.
+  return run_factor(X, rows, d, alpha, beta, out, scratch, kNoAllocBytes,
+                    (cudaStream_t)stream);
 }

@@ -74,6 +74,26 @@ int kfac_factor_conv_grad(const float* gy, int n, int c, int ho, int wo,
                           void* workspace, size_t workspace_bytes,
                           void* stream);
 
+/* Same result as kfac_factor_dense, for callers that can neither allocate
+ * device memory nor pass a workspace: code that runs inside a framework whose
+ * own pool has taken all of the device's memory, so that a cudaMalloc would
+ * fail, or on a path where an allocation's implicit device-wide wait is not
+ * acceptable.  No counterpart in the reference (which allocates freely through
+ * CuPy's pool).  The partial tiles go to a fixed array inside the library
+ * (kfac_factor_noalloc_max_bytes() bytes, 32 MiB, held by every GPU context
+ * that loads the library until it exits); the call performs no cudaMalloc,
+ * cudaFree or other allocating routine.  Shapes whose split needs more than
+ * that (kfac_factor_workspace_bytes(rows, d) > the maximum) are rejected with
+ * KFAC_ERR_WORKSPACE.  The first call on each device looks up the array's
+ * device address; make that first call outside any stream capture.  All calls
+ * on a device share the one array, which keeps the previous call's partial
+ * tiles (none need clearing: each is rewritten before it is read); two calls
+ * whose kernels can overlap on the GPU (different streams) race on it. */
+size_t kfac_factor_noalloc_max_bytes(void);
+int kfac_factor_dense_noalloc(const float* x, int64_t rows, int d_in,
+                              int64_t ld, int add_ones_col, float alpha,
+                              float beta, float* out, void* stream);
+
 /* Per-sample BatchNormalization gradients: out is (n x 2c),
  * out[s, j] = scale * sum_hw gy[s,j,:] * xhat[s,j,:] and
  * out[s, c+j] = scale * sum_hw gy[s,j,:], xhat = x normalised with the batch
