@@ -1,0 +1,39 @@
+"""Block of a 2-D convolution; mirrors
+``chainerkfac/optimizers/fisher_blocks/connections/convolution_2d.py``.  The
+im2col patch matrix of the reference is never built: the factor kernel
+gathers patches while it multiplies."""
+
+from chainerkfac_b200 import ops
+from chainerkfac_b200.optimizers.fisher_blocks.connection import \
+    FisherBlockConnection
+
+
+class Convolution2DFunction(object):
+    """Marks a call of a convolution layer in the hook protocol."""
+
+
+class FisherBlockConvolution2D(FisherBlockConnection):
+
+    @property
+    def funcclass(self):
+        return Convolution2DFunction
+
+    def compute_A(self, in_data):
+        # convolution_2d.py:19-41: A = P^T P / n, P = patches (+ ones column)
+        x = in_data[0].contiguous()
+        ksize, stride, pad = \
+            self._link.ksize, self._link.stride[0], self._link.pad[0]
+        n, c = x.shape[0], x.shape[1]
+        bias = self._link.b is not None
+        out = self.factor_buffer(0, c * ksize * ksize + int(bias), x.device)
+        return ops.factor_conv_input(x, ksize, stride, pad, bias,
+                                     alpha=1.0 / n, out=out)
+
+    def compute_G(self, in_data, out_grad_data):
+        # convolution_2d.py:43-72: G = g^T g * s^2 / (n ho wo), s = n/loss_scale
+        gy = out_grad_data[0].contiguous()
+        n, c, ho, wo = gy.shape
+        s = self.gy_scale(n)
+        out = self.factor_buffer(1, c, gy.device)
+        return ops.factor_conv_grad(gy, alpha=s * s / float(n * ho * wo),
+                                    out=out)

@@ -1,0 +1,112 @@
+"""Full (2C x 2C) block of a BatchNormalization layer's scale and shift;
+mirrors ``chainerkfac/optimizers/fisher_blocks/normalizations/
+batch_normalization.py``."""
+
+import warnings
+
+import torch
+
+from chainerkfac_b200 import ops
+from chainerkfac_b200.optimizers.fisher_block import FisherBlock
+
+
+class BatchNormalizationFunction(object):
+    """Marks a call of a batch-normalization layer in the hook protocol."""
+
+
+class FisherBlockBatchNormalization(FisherBlock):
+
+    def __init__(self, *args, **kwargs):
+        self._F = None
+        self._nan_flag = None
+        super(FisherBlockBatchNormalization, self).__init__(*args, **kwargs)
+        if self.link.gamma is None or self.link.beta is None:
+            raise NotImplementedError(
+                'BatchNormalization blocks need both gamma and beta')
+
+    @property
+    def funcclass(self):
+        return BatchNormalizationFunction
+
+    cov_forward = property(lambda self: None)
+    cov_backward = property(lambda self: self.covs[0])
+    inv_forward = property(lambda self: None)
+    inv_backward = property(lambda self: self.invs[0])
+
+    def is_mine(self, func, in_data, out_grad_data=None):
+        if not isinstance(func, self.funcclass):
+            return False
+        return in_data[1] is self.link.gamma.data or \
+            in_data[2] is self.link.beta.data
+
+    def forward_postprocess(self, func, in_data):
+        pass  # F needs the output gradient
+
+    def backward_preprocess(self, func, in_data, out_grad_data):
+        self._F = self.compute_F(in_data, out_grad_data)
+        self.covs = [self._F]
+
+    def compute_F(self, in_data, out_grad_data):
+        # batch_normalization.py:78-131: per-sample gradients of (gamma, beta)
+        # with xhat from batch statistics, F = grad^T grad / n
+        x = in_data[0].contiguous()
+        gy = out_grad_data[0].contiguous()
+        if x.dim() not in (2, 4):
+            raise RuntimeError(
+                'len(x.shape) must be 2 or 4, not {}.'.format(x.dim()))
+        n, c = x.shape[0], x.shape[1]
+        grads = ops.bn_sample_grads(x, gy, float(self.link.eps),
+                                    self.gy_scale(n))
+        out = self._F
+        if out is None or out.shape[0] != 2 * c or out.device != x.device:
+            out = torch.empty((2 * c, 2 * c), dtype=torch.float32,
+                              device=x.device)
+        return ops.factor_dense(grads, False, alpha=1.0 / n, out=out)
+
+    def plan_entries(self):
+        # batch_normalization.py:133-157: max(l2_coef, damping) * stab_coeff
+        l2 = max(getattr(self.link.gamma, 'l2_coef', 0.0) or 0.0,
+                 getattr(self.link.beta, 'l2_coef', 0.0) or 0.0)
+        return [(2, l2, float(self.stab_coeff))]
+
+    def set_diag_vals(self, diag):
+        self.diag_val_backward = diag[0]
+
+    def get_diagvals(self):
+        if self._plan is None:
+            self.update_invs()
+        return [self.diag_val_backward.expand(self.cov_emas[0].shape[0])]
+
+    def update_kfgrads(self):
+        # batch_normalization.py:159-191: F_inv [grad_gamma; grad_beta]; on
+        # NaN the raw gradients are used instead (checked on the host, as the
+        # reference does with xp.any(xp.isnan(..)))
+        self.check_attr('invs')
+        gamma, beta = self.link.gamma, self.link.beta
+        for p in (gamma, beta):
+            if getattr(p, 'kfgrad', None) is None or p.kfgrad is p.grad:
+                p.kfgrad = torch.empty_like(p.data)
+        if self._nan_flag is None:
+            self._nan_flag = torch.zeros(1, dtype=torch.int32,
+                                         device=gamma.data.device)
+        ops.symv_split(self.invs[0], gamma.grad.contiguous(),
+                       beta.grad.contiguous(), gamma.kfgrad, beta.kfgrad,
+                       self._nan_flag)
+
+    def check_nan(self):
+        """Host check of the NaN flag (synchronises); substitutes the raw
+        gradients like ``_check_nan`` of the reference."""
+        if self._nan_flag is not None and int(self._nan_flag.item()) != 0:
+            warnings.warn(
+                'Detected NaN in the kfgrads of the batch normalization layer'
+                'Substitue ``grad`` as ``kfgrad`` to avoid crashing')
+            self.link.gamma.kfgrad = self.link.gamma.grad
+            self.link.beta.kfgrad = self.link.beta.grad
+            self._nan_flag.zero_()
+            return True
+        return False
+
+    def extract_for_reduce_scatter_v(self):
+        arrays = self.extract_attr_from_params('grad')
+        arrays.append((self.cov_backward, True))
+        return arrays

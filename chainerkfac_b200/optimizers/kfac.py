@@ -1,0 +1,543 @@
+"""K-FAC optimizers with the interface of ``chainerkfac/optimizers/kfac.py``.
+
+``KFAC`` / ``DistributedKFAC`` keep the reference's constructor arguments,
+run-time mutable hyper-parameters (``lr``, ``lr_pre``, ``momentum``,
+``cov_ema_decay``, ``damping``), public state (``fblocks``, ``kfhook``,
+``acc_*``, ``indices`` / ``local_indices`` / ``local_fblocks``) and call
+sequence.  Differences in mechanism, not in results: the per-block loop of
+``update_kfgrads`` (``kfac.py:306-310``) becomes three batched device stages
+(running averages, one inverse plan over every owned factor, one grouped
+preconditioning launch pair, optionally with the momentum update fused in),
+and hook dispatch is a dictionary lookup instead of a scan.
+"""
+
+import numpy as np
+import torch
+from torch import nn
+
+from chainerkfac_b200 import links as L
+from chainerkfac_b200 import ops
+from chainerkfac_b200.optimizers import _base
+from chainerkfac_b200.optimizers import fisher_blocks as FB
+from chainerkfac_b200.optimizers.fisher_block import PI_TYPE_TRACENORM
+
+_default_hyperparam = _base.Hyperparameter()
+_default_hyperparam.lr = 0.001
+_default_hyperparam.lr_pre = 0.001
+_default_hyperparam.momentum = 0.9
+_default_hyperparam.cov_ema_decay = 0.99
+_default_hyperparam.damping = 0.03
+
+
+def fblock_constructor(sub_linkname, sub_link, **kwargs):
+    """``kfac.py:19-30``."""
+    args = (sub_linkname, sub_link)
+    if isinstance(sub_link, L.Linear):
+        return FB.FisherBlockLinear(*args, **kwargs)
+    elif isinstance(sub_link, L.Convolution2D):
+        return FB.FisherBlockConvolution2D(*args, **kwargs)
+    elif isinstance(sub_link, L.BatchNormalization):
+        if sub_link.gamma is None and sub_link.beta is None:
+            return None
+        return FB.FisherBlockBatchNormalization(*args, **kwargs)
+    else:
+        return None
+
+
+def connection_only_constructor(sub_linkname, sub_link, **kwargs):
+    """Constructor that leaves BatchNormalization layers to the plain momentum
+    rule (the ``constructor`` hook point of ``kfac.py:151,196-199``)."""
+    if isinstance(sub_link, L.BatchNormalization):
+        return None
+    return fblock_constructor(sub_linkname, sub_link, **kwargs)
+
+
+class KFACHook(object):
+    """Function hook of ``kfac.py:33-48`` on top of torch module hooks: inside
+    the ``with`` block every forward call of a layer that owns a block fires
+    ``forward_postprocess(func, in_data)`` and, when the gradient of its
+    output arrives, ``backward_preprocess(func, in_data, out_grad_data)``."""
+
+    name = 'KFACHook'
+
+    def __init__(self, fblocks):
+        self.fblocks = fblocks
+        self._handles = []
+        self._by_array = None
+
+    def _lookup(self, func, in_data, out_grad_data=None):
+        if self._by_array is None or len(self._by_array) != len(self.fblocks):
+            self._by_array = {}
+            for fb in self.fblocks:
+                first = fb.link.W if hasattr(fb.link, 'W') else fb.link.gamma
+                self._by_array[id(first.data)] = fb
+        fb = self._by_array.get(id(in_data[1]))
+        if fb is not None and fb.is_mine(func, in_data, out_grad_data):
+            return fb
+        for fb in self.fblocks:
+            if fb.is_mine(func, in_data, out_grad_data):
+                return fb
+        return None
+
+    def forward_postprocess(self, func, in_data):
+        fblock = self._lookup(func, in_data)
+        if fblock is not None:
+            fblock.forward_postprocess(func, in_data)
+
+    def backward_preprocess(self, func, in_data, out_grad_data):
+        fblock = self._lookup(func, in_data, out_grad_data)
+        if fblock is not None:
+            fblock.backward_preprocess(func, in_data, out_grad_data)
+
+    def _make_forward_hook(self, fblock):
+        link = fblock.link
+
+        def hook(module, inputs, output):
+            if not (torch.is_grad_enabled() and output.requires_grad):
+                return
+            if isinstance(link, L.BatchNormalization):
+                if not module.training:
+                    return
+                in_data = (inputs[0].detach(), link.gamma.data, link.beta.data)
+            else:
+                in_data = (inputs[0].detach(), link.W.data) + (
+                    () if link.b is None else (link.b.data,))
+            func = fblock.funcclass()
+            self.forward_postprocess(func, in_data)
+            output.register_hook(
+                lambda g: self.backward_preprocess(func, in_data,
+                                                   (g.detach(),)))
+        return hook
+
+    def __enter__(self):
+        for fb in self.fblocks:
+            self._handles.append(
+                fb.link.module.register_forward_hook(
+                    self._make_forward_hook(fb)))
+        return self
+
+    def __exit__(self, *exc):
+        for h in self._handles:
+            h.remove()
+        self._handles = []
+        return False
+
+
+class KFACUpdateRule(_base.UpdateRule):
+    """``kfac.py:51-116``: momentum SGD on ``param.kfgrad`` (falling back to
+    ``param.grad``), one fused kernel per parameter."""
+
+    def __init__(self, parent_hyperparam=None, adjust_momentum=False):
+        super(KFACUpdateRule, self).__init__(
+            parent_hyperparam or _default_hyperparam)
+        self.adjust_momentum = adjust_momentum
+
+    def init_state(self, param):
+        self.state['v'] = torch.zeros_like(param.data)
+
+    def velocity(self, param):
+        if self._state is None:
+            self._state = {}
+            self.init_state(param)
+        return self.state['v']
+
+    def effective_momentum(self):
+        lr, lr_pre = self.hyperparam.lr, self.hyperparam.lr_pre
+        momentum = self.hyperparam.momentum
+        if self.adjust_momentum and lr < lr_pre:
+            momentum *= lr / lr_pre
+        return momentum
+
+    def update(self, param):
+        if getattr(param, '_kfac_applied', False):
+            # the preconditioning epilogue already applied this step's update
+            param._kfac_applied = False
+            self.t += 1
+            return
+        if param._loss_scale is not None and \
+                getattr(param, 'kfgrad', None) is not None:
+            param.kfgrad /= param._loss_scale
+        super(KFACUpdateRule, self).update(param)
+
+    def update_core(self, param):
+        grad = getattr(param, 'kfgrad', None)
+        if grad is None:
+            grad = param.grad
+        if grad is None:
+            return
+        ops.momentum_update(grad.contiguous(), param.data, self.state['v'],
+                            self.hyperparam.lr, self.effective_momentum())
+
+    update_core_gpu = update_core
+
+
+class KFAC(_base.GradientMethod):
+    """K-FAC optimizer (``kfac.py:119-310``); same arguments and defaults."""
+
+    def __init__(self, lr=_default_hyperparam.lr,
+                 momentum=_default_hyperparam.momentum,
+                 cov_ema_decay=_default_hyperparam.cov_ema_decay,
+                 damping=_default_hyperparam.damping, stab_coeff=16.0,
+                 constructor=fblock_constructor, pi_type='tracenorm',
+                 use_cholesky=True, loss_scale=None, adjust_momentum=False,
+                 acc_iters=1):
+        super(KFAC, self).__init__()
+        self.hyperparam.lr = lr
+        self.hyperparam.lr_pre = lr
+        self.hyperparam.momentum = momentum
+        self.hyperparam.cov_ema_decay = cov_ema_decay
+        self.hyperparam.damping = damping
+        self.pi_type = pi_type
+        self.constructor = constructor
+        self.adjust_momentum = adjust_momentum
+        self.stab_coeff = stab_coeff
+        self.fblocks = []
+        self.kfhook = None
+        self._loss_scale = loss_scale
+        self.constructor_kwargs = {
+            'cov_ema_decay': self.hyperparam.cov_ema_decay,
+            'damping': self.hyperparam.damping,
+            'use_cholesky': use_cholesky,
+            'pi_type': self.pi_type,
+            'stab_coeff': self.stab_coeff,
+            'loss_scale': self._loss_scale,
+        }
+        assert acc_iters >= 1, 'Accumulation iterations should be 1 or larger'
+        self.acc_iters = acc_iters
+        self.acc_count = 0
+        self.acc_aware_iterations = 0
+        self.only_pic_update_weight = False  # True only if in DistributedKFAC
+        # apply v = m v - lr kf; W += v inside the preconditioning epilogue
+        self.fuse_update = True
+        self._plans = {}
+        self.observation = {}
+
+    lr = _base.HyperparameterProxy('lr')
+    lr_pre = _base.HyperparameterProxy('lr_pre')
+    momentum = _base.HyperparameterProxy('momentum')
+    cov_ema_decay = _base.HyperparameterProxy('cov_ema_decay')
+    damping = _base.HyperparameterProxy('damping')
+
+    def setup(self, link):
+        super(KFAC, self).setup(link)
+        self.fblocks = []
+        for sub_linkname, sub_link in sorted(self.target.namedlinks(),
+                                             key=lambda kv: kv[0]):
+            fblock = self.constructor(sub_linkname, sub_link,
+                                      **self.constructor_kwargs)
+            if fblock is None:
+                continue
+            self.fblocks.append(fblock)
+        self.kfhook = KFACHook(self.fblocks)
+        return self
+
+    def reallocate_cleared_grads(self):
+        for name, param in self.target.namedparams(include_uninit=False):
+            if hasattr(param, 'kfgrad') and param.kfgrad is None:
+                param.kfgrad = torch.zeros_like(param.data)
+        super(KFAC, self).reallocate_cleared_grads()
+
+    def create_update_rule(self):
+        return KFACUpdateRule(self.hyperparam,
+                              adjust_momentum=self.adjust_momentum)
+
+    def _forward_backward(self, lossfun, args, kwargs, after_forward=None):
+        with self.kfhook:
+            loss = lossfun(*args, **kwargs)
+            if after_forward is not None:
+                after_forward()
+            if self._use_cleargrads:
+                self.target.cleargrads()
+            else:
+                self.target.zerograds()
+            if self._loss_scale is not None:
+                loss.backward(torch.full_like(loss, self._loss_scale))
+            else:
+                loss.backward()
+        self.loss = loss.detach()
+
+    def update(self, lossfun=None, *args, **kwargs):
+        if lossfun is not None:
+            self._forward_backward(lossfun, args, kwargs)
+
+        if self.acc_iters > 1:
+            if self.accumulate():
+                return
+
+        self.reallocate_cleared_grads()
+        self.call_hooks('pre')
+        self.t += 1
+        self.update_kfgrads(self.fblocks)
+
+        if not self.only_pic_update_weight:
+            for param in self.target.params():
+                param.update()
+
+        self.reallocate_cleared_grads()
+        self.call_hooks('post')
+        self.acc_aware_iterations += 1
+        self.observation['acc_aware_iterations'] = self.acc_aware_iterations
+
+    # -- accumulation over micro-steps (kfac.py:259-304) -------------------
+    def accumulate(self):
+        if self.acc_count == 0:
+            for param in self.target.params():
+                param.acc_grad = None
+            for fblock in self.fblocks:
+                fblock.acc_covs = None
+        self.accumulate_grads()
+        self.accumulate_covs()
+        self.acc_count += 1
+        if self.acc_count == self.acc_iters:
+            self.acc_count = 0
+            for param in self.target.params():
+                param.grad = param.acc_grad
+            for fblock in self.fblocks:
+                fblock.covs = fblock.acc_covs
+            return False
+        elif self.acc_count < self.acc_iters:
+            return True
+        raise ValueError(
+            'acc_count {} should not be larger than acc_iters {}'.format(
+                self.acc_count, self.acc_iters))
+
+    def accumulate_grads(self):
+        s = 1.0 / self.acc_iters
+        for param in self.target.params():
+            if param.grad is None:
+                continue
+            g = param.grad.contiguous()
+            if getattr(param, 'acc_grad', None) is None:
+                param.acc_grad = torch.empty_like(g)
+                ops.axpby(s, g, 0.0, param.acc_grad, param.acc_grad)
+            else:
+                ops.axpby(s, g, 1.0, param.acc_grad, param.acc_grad)
+
+    def accumulate_covs(self):
+        s = 1.0 / self.acc_iters
+        for fblock in self.fblocks:
+            fblock.check_attr('covs')
+            if getattr(fblock, 'acc_covs', None) is None:
+                fblock.acc_covs = [torch.empty_like(c) for c in fblock.covs]
+                for c, a in zip(fblock.covs, fblock.acc_covs):
+                    ops.axpby(s, c, 0.0, a, a)
+            else:
+                for c, a in zip(fblock.covs, fblock.acc_covs):
+                    ops.axpby(s, c, 1.0, a, a)
+
+    # -- curvature stages (kfac.py:306-310), batched over blocks ------------
+    def _plan_for(self, fblocks):
+        key = tuple(id(fb) for fb in fblocks)
+        entry = self._plans.get(key)
+        bufs = tuple(e.data_ptr() for fb in fblocks for e in fb.cov_emas)
+        if entry is not None and entry[1] == bufs:
+            return entry[0]
+        if entry is not None:
+            entry[0].close()
+        factors, inverses, partner, role, l2, scale = [], [], [], [], [], []
+        for fb in fblocks:
+            ents = fb.plan_entries()
+            base = len(factors)
+            fb.ensure_invs()
+            for j, (rl, l2c, sc) in enumerate(ents):
+                factors.append(fb.cov_emas[j])
+                inverses.append(fb.invs[j])
+                partner.append(base + 1 - j if len(ents) == 2 else -1)
+                role.append(rl)
+                l2.append(l2c)
+                scale.append(sc)
+        plan = ops.InversePlan(factors, inverses, partner, role, l2, scale)
+        self._plans[key] = (plan, bufs)
+        return plan
+
+    def update_kfgrads(self, fblocks):
+        fblocks = list(fblocks)
+        if not fblocks:
+            return
+        for fblock in fblocks:
+            fblock.update_cov_emas()
+        # one batched damped inverse per (damping, pi rule) group
+        groups = {}
+        for fb in fblocks:
+            groups.setdefault((fb.damping, fb._pi_type), []).append(fb)
+        for (damping, pi_type), group in groups.items():
+            plan = self._plan_for(group)
+            plan.run(damping, pi_type == PI_TYPE_TRACENORM)
+            k = 0
+            for fb in group:
+                n = len(fb.cov_emas)
+                fb.set_diag_vals(plan.diag[k:k + n])
+                k += n
+        conn = [fb for fb in fblocks
+                if isinstance(fb, FB.FisherBlockConnection)]
+        if conn:
+            self._precondition(conn)
+        for fb in fblocks:
+            if isinstance(fb, FB.FisherBlockBatchNormalization):
+                fb.update_kfgrads()
+
+    def _can_fuse(self, param):
+        rule = param.update_rule
+        return (self.fuse_update and isinstance(rule, KFACUpdateRule) and
+                rule.enabled and param._loss_scale is None and
+                not rule._pre_update_hooks and not rule._post_update_hooks)
+
+    def _precondition(self, conn):
+        Gi, Ai, gW, gb, kW, kb = [], [], [], [], [], []
+        pW, pb, vW, vb = [], [], [], []
+        fused_params = []
+        lr = self.hyperparam.lr
+        mom = None
+        for fb in conn:
+            W, b = fb.link.W, fb.link.b
+            kfW, kfb = fb.kfgrad_buffers()
+            Ai.append(fb.invs[0])
+            Gi.append(fb.invs[1])
+            gW.append(W.grad.contiguous())
+            gb.append(None if b is None else b.grad.contiguous())
+            kW.append(kfW)
+            kb.append(kfb)
+            fuse = self._can_fuse(W) and (b is None or self._can_fuse(b))
+            if fuse:
+                m = W.update_rule.effective_momentum()
+                mom = m if mom is None else mom
+                fuse = (m == mom)
+            if fuse:
+                pW.append(W.data)
+                vW.append(W.update_rule.velocity(W))
+                pb.append(None if b is None else b.data)
+                vb.append(None if b is None else b.update_rule.velocity(b))
+                fused_params += [W] + ([] if b is None else [b])
+            else:
+                pW.append(None)
+                vW.append(None)
+                pb.append(None)
+                vb.append(None)
+        ops.precondition(Gi, Ai, gW, gb, kW, kb, pW, pb, vW, vb, lr=lr,
+                         momentum=mom if mom is not None else 0.0)
+        for p in fused_params:
+            p._kfac_applied = True
+
+
+class DistributedKFAC(KFAC):
+    """K-FAC with layer-ownership partition (``kfac.py:313-453``): every rank
+    builds factors from its local batch, factors and gradients are
+    reduce-scattered to the block's owner, the owner inverts, preconditions
+    and (by default) updates its layers, and the updated weights are
+    all-gathered."""
+
+    def __init__(self, comm, *args, communicate_after_forward=False,
+                 only_pic_update_weight=True, **kwargs):
+        super(DistributedKFAC, self).__init__(*args, **kwargs)
+        self.comm = comm
+        self.only_pic_update_weight = only_pic_update_weight
+        cuda = torch.cuda.is_available()
+        self.stream = torch.cuda.Stream() \
+            if cuda and communicate_after_forward else None
+        self.cuda_event = torch.cuda.Event(blocking=True) \
+            if cuda and communicate_after_forward else None
+        self.target_params = []
+        self.constructor_kwargs['communicate_after_forward'] = \
+            communicate_after_forward
+        self.communicate_after_forward = communicate_after_forward
+
+    def setup(self, link):
+        super(DistributedKFAC, self).setup(link)
+        local_size = self.comm.size
+        local_rank = self.comm.rank
+        indices = np.array_split(np.arange(len(self.fblocks)), local_size)
+        indices = [local_indices.tolist() for local_indices in indices]
+        local_indices = indices[local_rank]
+        self.indices = indices
+        self.local_indices = local_indices
+        self.local_fblocks = [self.fblocks[i] for i in local_indices]
+        setattr(self.comm, 'indices', indices)
+        return self
+
+    def update(self, lossfun=None, *args, **kwargs):
+        if lossfun is not None:
+            self._forward_backward(
+                lossfun, args, kwargs,
+                after_forward=self.reduce_scatter_v_after_forward)
+        if self.is_changed(self.target):
+            self.comm.bcast_data(self.target)
+        else:
+            self.reduce_scatter_v_after_backward()
+            super(DistributedKFAC, self).update()
+
+    def reduce_scatter_v_after_forward(self):
+        if not self.communicate_after_forward:
+            return
+        if self.cuda_event is not None:
+            self.cuda_event.record(torch.cuda.current_stream())
+            self.stream.wait_event(self.cuda_event)
+        arrays = extract(
+            self.fblocks, self.indices,
+            lambda block: block.extract_for_reduce_scatter_v_after_forward())
+        self.comm.reduce_scatter_v_arrays(arrays, self.stream)
+
+    def reduce_scatter_v_after_backward(self):
+        if self.cuda_event is not None:
+            self.cuda_event.record(self.stream)
+            torch.cuda.current_stream().wait_event(self.cuda_event)
+        arrays = extract(self.fblocks, self.indices,
+                         lambda block: block.extract_for_reduce_scatter_v())
+        self.comm.reduce_scatter_v_arrays(arrays)
+
+    def is_changed(self, target):
+        previous_params = self.target_params
+        self.target_params = [(name, param.data is not None)
+                              for name, param in sorted(target.namedparams(),
+                                                        key=lambda kv: kv[0])]
+        if len(previous_params) != len(self.target_params):
+            return True
+        for param1, param2 in zip(self.target_params, previous_params):
+            if (param1[0] != param2[0]) or param1[1] != param2[1]:
+                return True
+        return False
+
+    def allocate_asgrad(self, attr):
+        for block in self.fblocks:
+            for _, param in sorted(block.link.namedparams()):
+                if getattr(param, attr, None) is None:
+                    setattr(param, attr, torch.zeros_like(param.data))
+
+    def update_kfgrads(self, fblocks):
+        # owners run the curvature stages for their blocks; with
+        # only_pic_update_weight the momentum update rides in the
+        # preconditioning epilogue of the owner
+        self.allocate_asgrad('kfgrad')
+        super(DistributedKFAC, self).update_kfgrads(self.local_fblocks)
+
+        if self.only_pic_update_weight:
+            for fblock in self.local_fblocks:
+                for param in fblock.link.params():
+                    param.update()
+            arrays = extract(fblocks, self.indices,
+                             lambda block:
+                             block.extract_for_all_gather_v('data'))
+        else:
+            # every rank applies the gathered kfgrads itself
+            arrays = extract(fblocks, self.indices,
+                             lambda block:
+                             block.extract_for_all_gather_v('kfgrad'))
+        self.comm.all_gather_v_arrays(arrays)
+
+    def _can_fuse(self, param):
+        # when kfgrads are gathered and applied by every rank, the owner must
+        # not apply its update early
+        if not self.only_pic_update_weight:
+            return False
+        return super(DistributedKFAC, self)._can_fuse(param)
+
+
+def extract(blocks, indices, extractor):
+    """``kfac.py:456-464``: arrays[rank] = [(array, triangular), ...]."""
+    arrays = []
+    for local_indices in indices:
+        local_arrays = []
+        for index in local_indices:
+            for array in extractor(blocks[index]):
+                local_arrays.append(array)
+        arrays.append(local_arrays)
+    return arrays

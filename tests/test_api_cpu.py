@@ -1,0 +1,159 @@
+"""Host-side logic of the optimizer / communicator classes (no GPU): the
+reference's interface, ownership split, wire layout and the two collectives
+over gloo with two processes."""
+
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+from torch import nn
+
+from oracle import kfac_oracle as orc
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def small_model():
+    return nn.Sequential(nn.Conv2d(3, 4, 3, 1, 1), nn.BatchNorm2d(4),
+                         nn.ReLU(), nn.Flatten(), nn.Linear(4 * 4 * 4, 5))
+
+
+def test_public_interface_and_defaults():
+    import chainerkfac_b200 as ck
+    from chainerkfac_b200.optimizers import fisher_blocks as FB
+    opt = ck.KFAC()
+    assert (opt.lr, opt.momentum, opt.cov_ema_decay, opt.damping) == \
+        (0.001, 0.9, 0.99, 0.03)
+    assert opt.stab_coeff == 16.0 and opt.acc_iters == 1
+    assert opt.pi_type == 'tracenorm'
+    opt.lr = 0.5                       # run-time mutable proxies
+    assert opt.hyperparam.lr == 0.5 and opt.lr_pre == 0.001
+    opt.setup(small_model())
+    kinds = [type(fb) for fb in opt.fblocks]
+    assert kinds == [FB.FisherBlockConvolution2D,
+                     FB.FisherBlockBatchNormalization, FB.FisherBlockLinear]
+    assert [fb.linkname for fb in opt.fblocks] == ['/0', '/1', '/4']
+    fb = opt.fblocks[0]
+    assert fb.link.ksize == 3 and fb.link.stride == (1, 1) and fb.link.pad == (1, 1)
+    assert fb.covs is None and fb.cov_emas is None and fb.invs is None
+    with pytest.raises(RuntimeError):
+        fb.update_cov_emas()           # 'covs is None', as in the reference
+    names = [n for n, _ in opt.target.namedparams()]
+    assert names == ['/0/W', '/0/b', '/1/gamma', '/1/beta', '/4/W', '/4/b']
+    rule = opt.target.__dict__['_children'][0][1].W.update_rule
+    assert rule.hyperparam.lr == 0.5   # rules see the optimizer's values
+    with pytest.raises(ValueError):
+        ck.create_communicator('mpi')
+    with pytest.raises(NotImplementedError):
+        ck.KFAC(use_cholesky=False).setup(small_model())
+
+
+def test_adjust_momentum_rule():
+    from chainerkfac_b200.optimizers.kfac import KFACUpdateRule, _base
+    hp = _base.Hyperparameter()
+    hp.lr, hp.lr_pre, hp.momentum = 0.05, 0.1, 0.9
+    assert KFACUpdateRule(hp, adjust_momentum=True).effective_momentum() == \
+        pytest.approx(0.45)
+    assert KFACUpdateRule(hp).effective_momentum() == 0.9
+
+
+class NumpyWire(object):
+    """Pack/unpack of the wire format with the oracle (CPU stand-in for the
+    library kernels, injected by these tests only)."""
+
+    def _pack(self, flat, tri, wire, select):
+        off = 0
+        for i, (a, t) in enumerate(zip(flat, tri)):
+            p = orc.pack_lower(a.numpy()) if t else a.numpy().reshape(-1)
+            if select is None or select[i]:
+                wire[off:off + p.size] = torch.from_numpy(p.copy())
+            off += p.size
+
+    def _unpack(self, flat, tri, wire, select, scale):
+        off = 0
+        for i, (a, t) in enumerate(zip(flat, tri)):
+            n = a.shape[0] * (a.shape[0] + 1) // 2 if t else a.numel()
+            if select is None or select[i]:
+                seg = wire[off:off + n].numpy() * np.float32(scale)
+                if t:
+                    a.copy_(torch.from_numpy(orc.unpack_lower(seg, a.shape[0])))
+                else:
+                    a.copy_(torch.from_numpy(seg.reshape(a.shape)))
+            off += n
+
+
+def make_arrays(rng, size):
+    shapes = [[((4, 4), True), ((5,), False)], [((3, 3), True), ((2, 6), False)],
+              [((6, 6), True)]][:size]
+    out = []
+    for local in shapes:
+        row = []
+        for shp, tri in local:
+            a = rng.standard_normal(shp).astype(np.float32)
+            if tri:
+                a = (a + a.T).astype(np.float32)
+            row.append((a, tri))
+        out.append(row)
+    return out
+
+
+def _worker(rank, size, port, tmp):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR='127.0.0.1', MASTER_PORT=str(port),
+                      RANK=str(rank), WORLD_SIZE=str(size))
+    dist.init_process_group('gloo', rank=rank, world_size=size)
+    import chainerkfac_b200 as ck
+    from chainerkfac_b200.communicators.pure_nccl_communicator import \
+        PureNcclCommunicator
+
+    class TestComm(NumpyWire, PureNcclCommunicator):
+        pass
+    comm = TestComm()
+    assert comm.rank == rank and comm.size == size
+    # every rank's local values (seeded per rank), same nested structure
+    per_rank = [make_arrays(np.random.default_rng(10 + q), size)
+                for q in range(size)]
+    mine = [[(torch.from_numpy(a.copy()), t) for a, t in loc]
+            for loc in per_rank[rank]]
+    comm.reduce_scatter_v_arrays(mine)
+    want = [[[(a.copy(), t) for a, t in loc] for loc in r] for r in per_rank]
+    orc.reduce_scatter_v_sim(want)
+    for o in range(size):
+        for (a, _), (w, _) in zip(mine[o], want[rank][o]):
+            assert np.allclose(a.numpy(), w, rtol=1e-6, atol=1e-7), (rank, o)
+    comm.all_gather_v_arrays(mine)
+    orc.all_gather_v_sim(want)
+    for o in range(size):
+        for (a, _), (w, _) in zip(mine[o], want[rank][o]):
+            assert np.allclose(a.numpy(), w, rtol=1e-6, atol=1e-7), (rank, o)
+    # ownership split and first-call broadcast of DistributedKFAC
+    torch.manual_seed(rank)            # different initial weights per rank
+    model = small_model()
+    opt = ck.DistributedKFAC(comm, lr=0.1)
+    opt.setup(model)
+    assert opt.indices == orc.split_indices(3, size)
+    assert opt.local_indices == opt.indices[rank]
+    assert comm.indices == opt.indices
+    assert opt.only_pic_update_weight is True
+    opt.update()                       # first call: parameters changed -> bcast
+    assert opt.t == 0
+    flat = torch.cat([p.data.reshape(-1) for p in opt.target.params()])
+    gathered = [torch.empty_like(flat) for _ in range(size)]
+    dist.all_gather(gathered, flat)
+    assert all(torch.equal(gathered[0], g) for g in gathered)
+    with pytest.warns(UserWarning):
+        comm.allreduce_grad()
+    open(os.path.join(tmp, 'ok%d' % rank), 'w').close()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize('size', [2, 3])
+def test_collectives_and_ownership_over_gloo(tmp_path, size):
+    port = 29500 + (os.getpid() + size) % 2000
+    mp.spawn(_worker, args=(size, port, str(tmp_path)), nprocs=size, join=True)
+    assert all(os.path.exists(str(tmp_path / ('ok%d' % r)))
+               for r in range(size))
