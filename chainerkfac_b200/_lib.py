@@ -26,6 +26,9 @@ SIGNATURES = {
     'kfac_abi_version': (I, []),
     'kfac_last_error': (ctypes.c_char_p, []),
     'kfac_launch_count': (I64, []),
+    'kfac_set_engine': (I, [I]),
+    'kfac_get_engine': (I, []),
+    'kfac_tc_status': (I, [c_int_p]),
     'kfac_factor_workspace_bytes': (SZ, [I64, I]),
     'kfac_factor_dense': (I, [VP, I64, I, I64, I, F, F, VP, VP, SZ, VP]),
     'kfac_factor_noalloc_max_bytes': (SZ, []),

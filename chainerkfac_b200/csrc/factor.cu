@@ -152,6 +152,9 @@ static int run_factor(const Operand& X, long long rows, int d, float alpha,
   KFAC_REQUIRE(out != nullptr && X.base != nullptr, "factor: null pointer");
   KFAC_REQUIRE(rows > 0 && d > 0, "factor: rows=%lld d=%d must be positive",
                rows, d);
+  if (engine() == 1)
+    return run_factor_tc(X, rows, d, alpha, beta, out, workspace,
+                         workspace_bytes, stream);
   FactorSplit s = factor_split(rows, d);
   float* partial = nullptr;
   if (s.splits > 1) {
@@ -275,6 +278,7 @@ using namespace kfac;
 
 extern "C" size_t kfac_factor_workspace_bytes(int64_t rows, int d) {
   if (rows <= 0 || d <= 0) return 0;
+  if (engine() == 1) return tc_factor_workspace_bytes(rows, d);
   FactorSplit s = factor_split(rows, d);
   if (s.splits <= 1) return 0;
   return (size_t)s.splits * s.tiles * TM * TN * sizeof(float);

@@ -251,11 +251,23 @@ struct GemmDesc {
   int tiles_m, tiles_n;
   float *kfW, *kfb, *pW, *pb, *vW, *vb;
   int dW;
-  int pad_;
+  int splits;              // tensor-core engine: CTAs along the contraction
+  long long k_per_split;
+  float* partial;          // partial tiles when splits > 1
 };
 
 int launch_grouped_gemm(const GemmDesc* descs_dev, int ndesc, int total_tiles,
                         float lr, float momentum, cudaStream_t stream);
+
+// Tensor-core engine (tc_gemm.cu): 128 x 256 tiles, tcgen05 split-TF32.
+int engine();   // 1: tensor cores (default), 0: fp32 FFMA tiles
+int tc_tiles(GemmDesc& g);
+int launch_tc_grouped(const GemmDesc* descs_dev, int ndesc, int total_tiles,
+                      float lr, float momentum, cudaStream_t stream);
+size_t tc_factor_workspace_bytes(long long rows, int d);
+int run_factor_tc(const Operand& X, long long rows, int d, float alpha,
+                  float beta, float* out, void* workspace,
+                  size_t workspace_bytes, cudaStream_t stream);
 
 // Host helper: fill tile counts of a descriptor and return its tile count.
 inline int gemm_desc_tiles(GemmDesc& g) {

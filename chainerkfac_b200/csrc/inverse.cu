@@ -232,6 +232,7 @@ struct kfac_inverse_plan {
   GemmDesc* descs_dev;
   std::vector<Launch> launches;
   long long total_elems;
+  bool use_tc;
 };
 
 static size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
@@ -272,6 +273,9 @@ extern "C" int kfac_inverse_plan_create(
                 "inverse_plan_create: workspace of %zu bytes needed, %zu given",
                 need, workspace_bytes);
 
+  // Blocks of X above the diagonal blocks are never written and are read as
+  // zeros by the wide tiles of the triangular-inverse products.
+  KFAC_CUDA(cudaMemset(workspace, 0, need));
   std::vector<MatInfo> mats(count);
   char* ws = static_cast<char*>(workspace);
   int dmax = 0;
@@ -301,6 +305,7 @@ extern "C" int kfac_inverse_plan_create(
   std::vector<GemmDesc> descs;
   std::vector<int> ids;
   std::vector<Launch> launches;
+  const bool use_tc = engine() == 1;
 
   auto begin_gemm = [&]() {
     Launch l = {1, (int)descs.size(), 0, 0, 0};
@@ -308,10 +313,12 @@ extern "C" int kfac_inverse_plan_create(
   };
   auto push_desc = [&](Launch& l, GemmDesc g) {
     g.tile_begin = l.tiles;
-    l.tiles += gemm_desc_tiles(g);
+    l.tiles += use_tc ? tc_tiles(g) : gemm_desc_tiles(g);
     g.kfW = g.kfb = g.pW = g.pb = g.vW = g.vb = nullptr;
     g.dW = 0;
-    g.pad_ = 0;
+    g.splits = 1;
+    g.k_per_split = 0;
+    g.partial = nullptr;
     descs.push_back(g);
     l.n += 1;
   };
@@ -414,6 +421,7 @@ extern "C" int kfac_inverse_plan_create(
   p->count = count;
   p->total_elems = total_elems;
   p->launches = launches;
+  p->use_tc = use_tc;
   p->mats_dev = nullptr; p->trace_dev = nullptr; p->add_dev = nullptr;
   p->info_dev = nullptr; p->ids_dev = nullptr; p->descs_dev = nullptr;
   cudaError_t e = cudaGetDevice(&p->device);
@@ -462,8 +470,11 @@ extern "C" int kfac_inverse_plan_run(kfac_inverse_plan* p, float damping,
                                               l.step, info);
       KFAC_LAUNCH_CHECK("chol_diag_kernel");
     } else {
-      int rc = launch_grouped_gemm(p->descs_dev + l.off, l.n, l.tiles, 0.f, 0.f,
-                                   st);
+      int rc = p->use_tc
+                   ? launch_tc_grouped(p->descs_dev + l.off, l.n, l.tiles, 0.f,
+                                       0.f, st)
+                   : launch_grouped_gemm(p->descs_dev + l.off, l.n, l.tiles,
+                                         0.f, 0.f, st);
       if (rc != KFAC_OK) return rc;
     }
   }

@@ -61,6 +61,7 @@ extern "C" int kfac_precondition(
 
   std::vector<GemmDesc> descs(2 * count);
   int tiles1 = 0, tiles2 = 0;
+  const bool use_tc = engine() == 1;
   for (int i = 0; i < count; ++i) {
     const int dg = dG[i], dw = dW[i], da = dw + hb[i];
     float* T = reinterpret_cast<float*>(ws);
@@ -74,7 +75,8 @@ extern "C" int kfac_precondition(
     g.C = T; g.ldc = da; g.M = dg; g.N = da; g.K = dg;
     g.alpha = 1.f; g.beta = 0.f; g.flags = 0;
     g.tile_begin = tiles1;
-    tiles1 += gemm_desc_tiles(g);
+    g.splits = 1;
+    tiles1 += use_tc ? tc_tiles(g) : gemm_desc_tiles(g);
     // kf = T * A_inv, split and (optionally) applied
     GemmDesc& h = descs[count + i];
     h = GemmDesc();
@@ -91,11 +93,18 @@ extern "C" int kfac_precondition(
     h.vb = (fused && hb[i]) ? mom_b[i] : nullptr;
     h.dW = dw;
     h.tile_begin = tiles2;
-    tiles2 += gemm_desc_tiles(h);
+    h.splits = 1;
+    tiles2 += use_tc ? tc_tiles(h) : gemm_desc_tiles(h);
   }
   KFAC_CUDA(cudaMemcpyAsync(descs_dev, descs.data(),
                             descs.size() * sizeof(GemmDesc),
                             cudaMemcpyHostToDevice, st));
+  if (use_tc) {
+    int rc = launch_tc_grouped(descs_dev, count, tiles1, 0.f, 0.f, st);
+    if (rc != KFAC_OK) return rc;
+    return launch_tc_grouped(descs_dev + count, count, tiles2, lr, momentum,
+                             st);
+  }
   int rc = launch_grouped_gemm(descs_dev, count, tiles1, 0.f, 0.f, st);
   if (rc != KFAC_OK) return rc;
   return launch_grouped_gemm(descs_dev + count, count, tiles2, lr, momentum, st);

@@ -1,0 +1,704 @@
+// Tensor-core tile engine for sm_100a: tcgen05.mma (kind::tf32) with fp32
+// accumulators in tensor memory, fp32 operands split into two TF32 terms
+// (x = hi + lo, C += hi*hi + hi*lo + lo*hi) so that results keep fp32-level
+// accuracy (a single TF32 pass misses the 1e-4 bound on large factors).
+//
+// One CTA (8 producer/epilogue warps + 1 MMA warp) owns a 128 x N tile,
+// N <= 256.  Producer warps gather the operands from global memory (strided
+// views, transposing views or im2col patches of an NCHW tensor), split them
+// and write the K-major, 128-byte-swizzled shared-memory layout that the MMA
+// descriptors expect; two stages of 32 k each are kept in flight through
+// mbarriers.  The epilogue moves the accumulator tile TMEM -> registers ->
+// shared memory and writes rows (and, for symmetric outputs, mirrored columns)
+// with coalesced stores.  Every barrier wait is bounded; a wait that runs out
+// raises a status word instead of hanging.
+#include <mutex>
+
+#include "gemm_simt.cuh"
+
+namespace kfac {
+
+constexpr int TC_BM = 128;
+constexpr int TC_BN = 256;
+constexpr int TC_BK = 32;
+constexpr int TC_PRODUCERS = 256;
+constexpr int TC_THREADS = TC_PRODUCERS + 32;
+constexpr int TC_A_BYTES = TC_BM * TC_BK * 4;   // 16 KB
+constexpr int TC_B_BYTES = TC_BN * TC_BK * 4;   // 32 KB
+constexpr int TC_STAGE_BYTES = 2 * TC_A_BYTES + 2 * TC_B_BYTES;  // 96 KB
+constexpr int TC_STAGES = 2;
+constexpr int TC_EPI_PITCH = TC_BN + 1;         // floats
+constexpr int TC_SMEM_BYTES = TC_STAGES * TC_STAGE_BYTES + 8192 + 1024;
+constexpr unsigned TC_SPIN_LIMIT = 1u << 22;
+// Two accumulators per tile: columns [0, 256) collect hi*hi, columns
+// [256, 512) the two small cross terms.  The tensor core truncates when it
+// adds into an accumulator, so keeping the (2^-11 smaller) cross terms apart
+// cuts the accumulations that touch the large sum to a third.
+constexpr int TC_TMEM_COLS = 2 * TC_BN;
+
+static __device__ int g_tc_status = 0;
+
+struct TcControl {
+  unsigned long long full[TC_STAGES];
+  unsigned long long empty[TC_STAGES];
+  unsigned long long accum;
+  unsigned tmem_base;
+  volatile int abort_flag;
+  int coff_a[TC_BM];
+  int kykx_a[TC_BM];
+  int coff_b[TC_BN];
+  int kykx_b[TC_BN];
+  GemmDesc desc;
+};
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) {
+  return (unsigned)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)),
+               "r"(count));
+}
+
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+
+// Bounded wait on a phase parity; false if the limit ran out or the CTA is
+// already aborting.
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar,
+                                          unsigned parity,
+                                          volatile int* abort_flag) {
+  const unsigned addr = smem_u32(bar);
+  for (unsigned i = 0; i < TC_SPIN_LIMIT; ++i) {
+    unsigned done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if (*abort_flag) return false;
+  }
+  *abort_flag = 1;
+  atomicExch(&g_tc_status, 1);
+  return false;
+}
+
+__device__ __forceinline__ unsigned long long tc_smem_desc(unsigned addr) {
+  // K-major, 128-byte swizzle: 8-row groups 1024 bytes apart.
+  unsigned long long d = 0;
+  d |= (unsigned long long)((addr & 0x3FFFF) >> 4);         // start address
+  d |= (unsigned long long)1 << 16;                         // LBO (unused)
+  d |= (unsigned long long)(1024 >> 4) << 32;               // SBO
+  d |= (unsigned long long)1 << 46;                         // descriptor version
+  d |= (unsigned long long)2 << 61;                         // SWIZZLE_128B
+  return d;
+}
+
+__device__ __forceinline__ unsigned tc_instr_desc(int n) {
+  // D = f32, A = B = tf32, both K-major, M = 128, N = n
+  return (1u << 4) | (2u << 7) | (2u << 10) | ((unsigned)(n >> 3) << 17) |
+         ((unsigned)(TC_BM >> 4) << 24);
+}
+
+__device__ __forceinline__ void tc_mma(unsigned tmem_d, unsigned long long da,
+                                       unsigned long long db, unsigned idesc,
+                                       unsigned accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_commit(unsigned long long* bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+      ::"r"(smem_u32(bar))
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_ld16(unsigned taddr, float v[16]) {
+  unsigned r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]),
+        "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+        "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Byte offset of element (row, k) inside a K-major SW128 tile (k < 32).
+__device__ __forceinline__ int sw128_chunk_off(int row, int chunk) {
+  return row * 128 + ((chunk ^ (row & 7)) << 4);
+}
+
+__device__ __forceinline__ void store_split(unsigned char* hi_tile,
+                                            unsigned char* lo_tile, int row,
+                                            int chunk, float4 x) {
+  float4 h, l;
+  h.x = __uint_as_float(__float_as_uint(x.x) & 0xFFFFE000u);
+  h.y = __uint_as_float(__float_as_uint(x.y) & 0xFFFFE000u);
+  h.z = __uint_as_float(__float_as_uint(x.z) & 0xFFFFE000u);
+  h.w = __uint_as_float(__float_as_uint(x.w) & 0xFFFFE000u);
+  l.x = x.x - h.x; l.y = x.y - h.y; l.z = x.z - h.z; l.w = x.w - h.w;
+  const int off = sw128_chunk_off(row, chunk);
+  *reinterpret_cast<float4*>(hi_tile + off) = h;
+  *reinterpret_cast<float4*>(lo_tile + off) = l;
+}
+
+// im2col column tables for `rows` columns of a tile starting at column c0.
+__device__ __forceinline__ void tc_im2col_tables(const Operand& op, int c0,
+                                                 int rows, int* coff, int* kykx,
+                                                 int tid) {
+  for (int i = tid; i < rows; i += TC_PRODUCERS) {
+    int c = c0 + i;
+    int off = 0, info = -1;
+    if (c < op.ncols) {
+      int kk = op.ks * op.ks;
+      int ch = c / kk;
+      int r = c - ch * kk;
+      int ky = r / op.ks;
+      int kx = r - ky * op.ks;
+      off = ch * op.H * op.W + ky * op.W + kx;
+      info = (ky << 16) | kx;
+    } else if (c == op.extra_idx) {
+      info = -2;
+    }
+    coff[i] = off;
+    kykx[i] = info;
+  }
+}
+
+// Fill `rows` (multiple of 4... any) rows of one operand tile for the k-block
+// [k0, k0 + 32): gather, split into hi/lo, store swizzled.  Rows are tile-local
+// columns c0 + row of the operand; elements with k >= kend or column beyond
+// the operand are zero.
+__device__ __forceinline__ void tc_fill_tile(const Operand& op, int c0,
+                                             int rows, long long k0,
+                                             long long kend,
+                                             unsigned char* hi_tile,
+                                             unsigned char* lo_tile,
+                                             const int* coff, const int* kykx,
+                                             int warp, int lane) {
+  const int total_cols = op.ncols + (op.extra_idx >= 0 ? 1 : 0);
+  if (op.mode == 1) {
+    // im2col: lane = 8 * (row % 4) + chunk; this thread's 4 k are fixed for
+    // the whole k-block, so the pixel decomposition is done once.
+    const int chunk = lane & 7;
+    const int how = op.Ho * op.Wo;
+    long long base[4];
+    int iy0[4], ix0[4];
+    bool kv[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      long long k = k0 + chunk * 4 + j;
+      kv[j] = k < kend;
+      long long n = k / how;
+      int rem = (int)(k - n * how);
+      int oy = rem / op.Wo;
+      int ox = rem - oy * op.Wo;
+      iy0[j] = oy * op.st - op.pd;
+      ix0[j] = ox * op.st - op.pd;
+      base[j] = n * op.C * op.H * op.W + (long long)iy0[j] * op.W + ix0[j];
+    }
+    for (int r0 = warp * 4; r0 < rows; r0 += 32) {
+      const int row = r0 + (lane >> 3);
+      float v[4] = {0.f, 0.f, 0.f, 0.f};
+      if (row < rows) {
+        const int info = kykx[row];
+        if (info >= 0) {
+          const int ky = info >> 16, kx = info & 0xffff, co = coff[row];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            int iy = iy0[j] + ky, ix = ix0[j] + kx;
+            if (kv[j] && (unsigned)iy < (unsigned)op.H &&
+                (unsigned)ix < (unsigned)op.W)
+              v[j] = op.base[base[j] + co];
+          }
+        } else if (info == -2) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) v[j] = kv[j] ? 1.f : 0.f;
+        }
+        store_split(hi_tile, lo_tile, row, chunk,
+                    make_float4(v[0], v[1], v[2], v[3]));
+      }
+    }
+    return;
+  }
+  if (op.kfast) {
+    // contiguous along k: lane = 8 * (row % 4) + chunk, one 16-byte chunk each
+    const int chunk = lane & 7;
+    const long long k = k0 + chunk * 4;
+    long long roff[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) roff[j] = operand_rowoff(op, k + j);
+    const bool contiguous = (roff[3] - roff[0]) == 3 && (k + 3) < kend;
+    for (int r0 = warp * 4; r0 < rows; r0 += 32) {
+      const int row = r0 + (lane >> 3);
+      if (row >= rows) continue;
+      const int c = c0 + row;
+      float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (c < op.ncols) {
+        const float* p = op.base + (long long)c * op.s_col;
+        if (contiguous && ((reinterpret_cast<uintptr_t>(p + roff[0]) & 15) == 0)) {
+          x = *reinterpret_cast<const float4*>(p + roff[0]);
+        } else {
+          if (k + 0 < kend) x.x = p[roff[0]];
+          if (k + 1 < kend) x.y = p[roff[1]];
+          if (k + 2 < kend) x.z = p[roff[2]];
+          if (k + 3 < kend) x.w = p[roff[3]];
+        }
+      } else if (c == op.extra_idx) {
+        if (k + 0 < kend) x.x = op.extra ? op.extra[k + 0] : 1.f;
+        if (k + 1 < kend) x.y = op.extra ? op.extra[k + 1] : 1.f;
+        if (k + 2 < kend) x.z = op.extra ? op.extra[k + 2] : 1.f;
+        if (k + 3 < kend) x.w = op.extra ? op.extra[k + 3] : 1.f;
+      }
+      store_split(hi_tile, lo_tile, row, chunk, x);
+    }
+    return;
+  }
+  // contiguous along the column index: lanes walk 32 consecutive columns for
+  // a fixed k (coalesced), each thread assembles one 16-byte chunk of 4 k.
+  const int groups = (rows + 31) >> 5;
+  for (int task = warp; task < groups * 8; task += 8) {
+    const int g = task >> 3, chunk = task & 7;
+    const int row = g * 32 + lane;
+    if (row >= rows) continue;
+    const int c = c0 + row;
+    const long long k = k0 + chunk * 4;
+    float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (c < op.ncols) {
+      const float* p = op.base + (long long)c * op.s_col;
+      if (k + 0 < kend) x.x = p[operand_rowoff(op, k + 0)];
+      if (k + 1 < kend) x.y = p[operand_rowoff(op, k + 1)];
+      if (k + 2 < kend) x.z = p[operand_rowoff(op, k + 2)];
+      if (k + 3 < kend) x.w = p[operand_rowoff(op, k + 3)];
+    } else if (c == op.extra_idx && c < total_cols) {
+      if (k + 0 < kend) x.x = op.extra ? op.extra[k + 0] : 1.f;
+      if (k + 1 < kend) x.y = op.extra ? op.extra[k + 1] : 1.f;
+      if (k + 2 < kend) x.z = op.extra ? op.extra[k + 2] : 1.f;
+      if (k + 3 < kend) x.w = op.extra ? op.extra[k + 3] : 1.f;
+    }
+    store_split(hi_tile, lo_tile, row, chunk, x);
+  }
+}
+
+// Lower-triangular enumeration with 128-row x 256-column tiles: tile (bi, bj)
+// exists iff 2 * bj <= bi.  Tiles before row bi: a(a+1) for bi = 2a, (a+1)^2
+// for bi = 2a + 1.
+__device__ __forceinline__ void tc_tri_tile(int t, int& bi, int& bj) {
+  int a = (int)sqrtf((float)t);
+  while ((a + 1) * (a + 1) <= t) ++a;
+  while (a * a > t) --a;
+  if (t < a * (a + 1)) {
+    bi = 2 * a - 1;
+    bj = t - a * a;
+  } else {
+    bi = 2 * a;
+    bj = t - a * (a + 1);
+  }
+}
+
+__global__ void __launch_bounds__(TC_THREADS, 1)
+tc_gemm_kernel(const GemmDesc* __restrict__ descs, int ndesc,
+               const __grid_constant__ GemmDesc inline_desc, float lr,
+               float momentum) {
+  extern __shared__ unsigned char tc_smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
+  TcControl* ctl =
+      reinterpret_cast<TcControl*>(smem + TC_STAGES * TC_STAGE_BYTES);
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
+  const int tile = blockIdx.x;
+
+  // ---- locate the problem and copy its descriptor to shared memory
+  {
+    const GemmDesc* src = &inline_desc;
+    if (descs != nullptr) {
+      int lo = 0, hi = ndesc - 1;
+      while (lo < hi) {
+        int mid = (lo + hi + 1) >> 1;
+        if (descs[mid].tile_begin <= tile) lo = mid; else hi = mid - 1;
+      }
+      src = descs + lo;
+    }
+    const int* s = reinterpret_cast<const int*>(src);
+    int* d = reinterpret_cast<int*>(&ctl->desc);
+    for (int i = tid; i < (int)(sizeof(GemmDesc) / sizeof(int)); i += TC_THREADS)
+      d[i] = s[i];
+  }
+  if (tid == 0) {
+    for (int s = 0; s < TC_STAGES; ++s) {
+      mbar_init(&ctl->full[s], TC_PRODUCERS / 32);
+      mbar_init(&ctl->empty[s], 1);
+    }
+    mbar_init(&ctl->accum, 1);
+    ctl->abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == TC_PRODUCERS / 32) {
+    asm volatile(
+        "tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+        ::"r"(smem_u32(&ctl->tmem_base)), "r"(TC_TMEM_COLS)
+        : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;"
+                 ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+
+  const GemmDesc& g = ctl->desc;
+  const unsigned tmem = ctl->tmem_base;
+  const int lt = tile - g.tile_begin;
+  int bi, bj;
+  if (g.flags & G_LOWER) {
+    tc_tri_tile(lt, bi, bj);
+  } else {
+    bi = lt / g.tiles_n;
+    bj = lt - bi * g.tiles_n;
+  }
+  const int m0 = bi * TC_BM, n0 = bj * TC_BN;
+  int n_valid = min(TC_BN, g.N - n0);
+  if (g.flags & G_LOWER) n_valid = min(n_valid, m0 + TC_BM - n0);
+  const int n_inst = (n_valid + 15) & ~15;
+  const int m_valid = min(TC_BM, g.M - m0);
+
+  long long kbeg = 0, kend = g.K;
+  if (g.splits > 1) {
+    kbeg = (long long)blockIdx.y * g.k_per_split;
+    kend = min(g.K, kbeg + g.k_per_split);
+  }
+  if (g.flags & G_KBEG_N0) kbeg = max(kbeg, (long long)n0);
+  if (g.flags & G_KBEG_M0) kbeg = max(kbeg, (long long)m0);
+  if (g.flags & G_KEND_M0) kend = min(kend, (long long)(m0 + TC_BM));
+  const int nkb = kend > kbeg ? (int)((kend - kbeg + TC_BK - 1) / TC_BK) : 0;
+
+  if (warp < TC_PRODUCERS / 32) {
+    // ===================== producers =====================
+    if (g.A.mode == 1) tc_im2col_tables(g.A, m0, TC_BM, ctl->coff_a, ctl->kykx_a, tid);
+    if (g.B.mode == 1) tc_im2col_tables(g.B, n0, n_inst, ctl->coff_b, ctl->kykx_b, tid);
+    if (g.A.mode == 1 || g.B.mode == 1)
+      asm volatile("bar.sync 1, %0;" ::"r"(TC_PRODUCERS) : "memory");
+    for (int kb = 0; kb < nkb; ++kb) {
+      const int s = kb % TC_STAGES;
+      if (kb >= TC_STAGES) {
+        if (!mbar_wait(&ctl->empty[s], ((kb / TC_STAGES) - 1) & 1,
+                       &ctl->abort_flag))
+          break;
+      }
+      unsigned char* st = smem + s * TC_STAGE_BYTES;
+      const long long k0 = kbeg + (long long)kb * TC_BK;
+      tc_fill_tile(g.A, m0, TC_BM, k0, kend, st, st + TC_A_BYTES, ctl->coff_a,
+                   ctl->kykx_a, warp, lane);
+      tc_fill_tile(g.B, n0, n_inst, k0, kend, st + 2 * TC_A_BYTES,
+                   st + 2 * TC_A_BYTES + TC_B_BYTES, ctl->coff_b, ctl->kykx_b,
+                   warp, lane);
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ctl->full[s]);
+    }
+  } else {
+    // ===================== MMA issuer =====================
+    if (lane == 0) {
+      const unsigned idesc = tc_instr_desc(n_inst);
+      for (int kb = 0; kb < nkb; ++kb) {
+        const int s = kb % TC_STAGES;
+        if (!mbar_wait(&ctl->full[s], (kb / TC_STAGES) & 1, &ctl->abort_flag))
+          break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const unsigned sa = smem_u32(smem + s * TC_STAGE_BYTES);
+        const unsigned long long a_hi = tc_smem_desc(sa);
+        const unsigned long long a_lo = tc_smem_desc(sa + TC_A_BYTES);
+        const unsigned long long b_hi = tc_smem_desc(sa + 2 * TC_A_BYTES);
+        const unsigned long long b_lo =
+            tc_smem_desc(sa + 2 * TC_A_BYTES + TC_B_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < TC_BK / 8; ++kk) {
+          const unsigned long long adv = (unsigned long long)(kk * 32 >> 4);
+          tc_mma(tmem + TC_BN, a_lo + adv, b_hi + adv, idesc, (kb | kk) != 0);
+          tc_mma(tmem + TC_BN, a_hi + adv, b_lo + adv, idesc, 1);
+          tc_mma(tmem, a_hi + adv, b_hi + adv, idesc, (kb | kk) != 0);
+        }
+        tc_commit(&ctl->empty[s]);
+      }
+      tc_commit(&ctl->accum);
+    }
+    __syncwarp();
+  }
+
+  // ===================== epilogue =====================
+  float* stage = reinterpret_cast<float*>(smem);
+  bool ok = true;
+  if (warp < TC_PRODUCERS / 32) {
+    if (nkb > 0) {
+      ok = mbar_wait(&ctl->accum, 0, &ctl->abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    }
+    const int q = warp & 3, h = warp >> 2;
+    const int row = q * 32 + lane;
+    for (int c0 = h * 128; c0 < min(n_inst, h * 128 + 128); c0 += 16) {
+      float v[16];
+      if (nkb > 0 && ok) {
+        float w[16];
+        tc_ld16(tmem + ((unsigned)(q * 32) << 16) + (unsigned)c0, v);
+        tc_ld16(tmem + ((unsigned)(q * 32) << 16) + (unsigned)(TC_BN + c0), w);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] += w[i];
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = 0.f;
+      }
+#pragma unroll
+      for (int i = 0; i < 16; ++i) stage[row * TC_EPI_PITCH + c0 + i] = v[i];
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == TC_PRODUCERS / 32) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
+                 ::"r"(tmem), "r"(TC_TMEM_COLS)
+                 : "memory");
+  }
+  if (warp >= TC_PRODUCERS / 32 || ctl->abort_flag) return;
+
+  if (g.splits > 1) {
+    float* p = g.partial +
+               ((long long)blockIdx.y * gridDim.x + tile) * (TC_BM * TC_BN);
+    for (int r = warp; r < TC_BM; r += 8)
+      for (int c = lane; c < n_inst; c += 32)
+        p[r * TC_BN + c] = stage[r * TC_EPI_PITCH + c];
+    return;
+  }
+  if (g.flags & G_PRECOND) {
+    const int dW = g.dW;
+    for (int r = warp; r < m_valid; r += 8) {
+      const int gr = m0 + r;
+      for (int c = lane; c < n_valid; c += 32) {
+        const int gc = n0 + c;
+        const float kf = stage[r * TC_EPI_PITCH + c];
+        float *okf, *op, *ov;
+        long long idx;
+        if (gc < dW) {
+          idx = (long long)gr * dW + gc;
+          okf = g.kfW; op = g.pW; ov = g.vW;
+        } else {
+          idx = gr;
+          okf = g.kfb; op = g.pb; ov = g.vb;
+        }
+        if (okf) okf[idx] = kf;
+        if (op) {
+          float nv = momentum * ov[idx] - lr * kf;
+          ov[idx] = nv;
+          op[idx] += nv;
+        }
+      }
+    }
+    return;
+  }
+  const float alpha = g.alpha, beta = g.beta;
+  const bool lower = (g.flags & G_LOWER) != 0;
+  const bool mirror = (g.flags & G_MIRROR) != 0;
+  // rows: C[gr][gc] = alpha * acc + beta * C[gr][gc]; the final value is kept
+  // in the staging tile for the mirrored pass
+  for (int r = warp; r < m_valid; r += 8) {
+    const int gr = m0 + r;
+    for (int c = lane; c < n_valid; c += 32) {
+      const int gc = n0 + c;
+      if (lower && gc > gr) continue;
+      float* p = g.C + (long long)gr * g.ldc + gc;
+      float v = alpha * stage[r * TC_EPI_PITCH + c];
+      if (beta != 0.f) v += beta * (*p);
+      *p = v;
+      if (mirror) stage[r * TC_EPI_PITCH + c] = v;
+    }
+  }
+  if (mirror) {
+    asm volatile("bar.sync 1, %0;" ::"r"(TC_PRODUCERS) : "memory");
+    for (int c = warp; c < n_valid; c += 8) {
+      const int gc = n0 + c;
+      for (int r = lane; r < m_valid; r += 32) {
+        const int gr = m0 + r;
+        if (gc < gr) g.C[(long long)gc * g.ldc + gr] = stage[r * TC_EPI_PITCH + c];
+      }
+    }
+  }
+}
+
+// Sum split partial tiles (ascending split order), then scale / blend / store
+// the lower part and its mirror.
+__global__ void __launch_bounds__(256)
+tc_reduce_kernel(const float* __restrict__ partial, int tiles, int splits,
+                 int d, float alpha, float beta, float* __restrict__ out) {
+  int bi, bj;
+  tc_tri_tile(blockIdx.x, bi, bj);
+  const int m0 = bi * TC_BM, n0 = bj * TC_BN;
+  const int c = threadIdx.x;
+  const int gc = n0 + c;
+  for (int rr = 0; rr < 8; ++rr) {
+    const int r = blockIdx.y * 8 + rr;
+    const int gr = m0 + r;
+    if (gr >= d || gc >= d || gc > gr) continue;
+    const float* p = partial + (long long)blockIdx.x * (TC_BM * TC_BN) +
+                     r * TC_BN + c;
+    float s = 0.f;
+    for (int sp = 0; sp < splits; ++sp)
+      s += p[(long long)sp * tiles * (TC_BM * TC_BN)];
+    float* q = out + (long long)gr * d + gc;
+    float v = alpha * s;
+    if (beta != 0.f) v += beta * (*q);
+    *q = v;
+    if (gc < gr) out[(long long)gc * d + gr] = v;
+  }
+}
+
+// ------------------------------------------------------------------ host side
+static int g_engine = 1;
+
+int tc_tiles(GemmDesc& g) {
+  g.tiles_m = (g.M + TC_BM - 1) / TC_BM;
+  g.tiles_n = (g.N + TC_BN - 1) / TC_BN;
+  if (g.flags & G_LOWER) {
+    int nt = g.tiles_m, a = nt / 2;
+    return (nt & 1) ? (a + 1) * (a + 1) : a * (a + 1);
+  }
+  return g.tiles_m * g.tiles_n;
+}
+
+static int tc_prepare() {
+  static std::mutex mu;
+  static bool done[64] = {false};
+  int dev = 0;
+  KFAC_CUDA(cudaGetDevice(&dev));
+  KFAC_REQUIRE(dev >= 0 && dev < 64, "device index %d unsupported", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (!done[dev]) {
+    KFAC_CUDA(cudaFuncSetAttribute(tc_gemm_kernel,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   TC_SMEM_BYTES));
+    done[dev] = true;
+  }
+  return KFAC_OK;
+}
+
+int launch_tc_grouped(const GemmDesc* descs_dev, int ndesc, int total_tiles,
+                      float lr, float momentum, cudaStream_t stream) {
+  if (ndesc <= 0 || total_tiles <= 0) return KFAC_OK;
+  int rc = tc_prepare();
+  if (rc != KFAC_OK) return rc;
+  GemmDesc dummy = {};
+  tc_gemm_kernel<<<total_tiles, TC_THREADS, TC_SMEM_BYTES, stream>>>(
+      descs_dev, ndesc, dummy, lr, momentum);
+  KFAC_LAUNCH_CHECK("tc_gemm_kernel");
+  return KFAC_OK;
+}
+
+struct TcFactorSplit {
+  int tiles, splits;
+  long long k_per_split;
+};
+
+static TcFactorSplit tc_factor_split(long long rows, int d) {
+  TcFactorSplit s;
+  GemmDesc g = {};
+  g.M = g.N = d;
+  g.flags = G_LOWER;
+  s.tiles = tc_tiles(g);
+  long long target = 2LL * sm_count();
+  long long by_tiles = (target + s.tiles - 1) / s.tiles;
+  long long by_rows = (rows + 2047) / 2048;  // >= 64 k-blocks per CTA
+  long long sp = by_tiles < by_rows ? by_tiles : by_rows;
+  if (s.tiles >= sm_count()) sp = 1;
+  if (sp < 1) sp = 1;
+  long long kps = (rows + sp - 1) / sp;
+  kps = (kps + TC_BK - 1) / TC_BK * TC_BK;
+  s.splits = (int)((rows + kps - 1) / kps);
+  if (s.splits < 1) s.splits = 1;
+  s.k_per_split = kps;
+  return s;
+}
+
+size_t tc_factor_workspace_bytes(long long rows, int d) {
+  TcFactorSplit s = tc_factor_split(rows, d);
+  if (s.splits <= 1) return 0;
+  return (size_t)s.splits * s.tiles * TC_BM * TC_BN * sizeof(float);
+}
+
+int run_factor_tc(const Operand& X, long long rows, int d, float alpha,
+                  float beta, float* out, void* workspace,
+                  size_t workspace_bytes, cudaStream_t stream) {
+  int rc = tc_prepare();
+  if (rc != KFAC_OK) return rc;
+  TcFactorSplit s = tc_factor_split(rows, d);
+  GemmDesc g = {};
+  g.A = X;
+  g.B = X;
+  g.C = out;
+  g.ldc = d;
+  g.K = rows;
+  g.M = d;
+  g.N = d;
+  g.alpha = alpha;
+  g.beta = beta;
+  g.flags = G_LOWER | G_MIRROR;
+  g.tile_begin = 0;
+  tc_tiles(g);
+  g.splits = s.splits;
+  g.k_per_split = s.k_per_split;
+  g.partial = nullptr;
+  if (s.splits > 1) {
+    size_t need = (size_t)s.splits * s.tiles * TC_BM * TC_BN * sizeof(float);
+    if (workspace == nullptr || workspace_bytes < need)
+      return fail(KFAC_ERR_WORKSPACE,
+                  "factor: workspace of %zu bytes needed, %zu given", need,
+                  workspace_bytes);
+    g.partial = static_cast<float*>(workspace);
+  }
+  dim3 grid(s.tiles, s.splits);
+  tc_gemm_kernel<<<grid, TC_THREADS, TC_SMEM_BYTES, stream>>>(nullptr, 1, g,
+                                                              0.f, 0.f);
+  KFAC_LAUNCH_CHECK("tc_gemm_kernel");
+  if (s.splits > 1) {
+    dim3 rgrid(s.tiles, TC_BM / 8);
+    tc_reduce_kernel<<<rgrid, 256, 0, stream>>>(g.partial, s.tiles, s.splits, d,
+                                                alpha, beta, out);
+    KFAC_LAUNCH_CHECK("tc_reduce_kernel");
+  }
+  return KFAC_OK;
+}
+
+int engine() { return g_engine; }
+
+}  // namespace kfac
+
+extern "C" int kfac_set_engine(int engine) {
+  if (engine != 0 && engine != 1)
+    return kfac::fail(KFAC_ERR_INVALID, "set_engine: engine must be 0 or 1");
+  kfac::g_engine = engine;
+  return KFAC_OK;
+}
+
+extern "C" int kfac_get_engine(void) { return kfac::g_engine; }
+
+extern "C" int kfac_tc_status(int* status_out) {
+  KFAC_REQUIRE(status_out != nullptr, "tc_status: null pointer");
+  KFAC_CUDA(cudaDeviceSynchronize());
+  int v = 0;
+  KFAC_CUDA(cudaMemcpyFromSymbol(&v, kfac::g_tc_status, sizeof(int)));
+  *status_out = v;
+  return KFAC_OK;
+}

@@ -35,6 +35,17 @@ const char* kfac_last_error(void);
 /* Number of kernels this library has launched in this process so far. */
 int64_t kfac_launch_count(void);
 
+/* Arithmetic engine of the factor / inverse / precondition products.
+ * 1 (default): tcgen05 tensor cores, fp32 operands split into two TF32 terms
+ * (three MMAs per product, fp32-level accuracy).  0: fp32 FFMA tiles.  The
+ * choice is read when a call is made or a plan is created. */
+int kfac_set_engine(int engine);
+int kfac_get_engine(void);
+/* Synchronises the device and returns in *status_out the tensor-core engine's
+ * status word: 0, or 1 if a bounded barrier wait inside a kernel ran out (the
+ * results of that launch are then invalid). */
+int kfac_tc_status(int* status_out);
+
 /* ------------------------------------------------------------------ factors
  * out(d x d) = alpha * X^T X + beta * out, X a (rows x d) matrix that is never
  * materialised.  Only one triangle of tiles is computed; both triangles of

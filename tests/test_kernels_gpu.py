@@ -24,6 +24,22 @@ def ops():
     return _ops
 
 
+@pytest.fixture(autouse=True, params=[1, 0], ids=['tcgen05', 'fp32'])
+def engine(request):
+    """Every test runs on both arithmetic engines: tcgen05 split-TF32 tensor
+    cores (the default) and the fp32 FFMA tiles.  After a tensor-core run the
+    engine's status word must be clean (no barrier wait ran out)."""
+    import ctypes
+    from chainerkfac_b200 import _lib
+    lib = _lib.load()
+    _lib.check(lib.kfac_set_engine(request.param), 'kfac_set_engine')
+    yield request.param
+    status = ctypes.c_int(-1)
+    _lib.check(lib.kfac_tc_status(ctypes.byref(status)), 'kfac_tc_status')
+    _lib.check(lib.kfac_set_engine(1), 'kfac_set_engine')
+    assert status.value == 0
+
+
 def dev(a):
     return torch.from_numpy(np.ascontiguousarray(a)).cuda()
 
