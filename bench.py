@@ -456,6 +456,70 @@ def run_reference(args):
     print(json.dumps(line))
 
 
+MICRO_CASES = {
+    # name: (kind, parameters) -- single-kernel cases for profiling
+    'conv_grad_c256_hw56': ('conv_grad', dict(n=32, c=256, hw=56)),
+    'conv_grad_c64_hw56': ('conv_grad', dict(n=32, c=64, hw=56)),
+    'conv3x3_c64_hw56': ('conv_input', dict(n=32, c=64, hw=56, k=3, s=1, p=1)),
+    'conv3x3_c256_hw14': ('conv_input', dict(n=32, c=256, hw=14, k=3, s=1, p=1)),
+    'conv3x3_c512_hw7': ('conv_input', dict(n=32, c=512, hw=7, k=3, s=1, p=1)),
+    'conv7x7_c3_hw224': ('conv_input', dict(n=32, c=3, hw=224, k=7, s=2, p=3)),
+    'dense_rows8192_d4608': ('dense', dict(rows=8192, d=4608)),
+    'inverse_d2304': ('inverse', dict(dims=[2304])),
+    'inverse_d4608': ('inverse', dict(dims=[4608])),
+}
+
+
+def run_micro(args):
+    """Time one small case (CUDA events); the command line used for the ncu
+    captures summarised under profiles/."""
+    import torch
+    from chainerkfac_b200 import ops
+    kind, p = MICRO_CASES[args.micro]
+    torch.manual_seed(0)
+    if kind == 'conv_grad':
+        x = torch.randn(p['n'], p['c'], p['hw'], p['hw'], device='cuda')
+        out = torch.empty(p['c'], p['c'], device='cuda')
+        fn = lambda: ops.factor_conv_grad(x, alpha=1.0, out=out)
+        flops = p['n'] * p['hw'] ** 2 * p['c'] * (p['c'] + 1)
+    elif kind == 'conv_input':
+        x = torch.randn(p['n'], p['c'], p['hw'], p['hw'], device='cuda')
+        d = p['c'] * p['k'] ** 2
+        out = torch.empty(d, d, device='cuda')
+        fn = lambda: ops.factor_conv_input(x, p['k'], p['s'], p['p'], False,
+                                           alpha=1.0, out=out)
+        ho = (p['hw'] + 2 * p['p'] - p['k']) // p['s'] + 1
+        flops = p['n'] * ho * ho * d * (d + 1)
+    elif kind == 'dense':
+        x = torch.randn(p['rows'], p['d'], device='cuda')
+        out = torch.empty(p['d'], p['d'], device='cuda')
+        fn = lambda: ops.factor_dense(x, False, alpha=1.0, out=out)
+        flops = p['rows'] * p['d'] * (p['d'] + 1)
+    else:
+        F = []
+        for d in p['dims']:
+            X = torch.randn(2 * d, d, device='cuda')
+            F.append((X.T @ X) / (2 * d) + 1e-3 * torch.eye(d, device='cuda'))
+        inv = [torch.empty_like(f) for f in F]
+        plan = ops.InversePlan(F, inv, [-1] * len(F), [2] * len(F),
+                               scale=[0.0] * len(F))
+        fn = lambda: plan.run(0.0)
+        flops = sum(d ** 3 for d in p['dims'])
+    for _ in range(max(args.warmup, 1)):
+        fn()
+    torch.cuda.synchronize()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    print(json.dumps({'micro': args.micro, 'ms': ms,
+                      'tflops': flops / (ms * 1e-3) / 1e12}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('--gpus', type=int, default=1)
@@ -464,8 +528,12 @@ def main():
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--no-e2e', action='store_true')
     ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--micro', choices=sorted(MICRO_CASES), default=None,
+                    help='time one single-kernel case instead of the step')
     args = ap.parse_args()
-    if args.impl == 'reference':
+    if args.micro:
+        run_micro(args)
+    elif args.impl == 'reference':
         run_reference(args)
     else:
         run_ours(args)

@@ -19,6 +19,7 @@ namespace kfac {
 
 constexpr int DB = 128;        // diagonal block
 constexpr int DLD = DB + 1;    // shared-memory pitch
+constexpr int PW = 512;        // Cholesky panel width (outer blocking)
 
 struct MatInfo {
   const float* F;
@@ -326,42 +327,67 @@ extern "C" int kfac_inverse_plan_create(
     if (l.n > 0) launches.push_back(l);
   };
 
-  const int nsteps = (dmax + DB - 1) / DB;
-  for (int j = 0; j < nsteps; ++j) {
-    const int o = j * DB;
-    Launch dl = {0, (int)ids.size(), 0, 0, j};
-    for (int i : order)
-      if (dims[i] > o) { ids.push_back(i); dl.n += 1; }
-    launches.push_back(dl);
+  // Two-level right-looking Cholesky: panels of PW columns are factored by
+  // 128-wide inner steps whose updates stay inside the panel (short
+  // contractions, little work); the bulk of the flops is the update of the
+  // trailing matrix with the whole panel (contraction length PW).
+  for (int po = 0; po < dmax; po += PW) {
+    const int inner = std::min(PW, dmax - po);
+    for (int o = po; o < po + inner; o += DB) {
+      Launch dl = {0, (int)ids.size(), 0, 0, o / DB};
+      for (int i : order)
+        if (dims[i] > o) { ids.push_back(i); dl.n += 1; }
+      launches.push_back(dl);
 
-    Launch trsm = begin_gemm();
-    for (int i : order) {
-      const int d = dims[i];
-      const int M = d - o - DB;
-      if (M <= 0) continue;
-      const MatInfo& m = mats[i];
-      GemmDesc g = {};
-      float* panel = m.W + (long long)(o + DB) * d + o;
-      g.A = strided_operand(panel, 1, d, M);
-      g.B = strided_operand(m.X + (long long)o * d + o, 1, d, DB);
-      g.C = panel; g.ldc = d; g.M = M; g.N = DB; g.K = DB;
-      g.alpha = 1.f; g.beta = 0.f; g.flags = 0;
-      push_desc(trsm, g);
+      Launch trsm = begin_gemm();
+      for (int i : order) {
+        const int d = dims[i];
+        const int M = d - o - DB;
+        if (M <= 0) continue;
+        const MatInfo& m = mats[i];
+        GemmDesc g = {};
+        float* panel = m.W + (long long)(o + DB) * d + o;
+        g.A = strided_operand(panel, 1, d, M);
+        g.B = strided_operand(m.X + (long long)o * d + o, 1, d, DB);
+        g.C = panel; g.ldc = d; g.M = M; g.N = DB; g.K = DB;
+        g.alpha = 1.f; g.beta = 0.f; g.flags = 0;
+        push_desc(trsm, g);
+      }
+      end_gemm(trsm);
+
+      // update the rest of this panel's columns (full rectangle; entries
+      // above the diagonal are written but never read)
+      Launch upd = begin_gemm();
+      for (int i : order) {
+        const int d = dims[i];
+        const int M = d - o - DB;
+        const int N = std::min(po + PW, d) - (o + DB);
+        if (M <= 0 || N <= 0) continue;
+        const MatInfo& m = mats[i];
+        GemmDesc g = {};
+        float* panel = m.W + (long long)(o + DB) * d + o;
+        g.A = strided_operand(panel, 1, d, M);
+        g.B = strided_operand(panel, 1, d, N);
+        g.C = m.W + (long long)(o + DB) * d + (o + DB);
+        g.ldc = d; g.M = M; g.N = N; g.K = DB;
+        g.alpha = -1.f; g.beta = 1.f; g.flags = 0;
+        push_desc(upd, g);
+      }
+      end_gemm(upd);
     }
-    end_gemm(trsm);
 
     Launch trail = begin_gemm();
     for (int i : order) {
       const int d = dims[i];
-      const int M = d - o - DB;
+      const int M = d - po - PW;
       if (M <= 0) continue;
       const MatInfo& m = mats[i];
       GemmDesc g = {};
-      float* panel = m.W + (long long)(o + DB) * d + o;
+      float* panel = m.W + (long long)(po + PW) * d + po;
       g.A = strided_operand(panel, 1, d, M);
       g.B = g.A;
-      g.C = m.W + (long long)(o + DB) * d + (o + DB);
-      g.ldc = d; g.M = M; g.N = M; g.K = DB;
+      g.C = m.W + (long long)(po + PW) * d + (po + PW);
+      g.ldc = d; g.M = M; g.N = M; g.K = PW;
       g.alpha = -1.f; g.beta = 1.f; g.flags = G_LOWER;
       push_desc(trail, g);
     }

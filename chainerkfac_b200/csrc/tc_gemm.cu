@@ -21,7 +21,8 @@ namespace kfac {
 constexpr int TC_BM = 128;
 constexpr int TC_BN = 256;
 constexpr int TC_BK = 32;
-constexpr int TC_PRODUCERS = 256;
+constexpr int TC_PRODUCERS = 512;
+constexpr int TC_PWARPS = TC_PRODUCERS / 32;
 constexpr int TC_THREADS = TC_PRODUCERS + 32;
 constexpr int TC_A_BYTES = TC_BM * TC_BK * 4;   // 16 KB
 constexpr int TC_B_BYTES = TC_BN * TC_BK * 4;   // 32 KB
@@ -37,6 +38,21 @@ constexpr unsigned TC_SPIN_LIMIT = 1u << 22;
 constexpr int TC_TMEM_COLS = 2 * TC_BN;
 
 static __device__ int g_tc_status = 0;
+
+#ifdef KFAC_TC_TRACE
+// Debug build only: CTA (0,0) records clock64() at fixed points of the
+// producer / MMA loops, 8 slots per k-block.
+__device__ long long* g_tc_trace = nullptr;
+__device__ int g_tc_trace_cap = 0;
+#define TC_TRACE(kb, slot)                                                   \
+  do {                                                                       \
+    if (g_tc_trace && blockIdx.x == 0 && blockIdx.y == 0 &&                  \
+        ((kb) * 8 + (slot)) < g_tc_trace_cap)                                \
+      g_tc_trace[(kb) * 8 + (slot)] = clock64();                             \
+  } while (0)
+#else
+#define TC_TRACE(kb, slot) do {} while (0)
+#endif
 
 struct TcControl {
   unsigned long long full[TC_STAGES];
@@ -143,18 +159,24 @@ __device__ __forceinline__ int sw128_chunk_off(int row, int chunk) {
   return row * 128 + ((chunk ^ (row & 7)) << 4);
 }
 
-__device__ __forceinline__ void store_split(unsigned char* hi_tile,
-                                            unsigned char* lo_tile, int row,
-                                            int chunk, float4 x) {
+__device__ __forceinline__ void sts128(unsigned addr, float4 v) {
+  asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr),
+               "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+               : "memory");
+}
+
+// hi = x with the low 13 mantissa bits cleared (exactly a TF32 value),
+// lo = x - hi (exact in fp32; the tensor core reads its top 11 bits).
+__device__ __forceinline__ void store_split(unsigned hi_addr, unsigned lo_addr,
+                                            float4 x) {
   float4 h, l;
   h.x = __uint_as_float(__float_as_uint(x.x) & 0xFFFFE000u);
   h.y = __uint_as_float(__float_as_uint(x.y) & 0xFFFFE000u);
   h.z = __uint_as_float(__float_as_uint(x.z) & 0xFFFFE000u);
   h.w = __uint_as_float(__float_as_uint(x.w) & 0xFFFFE000u);
   l.x = x.x - h.x; l.y = x.y - h.y; l.z = x.z - h.z; l.w = x.w - h.w;
-  const int off = sw128_chunk_off(row, chunk);
-  *reinterpret_cast<float4*>(hi_tile + off) = h;
-  *reinterpret_cast<float4*>(lo_tile + off) = l;
+  sts128(hi_addr, h);
+  sts128(lo_addr, l);
 }
 
 // im2col column tables for `rows` columns of a tile starting at column c0.
@@ -180,119 +202,230 @@ __device__ __forceinline__ void tc_im2col_tables(const Operand& op, int c0,
   }
 }
 
-// Fill `rows` (multiple of 4... any) rows of one operand tile for the k-block
-// [k0, k0 + 32): gather, split into hi/lo, store swizzled.  Rows are tile-local
-// columns c0 + row of the operand; elements with k >= kend or column beyond
-// the operand are zero.
-__device__ __forceinline__ void tc_fill_tile(const Operand& op, int c0,
-                                             int rows, long long k0,
-                                             long long kend,
-                                             unsigned char* hi_tile,
-                                             unsigned char* lo_tile,
-                                             const int* coff, const int* kykx,
-                                             int warp, int lane) {
-  const int total_cols = op.ncols + (op.extra_idx >= 0 ? 1 : 0);
-  if (op.mode == 1) {
-    // im2col: lane = 8 * (row % 4) + chunk; this thread's 4 k are fixed for
-    // the whole k-block, so the pixel decomposition is done once.
-    const int chunk = lane & 7;
-    const int how = op.Ho * op.Wo;
-    long long base[4];
-    int iy0[4], ix0[4];
-    bool kv[4];
+// Sources of constant columns: rows of the tile that lie beyond the operand
+// read zeros, the appended bias column reads ones; both without branches in
+// the hot loop (their address multiplier is 0).
+static __device__ __align__(256) float g_zero_page[64];
+static __device__ __align__(256) float g_ones_page[64] = {
+    1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1,
+    1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1,
+    1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1};
+
+// A producer thread moves NTASK 16-byte chunks (4 consecutive k of one tile
+// row) of an operand tile per k-block.  Operands contiguous along k (and
+// im2col operands) map task t to row = 4*warp + 4*PWARPS*t + lane/8, chunk =
+// lane%8; operands contiguous along the column index map it to row =
+// 32*((PWARPS/8)*t + warp/8) + lane, chunk = warp%8, so that a warp's loads of
+// one k are 32 consecutive addresses.  Per task everything that does not
+// change with k is computed once: the element address is
+//     p + (long long)o_j * mul        (one multiply-add per element)
+// where o_j is the k-dependent offset shared by all tasks of the thread.
+struct PTask {
+  const float* p;   // column base (or the zero / ones page)
+  int m;            // strided: multiplier of the k-dependent offset (0 for
+                    // pages); im2col: (ky << 8) | kx, or -1 for pages
+  unsigned soff;    // swizzled byte offset inside the tile, ~0u: idle task
+};
+
+template <int NTASK, bool IM2COL>
+__device__ __forceinline__ void tc_task_setup(const Operand& op, int c0,
+                                              int rows, const int* coff,
+                                              const int* kykx, int warp,
+                                              int lane, PTask task[NTASK]) {
+  const bool kf = IM2COL || op.kfast;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      long long k = k0 + chunk * 4 + j;
-      kv[j] = k < kend;
-      long long n = k / how;
-      int rem = (int)(k - n * how);
-      int oy = rem / op.Wo;
-      int ox = rem - oy * op.Wo;
-      iy0[j] = oy * op.st - op.pd;
-      ix0[j] = ox * op.st - op.pd;
-      base[j] = n * op.C * op.H * op.W + (long long)iy0[j] * op.W + ix0[j];
-    }
-    for (int r0 = warp * 4; r0 < rows; r0 += 32) {
-      const int row = r0 + (lane >> 3);
-      float v[4] = {0.f, 0.f, 0.f, 0.f};
-      if (row < rows) {
+  for (int t = 0; t < NTASK; ++t) {
+    const int row = kf ? warp * 4 + (TC_PWARPS * 4) * t + (lane >> 3)
+                       : 32 * ((TC_PWARPS / 8) * t + (warp >> 3)) + lane;
+    const int chunk = kf ? (lane & 7) : (warp & 7);
+    PTask v;
+    v.soff = row < rows
+                 ? (unsigned)(row * 128 + ((chunk ^ (row & 7)) << 4)) : ~0u;
+    v.p = g_zero_page;
+    v.m = IM2COL ? -1 : 0;
+    if (row < rows) {
+      const int c = c0 + row;
+      if (IM2COL) {
         const int info = kykx[row];
         if (info >= 0) {
-          const int ky = info >> 16, kx = info & 0xffff, co = coff[row];
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            int iy = iy0[j] + ky, ix = ix0[j] + kx;
-            if (kv[j] && (unsigned)iy < (unsigned)op.H &&
-                (unsigned)ix < (unsigned)op.W)
-              v[j] = op.base[base[j] + co];
-          }
+          v.p = op.base + coff[row];
+          v.m = ((info >> 16) << 8) | (info & 0xff);
         } else if (info == -2) {
-#pragma unroll
-          for (int j = 0; j < 4; ++j) v[j] = kv[j] ? 1.f : 0.f;
+          v.p = g_ones_page;
         }
-        store_split(hi_tile, lo_tile, row, chunk,
-                    make_float4(v[0], v[1], v[2], v[3]));
-      }
-    }
-    return;
-  }
-  if (op.kfast) {
-    // contiguous along k: lane = 8 * (row % 4) + chunk, one 16-byte chunk each
-    const int chunk = lane & 7;
-    const long long k = k0 + chunk * 4;
-    long long roff[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) roff[j] = operand_rowoff(op, k + j);
-    const bool contiguous = (roff[3] - roff[0]) == 3 && (k + 3) < kend;
-    for (int r0 = warp * 4; r0 < rows; r0 += 32) {
-      const int row = r0 + (lane >> 3);
-      if (row >= rows) continue;
-      const int c = c0 + row;
-      float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (c < op.ncols) {
-        const float* p = op.base + (long long)c * op.s_col;
-        if (contiguous && ((reinterpret_cast<uintptr_t>(p + roff[0]) & 15) == 0)) {
-          x = *reinterpret_cast<const float4*>(p + roff[0]);
-        } else {
-          if (k + 0 < kend) x.x = p[roff[0]];
-          if (k + 1 < kend) x.y = p[roff[1]];
-          if (k + 2 < kend) x.z = p[roff[2]];
-          if (k + 3 < kend) x.w = p[roff[3]];
-        }
+      } else if (c < op.ncols) {
+        v.p = op.base + (long long)c * op.s_col;
+        v.m = op.period == 1 ? (int)op.s_outer : 1;
       } else if (c == op.extra_idx) {
-        if (k + 0 < kend) x.x = op.extra ? op.extra[k + 0] : 1.f;
-        if (k + 1 < kend) x.y = op.extra ? op.extra[k + 1] : 1.f;
-        if (k + 2 < kend) x.z = op.extra ? op.extra[k + 2] : 1.f;
-        if (k + 3 < kend) x.w = op.extra ? op.extra[k + 3] : 1.f;
+        if (op.extra) { v.p = op.extra; v.m = 1; }
+        else v.p = g_ones_page;
       }
-      store_split(hi_tile, lo_tile, row, chunk, x);
+    }
+    task[t] = v;
+  }
+}
+
+// Position of a thread's chunk (4 consecutive k) in an operand's row space,
+// kept incrementally from k-block to k-block so that the hot loop has no
+// integer division.
+struct KState {
+  int k;           // first k of the chunk (contractions are < 2^31 long)
+  int a, b, c;     // strided with a period: k = a * period + b
+                   // im2col: k = (a * Ho + b) * Wo + c
+};
+
+template <bool IM2COL>
+__device__ __forceinline__ void kstate_init(const Operand& op, long long k,
+                                            KState& s) {
+  s.k = (int)k;
+  s.a = s.b = s.c = 0;
+  if (IM2COL) {
+    const int how = op.Ho * op.Wo;
+    s.a = (int)(k / how);
+    const int rem = (int)(k - (long long)s.a * how);
+    s.b = rem / op.Wo;
+    s.c = rem - s.b * op.Wo;
+  } else if (op.period != 1) {
+    s.a = (int)(k / op.period);
+    s.b = (int)(k - (long long)s.a * op.period);
+  }
+}
+
+template <bool IM2COL>
+__device__ __forceinline__ void kstate_advance(const Operand& op, KState& s) {
+  s.k += TC_BK;
+  if (IM2COL) {
+    s.c += TC_BK;
+    while (s.c >= op.Wo) {
+      s.c -= op.Wo;
+      if (++s.b >= op.Ho) { s.b = 0; ++s.a; }
+    }
+  } else if (op.period != 1) {
+    s.b += TC_BK;
+    while (s.b >= op.period) { s.b -= op.period; ++s.a; }
+  }
+}
+
+// Gather the NTASK chunks of one k-block into registers.  The loads are
+// issued back to back, each from an address that is always legal; nothing
+// between two loads depends on a loaded value.  `vec` (uniform per tile):
+// every chunk of this operand is 16-byte aligned and contiguous.
+template <int NTASK, bool IM2COL>
+__device__ __forceinline__ void tc_load_tile(const Operand& op,
+                                             const PTask task[NTASK],
+                                             const KState& ks, int kend,
+                                             bool vec, float4 v[NTASK]) {
+  const int k = ks.k;
+  const bool tail = k + 3 >= kend;
+
+  if (IM2COL) {
+    int pix[4];
+    unsigned rm[4], cm[4];   // bit ky / kx set: that tap lies inside the image
+    {
+      int n = ks.a, oy = ks.b, ox = ks.c;
+      const int chw = op.C * op.H * op.W;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int iy0 = oy * op.st - op.pd, ix0 = ox * op.st - op.pd;
+        pix[j] = n * chw + iy0 * op.W + ix0;
+        unsigned r = 0, c = 0;
+        for (int kk = 0; kk < op.ks; ++kk) {
+          r |= ((unsigned)(iy0 + kk) < (unsigned)op.H) ? (1u << kk) : 0u;
+          c |= ((unsigned)(ix0 + kk) < (unsigned)op.W) ? (1u << kk) : 0u;
+        }
+        if (k + j >= kend) r = 0;
+        rm[j] = r;
+        cm[j] = c;
+        if (++ox >= op.Wo) {
+          ox = 0;
+          if (++oy >= op.Ho) { oy = 0; ++n; }
+        }
+      }
+    }
+#pragma unroll
+    for (int t = 0; t < NTASK; ++t) {
+      if (task[t].soff == ~0u) continue;
+      const int aux = task[t].m;
+      const int ky = (aux >> 8) & 0xff, kx = aux & 0xff;
+      float x[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        // pages (aux < 0): valid wherever k is, offset 0
+        const bool valid = aux < 0 ? (k + j < kend)
+                                   : (((rm[j] >> ky) & (cm[j] >> kx) & 1u) != 0);
+        const float* q = valid ? task[t].p + (aux < 0 ? 0 : pix[j])
+                               : g_zero_page;
+        x[j] = *q;
+      }
+      v[t] = make_float4(x[0], x[1], x[2], x[3]);
     }
     return;
   }
-  // contiguous along the column index: lanes walk 32 consecutive columns for
-  // a fixed k (coalesced), each thread assembles one 16-byte chunk of 4 k.
-  const int groups = (rows + 31) >> 5;
-  for (int task = warp; task < groups * 8; task += 8) {
-    const int g = task >> 3, chunk = task & 7;
-    const int row = g * 32 + lane;
-    if (row >= rows) continue;
-    const int c = c0 + row;
-    const long long k = k0 + chunk * 4;
-    float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (c < op.ncols) {
-      const float* p = op.base + (long long)c * op.s_col;
-      if (k + 0 < kend) x.x = p[operand_rowoff(op, k + 0)];
-      if (k + 1 < kend) x.y = p[operand_rowoff(op, k + 1)];
-      if (k + 2 < kend) x.z = p[operand_rowoff(op, k + 2)];
-      if (k + 3 < kend) x.w = p[operand_rowoff(op, k + 3)];
-    } else if (c == op.extra_idx && c < total_cols) {
-      if (k + 0 < kend) x.x = op.extra ? op.extra[k + 0] : 1.f;
-      if (k + 1 < kend) x.y = op.extra ? op.extra[k + 1] : 1.f;
-      if (k + 2 < kend) x.z = op.extra ? op.extra[k + 2] : 1.f;
-      if (k + 3 < kend) x.w = op.extra ? op.extra[k + 3] : 1.f;
+
+  int o[4];
+  if (op.period == 1) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[j] = k + j;
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      int q = ks.a, r = ks.b + j;
+      while (r >= op.period) { r -= op.period; ++q; }
+      o[j] = (int)((long long)q * op.s_outer + (long long)r * op.s_inner);
     }
-    store_split(hi_tile, lo_tile, row, chunk, x);
   }
+  if (tail) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) if (k + j >= kend) o[j] = 0;
+  }
+  if (vec && !tail) {
+#pragma unroll
+    for (int t = 0; t < NTASK; ++t)
+      if (task[t].soff != ~0u)
+        v[t] = *reinterpret_cast<const float4*>(
+            task[t].p + (long long)o[0] * task[t].m);
+  } else {
+#pragma unroll
+    for (int t = 0; t < NTASK; ++t) {
+      if (task[t].soff == ~0u) continue;
+      v[t].x = task[t].p[(long long)o[0] * task[t].m];
+      v[t].y = task[t].p[(long long)o[1] * task[t].m];
+      v[t].z = task[t].p[(long long)o[2] * task[t].m];
+      v[t].w = task[t].p[(long long)o[3] * task[t].m];
+    }
+  }
+  if (tail) {
+#pragma unroll
+    for (int t = 0; t < NTASK; ++t) {
+      if (k + 0 >= kend) v[t].x = 0.f;
+      if (k + 1 >= kend) v[t].y = 0.f;
+      if (k + 2 >= kend) v[t].z = 0.f;
+      if (k + 3 >= kend) v[t].w = 0.f;
+    }
+  }
+}
+
+// True when every 16-byte chunk of a k-contiguous strided operand is aligned
+// and contiguous for k-blocks that start at kbeg (uniform for the tile).
+__device__ __forceinline__ bool tc_operand_vec(const Operand& op,
+                                               long long kbeg) {
+  if (op.mode != 0 || !op.kfast) return false;
+  if ((reinterpret_cast<uintptr_t>(op.base) & 15) != 0) return false;
+  if ((op.s_col & 3) != 0 || (kbeg & 3) != 0) return false;
+  if (op.extra_idx >= 0 && op.extra != nullptr) return false;
+  if (op.period == 1) return op.s_outer == 1;
+  return (op.period & 3) == 0 && (op.s_outer & 3) == 0 && op.s_inner == 1;
+}
+
+template <int NTASK>
+__device__ __forceinline__ void tc_store_tile(const PTask task[NTASK],
+                                              unsigned hi_tile,
+                                              unsigned lo_tile,
+                                              const float4 v[NTASK]) {
+#pragma unroll
+  for (int t = 0; t < NTASK; ++t)
+    if (task[t].soff != ~0u)
+      store_split(hi_tile + task[t].soff, lo_tile + task[t].soff, v[t]);
 }
 
 // Lower-triangular enumeration with 128-row x 256-column tiles: tile (bi, bj)
@@ -311,6 +444,7 @@ __device__ __forceinline__ void tc_tri_tile(int t, int& bi, int& bj) {
   }
 }
 
+template <bool IM2COL>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 tc_gemm_kernel(const GemmDesc* __restrict__ descs, int ndesc,
                const __grid_constant__ GemmDesc inline_desc, float lr,
@@ -389,27 +523,63 @@ tc_gemm_kernel(const GemmDesc* __restrict__ descs, int ndesc,
 
   if (warp < TC_PRODUCERS / 32) {
     // ===================== producers =====================
-    if (g.A.mode == 1) tc_im2col_tables(g.A, m0, TC_BM, ctl->coff_a, ctl->kykx_a, tid);
-    if (g.B.mode == 1) tc_im2col_tables(g.B, n0, n_inst, ctl->coff_b, ctl->kykx_b, tid);
-    if (g.A.mode == 1 || g.B.mode == 1)
+    if (IM2COL) {
+      tc_im2col_tables(g.A, m0, TC_BM, ctl->coff_a, ctl->kykx_a, tid);
+      tc_im2col_tables(g.B, n0, n_inst, ctl->coff_b, ctl->kykx_b, tid);
       asm volatile("bar.sync 1, %0;" ::"r"(TC_PRODUCERS) : "memory");
-    for (int kb = 0; kb < nkb; ++kb) {
-      const int s = kb % TC_STAGES;
-      if (kb >= TC_STAGES) {
-        if (!mbar_wait(&ctl->empty[s], ((kb / TC_STAGES) - 1) & 1,
-                       &ctl->abort_flag))
-          break;
+    }
+    constexpr int NTA = TC_BM * 8 / TC_PRODUCERS;   // chunks per thread
+    constexpr int NTB = TC_BN * 8 / TC_PRODUCERS;
+    const Operand A = g.A, B = g.B;   // register copies: loop invariant
+    float4 va[NTA], vb[NTB];
+    PTask ia[NTA], ib[NTB];
+    tc_task_setup<NTA, IM2COL>(A, m0, TC_BM, ctl->coff_a, ctl->kykx_a, warp,
+                               lane, ia);
+    tc_task_setup<NTB, IM2COL>(B, n0, n_inst, ctl->coff_b, ctl->kykx_b, warp,
+                               lane, ib);
+    const int kend_i = (int)kend;
+    KState ka, kb_state;
+    {
+      const bool a_kf = IM2COL || A.kfast;
+      const bool b_kf = IM2COL || B.kfast;
+      kstate_init<IM2COL>(A, kbeg + 4 * (a_kf ? (lane & 7) : (warp & 7)), ka);
+      kstate_init<IM2COL>(B, kbeg + 4 * (b_kf ? (lane & 7) : (warp & 7)),
+                          kb_state);
+    }
+    const unsigned smem_base = smem_u32(smem);
+    const bool vec_a = !IM2COL && tc_operand_vec(A, kbeg);
+    const bool vec_b = !IM2COL && tc_operand_vec(B, kbeg);
+    // iteration kb stores k-block kb-1 (loaded one iteration earlier) and
+    // issues the loads of k-block kb, which then fly while the tensor core
+    // works and while this warp waits for the stage to drain
+    for (int kb = 0; kb <= nkb; ++kb) {
+      if (kb > 0) {
+        const int pb = kb - 1;
+        const int s = pb % TC_STAGES;
+        if (tid == 0) TC_TRACE(pb, 0);
+        if (pb >= TC_STAGES) {
+          if (!mbar_wait(&ctl->empty[s], ((pb / TC_STAGES) - 1) & 1,
+                         &ctl->abort_flag))
+            break;
+        }
+        if (tid == 0) TC_TRACE(pb, 1);
+        const unsigned st = smem_base + s * TC_STAGE_BYTES;
+        tc_store_tile<NTA>(ia, st, st + TC_A_BYTES, va);
+        tc_store_tile<NTB>(ib, st + 2 * TC_A_BYTES,
+                           st + 2 * TC_A_BYTES + TC_B_BYTES, vb);
+        if (tid == 0) TC_TRACE(pb, 2);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ctl->full[s]);
+        if (tid == 0) TC_TRACE(pb, 3);
       }
-      unsigned char* st = smem + s * TC_STAGE_BYTES;
-      const long long k0 = kbeg + (long long)kb * TC_BK;
-      tc_fill_tile(g.A, m0, TC_BM, k0, kend, st, st + TC_A_BYTES, ctl->coff_a,
-                   ctl->kykx_a, warp, lane);
-      tc_fill_tile(g.B, n0, n_inst, k0, kend, st + 2 * TC_A_BYTES,
-                   st + 2 * TC_A_BYTES + TC_B_BYTES, ctl->coff_b, ctl->kykx_b,
-                   warp, lane);
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&ctl->full[s]);
+      if (kb < nkb) {
+        tc_load_tile<NTA, IM2COL>(A, ia, ka, kend_i, vec_a, va);
+        tc_load_tile<NTB, IM2COL>(B, ib, kb_state, kend_i, vec_b, vb);
+        kstate_advance<IM2COL>(A, ka);
+        kstate_advance<IM2COL>(B, kb_state);
+        if (tid == 0) TC_TRACE(kb, 4);
+      }
     }
   } else {
     // ===================== MMA issuer =====================
@@ -417,8 +587,10 @@ tc_gemm_kernel(const GemmDesc* __restrict__ descs, int ndesc,
       const unsigned idesc = tc_instr_desc(n_inst);
       for (int kb = 0; kb < nkb; ++kb) {
         const int s = kb % TC_STAGES;
+        TC_TRACE(kb, 5);
         if (!mbar_wait(&ctl->full[s], (kb / TC_STAGES) & 1, &ctl->abort_flag))
           break;
+        TC_TRACE(kb, 6);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const unsigned sa = smem_u32(smem + s * TC_STAGE_BYTES);
         const unsigned long long a_hi = tc_smem_desc(sa);
@@ -434,6 +606,7 @@ tc_gemm_kernel(const GemmDesc* __restrict__ descs, int ndesc,
           tc_mma(tmem, a_hi + adv, b_hi + adv, idesc, (kb | kk) != 0);
         }
         tc_commit(&ctl->empty[s]);
+        TC_TRACE(kb, 7);
       }
       tc_commit(&ctl->accum);
     }
@@ -449,9 +622,10 @@ tc_gemm_kernel(const GemmDesc* __restrict__ descs, int ndesc,
       ok = __all_sync(0xffffffffu, ok);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     }
+    constexpr int CW = TC_BN / (TC_PWARPS / 4);   // columns per warp
     const int q = warp & 3, h = warp >> 2;
     const int row = q * 32 + lane;
-    for (int c0 = h * 128; c0 < min(n_inst, h * 128 + 128); c0 += 16) {
+    for (int c0 = h * CW; c0 < min(n_inst, h * CW + CW); c0 += 16) {
       float v[16];
       if (nkb > 0 && ok) {
         float w[16];
@@ -479,14 +653,14 @@ tc_gemm_kernel(const GemmDesc* __restrict__ descs, int ndesc,
   if (g.splits > 1) {
     float* p = g.partial +
                ((long long)blockIdx.y * gridDim.x + tile) * (TC_BM * TC_BN);
-    for (int r = warp; r < TC_BM; r += 8)
+    for (int r = warp; r < TC_BM; r += TC_PWARPS)
       for (int c = lane; c < n_inst; c += 32)
         p[r * TC_BN + c] = stage[r * TC_EPI_PITCH + c];
     return;
   }
   if (g.flags & G_PRECOND) {
     const int dW = g.dW;
-    for (int r = warp; r < m_valid; r += 8) {
+    for (int r = warp; r < m_valid; r += TC_PWARPS) {
       const int gr = m0 + r;
       for (int c = lane; c < n_valid; c += 32) {
         const int gc = n0 + c;
@@ -515,7 +689,7 @@ tc_gemm_kernel(const GemmDesc* __restrict__ descs, int ndesc,
   const bool mirror = (g.flags & G_MIRROR) != 0;
   // rows: C[gr][gc] = alpha * acc + beta * C[gr][gc]; the final value is kept
   // in the staging tile for the mirrored pass
-  for (int r = warp; r < m_valid; r += 8) {
+  for (int r = warp; r < m_valid; r += TC_PWARPS) {
     const int gr = m0 + r;
     for (int c = lane; c < n_valid; c += 32) {
       const int gc = n0 + c;
@@ -529,7 +703,7 @@ tc_gemm_kernel(const GemmDesc* __restrict__ descs, int ndesc,
   }
   if (mirror) {
     asm volatile("bar.sync 1, %0;" ::"r"(TC_PRODUCERS) : "memory");
-    for (int c = warp; c < n_valid; c += 8) {
+    for (int c = warp; c < n_valid; c += TC_PWARPS) {
       const int gc = n0 + c;
       for (int r = lane; r < m_valid; r += 32) {
         const int gr = m0 + r;
@@ -587,7 +761,10 @@ static int tc_prepare() {
   KFAC_REQUIRE(dev >= 0 && dev < 64, "device index %d unsupported", dev);
   std::lock_guard<std::mutex> lock(mu);
   if (!done[dev]) {
-    KFAC_CUDA(cudaFuncSetAttribute(tc_gemm_kernel,
+    KFAC_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<false>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   TC_SMEM_BYTES));
+    KFAC_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<true>,
                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    TC_SMEM_BYTES));
     done[dev] = true;
@@ -601,7 +778,7 @@ int launch_tc_grouped(const GemmDesc* descs_dev, int ndesc, int total_tiles,
   int rc = tc_prepare();
   if (rc != KFAC_OK) return rc;
   GemmDesc dummy = {};
-  tc_gemm_kernel<<<total_tiles, TC_THREADS, TC_SMEM_BYTES, stream>>>(
+  tc_gemm_kernel<false><<<total_tiles, TC_THREADS, TC_SMEM_BYTES, stream>>>(
       descs_dev, ndesc, dummy, lr, momentum);
   KFAC_LAUNCH_CHECK("tc_gemm_kernel");
   return KFAC_OK;
@@ -643,6 +820,8 @@ int run_factor_tc(const Operand& X, long long rows, int d, float alpha,
                   size_t workspace_bytes, cudaStream_t stream) {
   int rc = tc_prepare();
   if (rc != KFAC_OK) return rc;
+  KFAC_REQUIRE(rows < (1LL << 31) && (long long)rows * d < (1LL << 40),
+               "factor: contraction of %lld rows is too long", rows);
   TcFactorSplit s = tc_factor_split(rows, d);
   GemmDesc g = {};
   g.A = X;
@@ -669,8 +848,12 @@ int run_factor_tc(const Operand& X, long long rows, int d, float alpha,
     g.partial = static_cast<float*>(workspace);
   }
   dim3 grid(s.tiles, s.splits);
-  tc_gemm_kernel<<<grid, TC_THREADS, TC_SMEM_BYTES, stream>>>(nullptr, 1, g,
-                                                              0.f, 0.f);
+  if (X.mode == 1)
+    tc_gemm_kernel<true><<<grid, TC_THREADS, TC_SMEM_BYTES, stream>>>(
+        nullptr, 1, g, 0.f, 0.f);
+  else
+    tc_gemm_kernel<false><<<grid, TC_THREADS, TC_SMEM_BYTES, stream>>>(
+        nullptr, 1, g, 0.f, 0.f);
   KFAC_LAUNCH_CHECK("tc_gemm_kernel");
   if (s.splits > 1) {
     dim3 rgrid(s.tiles, TC_BM / 8);
@@ -693,6 +876,14 @@ extern "C" int kfac_set_engine(int engine) {
 }
 
 extern "C" int kfac_get_engine(void) { return kfac::g_engine; }
+
+#ifdef KFAC_TC_TRACE
+extern "C" int kfac_tc_trace(long long* buf_dev, int capacity) {
+  KFAC_CUDA(cudaMemcpyToSymbol(kfac::g_tc_trace, &buf_dev, sizeof(buf_dev)));
+  KFAC_CUDA(cudaMemcpyToSymbol(kfac::g_tc_trace_cap, &capacity, sizeof(int)));
+  return KFAC_OK;
+}
+#endif
 
 extern "C" int kfac_tc_status(int* status_out) {
   KFAC_REQUIRE(status_out != nullptr, "tc_status: null pointer");
