@@ -33,6 +33,7 @@ SIGNATURES = {
     'kfac_factor_dense': (I, [VP, I64, I, I64, I, F, F, VP, VP, SZ, VP]),
     'kfac_factor_noalloc_max_bytes': (SZ, []),
     'kfac_factor_dense_noalloc': (I, [VP, I64, I, I64, I, F, F, VP, VP]),
+    'kfac_factor_conv_workspace_bytes': (SZ, [I, I, I, I, I, I, I, I]),
     'kfac_factor_conv_input': (I, [VP, I, I, I, I, I, I, I, I, F, F, VP, VP,
                                    SZ, VP]),
     'kfac_factor_conv_grad': (I, [VP, I, I, I, I, F, F, VP, VP, SZ, VP]),

@@ -296,20 +296,11 @@ extern "C" int kfac_factor_dense(const float* x, int64_t rows, int d_in,
                     workspace, workspace_bytes, (cudaStream_t)stream);
 }
 
-extern "C" int kfac_factor_conv_input(const float* x, int n, int c, int h,
-                                      int w, int ksize, int stride, int pad,
-                                      int add_ones_col, float alpha, float beta,
-                                      float* out, void* workspace,
-                                      size_t workspace_bytes, void* stream) {
-  KFAC_REQUIRE(n > 0 && c > 0 && h > 0 && w > 0 && ksize > 0 && stride > 0 &&
-                   pad >= 0,
-               "factor_conv_input: bad geometry n=%d c=%d h=%d w=%d k=%d s=%d "
-               "p=%d", n, c, h, w, ksize, stride, pad);
-  KFAC_REQUIRE((long long)n * c * h * w < (1LL << 31),
-               "factor_conv_input: input has more than 2^31 elements");
-  int ho = (h + 2 * pad - ksize) / stride + 1;
-  int wo = (w + 2 * pad - ksize) / stride + 1;
-  KFAC_REQUIRE(ho > 0 && wo > 0, "factor_conv_input: empty output");
+static Operand conv_input_operand(const float* x, int c, int h, int w,
+                                  int ksize, int stride, int pad,
+                                  int add_ones_col) {
+  const int ho = (h + 2 * pad - ksize) / stride + 1;
+  const int wo = (w + 2 * pad - ksize) / stride + 1;
   Operand X = {};
   X.base = x;
   X.ncols = c * ksize * ksize;
@@ -329,6 +320,44 @@ extern "C" int kfac_factor_conv_input(const float* x, int n, int c, int h,
     X.kfast = 1;
     X.extra_idx = add_ones_col ? c : -1;
   }
+  return X;
+}
+
+extern "C" size_t kfac_factor_conv_workspace_bytes(int n, int c, int h, int w,
+                                                   int ksize, int stride,
+                                                   int pad, int add_ones_col) {
+  if (n <= 0 || c <= 0 || h <= 0 || w <= 0 || ksize <= 0 || stride <= 0 ||
+      pad < 0)
+    return 0;
+  const int ho = (h + 2 * pad - ksize) / stride + 1;
+  const int wo = (w + 2 * pad - ksize) / stride + 1;
+  if (ho <= 0 || wo <= 0) return 0;
+  const int d = c * ksize * ksize + (add_ones_col ? 1 : 0);
+  size_t bytes = kfac_factor_workspace_bytes((int64_t)n * ho * wo, d);
+  if (engine() == 1) {
+    Operand X = conv_input_operand(nullptr, c, h, w, ksize, stride, pad,
+                                   add_ones_col);
+    bytes += tc_pad_bytes(X, n);
+  }
+  return bytes;
+}
+
+extern "C" int kfac_factor_conv_input(const float* x, int n, int c, int h,
+                                      int w, int ksize, int stride, int pad,
+                                      int add_ones_col, float alpha, float beta,
+                                      float* out, void* workspace,
+                                      size_t workspace_bytes, void* stream) {
+  KFAC_REQUIRE(n > 0 && c > 0 && h > 0 && w > 0 && ksize > 0 && stride > 0 &&
+                   pad >= 0,
+               "factor_conv_input: bad geometry n=%d c=%d h=%d w=%d k=%d s=%d "
+               "p=%d", n, c, h, w, ksize, stride, pad);
+  KFAC_REQUIRE((long long)n * c * h * w < (1LL << 31),
+               "factor_conv_input: input has more than 2^31 elements");
+  int ho = (h + 2 * pad - ksize) / stride + 1;
+  int wo = (w + 2 * pad - ksize) / stride + 1;
+  KFAC_REQUIRE(ho > 0 && wo > 0, "factor_conv_input: empty output");
+  Operand X = conv_input_operand(x, c, h, w, ksize, stride, pad,
+                                 add_ones_col);
   int d = c * ksize * ksize + (add_ones_col ? 1 : 0);
   return run_factor(X, (long long)n * ho * wo, d, alpha, beta, out, workspace,
                     workspace_bytes, (cudaStream_t)stream);

@@ -265,6 +265,7 @@ int tc_tiles(GemmDesc& g);
 int launch_tc_grouped(const GemmDesc* descs_dev, int ndesc, int total_tiles,
                       float lr, float momentum, cudaStream_t stream);
 size_t tc_factor_workspace_bytes(long long rows, int d);
+size_t tc_pad_bytes(const Operand& X, int n);
 int run_factor_tc(const Operand& X, long long rows, int d, float alpha,
                   float beta, float* out, void* workspace,
                   size_t workspace_bytes, cudaStream_t stream);

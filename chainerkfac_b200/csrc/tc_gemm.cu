@@ -222,8 +222,7 @@ static __device__ __align__(256) float g_ones_page[64] = {
 // where o_j is the k-dependent offset shared by all tasks of the thread.
 struct PTask {
   const float* p;   // column base (or the zero / ones page)
-  int m;            // strided: multiplier of the k-dependent offset (0 for
-                    // pages); im2col: (ky << 8) | kx, or -1 for pages
+  int m;            // multiplier of the k-dependent offset (0 for pages)
   unsigned soff;    // swizzled byte offset inside the tile, ~0u: idle task
 };
 
@@ -242,14 +241,14 @@ __device__ __forceinline__ void tc_task_setup(const Operand& op, int c0,
     v.soff = row < rows
                  ? (unsigned)(row * 128 + ((chunk ^ (row & 7)) << 4)) : ~0u;
     v.p = g_zero_page;
-    v.m = IM2COL ? -1 : 0;
+    v.m = 0;
     if (row < rows) {
       const int c = c0 + row;
       if (IM2COL) {
         const int info = kykx[row];
         if (info >= 0) {
           v.p = op.base + coff[row];
-          v.m = ((info >> 16) << 8) | (info & 0xff);
+          v.m = 1;
         } else if (info == -2) {
           v.p = g_ones_page;
         }
@@ -319,23 +318,16 @@ __device__ __forceinline__ void tc_load_tile(const Operand& op,
   const bool tail = k + 3 >= kend;
 
   if (IM2COL) {
+    // The tensor-core path always sees an unpadded convolution (a padded
+    // input is copied into a zero-bordered buffer first), so every tap of
+    // every pixel is in range and the gather needs no bounds logic.
     int pix[4];
-    unsigned rm[4], cm[4];   // bit ky / kx set: that tap lies inside the image
     {
       int n = ks.a, oy = ks.b, ox = ks.c;
       const int chw = op.C * op.H * op.W;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const int iy0 = oy * op.st - op.pd, ix0 = ox * op.st - op.pd;
-        pix[j] = n * chw + iy0 * op.W + ix0;
-        unsigned r = 0, c = 0;
-        for (int kk = 0; kk < op.ks; ++kk) {
-          r |= ((unsigned)(iy0 + kk) < (unsigned)op.H) ? (1u << kk) : 0u;
-          c |= ((unsigned)(ix0 + kk) < (unsigned)op.W) ? (1u << kk) : 0u;
-        }
-        if (k + j >= kend) r = 0;
-        rm[j] = r;
-        cm[j] = c;
+        pix[j] = (k + j < kend) ? n * chw + oy * op.st * op.W + ox * op.st : 0;
         if (++ox >= op.Wo) {
           ox = 0;
           if (++oy >= op.Ho) { oy = 0; ++n; }
@@ -345,19 +337,19 @@ __device__ __forceinline__ void tc_load_tile(const Operand& op,
 #pragma unroll
     for (int t = 0; t < NTASK; ++t) {
       if (task[t].soff == ~0u) continue;
-      const int aux = task[t].m;
-      const int ky = (aux >> 8) & 0xff, kx = aux & 0xff;
-      float x[4];
+      v[t].x = task[t].p[(long long)pix[0] * task[t].m];
+      v[t].y = task[t].p[(long long)pix[1] * task[t].m];
+      v[t].z = task[t].p[(long long)pix[2] * task[t].m];
+      v[t].w = task[t].p[(long long)pix[3] * task[t].m];
+    }
+    if (tail) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        // pages (aux < 0): valid wherever k is, offset 0
-        const bool valid = aux < 0 ? (k + j < kend)
-                                   : (((rm[j] >> ky) & (cm[j] >> kx) & 1u) != 0);
-        const float* q = valid ? task[t].p + (aux < 0 ? 0 : pix[j])
-                               : g_zero_page;
-        x[j] = *q;
+      for (int t = 0; t < NTASK; ++t) {
+        if (k + 0 >= kend) v[t].x = 0.f;
+        if (k + 1 >= kend) v[t].y = 0.f;
+        if (k + 2 >= kend) v[t].z = 0.f;
+        if (k + 3 >= kend) v[t].w = 0.f;
       }
-      v[t] = make_float4(x[0], x[1], x[2], x[3]);
     }
     return;
   }
@@ -713,31 +705,64 @@ tc_gemm_kernel(const GemmDesc* __restrict__ descs, int ndesc,
   }
 }
 
+// Copy an NCHW tensor into a buffer with a zero border of `pad` pixels.
+__global__ void pad_copy_kernel(const float* __restrict__ x, long long planes,
+                                int h, int w, int pad,
+                                float* __restrict__ out) {
+  const int hp = h + 2 * pad, wp = w + 2 * pad;
+  const long long total = planes * hp * wp;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+       i < total; i += stride) {
+    const long long plane = i / (hp * wp);
+    const int rem = (int)(i - plane * hp * wp);
+    const int y = rem / wp - pad, xx = rem - (rem / wp) * wp - pad;
+    float v = 0.f;
+    if ((unsigned)y < (unsigned)h && (unsigned)xx < (unsigned)w)
+      v = x[(plane * h + y) * w + xx];
+    out[i] = v;
+  }
+}
+
 // Sum split partial tiles (ascending split order), then scale / blend / store
 // the lower part and its mirror.
 __global__ void __launch_bounds__(256)
 tc_reduce_kernel(const float* __restrict__ partial, int tiles, int splits,
                  int d, float alpha, float beta, float* __restrict__ out) {
+  // Four lanes share one output element: lane q sums the splits
+  // q, q+4, q+8, ... (always in that order), then the four sums are added in
+  // a fixed tree, so the result does not depend on scheduling.
   int bi, bj;
   tc_tri_tile(blockIdx.x, bi, bj);
   const int m0 = bi * TC_BM, n0 = bj * TC_BN;
-  const int c = threadIdx.x;
-  const int gc = n0 + c;
-  for (int rr = 0; rr < 8; ++rr) {
-    const int r = blockIdx.y * 8 + rr;
-    const int gr = m0 + r;
-    if (gr >= d || gc >= d || gc > gr) continue;
-    const float* p = partial + (long long)blockIdx.x * (TC_BM * TC_BN) +
-                     r * TC_BN + c;
-    float s = 0.f;
-    for (int sp = 0; sp < splits; ++sp)
-      s += p[(long long)sp * tiles * (TC_BM * TC_BN)];
-    float* q = out + (long long)gr * d + gc;
-    float v = alpha * s;
-    if (beta != 0.f) v += beta * (*q);
-    *q = v;
-    if (gc < gr) out[(long long)gc * d + gr] = v;
+  const int rows = min(TC_BM, d - m0);
+  const int cols = min(min(TC_BN, d - n0), m0 + TC_BM - n0);
+  const int e = (blockIdx.y * 256 + threadIdx.x) >> 2;
+  const int q = threadIdx.x & 3;
+  const bool live = e < rows * cols;
+  const int r = live ? e / cols : 0, c = live ? e - (e / cols) * cols : 0;
+  const float* p = partial + (long long)blockIdx.x * (TC_BM * TC_BN) +
+                   r * TC_BN + c;
+  const long long sstride = (long long)tiles * (TC_BM * TC_BN);
+  float s0 = 0.f, s1 = 0.f;
+  if (live) {
+    int sp = q;
+    for (; sp + 4 < splits; sp += 8) {
+      s0 += p[sp * sstride];
+      s1 += p[(sp + 4) * sstride];
+    }
+    if (sp < splits) s0 += p[sp * sstride];
   }
+  float s = s0 + s1;
+  s += __shfl_xor_sync(0xffffffffu, s, 1);
+  s += __shfl_xor_sync(0xffffffffu, s, 2);
+  const int gr = m0 + r, gc = n0 + c;
+  if (!live || q != 0 || gc > gr) return;
+  float* o = out + (long long)gr * d + gc;
+  float v = alpha * s;
+  if (beta != 0.f) v += beta * (*o);
+  *o = v;
+  if (gc < gr) out[(long long)gc * d + gr] = v;
 }
 
 // ------------------------------------------------------------------ host side
@@ -815,11 +840,42 @@ size_t tc_factor_workspace_bytes(long long rows, int d) {
   return (size_t)s.splits * s.tiles * TC_BM * TC_BN * sizeof(float);
 }
 
-int run_factor_tc(const Operand& X, long long rows, int d, float alpha,
+size_t tc_pad_bytes(const Operand& X, int n) {
+  if (X.mode != 1 || X.pd == 0) return 0;
+  size_t e = (size_t)n * X.C * (X.H + 2 * X.pd) * (X.W + 2 * X.pd);
+  return (e * sizeof(float) + 255) & ~(size_t)255;
+}
+
+int run_factor_tc(const Operand& X_in, long long rows, int d, float alpha,
                   float beta, float* out, void* workspace,
                   size_t workspace_bytes, cudaStream_t stream) {
   int rc = tc_prepare();
   if (rc != KFAC_OK) return rc;
+  Operand X = X_in;
+  if (X.mode == 1 && X.pd > 0) {
+    // zero-bordered copy first; the gather then runs without bounds checks
+    const int n = (int)(rows / ((long long)X.Ho * X.Wo));
+    const size_t pad_bytes = tc_pad_bytes(X, n);
+    if (workspace == nullptr || workspace_bytes < pad_bytes)
+      return fail(KFAC_ERR_WORKSPACE,
+                  "factor: workspace of %zu bytes needed for the padded "
+                  "input, %zu given", pad_bytes, workspace_bytes);
+    float* padded = static_cast<float*>(workspace);
+    const long long planes = (long long)n * X.C;
+    const long long total = planes * (X.H + 2 * X.pd) * (X.W + 2 * X.pd);
+    KFAC_REQUIRE(total < (1LL << 31), "factor: padded input too large");
+    int blocks = (int)((total + 1023) / 1024);
+    if (blocks > sm_count() * 16) blocks = sm_count() * 16;
+    pad_copy_kernel<<<blocks, 256, 0, stream>>>(X.base, planes, X.H, X.W, X.pd,
+                                                padded);
+    KFAC_LAUNCH_CHECK("pad_copy_kernel");
+    X.base = padded;
+    X.H += 2 * X.pd;
+    X.W += 2 * X.pd;
+    X.pd = 0;
+    workspace = static_cast<char*>(workspace) + pad_bytes;
+    workspace_bytes -= pad_bytes;
+  }
   KFAC_REQUIRE(rows < (1LL << 31) && (long long)rows * d < (1LL << 40),
                "factor: contraction of %lld rows is too long", rows);
   TcFactorSplit s = tc_factor_split(rows, d);
@@ -856,7 +912,8 @@ int run_factor_tc(const Operand& X, long long rows, int d, float alpha,
         nullptr, 1, g, 0.f, 0.f);
   KFAC_LAUNCH_CHECK("tc_gemm_kernel");
   if (s.splits > 1) {
-    dim3 rgrid(s.tiles, TC_BM / 8);
+    const int rmax = d < TC_BM ? d : TC_BM, cmax = d < TC_BN ? d : TC_BN;
+    dim3 rgrid(s.tiles, (rmax * cmax * 4 + 255) / 256);
     tc_reduce_kernel<<<rgrid, 256, 0, stream>>>(g.partial, s.tiles, s.splits, d,
                                                 alpha, beta, out);
     KFAC_LAUNCH_CHECK("tc_reduce_kernel");

@@ -86,7 +86,8 @@ def factor_conv_input(x, ksize, stride, pad, add_ones_col=False, alpha=1.0,
     wo = (w + 2 * pad - ksize) // stride + 1
     d = c * ksize * ksize + int(bool(add_ones_col))
     out = _factor_out(d, out, beta, x.device)
-    nbytes = lib.kfac_factor_workspace_bytes(n * ho * wo, d)
+    nbytes = lib.kfac_factor_conv_workspace_bytes(
+        n, c, h, w, ksize, stride, pad, int(bool(add_ones_col)))
     ws = _factor_ws.get(nbytes, x.device)
     _lib.check(lib.kfac_factor_conv_input(
         _p(x), n, c, h, w, ksize, stride, pad, int(bool(add_ones_col)), alpha,

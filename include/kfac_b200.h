@@ -70,7 +70,13 @@ int kfac_factor_dense(const float* x, int64_t rows, int d_in, int64_t ld,
  * (c, ky, kx) with c slowest, zero padding, square kernel, then the optional
  * ones column.  Replaces FisherBlockConvolution2D.compute_A,
  * optimizers/fisher_blocks/connections/convolution_2d.py:19-41 (including the
- * chainer.functions.im2col call, the NHWC transpose and column_stack). */
+ * chainer.functions.im2col call, the NHWC transpose and column_stack).
+ * Workspace: kfac_factor_conv_workspace_bytes (partial tiles plus, on the
+ * tensor-core engine, a zero-bordered copy of the input when pad > 0, which
+ * lets the gather run without bounds checks). */
+size_t kfac_factor_conv_workspace_bytes(int n, int c, int h, int w, int ksize,
+                                        int stride, int pad,
+                                        int add_ones_col);
 int kfac_factor_conv_input(const float* x, int n, int c, int h, int w,
                            int ksize, int stride, int pad, int add_ones_col,
                            float alpha, float beta, float* out,
