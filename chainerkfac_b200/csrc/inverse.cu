@@ -100,115 +100,156 @@ __global__ void damp_copy_kernel(const MatInfo* __restrict__ mats,
   }
 }
 
-// Factor one diagonal block (<= 128 x 128) of W in shared memory and invert
-// the resulting triangle: W_jj <- L_jj (lower), X_jj <- L_jj^-1 (lower, upper
-// part zero).  One CTA per matrix that still has a block at `step`.
+// Factor one diagonal block (<= 128 x 128) of W and invert the resulting
+// triangle: W_jj <- L_jj (lower), X_jj <- L_jj^-1 (lower, upper part zero).
+// One CTA of 256 threads per matrix that still has a block at `step`; thread
+// (br, bc) = (tid % 16, tid / 16) keeps the 8 x 8 block (br, bc) in registers.
+// Both sweeps go column by column with one barrier per column: the column of
+// L (Cholesky) or the finished row of X (inverse) is broadcast through a
+// double-buffered line of shared memory and every thread applies the rank-1
+// update to its register block.
 __global__ void __launch_bounds__(256)
 chol_diag_kernel(const MatInfo* __restrict__ mats, const int* __restrict__ ids,
                  int step, int* __restrict__ info) {
-  extern __shared__ float dsm[];
-  float (*S)[DLD] = reinterpret_cast<float (*)[DLD]>(dsm);
-  float (*X)[DLD] = reinterpret_cast<float (*)[DLD]>(dsm + DB * DLD);
-  float* dg = dsm + 2 * DB * DLD;
+  extern __shared__ __align__(16) float dsm[];
+  float (*Lt)[DB + 4] = reinterpret_cast<float (*)[DB + 4]>(dsm);  // L^T
+  float (*line)[DB] = reinterpret_cast<float (*)[DB]>(dsm + DB * (DB + 4));
+  float* rdiag = dsm + DB * (DB + 4) + 2 * DB;
   const int id = ids[blockIdx.x];
   const MatInfo mi = mats[id];
-  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const int tid = threadIdx.x, br = tid & 15, bc = tid >> 4;
+  const int lane = tid & 31;
   const int o = step * DB;
   const int bs = min(DB, mi.d - o);
-  const int pb = (bs + 15) & ~15;
+  const int nkb = (bs + 7) >> 3;
   const long long ld = mi.d;
   float* Wd = mi.W + (long long)o * ld + o;
   float* Xd = mi.X + (long long)o * ld + o;
 
-  for (int idx = tid; idx < pb * pb; idx += 256) {
-    int i = idx / pb, j = idx - i * pb;
-    float v = 0.f;
-    if (i < bs && j <= i) v = Wd[i * ld + j];
-    else if (i == j) v = 1.f;
-    S[i][j] = v;
-    X[i][j] = 0.f;
+  float a[8][8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int gi = 8 * br + i;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int gj = 8 * bc + j;
+      float v = (gi == gj) ? 1.f : 0.f;          // identity beyond the block
+      if (gi < bs && gj <= gi) v = Wd[gi * ld + gj];
+      a[i][j] = v;
+    }
   }
 
-  for (int k = 0; k < pb; ++k) {
-    __syncthreads();
-    float akk = S[k][k];
-    if (!(akk > 0.f)) {
-      if (tid == 0) atomicCAS(&info[id], 0, o + k + 1);
-      akk = 1.f;
-    }
-    const float l = sqrtf(akk);
-    const float rl = 1.f / l;
-    if (tid == 0) dg[k] = l;
-    for (int i = k + 1 + tid; i < pb; i += 256) S[i][k] *= rl;
-    __syncthreads();
-    const int n = pb - k - 1;
-    for (int ii = ty; ii < n; ii += 16) {
-      const int i = k + 1 + ii;
-      const float lik = S[i][k];
-      for (int jj = tx; jj <= ii; jj += 16) {
-        const int j = k + 1 + jj;
-        S[i][j] -= lik * S[j][k];
+  // ---- Cholesky, right-looking, one column per barrier
+  int buf = 0;
+  for (int kb = 0; kb < nkb; ++kb) {
+#pragma unroll
+    for (int lk = 0; lk < 8; ++lk) {
+      const int k = 8 * kb + lk;
+      // the pivot lives in thread (kb, kb) of the half-warp that owns block
+      // column kb; every lane takes part in the shuffle
+      float piv = __shfl_sync(0xffffffffu, a[lk][lk], (lane & 16) | kb);
+      if (bc == kb) {
+        if (!(piv > 0.f)) {
+          if (br == kb) atomicCAS(&info[id], 0, o + k + 1);
+          piv = 1.f;
+        }
+        const float l = sqrtf(piv);
+        const float rl = 1.f / l;
+        if (br == kb) rdiag[k] = rl;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int gi = 8 * br + i;
+          float v = 0.f;
+          if (gi > k) { v = a[i][lk] * rl; a[i][lk] = v; }
+          else if (gi == k) a[i][lk] = l;
+          line[buf][gi] = v;                       // strictly below the pivot
+        }
       }
+      __syncthreads();
+      if (br >= kb && bc >= kb && bc <= br) {
+        const float4 r0 = *reinterpret_cast<const float4*>(&line[buf][8 * br]);
+        const float4 r1 = *reinterpret_cast<const float4*>(&line[buf][8 * br + 4]);
+        const float4 c0 = *reinterpret_cast<const float4*>(&line[buf][8 * bc]);
+        const float4 c1 = *reinterpret_cast<const float4*>(&line[buf][8 * bc + 4]);
+        const float cr[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+        const float cc[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+          for (int j = 0; j < 8; ++j) a[i][j] = fmaf(-cr[i], cc[j], a[i][j]);
+      }
+      buf ^= 1;
     }
   }
+
+  // ---- L to global memory (lower part) and, transposed, to shared memory
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int gi = 8 * br + i;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int gj = 8 * bc + j;
+      if (gi < bs && gj <= gi) Wd[gi * ld + gj] = a[i][j];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int gj = 8 * bc + j;
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = (8 * br + i > gj) ? a[i][j] : 0.f;
+    *reinterpret_cast<float4*>(&Lt[gj][8 * br]) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(&Lt[gj][8 * br + 4]) = make_float4(v[4], v[5], v[6], v[7]);
+  }
+  // ---- inverse of the triangle: X starts as I; at column k row k is final
+  // after scaling by 1 / l_kk, and every row below subtracts L[i][k] * X[k][:]
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) a[i][j] = (8 * br + i == 8 * bc + j) ? 1.f : 0.f;
   __syncthreads();
-  if (tid < pb) S[tid][tid] = dg[tid];
-  __syncthreads();
-
-  for (int idx = tid; idx < bs * bs; idx += 256) {
-    int i = idx / bs, j = idx - i * bs;
-    if (j <= i) Wd[i * ld + j] = S[i][j];
-  }
-
-  // inverse of the 16x16 diagonal blocks, one thread per column
-  if (tid < pb) {
-    const int base = tid & ~15, c = tid & 15;
-    X[base + c][base + c] = 1.f / S[base + c][base + c];
-    for (int i = c + 1; i < 16; ++i) {
-      float s = 0.f;
-      for (int k = c; k < i; ++k) s += S[base + i][base + k] * X[base + k][base + c];
-      X[base + i][base + c] = -s / S[base + i][base + i];
+  for (int kb = 0; kb < nkb; ++kb) {
+#pragma unroll
+    for (int lk = 0; lk < 8; ++lk) {
+      const int k = 8 * kb + lk;
+      if (br == kb) {
+        const float rl = rdiag[k];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int gj = 8 * bc + j;
+          float v = 0.f;
+          if (gj <= k) { v = a[lk][j] * rl; a[lk][j] = v; }
+          line[buf][gj] = v;
+        }
+      }
+      __syncthreads();
+      if (br >= kb && bc <= kb) {
+        const float4 x0 = *reinterpret_cast<const float4*>(&line[buf][8 * bc]);
+        const float4 x1 = *reinterpret_cast<const float4*>(&line[buf][8 * bc + 4]);
+        const float4 l0 = *reinterpret_cast<const float4*>(&Lt[k][8 * br]);
+        const float4 l1 = *reinterpret_cast<const float4*>(&Lt[k][8 * br + 4]);
+        const float xr[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+        const float lc[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+          for (int j = 0; j < 8; ++j) a[i][j] = fmaf(-lc[i], xr[j], a[i][j]);
+      }
+      buf ^= 1;
     }
   }
-  __syncthreads();
-
-  // recursive doubling: X21 = -X22 * (L21 * X11)
-  for (int b = 16; b < pb; b <<= 1) {
-    const int nch = (pb + 2 * b - 1) / (2 * b);
-    const int total = nch * b * b;
-    for (int idx = tid; idx < total; idx += 256) {
-      int ch = idx / (b * b);
-      int rem = idx - ch * b * b;
-      int m = rem / b, n = rem - m * b;
-      int s = ch * 2 * b;
-      if (s + b >= pb) continue;
-      int r = min(b, pb - s - b);
-      if (m >= r) continue;
-      float t = 0.f;
-      for (int k = n; k < b; ++k) t += S[s + b + m][s + k] * X[s + k][s + n];
-      X[s + n][s + b + m] = t;  // parked in the unused upper block
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int gi = 8 * br + i;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int gj = 8 * bc + j;
+      if (gi < bs && gj < bs) Xd[gi * ld + gj] = (gj <= gi) ? a[i][j] : 0.f;
     }
-    __syncthreads();
-    for (int idx = tid; idx < total; idx += 256) {
-      int ch = idx / (b * b);
-      int rem = idx - ch * b * b;
-      int m = rem / b, n = rem - m * b;
-      int s = ch * 2 * b;
-      if (s + b >= pb) continue;
-      int r = min(b, pb - s - b);
-      if (m >= r) continue;
-      float t = 0.f;
-      for (int k = 0; k <= m; ++k) t += X[s + b + m][s + b + k] * X[s + n][s + b + k];
-      X[s + b + m][s + n] = -t;
-    }
-    __syncthreads();
-  }
-
-  for (int idx = tid; idx < bs * bs; idx += 256) {
-    int i = idx / bs, j = idx - i * bs;
-    Xd[i * ld + j] = (j <= i) ? X[i][j] : 0.f;
   }
 }
+
+constexpr size_t kDiagSmemBytes = (DB * (DB + 4) + 3 * DB) * sizeof(float);
 
 struct Launch {
   int kind;      // 0 diag kernel, 1 grouped gemm
@@ -463,7 +504,7 @@ extern "C" int kfac_inverse_plan_create(
   if (e == cudaSuccess)
     e = cudaFuncSetAttribute(chol_diag_kernel,
                              cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)((2 * DB * DLD + DB) * sizeof(float)));
+                             (int)kDiagSmemBytes);
   if (e != cudaSuccess) {
     kfac_inverse_plan_destroy(p);
     return fail(KFAC_ERR_CUDA, "inverse_plan_create: %s", cudaGetErrorString(e));
@@ -489,10 +530,9 @@ extern "C" int kfac_inverse_plan_run(kfac_inverse_plan* p, float damping,
     damp_copy_kernel<<<grid, 256, 0, st>>>(p->mats_dev, p->add_dev);
     KFAC_LAUNCH_CHECK("damp_copy_kernel");
   }
-  const size_t dsm = (2 * DB * DLD + DB) * sizeof(float);
   for (const Launch& l : p->launches) {
     if (l.kind == 0) {
-      chol_diag_kernel<<<l.n, 256, dsm, st>>>(p->mats_dev, p->ids_dev + l.off,
+      chol_diag_kernel<<<l.n, 256, kDiagSmemBytes, st>>>(p->mats_dev, p->ids_dev + l.off,
                                               l.step, info);
       KFAC_LAUNCH_CHECK("chol_diag_kernel");
     } else {

@@ -822,7 +822,7 @@ static TcFactorSplit tc_factor_split(long long rows, int d) {
   s.tiles = tc_tiles(g);
   long long target = 2LL * sm_count();
   long long by_tiles = (target + s.tiles - 1) / s.tiles;
-  long long by_rows = (rows + 2047) / 2048;  // >= 64 k-blocks per CTA
+  long long by_rows = (rows + 511) / 512;  // >= 16 k-blocks per CTA
   long long sp = by_tiles < by_rows ? by_tiles : by_rows;
   if (s.tiles >= sm_count()) sp = 1;
   if (sp < 1) sp = 1;
