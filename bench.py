@@ -40,6 +40,7 @@ DAMPING = 2.5e-4
 LR = 0.01
 MOMENTUM = 0.9
 WORKLOAD = 'resnet50_kfac_step_b32_224'
+OWNERSHIP = 'balanced'   # layer ownership at N > 1 ('reference': by count)
 
 
 def layer_table():
@@ -222,6 +223,92 @@ class DeviceWorkload(object):
         self.precondition()
 
 
+class DistributedWorkload(DeviceWorkload):
+    """The same per-GPU work as DeviceWorkload for the factor build (every rank
+    builds all factors from its own batch), then the reference's two
+    exchanges: gradients and packed factors are reduce-scattered to the
+    layer's owner, the owner averages them into its running average, inverts
+    and preconditions/updates only its own layers, and the updated weights
+    are all-gathered.  Ownership is cost-balanced by default (OWNERSHIP);
+    'reference' is the reference's contiguous split of the layer list by
+    count."""
+
+    def __init__(self, device, seed, comm):
+        super(DistributedWorkload, self).__init__(device, seed)
+        import torch
+        from oracle import kfac_oracle as orc
+        self.comm = comm
+        from chainerkfac_b200.optimizers.kfac import balanced_split
+        cnt = len(self.layers)
+        if OWNERSHIP == 'balanced':
+            self.indices = balanced_split(
+                [float(dA) ** 3 + float(dG) ** 3
+                 for dA, dG, _, _ in self.dims], comm.size)
+        else:
+            self.indices = orc.split_indices(cnt, comm.size)
+        self.mine = self.indices[comm.rank]
+        self.cov = [torch.zeros_like(e) for e in self.ema]
+        self.plan.close()
+        own = self.mine
+        self.plan = self.ops.InversePlan(
+            [self.ema[2 * i + j] for i in own for j in (0, 1)],
+            [self.inv[2 * i + j] for i in own for j in (0, 1)],
+            [k ^ 1 for k in range(2 * len(own))],
+            [k & 1 for k in range(2 * len(own))])
+        self.rs_arrays = []
+        self.ag_arrays = []
+        for idx in self.indices:
+            rs, ag = [], []
+            for i in idx:
+                # sorted parameter names: W before b
+                rs.append((self.gW[i], False))
+                if self.gb[i] is not None:
+                    rs.append((self.gb[i], False))
+                rs.append((self.cov[2 * i], True))
+                rs.append((self.cov[2 * i + 1], True))
+                ag.append((self.W[i], False))
+                if self.b[i] is not None:
+                    ag.append((self.b[i], False))
+            self.rs_arrays.append(rs)
+            self.ag_arrays.append(ag)
+
+    def factors(self):
+        ops = self.ops
+        for i, l in enumerate(self.layers):
+            n = l['n']
+            A, G = self.cov[2 * i], self.cov[2 * i + 1]
+            if l['kind'] == 'conv':
+                ops.factor_conv_input(self.x[i], l['k'], l['stride'], l['pad'],
+                                      l['bias'], alpha=1.0 / n, out=A)
+                ops.factor_conv_grad(self.gy[i], alpha=n / float(l['hout'] ** 2),
+                                     out=G)
+            else:
+                ops.factor_dense(self.x[i], l['bias'], alpha=1.0 / n, out=A)
+                ops.factor_dense(self.gy[i], False, alpha=float(n), out=G)
+
+    def inverses(self):
+        # exchange 1, then the owner's running average and inverses
+        self.comm.reduce_scatter_v_arrays(self.rs_arrays)
+        r, rest = (1.0, 0.0) if self.first else (DECAY, 1.0 - DECAY)
+        for i in self.mine:
+            for j in (0, 1):
+                self.ops.axpby(r, self.cov[2 * i + j], rest,
+                               self.ema[2 * i + j], self.ema[2 * i + j])
+        self.first = False
+        self.plan.run(DAMPING, True)
+
+    def precondition(self):
+        own = self.mine
+        self.ops.precondition(
+            [self.inv[2 * i + 1] for i in own], [self.inv[2 * i] for i in own],
+            [self.gW[i] for i in own], [self.gb[i] for i in own], None, None,
+            [self.W[i] for i in own], [self.b[i] for i in own],
+            [self.vW[i] for i in own], [self.vb[i] for i in own], lr=LR,
+            momentum=MOMENTUM)
+        # exchange 2: updated weights to everyone
+        self.comm.all_gather_v_arrays(self.ag_arrays)
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -238,7 +325,12 @@ def run_ours(args):
         dist.init_process_group('nccl', device_id=device)
     lib = _lib.load()
 
-    wl = DeviceWorkload(device, seed=1234 + rank)
+    if world > 1:
+        from chainerkfac_b200.communicators import create_communicator
+        wl = DistributedWorkload(device, 1234 + rank,
+                                 create_communicator('pure_nccl'))
+    else:
+        wl = DeviceWorkload(device, seed=1234 + rank)
     flops = algorithmic_flops(wl.dims)
 
     def barrier():
@@ -308,7 +400,8 @@ def run_ours(args):
                        'l2_flush': 'inputs larger than L2 (%.1f GB of '
                                    'activations and gradients per step)'
                                    % (wl.input_bytes / 1e9),
-                       'parallelism': 'dp%d' % world},
+                       'parallelism': 'dp%d' % world,
+                       'ownership': OWNERSHIP if world > 1 else None},
             'stages': stage,
             'factor_inverse_ms': float(phase[0] + phase[1]),
             'roofline': {
@@ -528,9 +621,14 @@ def main():
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--no-e2e', action='store_true')
     ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--ownership', default=None,
+                    choices=['balanced', 'reference'])
     ap.add_argument('--micro', choices=sorted(MICRO_CASES), default=None,
                     help='time one single-kernel case instead of the step')
     args = ap.parse_args()
+    if args.ownership:
+        global OWNERSHIP
+        OWNERSHIP = args.ownership
     if args.micro:
         run_micro(args)
     elif args.impl == 'reference':

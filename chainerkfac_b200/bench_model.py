@@ -73,7 +73,7 @@ def build_training_step(device, batch, world, rank, cov_ema_decay, damping,
                   damping=damping, constructor=ctor)
     if world > 1:
         comm = ck.create_communicator('pure_nccl')
-        opt = ck.DistributedKFAC(comm, **kwargs)
+        opt = ck.DistributedKFAC(comm, ownership='balanced', **kwargs)
     else:
         opt = ck.KFAC(**kwargs)
     opt.setup(model)

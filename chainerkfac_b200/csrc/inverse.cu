@@ -90,10 +90,13 @@ __global__ void damp_copy_kernel(const MatInfo* __restrict__ mats,
   const float a = add[blockIdx.y];
   const long long total = (long long)mi.d * mi.d;
   const long long stride = (long long)gridDim.x * blockDim.x;
+  // only the lower triangle (and the rest of each diagonal 128-block, which
+  // the trailing updates read-modify-write) is ever used
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
        i < total; i += stride) {
     int r = (int)(i / mi.d);
     int c = (int)(i - (long long)r * mi.d);
+    if (c > (r | (DB - 1))) continue;
     float v = mi.F[i];
     if (r == c) v += a;
     mi.W[i] = v;
@@ -153,8 +156,11 @@ chol_diag_kernel(const MatInfo* __restrict__ mats, const int* __restrict__ ids,
           if (br == kb) atomicCAS(&info[id], 0, o + k + 1);
           piv = 1.f;
         }
-        const float l = sqrtf(piv);
-        const float rl = 1.f / l;
+        // rsqrt + one Newton step: full fp32 accuracy without the slow
+        // IEEE square root and division on the per-column critical path
+        float rl = rsqrtf(piv);
+        rl = rl * (1.5f - 0.5f * piv * rl * rl);
+        const float l = piv * rl;
         if (br == kb) rdiag[k] = rl;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {

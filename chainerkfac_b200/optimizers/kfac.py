@@ -427,8 +427,15 @@ class DistributedKFAC(KFAC):
     all-gathered."""
 
     def __init__(self, comm, *args, communicate_after_forward=False,
-                 only_pic_update_weight=True, **kwargs):
+                 only_pic_update_weight=True, ownership='reference',
+                 **kwargs):
         super(DistributedKFAC, self).__init__(*args, **kwargs)
+        if ownership not in ('reference', 'balanced'):
+            raise ValueError("ownership must be 'reference' or 'balanced'")
+        # 'reference': contiguous split of the name-sorted block list by count
+        # (kfac.py:344-348).  'balanced': longest-processing-time assignment
+        # by inverse cost (sum of d^3), which evens out the owners' work.
+        self.ownership = ownership
         self.comm = comm
         self.only_pic_update_weight = only_pic_update_weight
         cuda = torch.cuda.is_available()
@@ -445,8 +452,12 @@ class DistributedKFAC(KFAC):
         super(DistributedKFAC, self).setup(link)
         local_size = self.comm.size
         local_rank = self.comm.rank
-        indices = np.array_split(np.arange(len(self.fblocks)), local_size)
-        indices = [local_indices.tolist() for local_indices in indices]
+        if self.ownership == 'balanced':
+            indices = balanced_split(
+                [block_cost(fb) for fb in self.fblocks], local_size)
+        else:
+            indices = np.array_split(np.arange(len(self.fblocks)), local_size)
+            indices = [local_indices.tolist() for local_indices in indices]
         local_indices = indices[local_rank]
         self.indices = indices
         self.local_indices = local_indices
@@ -529,6 +540,30 @@ class DistributedKFAC(KFAC):
         if not self.only_pic_update_weight:
             return False
         return super(DistributedKFAC, self)._can_fuse(param)
+
+
+def block_cost(fblock):
+    """Inverse cost of a block: sum of d^3 over its factors."""
+    link = fblock.link
+    if hasattr(link, 'W'):
+        dG = link.W.shape[0]
+        dA = link.W.size // dG + (0 if link.b is None else 1)
+        return float(dA) ** 3 + float(dG) ** 3
+    return float(2 * link.gamma.size) ** 3
+
+
+def balanced_split(costs, size):
+    """Longest-processing-time assignment of blocks to `size` owners; each
+    owner's list is ascending.  Deterministic, so every rank computes the same
+    partition."""
+    loads = [0.0] * size
+    owned = [[] for _ in range(size)]
+    order = sorted(range(len(costs)), key=lambda i: (-costs[i], i))
+    for i in order:
+        r = min(range(size), key=lambda q: (loads[q], q))
+        owned[r].append(i)
+        loads[r] += costs[i]
+    return [sorted(o) for o in owned]
 
 
 def extract(blocks, indices, extractor):

@@ -52,6 +52,21 @@ def test_public_interface_and_defaults():
         ck.KFAC(use_cholesky=False).setup(small_model())
 
 
+def test_balanced_ownership_is_deterministic_and_even():
+    from chainerkfac_b200.optimizers.kfac import balanced_split
+    dims = [orc.layer_dims(l) for l in orc.resnet50_layers()]
+    costs = [float(a) ** 3 + float(g) ** 3 for a, g, _, _ in dims]
+    for size in (2, 4, 8):
+        owned = balanced_split(costs, size)
+        assert sorted(i for o in owned for i in o) == list(range(54))
+        loads = [sum(costs[i] for i in o) for o in owned]
+        ref = [sum(costs[i] for i in o) for o in orc.split_indices(54, size)]
+        assert max(loads) <= max(ref)
+        assert owned == balanced_split(costs, size)
+    two = [sum(costs[i] for i in o) for o in balanced_split(costs, 2)]
+    assert max(two) / (sum(two) / 2) < 1.02
+
+
 def test_adjust_momentum_rule():
     from chainerkfac_b200.optimizers.kfac import KFACUpdateRule, _base
     hp = _base.Hyperparameter()

@@ -1,0 +1,84 @@
+"""DistributedKFAC on two GPUs (one process each, NCCL) against single-process
+KFAC on the concatenated batch.  Skipped where fewer than two GPUs exist."""
+
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+WORKER = r'''
+import os, sys
+sys.path.insert(0, %(root)r)
+import numpy as np, torch, torch.distributed as dist
+import torch.nn.functional as F
+from torch import nn
+import chainerkfac_b200 as ck
+
+rank = int(os.environ['RANK']); world = int(os.environ['WORLD_SIZE'])
+torch.cuda.set_device(rank)
+dist.init_process_group('nccl', device_id=torch.device('cuda', rank))
+
+def make():
+    torch.manual_seed(7)
+    return nn.Sequential(nn.Conv2d(3, 6, 3, 1, 1), nn.ReLU(),
+                         nn.Conv2d(6, 8, 3, 2, 1, bias=False), nn.ReLU(),
+                         nn.AdaptiveAvgPool2d(1), nn.Flatten(),
+                         nn.Linear(8, 5)).cuda()
+
+g = torch.Generator().manual_seed(3)
+X = torch.randn(8, 3, 8, 8, generator=g).cuda()
+T = torch.randint(0, 5, (8,), generator=g).cuda()
+half = 8 // world
+xs, ts = X[rank * half:(rank + 1) * half], T[rank * half:(rank + 1) * half]
+
+for pic in (True, False):
+    model = make()
+    comm = ck.create_communicator('pure_nccl')
+    opt = ck.DistributedKFAC(comm, lr=0.05, momentum=0.9, cov_ema_decay=1.0,
+                             damping=1e-2, only_pic_update_weight=pic)
+    opt.setup(model)
+    lossfun = lambda a, b: F.cross_entropy(model(a), b)
+    opt.update(lossfun, xs, ts)          # first call: broadcast only
+    assert opt.t == 0
+    opt.update(lossfun, xs, ts)
+    assert opt.t == 1
+    # every rank holds the same weights afterwards
+    flat = torch.cat([p.detach().reshape(-1) for p in model.parameters()])
+    other = [torch.empty_like(flat) for _ in range(world)]
+    dist.all_gather(other, flat)
+    assert all(torch.equal(other[0], o) for o in other), 'ranks diverged'
+    if rank == 0:
+        # reference: one process, whole batch.  Gradients of the mean loss
+        # average exactly; factors of the halves average to the whole-batch
+        # factor for A (scaled 1/n_local) and G (per-rank n_local * gy^T gy).
+        ref = make()
+        o1 = ck.KFAC(lr=0.05, momentum=0.9, cov_ema_decay=1.0, damping=1e-2)
+        o1.setup(ref)
+        o1.update(lambda a, b: F.cross_entropy(ref(a), b), X, T)
+        for (n1, p1), (n2, p2) in zip(ref.named_parameters(),
+                                      model.named_parameters()):
+            err = float((p1 - p2).norm() / p1.norm())
+            assert err < 2e-3, (pic, n1, err)
+dist.barrier()
+if rank == 0:
+    print('DISTRIBUTED_OK')
+dist.destroy_process_group()
+'''
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason='needs 2 GPUs')
+def test_distributed_kfac_two_gpus(tmp_path):
+    script = tmp_path / 'worker.py'
+    script.write_text(WORKER % {'root': ROOT})
+    env = dict(os.environ, NCCL_NVLS_ENABLE='0')
+    res = subprocess.run(
+        [sys.executable, '-m', 'torch.distributed.run', '--nnodes=1',
+         '--nproc-per-node=2', '--master-addr', '127.0.0.1', '--master-port',
+         '29671', str(script)], env=env, stdout=subprocess.PIPE,
+        stderr=subprocess.STDOUT, text=True, timeout=600)
+    assert 'DISTRIBUTED_OK' in res.stdout, res.stdout[-3000:]
