@@ -183,23 +183,28 @@ class DeviceWorkload(object):
         self.first = True
         self.input_bytes = sum(t.numel() * 4 for t in self.x + self.gy)
 
-    def factors(self):
-        ops = self.ops
-        r, rest = (1.0, 0.0) if self.first else (DECAY, 1.0 - DECAY)
+    def factor_items(self, outs, r, rest):
+        ops, items = self.ops, []
         for i, l in enumerate(self.layers):
             n = l['n']
-            A, G = self.ema[2 * i], self.ema[2 * i + 1]
+            A, G = outs[2 * i], outs[2 * i + 1]
             if l['kind'] == 'conv':
-                ops.factor_conv_input(self.x[i], l['k'], l['stride'], l['pad'],
-                                      l['bias'], alpha=r / n, beta=rest, out=A)
-                ops.factor_conv_grad(self.gy[i],
-                                     alpha=r * n / float(l['hout'] ** 2),
-                                     beta=rest, out=G)
+                items.append(ops.conv_input_item(
+                    self.x[i], l['k'], l['stride'], l['pad'], l['bias'],
+                    r / n, rest, A))
+                items.append(ops.conv_grad_item(
+                    self.gy[i], r * n / float(l['hout'] ** 2), rest, G))
             else:
-                ops.factor_dense(self.x[i], l['bias'], alpha=r / n, beta=rest,
-                                 out=A)
-                ops.factor_dense(self.gy[i], False, alpha=r * n, beta=rest,
-                                 out=G)
+                items.append(ops.dense_item(self.x[i], l['bias'], r / n, rest,
+                                            A))
+                items.append(ops.dense_item(self.gy[i], False, r * n, rest, G))
+        return items
+
+    def factors(self):
+        # all 108 factors in one grouped call, running average fused in
+        r, rest = (1.0, 0.0) if self.first else (DECAY, 1.0 - DECAY)
+        self.ops.factor_group(self.factor_items(self.ema, r, rest),
+                              self.ema[0].device)
         self.first = False
 
     def inverses(self):
@@ -273,18 +278,8 @@ class DistributedWorkload(DeviceWorkload):
             self.ag_arrays.append(ag)
 
     def factors(self):
-        ops = self.ops
-        for i, l in enumerate(self.layers):
-            n = l['n']
-            A, G = self.cov[2 * i], self.cov[2 * i + 1]
-            if l['kind'] == 'conv':
-                ops.factor_conv_input(self.x[i], l['k'], l['stride'], l['pad'],
-                                      l['bias'], alpha=1.0 / n, out=A)
-                ops.factor_conv_grad(self.gy[i], alpha=n / float(l['hout'] ** 2),
-                                     out=G)
-            else:
-                ops.factor_dense(self.x[i], l['bias'], alpha=1.0 / n, out=A)
-                ops.factor_dense(self.gy[i], False, alpha=float(n), out=G)
+        self.ops.factor_group(self.factor_items(self.cov, 1.0, 0.0),
+                              self.cov[0].device)
 
     def inverses(self):
         # exchange 1, then the owner's running average and inverses

@@ -21,6 +21,18 @@ I64 = ctypes.c_int64
 F = ctypes.c_float
 SZ = ctypes.c_size_t
 
+class FactorItem(ctypes.Structure):
+    """struct kfac_factor_item of include/kfac_b200.h."""
+    _fields_ = [('kind', ctypes.c_int), ('add_ones_col', ctypes.c_int),
+                ('x', ctypes.c_void_p), ('rows', ctypes.c_int64),
+                ('ld', ctypes.c_int64), ('d_in', ctypes.c_int),
+                ('n', ctypes.c_int), ('c', ctypes.c_int), ('h', ctypes.c_int),
+                ('w', ctypes.c_int), ('ksize', ctypes.c_int),
+                ('stride', ctypes.c_int), ('pad', ctypes.c_int),
+                ('alpha', ctypes.c_float), ('beta', ctypes.c_float),
+                ('out', ctypes.c_void_p)]
+
+
 # name -> (restype, argtypes); mirrors include/kfac_b200.h one to one.
 SIGNATURES = {
     'kfac_abi_version': (I, []),
@@ -37,6 +49,8 @@ SIGNATURES = {
     'kfac_factor_conv_input': (I, [VP, I, I, I, I, I, I, I, I, F, F, VP, VP,
                                    SZ, VP]),
     'kfac_factor_conv_grad': (I, [VP, I, I, I, I, F, F, VP, VP, SZ, VP]),
+    'kfac_factor_group_workspace_bytes': (SZ, [I, ctypes.POINTER(FactorItem)]),
+    'kfac_factor_group': (I, [I, ctypes.POINTER(FactorItem), VP, SZ, VP]),
     'kfac_bn_sample_grads': (I, [VP, VP, I, I, I, F, F, VP, VP, VP]),
     'kfac_axpby': (I, [I64, F, VP, F, VP, VP, VP]),
     'kfac_inverse_workspace_bytes': (SZ, [I, c_int_p]),

@@ -48,6 +48,10 @@ inline int ceil_div(int64_t a, int64_t b) { return (int)((a + b - 1) / b); }
 // Counter behind kfac_launch_count().
 void count_launch();
 
+// Slice of a small per-device ring of device memory for descriptor tables
+// built per call (see pack.cu).
+int ring_alloc(size_t bytes, void** out);
+
 // Number of streaming multiprocessors of the current device (cached).
 int sm_count();
 

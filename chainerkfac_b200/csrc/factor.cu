@@ -4,7 +4,9 @@
 // written to memory.  Only tiles on or below the diagonal are computed; the
 // epilogue mirrors them.  Long contractions are split across CTAs; partial
 // tiles go through a workspace and are summed in a fixed order.
+#include <algorithm>
 #include <mutex>
+#include <vector>
 
 #include "gemm_simt.cuh"
 
@@ -448,4 +450,89 @@ extern "C" int kfac_factor_dense_noalloc(const float* x, int64_t rows,
   // the shared scratch has to be cleared between calls.
   return run_factor(X, rows, d, alpha, beta, out, scratch, kNoAllocBytes,
                     (cudaStream_t)stream);
+}
+
+// ------------------------------------------------------------ grouped build
+static int job_from_item(const kfac_factor_item& it, FactorJob& job) {
+  job.alpha = it.alpha;
+  job.beta = it.beta;
+  job.out = it.out;
+  job.n = it.n;
+  if (it.kind == KFAC_FACTOR_DENSE) {
+    KFAC_REQUIRE(it.ld >= it.d_in && it.rows > 0 && it.d_in > 0,
+                 "factor_group: bad dense item");
+    job.X = strided_operand(it.x, it.ld, 1, it.d_in);
+    if (it.add_ones_col) job.X.extra_idx = it.d_in;
+    job.rows = it.rows;
+    job.d = it.d_in + (it.add_ones_col ? 1 : 0);
+    job.n = 0;
+  } else if (it.kind == KFAC_FACTOR_CONV_INPUT) {
+    KFAC_REQUIRE(it.n > 0 && it.c > 0 && it.h > 0 && it.w > 0 && it.ksize > 0 &&
+                     it.stride > 0 && it.pad >= 0,
+                 "factor_group: bad conv input item");
+    KFAC_REQUIRE((long long)it.n * it.c * it.h * it.w < (1LL << 31),
+                 "factor_group: input has more than 2^31 elements");
+    const int ho = (it.h + 2 * it.pad - it.ksize) / it.stride + 1;
+    const int wo = (it.w + 2 * it.pad - it.ksize) / it.stride + 1;
+    KFAC_REQUIRE(ho > 0 && wo > 0, "factor_group: empty output");
+    job.X = conv_input_operand(it.x, it.c, it.h, it.w, it.ksize, it.stride,
+                               it.pad, it.add_ones_col);
+    job.rows = (long long)it.n * ho * wo;
+    job.d = it.c * it.ksize * it.ksize + (it.add_ones_col ? 1 : 0);
+  } else if (it.kind == KFAC_FACTOR_CONV_GRAD) {
+    KFAC_REQUIRE(it.n > 0 && it.c > 0 && it.h > 0 && it.w > 0,
+                 "factor_group: bad conv grad item");
+    job.X = strided_operand(it.x, 0, (long long)it.h * it.w, it.c);
+    job.X.period = it.h * it.w;
+    job.X.s_outer = (long long)it.c * it.h * it.w;
+    job.X.s_inner = 1;
+    job.X.kfast = 1;
+    job.rows = (long long)it.n * it.h * it.w;
+    job.d = it.c;
+    job.n = 0;
+  } else {
+    return fail(KFAC_ERR_INVALID, "factor_group: unknown kind %d", it.kind);
+  }
+  KFAC_REQUIRE(it.x != nullptr && it.out != nullptr,
+               "factor_group: null pointer");
+  return KFAC_OK;
+}
+
+static size_t simt_item_bytes(const FactorJob& job) {
+  FactorSplit s = factor_split(job.rows, job.d);
+  return s.splits > 1 ? (size_t)s.splits * s.tiles * TM * TN * sizeof(float)
+                      : 0;
+}
+
+extern "C" size_t kfac_factor_group_workspace_bytes(
+    int count, const kfac_factor_item* items) {
+  if (count <= 0 || items == nullptr) return 0;
+  std::vector<FactorJob> jobs(count);
+  for (int i = 0; i < count; ++i)
+    if (job_from_item(items[i], jobs[i]) != KFAC_OK) return 0;
+  if (engine() == 1) return tc_factor_group_workspace_bytes(count, jobs.data());
+  size_t m = 0;
+  for (int i = 0; i < count; ++i) m = std::max(m, simt_item_bytes(jobs[i]));
+  return m;
+}
+
+extern "C" int kfac_factor_group(int count, const kfac_factor_item* items,
+                                 void* workspace, size_t workspace_bytes,
+                                 void* stream) {
+  KFAC_REQUIRE(count > 0 && items != nullptr, "factor_group: no items");
+  std::vector<FactorJob> jobs(count);
+  for (int i = 0; i < count; ++i) {
+    int rc = job_from_item(items[i], jobs[i]);
+    if (rc != KFAC_OK) return rc;
+  }
+  if (engine() == 1)
+    return run_factor_group_tc(count, jobs.data(), workspace, workspace_bytes,
+                               (cudaStream_t)stream);
+  for (int i = 0; i < count; ++i) {   // fp32 engine: one factor after another
+    int rc = run_factor(jobs[i].X, jobs[i].rows, jobs[i].d, jobs[i].alpha,
+                        jobs[i].beta, jobs[i].out, workspace, workspace_bytes,
+                        (cudaStream_t)stream);
+    if (rc != KFAC_OK) return rc;
+  }
+  return KFAC_OK;
 }

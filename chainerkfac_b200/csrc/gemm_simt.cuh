@@ -252,6 +252,7 @@ struct GemmDesc {
   float *kfW, *kfb, *pW, *pb, *vW, *vb;
   int dW;
   int splits;              // tensor-core engine: CTAs along the contraction
+  int ntiles;              // tiles of one split (virtual tile = split * ntiles + tile)
   long long k_per_split;
   float* partial;          // partial tiles when splits > 1
 };
@@ -269,6 +270,17 @@ size_t tc_pad_bytes(const Operand& X, int n);
 int run_factor_tc(const Operand& X, long long rows, int d, float alpha,
                   float beta, float* out, void* workspace,
                   size_t workspace_bytes, cudaStream_t stream);
+struct FactorJob {      // one factor of a grouped build
+  Operand X;
+  long long rows;
+  int d;
+  int n;                // batch size (im2col operands)
+  float alpha, beta;
+  float* out;
+};
+size_t tc_factor_group_workspace_bytes(int count, const FactorJob* jobs);
+int run_factor_group_tc(int count, const FactorJob* jobs, void* workspace,
+                        size_t workspace_bytes, cudaStream_t stream);
 
 // Host helper: fill tile counts of a descriptor and return its tile count.
 inline int gemm_desc_tiles(GemmDesc& g) {

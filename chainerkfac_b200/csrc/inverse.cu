@@ -365,6 +365,7 @@ extern "C" int kfac_inverse_plan_create(
     g.kfW = g.kfb = g.pW = g.pb = g.vW = g.vb = nullptr;
     g.dW = 0;
     g.splits = 1;
+    g.ntiles = 0;
     g.k_per_split = 0;
     g.partial = nullptr;
     descs.push_back(g);

@@ -27,7 +27,7 @@ static std::mutex g_ring_mu;
 static char* g_ring[64] = {nullptr};
 static size_t g_ring_pos[64] = {0};
 
-static int ring_alloc(size_t bytes, void** out) {
+int ring_alloc(size_t bytes, void** out) {
   int dev = 0;
   KFAC_CUDA(cudaGetDevice(&dev));
   KFAC_REQUIRE(dev >= 0 && dev < 64, "device index %d unsupported", dev);

@@ -12,7 +12,9 @@
 // shared memory and writes rows (and, for symmetric outputs, mirrored columns)
 // with coalesced stores.  Every barrier wait is bounded; a wait that runs out
 // raises a status word instead of hanging.
+#include <algorithm>
 #include <mutex>
+#include <vector>
 
 #include "gemm_simt.cuh"
 
@@ -46,7 +48,7 @@ __device__ long long* g_tc_trace = nullptr;
 __device__ int g_tc_trace_cap = 0;
 #define TC_TRACE(kb, slot)                                                   \
   do {                                                                       \
-    if (g_tc_trace && blockIdx.x == 0 && blockIdx.y == 0 &&                  \
+    if (g_tc_trace && blockIdx.x == 0 &&                  \
         ((kb) * 8 + (slot)) < g_tc_trace_cap)                                \
       g_tc_trace[(kb) * 8 + (slot)] = clock64();                             \
   } while (0)
@@ -489,7 +491,11 @@ tc_gemm_kernel(const GemmDesc* __restrict__ descs, int ndesc,
 
   const GemmDesc& g = ctl->desc;
   const unsigned tmem = ctl->tmem_base;
-  const int lt = tile - g.tile_begin;
+  int lt = tile - g.tile_begin, split = 0;
+  if (g.splits > 1) {
+    split = lt / g.ntiles;
+    lt -= split * g.ntiles;
+  }
   int bi, bj;
   if (g.flags & G_LOWER) {
     tc_tri_tile(lt, bi, bj);
@@ -505,7 +511,7 @@ tc_gemm_kernel(const GemmDesc* __restrict__ descs, int ndesc,
 
   long long kbeg = 0, kend = g.K;
   if (g.splits > 1) {
-    kbeg = (long long)blockIdx.y * g.k_per_split;
+    kbeg = (long long)split * g.k_per_split;
     kend = min(g.K, kbeg + g.k_per_split);
   }
   if (g.flags & G_KBEG_N0) kbeg = max(kbeg, (long long)n0);
@@ -643,8 +649,7 @@ tc_gemm_kernel(const GemmDesc* __restrict__ descs, int ndesc,
   if (warp >= TC_PRODUCERS / 32 || ctl->abort_flag) return;
 
   if (g.splits > 1) {
-    float* p = g.partial +
-               ((long long)blockIdx.y * gridDim.x + tile) * (TC_BM * TC_BN);
+    float* p = g.partial + ((long long)split * g.ntiles + lt) * (TC_BM * TC_BN);
     for (int r = warp; r < TC_BM; r += TC_PWARPS)
       for (int c = lane; c < n_inst; c += 32)
         p[r * TC_BN + c] = stage[r * TC_EPI_PITCH + c];
@@ -726,43 +731,50 @@ __global__ void pad_copy_kernel(const float* __restrict__ x, long long planes,
 
 // Sum split partial tiles (ascending split order), then scale / blend / store
 // the lower part and its mirror.
+struct ReduceItem {     // one output tile whose split partials are summed
+  const float* partial; // first split's copy of this tile
+  float* out;
+  long long sstride;    // elements between consecutive splits
+  int d, tile, splits;
+  float alpha, beta;
+};
+
 __global__ void __launch_bounds__(256)
-tc_reduce_kernel(const float* __restrict__ partial, int tiles, int splits,
-                 int d, float alpha, float beta, float* __restrict__ out) {
+tc_reduce_kernel(const ReduceItem* __restrict__ items) {
   // Four lanes share one output element: lane q sums the splits
   // q, q+4, q+8, ... (always in that order), then the four sums are added in
   // a fixed tree, so the result does not depend on scheduling.
+  const ReduceItem it = items[blockIdx.x];
   int bi, bj;
-  tc_tri_tile(blockIdx.x, bi, bj);
+  tc_tri_tile(it.tile, bi, bj);
+  const int d = it.d;
   const int m0 = bi * TC_BM, n0 = bj * TC_BN;
   const int rows = min(TC_BM, d - m0);
   const int cols = min(min(TC_BN, d - n0), m0 + TC_BM - n0);
-  const int e = (blockIdx.y * 256 + threadIdx.x) >> 2;
   const int q = threadIdx.x & 3;
-  const bool live = e < rows * cols;
-  const int r = live ? e / cols : 0, c = live ? e - (e / cols) * cols : 0;
-  const float* p = partial + (long long)blockIdx.x * (TC_BM * TC_BN) +
-                   r * TC_BN + c;
-  const long long sstride = (long long)tiles * (TC_BM * TC_BN);
-  float s0 = 0.f, s1 = 0.f;
-  if (live) {
+  const int total = rows * cols;
+  for (int e = blockIdx.y * 1024 + (threadIdx.x >> 2);
+       e < min(total, (int)(blockIdx.y + 1) * 1024); e += 64) {
+    const int r = e / cols, c = e - r * cols;
+    const float* p = it.partial + r * TC_BN + c;
+    float s0 = 0.f, s1 = 0.f;
     int sp = q;
-    for (; sp + 4 < splits; sp += 8) {
-      s0 += p[sp * sstride];
-      s1 += p[(sp + 4) * sstride];
+    for (; sp + 4 < it.splits; sp += 8) {
+      s0 += p[sp * it.sstride];
+      s1 += p[(sp + 4) * it.sstride];
     }
-    if (sp < splits) s0 += p[sp * sstride];
+    if (sp < it.splits) s0 += p[sp * it.sstride];
+    float s = s0 + s1;
+    s += __shfl_xor_sync(0xffffffffu, s, 1);
+    s += __shfl_xor_sync(0xffffffffu, s, 2);
+    const int gr = m0 + r, gc = n0 + c;
+    if (q != 0 || gc > gr) continue;
+    float* o = it.out + (long long)gr * d + gc;
+    float v = it.alpha * s;
+    if (it.beta != 0.f) v += it.beta * (*o);
+    *o = v;
+    if (gc < gr) it.out[(long long)gc * d + gr] = v;
   }
-  float s = s0 + s1;
-  s += __shfl_xor_sync(0xffffffffu, s, 1);
-  s += __shfl_xor_sync(0xffffffffu, s, 2);
-  const int gr = m0 + r, gc = n0 + c;
-  if (!live || q != 0 || gc > gr) return;
-  float* o = out + (long long)gr * d + gc;
-  float v = alpha * s;
-  if (beta != 0.f) v += beta * (*o);
-  *o = v;
-  if (gc < gr) out[(long long)gc * d + gr] = v;
 }
 
 // ------------------------------------------------------------------ host side
@@ -814,24 +826,37 @@ struct TcFactorSplit {
   long long k_per_split;
 };
 
-static TcFactorSplit tc_factor_split(long long rows, int d) {
-  TcFactorSplit s;
+static int tc_lower_tiles(int d) {
   GemmDesc g = {};
   g.M = g.N = d;
   g.flags = G_LOWER;
-  s.tiles = tc_tiles(g);
-  long long target = 2LL * sm_count();
-  long long by_tiles = (target + s.tiles - 1) / s.tiles;
-  long long by_rows = (rows + 511) / 512;  // >= 16 k-blocks per CTA
-  long long sp = by_tiles < by_rows ? by_tiles : by_rows;
-  if (s.tiles >= sm_count()) sp = 1;
+  return tc_tiles(g);
+}
+
+// Split of one factor's contraction.  `chunk` is the number of k-blocks a CTA
+// should own (>= 16 so that prologue and epilogue stay amortised).
+static TcFactorSplit tc_split_for(long long rows, int d, long long chunk) {
+  TcFactorSplit s;
+  s.tiles = tc_lower_tiles(d);
+  if (chunk < 16) chunk = 16;
+  const long long kblocks = (rows + TC_BK - 1) / TC_BK;
+  long long sp = (kblocks + chunk - 1) / chunk;
   if (sp < 1) sp = 1;
-  long long kps = (rows + sp - 1) / sp;
-  kps = (kps + TC_BK - 1) / TC_BK * TC_BK;
+  long long kps = (kblocks + sp - 1) / sp * TC_BK;
   s.splits = (int)((rows + kps - 1) / kps);
   if (s.splits < 1) s.splits = 1;
   s.k_per_split = kps;
   return s;
+}
+
+static TcFactorSplit tc_factor_split(long long rows, int d) {
+  // a factor built on its own: aim at two waves of CTAs
+  const int tiles = tc_lower_tiles(d);
+  const long long kblocks = (rows + TC_BK - 1) / TC_BK;
+  long long want = (2LL * sm_count() + tiles - 1) / tiles;   // splits wanted
+  if (tiles >= sm_count()) want = 1;
+  long long chunk = (kblocks + want - 1) / want;
+  return tc_split_for(rows, d, chunk);
 }
 
 size_t tc_factor_workspace_bytes(long long rows, int d) {
@@ -846,79 +871,171 @@ size_t tc_pad_bytes(const Operand& X, int n) {
   return (e * sizeof(float) + 255) & ~(size_t)255;
 }
 
-int run_factor_tc(const Operand& X_in, long long rows, int d, float alpha,
-                  float beta, float* out, void* workspace,
-                  size_t workspace_bytes, cudaStream_t stream) {
+// k-blocks per CTA for a group of factors: total work spread over ~4 waves.
+static long long tc_group_chunk(int count, const FactorJob* jobs) {
+  long long work = 0;
+  for (int i = 0; i < count; ++i)
+    work += (long long)tc_lower_tiles(jobs[i].d) *
+            ((jobs[i].rows + TC_BK - 1) / TC_BK);
+  long long chunk = work / (4LL * sm_count());
+  return chunk < 16 ? 16 : chunk;
+}
+
+size_t tc_factor_group_workspace_bytes(int count, const FactorJob* jobs) {
+  const long long chunk = tc_group_chunk(count, jobs);
+  size_t total = 0;
+  for (int i = 0; i < count; ++i) {
+    total += tc_pad_bytes(jobs[i].X, jobs[i].n);
+    TcFactorSplit s = count == 1 ? tc_factor_split(jobs[i].rows, jobs[i].d)
+                                 : tc_split_for(jobs[i].rows, jobs[i].d, chunk);
+    if (s.splits > 1)
+      total += (size_t)s.splits * s.tiles * TC_BM * TC_BN * sizeof(float);
+  }
+  return total;
+}
+
+int run_factor_group_tc(int count, const FactorJob* jobs, void* workspace,
+                        size_t workspace_bytes, cudaStream_t stream) {
   int rc = tc_prepare();
   if (rc != KFAC_OK) return rc;
-  Operand X = X_in;
-  if (X.mode == 1 && X.pd > 0) {
-    // zero-bordered copy first; the gather then runs without bounds checks
-    const int n = (int)(rows / ((long long)X.Ho * X.Wo));
-    const size_t pad_bytes = tc_pad_bytes(X, n);
-    if (workspace == nullptr || workspace_bytes < pad_bytes)
-      return fail(KFAC_ERR_WORKSPACE,
-                  "factor: workspace of %zu bytes needed for the padded "
-                  "input, %zu given", pad_bytes, workspace_bytes);
-    float* padded = static_cast<float*>(workspace);
-    const long long planes = (long long)n * X.C;
-    const long long total = planes * (X.H + 2 * X.pd) * (X.W + 2 * X.pd);
-    KFAC_REQUIRE(total < (1LL << 31), "factor: padded input too large");
-    int blocks = (int)((total + 1023) / 1024);
-    if (blocks > sm_count() * 16) blocks = sm_count() * 16;
-    pad_copy_kernel<<<blocks, 256, 0, stream>>>(X.base, planes, X.H, X.W, X.pd,
-                                                padded);
-    KFAC_LAUNCH_CHECK("pad_copy_kernel");
-    X.base = padded;
-    X.H += 2 * X.pd;
-    X.W += 2 * X.pd;
-    X.pd = 0;
-    workspace = static_cast<char*>(workspace) + pad_bytes;
-    workspace_bytes -= pad_bytes;
+  const size_t need = tc_factor_group_workspace_bytes(count, jobs);
+  if (need > 0 && (workspace == nullptr || workspace_bytes < need))
+    return fail(KFAC_ERR_WORKSPACE,
+                "factor: workspace of %zu bytes needed, %zu given", need,
+                workspace_bytes);
+  const long long chunk = tc_group_chunk(count, jobs);
+  char* ws = static_cast<char*>(workspace);
+
+  std::vector<GemmDesc> descs[2];       // [0] strided, [1] im2col
+  std::vector<ReduceItem> reduces;
+  for (int i = 0; i < count; ++i) {
+    const FactorJob& job = jobs[i];
+    KFAC_REQUIRE(job.out != nullptr && job.X.base != nullptr,
+                 "factor: null pointer");
+    KFAC_REQUIRE(job.rows > 0 && job.d > 0 && job.rows < (1LL << 31),
+                 "factor: rows=%lld d=%d out of range", job.rows, job.d);
+    Operand X = job.X;
+    if (X.mode == 1 && X.pd > 0) {
+      // zero-bordered copy first; the gather then needs no bounds checks
+      const size_t pad_bytes = tc_pad_bytes(X, job.n);
+      float* padded = reinterpret_cast<float*>(ws);
+      ws += pad_bytes;
+      const long long planes = (long long)job.n * X.C;
+      const long long total = planes * (X.H + 2 * X.pd) * (X.W + 2 * X.pd);
+      KFAC_REQUIRE(total < (1LL << 31), "factor: padded input too large");
+      int blocks = (int)((total + 1023) / 1024);
+      if (blocks > sm_count() * 16) blocks = sm_count() * 16;
+      pad_copy_kernel<<<blocks, 256, 0, stream>>>(X.base, planes, X.H, X.W,
+                                                  X.pd, padded);
+      KFAC_LAUNCH_CHECK("pad_copy_kernel");
+      X.base = padded;
+      X.H += 2 * X.pd;
+      X.W += 2 * X.pd;
+      X.pd = 0;
+    }
+    TcFactorSplit s = count == 1 ? tc_factor_split(job.rows, job.d)
+                                 : tc_split_for(job.rows, job.d, chunk);
+    GemmDesc g = {};
+    g.A = X;
+    g.B = X;
+    g.C = job.out;
+    g.ldc = job.d;
+    g.K = job.rows;
+    g.M = job.d;
+    g.N = job.d;
+    g.alpha = job.alpha;
+    g.beta = job.beta;
+    g.flags = G_LOWER | G_MIRROR;
+    g.ntiles = tc_tiles(g);
+    g.splits = s.splits;
+    g.k_per_split = s.k_per_split;
+    g.partial = nullptr;
+    if (s.splits > 1) {
+      g.partial = reinterpret_cast<float*>(ws);
+      ws += (size_t)s.splits * s.tiles * TC_BM * TC_BN * sizeof(float);
+      for (int t = 0; t < s.tiles; ++t) {
+        ReduceItem it;
+        it.partial = g.partial + (long long)t * (TC_BM * TC_BN);
+        it.out = job.out;
+        it.sstride = (long long)s.tiles * (TC_BM * TC_BN);
+        it.d = job.d;
+        it.tile = t;
+        it.splits = s.splits;
+        it.alpha = job.alpha;
+        it.beta = job.beta;
+        reduces.push_back(it);
+      }
+    }
+    descs[X.mode == 1 ? 1 : 0].push_back(g);
   }
-  KFAC_REQUIRE(rows < (1LL << 31) && (long long)rows * d < (1LL << 40),
-               "factor: contraction of %lld rows is too long", rows);
-  TcFactorSplit s = tc_factor_split(rows, d);
-  GemmDesc g = {};
-  g.A = X;
-  g.B = X;
-  g.C = out;
-  g.ldc = d;
-  g.K = rows;
-  g.M = d;
-  g.N = d;
-  g.alpha = alpha;
-  g.beta = beta;
-  g.flags = G_LOWER | G_MIRROR;
-  g.tile_begin = 0;
-  tc_tiles(g);
-  g.splits = s.splits;
-  g.k_per_split = s.k_per_split;
-  g.partial = nullptr;
-  if (s.splits > 1) {
-    size_t need = (size_t)s.splits * s.tiles * TC_BM * TC_BN * sizeof(float);
-    if (workspace == nullptr || workspace_bytes < need)
-      return fail(KFAC_ERR_WORKSPACE,
-                  "factor: workspace of %zu bytes needed, %zu given", need,
-                  workspace_bytes);
-    g.partial = static_cast<float*>(workspace);
+  for (int m = 0; m < 2; ++m) {
+    std::vector<GemmDesc>& v = descs[m];
+    if (v.empty()) continue;
+    // long-running CTAs first
+    std::stable_sort(v.begin(), v.end(), [](const GemmDesc& a, const GemmDesc& b) {
+      long long ka = a.splits > 1 ? a.k_per_split : a.K;
+      long long kb = b.splits > 1 ? b.k_per_split : b.K;
+      return ka > kb;
+    });
+    int total = 0;
+    for (GemmDesc& g : v) {
+      g.tile_begin = total;
+      total += g.ntiles * (g.splits > 1 ? g.splits : 1);
+    }
+    if (v.size() == 1) {
+      if (m == 1)
+        tc_gemm_kernel<true><<<total, TC_THREADS, TC_SMEM_BYTES, stream>>>(
+            nullptr, 1, v[0], 0.f, 0.f);
+      else
+        tc_gemm_kernel<false><<<total, TC_THREADS, TC_SMEM_BYTES, stream>>>(
+            nullptr, 1, v[0], 0.f, 0.f);
+    } else {
+      void* dev = nullptr;
+      rc = ring_alloc(v.size() * sizeof(GemmDesc), &dev);
+      if (rc != KFAC_OK) return rc;
+      KFAC_CUDA(cudaMemcpyAsync(dev, v.data(), v.size() * sizeof(GemmDesc),
+                                cudaMemcpyHostToDevice, stream));
+      GemmDesc dummy = {};
+      if (m == 1)
+        tc_gemm_kernel<true><<<total, TC_THREADS, TC_SMEM_BYTES, stream>>>(
+            static_cast<const GemmDesc*>(dev), (int)v.size(), dummy, 0.f, 0.f);
+      else
+        tc_gemm_kernel<false><<<total, TC_THREADS, TC_SMEM_BYTES, stream>>>(
+            static_cast<const GemmDesc*>(dev), (int)v.size(), dummy, 0.f, 0.f);
+    }
+    KFAC_LAUNCH_CHECK("tc_gemm_kernel");
   }
-  dim3 grid(s.tiles, s.splits);
-  if (X.mode == 1)
-    tc_gemm_kernel<true><<<grid, TC_THREADS, TC_SMEM_BYTES, stream>>>(
-        nullptr, 1, g, 0.f, 0.f);
-  else
-    tc_gemm_kernel<false><<<grid, TC_THREADS, TC_SMEM_BYTES, stream>>>(
-        nullptr, 1, g, 0.f, 0.f);
-  KFAC_LAUNCH_CHECK("tc_gemm_kernel");
-  if (s.splits > 1) {
-    const int rmax = d < TC_BM ? d : TC_BM, cmax = d < TC_BN ? d : TC_BN;
-    dim3 rgrid(s.tiles, (rmax * cmax * 4 + 255) / 256);
-    tc_reduce_kernel<<<rgrid, 256, 0, stream>>>(g.partial, s.tiles, s.splits, d,
-                                                alpha, beta, out);
+  if (!reduces.empty()) {
+    void* dev = nullptr;
+    rc = ring_alloc(reduces.size() * sizeof(ReduceItem), &dev);
+    if (rc != KFAC_OK) return rc;
+    KFAC_CUDA(cudaMemcpyAsync(dev, reduces.data(),
+                              reduces.size() * sizeof(ReduceItem),
+                              cudaMemcpyHostToDevice, stream));
+    int dmax = 0;
+    for (const ReduceItem& it : reduces) dmax = it.d > dmax ? it.d : dmax;
+    const int rmax = dmax < TC_BM ? dmax : TC_BM;
+    const int cmax = dmax < TC_BN ? dmax : TC_BN;
+    dim3 rgrid((unsigned)reduces.size(), (rmax * cmax + 1023) / 1024);
+    tc_reduce_kernel<<<rgrid, 256, 0, stream>>>(
+        static_cast<const ReduceItem*>(dev));
     KFAC_LAUNCH_CHECK("tc_reduce_kernel");
   }
   return KFAC_OK;
+}
+
+int run_factor_tc(const Operand& X, long long rows, int d, float alpha,
+                  float beta, float* out, void* workspace,
+                  size_t workspace_bytes, cudaStream_t stream) {
+  FactorJob job;
+  job.X = X;
+  job.rows = rows;
+  job.d = d;
+  job.n = X.mode == 1 ? (int)(rows / ((long long)X.Ho * X.Wo)) : 0;
+  job.alpha = alpha;
+  job.beta = beta;
+  job.out = out;
+  return run_factor_group_tc(1, &job, workspace, workspace_bytes, stream);
 }
 
 int engine() { return g_engine; }

@@ -110,6 +110,53 @@ def factor_conv_grad(gy, alpha=1.0, beta=0.0, out=None):
     return out
 
 
+def dense_item(x, add_ones_col, alpha, beta, out):
+    _chk(x, 'x')
+    _chk(out, 'out')
+    it = _lib.FactorItem()
+    it.kind, it.add_ones_col = 0, int(bool(add_ones_col))
+    it.x, it.rows, it.ld, it.d_in = x.data_ptr(), x.shape[0], x.stride(0), \
+        x.shape[1]
+    it.alpha, it.beta, it.out = alpha, beta, out.data_ptr()
+    return it
+
+
+def conv_input_item(x, ksize, stride, pad, add_ones_col, alpha, beta, out):
+    _chk(x, 'x')
+    _chk(out, 'out')
+    it = _lib.FactorItem()
+    it.kind, it.add_ones_col = 1, int(bool(add_ones_col))
+    it.x = x.data_ptr()
+    it.n, it.c, it.h, it.w = x.shape
+    it.ksize, it.stride, it.pad = ksize, stride, pad
+    it.alpha, it.beta, it.out = alpha, beta, out.data_ptr()
+    return it
+
+
+def conv_grad_item(gy, alpha, beta, out):
+    _chk(gy, 'gy')
+    _chk(out, 'out')
+    it = _lib.FactorItem()
+    it.kind = 2
+    it.x = gy.data_ptr()
+    it.n, it.c, it.h, it.w = gy.shape
+    it.alpha, it.beta, it.out = alpha, beta, out.data_ptr()
+    return it
+
+
+_group_ws = Workspace()
+
+
+def factor_group(items, device):
+    """Build all given factors (see *_item) in one grouped call."""
+    lib = _lib.load()
+    arr = (_lib.FactorItem * len(items))(*items)
+    nbytes = lib.kfac_factor_group_workspace_bytes(len(items), arr)
+    ws = _group_ws.get(nbytes, device)
+    _lib.check(lib.kfac_factor_group(len(items), arr, _p(ws), ws.numel(),
+                                     _stream()), 'kfac_factor_group')
+
+
 def bn_sample_grads(x, gy, eps, scale):
     """(n, 2c) per-sample gradients of the BatchNormalization scale/shift."""
     lib = _lib.load()

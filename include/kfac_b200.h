@@ -111,6 +111,31 @@ int kfac_factor_dense_noalloc(const float* x, int64_t rows, int d_in,
                               int64_t ld, int add_ones_col, float alpha,
                               float beta, float* out, void* stream);
 
+/* Grouped build: all factors of a step in one call, so that the tiles of small
+ * layers fill the GPU together (the reference builds one factor per hook
+ * call; results are identical).  Each item is one of the three builds above
+ * with the same meaning of its fields; conv gradients pass ho, wo in h, w.
+ * `items` is a host array read during the call; outputs must not alias. */
+#define KFAC_FACTOR_DENSE 0
+#define KFAC_FACTOR_CONV_INPUT 1
+#define KFAC_FACTOR_CONV_GRAD 2
+typedef struct kfac_factor_item {
+  int kind;
+  int add_ones_col;
+  const float* x;
+  int64_t rows;   /* dense */
+  int64_t ld;     /* dense */
+  int d_in;       /* dense */
+  int n, c, h, w, ksize, stride, pad; /* conv */
+  float alpha, beta;
+  float* out;
+} kfac_factor_item;
+
+size_t kfac_factor_group_workspace_bytes(int count,
+                                         const kfac_factor_item* items);
+int kfac_factor_group(int count, const kfac_factor_item* items,
+                      void* workspace, size_t workspace_bytes, void* stream);
+
 /* Per-sample BatchNormalization gradients: out is (n x 2c),
  * out[s, j] = scale * sum_hw gy[s,j,:] * xhat[s,j,:] and
  * out[s, c+j] = scale * sum_hw gy[s,j,:], xhat = x normalised with the batch

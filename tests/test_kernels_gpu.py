@@ -168,6 +168,37 @@ def test_factor_conv_grad_sweep(ops, n, c, hw):
     check_symmetric(got)
 
 
+def test_factor_group_matches_single_calls(ops):
+    rng = np.random.default_rng(21)
+    xd = dev(rng.random((300, 70)).astype(np.float32))
+    xc = dev(rng.standard_normal((3, 16, 12, 12)).astype(np.float32))
+    xs = dev(rng.standard_normal((2, 24, 10, 10)).astype(np.float32))
+    gy = dev(rng.standard_normal((3, 40, 12, 12)).astype(np.float32))
+    big = dev(rng.standard_normal((2, 8, 40, 40)).astype(np.float32))
+    prev = dev(np.eye(71, dtype=np.float32))
+    want = [
+        ops.factor_dense(xd, True, alpha=0.5, beta=0.25, out=prev.clone()),
+        ops.factor_conv_input(xc, 3, 1, 1, False, alpha=1 / 3.),
+        ops.factor_conv_input(xs, 1, 2, 0, True, alpha=0.5),
+        ops.factor_conv_grad(gy, alpha=2.0),
+        ops.factor_conv_input(big, 3, 1, 1, True, alpha=1.0),
+    ]
+    outs = [prev.clone()] + [torch.empty_like(w) for w in want[1:]]
+    items = [
+        ops.dense_item(xd, True, 0.5, 0.25, outs[0]),
+        ops.conv_input_item(xc, 3, 1, 1, False, 1 / 3., 0.0, outs[1]),
+        ops.conv_input_item(xs, 1, 2, 0, True, 0.5, 0.0, outs[2]),
+        ops.conv_grad_item(gy, 2.0, 0.0, outs[3]),
+        ops.conv_input_item(big, 3, 1, 1, True, 1.0, 0.0, outs[4]),
+    ]
+    ops.factor_group(items, xd.device)
+    for w, o in zip(want, outs):
+        assert rel(host(o), host(w)) < 1e-5
+        check_symmetric(host(o))
+    assert rel(host(outs[1]), orc.conv_A(host(xc).astype(np.float64), 3, 1, 1,
+                                         False)) < FACTOR_TOL
+
+
 @pytest.mark.parametrize('name', ['bn_4d', 'bn_2d'])
 def test_bn_factor_golden(ops, golden, name):
     g = golden(name)
