@@ -60,6 +60,31 @@ def algorithmic_flops(dims):
                 precondition=float(precond))
 
 
+def measure_tf32_peak(device):
+    """Dense TF32 matmul throughput (8192^3, best of 10), measured the way the
+    bf16 figure of MEASURED_PEAKS.json was: the fp32 data of this path can at
+    best run at this rate (a third of it with the split-TF32 scheme)."""
+    import torch
+    old = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = True
+    try:
+        a = torch.randn(8192, 8192, device=device)
+        b = torch.randn(8192, 8192, device=device)
+        torch.matmul(a, b)
+        best = float('inf')
+        for _ in range(10):
+            e0 = torch.cuda.Event(enable_timing=True)
+            e1 = torch.cuda.Event(enable_timing=True)
+            e0.record()
+            torch.matmul(a, b)
+            e1.record()
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        return 2 * 8192 ** 3 / (best * 1e-3) / 1e12
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = old
+
+
 def measured_peaks():
     path = os.path.join(ROOT, 'MEASURED_PEAKS.json')
     if os.path.exists(path):
@@ -91,7 +116,7 @@ class ClockSampler(object):
             self.proc = subprocess.Popen(
                 ['nvidia-smi', '-i', str(self.index),
                  '--query-gpu=' + self.QUERY, '--format=csv,noheader,nounits',
-                 '-lms', '100'], stdout=subprocess.PIPE,
+                 '-lms', '50'], stdout=subprocess.PIPE,
                 stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -376,8 +401,11 @@ def run_ours(args):
 
     if rank == 0:
         peaks = measured_peaks()
+        tf32 = measure_tf32_peak(device)
         names = ['factor', 'inverse', 'precondition']
-        dom = int(np.argmax(phase))
+        # the factor stage is the grouped launches of tc_gemm_kernel, the
+        # kernel that also carries the inverse and precondition products
+        dom = 0
         achieved = flops[names[dom]] / (phase[dom] * 1e-3) / 1e12
         stage = {nm: dict(ms=float(ms), tflops=float(flops[nm] / (ms * 1e-3) / 1e12))
                  for nm, ms in zip(names, phase)}
@@ -400,12 +428,26 @@ def run_ours(args):
             'stages': stage,
             'factor_inverse_ms': float(phase[0] + phase[1]),
             'roofline': {
-                'bound': 'tensor', 'kernel': names[dom] + ' stage',
+                'bound': 'tensor',
+                'kernel': 'tc_gemm_kernel (factor stage: two grouped launches '
+                          'over all 108 factors, plus split reduce)',
                 'achieved': achieved, 'peak': peaks['tflops'],
                 'unit': 'TFLOP/s', 'frac': achieved / peaks['tflops'],
-                'peak_source': '%s dense bf16 sustained (no tf32 figure in '
-                               'the file); fp32 data' % peaks['source'],
-                'traffic': None},
+                'peak_source': 'of %s: dense bf16 sustained from '
+                               'MEASURED_PEAKS.json (it has no tf32 figure)'
+                               % peaks['source'],
+                'tf32_tflops_measured_here': tf32,
+                'frac_of_tf32': achieved / tf32,
+                'frac_of_split_tf32_ceiling': achieved / (tf32 / 3.0),
+                'step_tflops': float(sum(flops.values()) /
+                                     (ms_per_step * 1e-3) / 1e12),
+                # full-size launches are too large for a multi-pass capture;
+                # see profiles/tc_gemm_dense_rows8192_d4608.md for the DRAM
+                # traffic of one factor measured on a smaller case
+                'traffic': None,
+                'traffic_case': {'case': 'dense_rows8192_d4608',
+                                 'dram_bytes': 4.706e8,
+                                 'algorithmic_bytes': 2.359e8}},
             'cpu_baseline': cpu,
             'gpu_launches': int(launches),
             'clocks': clocks,
@@ -611,7 +653,7 @@ def run_micro(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('--gpus', type=int, default=1)
-    ap.add_argument('--steps', type=int, default=10)
+    ap.add_argument('--steps', type=int, default=20)
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--no-e2e', action='store_true')

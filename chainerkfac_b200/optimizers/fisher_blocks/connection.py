@@ -37,13 +37,46 @@ class FisherBlockConnection(FisherBlock):
             return False
         return True
 
+    # With ``deferred`` set (by the optimizer) the hooks only remember their
+    # arguments; the optimizer then builds the factors of all blocks in one
+    # grouped launch (``flush_items``) before anything reads ``covs``.
+    deferred = False
+
     def forward_postprocess(self, func, in_data):
+        if self.deferred:
+            self._pending_A = in_data
+            return
         self._A = self.compute_A(in_data)
         self.covs = [self._A, self._G]
 
     def backward_preprocess(self, func, in_data, out_grad_data):
+        if self.deferred:
+            self._pending_G = (in_data, out_grad_data)
+            return
         self._G = self.compute_G(in_data, out_grad_data)
         self.covs = [self._A, self._G]
+
+    def item_A(self, in_data):
+        """Grouped-build item equivalent to compute_A; sets ``_A``."""
+        raise NotImplementedError
+
+    def item_G(self, in_data, out_grad_data):
+        raise NotImplementedError
+
+    def flush_items(self, forward_only=False):
+        """Items for the factors whose hook arguments are pending."""
+        items = []
+        pend = getattr(self, '_pending_A', None)
+        if pend is not None:
+            items.append(self.item_A(pend))
+            self._pending_A = None
+        pend = getattr(self, '_pending_G', None)
+        if pend is not None and not forward_only:
+            items.append(self.item_G(*pend))
+            self._pending_G = None
+        if items:
+            self.covs = [self._A, self._G]
+        return items
 
     def compute_A(self, in_data):
         raise NotImplementedError

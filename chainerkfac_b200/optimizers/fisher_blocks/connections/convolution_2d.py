@@ -37,3 +37,24 @@ class FisherBlockConvolution2D(FisherBlockConnection):
         out = self.factor_buffer(1, c, gy.device)
         return ops.factor_conv_grad(gy, alpha=s * s / float(n * ho * wo),
                                     out=out)
+
+    def item_A(self, in_data):
+        x = in_data[0].contiguous()
+        ksize, stride, pad = \
+            self._link.ksize, self._link.stride[0], self._link.pad[0]
+        n, c = x.shape[0], x.shape[1]
+        bias = self._link.b is not None
+        self._A = self.factor_buffer(0, c * ksize * ksize + int(bias),
+                                     x.device)
+        self._keep_x = x
+        return ops.conv_input_item(x, ksize, stride, pad, bias, 1.0 / n, 0.0,
+                                   self._A)
+
+    def item_G(self, in_data, out_grad_data):
+        gy = out_grad_data[0].contiguous()
+        n, c, ho, wo = gy.shape
+        s = self.gy_scale(n)
+        self._G = self.factor_buffer(1, c, gy.device)
+        self._keep_gy = gy
+        return ops.conv_grad_item(gy, s * s / float(n * ho * wo), 0.0,
+                                  self._G)

@@ -33,3 +33,20 @@ class FisherBlockLinear(FisherBlockConnection):
         s = self.gy_scale(n)
         out = self.factor_buffer(1, gy.shape[1], gy.device)
         return ops.factor_dense(gy, False, alpha=s * s / n, out=out)
+
+    def item_A(self, in_data):
+        x = in_data[0]
+        x = x.reshape(-1, x.shape[-1]).contiguous()
+        bias = self.link.b is not None
+        self._A = self.factor_buffer(0, x.shape[1] + int(bias), x.device)
+        self._keep_x = x
+        return ops.dense_item(x, bias, 1.0 / x.shape[0], 0.0, self._A)
+
+    def item_G(self, in_data, out_grad_data):
+        gy = out_grad_data[0]
+        gy = gy.reshape(-1, gy.shape[-1]).contiguous()
+        n = gy.shape[0]
+        s = self.gy_scale(n)
+        self._G = self.factor_buffer(1, gy.shape[1], gy.device)
+        self._keep_gy = gy
+        return ops.dense_item(gy, False, s * s / n, 0.0, self._G)

@@ -209,6 +209,9 @@ class KFAC(_base.GradientMethod):
         self.only_pic_update_weight = False  # True only if in DistributedKFAC
         # apply v = m v - lr kf; W += v inside the preconditioning epilogue
         self.fuse_update = True
+        # build the factors of all layers in one grouped launch after
+        # backward instead of one launch per hook call (same values)
+        self.group_factors = True
         self._plans = {}
         self.observation = {}
 
@@ -241,7 +244,23 @@ class KFAC(_base.GradientMethod):
         return KFACUpdateRule(self.hyperparam,
                               adjust_momentum=self.adjust_momentum)
 
+    def flush_factors(self, forward_only=False):
+        """Grouped build of every factor whose hook arguments are pending."""
+        items = []
+        for fb in self.fblocks:
+            if isinstance(fb, FB.FisherBlockConnection):
+                items += fb.flush_items(forward_only)
+        if items:
+            dev = next(self.target.params()).data.device
+            ops.factor_group(items, dev)
+        if not forward_only:
+            for fb in self.fblocks:
+                fb._keep_x = fb._keep_gy = None
+
     def _forward_backward(self, lossfun, args, kwargs, after_forward=None):
+        for fb in self.fblocks:
+            if isinstance(fb, FB.FisherBlockConnection):
+                fb.deferred = self.group_factors
         with self.kfhook:
             loss = lossfun(*args, **kwargs)
             if after_forward is not None:
@@ -254,6 +273,7 @@ class KFAC(_base.GradientMethod):
                 loss.backward(torch.full_like(loss, self._loss_scale))
             else:
                 loss.backward()
+        self.flush_factors()
         self.loss = loss.detach()
 
     def update(self, lossfun=None, *args, **kwargs):
@@ -479,6 +499,7 @@ class DistributedKFAC(KFAC):
     def reduce_scatter_v_after_forward(self):
         if not self.communicate_after_forward:
             return
+        self.flush_factors(forward_only=True)
         if self.cuda_event is not None:
             self.cuda_event.record(torch.cuda.current_stream())
             self.stream.wait_event(self.cuda_event)
