@@ -83,23 +83,23 @@ __global__ void damping_kernel(const MatInfo* __restrict__ mats, int count,
   if (add_out) add_out[i] = v;
 }
 
-// W = F + add * I, blockIdx.y = matrix.
+// W = F + add * I, blockIdx.y = matrix, blockIdx.x strides over rows.  Only
+// the lower triangle and the rest of each diagonal 128-block (which the
+// trailing updates read-modify-write) is ever used, so only that is copied.
 __global__ void damp_copy_kernel(const MatInfo* __restrict__ mats,
                                  const float* __restrict__ add) {
   const MatInfo mi = mats[blockIdx.y];
   const float a = add[blockIdx.y];
-  const long long total = (long long)mi.d * mi.d;
-  const long long stride = (long long)gridDim.x * blockDim.x;
-  // only the lower triangle (and the rest of each diagonal 128-block, which
-  // the trailing updates read-modify-write) is ever used
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-       i < total; i += stride) {
-    int r = (int)(i / mi.d);
-    int c = (int)(i - (long long)r * mi.d);
-    if (c > (r | (DB - 1))) continue;
-    float v = mi.F[i];
-    if (r == c) v += a;
-    mi.W[i] = v;
+  const int d = mi.d;
+  for (int r = blockIdx.x; r < d; r += gridDim.x) {
+    const int cend = min(d, (r | (DB - 1)) + 1);
+    const float* src = mi.F + (long long)r * d;
+    float* dst = mi.W + (long long)r * d;
+    for (int c = threadIdx.x; c < cend; c += blockDim.x) {
+      float v = src[c];
+      if (r == c) v += a;
+      dst[c] = v;
+    }
   }
 }
 

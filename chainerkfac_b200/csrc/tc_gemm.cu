@@ -62,6 +62,7 @@ struct TcControl {
   unsigned long long accum;
   unsigned tmem_base;
   volatile int abort_flag;
+  int found;
   int coff_a[TC_BM];
   int kykx_a[TC_BM];
   int coff_b[TC_BN];
@@ -452,16 +453,19 @@ tc_gemm_kernel(const GemmDesc* __restrict__ descs, int ndesc,
   const int warp = tid >> 5, lane = tid & 31;
   const int tile = blockIdx.x;
 
-  // ---- locate the problem and copy its descriptor to shared memory
+  // ---- locate the problem and copy its descriptor to shared memory.  The
+  // search is one parallel round: thread t tests descriptor t (tile_begin is
+  // ascending), instead of a chain of dependent global loads.
   {
     const GemmDesc* src = &inline_desc;
     if (descs != nullptr) {
-      int lo = 0, hi = ndesc - 1;
-      while (lo < hi) {
-        int mid = (lo + hi + 1) >> 1;
-        if (descs[mid].tile_begin <= tile) lo = mid; else hi = mid - 1;
+      for (int i = tid; i < ndesc; i += TC_THREADS) {
+        const int lo = descs[i].tile_begin;
+        const int hi = (i + 1 < ndesc) ? descs[i + 1].tile_begin : 0x7fffffff;
+        if (lo <= tile && tile < hi) ctl->found = i;
       }
-      src = descs + lo;
+      __syncthreads();
+      src = descs + ctl->found;
     }
     const int* s = reinterpret_cast<const int*>(src);
     int* d = reinterpret_cast<int*>(&ctl->desc);
@@ -659,23 +663,43 @@ tc_gemm_kernel(const GemmDesc* __restrict__ descs, int ndesc,
     const int dW = g.dW;
     for (int r = warp; r < m_valid; r += TC_PWARPS) {
       const int gr = m0 + r;
-      for (int c = lane; c < n_valid; c += 32) {
-        const int gc = n0 + c;
-        const float kf = stage[r * TC_EPI_PITCH + c];
-        float *okf, *op, *ov;
-        long long idx;
-        if (gc < dW) {
-          idx = (long long)gr * dW + gc;
-          okf = g.kfW; op = g.pW; ov = g.vW;
-        } else {
-          idx = gr;
-          okf = g.kfb; op = g.pb; ov = g.vb;
+      float ov[TC_BN / 32], op[TC_BN / 32];
+      if (g.pW != nullptr) {
+#pragma unroll
+        for (int i = 0; i < TC_BN / 32; ++i) {
+          const int c = lane + 32 * i, gc = n0 + c;
+          ov[i] = op[i] = 0.f;
+          if (c < n_valid) {
+            if (gc < dW) {
+              ov[i] = g.vW[(long long)gr * dW + gc];
+              op[i] = g.pW[(long long)gr * dW + gc];
+            } else if (g.pb != nullptr) {
+              ov[i] = g.vb[gr];
+              op[i] = g.pb[gr];
+            }
+          }
         }
-        if (okf) okf[idx] = kf;
-        if (op) {
-          float nv = momentum * ov[idx] - lr * kf;
-          ov[idx] = nv;
-          op[idx] += nv;
+      }
+#pragma unroll
+      for (int i = 0; i < TC_BN / 32; ++i) {
+        const int c = lane + 32 * i, gc = n0 + c;
+        if (c >= n_valid) continue;
+        const float kf = stage[r * TC_EPI_PITCH + c];
+        if (gc < dW) {
+          const long long idx = (long long)gr * dW + gc;
+          if (g.kfW) g.kfW[idx] = kf;
+          if (g.pW) {
+            const float nv = momentum * ov[i] - lr * kf;
+            g.vW[idx] = nv;
+            g.pW[idx] = op[i] + nv;
+          }
+        } else {
+          if (g.kfb) g.kfb[gr] = kf;
+          if (g.pb) {
+            const float nv = momentum * ov[i] - lr * kf;
+            g.vb[gr] = nv;
+            g.pb[gr] = op[i] + nv;
+          }
         }
       }
     }
@@ -685,17 +709,29 @@ tc_gemm_kernel(const GemmDesc* __restrict__ descs, int ndesc,
   const bool lower = (g.flags & G_LOWER) != 0;
   const bool mirror = (g.flags & G_MIRROR) != 0;
   // rows: C[gr][gc] = alpha * acc + beta * C[gr][gc]; the final value is kept
-  // in the staging tile for the mirrored pass
+  // in the staging tile for the mirrored pass.  A lane owns columns lane,
+  // lane + 32, ...; all of a row's reads of C are issued before any is used.
   for (int r = warp; r < m_valid; r += TC_PWARPS) {
     const int gr = m0 + r;
-    for (int c = lane; c < n_valid; c += 32) {
-      const int gc = n0 + c;
-      if (lower && gc > gr) continue;
-      float* p = g.C + (long long)gr * g.ldc + gc;
-      float v = alpha * stage[r * TC_EPI_PITCH + c];
-      if (beta != 0.f) v += beta * (*p);
-      *p = v;
-      if (mirror) stage[r * TC_EPI_PITCH + c] = v;
+    float* crow = g.C + (long long)gr * g.ldc + n0;
+    const int cend = lower ? min(n_valid, gr - n0 + 1) : n_valid;
+    float old[TC_BN / 32];
+    if (beta != 0.f) {
+#pragma unroll
+      for (int i = 0; i < TC_BN / 32; ++i) {
+        const int c = lane + 32 * i;
+        old[i] = c < cend ? crow[c] : 0.f;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < TC_BN / 32; ++i) {
+      const int c = lane + 32 * i;
+      if (c < cend) {
+        float v = alpha * stage[r * TC_EPI_PITCH + c];
+        if (beta != 0.f) v += beta * old[i];
+        crow[c] = v;
+        if (mirror) stage[r * TC_EPI_PITCH + c] = v;
+      }
     }
   }
   if (mirror) {
@@ -711,26 +747,28 @@ tc_gemm_kernel(const GemmDesc* __restrict__ descs, int ndesc,
 }
 
 // Copy an NCHW tensor into a buffer with a zero border of `pad` pixels.
+// blockIdx.y walks the (n, c) planes, threads walk one padded plane: no
+// division by run-time 64-bit values in the inner loop.
 __global__ void pad_copy_kernel(const float* __restrict__ x, long long planes,
                                 int h, int w, int pad,
                                 float* __restrict__ out) {
   const int hp = h + 2 * pad, wp = w + 2 * pad;
-  const long long total = planes * hp * wp;
-  const long long stride = (long long)gridDim.x * blockDim.x;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-       i < total; i += stride) {
-    const long long plane = i / (hp * wp);
-    const int rem = (int)(i - plane * hp * wp);
-    const int y = rem / wp - pad, xx = rem - (rem / wp) * wp - pad;
-    float v = 0.f;
-    if ((unsigned)y < (unsigned)h && (unsigned)xx < (unsigned)w)
-      v = x[(plane * h + y) * w + xx];
-    out[i] = v;
+  const int per = hp * wp;
+  for (long long plane = blockIdx.y; plane < planes; plane += gridDim.y) {
+    const float* src = x + plane * h * w;
+    float* dst = out + plane * per;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < per;
+         i += gridDim.x * blockDim.x) {
+      const int yy = i / wp;
+      const int y = yy - pad, xx = i - yy * wp - pad;
+      float v = 0.f;
+      if ((unsigned)y < (unsigned)h && (unsigned)xx < (unsigned)w)
+        v = src[y * w + xx];
+      dst[i] = v;
+    }
   }
 }
 
-// Sum split partial tiles (ascending split order), then scale / blend / store
-// the lower part and its mirror.
 struct ReduceItem {     // one output tile whose split partials are summed
   const float* partial; // first split's copy of this tile
   float* out;
@@ -923,10 +961,11 @@ int run_factor_group_tc(int count, const FactorJob* jobs, void* workspace,
       const long long planes = (long long)job.n * X.C;
       const long long total = planes * (X.H + 2 * X.pd) * (X.W + 2 * X.pd);
       KFAC_REQUIRE(total < (1LL << 31), "factor: padded input too large");
-      int blocks = (int)((total + 1023) / 1024);
-      if (blocks > sm_count() * 16) blocks = sm_count() * 16;
-      pad_copy_kernel<<<blocks, 256, 0, stream>>>(X.base, planes, X.H, X.W,
-                                                  X.pd, padded);
+      const int per = (X.H + 2 * X.pd) * (X.W + 2 * X.pd);
+      dim3 pgrid((per + 1023) / 1024 > 8 ? 8 : (per + 1023) / 1024,
+                 (unsigned)(planes < 16384 ? planes : 16384));
+      pad_copy_kernel<<<pgrid, 256, 0, stream>>>(X.base, planes, X.H, X.W,
+                                                 X.pd, padded);
       KFAC_LAUNCH_CHECK("pad_copy_kernel");
       X.base = padded;
       X.H += 2 * X.pd;
