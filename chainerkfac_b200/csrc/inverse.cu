@@ -533,7 +533,7 @@ extern "C" int kfac_inverse_plan_run(kfac_inverse_plan* p, float damping,
       diag_dev);
   KFAC_LAUNCH_CHECK("damping_kernel");
   {
-    dim3 grid(64, p->count);
+    dim3 grid(512, p->count);
     damp_copy_kernel<<<grid, 256, 0, st>>>(p->mats_dev, p->add_dev);
     KFAC_LAUNCH_CHECK("damp_copy_kernel");
   }

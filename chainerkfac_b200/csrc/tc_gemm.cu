@@ -90,6 +90,19 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long* bar,
                                           unsigned parity,
                                           volatile int* abort_flag) {
   const unsigned addr = smem_u32(bar);
+  {
+    // fast path: the phase is usually complete already; test_wait answers
+    // without the suspend machinery of try_wait
+    unsigned done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
   for (unsigned i = 0; i < TC_SPIN_LIMIT; ++i) {
     unsigned done;
     asm volatile(
