@@ -204,7 +204,7 @@ class DeviceWorkload(object):
         cnt = len(self.layers)
         partner = [j ^ 1 for j in range(2 * cnt)]
         role = [j & 1 for j in range(2 * cnt)]
-        self.plan = ops.InversePlan(self.ema, self.inv, partner, role)
+        self.plan = ops.InversePlanSet(self.ema, self.inv, partner, role)
         self.first = True
         self.input_bytes = sum(t.numel() * 4 for t in self.x + self.gy)
 

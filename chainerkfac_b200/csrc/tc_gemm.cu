@@ -181,15 +181,18 @@ __device__ __forceinline__ void sts128(unsigned addr, float4 v) {
                : "memory");
 }
 
-// hi = x with the low 13 mantissa bits cleared (exactly a TF32 value),
-// lo = x - hi (exact in fp32; the tensor core reads its top 11 bits).
+// hi = x rounded to TF32, lo = x - hi (exact in fp32; the tensor core reads
+// its top 11 bits).
 __device__ __forceinline__ void store_split(unsigned hi_addr, unsigned lo_addr,
                                             float4 x) {
   float4 h, l;
-  h.x = __uint_as_float(__float_as_uint(x.x) & 0xFFFFE000u);
-  h.y = __uint_as_float(__float_as_uint(x.y) & 0xFFFFE000u);
-  h.z = __uint_as_float(__float_as_uint(x.z) & 0xFFFFE000u);
-  h.w = __uint_as_float(__float_as_uint(x.w) & 0xFFFFE000u);
+  // round to nearest TF32 (add half an ulp of the 10-bit mantissa to the
+  // magnitude, then clear the low 13 bits): |lo| <= 2^-12 |x|, so what the
+  // tensor core drops from lo is below 2^-23 |x|
+  h.x = __uint_as_float((__float_as_uint(x.x) + 0x1000u) & 0xFFFFE000u);
+  h.y = __uint_as_float((__float_as_uint(x.y) + 0x1000u) & 0xFFFFE000u);
+  h.z = __uint_as_float((__float_as_uint(x.z) + 0x1000u) & 0xFFFFE000u);
+  h.w = __uint_as_float((__float_as_uint(x.w) + 0x1000u) & 0xFFFFE000u);
   l.x = x.x - h.x; l.y = x.y - h.y; l.z = x.z - h.z; l.w = x.w - h.w;
   sts128(hi_addr, h);
   sts128(lo_addr, l);

@@ -118,6 +118,7 @@ def dense_item(x, add_ones_col, alpha, beta, out):
     it.x, it.rows, it.ld, it.d_in = x.data_ptr(), x.shape[0], x.stride(0), \
         x.shape[1]
     it.alpha, it.beta, it.out = alpha, beta, out.data_ptr()
+    it._keep = (locals().get('x', None), locals().get('gy', None), out)
     return it
 
 
@@ -130,6 +131,7 @@ def conv_input_item(x, ksize, stride, pad, add_ones_col, alpha, beta, out):
     it.n, it.c, it.h, it.w = x.shape
     it.ksize, it.stride, it.pad = ksize, stride, pad
     it.alpha, it.beta, it.out = alpha, beta, out.data_ptr()
+    it._keep = (locals().get('x', None), locals().get('gy', None), out)
     return it
 
 
@@ -141,6 +143,7 @@ def conv_grad_item(gy, alpha, beta, out):
     it.x = gy.data_ptr()
     it.n, it.c, it.h, it.w = gy.shape
     it.alpha, it.beta, it.out = alpha, beta, out.data_ptr()
+    it._keep = (locals().get('x', None), locals().get('gy', None), out)
     return it
 
 
@@ -235,6 +238,75 @@ class InversePlan(object):
             self.close()
         except Exception:
             pass
+
+
+class InversePlanSet(object):
+    """Several InversePlans over disjoint subsets of (factor, inverse) pairs,
+    run on separate CUDA streams.  The long serial chain of diagonal-block
+    steps of the largest matrices leaves most SMs idle; running the other
+    size classes next to it fills them.  Pairs (forward/backward factor of one
+    layer) stay in one plan so that pi sees both traces."""
+
+    def __init__(self, factors, inverses, partner, role, l2_coef=None,
+                 scale=None, bounds=(1024, 3000)):
+        n = len(factors)
+        l2_coef = l2_coef if l2_coef is not None else [0.0] * n
+        scale = scale if scale is not None else [1.0] * n
+
+        def size_class(i):
+            d = max(factors[i].shape[0],
+                    factors[partner[i]].shape[0] if partner[i] >= 0 else 0)
+            return sum(d > b for b in bounds)
+        groups = {}
+        for i in range(n):
+            groups.setdefault(size_class(i), []).append(i)
+        self.plans, self.index = [], []
+        for _, idx in sorted(groups.items(), reverse=True):
+            pos = {g: j for j, g in enumerate(idx)}
+            self.plans.append(InversePlan(
+                [factors[i] for i in idx], [inverses[i] for i in idx],
+                [pos[partner[i]] if partner[i] >= 0 else -1 for i in idx],
+                [role[i] for i in idx], [l2_coef[i] for i in idx],
+                [scale[i] for i in idx]))
+            self.index.append(idx)
+        self.streams = [torch.cuda.Stream() for _ in self.plans[1:]]
+        self.count = n
+        dev = factors[0].device
+        self._perm = [torch.tensor(idx, device=dev) for idx in self.index]
+
+    def run(self, damping, use_pi=True):
+        cur = torch.cuda.current_stream()
+        start = torch.cuda.Event()
+        start.record(cur)
+        for plan, st in zip(self.plans[1:], self.streams):
+            st.wait_event(start)
+            with torch.cuda.stream(st):
+                plan.run(damping, use_pi)
+        self.plans[0].run(damping, use_pi)
+        for st in self.streams:
+            done = torch.cuda.Event()
+            done.record(st)
+            cur.wait_event(done)
+
+    def gather(self, attr):
+        """Per-factor values (info / diag) in the caller's original order."""
+        first = getattr(self.plans[0], attr)
+        out = torch.empty(self.count, dtype=first.dtype, device=first.device)
+        for plan, idx in zip(self.plans, self.index):
+            out[self._perm[self.plans.index(plan)]] = getattr(plan, attr)
+        return out
+
+    @property
+    def info(self):
+        return self.gather('info')
+
+    @property
+    def diag(self):
+        return self.gather('diag')
+
+    def close(self):
+        for p in self.plans:
+            p.close()
 
 
 _precond_ws = Workspace()

@@ -366,7 +366,7 @@ class KFAC(_base.GradientMethod):
                 role.append(rl)
                 l2.append(l2c)
                 scale.append(sc)
-        plan = ops.InversePlan(factors, inverses, partner, role, l2, scale)
+        plan = ops.InversePlanSet(factors, inverses, partner, role, l2, scale)
         self._plans[key] = (plan, bufs)
         return plan
 
@@ -383,10 +383,11 @@ class KFAC(_base.GradientMethod):
         for (damping, pi_type), group in groups.items():
             plan = self._plan_for(group)
             plan.run(damping, pi_type == PI_TYPE_TRACENORM)
+            diag = plan.diag
             k = 0
             for fb in group:
                 n = len(fb.cov_emas)
-                fb.set_diag_vals(plan.diag[k:k + n])
+                fb.set_diag_vals(diag[k:k + n])
                 k += n
         conn = [fb for fb in fblocks
                 if isinstance(fb, FB.FisherBlockConnection)]

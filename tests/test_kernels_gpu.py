@@ -425,3 +425,86 @@ def test_wire_pack_unpack_bit_exact(ops):
     ops.wire_unpack(prev, tri, wire, scale=1.0, ema_r=0.5)
     for a, o in zip(arrs, prev):
         assert rel(host(o), 0.5 * a + 0.5) < 1e-6
+
+
+# ------------------------------------------- full-size, size-independent checks
+def test_config4_full_size_inverse_property(ops, engine):
+    """The isolated curvature microbench at its full sizes: factors with the
+    dimensions of every ResNet-50 layer, each X^T X / m + 1e-3 I with m = 8192
+    rows of N(0,1), built by the factor kernel, inverted in one batch (three
+    streams by size class).  Checked through inv * F ~ I, which needs no CPU
+    inverse of a 4608 x 4608 matrix."""
+    if engine == 0:
+        pytest.skip('full-size sweep runs on the tensor-core engine only')
+    dims = sorted({d for l in orc.resnet50_layers()
+                   for d in orc.layer_dims(l)[:2]})
+    g = torch.Generator(device='cuda')
+    g.manual_seed(4)
+    m = 8192
+    F = []
+    for d in dims:
+        X = torch.randn((m, d), device='cuda', generator=g)
+        eye = torch.eye(d, device='cuda') * 1e-3
+        F.append(ops.factor_dense(X, False, alpha=1.0 / m, beta=1.0, out=eye))
+        del X
+    inv = [torch.empty_like(f) for f in F]
+    plan = ops.InversePlanSet(F, inv, [-1] * len(F), [2] * len(F),
+                              scale=[0.0] * len(F))
+    plan.run(0.0)
+    torch.cuda.synchronize()
+    assert int(plan.info.abs().sum()) == 0
+    for d, f, i in zip(dims, F, inv):
+        resid = (i.double() @ f.double() -
+                 torch.eye(d, device='cuda', dtype=torch.float64))
+        err = float(resid.norm() / d ** 0.5)
+        assert err < INVERSE_TOL, (d, err)
+        assert torch.equal(i, i.T)
+    plan.close()
+
+
+def test_config1_mlp_shapes_step(ops):
+    """One K-FAC pass at the MNIST-MLP shapes (784-1000-1000-10, batch 128,
+    damping 1e-3) against the oracle, all three layers in grouped calls."""
+    rng = np.random.default_rng(1)
+    dims = [(784, 1000), (1000, 1000), (1000, 10)]
+    xs = [rng.random((128, di)).astype(np.float32) for di, _ in dims]
+    gys = [(rng.standard_normal((128, do)) / 128).astype(np.float32)
+           for _, do in dims]
+    gWs = [rng.standard_normal((do, di)).astype(np.float32) for di, do in dims]
+    gbs = [rng.standard_normal(do).astype(np.float32) for _, do in dims]
+    F, items = [], []
+    for (di, do), x, gy in zip(dims, xs, gys):
+        A = torch.empty((di + 1, di + 1), device='cuda')
+        G = torch.empty((do, do), device='cuda')
+        F += [A, G]
+        items.append(ops.dense_item(dev(x), True, 1.0 / 128, 0.0, A))
+        items.append(ops.dense_item(dev(gy), False, 128.0, 0.0, G))
+    ops.factor_group(items, F[0].device)
+    inv = [torch.empty_like(f) for f in F]
+    plan = ops.InversePlan(F, inv, [1, 0, 3, 2, 5, 4], [0, 1] * 3)
+    plan.run(1e-3)
+    kW = [torch.empty(w.shape, device='cuda') for w in gWs]
+    kb = [torch.empty(b.shape, device='cuda') for b in gbs]
+    ops.precondition([inv[1], inv[3], inv[5]], [inv[0], inv[2], inv[4]],
+                     [dev(w) for w in gWs], [dev(b) for b in gbs], kW, kb)
+    for i in range(3):
+        want = orc.connection_step(orc.linear_A(xs[i], True),
+                                   orc.linear_G(gys[i]), gWs[i], gbs[i], 1e-3)
+        assert rel(host(F[2 * i]), want['ema_A']) < FACTOR_TOL
+        # These factors are ill-conditioned (uniform[0,1) inputs: cond ~ 6e3
+        # to 1.2e4 with damping 1e-3).  An fp32 inverse can only be expected
+        # to be within cond * u (u = 2^-24) of the exact one: cuSOLVER-class
+        # fp32 code (torch.linalg.inv) is at 6e-5 to 1.2e-4 on these matrices,
+        # while the NumPy path that produced the oracle is at 4e-7.  Each
+        # inverse is therefore judged against the fp64 inverse with the
+        # stated bound or cond * u, whichever is larger.
+        for j, key, diag in ((0, 'A_inv', 'diag_A'), (1, 'G_inv', 'diag_G')):
+            f64 = host(F[2 * i + j]).astype(np.float64)
+            damped = f64 + float(want[diag]) * np.eye(len(f64))
+            truth = np.linalg.inv(damped)
+            tol = max(INVERSE_TOL, np.linalg.cond(damped) * 2.0 ** -24)
+            got_err = rel(host(inv[2 * i + j]), truth)
+            assert got_err < tol, (i, key, got_err, tol)
+        assert rel(host(kW[i]), want['kfgrad_W']) < KFGRAD_TOL
+        assert rel(host(kb[i]), want['kfgrad_b']) < KFGRAD_TOL
+    plan.close()
