@@ -18,7 +18,6 @@
 namespace kfac {
 
 constexpr int DB = 128;        // diagonal block
-constexpr int DLD = DB + 1;    // shared-memory pitch
 constexpr int PW = 512;        // Cholesky panel width (outer blocking)
 
 struct MatInfo {

@@ -1,9 +1,10 @@
 // Tensor-core tile engine for sm_100a: tcgen05.mma (kind::tf32) with fp32
 // accumulators in tensor memory, fp32 operands split into two TF32 terms
-// (x = hi + lo, C += hi*hi + hi*lo + lo*hi) so that results keep fp32-level
-// accuracy (a single TF32 pass misses the 1e-4 bound on large factors).
+// (x = hi + lo with hi rounded to nearest, C += hi*hi + hi*lo + lo*hi) so that
+// results keep near-fp32 accuracy (a single TF32 pass misses the 1e-4 bound on
+// large factors).
 //
-// One CTA (8 producer/epilogue warps + 1 MMA warp) owns a 128 x N tile,
+// One CTA (16 producer/epilogue warps + 1 MMA warp) owns a 128 x N tile,
 // N <= 256.  Producer warps gather the operands from global memory (strided
 // views, transposing views or im2col patches of an NCHW tensor), split them
 // and write the K-major, 128-byte-swizzled shared-memory layout that the MMA
@@ -34,9 +35,9 @@ constexpr int TC_EPI_PITCH = TC_BN + 1;         // floats
 constexpr int TC_SMEM_BYTES = TC_STAGES * TC_STAGE_BYTES + 8192 + 1024;
 constexpr unsigned TC_SPIN_LIMIT = 1u << 22;
 // Two accumulators per tile: columns [0, 256) collect hi*hi, columns
-// [256, 512) the two small cross terms.  The tensor core truncates when it
-// adds into an accumulator, so keeping the (2^-11 smaller) cross terms apart
-// cuts the accumulations that touch the large sum to a third.
+// [256, 512) the two cross terms, which are 2^-12 smaller; they are added in
+// the epilogue.  Keeping them apart means only one MMA in three adds into the
+// large sum.
 constexpr int TC_TMEM_COLS = 2 * TC_BN;
 
 static __device__ int g_tc_status = 0;

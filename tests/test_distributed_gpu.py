@@ -36,11 +36,13 @@ T = torch.randint(0, 5, (8,), generator=g).cuda()
 half = 8 // world
 xs, ts = X[rank * half:(rank + 1) * half], T[rank * half:(rank + 1) * half]
 
-for pic in (True, False):
+for pic, early, own in ((True, False, 'reference'), (False, False, 'reference'),
+                        (True, True, 'balanced')):
     model = make()
     comm = ck.create_communicator('pure_nccl')
     opt = ck.DistributedKFAC(comm, lr=0.05, momentum=0.9, cov_ema_decay=1.0,
-                             damping=1e-2, only_pic_update_weight=pic)
+                             damping=1e-2, only_pic_update_weight=pic,
+                             communicate_after_forward=early, ownership=own)
     opt.setup(model)
     lossfun = lambda a, b: F.cross_entropy(model(a), b)
     opt.update(lossfun, xs, ts)          # first call: broadcast only
@@ -63,7 +65,7 @@ for pic in (True, False):
         for (n1, p1), (n2, p2) in zip(ref.named_parameters(),
                                       model.named_parameters()):
             err = float((p1 - p2).norm() / p1.norm())
-            assert err < 2e-3, (pic, n1, err)
+            assert err < 2e-3, (pic, early, own, n1, err)
 dist.barrier()
 if rank == 0:
     print('DISTRIBUTED_OK')
