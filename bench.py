@@ -591,6 +591,7 @@ MICRO_CASES = {
     'conv_grad_c256_hw56': ('conv_grad', dict(n=32, c=256, hw=56)),
     'conv_grad_c64_hw56': ('conv_grad', dict(n=32, c=64, hw=56)),
     'conv3x3_c64_hw56': ('conv_input', dict(n=32, c=64, hw=56, k=3, s=1, p=1)),
+    'conv3x3_c64_hw128': ('conv_input', dict(n=32, c=64, hw=128, k=3, s=1, p=1)),
     'conv3x3_c256_hw14': ('conv_input', dict(n=32, c=256, hw=14, k=3, s=1, p=1)),
     'conv3x3_c512_hw7': ('conv_input', dict(n=32, c=512, hw=7, k=3, s=1, p=1)),
     'conv7x7_c3_hw224': ('conv_input', dict(n=32, c=3, hw=224, k=7, s=2, p=3)),

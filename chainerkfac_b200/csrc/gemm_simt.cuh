@@ -264,7 +264,9 @@ int launch_grouped_gemm(const GemmDesc* descs_dev, int ndesc, int total_tiles,
 int engine();   // 1: tensor cores (default), 0: fp32 FFMA tiles
 int tc_tiles(GemmDesc& g);
 int launch_tc_grouped(const GemmDesc* descs_dev, int ndesc, int total_tiles,
-                      float lr, float momentum, cudaStream_t stream);
+                      float lr, float momentum, bool tails,
+                      cudaStream_t stream);
+bool tc_desc_has_tails(const GemmDesc& g);
 size_t tc_factor_workspace_bytes(long long rows, int d);
 size_t tc_pad_bytes(const Operand& X, int n);
 int run_factor_tc(const Operand& X, long long rows, int d, float alpha,

@@ -257,6 +257,7 @@ chol_diag_kernel(const MatInfo* __restrict__ mats, const int* __restrict__ ids,
 constexpr size_t kDiagSmemBytes = (DB * (DB + 4) + 3 * DB) * sizeof(float);
 
 struct Launch {
+  int tails;     // grouped gemm: some contraction is not a multiple of 32
   int kind;      // 0 diag kernel, 1 grouped gemm
   int off;       // offset into ids / descs
   int n;         // number of ids / descs
@@ -355,12 +356,13 @@ extern "C" int kfac_inverse_plan_create(
   const bool use_tc = engine() == 1;
 
   auto begin_gemm = [&]() {
-    Launch l = {1, (int)descs.size(), 0, 0, 0};
+    Launch l = {0, 1, (int)descs.size(), 0, 0, 0};
     return l;
   };
   auto push_desc = [&](Launch& l, GemmDesc g) {
     g.tile_begin = l.tiles;
     l.tiles += use_tc ? tc_tiles(g) : gemm_desc_tiles(g);
+    if (tc_desc_has_tails(g)) l.tails = 1;
     g.kfW = g.kfb = g.pW = g.pb = g.vW = g.vb = nullptr;
     g.dW = 0;
     g.splits = 1;
@@ -381,7 +383,7 @@ extern "C" int kfac_inverse_plan_create(
   for (int po = 0; po < dmax; po += PW) {
     const int inner = std::min(PW, dmax - po);
     for (int o = po; o < po + inner; o += DB) {
-      Launch dl = {0, (int)ids.size(), 0, 0, o / DB};
+      Launch dl = {0, 0, (int)ids.size(), 0, 0, o / DB};
       for (int i : order)
         if (dims[i] > o) { ids.push_back(i); dl.n += 1; }
       launches.push_back(dl);
@@ -544,7 +546,7 @@ extern "C" int kfac_inverse_plan_run(kfac_inverse_plan* p, float damping,
     } else {
       int rc = p->use_tc
                    ? launch_tc_grouped(p->descs_dev + l.off, l.n, l.tiles, 0.f,
-                                       0.f, st)
+                                       0.f, l.tails != 0, st)
                    : launch_grouped_gemm(p->descs_dev + l.off, l.n, l.tiles,
                                          0.f, 0.f, st);
       if (rc != KFAC_OK) return rc;

@@ -100,10 +100,15 @@ extern "C" int kfac_precondition(
                             descs.size() * sizeof(GemmDesc),
                             cudaMemcpyHostToDevice, st));
   if (use_tc) {
-    int rc = launch_tc_grouped(descs_dev, count, tiles1, 0.f, 0.f, st);
+    bool t1 = false, t2 = false;
+    for (int i = 0; i < count; ++i) {
+      t1 = t1 || tc_desc_has_tails(descs[i]);
+      t2 = t2 || tc_desc_has_tails(descs[count + i]);
+    }
+    int rc = launch_tc_grouped(descs_dev, count, tiles1, 0.f, 0.f, t1, st);
     if (rc != KFAC_OK) return rc;
     return launch_tc_grouped(descs_dev + count, count, tiles2, lr, momentum,
-                             st);
+                             t2, st);
   }
   int rc = launch_grouped_gemm(descs_dev, count, tiles1, 0.f, 0.f, st);
   if (rc != KFAC_OK) return rc;

@@ -187,13 +187,11 @@ __device__ __forceinline__ void sts128(unsigned addr, float4 v) {
 __device__ __forceinline__ void store_split(unsigned hi_addr, unsigned lo_addr,
                                             float4 x) {
   float4 h, l;
-  // round to nearest TF32 (add half an ulp of the 10-bit mantissa to the
-  // magnitude, then clear the low 13 bits): |lo| <= 2^-12 |x|, so what the
-  // tensor core drops from lo is below 2^-23 |x|
-  h.x = __uint_as_float((__float_as_uint(x.x) + 0x1000u) & 0xFFFFE000u);
-  h.y = __uint_as_float((__float_as_uint(x.y) + 0x1000u) & 0xFFFFE000u);
-  h.z = __uint_as_float((__float_as_uint(x.z) + 0x1000u) & 0xFFFFE000u);
-  h.w = __uint_as_float((__float_as_uint(x.w) + 0x1000u) & 0xFFFFE000u);
+  // hi = x rounded to the nearest TF32 value (one cvt instruction)
+  { unsigned u; asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x.x)); h.x = __uint_as_float(u); }
+  { unsigned u; asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x.y)); h.y = __uint_as_float(u); }
+  { unsigned u; asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x.z)); h.z = __uint_as_float(u); }
+  { unsigned u; asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x.w)); h.w = __uint_as_float(u); }
   l.x = x.x - h.x; l.y = x.y - h.y; l.z = x.z - h.z; l.w = x.w - h.w;
   sts128(hi_addr, h);
   sts128(lo_addr, l);
@@ -325,56 +323,30 @@ __device__ __forceinline__ void kstate_advance(const Operand& op, KState& s) {
   }
 }
 
-// Gather the NTASK chunks of one k-block into registers.  The loads are
-// issued back to back, each from an address that is always legal; nothing
-// between two loads depends on a loaded value.  `vec` (uniform per tile):
-// every chunk of this operand is 16-byte aligned and contiguous.
-template <int NTASK, bool IM2COL>
-__device__ __forceinline__ void tc_load_tile(const Operand& op,
-                                             const PTask task[NTASK],
-                                             const KState& ks, int kend,
-                                             bool vec, float4 v[NTASK]) {
+// Element offsets of a chunk's 4 k (strided: row offsets; im2col: pixel
+// offsets of an unpadded convolution -- a padded input is copied into a
+// zero-bordered buffer first, so every tap of every pixel is in range).
+// With TAILS, offsets of k at or beyond kend are 0 (a legal address; the
+// value is zeroed after the load).
+template <bool IM2COL, bool TAILS>
+__device__ __forceinline__ void tc_koffsets(const Operand& op,
+                                            const KState& ks, int kend,
+                                            int o[4]) {
   const int k = ks.k;
-  const bool tail = k + 3 >= kend;
-
   if (IM2COL) {
-    // The tensor-core path always sees an unpadded convolution (a padded
-    // input is copied into a zero-bordered buffer first), so every tap of
-    // every pixel is in range and the gather needs no bounds logic.
-    int pix[4];
-    {
-      int n = ks.a, oy = ks.b, ox = ks.c;
-      const int chw = op.C * op.H * op.W;
+    int n = ks.a, oy = ks.b, ox = ks.c;
+    const int chw = op.C * op.H * op.W;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        pix[j] = (k + j < kend) ? n * chw + oy * op.st * op.W + ox * op.st : 0;
-        if (++ox >= op.Wo) {
-          ox = 0;
-          if (++oy >= op.Ho) { oy = 0; ++n; }
-        }
-      }
-    }
-#pragma unroll
-    for (int t = 0; t < NTASK; ++t) {
-      if (task[t].soff == ~0u) continue;
-      v[t].x = task[t].p[(long long)pix[0] * task[t].m];
-      v[t].y = task[t].p[(long long)pix[1] * task[t].m];
-      v[t].z = task[t].p[(long long)pix[2] * task[t].m];
-      v[t].w = task[t].p[(long long)pix[3] * task[t].m];
-    }
-    if (tail) {
-#pragma unroll
-      for (int t = 0; t < NTASK; ++t) {
-        if (k + 0 >= kend) v[t].x = 0.f;
-        if (k + 1 >= kend) v[t].y = 0.f;
-        if (k + 2 >= kend) v[t].z = 0.f;
-        if (k + 3 >= kend) v[t].w = 0.f;
+    for (int j = 0; j < 4; ++j) {
+      o[j] = n * chw + oy * op.st * op.W + ox * op.st;
+      if (TAILS && k + j >= kend) o[j] = 0;
+      if (++ox >= op.Wo) {
+        ox = 0;
+        if (++oy >= op.Ho) { oy = 0; ++n; }
       }
     }
     return;
   }
-
-  int o[4];
   if (op.period == 1) {
 #pragma unroll
     for (int j = 0; j < 4; ++j) o[j] = k + j;
@@ -386,10 +358,21 @@ __device__ __forceinline__ void tc_load_tile(const Operand& op,
       o[j] = (int)((long long)q * op.s_outer + (long long)r * op.s_inner);
     }
   }
-  if (tail) {
+  if (TAILS) {
 #pragma unroll
     for (int j = 0; j < 4; ++j) if (k + j >= kend) o[j] = 0;
   }
+}
+
+// Gather the NTASK chunks of one k-block into registers.  The loads are
+// issued back to back, each from an address that is always legal; nothing
+// between two loads depends on a loaded value.  `vec` (uniform per tile):
+// every chunk of this operand is 16-byte aligned and contiguous.
+template <int NTASK, bool TAILS>
+__device__ __forceinline__ void tc_load_tile(const PTask task[NTASK],
+                                             const int o[4], int k, int kend,
+                                             bool vec, float4 v[NTASK]) {
+  const bool tail = TAILS && (k + 3 >= kend);
   if (vec && !tail) {
 #pragma unroll
     for (int t = 0; t < NTASK; ++t)
@@ -456,7 +439,7 @@ __device__ __forceinline__ void tc_tri_tile(int t, int& bi, int& bj) {
   }
 }
 
-template <bool IM2COL>
+template <bool IM2COL, bool TAILS>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 tc_gemm_kernel(const GemmDesc* __restrict__ descs, int ndesc,
                const __grid_constant__ GemmDesc inline_desc, float lr,
@@ -593,10 +576,21 @@ tc_gemm_kernel(const GemmDesc* __restrict__ descs, int ndesc,
         if (tid == 0) TC_TRACE(pb, 3);
       }
       if (kb < nkb) {
-        tc_load_tile<NTA, IM2COL>(A, ia, ka, kend_i, vec_a, va);
-        tc_load_tile<NTB, IM2COL>(B, ib, kb_state, kend_i, vec_b, vb);
+        int oa[4], ob[4];
+        tc_koffsets<IM2COL, TAILS>(A, ka, kend_i, oa);
+        if (IM2COL) {
+          // both operands are the same patch matrix and use the same chunk
+          // mapping: one set of pixel offsets serves both
+#pragma unroll
+          for (int j = 0; j < 4; ++j) ob[j] = oa[j];
+        } else {
+          tc_koffsets<IM2COL, TAILS>(B, kb_state, kend_i, ob);
+        }
+        tc_load_tile<NTA, TAILS>(ia, oa, ka.k, kend_i, vec_a, va);
+        tc_load_tile<NTB, TAILS>(ib, ob, IM2COL ? ka.k : kb_state.k, kend_i,
+                                 vec_b, vb);
         kstate_advance<IM2COL>(A, ka);
-        kstate_advance<IM2COL>(B, kb_state);
+        if (!IM2COL) kstate_advance<IM2COL>(B, kb_state);
         if (tid == 0) TC_TRACE(kb, 4);
       }
     }
@@ -853,10 +847,16 @@ static int tc_prepare() {
   KFAC_REQUIRE(dev >= 0 && dev < 64, "device index %d unsupported", dev);
   std::lock_guard<std::mutex> lock(mu);
   if (!done[dev]) {
-    KFAC_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<false>,
+    KFAC_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<false, false>,
                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    TC_SMEM_BYTES));
-    KFAC_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<true>,
+    KFAC_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<false, true>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   TC_SMEM_BYTES));
+    KFAC_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<true, false>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   TC_SMEM_BYTES));
+    KFAC_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<true, true>,
                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    TC_SMEM_BYTES));
     done[dev] = true;
@@ -865,15 +865,31 @@ static int tc_prepare() {
 }
 
 int launch_tc_grouped(const GemmDesc* descs_dev, int ndesc, int total_tiles,
-                      float lr, float momentum, cudaStream_t stream) {
+                      float lr, float momentum, bool tails,
+                      cudaStream_t stream) {
   if (ndesc <= 0 || total_tiles <= 0) return KFAC_OK;
   int rc = tc_prepare();
   if (rc != KFAC_OK) return rc;
   GemmDesc dummy = {};
-  tc_gemm_kernel<false><<<total_tiles, TC_THREADS, TC_SMEM_BYTES, stream>>>(
-      descs_dev, ndesc, dummy, lr, momentum);
+  if (tails)
+    tc_gemm_kernel<false, true><<<total_tiles, TC_THREADS, TC_SMEM_BYTES,
+                                  stream>>>(descs_dev, ndesc, dummy, lr,
+                                            momentum);
+  else
+    tc_gemm_kernel<false, false><<<total_tiles, TC_THREADS, TC_SMEM_BYTES,
+                                   stream>>>(descs_dev, ndesc, dummy, lr,
+                                             momentum);
   KFAC_LAUNCH_CHECK("tc_gemm_kernel");
   return KFAC_OK;
+}
+
+// True when some k-block of the problem can be cut by the end of its
+// contraction range (ranges start at multiples of 128 or of k_per_split, both
+// multiples of the k-block).
+bool tc_desc_has_tails(const GemmDesc& g) {
+  if (g.K % TC_BK != 0) return true;
+  if (g.splits > 1 && g.k_per_split % TC_BK != 0) return true;
+  return false;
 }
 
 struct TcFactorSplit {
@@ -1038,27 +1054,33 @@ int run_factor_group_tc(int count, const FactorJob* jobs, void* workspace,
       g.tile_begin = total;
       total += g.ntiles * (g.splits > 1 ? g.splits : 1);
     }
+    bool tails = false;
+    for (const GemmDesc& g : v) tails = tails || tc_desc_has_tails(g);
+    const GemmDesc* dev_descs = nullptr;
+    GemmDesc inl = {};
     if (v.size() == 1) {
-      if (m == 1)
-        tc_gemm_kernel<true><<<total, TC_THREADS, TC_SMEM_BYTES, stream>>>(
-            nullptr, 1, v[0], 0.f, 0.f);
-      else
-        tc_gemm_kernel<false><<<total, TC_THREADS, TC_SMEM_BYTES, stream>>>(
-            nullptr, 1, v[0], 0.f, 0.f);
+      inl = v[0];
     } else {
       void* dev = nullptr;
       rc = ring_alloc(v.size() * sizeof(GemmDesc), &dev);
       if (rc != KFAC_OK) return rc;
       KFAC_CUDA(cudaMemcpyAsync(dev, v.data(), v.size() * sizeof(GemmDesc),
                                 cudaMemcpyHostToDevice, stream));
-      GemmDesc dummy = {};
-      if (m == 1)
-        tc_gemm_kernel<true><<<total, TC_THREADS, TC_SMEM_BYTES, stream>>>(
-            static_cast<const GemmDesc*>(dev), (int)v.size(), dummy, 0.f, 0.f);
-      else
-        tc_gemm_kernel<false><<<total, TC_THREADS, TC_SMEM_BYTES, stream>>>(
-            static_cast<const GemmDesc*>(dev), (int)v.size(), dummy, 0.f, 0.f);
+      dev_descs = static_cast<const GemmDesc*>(dev);
     }
+    const int nd = (int)v.size();
+    if (m == 1 && tails)
+      tc_gemm_kernel<true, true><<<total, TC_THREADS, TC_SMEM_BYTES, stream>>>(
+          dev_descs, nd, inl, 0.f, 0.f);
+    else if (m == 1)
+      tc_gemm_kernel<true, false><<<total, TC_THREADS, TC_SMEM_BYTES, stream>>>(
+          dev_descs, nd, inl, 0.f, 0.f);
+    else if (tails)
+      tc_gemm_kernel<false, true><<<total, TC_THREADS, TC_SMEM_BYTES, stream>>>(
+          dev_descs, nd, inl, 0.f, 0.f);
+    else
+      tc_gemm_kernel<false, false><<<total, TC_THREADS, TC_SMEM_BYTES,
+                                     stream>>>(dev_descs, nd, inl, 0.f, 0.f);
     KFAC_LAUNCH_CHECK("tc_gemm_kernel");
   }
   if (!reduces.empty()) {
