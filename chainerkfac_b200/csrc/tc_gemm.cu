@@ -239,8 +239,8 @@ static __device__ __align__(256) float g_ones_page[64] = {
 //     p + (long long)o_j * mul        (one multiply-add per element)
 // where o_j is the k-dependent offset shared by all tasks of the thread.
 struct PTask {
-  const float* p;   // column base (or the zero / ones page)
-  int m;            // multiplier of the k-dependent offset (0 for pages)
+  const char* p;    // column base (or the zero / ones page), as bytes
+  int m;            // byte multiplier of the k-dependent offset (0 for pages)
   unsigned soff;    // swizzled byte offset inside the tile, ~0u: idle task
 };
 
@@ -258,26 +258,28 @@ __device__ __forceinline__ void tc_task_setup(const Operand& op, int c0,
     PTask v;
     v.soff = row < rows
                  ? (unsigned)(row * 128 + ((chunk ^ (row & 7)) << 4)) : ~0u;
-    v.p = g_zero_page;
-    v.m = 0;
+    const float* p = g_zero_page;
+    int m = 0;
     if (row < rows) {
       const int c = c0 + row;
       if (IM2COL) {
         const int info = kykx[row];
         if (info >= 0) {
-          v.p = op.base + coff[row];
-          v.m = 1;
+          p = op.base + coff[row];
+          m = 1;
         } else if (info == -2) {
-          v.p = g_ones_page;
+          p = g_ones_page;
         }
       } else if (c < op.ncols) {
-        v.p = op.base + (long long)c * op.s_col;
-        v.m = op.period == 1 ? (int)op.s_outer : 1;
+        p = op.base + (long long)c * op.s_col;
+        m = op.period == 1 ? (int)op.s_outer : 1;
       } else if (c == op.extra_idx) {
-        if (op.extra) { v.p = op.extra; v.m = 1; }
-        else v.p = g_ones_page;
+        if (op.extra) { p = op.extra; m = 1; }
+        else p = g_ones_page;
       }
     }
+    v.p = reinterpret_cast<const char*>(p);
+    v.m = m * 4;
     task[t] = v;
   }
 }
@@ -383,10 +385,10 @@ __device__ __forceinline__ void tc_load_tile(const PTask task[NTASK],
 #pragma unroll
     for (int t = 0; t < NTASK; ++t) {
       if (task[t].soff == ~0u) continue;
-      v[t].x = task[t].p[(long long)o[0] * task[t].m];
-      v[t].y = task[t].p[(long long)o[1] * task[t].m];
-      v[t].z = task[t].p[(long long)o[2] * task[t].m];
-      v[t].w = task[t].p[(long long)o[3] * task[t].m];
+      v[t].x = *reinterpret_cast<const float*>(task[t].p + (long long)o[0] * task[t].m);
+      v[t].y = *reinterpret_cast<const float*>(task[t].p + (long long)o[1] * task[t].m);
+      v[t].z = *reinterpret_cast<const float*>(task[t].p + (long long)o[2] * task[t].m);
+      v[t].w = *reinterpret_cast<const float*>(task[t].p + (long long)o[3] * task[t].m);
     }
   }
   if (tail) {
