@@ -40,6 +40,7 @@ DAMPING = 2.5e-4
 LR = 0.01
 MOMENTUM = 0.9
 WORKLOAD = 'resnet50_kfac_step_b32_224'
+OVERLAP = True           # start the largest factors' inverse during the factor build
 OWNERSHIP = 'balanced'   # layer ownership at N > 1 ('reference': by count)
 
 
@@ -226,10 +227,21 @@ class DeviceWorkload(object):
         return items
 
     def factors(self):
-        # all 108 factors in one grouped call, running average fused in
+        # all 108 factors in one grouped call per size class, running average
+        # fused in, largest class first: its inverse (a long serial chain that
+        # uses few SMs) starts on a side stream while the other layers'
+        # factors are still being built
         r, rest = (1.0, 0.0) if self.first else (DECAY, 1.0 - DECAY)
-        self.ops.factor_group(self.factor_items(self.ema, r, rest),
-                              self.ema[0].device)
+        items = self.factor_items(self.ema, r, rest)
+        dev = self.ema[0].device
+        classes = self.plan.classes() if OVERLAP else []
+        done = set()
+        for c, idx in enumerate(classes[:-1]):
+            self.ops.factor_group([items[i] for i in idx], dev)
+            self.plan.start_class(c, DAMPING, True)
+            done.update(idx)
+        self.ops.factor_group([it for i, it in enumerate(items)
+                               if i not in done], dev)
         self.first = False
 
     def inverses(self):
@@ -303,6 +315,7 @@ class DistributedWorkload(DeviceWorkload):
             self.ag_arrays.append(ag)
 
     def factors(self):
+        # factors must be reduced across ranks before any inverse can start
         self.ops.factor_group(self.factor_items(self.cov, 1.0, 0.0),
                               self.cov[0].device)
 
@@ -659,14 +672,19 @@ def main():
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--no-e2e', action='store_true')
     ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--no-overlap', action='store_true',
+                    help='do not start the largest inverses during the '
+                         'factor build')
     ap.add_argument('--ownership', default=None,
                     choices=['balanced', 'reference'])
     ap.add_argument('--micro', choices=sorted(MICRO_CASES), default=None,
                     help='time one single-kernel case instead of the step')
     args = ap.parse_args()
+    global OWNERSHIP, OVERLAP
     if args.ownership:
-        global OWNERSHIP
         OWNERSHIP = args.ownership
+    if args.no_overlap:
+        OVERLAP = False
     if args.micro:
         run_micro(args)
     elif args.impl == 'reference':

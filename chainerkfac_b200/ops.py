@@ -270,23 +270,54 @@ class InversePlanSet(object):
                 [scale[i] for i in idx]))
             self.index.append(idx)
         self.streams = [torch.cuda.Stream() for _ in self.plans[1:]]
+        # optional early start of a class (see start_class)
+        self.early_streams = [torch.cuda.Stream(priority=-1)
+                              for _ in self.plans]
+        self._early = {}
         self.count = n
         dev = factors[0].device
         self._perm = [torch.tensor(idx, device=dev) for idx in self.index]
+
+    def classes(self):
+        """Index lists (caller's order) of the size classes, largest first."""
+        return [list(idx) for idx in self.index]
+
+    def start_class(self, c, damping, use_pi=True):
+        """Start the plan of size class ``c`` now, on its own high-priority
+        side stream, ordered after the work queued so far on the current
+        stream.  The long serial chains of the large classes then overlap
+        whatever the caller queues next (typically the factor build of the
+        other layers); ``run`` later skips started classes and joins their
+        streams.  Only legal once the factors of that class are final."""
+        cur = torch.cuda.current_stream()
+        ready = torch.cuda.Event()
+        ready.record(cur)
+        st = self.early_streams[c]
+        st.wait_event(ready)
+        with torch.cuda.stream(st):
+            self.plans[c].run(damping, use_pi)
+            ev = torch.cuda.Event()
+            ev.record(st)
+        self._early[c] = ev
 
     def run(self, damping, use_pi=True):
         cur = torch.cuda.current_stream()
         start = torch.cuda.Event()
         start.record(cur)
-        for plan, st in zip(self.plans[1:], self.streams):
+        rest = [p for c, p in enumerate(self.plans) if c not in self._early]
+        for plan, st in zip(rest[1:], self.streams):
             st.wait_event(start)
             with torch.cuda.stream(st):
                 plan.run(damping, use_pi)
-        self.plans[0].run(damping, use_pi)
-        for st in self.streams:
+        if rest:
+            rest[0].run(damping, use_pi)
+        for plan, st in zip(rest[1:], self.streams):
             done = torch.cuda.Event()
             done.record(st)
             cur.wait_event(done)
+        for ev in self._early.values():
+            cur.wait_event(ev)
+        self._early = {}
 
     def gather(self, attr):
         """Per-factor values (info / diag) in the caller's original order."""

@@ -212,6 +212,7 @@ class KFAC(_base.GradientMethod):
         # build the factors of all layers in one grouped launch after
         # backward instead of one launch per hook call (same values)
         self.group_factors = True
+        self._factors_pending = False
         self._plans = {}
         self.observation = {}
 
@@ -273,7 +274,11 @@ class KFAC(_base.GradientMethod):
                 loss.backward(torch.full_like(loss, self._loss_scale))
             else:
                 loss.backward()
-        self.flush_factors()
+        # with a valid inverse plan the factor build is pipelined with the
+        # inverses inside update_kfgrads; otherwise build everything now
+        self._factors_pending = self._pipeline_ready()
+        if not self._factors_pending:
+            self.flush_factors()
         self.loss = loss.detach()
 
     def update(self, lossfun=None, *args, **kwargs):
@@ -370,12 +375,62 @@ class KFAC(_base.GradientMethod):
         self._plans[key] = (plan, bufs)
         return plan
 
+    def _pipeline_ready(self):
+        """True when the factor build may be pipelined with the inverses: a
+        single process, no accumulation, grouped factors, one (damping, pi)
+        group, and the inverse plans of an earlier step still valid."""
+        if type(self) is not KFAC or self.acc_iters != 1 or \
+                not self.group_factors or not self.fblocks:
+            return False
+        first = self.fblocks[0]
+        if any(fb.cov_emas is None or
+               (fb.damping, fb._pi_type) != (first.damping, first._pi_type)
+               for fb in self.fblocks):
+            return False
+        return tuple(id(fb) for fb in self.fblocks) in self._plans
+
+    def _pipelined_factors_and_emas(self, fblocks, plan):
+        """Build factors and running averages size class by size class,
+        largest first, and start each class's inverses on a side stream as
+        soon as its factors are final: the long serial chains of the largest
+        factors then run next to the factor build of the other layers."""
+        owner = []
+        for fb in fblocks:
+            owner += [fb] * len(fb.cov_emas)
+        classes = plan.classes()
+        dev = next(self.target.params()).data.device
+        first = fblocks[0]
+        for c, idx in enumerate(classes):
+            blocks, seen = [], set()
+            for i in idx:
+                if id(owner[i]) not in seen:
+                    seen.add(id(owner[i]))
+                    blocks.append(owner[i])
+            items = []
+            for fb in blocks:
+                if isinstance(fb, FB.FisherBlockConnection):
+                    items += fb.flush_items()
+            if items:
+                ops.factor_group(items, dev)
+            for fb in blocks:
+                fb.update_cov_emas()
+            if c + 1 < len(classes):
+                plan.start_class(c, first.damping,
+                                 first._pi_type == PI_TYPE_TRACENORM)
+        for fb in fblocks:
+            fb._keep_x = fb._keep_gy = None
+
     def update_kfgrads(self, fblocks):
         fblocks = list(fblocks)
         if not fblocks:
             return
-        for fblock in fblocks:
-            fblock.update_cov_emas()
+        if self._factors_pending:
+            self._factors_pending = False
+            plan = self._plan_for(fblocks)
+            self._pipelined_factors_and_emas(fblocks, plan)
+        else:
+            for fblock in fblocks:
+                fblock.update_cov_emas()
         # one batched damped inverse per (damping, pi rule) group
         groups = {}
         for fb in fblocks:
