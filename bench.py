@@ -40,6 +40,7 @@ DAMPING = 2.5e-4
 LR = 0.01
 MOMENTUM = 0.9
 WORKLOAD = 'resnet50_kfac_step_b32_224'
+COMMUNICATOR = 'peer_memory'   # or 'pure_nccl' (NCCL reduce / broadcast)
 OVERLAP = True           # start the largest factors' inverse during the factor build
 OWNERSHIP = 'balanced'   # layer ownership at N > 1 ('reference': by count)
 
@@ -226,6 +227,12 @@ class DeviceWorkload(object):
                 items.append(ops.dense_item(self.gy[i], False, r * n, rest, G))
         return items
 
+    def factors_alone(self):
+        """The factor stage with nothing else on the device: every factor in
+        one grouped call, no inverse started beside it."""
+        items = self.factor_items(self.ema, DECAY, 1.0 - DECAY)
+        self.ops.factor_group(items, self.ema[0].device)
+
     def factors(self):
         # all 108 factors in one grouped call per size class, running average
         # fused in, largest class first: its inverse (a long serial chain that
@@ -273,7 +280,11 @@ class DistributedWorkload(DeviceWorkload):
     and preconditions/updates only its own layers, and the updated weights
     are all-gathered.  Ownership is cost-balanced by default (OWNERSHIP);
     'reference' is the reference's contiguous split of the layer list by
-    count."""
+    count.
+
+    The first exchange runs size class by size class, largest first: as soon
+    as a class is reduced its owners start its inverses on a side stream, next
+    to the factor build and exchange of the remaining classes."""
 
     def __init__(self, device, seed, comm):
         super(DistributedWorkload, self).__init__(device, seed)
@@ -290,44 +301,73 @@ class DistributedWorkload(DeviceWorkload):
             self.indices = orc.split_indices(cnt, comm.size)
         self.mine = self.indices[comm.rank]
         self.cov = [torch.zeros_like(e) for e in self.ema]
+        bounds = self.plan.bounds
         self.plan.close()
         own = self.mine
-        self.plan = self.ops.InversePlan(
+        self.plan = self.ops.InversePlanSet(
             [self.ema[2 * i + j] for i in own for j in (0, 1)],
             [self.inv[2 * i + j] for i in own for j in (0, 1)],
             [k ^ 1 for k in range(2 * len(own))],
-            [k & 1 for k in range(2 * len(own))])
-        self.rs_arrays = []
+            [k & 1 for k in range(2 * len(own))], bounds=bounds)
+        # size classes over all layers, largest first, as the plan forms them
+        key_of = [sum(max(dA, dG) > b for b in bounds)
+                  for dA, dG, _, _ in self.dims]
+        keys = sorted(set(key_of), reverse=True) if OVERLAP else [None]
+        self.class_layers, self.class_rs, self.class_plan = [], [], []
+        for key in keys:
+            layers = [i for i in range(cnt) if key is None or key_of[i] == key]
+            rs = []
+            for idx in self.indices:
+                loc = []
+                for i in idx:
+                    if i not in layers:
+                        continue
+                    # sorted parameter names: W before b
+                    loc.append((self.gW[i], False))
+                    if self.gb[i] is not None:
+                        loc.append((self.gb[i], False))
+                    loc.append((self.cov[2 * i], True))
+                    loc.append((self.cov[2 * i + 1], True))
+                rs.append(loc)
+            self.class_layers.append(layers)
+            self.class_rs.append(rs)
+            self.class_plan.append(
+                self.plan.class_keys.index(key)
+                if key in self.plan.class_keys else None)
         self.ag_arrays = []
         for idx in self.indices:
-            rs, ag = [], []
+            ag = []
             for i in idx:
-                # sorted parameter names: W before b
-                rs.append((self.gW[i], False))
-                if self.gb[i] is not None:
-                    rs.append((self.gb[i], False))
-                rs.append((self.cov[2 * i], True))
-                rs.append((self.cov[2 * i + 1], True))
                 ag.append((self.W[i], False))
                 if self.b[i] is not None:
                     ag.append((self.b[i], False))
-            self.rs_arrays.append(rs)
             self.ag_arrays.append(ag)
+        if hasattr(comm, 'reserve'):
+            from chainerkfac_b200.communicators import _utility
+            comm.reserve(max([_utility.get_nelems(rs) for rs in self.class_rs]
+                             + [_utility.get_nelems(self.ag_arrays)]), device)
 
     def factors(self):
-        # factors must be reduced across ranks before any inverse can start
-        self.ops.factor_group(self.factor_items(self.cov, 1.0, 0.0),
-                              self.cov[0].device)
+        r, rest = (1.0, 0.0) if self.first else (DECAY, 1.0 - DECAY)
+        items = self.factor_items(self.cov, 1.0, 0.0)
+        dev = self.cov[0].device
+        mine = set(self.mine)
+        last = len(self.class_layers) - 1
+        for c, layers in enumerate(self.class_layers):
+            self.ops.factor_group(
+                [items[2 * i + j] for i in layers for j in (0, 1)], dev)
+            # exchange 1 for this class, then the owner's running average
+            self.comm.reduce_scatter_v_arrays(self.class_rs[c])
+            for i in layers:
+                if i in mine:
+                    for j in (0, 1):
+                        self.ops.axpby(r, self.cov[2 * i + j], rest,
+                                       self.ema[2 * i + j], self.ema[2 * i + j])
+            if c < last and self.class_plan[c] is not None:
+                self.plan.start_class(self.class_plan[c], DAMPING, True)
+        self.first = False
 
     def inverses(self):
-        # exchange 1, then the owner's running average and inverses
-        self.comm.reduce_scatter_v_arrays(self.rs_arrays)
-        r, rest = (1.0, 0.0) if self.first else (DECAY, 1.0 - DECAY)
-        for i in self.mine:
-            for j in (0, 1):
-                self.ops.axpby(r, self.cov[2 * i + j], rest,
-                               self.ema[2 * i + j], self.ema[2 * i + j])
-        self.first = False
         self.plan.run(DAMPING, True)
 
     def precondition(self):
@@ -361,7 +401,7 @@ def run_ours(args):
     if world > 1:
         from chainerkfac_b200.communicators import create_communicator
         wl = DistributedWorkload(device, 1234 + rank,
-                                 create_communicator('pure_nccl'))
+                                 create_communicator(COMMUNICATOR))
     else:
         wl = DeviceWorkload(device, seed=1234 + rank)
     flops = algorithmic_flops(wl.dims)
@@ -405,6 +445,24 @@ def run_ours(args):
 
     info_bad = int((wl.plan.info != 0).sum().item())
 
+    # The step overlaps the factor build with the first inverses, so the
+    # stage events above do not isolate the dominant kernel.  Time the factor
+    # stage alone for the roofline: the same grouped launches, nothing beside
+    # them, inputs larger than L2, CUDA events on the launching stream.
+    factor_alone_ms = None
+    if rank == 0 and world == 1:
+        reps = max(3, min(args.steps, 10))
+        wl.factors_alone()
+        torch.cuda.synchronize()
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            wl.factors_alone()
+        e1.record()
+        torch.cuda.synchronize()
+        factor_alone_ms = e0.elapsed_time(e1) / reps
+
     e2e = None
     if not args.no_e2e:
         try:
@@ -419,7 +477,8 @@ def run_ours(args):
         # the factor stage is the grouped launches of tc_gemm_kernel, the
         # kernel that also carries the inverse and precondition products
         dom = 0
-        achieved = flops[names[dom]] / (phase[dom] * 1e-3) / 1e12
+        dom_ms = factor_alone_ms if factor_alone_ms else phase[dom]
+        achieved = flops[names[dom]] / (dom_ms * 1e-3) / 1e12
         stage = {nm: dict(ms=float(ms), tflops=float(flops[nm] / (ms * 1e-3) / 1e12))
                  for nm, ms in zip(names, phase)}
         cpu = None if args.no_cpu_baseline else cpu_baseline_sample(steps=1, warmup=0)
@@ -437,8 +496,14 @@ def run_ours(args):
                                    'activations and gradients per step)'
                                    % (wl.input_bytes / 1e9),
                        'parallelism': 'dp%d' % world,
-                       'ownership': OWNERSHIP if world > 1 else None},
+                       'ownership': OWNERSHIP if world > 1 else None,
+                       'communicator': COMMUNICATOR if world > 1 else None},
+            # stage boundaries on the main stream; at one GPU the inverses of
+            # the larger size classes run on side streams during 'factor', so
+            # the per-stage rates there are not isolated kernel rates
             'stages': stage,
+            'stages_overlap': bool(OVERLAP and world == 1),
+            'factor_alone_ms': factor_alone_ms,
             'factor_inverse_ms': float(phase[0] + phase[1]),
             'roofline': {
                 'bound': 'tensor',
@@ -479,7 +544,8 @@ def run_e2e(args, device, world, rank):
     from chainerkfac_b200.bench_model import build_training_step
     step, h2d, d2h = build_training_step(device, BATCH, world, rank,
                                          cov_ema_decay=DECAY, damping=DAMPING,
-                                         lr=LR, momentum=MOMENTUM)
+                                         lr=LR, momentum=MOMENTUM,
+                                         communicator=COMMUNICATOR)
     for _ in range(max(args.warmup, 3)):
         step()
     torch.cuda.synchronize()
@@ -677,10 +743,14 @@ def main():
                          'factor build')
     ap.add_argument('--ownership', default=None,
                     choices=['balanced', 'reference'])
+    ap.add_argument('--communicator', default=None,
+                    choices=['peer_memory', 'pure_nccl'])
     ap.add_argument('--micro', choices=sorted(MICRO_CASES), default=None,
                     help='time one single-kernel case instead of the step')
     args = ap.parse_args()
-    global OWNERSHIP, OVERLAP
+    global OWNERSHIP, OVERLAP, COMMUNICATOR
+    if args.communicator:
+        COMMUNICATOR = args.communicator
     if args.ownership:
         OWNERSHIP = args.ownership
     if args.no_overlap:

@@ -69,6 +69,8 @@ SIGNATURES = {
                            VP]),
     'kfac_wire_unpack': (I, [I, c_void_pp, c_i64_p, c_int_p, c_int_p, F, F,
                              VP, VP]),
+    'kfac_wire_unpack_sum': (I, [I, c_void_pp, c_i64_p, c_int_p, c_int_p, F,
+                                 F, c_void_pp, I, VP]),
 }
 
 _lib = None

@@ -56,7 +56,7 @@ class ResNet50(nn.Module):
 
 def build_training_step(device, batch, world, rank, cov_ema_decay, damping,
                         lr, momentum, image=224, classes=1000,
-                        bn_blocks=False):
+                        bn_blocks=False, communicator='peer_memory'):
     """Returns (step, h2d_bytes, d2h_bytes).  ``step()`` copies one pinned
     host batch to the device, runs ``optimizer.update(lossfun, x, t)``
     (forward, backward, K-FAC factors / inverses / preconditioned update) and
@@ -72,7 +72,7 @@ def build_training_step(device, batch, world, rank, cov_ema_decay, damping,
     kwargs = dict(lr=lr, momentum=momentum, cov_ema_decay=cov_ema_decay,
                   damping=damping, constructor=ctor)
     if world > 1:
-        comm = ck.create_communicator('pure_nccl')
+        comm = ck.create_communicator(communicator)
         opt = ck.DistributedKFAC(comm, ownership='balanced', **kwargs)
     else:
         opt = ck.KFAC(**kwargs)

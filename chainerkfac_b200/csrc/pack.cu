@@ -14,6 +14,7 @@ struct WireArray {
   long long nelems;    // elements of the array in memory
   long long wire_off;  // offset of its slot in the wire buffer
   long long wire_n;    // elements of its slot
+  long long item_begin;  // first work item of this array in the launch
   int tri;             // matrix side if packed as a triangle, else 0
   int select;
 };
@@ -47,6 +48,20 @@ int ring_alloc(size_t bytes, void** out) {
   return KFAC_OK;
 }
 
+// Work is cut into items that one 256-thread block handles: a 64x64 tile of a
+// packed triangle (tile column <= tile row), or a run of kChunk elements of a
+// plain array.  item_begin is the running count of items over the arrays of
+// the call, so a block finds its array by bisection and its tile by inverting
+// t = tr(tr+1)/2 + tc.
+static const int kTile = 64;
+static const int kChunk = 8192;
+static const int kMaxWires = 16;
+
+struct WireSources {
+  const float* p[kMaxWires];
+  int n;
+};
+
 __device__ __forceinline__ void tri_index(long long w, int& r, int& c) {
   long long i = (long long)((sqrt(8.0 * (double)w + 1.0) - 1.0) * 0.5);
   while ((i + 1) * (i + 2) / 2 <= w) ++i;
@@ -55,58 +70,133 @@ __device__ __forceinline__ void tri_index(long long w, int& r, int& c) {
   c = (int)(w - i * (i + 1) / 2);
 }
 
-__global__ void wire_pack_kernel(const WireArray* __restrict__ arrs,
-                                 int zero_skipped, float* __restrict__ wire) {
-  const WireArray a = arrs[blockIdx.y];
-  float* dst = wire + a.wire_off;
-  const long long stride = (long long)gridDim.x * blockDim.x;
-  long long w = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (!a.select) {
-    if (zero_skipped)
-      for (; w < a.wire_n; w += stride) dst[w] = 0.f;
-    return;
+__device__ __forceinline__ int find_array(const WireArray* __restrict__ arrs,
+                                          int n_arrays, long long item) {
+  int lo = 0, hi = n_arrays - 1;
+  while (lo < hi) {
+    int mid = (lo + hi + 1) >> 1;
+    if (arrs[mid].item_begin <= item) lo = mid; else hi = mid - 1;
   }
-  if (a.tri > 0) {
-    for (; w < a.wire_n; w += stride) {
-      int r, c;
-      tri_index(w, r, c);
-      dst[w] = a.ptr[(long long)r * a.tri + c];
+  return lo;
+}
+
+__global__ void __launch_bounds__(256)
+wire_pack_kernel(const WireArray* __restrict__ arrs, int n_arrays,
+                 float* __restrict__ wire) {
+  const long long item = blockIdx.x;
+  const WireArray a = arrs[find_array(arrs, n_arrays, item)];
+  const long long t = item - a.item_begin;
+  float* __restrict__ dst = wire + a.wire_off;
+  if (a.tri > 0 && a.select) {
+    int tr, tc;
+    tri_index(t, tr, tc);
+    const int d = a.tri;
+    const int c = tc * kTile + (threadIdx.x & (kTile - 1));
+    const int r0 = tr * kTile + (threadIdx.x >> 6);
+    const float* __restrict__ src = a.ptr;
+#pragma unroll
+    for (int rr = 0; rr < kTile; rr += 4) {
+      const int r = r0 + rr;
+      if (r < d && c <= r)
+        dst[(long long)r * (r + 1) / 2 + c] = src[(long long)r * d + c];
     }
   } else {
-    for (; w < a.wire_n; w += stride) dst[w] = a.ptr[w];
+    // plain array, or the slot of a skipped array that is to be cleared
+    const long long base = t * kChunk;
+    const float* __restrict__ src = a.ptr;
+#pragma unroll 8
+    for (int k = threadIdx.x; k < kChunk; k += 256) {
+      const long long w = base + k;
+      if (w < a.wire_n) dst[w] = a.select ? src[w] : 0.f;
+    }
   }
 }
 
-__global__ void wire_unpack_kernel(const WireArray* __restrict__ arrs,
-                                   float scale, float ema_r,
-                                   const float* __restrict__ wire) {
-  const WireArray a = arrs[blockIdx.y];
-  if (!a.select) return;
-  const float* src = wire + a.wire_off;
-  const long long stride = (long long)gridDim.x * blockDim.x;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-       i < a.nelems; i += stride) {
-    long long w = i;
-    if (a.tri > 0) {
-      int r = (int)(i / a.tri);
-      int c = (int)(i - (long long)r * a.tri);
-      int hi = r > c ? r : c, lo = r > c ? c : r;
-      w = (long long)hi * (hi + 1) / 2 + lo;
+// Unpack sums the same slot of `srcs.n` wire buffers in the order given (this
+// GPU's own buffer and its peers' over NVLink when the pointers are peer
+// mappings), scales, optionally blends into the destination, and writes the
+// tile and its mirror image, both as coalesced rows.
+__global__ void __launch_bounds__(256)
+wire_unpack_kernel(const WireArray* __restrict__ arrs, int n_arrays,
+                   float scale, float ema_r, WireSources srcs) {
+  __shared__ float tile[kTile][kTile + 1];
+  const long long item = blockIdx.x;
+  const WireArray a = arrs[find_array(arrs, n_arrays, item)];
+  const long long t = item - a.item_begin;
+  float* __restrict__ dst = a.ptr;
+  if (a.tri > 0) {
+    int tr, tc;
+    tri_index(t, tr, tc);
+    const int d = a.tri;
+    const int tx = threadIdx.x & (kTile - 1), ty = threadIdx.x >> 6;
+    const int c = tc * kTile + tx;
+    float acc[kTile / 4];
+#pragma unroll
+    for (int i = 0; i < kTile / 4; ++i) acc[i] = 0.f;
+    for (int s = 0; s < srcs.n; ++s) {
+      const float* __restrict__ src = srcs.p[s] + a.wire_off;
+#pragma unroll
+      for (int i = 0; i < kTile / 4; ++i) {
+        const int r = tr * kTile + ty + 4 * i;
+        if (r < d && c <= r) acc[i] += src[(long long)r * (r + 1) / 2 + c];
+      }
     }
-    float v = src[w] * scale;
-    if (ema_r >= 0.f) v = ema_r * v + (1.f - ema_r) * a.ptr[i];
-    a.ptr[i] = v;
+#pragma unroll
+    for (int i = 0; i < kTile / 4; ++i) {
+      const int r = tr * kTile + ty + 4 * i;
+      float v = acc[i] * scale;
+      if (r < d && c <= r) {
+        float* q = dst + (long long)r * d + c;
+        if (ema_r >= 0.f) v = ema_r * v + (1.f - ema_r) * *q;
+        *q = v;
+      }
+      tile[ty + 4 * i][tx] = v;
+    }
+    __syncthreads();
+    // mirror: element (row cc, column rw) takes the value of (rw, cc), cc < rw
+    const int rw = tr * kTile + tx;
+#pragma unroll
+    for (int i = 0; i < kTile / 4; ++i) {
+      const int cc = tc * kTile + ty + 4 * i;
+      if (rw < d && cc < rw) dst[(long long)cc * d + rw] = tile[tx][ty + 4 * i];
+    }
+  } else {
+    const long long base = t * kChunk;
+    for (int k0 = 0; k0 < kChunk; k0 += 256 * 8) {
+      float acc[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+      for (int s = 0; s < srcs.n; ++s) {
+        const float* __restrict__ src = srcs.p[s] + a.wire_off;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const long long w = base + k0 + i * 256 + threadIdx.x;
+          if (w < a.wire_n) acc[i] += src[w];
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const long long w = base + k0 + i * 256 + threadIdx.x;
+        if (w < a.wire_n) {
+          float v = acc[i] * scale;
+          if (ema_r >= 0.f) v = ema_r * v + (1.f - ema_r) * dst[w];
+          dst[w] = v;
+        }
+      }
+    }
   }
 }
 
 static int build_table(int n_arrays, float* const* arrays,
                        const int64_t* nelems, const int* tri_dim,
-                       const int* select, std::vector<WireArray>& tab,
-                       long long& total) {
+                       const int* select, bool skipped_get_items,
+                       std::vector<WireArray>& tab, long long& total,
+                       long long& items) {
   KFAC_REQUIRE(n_arrays > 0 && arrays && nelems && tri_dim,
                "wire: null argument or n_arrays=%d", n_arrays);
   tab.resize(n_arrays);
   total = 0;
+  items = 0;
   for (int i = 0; i < n_arrays; ++i) {
     WireArray& a = tab[i];
     a.ptr = arrays[i];
@@ -126,7 +216,26 @@ static int build_table(int n_arrays, float* const* arrays,
                  "wire: null array pointer at %d", i);
     a.wire_off = total;
     total += a.wire_n;
+    a.item_begin = items;
+    if (a.select && a.tri > 0) {
+      long long t = (a.tri + kTile - 1) / kTile;
+      items += t * (t + 1) / 2;
+    } else if (a.select || skipped_get_items) {
+      items += (a.wire_n + kChunk - 1) / kChunk;
+    }
   }
+  KFAC_REQUIRE(items < (1ll << 31), "wire: too many work items (%lld)", items);
+  return KFAC_OK;
+}
+
+static int upload_table(const std::vector<WireArray>& tab, cudaStream_t st,
+                        const WireArray** out) {
+  void* tab_dev = nullptr;
+  int rc = ring_alloc(tab.size() * sizeof(WireArray), &tab_dev);
+  if (rc != KFAC_OK) return rc;
+  KFAC_CUDA(cudaMemcpyAsync(tab_dev, tab.data(), tab.size() * sizeof(WireArray),
+                            cudaMemcpyHostToDevice, st));
+  *out = static_cast<const WireArray*>(tab_dev);
   return KFAC_OK;
 }
 
@@ -148,21 +257,48 @@ extern "C" int kfac_wire_pack(int n_arrays, const float* const* arrays,
                               const int* select, int zero_skipped, float* wire,
                               void* stream) {
   std::vector<WireArray> tab;
-  long long total = 0;
+  long long total = 0, items = 0;
   int rc = build_table(n_arrays, const_cast<float* const*>(arrays), nelems,
-                       tri_dim, select, tab, total);
+                       tri_dim, select, zero_skipped != 0, tab, total, items);
   if (rc != KFAC_OK) return rc;
   KFAC_REQUIRE(wire != nullptr || total == 0, "wire_pack: null wire buffer");
-  void* tab_dev = nullptr;
-  rc = ring_alloc(tab.size() * sizeof(WireArray), &tab_dev);
-  if (rc != KFAC_OK) return rc;
+  if (items == 0) return KFAC_OK;
   cudaStream_t st = (cudaStream_t)stream;
-  KFAC_CUDA(cudaMemcpyAsync(tab_dev, tab.data(), tab.size() * sizeof(WireArray),
-                            cudaMemcpyHostToDevice, st));
-  dim3 grid(32, n_arrays);
-  wire_pack_kernel<<<grid, 256, 0, st>>>(
-      static_cast<const WireArray*>(tab_dev), zero_skipped, wire);
+  const WireArray* tab_dev = nullptr;
+  rc = upload_table(tab, st, &tab_dev);
+  if (rc != KFAC_OK) return rc;
+  wire_pack_kernel<<<(unsigned)items, 256, 0, st>>>(tab_dev, n_arrays, wire);
   KFAC_LAUNCH_CHECK("wire_pack_kernel");
+  return KFAC_OK;
+}
+
+extern "C" int kfac_wire_unpack_sum(int n_arrays, float* const* arrays,
+                                    const int64_t* nelems, const int* tri_dim,
+                                    const int* select, float scale,
+                                    float ema_r, const float* const* wires,
+                                    int n_wires, void* stream) {
+  KFAC_REQUIRE(wires != nullptr && n_wires >= 1 && n_wires <= kMaxWires,
+               "wire_unpack: %d wire buffers given, 1..%d supported", n_wires,
+               kMaxWires);
+  std::vector<WireArray> tab;
+  long long total = 0, items = 0;
+  int rc = build_table(n_arrays, arrays, nelems, tri_dim, select, false, tab,
+                       total, items);
+  if (rc != KFAC_OK) return rc;
+  WireSources srcs;
+  srcs.n = n_wires;
+  for (int s = 0; s < kMaxWires; ++s) srcs.p[s] = s < n_wires ? wires[s] : nullptr;
+  for (int s = 0; s < n_wires; ++s)
+    KFAC_REQUIRE(wires[s] != nullptr || total == 0,
+                 "wire_unpack: null wire buffer %d", s);
+  if (items == 0) return KFAC_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const WireArray* tab_dev = nullptr;
+  rc = upload_table(tab, st, &tab_dev);
+  if (rc != KFAC_OK) return rc;
+  wire_unpack_kernel<<<(unsigned)items, 256, 0, st>>>(tab_dev, n_arrays, scale,
+                                                      ema_r, srcs);
+  KFAC_LAUNCH_CHECK("wire_unpack_kernel");
   return KFAC_OK;
 }
 
@@ -170,20 +306,6 @@ extern "C" int kfac_wire_unpack(int n_arrays, float* const* arrays,
                                 const int64_t* nelems, const int* tri_dim,
                                 const int* select, float scale, float ema_r,
                                 const float* wire, void* stream) {
-  std::vector<WireArray> tab;
-  long long total = 0;
-  int rc = build_table(n_arrays, arrays, nelems, tri_dim, select, tab, total);
-  if (rc != KFAC_OK) return rc;
-  KFAC_REQUIRE(wire != nullptr || total == 0, "wire_unpack: null wire buffer");
-  void* tab_dev = nullptr;
-  rc = ring_alloc(tab.size() * sizeof(WireArray), &tab_dev);
-  if (rc != KFAC_OK) return rc;
-  cudaStream_t st = (cudaStream_t)stream;
-  KFAC_CUDA(cudaMemcpyAsync(tab_dev, tab.data(), tab.size() * sizeof(WireArray),
-                            cudaMemcpyHostToDevice, st));
-  dim3 grid(32, n_arrays);
-  wire_unpack_kernel<<<grid, 256, 0, st>>>(
-      static_cast<const WireArray*>(tab_dev), scale, ema_r, wire);
-  KFAC_LAUNCH_CHECK("wire_unpack_kernel");
-  return KFAC_OK;
+  return kfac_wire_unpack_sum(n_arrays, arrays, nelems, tri_dim, select, scale,
+                              ema_r, &wire, 1, stream);
 }

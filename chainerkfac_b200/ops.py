@@ -260,8 +260,10 @@ class InversePlanSet(object):
         groups = {}
         for i in range(n):
             groups.setdefault(size_class(i), []).append(i)
-        self.plans, self.index = [], []
-        for _, idx in sorted(groups.items(), reverse=True):
+        self.plans, self.index, self.class_keys = [], [], []
+        self.bounds = tuple(bounds)
+        for key, idx in sorted(groups.items(), reverse=True):
+            self.class_keys.append(key)
             pos = {g: j for j, g in enumerate(idx)}
             self.plans.append(InversePlan(
                 [factors[i] for i in idx], [inverses[i] for i in idx],
@@ -409,6 +411,18 @@ def wire_pack(arrays, tri, wire, select=None, zero_skipped=False):
     _lib.check(lib.kfac_wire_pack(n, ptrs, nelems, tri_dim, sel,
                                   int(bool(zero_skipped)), _p(wire),
                                   _stream()), 'kfac_wire_pack')
+
+
+def wire_unpack_sum(arrays, tri, wire_ptrs, select=None, scale=1.0,
+                    ema_r=-1.0):
+    """Unpack the sum of several wire buffers given as raw device addresses
+    (this GPU's buffer and peer mappings of the other ranks' buffers)."""
+    lib = _lib.load()
+    n, ptrs, nelems, tri_dim, sel = _wire_args(arrays, tri, select)
+    _lib.check(lib.kfac_wire_unpack_sum(
+        n, ptrs, nelems, tri_dim, sel, scale, ema_r,
+        _lib.ptr_array([int(q) for q in wire_ptrs]), len(wire_ptrs),
+        _stream()), 'kfac_wire_unpack_sum')
 
 
 def wire_unpack(arrays, tri, wire, select=None, scale=1.0, ema_r=-1.0):

@@ -267,6 +267,21 @@ int kfac_wire_unpack(int n_arrays, float* const* arrays, const int64_t* nelems,
                      const int* tri_dim, const int* select, float scale,
                      float ema_r, const float* wire, void* stream);
 
+/* kfac_wire_unpack over `n_wires` (1..16) wire buffers of the same layout:
+ * each unpacked element is wires[0][w] + wires[1][w] + ... in that order,
+ * then scaled and blended as above.  The buffers may be peer mappings of other
+ * GPUs' wire buffers (plain loads over NVLink); with every rank's buffer
+ * listed in rank order and scale = 1/size this is the reduction of the
+ * reference's reduce_scatter_v for the selected (owned) arrays, fused with the
+ * unpack (communicators/pure_nccl_communicator.py:47-108 does allreduce, then
+ * unpack).  The caller orders the launch after the peers' packs and keeps the
+ * peers from repacking until it has finished (a barrier on either side).
+ * `wires` is a host array read during the call. */
+int kfac_wire_unpack_sum(int n_arrays, float* const* arrays,
+                         const int64_t* nelems, const int* tri_dim,
+                         const int* select, float scale, float ema_r,
+                         const float* const* wires, int n_wires, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

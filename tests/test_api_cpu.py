@@ -101,6 +101,36 @@ class NumpyWire(object):
             off += n
 
 
+class FakePeerMemory(NumpyWire):
+    """CPU stand-in for the mapped wire buffers of the peer-memory
+    communicator: a 'device address' is a (buffer, rank) token, and the
+    barrier copies every rank's buffers to every rank (what peer loads would
+    see afterwards)."""
+
+    def _map_wire(self, nelems, device):
+        if not hasattr(self, '_bufs'):
+            self._bufs, self._seen = [], []
+        k = len(self._bufs)
+        t = torch.zeros(nelems)
+        self._bufs.append(t)
+        self._seen.append(None)
+        return t, [(k, r) for r in range(self.size)]
+
+    def _barrier(self, device):
+        dist.barrier()
+        for k, t in enumerate(self._bufs):
+            got = [torch.empty_like(t) for _ in range(self.size)]
+            dist.all_gather(got, t)
+            self._seen[k] = got
+
+    def _unpack_sum(self, flat, tri, ptrs, select, scale):
+        total = None
+        for k, r in ptrs:
+            w = self._seen[k][r]
+            total = w.clone() if total is None else total + w
+        self._unpack(flat, tri, total, select, scale)
+
+
 def make_arrays(rng, size):
     shapes = [[((4, 4), True), ((5,), False)], [((3, 3), True), ((2, 6), False)],
               [((6, 6), True)]][:size]
@@ -127,6 +157,33 @@ def _worker(rank, size, port, tmp):
 
     class TestComm(NumpyWire, PureNcclCommunicator):
         pass
+    from chainerkfac_b200.communicators.peer_memory_communicator import \
+        PeerMemoryCommunicator
+
+    class TestPeerComm(FakePeerMemory, PeerMemoryCommunicator):
+        pass
+    # same collectives through the peer-memory sequencing, twice, so that
+    # both alternating wire buffers are reused
+    peer = TestPeerComm()
+    for rep in range(2):
+        per_rank = [make_arrays(np.random.default_rng(70 + rep * 10 + q), size)
+                    for q in range(size)]
+        mine = [[(torch.from_numpy(a.copy()), t) for a, t in loc]
+                for loc in per_rank[rank]]
+        peer.reduce_scatter_v_arrays(mine)
+        want = [[[(a.copy(), t) for a, t in loc] for loc in r]
+                for r in per_rank]
+        orc.reduce_scatter_v_sim(want)
+        for o in range(size):
+            for (a, _), (w, _) in zip(mine[o], want[rank][o]):
+                assert np.allclose(a.numpy(), w, rtol=1e-6, atol=1e-7)
+        peer.all_gather_v_arrays(mine)
+        orc.all_gather_v_sim(want)
+        for o in range(size):
+            for (a, _), (w, _) in zip(mine[o], want[rank][o]):
+                assert np.allclose(a.numpy(), w, rtol=1e-6, atol=1e-7)
+    assert len(peer._bufs) == 2
+
     comm = TestComm()
     assert comm.rank == rank and comm.size == size
     # every rank's local values (seeded per rank), same nested structure

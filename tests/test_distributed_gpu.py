@@ -36,10 +36,42 @@ T = torch.randint(0, 5, (8,), generator=g).cuda()
 half = 8 // world
 xs, ts = X[rank * half:(rank + 1) * half], T[rank * half:(rank + 1) * half]
 
-for pic, early, own in ((True, False, 'reference'), (False, False, 'reference'),
-                        (True, True, 'balanced')):
+# one communicator of each kind for the whole run: the peer-memory one maps
+# its wire buffers once and reuses them across optimizers
+comms = {name: ck.create_communicator(name)
+         for name in ('pure_nccl', 'peer_memory')}
+
+# the two communicators must deliver identical arrays for identical input
+gen = torch.Generator().manual_seed(100 + rank)
+def arrays():
+    out = []
+    for o in range(world):
+        f = torch.randn(70 + o, 70 + o, generator=gen)
+        out.append([((f + f.T).cuda(), True),
+                    (torch.randn(9000 + o, generator=gen).cuda(), False)])
+    return out
+a_nccl = arrays()
+a_peer = [[(t.clone(), tri) for t, tri in loc] for loc in a_nccl]
+for rep in range(3):
+    comms['pure_nccl'].reduce_scatter_v_arrays(a_nccl)
+    comms['peer_memory'].reduce_scatter_v_arrays(a_peer)
+    for (x, _), (y, _) in zip(a_nccl[rank], a_peer[rank]):
+        assert float((x - y).abs().max()) <= 1e-6 * float(x.abs().max()), rep
+        y.copy_(x)
+    comms['pure_nccl'].all_gather_v_arrays(a_nccl)
+    comms['peer_memory'].all_gather_v_arrays(a_peer)
+    for o in range(world):
+        for (x, _), (y, _) in zip(a_nccl[o], a_peer[o]):
+            assert torch.equal(x, y), (rep, o)
+
+for pic, early, own, cname in (
+        (True, False, 'reference', 'pure_nccl'),
+        (False, False, 'reference', 'pure_nccl'),
+        (True, True, 'balanced', 'pure_nccl'),
+        (True, False, 'balanced', 'peer_memory'),
+        (False, True, 'reference', 'peer_memory')):
     model = make()
-    comm = ck.create_communicator('pure_nccl')
+    comm = comms[cname]
     opt = ck.DistributedKFAC(comm, lr=0.05, momentum=0.9, cov_ema_decay=1.0,
                              damping=1e-2, only_pic_update_weight=pic,
                              communicate_after_forward=early, ownership=own)
@@ -65,7 +97,7 @@ for pic, early, own in ((True, False, 'reference'), (False, False, 'reference'),
         for (n1, p1), (n2, p2) in zip(ref.named_parameters(),
                                       model.named_parameters()):
             err = float((p1 - p2).norm() / p1.norm())
-            assert err < 2e-3, (pic, early, own, n1, err)
+            assert err < 2e-3, (pic, early, own, cname, n1, err)
 dist.barrier()
 if rank == 0:
     print('DISTRIBUTED_OK')

@@ -427,6 +427,52 @@ def test_wire_pack_unpack_bit_exact(ops):
         assert rel(host(o), 0.5 * a + 0.5) < 1e-6
 
 
+def test_wire_unpack_sum_of_rank_buffers(ops):
+    """The owner's side of the peer-memory reduce-scatter: the same slot of
+    several wire buffers (one per rank; here all on this GPU) summed in rank
+    order, scaled to the mean and mirrored.  Sizes straddle the 64-wide tiles
+    and the 8192-element runs; unselected arrays must stay untouched and must
+    not shift the offsets of the others."""
+    rng = np.random.default_rng(41)
+    shapes = [((130, 130), True), ((8192 + 77,), False), ((64, 64), True),
+              ((5, 7), False), ((513, 513), True), ((0,), False),
+              ((65, 65), True)]
+    tri = [t for _, t in shapes]
+    ranks = 5
+    per_rank, wires = [], []
+    for q in range(ranks):
+        arrs = []
+        for shp, t in shapes:
+            a = rng.standard_normal(shp).astype(np.float32)
+            if t:
+                a = (a + a.T).astype(np.float32)
+            arrs.append(a)
+        per_rank.append(arrs)
+        d = [dev(a) for a in arrs]
+        w = torch.empty(ops.wire_nelems(d, tri), device='cuda')
+        ops.wire_pack(d, tri, w)
+        assert np.array_equal(
+            host(w), orc.pack_arrays([[(a, t) for a, t in zip(arrs, tri)]]))
+        wires.append(w)
+    sel = [1, 1, 0, 1, 1, 1, 1]
+    outs = [torch.full(shp, 3.0, device='cuda') for shp, _ in shapes]
+    ops.wire_unpack_sum(outs, tri, [w.data_ptr() for w in wires], select=sel,
+                        scale=1.0 / ranks)
+    for i, (o, s) in enumerate(zip(outs, sel)):
+        if not s:
+            assert np.array_equal(host(o), np.full(shapes[i][0], 3.0, np.float32))
+            continue
+        acc = np.zeros(shapes[i][0], np.float32)
+        for q in range(ranks):         # rank order, fp32, as the kernel sums
+            acc = acc + per_rank[q][i]
+        want = acc * np.float32(1.0 / ranks)
+        assert np.array_equal(host(o), want), i
+        if tri[i]:
+            assert np.array_equal(host(o), host(o).T)
+    with pytest.raises(Exception):
+        ops.wire_unpack_sum(outs, tri, [wires[0].data_ptr()] * 17)
+
+
 # ------------------------------------------- full-size, size-independent checks
 def test_config4_full_size_inverse_property(ops, engine):
     """The isolated curvature microbench at its full sizes: factors with the
