@@ -24,12 +24,31 @@ namespace kfac {
 constexpr int TC_BM = 128;
 constexpr int TC_BN = 256;
 constexpr int TC_BK = 32;
-constexpr int TC_PRODUCERS = 512;
-constexpr int TC_PWARPS = TC_PRODUCERS / 32;
-constexpr int TC_THREADS = TC_PRODUCERS + 32;
+// Producer warps per CTA (template parameter PW of the kernel, a multiple of
+// 8 that divides 96).  24 warps (72 registers per thread) gain 20 % on an
+// im2col gather with long image rows (128 pixels) but nothing at the 7..56
+// pixel rows of ResNet-50, where the per-thread offset bookkeeping that more
+// threads replicate costs as much as the extra warps hide; strided operands
+// need the 96 registers that only the 16-warp CTA leaves per thread.
+constexpr int TC_PW_IM2COL = 16;
+constexpr int TC_PW_STRIDED = 16;
 constexpr int TC_A_BYTES = TC_BM * TC_BK * 4;   // 16 KB
 constexpr int TC_B_BYTES = TC_BN * TC_BK * 4;   // 32 KB
-constexpr int TC_STAGE_BYTES = 2 * TC_A_BYTES + 2 * TC_B_BYTES;  // 96 KB
+// one stage: [A hi][B hi][A lo][B lo]; a lo tile lies TC_LO_OFF after its hi
+constexpr int TC_LO_OFF = TC_A_BYTES + TC_B_BYTES;
+constexpr int TC_STAGE_BYTES = 2 * TC_LO_OFF;   // 96 KB
+// The A rows and then the B rows of a tile form one space of 384 rows; a
+// task index covers a band of 4 * PW of them (each warp 4 rows, or one
+// 16-byte column of 32 rows) and a thread has one task per band.
+template <int PW>
+struct TcMap {
+  static constexpr int kProducers = PW * 32;
+  static constexpr int kThreads = PW * 32 + 32;
+  static constexpr int kBand = PW * 4;
+  static constexpr int kTasks = (TC_BM + TC_BN) / kBand;
+  static_assert((TC_BM + TC_BN) % kBand == 0 && PW % 8 == 0 && TC_BM % 32 == 0,
+                "producer mapping");
+};
 constexpr int TC_STAGES = 2;
 constexpr int TC_EPI_PITCH = TC_BN + 1;         // floats
 constexpr int TC_SMEM_BYTES = TC_STAGES * TC_STAGE_BYTES + 8192 + 1024;
@@ -200,8 +219,8 @@ __device__ __forceinline__ void store_split(unsigned hi_addr, unsigned lo_addr,
 // im2col column tables for `rows` columns of a tile starting at column c0.
 __device__ __forceinline__ void tc_im2col_tables(const Operand& op, int c0,
                                                  int rows, int* coff, int* kykx,
-                                                 int tid) {
-  for (int i = tid; i < rows; i += TC_PRODUCERS) {
+                                                 int tid, int nthreads) {
+  for (int i = tid; i < rows; i += nthreads) {
     int c = c0 + i;
     int off = 0, info = -1;
     if (c < op.ncols) {
@@ -229,43 +248,64 @@ static __device__ __align__(256) float g_ones_page[64] = {
     1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1,
     1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1};
 
-// A producer thread moves NTASK 16-byte chunks (4 consecutive k of one tile
-// row) of an operand tile per k-block.  Operands contiguous along k (and
-// im2col operands) map task t to row = 4*warp + 4*PWARPS*t + lane/8, chunk =
-// lane%8; operands contiguous along the column index map it to row =
-// 32*((PWARPS/8)*t + warp/8) + lane, chunk = warp%8, so that a warp's loads of
-// one k are 32 consecutive addresses.  Per task everything that does not
-// change with k is computed once: the element address is
-//     p + (long long)o_j * mul        (one multiply-add per element)
-// where o_j is the k-dependent offset shared by all tasks of the thread.
+// A producer thread moves TcMap<PW>::kTasks 16-byte chunks (4 consecutive k of one
+// tile row) per k-block, task t in band t of the 384 tile rows.  Within a
+// band the 8-warp group g = warp / 8 owns rows [32g, 32g + 32): operands
+// contiguous along k (and im2col operands) give a warp 4 rows x 8 chunks
+// (row = 4 * warp + lane / 8, chunk = lane % 8); operands contiguous along the
+// column index give it one chunk of 32 rows (row = 32g + lane, chunk =
+// warp % 8), so that a warp's loads of one k are 32 consecutive addresses.
+// Whether a task is an A row or a B row depends only on (t, g): uniform per
+// warp.  Per task everything that does not change with k is computed once:
+// the element address is
+//     p + (long long)o_j * m        (one multiply-add per element)
+// where o_j is the k-dependent offset shared by all tasks of the thread that
+// belong to the same operand.
 struct PTask {
   const char* p;    // column base (or the zero / ones page), as bytes
   int m;            // byte multiplier of the k-dependent offset (0 for pages)
-  unsigned soff;    // swizzled byte offset inside the tile, ~0u: idle task
+  unsigned soff;    // swizzled byte offset inside the stage, ~0u: idle task
 };
 
-template <int NTASK, bool IM2COL>
-__device__ __forceinline__ void tc_task_setup(const Operand& op, int c0,
-                                              int rows, const int* coff,
-                                              const int* kykx, int warp,
-                                              int lane, PTask task[NTASK]) {
-  const bool kf = IM2COL || op.kfast;
+// 1: band t holds only A rows, 0: only B rows, -1: depends on the warp group
+template <int PW>
+__host__ __device__ constexpr int tc_band_side(int t) {
+  return 4 * PW * (t + 1) <= TC_BM ? 1 : (4 * PW * t >= TC_BM ? 0 : -1);
+}
+
+template <int PW>
+__device__ __forceinline__ bool tc_task_is_a(int t, int warp) {
+  return tc_band_side<PW>(t) >= 0 ? tc_band_side<PW>(t) == 1
+                                  : 4 * PW * t + 32 * (warp >> 3) < TC_BM;
+}
+
+template <bool IM2COL, int PW>
+__device__ __forceinline__ void tc_task_setup(const Operand& A,
+                                              const Operand& B, int m0, int n0,
+                                              int rows_b, const TcControl* ctl,
+                                              int warp, int lane,
+                                              PTask task[TcMap<PW>::kTasks]) {
 #pragma unroll
-  for (int t = 0; t < NTASK; ++t) {
-    const int row = kf ? warp * 4 + (TC_PWARPS * 4) * t + (lane >> 3)
-                       : 32 * ((TC_PWARPS / 8) * t + (warp >> 3)) + lane;
+  for (int t = 0; t < TcMap<PW>::kTasks; ++t) {
+    const bool is_a = tc_task_is_a<PW>(t, warp);
+    const Operand& op = is_a ? A : B;
+    const bool kf = IM2COL || op.kfast;
+    const int band_row = kf ? warp * 4 + (lane >> 3) : 32 * (warp >> 3) + lane;
+    const int row = TcMap<PW>::kBand * t + band_row - (is_a ? 0 : TC_BM);
+    const int rows = is_a ? TC_BM : rows_b;
     const int chunk = kf ? (lane & 7) : (warp & 7);
     PTask v;
-    v.soff = row < rows
-                 ? (unsigned)(row * 128 + ((chunk ^ (row & 7)) << 4)) : ~0u;
+    v.soff = row < rows ? (unsigned)((is_a ? 0 : TC_A_BYTES) + row * 128 +
+                                     ((chunk ^ (row & 7)) << 4))
+                        : ~0u;
     const float* p = g_zero_page;
     int m = 0;
     if (row < rows) {
-      const int c = c0 + row;
+      const int c = (is_a ? m0 : n0) + row;
       if (IM2COL) {
-        const int info = kykx[row];
+        const int info = (is_a ? ctl->kykx_a : ctl->kykx_b)[row];
         if (info >= 0) {
-          p = op.base + coff[row];
+          p = op.base + (is_a ? ctl->coff_a : ctl->coff_b)[row];
           m = 1;
         } else if (info == -2) {
           p = g_ones_page;
@@ -366,25 +406,27 @@ __device__ __forceinline__ void tc_koffsets(const Operand& op,
   }
 }
 
-// Gather the NTASK chunks of one k-block into registers.  The loads are
-// issued back to back, each from an address that is always legal; nothing
-// between two loads depends on a loaded value.  `vec` (uniform per tile):
-// every chunk of this operand is 16-byte aligned and contiguous.
-template <int NTASK, bool TAILS>
-__device__ __forceinline__ void tc_load_tile(const PTask task[NTASK],
-                                             const int o[4], int k, int kend,
-                                             bool vec, float4 v[NTASK]) {
+// Gather the chunks of one operand (SIDE_A: the A rows, else the B rows) for
+// one k-block into registers.  The loads are issued back to back, each from
+// an address that is always legal; nothing between two loads depends on a
+// loaded value.  `vec` (uniform per tile): every chunk of this operand is
+// 16-byte aligned and contiguous.
+template <bool TAILS, int PW, bool SIDE_A>
+__device__ __forceinline__ void tc_load_side(
+    const PTask task[TcMap<PW>::kTasks], const int o[4], int k, int kend,
+    bool vec, int warp, float4 v[TcMap<PW>::kTasks]) {
+  constexpr int NT = TcMap<PW>::kTasks;
   const bool tail = TAILS && (k + 3 >= kend);
   if (vec && !tail) {
 #pragma unroll
-    for (int t = 0; t < NTASK; ++t)
-      if (task[t].soff != ~0u)
+    for (int t = 0; t < NT; ++t)
+      if (tc_task_is_a<PW>(t, warp) == SIDE_A && task[t].soff != ~0u)
         v[t] = *reinterpret_cast<const float4*>(
             task[t].p + (long long)o[0] * task[t].m);
   } else {
 #pragma unroll
-    for (int t = 0; t < NTASK; ++t) {
-      if (task[t].soff == ~0u) continue;
+    for (int t = 0; t < NT; ++t) {
+      if (tc_task_is_a<PW>(t, warp) != SIDE_A || task[t].soff == ~0u) continue;
       v[t].x = *reinterpret_cast<const float*>(task[t].p + (long long)o[0] * task[t].m);
       v[t].y = *reinterpret_cast<const float*>(task[t].p + (long long)o[1] * task[t].m);
       v[t].z = *reinterpret_cast<const float*>(task[t].p + (long long)o[2] * task[t].m);
@@ -393,7 +435,8 @@ __device__ __forceinline__ void tc_load_tile(const PTask task[NTASK],
   }
   if (tail) {
 #pragma unroll
-    for (int t = 0; t < NTASK; ++t) {
+    for (int t = 0; t < NT; ++t) {
+      if (tc_task_is_a<PW>(t, warp) != SIDE_A) continue;
       if (k + 0 >= kend) v[t].x = 0.f;
       if (k + 1 >= kend) v[t].y = 0.f;
       if (k + 2 >= kend) v[t].z = 0.f;
@@ -414,15 +457,14 @@ __device__ __forceinline__ bool tc_operand_vec(const Operand& op,
   return (op.period & 3) == 0 && (op.s_outer & 3) == 0 && op.s_inner == 1;
 }
 
-template <int NTASK>
-__device__ __forceinline__ void tc_store_tile(const PTask task[NTASK],
-                                              unsigned hi_tile,
-                                              unsigned lo_tile,
-                                              const float4 v[NTASK]) {
+template <int NT>
+__device__ __forceinline__ void tc_store_tile(const PTask task[NT],
+                                              unsigned stage,
+                                              const float4 v[NT]) {
 #pragma unroll
-  for (int t = 0; t < NTASK; ++t)
+  for (int t = 0; t < NT; ++t)
     if (task[t].soff != ~0u)
-      store_split(hi_tile + task[t].soff, lo_tile + task[t].soff, v[t]);
+      store_split(stage + task[t].soff, stage + TC_LO_OFF + task[t].soff, v[t]);
 }
 
 // Lower-triangular enumeration with 128-row x 256-column tiles: tile (bi, bj)
@@ -441,8 +483,8 @@ __device__ __forceinline__ void tc_tri_tile(int t, int& bi, int& bj) {
   }
 }
 
-template <bool IM2COL, bool TAILS>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+template <bool IM2COL, bool TAILS, int PW>
+__global__ void __launch_bounds__(TcMap<PW>::kThreads, 1)
 tc_gemm_kernel(const GemmDesc* __restrict__ descs, int ndesc,
                const __grid_constant__ GemmDesc inline_desc, float lr,
                float momentum) {
@@ -451,6 +493,10 @@ tc_gemm_kernel(const GemmDesc* __restrict__ descs, int ndesc,
       (reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
   TcControl* ctl =
       reinterpret_cast<TcControl*>(smem + TC_STAGES * TC_STAGE_BYTES);
+  constexpr int TC_PRODUCERS = TcMap<PW>::kProducers;
+  constexpr int TC_PWARPS = PW;
+  constexpr int TC_THREADS = TcMap<PW>::kThreads;
+  constexpr int TC_NTASK = TcMap<PW>::kTasks;
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
   const int tile = blockIdx.x;
@@ -528,19 +574,16 @@ tc_gemm_kernel(const GemmDesc* __restrict__ descs, int ndesc,
   if (warp < TC_PRODUCERS / 32) {
     // ===================== producers =====================
     if (IM2COL) {
-      tc_im2col_tables(g.A, m0, TC_BM, ctl->coff_a, ctl->kykx_a, tid);
-      tc_im2col_tables(g.B, n0, n_inst, ctl->coff_b, ctl->kykx_b, tid);
+      tc_im2col_tables(g.A, m0, TC_BM, ctl->coff_a, ctl->kykx_a, tid,
+                       TC_PRODUCERS);
+      tc_im2col_tables(g.B, n0, n_inst, ctl->coff_b, ctl->kykx_b, tid,
+                       TC_PRODUCERS);
       asm volatile("bar.sync 1, %0;" ::"r"(TC_PRODUCERS) : "memory");
     }
-    constexpr int NTA = TC_BM * 8 / TC_PRODUCERS;   // chunks per thread
-    constexpr int NTB = TC_BN * 8 / TC_PRODUCERS;
     const Operand A = g.A, B = g.B;   // register copies: loop invariant
-    float4 va[NTA], vb[NTB];
-    PTask ia[NTA], ib[NTB];
-    tc_task_setup<NTA, IM2COL>(A, m0, TC_BM, ctl->coff_a, ctl->kykx_a, warp,
-                               lane, ia);
-    tc_task_setup<NTB, IM2COL>(B, n0, n_inst, ctl->coff_b, ctl->kykx_b, warp,
-                               lane, ib);
+    float4 v[TC_NTASK];
+    PTask task[TC_NTASK];
+    tc_task_setup<IM2COL, PW>(A, B, m0, n0, n_inst, ctl, warp, lane, task);
     const int kend_i = (int)kend;
     KState ka, kb_state;
     {
@@ -567,10 +610,7 @@ tc_gemm_kernel(const GemmDesc* __restrict__ descs, int ndesc,
             break;
         }
         if (tid == 0) TC_TRACE(pb, 1);
-        const unsigned st = smem_base + s * TC_STAGE_BYTES;
-        tc_store_tile<NTA>(ia, st, st + TC_A_BYTES, va);
-        tc_store_tile<NTB>(ib, st + 2 * TC_A_BYTES,
-                           st + 2 * TC_A_BYTES + TC_B_BYTES, vb);
+        tc_store_tile<TC_NTASK>(task, smem_base + s * TC_STAGE_BYTES, v);
         if (tid == 0) TC_TRACE(pb, 2);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
@@ -588,9 +628,9 @@ tc_gemm_kernel(const GemmDesc* __restrict__ descs, int ndesc,
         } else {
           tc_koffsets<IM2COL, TAILS>(B, kb_state, kend_i, ob);
         }
-        tc_load_tile<NTA, TAILS>(ia, oa, ka.k, kend_i, vec_a, va);
-        tc_load_tile<NTB, TAILS>(ib, ob, IM2COL ? ka.k : kb_state.k, kend_i,
-                                 vec_b, vb);
+        tc_load_side<TAILS, PW, true>(task, oa, ka.k, kend_i, vec_a, warp, v);
+        tc_load_side<TAILS, PW, false>(task, ob, IM2COL ? ka.k : kb_state.k,
+                                       kend_i, vec_b, warp, v);
         kstate_advance<IM2COL>(A, ka);
         if (!IM2COL) kstate_advance<IM2COL>(B, kb_state);
         if (tid == 0) TC_TRACE(kb, 4);
@@ -609,10 +649,10 @@ tc_gemm_kernel(const GemmDesc* __restrict__ descs, int ndesc,
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const unsigned sa = smem_u32(smem + s * TC_STAGE_BYTES);
         const unsigned long long a_hi = tc_smem_desc(sa);
-        const unsigned long long a_lo = tc_smem_desc(sa + TC_A_BYTES);
-        const unsigned long long b_hi = tc_smem_desc(sa + 2 * TC_A_BYTES);
+        const unsigned long long b_hi = tc_smem_desc(sa + TC_A_BYTES);
+        const unsigned long long a_lo = tc_smem_desc(sa + TC_LO_OFF);
         const unsigned long long b_lo =
-            tc_smem_desc(sa + 2 * TC_A_BYTES + TC_B_BYTES);
+            tc_smem_desc(sa + TC_LO_OFF + TC_A_BYTES);
 #pragma unroll
         for (int kk = 0; kk < TC_BK / 8; ++kk) {
           const unsigned long long adv = (unsigned long long)(kk * 32 >> 4);
@@ -637,10 +677,11 @@ tc_gemm_kernel(const GemmDesc* __restrict__ descs, int ndesc,
       ok = __all_sync(0xffffffffu, ok);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     }
-    constexpr int CW = TC_BN / (TC_PWARPS / 4);   // columns per warp
+    // warp w reads the 32 accumulator rows of its TMEM quarter q = w % 4;
+    // the TC_PWARPS / 4 warps of a quarter take 16-column slices in turn
     const int q = warp & 3, h = warp >> 2;
     const int row = q * 32 + lane;
-    for (int c0 = h * CW; c0 < min(n_inst, h * CW + CW); c0 += 16) {
+    for (int c0 = h * 16; c0 < n_inst; c0 += 16 * (TC_PWARPS / 4)) {
       float v[16];
       if (nkb > 0 && ok) {
         float w[16];
@@ -849,16 +890,16 @@ static int tc_prepare() {
   KFAC_REQUIRE(dev >= 0 && dev < 64, "device index %d unsupported", dev);
   std::lock_guard<std::mutex> lock(mu);
   if (!done[dev]) {
-    KFAC_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<false, false>,
+    KFAC_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<false, false, TC_PW_STRIDED>,
                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    TC_SMEM_BYTES));
-    KFAC_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<false, true>,
+    KFAC_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<false, true, TC_PW_STRIDED>,
                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    TC_SMEM_BYTES));
-    KFAC_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<true, false>,
+    KFAC_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<true, false, TC_PW_IM2COL>,
                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    TC_SMEM_BYTES));
-    KFAC_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<true, true>,
+    KFAC_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<true, true, TC_PW_IM2COL>,
                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    TC_SMEM_BYTES));
     done[dev] = true;
@@ -874,11 +915,11 @@ int launch_tc_grouped(const GemmDesc* descs_dev, int ndesc, int total_tiles,
   if (rc != KFAC_OK) return rc;
   GemmDesc dummy = {};
   if (tails)
-    tc_gemm_kernel<false, true><<<total_tiles, TC_THREADS, TC_SMEM_BYTES,
+    tc_gemm_kernel<false, true, TC_PW_STRIDED><<<total_tiles, TcMap<TC_PW_STRIDED>::kThreads, TC_SMEM_BYTES,
                                   stream>>>(descs_dev, ndesc, dummy, lr,
                                             momentum);
   else
-    tc_gemm_kernel<false, false><<<total_tiles, TC_THREADS, TC_SMEM_BYTES,
+    tc_gemm_kernel<false, false, TC_PW_STRIDED><<<total_tiles, TcMap<TC_PW_STRIDED>::kThreads, TC_SMEM_BYTES,
                                    stream>>>(descs_dev, ndesc, dummy, lr,
                                              momentum);
   KFAC_LAUNCH_CHECK("tc_gemm_kernel");
@@ -1072,16 +1113,16 @@ int run_factor_group_tc(int count, const FactorJob* jobs, void* workspace,
     }
     const int nd = (int)v.size();
     if (m == 1 && tails)
-      tc_gemm_kernel<true, true><<<total, TC_THREADS, TC_SMEM_BYTES, stream>>>(
+      tc_gemm_kernel<true, true, TC_PW_IM2COL><<<total, TcMap<TC_PW_IM2COL>::kThreads, TC_SMEM_BYTES, stream>>>(
           dev_descs, nd, inl, 0.f, 0.f);
     else if (m == 1)
-      tc_gemm_kernel<true, false><<<total, TC_THREADS, TC_SMEM_BYTES, stream>>>(
+      tc_gemm_kernel<true, false, TC_PW_IM2COL><<<total, TcMap<TC_PW_IM2COL>::kThreads, TC_SMEM_BYTES, stream>>>(
           dev_descs, nd, inl, 0.f, 0.f);
     else if (tails)
-      tc_gemm_kernel<false, true><<<total, TC_THREADS, TC_SMEM_BYTES, stream>>>(
+      tc_gemm_kernel<false, true, TC_PW_STRIDED><<<total, TcMap<TC_PW_STRIDED>::kThreads, TC_SMEM_BYTES, stream>>>(
           dev_descs, nd, inl, 0.f, 0.f);
     else
-      tc_gemm_kernel<false, false><<<total, TC_THREADS, TC_SMEM_BYTES,
+      tc_gemm_kernel<false, false, TC_PW_STRIDED><<<total, TcMap<TC_PW_STRIDED>::kThreads, TC_SMEM_BYTES,
                                      stream>>>(dev_descs, nd, inl, 0.f, 0.f);
     KFAC_LAUNCH_CHECK("tc_gemm_kernel");
   }
