@@ -342,29 +342,51 @@ class DistributedWorkload(DeviceWorkload):
                 if self.b[i] is not None:
                     ag.append((self.b[i], False))
             self.ag_arrays.append(ag)
+        self.comm_stream = torch.cuda.Stream(priority=-1)
         if hasattr(comm, 'reserve'):
             from chainerkfac_b200.communicators import _utility
             comm.reserve(max([_utility.get_nelems(rs) for rs in self.class_rs]
                              + [_utility.get_nelems(self.ag_arrays)]), device)
 
     def factors(self):
+        torch = self.torch
         r, rest = (1.0, 0.0) if self.first else (DECAY, 1.0 - DECAY)
         items = self.factor_items(self.cov, 1.0, 0.0)
         dev = self.cov[0].device
         mine = set(self.mine)
         last = len(self.class_layers) - 1
+        main = torch.cuda.current_stream()
         for c, layers in enumerate(self.class_layers):
             self.ops.factor_group(
                 [items[2 * i + j] for i in layers for j in (0, 1)], dev)
-            # exchange 1 for this class, then the owner's running average
-            self.comm.reduce_scatter_v_arrays(self.class_rs[c])
-            for i in layers:
-                if i in mine:
-                    for j in (0, 1):
-                        self.ops.axpby(r, self.cov[2 * i + j], rest,
-                                       self.ema[2 * i + j], self.ema[2 * i + j])
-            if c < last and self.class_plan[c] is not None:
-                self.plan.start_class(self.class_plan[c], DAMPING, True)
+            # exchange 1 for this class and the owner's running average run
+            # on the exchange stream: the factor build of the next class does
+            # not wait for the other ranks
+            # (every exchange on the same stream: the communicator's buffer
+            # reuse relies on its calls being ordered with one another)
+            side = self.comm_stream if (OVERLAP and last > 0) else main
+            if side is not main:
+                built = torch.cuda.Event()
+                built.record(main)
+                side.wait_event(built)
+            with torch.cuda.stream(side):
+                self.comm.reduce_scatter_v_arrays(self.class_rs[c])
+                for i in layers:
+                    if i in mine:
+                        for j in (0, 1):
+                            self.ops.axpby(r, self.cov[2 * i + j], rest,
+                                           self.ema[2 * i + j],
+                                           self.ema[2 * i + j])
+                if c < last and self.class_plan[c] is not None:
+                    self.plan.start_class(self.class_plan[c], DAMPING, True)
+            if side is not main:
+                done = torch.cuda.Event()
+                done.record(side)
+                self._exchanged = done
+        if OVERLAP and last > 0:
+            # later work on the main stream (and the next step's factor build,
+            # which overwrites cov) comes after the exchanges
+            main.wait_event(self._exchanged)
         self.first = False
 
     def inverses(self):
