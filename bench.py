@@ -699,6 +699,10 @@ MICRO_CASES = {
     'dense_rows8192_d4608': ('dense', dict(rows=8192, d=4608)),
     'inverse_d2304': ('inverse', dict(dims=[2304])),
     'inverse_d4608': ('inverse', dict(dims=[4608])),
+    # wire format of the exchange: every factor of ResNet-50 (308 MB packed,
+    # 615 MB dense); the sum reads 4 rank buffers, all on this GPU here
+    'wire_pack_resnet50': ('wire_pack', dict()),
+    'wire_unpack_sum4_resnet50': ('wire_unpack', dict(ranks=4)),
 }
 
 
@@ -727,6 +731,24 @@ def run_micro(args):
         out = torch.empty(p['d'], p['d'], device='cuda')
         fn = lambda: ops.factor_dense(x, False, alpha=1.0, out=out)
         flops = p['rows'] * p['d'] * (p['d'] + 1)
+    elif kind in ('wire_pack', 'wire_unpack'):
+        _, dims = layer_table()
+        sides = [d for dA, dG, _, _ in dims for d in (dA, dG)]
+        arrs = [torch.randn(d, d, device='cuda') for d in sides]
+        tri = [True] * len(arrs)
+        n = ops.wire_nelems(arrs, tri)
+        dense = sum(d * d for d in sides)
+        if kind == 'wire_pack':
+            wire = torch.empty(n, device='cuda')
+            fn = lambda: ops.wire_pack(arrs, tri, wire)
+            nbytes = 4 * 2 * n                 # triangle read + packed write
+        else:
+            wires = [torch.randn(n, device='cuda') for _ in range(p['ranks'])]
+            ptrs = [w.data_ptr() for w in wires]
+            fn = lambda: ops.wire_unpack_sum(arrs, tri, ptrs,
+                                             scale=1.0 / p['ranks'])
+            nbytes = 4 * (p['ranks'] * n + dense)
+        flops = None
     else:
         F = []
         for d in p['dims']:
@@ -748,8 +770,12 @@ def run_micro(args):
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / args.steps
-    print(json.dumps({'micro': args.micro, 'ms': ms,
-                      'tflops': flops / (ms * 1e-3) / 1e12}))
+    if flops is None:
+        print(json.dumps({'micro': args.micro, 'ms': ms, 'bytes': nbytes,
+                          'gbs': nbytes / (ms * 1e-3) / 1e9}))
+    else:
+        print(json.dumps({'micro': args.micro, 'ms': ms,
+                          'tflops': flops / (ms * 1e-3) / 1e12}))
 
 
 def main():

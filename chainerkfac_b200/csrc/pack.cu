@@ -2,6 +2,7 @@
 // into one flat fp32 buffer, symmetric factors as packed row-major lower
 // triangles.  Pack visits only the d(d+1)/2 stored elements; unpack mirrors
 // the triangle, scales (mean over ranks) and can blend into a running average.
+#include <algorithm>
 #include <mutex>
 #include <vector>
 
@@ -70,44 +71,72 @@ __device__ __forceinline__ void tri_index(long long w, int& r, int& c) {
   c = (int)(w - i * (i + 1) / 2);
 }
 
-__device__ __forceinline__ int find_array(const WireArray* __restrict__ arrs,
-                                          int n_arrays, long long item) {
+// Both kernels are persistent: a block walks work items blockIdx.x,
+// blockIdx.x + gridDim.x, ... so that the start-up of a block (table load) is
+// paid once and the memory pipeline stays full across items.  The first work
+// item of every array is cached in shared memory; an item's array is found by
+// bisection there (arrays without items share their successor's first item
+// and are skipped by taking the last array whose first item is <= item).
+static const int kTabCap = 1024;
+static const int kBlocksPerSm = 8;
+
+__device__ __forceinline__ void load_item_table(
+    const WireArray* __restrict__ arrs, int n_arrays, int* s_begin) {
+  for (int i = threadIdx.x; i < n_arrays; i += blockDim.x)
+    s_begin[i] = (int)arrs[i].item_begin;
+  __syncthreads();
+}
+
+__device__ __forceinline__ int find_array(const int* s_begin, int n_arrays,
+                                          int item) {
   int lo = 0, hi = n_arrays - 1;
   while (lo < hi) {
-    int mid = (lo + hi + 1) >> 1;
-    if (arrs[mid].item_begin <= item) lo = mid; else hi = mid - 1;
+    const int mid = (lo + hi + 1) >> 1;
+    if (s_begin[mid] <= item) lo = mid; else hi = mid - 1;
   }
   return lo;
 }
 
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, kBlocksPerSm)
 wire_pack_kernel(const WireArray* __restrict__ arrs, int n_arrays,
-                 float* __restrict__ wire) {
-  const long long item = blockIdx.x;
-  const WireArray a = arrs[find_array(arrs, n_arrays, item)];
-  const long long t = item - a.item_begin;
-  float* __restrict__ dst = wire + a.wire_off;
-  if (a.tri > 0 && a.select) {
-    int tr, tc;
-    tri_index(t, tr, tc);
-    const int d = a.tri;
-    const int c = tc * kTile + (threadIdx.x & (kTile - 1));
-    const int r0 = tr * kTile + (threadIdx.x >> 6);
-    const float* __restrict__ src = a.ptr;
+                 int total_items, float* __restrict__ wire) {
+  __shared__ int s_begin[kTabCap];
+  load_item_table(arrs, n_arrays, s_begin);
+  const int tx = threadIdx.x & (kTile - 1), ty = threadIdx.x >> 6;
+  for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
+    const WireArray a = arrs[find_array(s_begin, n_arrays, item)];
+    const int t = item - (int)a.item_begin;
+    float* __restrict__ dst = wire + a.wire_off;
+    if (a.tri > 0 && a.select) {
+      int tr, tc;
+      tri_index(t, tr, tc);
+      const int d = a.tri;
+      const int c = tc * kTile + tx;
+      const float* __restrict__ src = a.ptr;
+#pragma unroll 1
+      for (int half = 0; half < 2; ++half) {
+        const int rb = tr * kTile + half * 32 + ty;
+        float v[8];
 #pragma unroll
-    for (int rr = 0; rr < kTile; rr += 4) {
-      const int r = r0 + rr;
-      if (r < d && c <= r)
-        dst[(long long)r * (r + 1) / 2 + c] = src[(long long)r * d + c];
-    }
-  } else {
-    // plain array, or the slot of a skipped array that is to be cleared
-    const long long base = t * kChunk;
-    const float* __restrict__ src = a.ptr;
+        for (int i = 0; i < 8; ++i) {
+          const int r = rb + 4 * i;
+          if (r < d && c <= r) v[i] = src[(long long)r * d + c];
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int r = rb + 4 * i;
+          if (r < d && c <= r) dst[(long long)r * (r + 1) / 2 + c] = v[i];
+        }
+      }
+    } else {
+      // plain array, or the slot of a skipped array that is to be cleared
+      const long long base = (long long)t * kChunk;
+      const float* __restrict__ src = a.ptr;
 #pragma unroll 8
-    for (int k = threadIdx.x; k < kChunk; k += 256) {
-      const long long w = base + k;
-      if (w < a.wire_n) dst[w] = a.select ? src[w] : 0.f;
+      for (int k = threadIdx.x; k < kChunk; k += 256) {
+        const long long w = base + k;
+        if (w < a.wire_n) dst[w] = a.select ? src[w] : 0.f;
+      }
     }
   }
 }
@@ -115,72 +144,87 @@ wire_pack_kernel(const WireArray* __restrict__ arrs, int n_arrays,
 // Unpack sums the same slot of `srcs.n` wire buffers in the order given (this
 // GPU's own buffer and its peers' over NVLink when the pointers are peer
 // mappings), scales, optionally blends into the destination, and writes the
-// tile and its mirror image, both as coalesced rows.
-__global__ void __launch_bounds__(256)
+// tile and its mirror image, both as coalesced rows.  A tile is handled in
+// four passes of 16 rows (4 elements per thread and source in flight, few
+// registers, 8 blocks per SM).
+__global__ void __launch_bounds__(256, kBlocksPerSm)
 wire_unpack_kernel(const WireArray* __restrict__ arrs, int n_arrays,
-                   float scale, float ema_r, WireSources srcs) {
+                   int total_items, float scale, float ema_r,
+                   WireSources srcs) {
   __shared__ float tile[kTile][kTile + 1];
-  const long long item = blockIdx.x;
-  const WireArray a = arrs[find_array(arrs, n_arrays, item)];
-  const long long t = item - a.item_begin;
-  float* __restrict__ dst = a.ptr;
-  if (a.tri > 0) {
-    int tr, tc;
-    tri_index(t, tr, tc);
-    const int d = a.tri;
-    const int tx = threadIdx.x & (kTile - 1), ty = threadIdx.x >> 6;
-    const int c = tc * kTile + tx;
-    float acc[kTile / 4];
+  __shared__ int s_begin[kTabCap];
+  load_item_table(arrs, n_arrays, s_begin);
+  const int tx = threadIdx.x & (kTile - 1), ty = threadIdx.x >> 6;
+  for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
+    const WireArray a = arrs[find_array(s_begin, n_arrays, item)];
+    const int t = item - (int)a.item_begin;
+    float* __restrict__ dst = a.ptr;
+    if (a.tri > 0) {
+      int tr, tc;
+      tri_index(t, tr, tc);
+      const int d = a.tri;
+      const int c = tc * kTile + tx;
+      const long long off = a.wire_off + c;
+#pragma unroll 1
+      for (int pass = 0; pass < 4; ++pass) {
+        const int rb = tr * kTile + pass * 16 + ty;   // rows rb, rb+4, ...
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int s = 0; s < srcs.n; ++s) {
+          const float* __restrict__ src = srcs.p[s] + off;
+          float x[4];
 #pragma unroll
-    for (int i = 0; i < kTile / 4; ++i) acc[i] = 0.f;
-    for (int s = 0; s < srcs.n; ++s) {
-      const float* __restrict__ src = srcs.p[s] + a.wire_off;
+          for (int i = 0; i < 4; ++i) {
+            const int r = rb + 4 * i;
+            x[i] = (r < d && c <= r) ? src[(long long)r * (r + 1) / 2] : 0.f;
+          }
 #pragma unroll
-      for (int i = 0; i < kTile / 4; ++i) {
-        const int r = tr * kTile + ty + 4 * i;
-        if (r < d && c <= r) acc[i] += src[(long long)r * (r + 1) / 2 + c];
-      }
-    }
+          for (int i = 0; i < 4; ++i) acc[i] += x[i];
+        }
 #pragma unroll
-    for (int i = 0; i < kTile / 4; ++i) {
-      const int r = tr * kTile + ty + 4 * i;
-      float v = acc[i] * scale;
-      if (r < d && c <= r) {
-        float* q = dst + (long long)r * d + c;
-        if (ema_r >= 0.f) v = ema_r * v + (1.f - ema_r) * *q;
-        *q = v;
-      }
-      tile[ty + 4 * i][tx] = v;
-    }
-    __syncthreads();
-    // mirror: element (row cc, column rw) takes the value of (rw, cc), cc < rw
-    const int rw = tr * kTile + tx;
-#pragma unroll
-    for (int i = 0; i < kTile / 4; ++i) {
-      const int cc = tc * kTile + ty + 4 * i;
-      if (rw < d && cc < rw) dst[(long long)cc * d + rw] = tile[tx][ty + 4 * i];
-    }
-  } else {
-    const long long base = t * kChunk;
-    for (int k0 = 0; k0 < kChunk; k0 += 256 * 8) {
-      float acc[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-      for (int s = 0; s < srcs.n; ++s) {
-        const float* __restrict__ src = srcs.p[s] + a.wire_off;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const long long w = base + k0 + i * 256 + threadIdx.x;
-          if (w < a.wire_n) acc[i] += src[w];
+        for (int i = 0; i < 4; ++i) {
+          const int r = rb + 4 * i;
+          float v = acc[i] * scale;
+          if (r < d && c <= r) {
+            float* q = dst + (long long)r * d + c;
+            if (ema_r >= 0.f) v = ema_r * v + (1.f - ema_r) * *q;
+            *q = v;
+          }
+          tile[pass * 16 + ty + 4 * i][tx] = v;
         }
       }
+      __syncthreads();
+      // mirror: element (row cc, column rw) takes the value of (rw, cc), cc < rw
+      const int rw = tr * kTile + tx;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const long long w = base + k0 + i * 256 + threadIdx.x;
-        if (w < a.wire_n) {
-          float v = acc[i] * scale;
-          if (ema_r >= 0.f) v = ema_r * v + (1.f - ema_r) * dst[w];
-          dst[w] = v;
+      for (int i = 0; i < kTile / 4; ++i) {
+        const int cc = tc * kTile + ty + 4 * i;
+        if (rw < d && cc < rw)
+          dst[(long long)cc * d + rw] = tile[tx][ty + 4 * i];
+      }
+      __syncthreads();
+    } else {
+      const long long base = (long long)t * kChunk;
+      for (int k0 = 0; k0 < kChunk; k0 += 256 * 4) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int s = 0; s < srcs.n; ++s) {
+          const float* __restrict__ src = srcs.p[s] + a.wire_off;
+          float x[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const long long w = base + k0 + i * 256 + threadIdx.x;
+            x[i] = w < a.wire_n ? src[w] : 0.f;
+          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) acc[i] += x[i];
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const long long w = base + k0 + i * 256 + threadIdx.x;
+          if (w < a.wire_n) {
+            float v = acc[i] * scale;
+            if (ema_r >= 0.f) v = ema_r * v + (1.f - ema_r) * dst[w];
+            dst[w] = v;
+          }
         }
       }
     }
@@ -225,6 +269,8 @@ static int build_table(int n_arrays, float* const* arrays,
     }
   }
   KFAC_REQUIRE(items < (1ll << 31), "wire: too many work items (%lld)", items);
+  KFAC_REQUIRE(n_arrays <= kTabCap, "wire: %d arrays in one call, at most %d",
+               n_arrays, kTabCap);
   return KFAC_OK;
 }
 
@@ -267,7 +313,9 @@ extern "C" int kfac_wire_pack(int n_arrays, const float* const* arrays,
   const WireArray* tab_dev = nullptr;
   rc = upload_table(tab, st, &tab_dev);
   if (rc != KFAC_OK) return rc;
-  wire_pack_kernel<<<(unsigned)items, 256, 0, st>>>(tab_dev, n_arrays, wire);
+  const long long grid = std::min<long long>(items, (long long)sm_count() * kBlocksPerSm);
+  wire_pack_kernel<<<(unsigned)grid, 256, 0, st>>>(tab_dev, n_arrays,
+                                                   (int)items, wire);
   KFAC_LAUNCH_CHECK("wire_pack_kernel");
   return KFAC_OK;
 }
@@ -296,8 +344,9 @@ extern "C" int kfac_wire_unpack_sum(int n_arrays, float* const* arrays,
   const WireArray* tab_dev = nullptr;
   rc = upload_table(tab, st, &tab_dev);
   if (rc != KFAC_OK) return rc;
-  wire_unpack_kernel<<<(unsigned)items, 256, 0, st>>>(tab_dev, n_arrays, scale,
-                                                      ema_r, srcs);
+  const long long grid = std::min<long long>(items, (long long)sm_count() * kBlocksPerSm);
+  wire_unpack_kernel<<<(unsigned)grid, 256, 0, st>>>(
+      tab_dev, n_arrays, (int)items, scale, ema_r, srcs);
   KFAC_LAUNCH_CHECK("wire_unpack_kernel");
   return KFAC_OK;
 }

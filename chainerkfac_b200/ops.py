@@ -7,6 +7,7 @@ library's kernels.
 """
 
 import ctypes
+import os
 
 import torch
 
@@ -248,8 +249,11 @@ class InversePlanSet(object):
     layer) stay in one plan so that pi sees both traces."""
 
     def __init__(self, factors, inverses, partner, role, l2_coef=None,
-                 scale=None, bounds=(1024, 3000)):
+                 scale=None, bounds=None):
         n = len(factors)
+        if bounds is None:
+            bounds = tuple(int(b) for b in os.environ.get(
+                'KFAC_CLASS_BOUNDS', '1024,3000').split(','))
         l2_coef = l2_coef if l2_coef is not None else [0.0] * n
         scale = scale if scale is not None else [1.0] * n
 
