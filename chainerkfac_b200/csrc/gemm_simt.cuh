@@ -236,7 +236,9 @@ enum GemmFlags {
   G_KBEG_N0 = 4,   // B(k, n) is zero for k < n: start at the tile's n0
   G_KEND_M0 = 8,   // A(k, m) is zero for k > m: stop after the tile's rows
   G_KBEG_M0 = 16,  // A(k, m) is zero for k < m: start at the tile's m0
-  G_PRECOND = 32   // epilogue splits into kf_W / kf_b and applies momentum
+  G_PRECOND = 32,  // epilogue splits into kf_W / kf_b and applies momentum
+  G_SAME_AB = 64   // A and B are the same operand (X^T X): a tile on the
+                   // diagonal may take its A rows from the staged B rows
 };
 
 struct GemmDesc {

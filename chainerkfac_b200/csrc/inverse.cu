@@ -90,14 +90,34 @@ __global__ void damp_copy_kernel(const MatInfo* __restrict__ mats,
   const MatInfo mi = mats[blockIdx.y];
   const float a = add[blockIdx.y];
   const int d = mi.d;
+  const bool vec = (d & 3) == 0 &&
+                   ((reinterpret_cast<uintptr_t>(mi.F) |
+                     reinterpret_cast<uintptr_t>(mi.W)) & 15) == 0;
   for (int r = blockIdx.x; r < d; r += gridDim.x) {
     const int cend = min(d, (r | (DB - 1)) + 1);
     const float* src = mi.F + (long long)r * d;
     float* dst = mi.W + (long long)r * d;
-    for (int c = threadIdx.x; c < cend; c += blockDim.x) {
-      float v = src[c];
-      if (r == c) v += a;
-      dst[c] = v;
+    if (vec) {
+      // cend is a multiple of 128 or equals d, itself a multiple of 4 here
+      const float4* s4 = reinterpret_cast<const float4*>(src);
+      float4* d4 = reinterpret_cast<float4*>(dst);
+#pragma unroll 4
+      for (int c4 = threadIdx.x; c4 < (cend >> 2); c4 += blockDim.x) {
+        float4 v = s4[c4];
+        if ((r >> 2) == c4) {
+          if ((r & 3) == 0) v.x += a;
+          else if ((r & 3) == 1) v.y += a;
+          else if ((r & 3) == 2) v.z += a;
+          else v.w += a;
+        }
+        d4[c4] = v;
+      }
+    } else {
+      for (int c = threadIdx.x; c < cend; c += blockDim.x) {
+        float v = src[c];
+        if (r == c) v += a;
+        dst[c] = v;
+      }
     }
   }
 }
@@ -437,7 +457,7 @@ extern "C" int kfac_inverse_plan_create(
       g.B = g.A;
       g.C = m.W + (long long)(po + PW) * d + (po + PW);
       g.ldc = d; g.M = M; g.N = M; g.K = PW;
-      g.alpha = -1.f; g.beta = 1.f; g.flags = G_LOWER;
+      g.alpha = -1.f; g.beta = 1.f; g.flags = G_LOWER | G_SAME_AB;
       push_desc(trail, g);
     }
     end_gemm(trail);
@@ -486,7 +506,7 @@ extern "C" int kfac_inverse_plan_create(
       g.B = g.A;
       g.C = m.inv; g.ldc = d; g.M = d; g.N = d; g.K = d;
       g.alpha = 1.f; g.beta = 0.f;
-      g.flags = G_LOWER | G_MIRROR | G_KBEG_M0;
+      g.flags = G_LOWER | G_MIRROR | G_KBEG_M0 | G_SAME_AB;
       push_desc(prod, g);
     }
     end_gemm(prod);

@@ -282,7 +282,8 @@ __device__ __forceinline__ bool tc_task_is_a(int t, int warp) {
 template <bool IM2COL, int PW>
 __device__ __forceinline__ void tc_task_setup(const Operand& A,
                                               const Operand& B, int m0, int n0,
-                                              int rows_b, const TcControl* ctl,
+                                              int rows_b, bool skip_a,
+                                              const TcControl* ctl,
                                               int warp, int lane,
                                               PTask task[TcMap<PW>::kTasks]) {
 #pragma unroll
@@ -292,7 +293,7 @@ __device__ __forceinline__ void tc_task_setup(const Operand& A,
     const bool kf = IM2COL || op.kfast;
     const int band_row = kf ? warp * 4 + (lane >> 3) : 32 * (warp >> 3) + lane;
     const int row = TcMap<PW>::kBand * t + band_row - (is_a ? 0 : TC_BM);
-    const int rows = is_a ? TC_BM : rows_b;
+    const int rows = is_a ? (skip_a ? 0 : TC_BM) : rows_b;
     const int chunk = kf ? (lane & 7) : (warp & 7);
     PTask v;
     v.soff = row < rows ? (unsigned)((is_a ? 0 : TC_A_BYTES) + row * 128 +
@@ -570,6 +571,11 @@ tc_gemm_kernel(const GemmDesc* __restrict__ descs, int ndesc,
   if (g.flags & G_KBEG_M0) kbeg = max(kbeg, (long long)m0);
   if (g.flags & G_KEND_M0) kend = min(kend, (long long)(m0 + TC_BM));
   const int nkb = kend > kbeg ? (int)((kend - kbeg + TC_BK - 1) / TC_BK) : 0;
+  // X^T X on a diagonal tile: the tile's A rows are rows [m0 - n0, m0 - n0 +
+  // 128) of its B rows (m0 - n0 is 0 or 128), so only B is staged and the A
+  // descriptors point into the B tiles.
+  const bool share_ab = (g.flags & G_SAME_AB) && (g.flags & G_LOWER) &&
+                        bj == (bi >> 1);
 
   if (warp < TC_PRODUCERS / 32) {
     // ===================== producers =====================
@@ -583,7 +589,8 @@ tc_gemm_kernel(const GemmDesc* __restrict__ descs, int ndesc,
     const Operand A = g.A, B = g.B;   // register copies: loop invariant
     float4 v[TC_NTASK];
     PTask task[TC_NTASK];
-    tc_task_setup<IM2COL, PW>(A, B, m0, n0, n_inst, ctl, warp, lane, task);
+    tc_task_setup<IM2COL, PW>(A, B, m0, n0, n_inst, share_ab, ctl, warp, lane,
+                              task);
     const int kend_i = (int)kend;
     KState ka, kb_state;
     {
@@ -648,9 +655,11 @@ tc_gemm_kernel(const GemmDesc* __restrict__ descs, int ndesc,
         TC_TRACE(kb, 6);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const unsigned sa = smem_u32(smem + s * TC_STAGE_BYTES);
-        const unsigned long long a_hi = tc_smem_desc(sa);
+        const unsigned a_off =
+            share_ab ? (unsigned)(TC_A_BYTES + (m0 - n0) * 128) : 0u;
+        const unsigned long long a_hi = tc_smem_desc(sa + a_off);
         const unsigned long long b_hi = tc_smem_desc(sa + TC_A_BYTES);
-        const unsigned long long a_lo = tc_smem_desc(sa + TC_LO_OFF);
+        const unsigned long long a_lo = tc_smem_desc(sa + TC_LO_OFF + a_off);
         const unsigned long long b_lo =
             tc_smem_desc(sa + TC_LO_OFF + TC_A_BYTES);
 #pragma unroll
@@ -1060,7 +1069,7 @@ int run_factor_group_tc(int count, const FactorJob* jobs, void* workspace,
     g.N = job.d;
     g.alpha = job.alpha;
     g.beta = job.beta;
-    g.flags = G_LOWER | G_MIRROR;
+    g.flags = G_LOWER | G_MIRROR | G_SAME_AB;
     g.ntiles = tc_tiles(g);
     g.splits = s.splits;
     g.k_per_split = s.k_per_split;
