@@ -201,16 +201,20 @@ __device__ __forceinline__ void sts128(unsigned addr, float4 v) {
                : "memory");
 }
 
-// hi = x rounded to TF32, lo = x - hi (exact in fp32; the tensor core reads
-// its top 11 bits).
+// hi = x rounded to TF32 (nearest, ties away from zero), lo = x - hi (exact in
+// fp32; the tensor core reads its top 11 bits).  The rounding is two integer
+// instructions (add half an ulp of TF32, clear the low 13 bits): cvt.rna
+// would be one, but conversions issue on the quarter-rate XU pipe, which the
+// producers saturate.
+__device__ __forceinline__ float tf32_round(float x) {
+  return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xffffe000u);
+}
+
 __device__ __forceinline__ void store_split(unsigned hi_addr, unsigned lo_addr,
                                             float4 x) {
   float4 h, l;
-  // hi = x rounded to the nearest TF32 value (one cvt instruction)
-  { unsigned u; asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x.x)); h.x = __uint_as_float(u); }
-  { unsigned u; asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x.y)); h.y = __uint_as_float(u); }
-  { unsigned u; asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x.z)); h.z = __uint_as_float(u); }
-  { unsigned u; asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x.w)); h.w = __uint_as_float(u); }
+  h.x = tf32_round(x.x); h.y = tf32_round(x.y);
+  h.z = tf32_round(x.z); h.w = tf32_round(x.w);
   l.x = x.x - h.x; l.y = x.y - h.y; l.z = x.z - h.z; l.w = x.w - h.w;
   sts128(hi_addr, h);
   sts128(lo_addr, l);
@@ -351,17 +355,17 @@ __device__ __forceinline__ void kstate_init(const Operand& op, long long k,
   }
 }
 
-template <bool IM2COL>
+template <bool IM2COL, int BK = TC_BK>
 __device__ __forceinline__ void kstate_advance(const Operand& op, KState& s) {
-  s.k += TC_BK;
+  s.k += BK;
   if (IM2COL) {
-    s.c += TC_BK;
+    s.c += BK;
     while (s.c >= op.Wo) {
       s.c -= op.Wo;
       if (++s.b >= op.Ho) { s.b = 0; ++s.a; }
     }
   } else if (op.period != 1) {
-    s.b += TC_BK;
+    s.b += BK;
     while (s.b >= op.period) { s.b -= op.period; ++s.a; }
   }
 }
@@ -371,16 +375,16 @@ __device__ __forceinline__ void kstate_advance(const Operand& op, KState& s) {
 // zero-bordered buffer first, so every tap of every pixel is in range).
 // With TAILS, offsets of k at or beyond kend are 0 (a legal address; the
 // value is zeroed after the load).
-template <bool IM2COL, bool TAILS>
+template <bool IM2COL, bool TAILS, int J = 4>
 __device__ __forceinline__ void tc_koffsets(const Operand& op,
                                             const KState& ks, int kend,
-                                            int o[4]) {
+                                            int o[J]) {
   const int k = ks.k;
   if (IM2COL) {
     int n = ks.a, oy = ks.b, ox = ks.c;
     const int chw = op.C * op.H * op.W;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < J; ++j) {
       o[j] = n * chw + oy * op.st * op.W + ox * op.st;
       if (TAILS && k + j >= kend) o[j] = 0;
       if (++ox >= op.Wo) {
@@ -392,10 +396,10 @@ __device__ __forceinline__ void tc_koffsets(const Operand& op,
   }
   if (op.period == 1) {
 #pragma unroll
-    for (int j = 0; j < 4; ++j) o[j] = k + j;
+    for (int j = 0; j < J; ++j) o[j] = k + j;
   } else {
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < J; ++j) {
       int q = ks.a, r = ks.b + j;
       while (r >= op.period) { r -= op.period; ++q; }
       o[j] = (int)((long long)q * op.s_outer + (long long)r * op.s_inner);
@@ -403,7 +407,7 @@ __device__ __forceinline__ void tc_koffsets(const Operand& op,
   }
   if (TAILS) {
 #pragma unroll
-    for (int j = 0; j < 4; ++j) if (k + j >= kend) o[j] = 0;
+    for (int j = 0; j < J; ++j) if (k + j >= kend) o[j] = 0;
   }
 }
 
@@ -809,6 +813,527 @@ tc_gemm_kernel(const GemmDesc* __restrict__ descs, int ndesc,
   }
 }
 
+// ---- split-bf16 operands (factor builds) ----
+// x = hi + lo with hi = bf16(x), lo = bf16(x - hi): 16 significant bits,
+// products hi*hi + hi*lo + lo*hi are exact in the fp32 accumulator.  Halves
+// the shared-memory bytes per k of the split-TF32 scheme (stores and tensor
+// core operand reads), which is what bounds the tile kernels.
+__device__ __forceinline__ unsigned tc_instr_desc_bf16(int n) {
+  // D = f32, A = B = bf16, both K-major, M = 128, N = n
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) |
+         ((unsigned)(TC_BM >> 4) << 24);
+}
+
+__device__ __forceinline__ void tc_mma_bf16(unsigned tmem_d,
+                                            unsigned long long da,
+                                            unsigned long long db,
+                                            unsigned idesc,
+                                            unsigned accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// Two consecutive k -> one word of the hi tile and one of the lo tile (the
+// first k in the low half).  Rounding to bf16 is an integer add of half an ulp
+// (ties away from zero); the byte permute then takes the upper halves.  No
+// cvt: conversions issue on the quarter-rate XU pipe (measured at 130 % of its
+// sustained peak with cvt.rn.bf16x2 here).
+__device__ __forceinline__ void split_bf16x2(float x0, float x1, unsigned& hi,
+                                             unsigned& lo) {
+  const unsigned r0 = __float_as_uint(x0) + 0x8000u;
+  const unsigned r1 = __float_as_uint(x1) + 0x8000u;
+  hi = __byte_perm(r0, r1, 0x7632);
+  const float l0 = x0 - __uint_as_float(r0 & 0xffff0000u);
+  const float l1 = x1 - __uint_as_float(r1 & 0xffff0000u);
+  lo = __byte_perm(__float_as_uint(l0) + 0x8000u,
+                   __float_as_uint(l1) + 0x8000u, 0x7632);
+}
+
+__device__ __forceinline__ void store_split_bf16(unsigned hi_addr,
+                                                 unsigned lo_addr, float4 a,
+                                                 float4 b) {
+  unsigned h[4], l[4];
+  split_bf16x2(a.x, a.y, h[0], l[0]);
+  split_bf16x2(a.z, a.w, h[1], l[1]);
+  split_bf16x2(b.x, b.y, h[2], l[2]);
+  split_bf16x2(b.z, b.w, h[3], l[3]);
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(hi_addr),
+               "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3])
+               : "memory");
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(lo_addr),
+               "r"(l[0]), "r"(l[1]), "r"(l[2]), "r"(l[3])
+               : "memory");
+}
+
+// ============================================================ X^T X, 256 x 256
+// Factor builds (C = alpha X^T X + beta C, lower tiles, mirrored) use a CTA
+// tile of 256 x 256: two 128-row accumulators that share one staged set of
+// 256 B rows, so a k-block needs 512 operand rows for 65536 outputs instead of
+// 384 for 32768; on diagonal tiles the A rows are the B rows and only those
+// are staged.  Operands are split into two bf16 terms (see above).  A stage
+// holds 32 k as 64-byte rows under the 64-byte swizzle ([A hi][B hi][A lo]
+// [B lo], 16 KB each), three stages are in flight, and each 128 x 256
+// accumulator takes 256 of the 512 tensor-memory columns (cross terms and
+// hi*hi go into the same accumulator, cross terms first).  Partial tiles of
+// split contractions keep the 128 x 256 numbering of tc_tri_tile, so
+// tc_reduce_kernel serves both kernels.
+constexpr int PK_BK = 32;
+constexpr int PK_ROWS = 256;                         // rows per operand tile
+constexpr int PK_TILE_BYTES = PK_ROWS * PK_BK * 2;   // 16 KB of bf16
+constexpr int PK_LO_OFF = 2 * PK_TILE_BYTES;
+constexpr int PK_STAGE_BYTES = 4 * PK_TILE_BYTES;    // 64 KB
+constexpr int PK_STAGES = 3;
+constexpr int PK_PRODUCERS = 512;
+constexpr int PK_PWARPS = PK_PRODUCERS / 32;
+constexpr int PK_THREADS = PK_PRODUCERS + 32;
+constexpr int PK_NTASK = 2 * PK_ROWS * (PK_BK / 8) / PK_PRODUCERS;   // 4
+
+struct __align__(16) PkControl {
+  unsigned long long full[PK_STAGES];
+  unsigned long long empty[PK_STAGES];
+  unsigned long long accum;
+  unsigned tmem_base;
+  volatile int abort_flag;
+  int found;
+  GemmDesc desc;
+};
+constexpr int PK_SMEM_BYTES =
+    PK_STAGES * PK_STAGE_BYTES + ((int)sizeof(PkControl) + 1023) / 1024 * 1024 +
+    1024;
+static_assert(PK_SMEM_BYTES <= 227 * 1024, "pair kernel shared memory");
+static_assert(TC_BM * TC_EPI_PITCH * 4 <= PK_STAGES * PK_STAGE_BYTES,
+              "epilogue staging tile");
+
+__device__ __forceinline__ unsigned long long pk_smem_desc(unsigned addr) {
+  // K-major, 64-byte swizzle: 8-row groups 512 bytes apart.
+  unsigned long long d = 0;
+  d |= (unsigned long long)((addr & 0x3FFFF) >> 4);         // start address
+  d |= (unsigned long long)1 << 16;                         // LBO (unused)
+  d |= (unsigned long long)(512 >> 4) << 32;                // SBO
+  d |= (unsigned long long)1 << 46;                         // descriptor version
+  d |= (unsigned long long)4 << 61;                         // SWIZZLE_64B
+  return d;
+}
+
+// Pair (Bi, Bj), Bj <= Bi, of 256-row blocks from its index Bi(Bi+1)/2 + Bj.
+__device__ __forceinline__ void pk_pair(int t, int& Bi, int& Bj) {
+  int a = (int)((sqrtf(8.f * (float)t + 1.f) - 1.f) * 0.5f);
+  while ((a + 1) * (a + 2) / 2 <= t) ++a;
+  while (a * (a + 1) / 2 > t) --a;
+  Bi = a;
+  Bj = t - a * (a + 1) / 2;
+}
+
+template <bool IM2COL, bool TAILS>
+__global__ void __launch_bounds__(PK_THREADS, 1)
+tc_pair_kernel(const GemmDesc* __restrict__ descs, int ndesc,
+               const __grid_constant__ GemmDesc inline_desc) {
+  extern __shared__ unsigned char tc_smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
+  PkControl* ctl =
+      reinterpret_cast<PkControl*>(smem + PK_STAGES * PK_STAGE_BYTES);
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
+  const int tile = blockIdx.x;
+  {
+    const GemmDesc* src = &inline_desc;
+    if (descs != nullptr) {
+      for (int i = tid; i < ndesc; i += PK_THREADS) {
+        const int lo = descs[i].tile_begin;
+        const int hi = (i + 1 < ndesc) ? descs[i + 1].tile_begin : 0x7fffffff;
+        if (lo <= tile && tile < hi) ctl->found = i;
+      }
+      __syncthreads();
+      src = descs + ctl->found;
+    }
+    const int* s = reinterpret_cast<const int*>(src);
+    int* d = reinterpret_cast<int*>(&ctl->desc);
+    for (int i = tid; i < (int)(sizeof(GemmDesc) / sizeof(int)); i += PK_THREADS)
+      d[i] = s[i];
+  }
+  if (tid == 0) {
+    for (int s = 0; s < PK_STAGES; ++s) {
+      mbar_init(&ctl->full[s], PK_PWARPS);
+      mbar_init(&ctl->empty[s], 1);
+    }
+    mbar_init(&ctl->accum, 1);
+    ctl->abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == PK_PWARPS) {
+    asm volatile(
+        "tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+        ::"r"(smem_u32(&ctl->tmem_base)), "r"(TC_TMEM_COLS)
+        : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;"
+                 ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+
+  const GemmDesc& g = ctl->desc;
+  const unsigned tmem = ctl->tmem_base;
+  const int nblk = (g.tiles_m + 1) >> 1;            // 256-row blocks
+  const int npairs = nblk * (nblk + 1) / 2;
+  int lt = tile - g.tile_begin, split = 0;
+  if (g.splits > 1) {
+    split = lt / npairs;
+    lt -= split * npairs;
+  }
+  int Bi, Bj;
+  pk_pair(lt, Bi, Bj);
+  const int m0 = Bi * PK_ROWS, n0 = Bj * PK_ROWS;
+  const bool share = Bi == Bj;
+  const int n_valid = min(PK_ROWS, g.N - n0);
+  const int n_inst = (n_valid + 15) & ~15;
+  const int rows_a = min(PK_ROWS, g.M - m0);
+  const bool two = rows_a > TC_BM;                  // second accumulator used
+  long long kbeg = 0, kend = g.K;
+  if (g.splits > 1) {
+    kbeg = (long long)split * g.k_per_split;
+    kend = min(g.K, kbeg + g.k_per_split);
+  }
+  const int nkb = kend > kbeg ? (int)((kend - kbeg + PK_BK - 1) / PK_BK) : 0;
+
+  if (warp < PK_PWARPS) {
+    // ===================== producers =====================
+    const Operand X = g.A;                          // A and B are the same
+    if (IM2COL) {
+      // ---- im2col gather: lanes walk k.  Half a warp reads 32 consecutive
+      // output pixels (16 lanes x 2) of one patch-matrix column, the other
+      // half the same pixels of the next column: a load instruction touches
+      // two to four cache lines instead of up to 32 sectors.  Warp w owns
+      // rows 2w + 32 j + h (j = 0..15, h = lane / 16; j < 8: A rows) of the
+      // 512 staged rows; a thread keeps the 16 row offsets in registers for
+      // the whole tile, loads pixels (k, k+1) of each row per k-block and
+      // packs them into one bf16x2 word per tile, so a warp's store covers
+      // 128 contiguous bytes.  Rows past the operand's edge read column 0:
+      // their products are never stored.  The appended ones column is
+      // patched in after the loads.
+      const int h = lane >> 4, kp = lane & 15;
+      int off[16];
+      unsigned ones = 0;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const int R = 2 * warp + 32 * j + h;
+        const bool is_a = j < 8;
+        const int c = (is_a ? m0 : n0 - PK_ROWS) + R;
+        int o = 0;
+        if (c < X.ncols) {
+          const int kk = X.ks * X.ks;
+          const int ch = c / kk;
+          const int r = c - ch * kk;
+          const int ky = r / X.ks;
+          const int kx = r - ky * X.ks;
+          o = ch * X.H * X.W + ky * X.W + kx;
+        } else if (c == X.extra_idx) {
+          ones |= 1u << j;
+        }
+        off[j] = o;
+      }
+      const int kend_i = (int)kend;
+      KState ks;
+      kstate_init<true>(X, kbeg + 2 * kp, ks);
+      const int chw = X.C * X.H * X.W, sw = X.st * X.W;
+      const unsigned lane_off = (unsigned)((((kp >> 2) ^ (warp & 3)) << 4) +
+                                           4 * (kp & 3) + h * 64 + warp * 128);
+      const unsigned smem_base = smem_u32(smem);
+      const int j0 = share ? 8 : 0;
+      float x[32];
+      for (int kb = 0; kb <= nkb; ++kb) {
+        if (kb > 0) {
+          const int pb = kb - 1;
+          const int s = pb % PK_STAGES;
+          if (pb >= PK_STAGES) {
+            if (!mbar_wait(&ctl->empty[s], ((pb / PK_STAGES) - 1) & 1,
+                           &ctl->abort_flag))
+              break;
+          }
+          const unsigned st = smem_base + s * PK_STAGE_BYTES + lane_off;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            if (j < j0) continue;
+            unsigned hi, lo;
+            split_bf16x2(x[2 * j], x[2 * j + 1], hi, lo);
+            asm volatile("st.shared.b32 [%0], %1;" ::"r"(st + 2048 * j), "r"(hi)
+                         : "memory");
+            asm volatile("st.shared.b32 [%0], %1;"
+                         ::"r"(st + PK_LO_OFF + 2048 * j), "r"(lo)
+                         : "memory");
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&ctl->full[s]);
+        }
+        if (kb < nkb) {
+          // pixel offsets of k and k + 1 (k + 1 may start the next image row)
+          const bool live0 = !TAILS || ks.k < kend_i;
+          const bool live1 = !TAILS || ks.k + 1 < kend_i;
+          int o0 = ks.a * chw + ks.b * sw + ks.c * X.st;
+          int o1 = o0 + X.st;
+          if (ks.c + 1 >= X.Wo) {
+            o1 = (ks.b + 1 >= X.Ho) ? (ks.a + 1) * chw
+                                    : ks.a * chw + (ks.b + 1) * sw;
+          }
+          if (!live0) o0 = 0;
+          if (!live1) o1 = 0;
+          const float* p0 = X.base + o0;
+          const float* p1 = X.base + o1;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            if (j < j0) continue;
+            x[2 * j] = p0[off[j]];
+            x[2 * j + 1] = p1[off[j]];
+          }
+          if (ones) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (ones & (1u << j)) x[2 * j] = x[2 * j + 1] = 1.f;
+          }
+          if (TAILS && !live1) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              if (!live0) x[2 * j] = 0.f;
+              x[2 * j + 1] = 0.f;
+            }
+          }
+          kstate_advance<true, PK_BK>(X, ks);
+        }
+      }
+    } else {
+      const bool kf = IM2COL || X.kfast;
+      // per task: 128 of the 512 (A then B) rows; a warp covers 8 rows x 4
+      // chunks of a k-contiguous operand, or one chunk of 32 rows of a
+      // column-contiguous one
+      PTask task[PK_NTASK];
+  #pragma unroll
+      for (int t = 0; t < PK_NTASK; ++t) {
+        const bool is_a = t < PK_NTASK / 2;
+        const int band_row = kf ? warp * 8 + (lane >> 2) : 32 * (warp >> 2) + lane;
+        const int row = 128 * t + band_row - (is_a ? 0 : PK_ROWS);
+        const int rows = is_a ? (share ? 0 : rows_a) : n_inst;
+        const int chunk = kf ? (lane & 3) : (warp & 3);
+        PTask v;
+        v.soff = row < rows
+                     ? (unsigned)((is_a ? 0 : PK_TILE_BYTES) + row * 64 +
+                                  ((chunk ^ ((row >> 1) & 3)) << 4))
+                     : ~0u;
+        const float* p = g_zero_page;
+        int m = 0;
+        if (row < rows) {
+          const int c = (is_a ? m0 : n0) + row;
+          if (c < X.ncols) {
+            p = X.base + (long long)c * X.s_col;
+            m = X.period == 1 ? (int)X.s_outer : 1;
+          } else if (c == X.extra_idx) {
+            if (X.extra) { p = X.extra; m = 1; }
+            else p = g_ones_page;
+          }
+        }
+        v.p = reinterpret_cast<const char*>(p);
+        v.m = m * 4;
+        task[t] = v;
+      }
+      const int kend_i = (int)kend;
+      KState ks;
+      kstate_init<IM2COL>(X, kbeg + 8 * (kf ? (lane & 3) : (warp & 3)), ks);
+      const unsigned smem_base = smem_u32(smem);
+      const bool vec = !IM2COL && tc_operand_vec(X, kbeg);
+      // a task is 8 consecutive k of one row: 16 bytes of each bf16 tile
+      float4 v[PK_NTASK][2];
+      for (int kb = 0; kb <= nkb; ++kb) {
+        if (kb > 0) {
+          const int pb = kb - 1;
+          const int s = pb % PK_STAGES;
+          if (pb >= PK_STAGES) {
+            if (!mbar_wait(&ctl->empty[s], ((pb / PK_STAGES) - 1) & 1,
+                           &ctl->abort_flag))
+              break;
+          }
+          const unsigned st = smem_base + s * PK_STAGE_BYTES;
+  #pragma unroll
+          for (int t = 0; t < PK_NTASK; ++t)
+            if (task[t].soff != ~0u)
+              store_split_bf16(st + task[t].soff, st + PK_LO_OFF + task[t].soff,
+                               v[t][0], v[t][1]);
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&ctl->full[s]);
+        }
+        if (kb < nkb) {
+          int o[8];
+          tc_koffsets<IM2COL, TAILS, 8>(X, ks, kend_i, o);
+          const int k = ks.k;
+          const bool tail = TAILS && (k + 7 >= kend_i);
+          if (vec && !tail) {
+  #pragma unroll
+            for (int t = 0; t < PK_NTASK; ++t)
+              if (task[t].soff != ~0u) {
+                v[t][0] = *reinterpret_cast<const float4*>(
+                    task[t].p + (long long)o[0] * task[t].m);
+                v[t][1] = *reinterpret_cast<const float4*>(
+                    task[t].p + (long long)o[4] * task[t].m);
+              }
+          } else {
+  #pragma unroll
+            for (int t = 0; t < PK_NTASK; ++t) {
+              if (task[t].soff == ~0u) continue;
+              v[t][0].x = *reinterpret_cast<const float*>(task[t].p + (long long)o[0] * task[t].m);
+              v[t][0].y = *reinterpret_cast<const float*>(task[t].p + (long long)o[1] * task[t].m);
+              v[t][0].z = *reinterpret_cast<const float*>(task[t].p + (long long)o[2] * task[t].m);
+              v[t][0].w = *reinterpret_cast<const float*>(task[t].p + (long long)o[3] * task[t].m);
+              v[t][1].x = *reinterpret_cast<const float*>(task[t].p + (long long)o[4] * task[t].m);
+              v[t][1].y = *reinterpret_cast<const float*>(task[t].p + (long long)o[5] * task[t].m);
+              v[t][1].z = *reinterpret_cast<const float*>(task[t].p + (long long)o[6] * task[t].m);
+              v[t][1].w = *reinterpret_cast<const float*>(task[t].p + (long long)o[7] * task[t].m);
+            }
+          }
+          if (tail) {
+  #pragma unroll
+            for (int t = 0; t < PK_NTASK; ++t) {
+              if (k + 0 >= kend_i) v[t][0].x = 0.f;
+              if (k + 1 >= kend_i) v[t][0].y = 0.f;
+              if (k + 2 >= kend_i) v[t][0].z = 0.f;
+              if (k + 3 >= kend_i) v[t][0].w = 0.f;
+              if (k + 4 >= kend_i) v[t][1].x = 0.f;
+              if (k + 5 >= kend_i) v[t][1].y = 0.f;
+              if (k + 6 >= kend_i) v[t][1].z = 0.f;
+              if (k + 7 >= kend_i) v[t][1].w = 0.f;
+            }
+          }
+          kstate_advance<IM2COL, PK_BK>(X, ks);
+        }
+      }
+    }
+  } else {
+    // ===================== MMA issuer =====================
+    if (lane == 0) {
+      const unsigned idesc = tc_instr_desc_bf16(n_inst);
+      const unsigned a_off = share ? (unsigned)PK_TILE_BYTES : 0u;
+      for (int kb = 0; kb < nkb; ++kb) {
+        const int s = kb % PK_STAGES;
+        if (!mbar_wait(&ctl->full[s], (kb / PK_STAGES) & 1, &ctl->abort_flag))
+          break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const unsigned sa = smem_u32(smem + s * PK_STAGE_BYTES);
+        const unsigned long long a_hi = pk_smem_desc(sa + a_off);
+        const unsigned long long a_lo = pk_smem_desc(sa + PK_LO_OFF + a_off);
+        const unsigned long long b_hi = pk_smem_desc(sa + PK_TILE_BYTES);
+        const unsigned long long b_lo =
+            pk_smem_desc(sa + PK_LO_OFF + PK_TILE_BYTES);
+        // second accumulator: A rows 128..255 start 128 * 64 bytes later
+        const unsigned long long up = (unsigned long long)(TC_BM * 64 >> 4);
+#pragma unroll
+        for (int kk = 0; kk < PK_BK / 16; ++kk) {
+          // 16 bf16 = 32 bytes per MMA along k
+          const unsigned long long adv = (unsigned long long)(kk * 32 >> 4);
+          const unsigned acc = (kb | kk) != 0;
+          tc_mma_bf16(tmem, a_lo + adv, b_hi + adv, idesc, acc);
+          tc_mma_bf16(tmem, a_hi + adv, b_lo + adv, idesc, 1);
+          tc_mma_bf16(tmem, a_hi + adv, b_hi + adv, idesc, 1);
+          if (two) {
+            tc_mma_bf16(tmem + TC_BN, a_lo + up + adv, b_hi + adv, idesc, acc);
+            tc_mma_bf16(tmem + TC_BN, a_hi + up + adv, b_lo + adv, idesc, 1);
+            tc_mma_bf16(tmem + TC_BN, a_hi + up + adv, b_hi + adv, idesc, 1);
+          }
+        }
+        tc_commit(&ctl->empty[s]);
+      }
+      tc_commit(&ctl->accum);
+    }
+    __syncwarp();
+  }
+
+  // ===================== epilogue =====================
+  if (warp < PK_PWARPS) {
+    float* stage = reinterpret_cast<float*>(smem);
+    if (nkb > 0) {
+      mbar_wait(&ctl->accum, 0, &ctl->abort_flag);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    }
+    asm volatile("bar.sync 1, %0;" ::"r"(PK_PRODUCERS) : "memory");
+    const bool dead = ctl->abort_flag != 0;        // uniform after the barrier
+    const float alpha = g.alpha, beta = g.beta;
+    const int q = warp & 3, h = warp >> 2;
+    for (int tt = 0; tt < (two ? 2 : 1) && !dead; ++tt) {
+      const int m0t = m0 + TC_BM * tt;
+      const int m_valid = min(TC_BM, g.M - m0t);
+      const int nv = min(n_valid, m0t + TC_BM - n0);   // lower triangle
+      const int row = q * 32 + lane;
+      for (int c0 = h * 16; c0 < n_inst; c0 += 16 * (PK_PWARPS / 4)) {
+        float v[16];
+        if (nkb > 0) {
+          tc_ld16(tmem + ((unsigned)(q * 32) << 16) + (unsigned)(TC_BN * tt + c0), v);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] = 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) stage[row * TC_EPI_PITCH + c0 + i] = v[i];
+      }
+      asm volatile("bar.sync 1, %0;" ::"r"(PK_PRODUCERS) : "memory");
+      if (g.splits > 1) {
+        // 128 x 256 numbering: row block 2 Bi + tt, column block Bj
+        const int lt128 = (tt == 0 ? Bi * (Bi + 1) : (Bi + 1) * (Bi + 1)) + Bj;
+        float* p = g.partial +
+                   ((long long)split * g.ntiles + lt128) * (TC_BM * TC_BN);
+        for (int r = warp; r < TC_BM; r += PK_PWARPS)
+          for (int c = lane; c < n_inst; c += 32)
+            p[r * TC_BN + c] = stage[r * TC_EPI_PITCH + c];
+      } else {
+        for (int r = warp; r < m_valid; r += PK_PWARPS) {
+          const int gr = m0t + r;
+          float* crow = g.C + (long long)gr * g.ldc + n0;
+          const int cend = min(nv, gr - n0 + 1);
+          float old[TC_BN / 32];
+          if (beta != 0.f) {
+#pragma unroll
+            for (int i = 0; i < TC_BN / 32; ++i) {
+              const int c = lane + 32 * i;
+              old[i] = c < cend ? crow[c] : 0.f;
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < TC_BN / 32; ++i) {
+            const int c = lane + 32 * i;
+            if (c < cend) {
+              float v = alpha * stage[r * TC_EPI_PITCH + c];
+              if (beta != 0.f) v += beta * old[i];
+              crow[c] = v;
+              stage[r * TC_EPI_PITCH + c] = v;
+            }
+          }
+        }
+        asm volatile("bar.sync 1, %0;" ::"r"(PK_PRODUCERS) : "memory");
+        for (int c = warp; c < nv; c += PK_PWARPS) {
+          const int gc = n0 + c;
+          for (int r = lane; r < m_valid; r += 32) {
+            const int gr = m0t + r;
+            if (gc < gr)
+              g.C[(long long)gc * g.ldc + gr] = stage[r * TC_EPI_PITCH + c];
+          }
+        }
+      }
+      // the second accumulator reuses the staging tile
+      asm volatile("bar.sync 1, %0;" ::"r"(PK_PRODUCERS) : "memory");
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == PK_PWARPS) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
+                 ::"r"(tmem), "r"(TC_TMEM_COLS)
+                 : "memory");
+  }
+}
+
+
 // Copy an NCHW tensor into a buffer with a zero border of `pad` pixels.
 // blockIdx.y walks the (n, c) planes, threads walk one padded plane: no
 // division by run-time 64-bit values in the inner loop.
@@ -911,6 +1436,18 @@ static int tc_prepare() {
     KFAC_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<true, true, TC_PW_IM2COL>,
                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    TC_SMEM_BYTES));
+    KFAC_CUDA(cudaFuncSetAttribute(tc_pair_kernel<false, false>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   PK_SMEM_BYTES));
+    KFAC_CUDA(cudaFuncSetAttribute(tc_pair_kernel<false, true>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   PK_SMEM_BYTES));
+    KFAC_CUDA(cudaFuncSetAttribute(tc_pair_kernel<true, false>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   PK_SMEM_BYTES));
+    KFAC_CUDA(cudaFuncSetAttribute(tc_pair_kernel<true, true>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   PK_SMEM_BYTES));
     done[dev] = true;
   }
   return KFAC_OK;
@@ -949,6 +1486,28 @@ struct TcFactorSplit {
   long long k_per_split;
 };
 
+// Factor builds run on the 256 x 256 kernel unless KFAC_TC_PAIR=0 is set in
+// the environment (kept for comparison runs).
+static bool tc_use_pair() {
+  static const bool on = [] {
+    const char* e = getenv("KFAC_TC_PAIR");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
+// CTAs that cover the lower tiles of a d x d output once.
+static int tc_factor_ctas(int d) {
+  if (!tc_use_pair()) {
+    GemmDesc g = {};
+    g.M = g.N = d;
+    g.flags = G_LOWER;
+    return tc_tiles(g);
+  }
+  const int nblk = (d + PK_ROWS - 1) / PK_ROWS;
+  return nblk * (nblk + 1) / 2;
+}
+
 static int tc_lower_tiles(int d) {
   GemmDesc g = {};
   g.M = g.N = d;
@@ -974,7 +1533,7 @@ static TcFactorSplit tc_split_for(long long rows, int d, long long chunk) {
 
 static TcFactorSplit tc_factor_split(long long rows, int d) {
   // a factor built on its own: aim at two waves of CTAs
-  const int tiles = tc_lower_tiles(d);
+  const int tiles = tc_factor_ctas(d);
   const long long kblocks = (rows + TC_BK - 1) / TC_BK;
   long long want = (2LL * sm_count() + tiles - 1) / tiles;   // splits wanted
   if (tiles >= sm_count()) want = 1;
@@ -998,9 +1557,14 @@ size_t tc_pad_bytes(const Operand& X, int n) {
 static long long tc_group_chunk(int count, const FactorJob* jobs) {
   long long work = 0;
   for (int i = 0; i < count; ++i)
-    work += (long long)tc_lower_tiles(jobs[i].d) *
+    work += (long long)tc_factor_ctas(jobs[i].d) *
             ((jobs[i].rows + TC_BK - 1) / TC_BK);
-  long long chunk = work / (4LL * sm_count());
+  static const long long waves = [] {
+    const char* e = getenv("KFAC_TC_WAVES");
+    const long long w = e ? atoll(e) : 4;
+    return w > 0 ? w : 4;
+  }();
+  long long chunk = work / (waves * sm_count());
   return chunk < 16 ? 16 : chunk;
 }
 
@@ -1096,15 +1660,18 @@ int run_factor_group_tc(int count, const FactorJob* jobs, void* workspace,
     std::vector<GemmDesc>& v = descs[m];
     if (v.empty()) continue;
     // long-running CTAs first
+    // (duration of a CTA ~ its k-blocks times the operand rows it stages)
     std::stable_sort(v.begin(), v.end(), [](const GemmDesc& a, const GemmDesc& b) {
-      long long ka = a.splits > 1 ? a.k_per_split : a.K;
-      long long kb = b.splits > 1 ? b.k_per_split : b.K;
+      long long ka = (a.splits > 1 ? a.k_per_split : a.K) * std::min(a.M, 512);
+      long long kb = (b.splits > 1 ? b.k_per_split : b.K) * std::min(b.M, 512);
       return ka > kb;
     });
+    const bool pair = tc_use_pair();
     int total = 0;
     for (GemmDesc& g : v) {
       g.tile_begin = total;
-      total += g.ntiles * (g.splits > 1 ? g.splits : 1);
+      total += (pair ? tc_factor_ctas(g.M) : g.ntiles) *
+               (g.splits > 1 ? g.splits : 1);
     }
     bool tails = false;
     for (const GemmDesc& g : v) tails = tails || tc_desc_has_tails(g);
@@ -1121,6 +1688,22 @@ int run_factor_group_tc(int count, const FactorJob* jobs, void* workspace,
       dev_descs = static_cast<const GemmDesc*>(dev);
     }
     const int nd = (int)v.size();
+    if (pair) {
+      if (m == 1 && tails)
+        tc_pair_kernel<true, true><<<total, PK_THREADS, PK_SMEM_BYTES, stream>>>(
+            dev_descs, nd, inl);
+      else if (m == 1)
+        tc_pair_kernel<true, false><<<total, PK_THREADS, PK_SMEM_BYTES, stream>>>(
+            dev_descs, nd, inl);
+      else if (tails)
+        tc_pair_kernel<false, true><<<total, PK_THREADS, PK_SMEM_BYTES, stream>>>(
+            dev_descs, nd, inl);
+      else
+        tc_pair_kernel<false, false><<<total, PK_THREADS, PK_SMEM_BYTES, stream>>>(
+            dev_descs, nd, inl);
+      KFAC_LAUNCH_CHECK("tc_pair_kernel");
+      continue;
+    }
     if (m == 1 && tails)
       tc_gemm_kernel<true, true, TC_PW_IM2COL><<<total, TcMap<TC_PW_IM2COL>::kThreads, TC_SMEM_BYTES, stream>>>(
           dev_descs, nd, inl, 0.f, 0.f);
