@@ -1515,14 +1515,26 @@ static int tc_lower_tiles(int d) {
   return tc_tiles(g);
 }
 
-// Split of one factor's contraction.  `chunk` is the number of k-blocks a CTA
-// should own (>= 16 so that prologue and epilogue stay amortised).
+// Relative duration of one k-block of a CTA of a d x d factor, in 1/512: a
+// CTA stages up to 512 operand rows per k-block, d of them when d <= 256; a
+// k-block with few rows still costs about a memory round trip.
+static long long tc_block_cost(int d) {
+  const int rows = d < 512 ? d : 512;
+  return rows < 256 ? 256 : rows;
+}
+
+// Split of one factor's contraction.  `chunk` is the cost (k-blocks x
+// tc_block_cost) a CTA should own; a CTA keeps at least 16 k-blocks so that
+// prologue and epilogue stay amortised, and a contraction is only cut when
+// that brings its CTAs closer to the target than leaving it whole (partial
+// tiles cost a write, a read and the reduce kernel).
 static TcFactorSplit tc_split_for(long long rows, int d, long long chunk) {
   TcFactorSplit s;
   s.tiles = tc_lower_tiles(d);
+  chunk /= tc_block_cost(d);
   if (chunk < 16) chunk = 16;
   const long long kblocks = (rows + TC_BK - 1) / TC_BK;
-  long long sp = (kblocks + chunk - 1) / chunk;
+  long long sp = (kblocks + chunk / 2) / chunk;
   if (sp < 1) sp = 1;
   long long kps = (kblocks + sp - 1) / sp * TC_BK;
   s.splits = (int)((rows + kps - 1) / kps);
@@ -1538,7 +1550,7 @@ static TcFactorSplit tc_factor_split(long long rows, int d) {
   long long want = (2LL * sm_count() + tiles - 1) / tiles;   // splits wanted
   if (tiles >= sm_count()) want = 1;
   long long chunk = (kblocks + want - 1) / want;
-  return tc_split_for(rows, d, chunk);
+  return tc_split_for(rows, d, chunk * tc_block_cost(d));
 }
 
 size_t tc_factor_workspace_bytes(long long rows, int d) {
@@ -1558,14 +1570,13 @@ static long long tc_group_chunk(int count, const FactorJob* jobs) {
   long long work = 0;
   for (int i = 0; i < count; ++i)
     work += (long long)tc_factor_ctas(jobs[i].d) *
-            ((jobs[i].rows + TC_BK - 1) / TC_BK);
+            ((jobs[i].rows + TC_BK - 1) / TC_BK) * tc_block_cost(jobs[i].d);
   static const long long waves = [] {
     const char* e = getenv("KFAC_TC_WAVES");
     const long long w = e ? atoll(e) : 4;
     return w > 0 ? w : 4;
   }();
-  long long chunk = work / (waves * sm_count());
-  return chunk < 16 ? 16 : chunk;
+  return work / (waves * sm_count());
 }
 
 size_t tc_factor_group_workspace_bytes(int count, const FactorJob* jobs) {
@@ -1581,8 +1592,35 @@ size_t tc_factor_group_workspace_bytes(int count, const FactorJob* jobs) {
   return total;
 }
 
+// Per-device helper stream: the strided and the im2col launch of a grouped
+// factor build do not depend on each other, and each has a tail of CTAs that
+// leaves SMs idle, so they run side by side (fork / join with events).
+struct SideStream {
+  cudaStream_t stream;
+  cudaEvent_t fork, join;
+};
+
+static int tc_side_stream(SideStream** out) {
+  static std::mutex mu;
+  static SideStream side[64];
+  static bool made[64] = {false};
+  int dev = 0;
+  KFAC_CUDA(cudaGetDevice(&dev));
+  KFAC_REQUIRE(dev >= 0 && dev < 64, "device index %d unsupported", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (!made[dev]) {
+    KFAC_CUDA(cudaStreamCreateWithFlags(&side[dev].stream, cudaStreamNonBlocking));
+    KFAC_CUDA(cudaEventCreateWithFlags(&side[dev].fork, cudaEventDisableTiming));
+    KFAC_CUDA(cudaEventCreateWithFlags(&side[dev].join, cudaEventDisableTiming));
+    made[dev] = true;
+  }
+  *out = &side[dev];
+  return KFAC_OK;
+}
+
 int run_factor_group_tc(int count, const FactorJob* jobs, void* workspace,
-                        size_t workspace_bytes, cudaStream_t stream) {
+                        size_t workspace_bytes, cudaStream_t main_stream) {
+  cudaStream_t stream = main_stream;
   int rc = tc_prepare();
   if (rc != KFAC_OK) return rc;
   const size_t need = tc_factor_group_workspace_bytes(count, jobs);
@@ -1656,14 +1694,23 @@ int run_factor_group_tc(int count, const FactorJob* jobs, void* workspace,
     }
     descs[X.mode == 1 ? 1 : 0].push_back(g);
   }
+  SideStream* side = nullptr;
+  if (!descs[0].empty() && !descs[1].empty()) {
+    rc = tc_side_stream(&side);
+    if (rc != KFAC_OK) return rc;
+    KFAC_CUDA(cudaEventRecord(side->fork, main_stream));
+    KFAC_CUDA(cudaStreamWaitEvent(side->stream, side->fork, 0));
+  }
   for (int m = 0; m < 2; ++m) {
     std::vector<GemmDesc>& v = descs[m];
     if (v.empty()) continue;
+    // strided problems on the helper stream when there are both kinds
+    stream = (m == 0 && side != nullptr) ? side->stream : main_stream;
     // long-running CTAs first
     // (duration of a CTA ~ its k-blocks times the operand rows it stages)
     std::stable_sort(v.begin(), v.end(), [](const GemmDesc& a, const GemmDesc& b) {
-      long long ka = (a.splits > 1 ? a.k_per_split : a.K) * std::min(a.M, 512);
-      long long kb = (b.splits > 1 ? b.k_per_split : b.K) * std::min(b.M, 512);
+      long long ka = (a.splits > 1 ? a.k_per_split : a.K) * tc_block_cost(a.M);
+      long long kb = (b.splits > 1 ? b.k_per_split : b.K) * tc_block_cost(b.M);
       return ka > kb;
     });
     const bool pair = tc_use_pair();
@@ -1717,6 +1764,11 @@ int run_factor_group_tc(int count, const FactorJob* jobs, void* workspace,
       tc_gemm_kernel<false, false, TC_PW_STRIDED><<<total, TcMap<TC_PW_STRIDED>::kThreads, TC_SMEM_BYTES,
                                      stream>>>(dev_descs, nd, inl, 0.f, 0.f);
     KFAC_LAUNCH_CHECK("tc_gemm_kernel");
+  }
+  stream = main_stream;
+  if (side != nullptr) {
+    KFAC_CUDA(cudaEventRecord(side->join, side->stream));
+    KFAC_CUDA(cudaStreamWaitEvent(main_stream, side->join, 0));
   }
   if (!reduces.empty()) {
     void* dev = nullptr;
