@@ -306,18 +306,33 @@ class InversePlanSet(object):
             ev.record(st)
         self._early[c] = ev
 
-    def run(self, damping, use_pi=True):
+    def run(self, damping, use_pi=True, after_class=None):
+        """Run every class not started yet and join all of them.
+        ``after_class(c)``, if given, is called on class c's stream right
+        after its plan (its kernels then overlap the other classes'
+        inverses); it must only touch data of that class."""
         cur = torch.cuda.current_stream()
         start = torch.cuda.Event()
         start.record(cur)
-        rest = [p for c, p in enumerate(self.plans) if c not in self._early]
-        for plan, st in zip(rest[1:], self.streams):
+        rest = [c for c in range(len(self.plans)) if c not in self._early]
+        for c, st in zip(rest[1:], self.streams):
             st.wait_event(start)
             with torch.cuda.stream(st):
-                plan.run(damping, use_pi)
+                self.plans[c].run(damping, use_pi)
+                if after_class is not None:
+                    after_class(c)
+        if after_class is not None:
+            for c in self._early:
+                with torch.cuda.stream(self.early_streams[c]):
+                    after_class(c)
+                    ev = torch.cuda.Event()
+                    ev.record(self.early_streams[c])
+                self._early[c] = ev
         if rest:
-            rest[0].run(damping, use_pi)
-        for plan, st in zip(rest[1:], self.streams):
+            self.plans[rest[0]].run(damping, use_pi)
+            if after_class is not None:
+                after_class(rest[0])
+        for c, st in zip(rest[1:], self.streams):
             done = torch.cuda.Event()
             done.record(st)
             cur.wait_event(done)
@@ -346,12 +361,12 @@ class InversePlanSet(object):
             p.close()
 
 
-_precond_ws = Workspace()
+_precond_ws = {}
 
 
 def precondition(G_inv, A_inv, grad_W, grad_b, kf_W=None, kf_b=None,
                  param_W=None, param_b=None, mom_W=None, mom_b=None, lr=0.0,
-                 momentum=0.0):
+                 momentum=0.0, ws_key=None):
     """Grouped kf = G_inv [grad_W, grad_b] A_inv over lists of layers, with
     the optional fused momentum update (see include/kfac_b200.h)."""
     lib = _lib.load()
@@ -369,7 +384,9 @@ def precondition(G_inv, A_inv, grad_W, grad_b, kf_W=None, kf_b=None,
                                for t in lst])
     nbytes = lib.kfac_precond_workspace_bytes(
         count, _lib.int_array(dG), _lib.int_array(dW), _lib.int_array(hb))
-    ws = _precond_ws.get(nbytes, G_inv[0].device)
+    # calls that may overlap on different streams pass different keys
+    ws = _precond_ws.setdefault(ws_key, Workspace()).get(
+        nbytes, G_inv[0].device)
     _lib.check(lib.kfac_precondition(
         count, _lib.int_array(dG), _lib.int_array(dW), ptrs(G_inv),
         ptrs(A_inv), ptrs(grad_W), ptrs(grad_b), ptrs(kf_W), ptrs(kf_b),

@@ -435,9 +435,30 @@ class KFAC(_base.GradientMethod):
         groups = {}
         for fb in fblocks:
             groups.setdefault((fb.damping, fb._pi_type), []).append(fb)
+        done = set()
         for (damping, pi_type), group in groups.items():
             plan = self._plan_for(group)
-            plan.run(damping, pi_type == PI_TYPE_TRACENORM)
+            after = None
+            if len(groups) == 1:
+                # precondition the layers of a size class on that class's
+                # stream as soon as its inverses are done
+                owner = []
+                for fb in group:
+                    owner += [fb] * len(fb.cov_emas)
+                classes = plan.classes()
+
+                def after(c, owner=owner, classes=classes):
+                    part, seen = [], set()
+                    for i in classes[c]:
+                        fb = owner[i]
+                        if id(fb) not in seen and \
+                                isinstance(fb, FB.FisherBlockConnection):
+                            seen.add(id(fb))
+                            part.append(fb)
+                    if part:
+                        self._precondition(part, ws_key=c)
+                        done.update(id(fb) for fb in part)
+            plan.run(damping, pi_type == PI_TYPE_TRACENORM, after_class=after)
             diag = plan.diag
             k = 0
             for fb in group:
@@ -445,7 +466,8 @@ class KFAC(_base.GradientMethod):
                 fb.set_diag_vals(diag[k:k + n])
                 k += n
         conn = [fb for fb in fblocks
-                if isinstance(fb, FB.FisherBlockConnection)]
+                if isinstance(fb, FB.FisherBlockConnection) and
+                id(fb) not in done]
         if conn:
             self._precondition(conn)
         for fb in fblocks:
@@ -458,7 +480,7 @@ class KFAC(_base.GradientMethod):
                 rule.enabled and param._loss_scale is None and
                 not rule._pre_update_hooks and not rule._post_update_hooks)
 
-    def _precondition(self, conn):
+    def _precondition(self, conn, ws_key=None):
         Gi, Ai, gW, gb, kW, kb = [], [], [], [], [], []
         pW, pb, vW, vb = [], [], [], []
         fused_params = []
@@ -490,7 +512,8 @@ class KFAC(_base.GradientMethod):
                 pb.append(None)
                 vb.append(None)
         ops.precondition(Gi, Ai, gW, gb, kW, kb, pW, pb, vW, vb, lr=lr,
-                         momentum=mom if mom is not None else 0.0)
+                         momentum=mom if mom is not None else 0.0,
+                         ws_key=ws_key)
         for p in fused_params:
             p._kfac_applied = True
 
