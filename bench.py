@@ -328,6 +328,8 @@ class DistributedWorkload(DeviceWorkload):
             [self.inv[2 * i + j] for i in own for j in (0, 1)],
             [k ^ 1 for k in range(2 * len(own))],
             [k & 1 for k in range(2 * len(own))], bounds=bounds)
+        self.own_class_layers = [sorted({own[i // 2] for i in idx})
+                                 for idx in self.plan.classes()]
         # size classes over all layers, largest first, as the plan forms them
         key_of = [sum(max(dA, dG) > b for b in bounds)
                   for dA, dG, _, _ in self.dims]
@@ -409,9 +411,23 @@ class DistributedWorkload(DeviceWorkload):
         self.first = False
 
     def inverses(self):
-        self.plan.run(DAMPING, True)
+        self.plan.run(DAMPING, True,
+                      after_class=self.precondition_class if OVERLAP else None)
+
+    def precondition_class(self, c):
+        own = self.own_class_layers[c]
+        self.ops.precondition(
+            [self.inv[2 * i + 1] for i in own], [self.inv[2 * i] for i in own],
+            [self.gW[i] for i in own], [self.gb[i] for i in own], None, None,
+            [self.W[i] for i in own], [self.b[i] for i in own],
+            [self.vW[i] for i in own], [self.vb[i] for i in own], lr=LR,
+            momentum=MOMENTUM, ws_key=c)
 
     def precondition(self):
+        if OVERLAP:
+            # owned layers were updated per size class inside inverses()
+            self.comm.all_gather_v_arrays(self.ag_arrays)
+            return
         own = self.mine
         self.ops.precondition(
             [self.inv[2 * i + 1] for i in own], [self.inv[2 * i] for i in own],
