@@ -40,6 +40,9 @@ DAMPING = 2.5e-4
 LR = 0.01
 MOMENTUM = 0.9
 WORKLOAD = 'resnet50_kfac_step_b32_224'
+# DRAM traffic of one factor measured with ncu (profiles/), bytes: measured,
+# algorithmic (padded input once + factor written once)
+TRAFFIC_CASE = (None, None)
 COMMUNICATOR = 'peer_memory'   # or 'pure_nccl' (NCCL reduce / broadcast)
 OVERLAP = True           # start the largest factors' inverse during the factor build
 OWNERSHIP = 'balanced'   # layer ownership at N > 1 ('reference': by count)
@@ -572,25 +575,27 @@ def run_ours(args):
             'factor_inverse_ms': float(phase[0] + phase[1]),
             'roofline': {
                 'bound': 'tensor',
-                'kernel': 'tc_gemm_kernel (factor stage: two grouped launches '
-                          'over all 108 factors, plus split reduce)',
+                'kernel': 'tc_pair_kernel (factor stage: grouped strided and '
+                          'im2col launches over all 108 factors, plus pad '
+                          'copies and split reduce)',
                 'achieved': achieved, 'peak': peaks['tflops'],
                 'unit': 'TFLOP/s', 'frac': achieved / peaks['tflops'],
                 'peak_source': 'of %s: dense bf16 sustained from '
-                               'MEASURED_PEAKS.json (it has no tf32 figure)'
-                               % peaks['source'],
+                               'MEASURED_PEAKS.json' % peaks['source'],
+                # fp32 operands are split into two bf16 terms: three MMAs per
+                # algorithmic product, so a third of the bf16 rate is the
+                # ceiling of this scheme
+                'frac_of_split_bf16_ceiling': achieved / (peaks['tflops'] / 3.0),
+                # the inverse and precondition products run as split TF32
                 'tf32_tflops_measured_here': tf32,
-                'frac_of_tf32': achieved / tf32,
-                'frac_of_split_tf32_ceiling': achieved / (tf32 / 3.0),
                 'step_tflops': float(sum(flops.values()) /
                                      (ms_per_step * 1e-3) / 1e12),
                 # full-size launches are too large for a multi-pass capture;
-                # see profiles/tc_gemm_dense_rows8192_d4608.md for the DRAM
-                # traffic of one factor measured on a smaller case
+                # profiles/ holds DRAM traffic of single factors
                 'traffic': None,
-                'traffic_case': {'case': 'dense_rows8192_d4608',
-                                 'dram_bytes': 4.706e8,
-                                 'algorithmic_bytes': 2.359e8}},
+                'traffic_case': {'case': 'conv3x3_c256_hw14 (tc_pair_kernel)',
+                                 'dram_bytes': TRAFFIC_CASE[0],
+                                 'algorithmic_bytes': TRAFFIC_CASE[1]}},
             'cpu_baseline': cpu,
             'gpu_launches': int(launches),
             'clocks': clocks,

@@ -13,6 +13,10 @@
 // shared memory and writes rows (and, for symmetric outputs, mirrored columns)
 // with coalesced stores.  Every barrier wait is bounded; a wait that runs out
 // raises a status word instead of hanging.
+//
+// Factor builds (X^T X) have their own kernel further down, tc_pair_kernel:
+// 256 x 256 tiles, operands split into two bf16 terms (kind::f16 MMAs), the
+// im2col gather laid out with lanes along k.
 #include <algorithm>
 #include <mutex>
 #include <vector>
