@@ -1047,7 +1047,8 @@ tc_pair_kernel(const GemmDesc* __restrict__ descs, int ndesc,
       const int chw = X.C * X.H * X.W, sw = X.st * X.W;
       const unsigned lane_off = (unsigned)((((kp >> 2) ^ (warp & 3)) << 4) +
                                            4 * (kp & 3) + h * 64 + warp * 128);
-      const unsigned smem_base = smem_u32(smem);
+      // offset of the 1024-byte-aligned stage area inside the dynamic array
+      const unsigned smem_skew = smem_u32(smem) - smem_u32(tc_smem_raw);
       const int j0 = share ? 8 : 0;
       float x[32];
       for (int kb = 0; kb <= nkb; ++kb) {
@@ -1059,17 +1060,17 @@ tc_pair_kernel(const GemmDesc* __restrict__ descs, int ndesc,
                            &ctl->abort_flag))
               break;
           }
-          const unsigned st = smem_base + s * PK_STAGE_BYTES + lane_off;
+          // plain stores through a pointer into the shared array: the
+          // per-row offsets (2048 j) fold into the instruction's immediate
+          unsigned* st = reinterpret_cast<unsigned*>(
+              tc_smem_raw + smem_skew + s * PK_STAGE_BYTES + lane_off);
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             if (j < j0) continue;
             unsigned hi, lo;
             split_bf16x2(x[2 * j], x[2 * j + 1], hi, lo);
-            asm volatile("st.shared.b32 [%0], %1;" ::"r"(st + 2048 * j), "r"(hi)
-                         : "memory");
-            asm volatile("st.shared.b32 [%0], %1;"
-                         ::"r"(st + PK_LO_OFF + 2048 * j), "r"(lo)
-                         : "memory");
+            st[512 * j] = hi;
+            st[PK_LO_OFF / 4 + 512 * j] = lo;
           }
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           __syncwarp();

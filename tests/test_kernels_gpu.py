@@ -91,7 +91,10 @@ def test_factor_conv_golden(ops, golden, name):
 @pytest.mark.parametrize('rows,d,bias', [
     (32, 10, False), (128, 27, True), (128, 784, True), (128, 1000, True),
     (5000, 64, False), (40000, 147, True), (3000, 513, False), (1, 5, True),
-    (17, 129, True), (2049, 300, False)])
+    (17, 129, True), (2049, 300, False),
+    # 256-row tile pairs: odd number of 128-row blocks with a bias column and
+    # a cut contraction; six 256-row blocks, the last with 20 rows
+    (70000, 600, True), (6272, 1300, False)])
 def test_factor_dense_sweep(ops, rows, d, bias):
     rng = np.random.default_rng(rows * 131 + d)
     x = np.maximum(rng.standard_normal((rows, d)), 0).astype(np.float32)
