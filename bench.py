@@ -131,9 +131,13 @@ class ClockSampler(object):
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.perf_counter(), line.strip()))
 
-    def stop(self):
+    def stop(self, t0=None, t1=None):
+        """Summary of the samples read between host times t0 and t1 (the
+        timed region); the sampler is started before the warm-up steps, which
+        run the same work, and their samples are used (and said so) when the
+        timed region was too short to catch one."""
         if self.proc is None:
             return dict(sm_mhz=None, sm_max_mhz=None, reasons=['unsampled'])
         self.proc.terminate()
@@ -144,7 +148,13 @@ class ClockSampler(object):
         sm, smax, reasons = [], [], set()
         names = ['hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown',
                  'sw_power_cap']
-        for line in self.lines:
+        window = 'timed region'
+        lines = [l for ts, l in self.lines
+                 if t0 is None or (t0 <= ts <= t1)]
+        if not lines:
+            window = 'warm-up and timed region'
+            lines = [l for ts, l in self.lines if t1 is None or ts <= t1]
+        for line in lines:
             parts = [p.strip() for p in line.split(',')]
             if len(parts) < 7:
                 continue
@@ -159,7 +169,7 @@ class ClockSampler(object):
         if not sm:
             return dict(sm_mhz=None, sm_max_mhz=None, reasons=['unsampled'])
         return dict(sm_mhz=float(np.median(sm)), sm_max_mhz=float(max(smax)),
-                    samples=len(sm), reasons=sorted(reasons))
+                    samples=len(sm), window=window, reasons=sorted(reasons))
 
 
 # ------------------------------------------------------------- GPU workload
@@ -471,24 +481,26 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
     for _ in range(max(args.warmup, 3)):
         wl.step()
     barrier()
 
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)]
           for _ in range(args.steps)]
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
     launches0 = lib.kfac_launch_count()
     barrier()
+    t_begin = time.perf_counter()
     for s in range(args.steps):
         ev[s][0].record()
         wl.step(ev[s])
         ev[s][3].record()
     barrier()
+    t_end = time.perf_counter()
     launches = lib.kfac_launch_count() - launches0
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop(t_begin, t_end) if rank == 0 else None
 
     total_ms = ev[0][0].elapsed_time(ev[-1][3])
     phase = np.zeros(3)
