@@ -42,7 +42,7 @@ MOMENTUM = 0.9
 WORKLOAD = 'resnet50_kfac_step_b32_224'
 # DRAM traffic of one factor measured with ncu (profiles/), bytes: measured,
 # algorithmic (padded input once + factor written once)
-TRAFFIC_CASE = (None, None)
+TRAFFIC_CASE = (33.9e6, 8.2e6 + 21.2e6)
 COMMUNICATOR = 'peer_memory'   # or 'pure_nccl' (NCCL reduce / broadcast)
 OVERLAP = True           # start the largest factors' inverse during the factor build
 OWNERSHIP = 'balanced'   # layer ownership at N > 1 ('reference': by count)

@@ -1,9 +1,9 @@
 """Generate the golden vectors under tests/golden/ by EXECUTING the reference.
 
-Run once, in a container that has the chainerkfac sources (default
-``/root/reference``; override with ``CHAINERKFAC_SRC``):
+Run once, where a checkout of the chainerkfac sources is available, with its
+location in ``CHAINERKFAC_SRC`` (the directory that holds ``chainerkfac/``):
 
-    python tests/golden/make_golden.py
+    CHAINERKFAC_SRC=<checkout> python tests/golden/make_golden.py
 
 The reference's NumPy (``--no_cuda``) arithmetic is imported unmodified and run
 on seeded inputs.  Chainer, CuPy and ChainerMN are not installed, so a small
@@ -29,7 +29,9 @@ ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
 from oracle import kfac_oracle as orc  # noqa: E402
 
-SRC = os.environ.get('CHAINERKFAC_SRC', '/root/reference')
+SRC = os.environ.get('CHAINERKFAC_SRC')
+if not SRC or not os.path.isdir(os.path.join(SRC, 'chainerkfac')):
+    raise SystemExit('set CHAINERKFAC_SRC to a checkout of chainerkfac')
 
 
 # ---------------------------------------------------------------- stand-ins

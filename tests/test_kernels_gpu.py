@@ -545,7 +545,7 @@ def test_config1_mlp_shapes_step(ops):
         # to be within cond * u (u = 2^-24) of the exact one: cuSOLVER-class
         # fp32 code (torch.linalg.inv) is at 6e-5 to 1.2e-4 on these matrices,
         # while the NumPy path that produced the oracle is at 4e-7.  Each
-        # inverse is therefore judged against the fp64 inverse with the
+        # inverse is therefore compared with the fp64 inverse under the
         # stated bound or cond * u, whichever is larger.
         for j, key, diag in ((0, 'A_inv', 'diag_A'), (1, 'G_inv', 'diag_G')):
             f64 = host(F[2 * i + j]).astype(np.float64)
