@@ -125,22 +125,31 @@ __global__ void damp_copy_kernel(const MatInfo* __restrict__ mats,
 // Factor one diagonal block (<= 128 x 128) of W and invert the resulting
 // triangle: W_jj <- L_jj (lower), X_jj <- L_jj^-1 (lower, upper part zero).
 // One CTA of 256 threads per matrix that still has a block at `step`; thread
-// (br, bc) = (tid % 16, tid / 16) keeps the 8 x 8 block (br, bc) in registers.
-// Both sweeps go column by column with one barrier per column: the column of
-// L (Cholesky) or the finished row of X (inverse) is broadcast through a
-// double-buffered line of shared memory and every thread applies the rank-1
-// update to its register block.
+// (br, bc) = (tid / 16, tid % 16) keeps the 8 x 8 block (br, bc) in registers
+// (consecutive lanes hold consecutive column blocks, so that rows of W and X
+// are read and written as contiguous 32-byte pieces).
+// Both sweeps advance by block columns of 8 with two barriers (Cholesky) or
+// one (inverse) per block column instead of one per column:
+//   Cholesky, block column kb: thread (kb, kb) factors its 8 x 8 block and
+//   inverts the small triangle, all in registers; the threads below multiply
+//   their blocks by that inverse (panel solve); every remaining block takes
+//   a rank-8 update from the panel, read from shared memory.
+//   Inverse, block row kb: the threads of block row kb apply the stored 8 x 8
+//   inverse to their blocks of the running right-hand side (rows kb of X are
+//   then final); the rows below take a rank-8 update.
 __global__ void __launch_bounds__(256)
 chol_diag_kernel(const MatInfo* __restrict__ mats, const int* __restrict__ ids,
                  int step, int* __restrict__ info) {
   extern __shared__ __align__(16) float dsm[];
   float (*Lt)[DB + 4] = reinterpret_cast<float (*)[DB + 4]>(dsm);  // L^T
-  float (*line)[DB] = reinterpret_cast<float (*)[DB]>(dsm + DB * (DB + 4));
-  float* rdiag = dsm + DB * (DB + 4) + 2 * DB;
+  float (*Pt)[DB] = reinterpret_cast<float (*)[DB]>(dsm + DB * (DB + 4));
+  float (*Xr)[8][DB] =
+      reinterpret_cast<float (*)[8][DB]>(dsm + DB * (DB + 4) + 8 * DB);
+  float (*Tk)[64] =
+      reinterpret_cast<float (*)[64]>(dsm + DB * (DB + 4) + 24 * DB);
   const int id = ids[blockIdx.x];
   const MatInfo mi = mats[id];
-  const int tid = threadIdx.x, br = tid & 15, bc = tid >> 4;
-  const int lane = tid & 31;
+  const int tid = threadIdx.x, br = tid >> 4, bc = tid & 15;
   const int o = step * DB;
   const int bs = min(DB, mi.d - o);
   const int nkb = (bs + 7) >> 3;
@@ -148,62 +157,120 @@ chol_diag_kernel(const MatInfo* __restrict__ mats, const int* __restrict__ ids,
   float* Wd = mi.W + (long long)o * ld + o;
   float* Xd = mi.X + (long long)o * ld + o;
 
+  // blocks strictly below the diagonal move as two 16-byte pieces per row
+  const bool vec = (ld & 3) == 0 && (o & 3) == 0 &&
+                   ((reinterpret_cast<uintptr_t>(mi.W) |
+                     reinterpret_cast<uintptr_t>(mi.X)) & 15) == 0;
   float a[8][8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const int gi = 8 * br + i;
+    if (vec && bc < br && gi < bs) {
+      const float4 v0 = *reinterpret_cast<const float4*>(&Wd[gi * ld + 8 * bc]);
+      const float4 v1 = *reinterpret_cast<const float4*>(&Wd[gi * ld + 8 * bc + 4]);
+      a[i][0] = v0.x; a[i][1] = v0.y; a[i][2] = v0.z; a[i][3] = v0.w;
+      a[i][4] = v1.x; a[i][5] = v1.y; a[i][6] = v1.z; a[i][7] = v1.w;
+    } else {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int gj = 8 * bc + j;
-      float v = (gi == gj) ? 1.f : 0.f;          // identity beyond the block
-      if (gi < bs && gj <= gi) v = Wd[gi * ld + gj];
-      a[i][j] = v;
+      for (int j = 0; j < 8; ++j) {
+        const int gj = 8 * bc + j;
+        float v = (gi == gj) ? 1.f : 0.f;        // identity beyond the block
+        if (gi < bs && gj <= gi) v = Wd[gi * ld + gj];
+        a[i][j] = v;
+      }
     }
   }
 
-  // ---- Cholesky, right-looking, one column per barrier
-  int buf = 0;
+  // ---- Cholesky by block columns
   for (int kb = 0; kb < nkb; ++kb) {
+    if (br == kb && bc == kb) {
+      // 8 x 8 Cholesky in registers; rl[c] = 1 / l_cc
+      float rl[8];
 #pragma unroll
-    for (int lk = 0; lk < 8; ++lk) {
-      const int k = 8 * kb + lk;
-      // the pivot lives in thread (kb, kb) of the half-warp that owns block
-      // column kb; every lane takes part in the shuffle
-      float piv = __shfl_sync(0xffffffffu, a[lk][lk], (lane & 16) | kb);
-      if (bc == kb) {
+      for (int c = 0; c < 8; ++c) {
+        float piv = a[c][c];
         if (!(piv > 0.f)) {
-          if (br == kb) atomicCAS(&info[id], 0, o + k + 1);
+          atomicCAS(&info[id], 0, o + 8 * kb + c + 1);
           piv = 1.f;
         }
-        // rsqrt + one Newton step: full fp32 accuracy without the slow
-        // IEEE square root and division on the per-column critical path
-        float rl = rsqrtf(piv);
-        rl = rl * (1.5f - 0.5f * piv * rl * rl);
-        const float l = piv * rl;
-        if (br == kb) rdiag[k] = rl;
+        // rsqrt + one Newton step: full fp32 accuracy without the slow IEEE
+        // square root and division
+        float r = rsqrtf(piv);
+        r = r * (1.5f - 0.5f * piv * r * r);
+        rl[c] = r;
+        a[c][c] = piv * r;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int gi = 8 * br + i;
-          float v = 0.f;
-          if (gi > k) { v = a[i][lk] * rl; a[i][lk] = v; }
-          else if (gi == k) a[i][lk] = l;
-          line[buf][gi] = v;                       // strictly below the pivot
+        for (int i = c + 1; i < 8; ++i) a[i][c] *= r;
+#pragma unroll
+        for (int j = c + 1; j < 8; ++j)
+#pragma unroll
+          for (int i = j; i < 8; ++i) a[i][j] = fmaf(-a[i][c], a[j][c], a[i][j]);
+      }
+      // T = L_kk^-1 (lower), column by column: T[c][c] = rl[c],
+      // T[i][c] = -rl[i] * sum_{m=c}^{i-1} L[i][m] T[m][c]
+      float t[8][8];
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        t[c][c] = rl[c];
+#pragma unroll
+        for (int i = c + 1; i < 8; ++i) {
+          float acc = 0.f;
+#pragma unroll
+          for (int m = c; m < i; ++m) acc = fmaf(a[i][m], t[m][c], acc);
+          t[i][c] = -rl[i] * acc;
         }
       }
-      __syncthreads();
-      if (br >= kb && bc >= kb && bc <= br) {
-        const float4 r0 = *reinterpret_cast<const float4*>(&line[buf][8 * br]);
-        const float4 r1 = *reinterpret_cast<const float4*>(&line[buf][8 * br + 4]);
-        const float4 c0 = *reinterpret_cast<const float4*>(&line[buf][8 * bc]);
-        const float4 c1 = *reinterpret_cast<const float4*>(&line[buf][8 * bc + 4]);
-        const float cr[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
-        const float cc[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) Tk[kb][8 * i + j] = (j <= i) ? t[i][j] : 0.f;
+    }
+    __syncthreads();
+    if (bc == kb && br > kb) {
+      // panel solve: L_blk = A_blk T^T, L[i][c] = sum_{m<=c} A[i][m] T[c][m]
+      float t[8][8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float4 t0 = *reinterpret_cast<const float4*>(&Tk[kb][8 * i]);
+        const float4 t1 = *reinterpret_cast<const float4*>(&Tk[kb][8 * i + 4]);
+        t[i][0] = t0.x; t[i][1] = t0.y; t[i][2] = t0.z; t[i][3] = t0.w;
+        t[i][4] = t1.x; t[i][5] = t1.y; t[i][6] = t1.z; t[i][7] = t1.w;
+      }
+      float l[8][8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          float acc = 0.f;
+#pragma unroll
+          for (int m = 0; m <= c; ++m) acc = fmaf(a[i][m], t[c][m], acc);
+          l[i][c] = acc;
+        }
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        *reinterpret_cast<float4*>(&Pt[c][8 * br]) =
+            make_float4(l[0][c], l[1][c], l[2][c], l[3][c]);
+        *reinterpret_cast<float4*>(&Pt[c][8 * br + 4]) =
+            make_float4(l[4][c], l[5][c], l[6][c], l[7][c]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) a[i][c] = l[i][c];
+      }
+    }
+    __syncthreads();
+    if (bc > kb && bc <= br) {
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const float4 r0 = *reinterpret_cast<const float4*>(&Pt[c][8 * br]);
+        const float4 r1 = *reinterpret_cast<const float4*>(&Pt[c][8 * br + 4]);
+        const float4 c0 = *reinterpret_cast<const float4*>(&Pt[c][8 * bc]);
+        const float4 c1 = *reinterpret_cast<const float4*>(&Pt[c][8 * bc + 4]);
+        const float pr[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+        const float pc[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
 #pragma unroll
         for (int i = 0; i < 8; ++i)
 #pragma unroll
-          for (int j = 0; j < 8; ++j) a[i][j] = fmaf(-cr[i], cc[j], a[i][j]);
+          for (int j = 0; j < 8; ++j) a[i][j] = fmaf(-pr[i], pc[j], a[i][j]);
       }
-      buf ^= 1;
     }
   }
 
@@ -211,10 +278,17 @@ chol_diag_kernel(const MatInfo* __restrict__ mats, const int* __restrict__ ids,
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const int gi = 8 * br + i;
+    if (vec && bc < br && gi < bs) {
+      *reinterpret_cast<float4*>(&Wd[gi * ld + 8 * bc]) =
+          make_float4(a[i][0], a[i][1], a[i][2], a[i][3]);
+      *reinterpret_cast<float4*>(&Wd[gi * ld + 8 * bc + 4]) =
+          make_float4(a[i][4], a[i][5], a[i][6], a[i][7]);
+    } else {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int gj = 8 * bc + j;
-      if (gi < bs && gj <= gi) Wd[gi * ld + gj] = a[i][j];
+      for (int j = 0; j < 8; ++j) {
+        const int gj = 8 * bc + j;
+        if (gi < bs && gj <= gi) Wd[gi * ld + gj] = a[i][j];
+      }
     }
   }
 #pragma unroll
@@ -226,55 +300,84 @@ chol_diag_kernel(const MatInfo* __restrict__ mats, const int* __restrict__ ids,
     *reinterpret_cast<float4*>(&Lt[gj][8 * br]) = make_float4(v[0], v[1], v[2], v[3]);
     *reinterpret_cast<float4*>(&Lt[gj][8 * br + 4]) = make_float4(v[4], v[5], v[6], v[7]);
   }
-  // ---- inverse of the triangle: X starts as I; at column k row k is final
-  // after scaling by 1 / l_kk, and every row below subtracts L[i][k] * X[k][:]
+  // ---- inverse of the triangle by block rows: R starts as I; the rows of
+  // block kb become X = T_kb R, every block row below subtracts L_blk X
 #pragma unroll
   for (int i = 0; i < 8; ++i)
 #pragma unroll
     for (int j = 0; j < 8; ++j) a[i][j] = (8 * br + i == 8 * bc + j) ? 1.f : 0.f;
   __syncthreads();
   for (int kb = 0; kb < nkb; ++kb) {
+    const int buf = kb & 1;
+    if (br == kb && bc <= kb) {
+      float t[8][8];
 #pragma unroll
-    for (int lk = 0; lk < 8; ++lk) {
-      const int k = 8 * kb + lk;
-      if (br == kb) {
-        const float rl = rdiag[k];
+      for (int i = 0; i < 8; ++i) {
+        const float4 t0 = *reinterpret_cast<const float4*>(&Tk[kb][8 * i]);
+        const float4 t1 = *reinterpret_cast<const float4*>(&Tk[kb][8 * i + 4]);
+        t[i][0] = t0.x; t[i][1] = t0.y; t[i][2] = t0.z; t[i][3] = t0.w;
+        t[i][4] = t1.x; t[i][5] = t1.y; t[i][6] = t1.z; t[i][7] = t1.w;
+      }
+      float x[8][8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          const int gj = 8 * bc + j;
-          float v = 0.f;
-          if (gj <= k) { v = a[lk][j] * rl; a[lk][j] = v; }
-          line[buf][gj] = v;
+          float acc = 0.f;
+#pragma unroll
+          for (int m = 0; m <= i; ++m) acc = fmaf(t[i][m], a[m][j], acc);
+          x[i][j] = acc;
         }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        *reinterpret_cast<float4*>(&Xr[buf][i][8 * bc]) =
+            make_float4(x[i][0], x[i][1], x[i][2], x[i][3]);
+        *reinterpret_cast<float4*>(&Xr[buf][i][8 * bc + 4]) =
+            make_float4(x[i][4], x[i][5], x[i][6], x[i][7]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) a[i][j] = x[i][j];
       }
-      __syncthreads();
-      if (br >= kb && bc <= kb) {
-        const float4 x0 = *reinterpret_cast<const float4*>(&line[buf][8 * bc]);
-        const float4 x1 = *reinterpret_cast<const float4*>(&line[buf][8 * bc + 4]);
-        const float4 l0 = *reinterpret_cast<const float4*>(&Lt[k][8 * br]);
-        const float4 l1 = *reinterpret_cast<const float4*>(&Lt[k][8 * br + 4]);
-        const float xr[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+    }
+    __syncthreads();
+    if (br > kb && bc <= kb) {
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const float4 l0 = *reinterpret_cast<const float4*>(&Lt[8 * kb + c][8 * br]);
+        const float4 l1 = *reinterpret_cast<const float4*>(&Lt[8 * kb + c][8 * br + 4]);
+        const float4 x0 = *reinterpret_cast<const float4*>(&Xr[buf][c][8 * bc]);
+        const float4 x1 = *reinterpret_cast<const float4*>(&Xr[buf][c][8 * bc + 4]);
         const float lc[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
+        const float xr[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
 #pragma unroll
         for (int i = 0; i < 8; ++i)
 #pragma unroll
           for (int j = 0; j < 8; ++j) a[i][j] = fmaf(-lc[i], xr[j], a[i][j]);
       }
-      buf ^= 1;
     }
   }
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const int gi = 8 * br + i;
+    if (vec && bc != br && gi < bs && 8 * bc + 7 < bs) {
+      const bool low = bc < br;
+      *reinterpret_cast<float4*>(&Xd[gi * ld + 8 * bc]) =
+          low ? make_float4(a[i][0], a[i][1], a[i][2], a[i][3])
+              : make_float4(0.f, 0.f, 0.f, 0.f);
+      *reinterpret_cast<float4*>(&Xd[gi * ld + 8 * bc + 4]) =
+          low ? make_float4(a[i][4], a[i][5], a[i][6], a[i][7])
+              : make_float4(0.f, 0.f, 0.f, 0.f);
+    } else {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int gj = 8 * bc + j;
-      if (gi < bs && gj < bs) Xd[gi * ld + gj] = (gj <= gi) ? a[i][j] : 0.f;
+      for (int j = 0; j < 8; ++j) {
+        const int gj = 8 * bc + j;
+        if (gi < bs && gj < bs) Xd[gi * ld + gj] = (gj <= gi) ? a[i][j] : 0.f;
+      }
     }
   }
 }
 
-constexpr size_t kDiagSmemBytes = (DB * (DB + 4) + 3 * DB) * sizeof(float);
+constexpr size_t kDiagSmemBytes =
+    (DB * (DB + 4) + 24 * DB + 16 * 64) * sizeof(float);   // Lt, Pt, Xr, Tk
 
 struct Launch {
   int tails;     // grouped gemm: some contraction is not a multiple of 32
