@@ -213,6 +213,7 @@ class KFAC(_base.GradientMethod):
         # backward instead of one launch per hook call (same values)
         self.group_factors = True
         self._factors_pending = False
+        self._emas_done = False
         self._plans = {}
         self.observation = {}
 
@@ -428,6 +429,8 @@ class KFAC(_base.GradientMethod):
             self._factors_pending = False
             plan = self._plan_for(fblocks)
             self._pipelined_factors_and_emas(fblocks, plan)
+        elif self._emas_done:
+            self._emas_done = False      # a pipelined exchange already did it
         else:
             for fblock in fblocks:
                 fblock.update_cov_emas()
@@ -546,6 +549,8 @@ class DistributedKFAC(KFAC):
         self.constructor_kwargs['communicate_after_forward'] = \
             communicate_after_forward
         self.communicate_after_forward = communicate_after_forward
+        self._real_updates = 0
+        self._exchange_stream = None
 
     def setup(self, link):
         super(DistributedKFAC, self).setup(link)
@@ -572,8 +577,74 @@ class DistributedKFAC(KFAC):
         if self.is_changed(self.target):
             self.comm.bcast_data(self.target)
         else:
-            self.reduce_scatter_v_after_backward()
+            if self._factors_pending:
+                self._factors_pending = False
+                self._pipelined_exchange()
+                self._emas_done = True
+            else:
+                self.reduce_scatter_v_after_backward()
             super(DistributedKFAC, self).update()
+            self._real_updates += 1
+
+    def _pipeline_ready(self):
+        """Whether this step builds, exchanges and averages the factors size
+        class by size class (largest first) and starts the owners' inverses
+        of a class while the next class is built and exchanged.  The answer
+        only depends on state that is the same on every rank: the ranks must
+        issue the same sequence of collectives."""
+        return (self._real_updates >= 1 and
+                not self.communicate_after_forward and
+                self.acc_iters == 1 and self.group_factors and
+                all(len(ix) > 0 for ix in self.indices) and
+                len({(fb.damping, fb._pi_type) for fb in self.fblocks}) == 1)
+
+    def _pipelined_exchange(self):
+        plan = self._plan_for(self.local_fblocks)
+        bounds = plan.bounds
+
+        def key_of(fb):
+            # covs exist on every rank from the first full update on
+            d = max(int(c.shape[0]) for c in fb.covs)
+            return sum(d > b for b in bounds)
+        keys = [key_of(fb) for fb in self.fblocks]
+        dev = next(self.target.params()).data.device
+        main = torch.cuda.current_stream()
+        if self._exchange_stream is None:
+            self._exchange_stream = torch.cuda.Stream(priority=-1)
+        side = self._exchange_stream
+        local = set(self.local_indices)
+        first = self.local_fblocks[0]
+        order = sorted(set(keys), reverse=True)
+        for n, key in enumerate(order):
+            members = [i for i, k in enumerate(keys) if k == key]
+            items = []
+            for i in members:
+                fb = self.fblocks[i]
+                if isinstance(fb, FB.FisherBlockConnection):
+                    items += fb.flush_items()
+            if items:
+                ops.factor_group(items, dev)
+            built = torch.cuda.Event()
+            built.record(main)
+            side.wait_event(built)
+            with torch.cuda.stream(side):
+                member_set = set(members)
+                arrays = extract(
+                    self.fblocks,
+                    [[i for i in ix if i in member_set] for ix in self.indices],
+                    lambda block: block.extract_for_reduce_scatter_v())
+                self.comm.reduce_scatter_v_arrays(arrays)
+                for i in members:
+                    if i in local:
+                        self.fblocks[i].update_cov_emas()
+                if n + 1 < len(order) and key in plan.class_keys:
+                    plan.start_class(plan.class_keys.index(key), first.damping,
+                                     first._pi_type == PI_TYPE_TRACENORM)
+        done = torch.cuda.Event()
+        done.record(side)
+        main.wait_event(done)
+        for fb in self.fblocks:
+            fb._keep_x = fb._keep_gy = None
 
     def reduce_scatter_v_after_forward(self):
         if not self.communicate_after_forward:

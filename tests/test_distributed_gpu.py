@@ -81,6 +81,14 @@ for pic, early, own, cname in (
     assert opt.t == 0
     opt.update(lossfun, xs, ts)
     assert opt.t == 1
+    # further steps take the pipelined exchange (size class by size class)
+    # when the configuration allows it
+    steps = 3 if not early else 1
+    for _ in range(steps - 1):
+        opt.update(lossfun, xs, ts)
+    assert opt._real_updates == steps
+    if not early:
+        assert opt._pipeline_ready()
     # every rank holds the same weights afterwards
     flat = torch.cat([p.detach().reshape(-1) for p in model.parameters()])
     other = [torch.empty_like(flat) for _ in range(world)]
@@ -93,7 +101,8 @@ for pic, early, own, cname in (
         ref = make()
         o1 = ck.KFAC(lr=0.05, momentum=0.9, cov_ema_decay=1.0, damping=1e-2)
         o1.setup(ref)
-        o1.update(lambda a, b: F.cross_entropy(ref(a), b), X, T)
+        for _ in range(steps):
+            o1.update(lambda a, b: F.cross_entropy(ref(a), b), X, T)
         for (n1, p1), (n2, p2) in zip(ref.named_parameters(),
                                       model.named_parameters()):
             err = float((p1 - p2).norm() / p1.norm())
@@ -109,7 +118,9 @@ dist.destroy_process_group()
 def test_distributed_kfac_two_gpus(tmp_path):
     script = tmp_path / 'worker.py'
     script.write_text(WORKER % {'root': ROOT})
-    env = dict(os.environ, NCCL_NVLS_ENABLE='0')
+    # small class bounds: the three layers fall into three size classes, so
+    # the pipelined exchange runs one collective per class
+    env = dict(os.environ, NCCL_NVLS_ENABLE='0', KFAC_CLASS_BOUNDS='20,40')
     res = subprocess.run(
         [sys.executable, '-m', 'torch.distributed.run', '--nnodes=1',
          '--nproc-per-node=2', '--master-addr', '127.0.0.1', '--master-port',
