@@ -56,7 +56,8 @@ class ResNet50(nn.Module):
 
 def build_training_step(device, batch, world, rank, cov_ema_decay, damping,
                         lr, momentum, image=224, classes=1000,
-                        bn_blocks=False, communicator='peer_memory'):
+                        bn_blocks=False, communicator='peer_memory',
+                        channels_last=True):
     """Returns (step, h2d_bytes, d2h_bytes).  ``step()`` copies one pinned
     host batch to the device, runs ``optimizer.update(lossfun, x, t)``
     (forward, backward, K-FAC factors / inverses / preconditioned update) and
@@ -79,7 +80,13 @@ def build_training_step(device, batch, world, rank, cov_ema_decay, damping,
     opt.setup(model)
 
     g = torch.Generator().manual_seed(99 + rank)
-    hx = torch.randn((batch, 3, image, image), generator=g).pin_memory()
+    hx = torch.randn((batch, 3, image, image), generator=g)
+    if channels_last:
+        # channels-last activations (weights keep their layout): cuDNN's NHWC
+        # kernels run the model, and the factor builds read the (n*h*w, c)
+        # activations and gradients in place
+        hx = hx.contiguous(memory_format=torch.channels_last)
+    hx = hx.pin_memory()
     ht = torch.randint(0, classes, (batch,), generator=g).pin_memory()
     hloss = torch.empty((), dtype=torch.float32).pin_memory()
 
@@ -88,6 +95,8 @@ def build_training_step(device, batch, world, rank, cov_ema_decay, damping,
 
     def step():
         x = hx.to(device, non_blocking=True)
+        if channels_last:
+            x = x.contiguous(memory_format=torch.channels_last)
         t = ht.to(device, non_blocking=True)
         opt.update(lossfun, x, t)
         hloss.copy_(opt.loss, non_blocking=True)

@@ -50,6 +50,24 @@ class Workspace(object):
 
 _factor_ws = Workspace()
 
+def _is_nhwc(t):
+    """4-D tensor stored channels-last (and not also plain NCHW-contiguous)."""
+    return (t.dim() == 4 and not t.is_contiguous() and
+            t.is_contiguous(memory_format=torch.channels_last))
+
+
+def _nhwc_rows(t):
+    """(n*h*w, c) view of a channels-last tensor: no copy."""
+    n, c, h, w = t.shape
+    return t.permute(0, 2, 3, 1).reshape(n * h * w, c)
+
+
+def _conv_input_as_dense(x, ksize, stride, pad):
+    """A channels-last input of a 1x1, stride-1, unpadded convolution is its
+    own patch matrix."""
+    return _is_nhwc(x) and ksize == 1 and stride == 1 and pad == 0
+
+
 
 def _factor_out(d, out, beta, device):
     if out is None:
@@ -79,8 +97,14 @@ def factor_dense(x, add_ones_col=False, alpha=1.0, beta=0.0, out=None):
 
 def factor_conv_input(x, ksize, stride, pad, add_ones_col=False, alpha=1.0,
                       beta=0.0, out=None):
-    """out = alpha * P^T P + beta * out, P the im2col patches of NCHW ``x``."""
+    """out = alpha * P^T P + beta * out, P the im2col patches of ``x`` (NCHW;
+    a channels-last tensor is read in place when it is its own patch matrix
+    and copied to NCHW otherwise)."""
     lib = _lib.load()
+    if _conv_input_as_dense(x, ksize, stride, pad):
+        return factor_dense(_nhwc_rows(x), add_ones_col, alpha, beta, out)
+    if _is_nhwc(x):
+        x = x.contiguous()
     _chk(x, 'x')
     n, c, h, w = x.shape
     ho = (h + 2 * pad - ksize) // stride + 1
@@ -98,8 +122,11 @@ def factor_conv_input(x, ksize, stride, pad, add_ones_col=False, alpha=1.0,
 
 
 def factor_conv_grad(gy, alpha=1.0, beta=0.0, out=None):
-    """out = alpha * g^T g + beta * out, g = NCHW ``gy`` as (n*ho*wo, c)."""
+    """out = alpha * g^T g + beta * out, g = ``gy`` as (n*ho*wo, c); NCHW, or
+    channels-last (then g is the tensor itself, read in place)."""
     lib = _lib.load()
+    if _is_nhwc(gy):
+        return factor_dense(_nhwc_rows(gy), False, alpha, beta, out)
     _chk(gy, 'gy')
     n, c, ho, wo = gy.shape
     out = _factor_out(c, out, beta, gy.device)
@@ -124,6 +151,10 @@ def dense_item(x, add_ones_col, alpha, beta, out):
 
 
 def conv_input_item(x, ksize, stride, pad, add_ones_col, alpha, beta, out):
+    if _conv_input_as_dense(x, ksize, stride, pad):
+        return dense_item(_nhwc_rows(x), add_ones_col, alpha, beta, out)
+    if _is_nhwc(x):
+        x = x.contiguous()
     _chk(x, 'x')
     _chk(out, 'out')
     it = _lib.FactorItem()
@@ -137,6 +168,8 @@ def conv_input_item(x, ksize, stride, pad, add_ones_col, alpha, beta, out):
 
 
 def conv_grad_item(gy, alpha, beta, out):
+    if _is_nhwc(gy):
+        return dense_item(_nhwc_rows(gy), False, alpha, beta, out)
     _chk(gy, 'gy')
     _chk(out, 'out')
     it = _lib.FactorItem()

@@ -3,9 +3,20 @@
 im2col patch matrix of the reference is never built: the factor kernel
 gathers patches while it multiplies."""
 
+import torch
+
 from chainerkfac_b200 import ops
 from chainerkfac_b200.optimizers.fisher_blocks.connection import \
     FisherBlockConnection
+
+
+def _dense_layout(t):
+    """NCHW-contiguous tensors as they are; channels-last tensors too (the
+    factor calls read them in place where they can); anything else is copied."""
+    if t.is_contiguous() or \
+            t.is_contiguous(memory_format=torch.channels_last):
+        return t
+    return t.contiguous()
 
 
 class Convolution2DFunction(object):
@@ -20,7 +31,7 @@ class FisherBlockConvolution2D(FisherBlockConnection):
 
     def compute_A(self, in_data):
         # convolution_2d.py:19-41: A = P^T P / n, P = patches (+ ones column)
-        x = in_data[0].contiguous()
+        x = _dense_layout(in_data[0])
         ksize, stride, pad = \
             self._link.ksize, self._link.stride[0], self._link.pad[0]
         n, c = x.shape[0], x.shape[1]
@@ -31,7 +42,7 @@ class FisherBlockConvolution2D(FisherBlockConnection):
 
     def compute_G(self, in_data, out_grad_data):
         # convolution_2d.py:43-72: G = g^T g * s^2 / (n ho wo), s = n/loss_scale
-        gy = out_grad_data[0].contiguous()
+        gy = _dense_layout(out_grad_data[0])
         n, c, ho, wo = gy.shape
         s = self.gy_scale(n)
         out = self.factor_buffer(1, c, gy.device)
@@ -39,7 +50,7 @@ class FisherBlockConvolution2D(FisherBlockConnection):
                                     out=out)
 
     def item_A(self, in_data):
-        x = in_data[0].contiguous()
+        x = _dense_layout(in_data[0])
         ksize, stride, pad = \
             self._link.ksize, self._link.stride[0], self._link.pad[0]
         n, c = x.shape[0], x.shape[1]
@@ -51,7 +62,7 @@ class FisherBlockConvolution2D(FisherBlockConnection):
                                    self._A)
 
     def item_G(self, in_data, out_grad_data):
-        gy = out_grad_data[0].contiguous()
+        gy = _dense_layout(out_grad_data[0])
         n, c, ho, wo = gy.shape
         s = self.gy_scale(n)
         self._G = self.factor_buffer(1, c, gy.device)

@@ -388,6 +388,34 @@ def test_bn_kfgrad(ops, golden):
 
 
 # -------------------------------------------------------------- wire format
+@pytest.mark.parametrize('n,c,h,k,s,p,bias', [
+    (2, 40, 9, 1, 1, 0, True),      # its own patch matrix: read in place
+    (2, 64, 14, 3, 1, 1, False),    # copied to NCHW for the gather
+    (2, 24, 10, 1, 2, 0, False)])
+def test_factor_conv_channels_last(ops, n, c, h, k, s, p, bias):
+    """Channels-last activations and gradients give the factors of the same
+    logical NCHW tensors."""
+    rng = np.random.default_rng(7 * n + c + h + k)
+    x = np.maximum(rng.standard_normal((n, c, h, h)), 0).astype(np.float32)
+    want = orc.conv_A(x.astype(np.float64), k, s, p, bias)
+    xd = dev(x).contiguous(memory_format=torch.channels_last)
+    got = host(ops.factor_conv_input(xd, k, s, p, bias, alpha=1.0 / n))
+    assert rel(got, want) < FACTOR_TOL
+    out = torch.empty_like(dev(got))
+    ops.factor_group([ops.conv_input_item(xd, k, s, p, bias, 1.0 / n, 0.0,
+                                          out)], out.device)
+    assert rel(host(out), want) < FACTOR_TOL
+    gy = (rng.standard_normal((n, c, h, h)) / n).astype(np.float32)
+    wantg = orc.conv_G(gy.astype(np.float64))
+    gd = dev(gy).contiguous(memory_format=torch.channels_last)
+    gotg = host(ops.factor_conv_grad(gd, alpha=n / float(h * h)))
+    assert rel(gotg, wantg) < FACTOR_TOL
+    outg = torch.empty_like(dev(gotg))
+    ops.factor_group([ops.conv_grad_item(gd, n / float(h * h), 0.0, outg)],
+                     outg.device)
+    assert rel(host(outg), wantg) < FACTOR_TOL
+
+
 def test_wire_pack_unpack_bit_exact(ops):
     rng = np.random.default_rng(14)
     shapes = [((37, 37), True), ((11,), False), ((1, 1), True),

@@ -214,3 +214,37 @@ def test_bench_resnet50_step_runs():
     l1 = step()
     assert np.isfinite(l0) and np.isfinite(l1)
     assert h2d == 2 * 3 * 64 * 64 * 4 + 2 * 8 and d2h == 4
+
+
+def test_channels_last_activations_give_the_same_update():
+    """The same model and batch with channels-last activations (weights keep
+    their layout): factors are read in place from the (n*h*w, c) tensors and
+    the update must match the NCHW run."""
+    import chainerkfac_b200 as ck
+
+    def make():
+        torch.manual_seed(11)
+        return nn.Sequential(nn.Conv2d(3, 16, 3, 1, 1), nn.ReLU(),
+                             nn.Conv2d(16, 24, 1, 1, 0, bias=False), nn.ReLU(),
+                             nn.Conv2d(24, 8, 3, 2, 1), nn.ReLU(),
+                             nn.AdaptiveAvgPool2d(1), nn.Flatten(),
+                             nn.Linear(8, 5)).cuda()
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(6, 3, 12, 12, generator=g).cuda()
+    t = torch.randint(0, 5, (6,), generator=g).cuda()
+    results = []
+    # fp32 convolutions: with TF32 the NCHW and NHWC algorithms of the
+    # library differ by 1e-3, which would hide a layout mistake
+    tf32 = torch.backends.cudnn.allow_tf32
+    torch.backends.cudnn.allow_tf32 = False
+    for fmt in (torch.contiguous_format, torch.channels_last):
+        m = make()
+        opt = ck.KFAC(lr=0.05, momentum=0.9, cov_ema_decay=0.9, damping=1e-2)
+        opt.setup(m)
+        xin = x.contiguous(memory_format=fmt)
+        for _ in range(3):
+            opt.update(lambda a, b: F.cross_entropy(m(a), b), xin, t)
+        results.append([host(p) for p in m.parameters()])
+    torch.backends.cudnn.allow_tf32 = tf32
+    errs = [rel(b, a) for a, b in zip(*results)]
+    assert max(errs) < 1e-3, errs
