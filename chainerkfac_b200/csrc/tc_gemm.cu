@@ -1339,25 +1339,50 @@ tc_pair_kernel(const GemmDesc* __restrict__ descs, int ndesc,
 }
 
 
-// Copy an NCHW tensor into a buffer with a zero border of `pad` pixels.
-// blockIdx.y walks the (n, c) planes, threads walk one padded plane: no
-// division by run-time 64-bit values in the inner loop.
-__global__ void pad_copy_kernel(const float* __restrict__ x, long long planes,
-                                int h, int w, int pad,
-                                float* __restrict__ out) {
-  const int hp = h + 2 * pad, wp = w + 2 * pad;
-  const int per = hp * wp;
-  for (long long plane = blockIdx.y; plane < planes; plane += gridDim.y) {
-    const float* src = x + plane * h * w;
-    float* dst = out + plane * per;
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < per;
-         i += gridDim.x * blockDim.x) {
-      const int yy = i / wp;
-      const int y = yy - pad, xx = i - yy * wp - pad;
-      float v = 0.f;
-      if ((unsigned)y < (unsigned)h && (unsigned)xx < (unsigned)w)
-        v = src[y * w + xx];
-      dst[i] = v;
+// Copies of NCHW tensors into buffers with a zero border of `pad` pixels.
+// The zero-bordered copies of a grouped factor build in one launch: a work
+// item is a run of whole planes of one job (about 4096 output elements),
+// items are numbered job after job, and a block finds its job by bisection in
+// a shared-memory copy of the first item of every job.
+struct PadJob {
+  const float* src;
+  float* dst;
+  long long planes;
+  int h, w, pad;
+  int group;        // planes per work item
+  int item_begin;   // first work item of this job
+};
+
+constexpr int kPadJobsMax = 256;
+
+__global__ void __launch_bounds__(256)
+pad_copy_group_kernel(const PadJob* __restrict__ jobs, int njobs,
+                      int total_items) {
+  __shared__ int s_begin[kPadJobsMax];
+  for (int i = threadIdx.x; i < njobs; i += blockDim.x)
+    s_begin[i] = jobs[i].item_begin;
+  __syncthreads();
+  for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
+    int lo = 0, hi = njobs - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (s_begin[mid] <= item) lo = mid; else hi = mid - 1;
+    }
+    const PadJob j = jobs[lo];
+    const int wp = j.w + 2 * j.pad, per = (j.h + 2 * j.pad) * wp;
+    const long long p0 = (long long)(item - j.item_begin) * j.group;
+    const long long p1 = min(j.planes, p0 + j.group);
+    for (long long plane = p0; plane < p1; ++plane) {
+      const float* src = j.src + plane * j.h * j.w;
+      float* dst = j.dst + plane * per;
+      for (int i = threadIdx.x; i < per; i += blockDim.x) {
+        const int yy = i / wp;
+        const int y = yy - j.pad, xx = i - yy * wp - j.pad;
+        float v = 0.f;
+        if ((unsigned)y < (unsigned)j.h && (unsigned)xx < (unsigned)j.w)
+          v = src[y * j.w + xx];
+        dst[i] = v;
+      }
     }
   }
 }
@@ -1638,6 +1663,8 @@ int run_factor_group_tc(int count, const FactorJob* jobs, void* workspace,
 
   std::vector<GemmDesc> descs[2];       // [0] strided, [1] im2col
   std::vector<ReduceItem> reduces;
+  std::vector<PadJob> pads;
+  int pad_items = 0;
   for (int i = 0; i < count; ++i) {
     const FactorJob& job = jobs[i];
     KFAC_REQUIRE(job.out != nullptr && job.X.base != nullptr,
@@ -1654,11 +1681,17 @@ int run_factor_group_tc(int count, const FactorJob* jobs, void* workspace,
       const long long total = planes * (X.H + 2 * X.pd) * (X.W + 2 * X.pd);
       KFAC_REQUIRE(total < (1LL << 31), "factor: padded input too large");
       const int per = (X.H + 2 * X.pd) * (X.W + 2 * X.pd);
-      dim3 pgrid((per + 1023) / 1024 > 8 ? 8 : (per + 1023) / 1024,
-                 (unsigned)(planes < 16384 ? planes : 16384));
-      pad_copy_kernel<<<pgrid, 256, 0, stream>>>(X.base, planes, X.H, X.W,
-                                                 X.pd, padded);
-      KFAC_LAUNCH_CHECK("pad_copy_kernel");
+      PadJob pj;
+      pj.src = X.base;
+      pj.dst = padded;
+      pj.planes = planes;
+      pj.h = X.H;
+      pj.w = X.W;
+      pj.pad = X.pd;
+      pj.group = per >= 4096 ? 1 : 4096 / per;
+      pj.item_begin = pad_items;
+      pad_items += (int)((planes + pj.group - 1) / pj.group);
+      pads.push_back(pj);
       X.base = padded;
       X.H += 2 * X.pd;
       X.W += 2 * X.pd;
@@ -1698,6 +1731,25 @@ int run_factor_group_tc(int count, const FactorJob* jobs, void* workspace,
       }
     }
     descs[X.mode == 1 ? 1 : 0].push_back(g);
+  }
+  for (size_t b = 0; b < pads.size(); b += kPadJobsMax) {
+    // (more than kPadJobsMax padded inputs in one group: several launches)
+    const int nj = (int)std::min<size_t>(kPadJobsMax, pads.size() - b);
+    std::vector<PadJob> part(pads.begin() + b, pads.begin() + b + nj);
+    const int first = part[0].item_begin;
+    for (PadJob& pj : part) pj.item_begin -= first;
+    const PadJob& lastj = part[nj - 1];
+    const int items = lastj.item_begin +
+                      (int)((lastj.planes + lastj.group - 1) / lastj.group);
+    void* dev = nullptr;
+    rc = ring_alloc(part.size() * sizeof(PadJob), &dev);
+    if (rc != KFAC_OK) return rc;
+    KFAC_CUDA(cudaMemcpyAsync(dev, part.data(), part.size() * sizeof(PadJob),
+                              cudaMemcpyHostToDevice, stream));
+    const int grid = std::min(items, sm_count() * 8);
+    pad_copy_group_kernel<<<grid, 256, 0, stream>>>(
+        static_cast<const PadJob*>(dev), nj, items);
+    KFAC_LAUNCH_CHECK("pad_copy_group_kernel");
   }
   SideStream* side = nullptr;
   if (!descs[0].empty() && !descs[1].empty()) {
