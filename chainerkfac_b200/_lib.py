@@ -53,6 +53,8 @@ SIGNATURES = {
     'kfac_factor_group': (I, [I, ctypes.POINTER(FactorItem), VP, SZ, VP]),
     'kfac_bn_sample_grads': (I, [VP, VP, I, I, I, F, F, VP, VP, VP]),
     'kfac_axpby': (I, [I64, F, VP, F, VP, VP, VP]),
+    'kfac_axpby_group': (I, [I, c_i64_p, F, c_void_pp, F, c_void_pp,
+                             c_void_pp, VP]),
     'kfac_inverse_workspace_bytes': (SZ, [I, c_int_p]),
     'kfac_inverse_plan_create': (I, [I, c_int_p, c_void_pp, c_void_pp,
                                      c_int_p, c_int_p, c_float_p, c_float_p,

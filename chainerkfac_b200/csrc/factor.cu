@@ -262,6 +262,47 @@ __global__ void axpby_kernel(long long count, float a,
   }
 }
 
+// out_i = a * x_i + b * y_i for many arrays in one launch: a work item is a
+// run of 8192 elements of one array; a block finds its array by bisection in a
+// shared-memory copy of the arrays' first items.
+struct AxpbyArr {
+  const float* x;
+  const float* y;
+  float* out;
+  long long n;
+  int item_begin;
+};
+
+constexpr int kAxpbyArrMax = 1024;
+constexpr int kAxpbyChunk = 8192;
+
+__global__ void __launch_bounds__(256)
+axpby_group_kernel(const AxpbyArr* __restrict__ arrs, int narr, int total_items,
+                   float a, float b) {
+  __shared__ int s_begin[kAxpbyArrMax];
+  for (int i = threadIdx.x; i < narr; i += blockDim.x)
+    s_begin[i] = arrs[i].item_begin;
+  __syncthreads();
+  for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
+    int lo = 0, hi = narr - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (s_begin[mid] <= item) lo = mid; else hi = mid - 1;
+    }
+    const AxpbyArr r = arrs[lo];
+    const long long base = (long long)(item - r.item_begin) * kAxpbyChunk;
+#pragma unroll 4
+    for (int k = threadIdx.x; k < kAxpbyChunk; k += 256) {
+      const long long i = base + k;
+      if (i < r.n) {
+        float v = a * r.x[i];
+        if (b != 0.f) v += b * r.y[i];
+        r.out[i] = v;
+      }
+    }
+  }
+}
+
 __global__ void momentum_kernel(long long count, const float* __restrict__ grad,
                                 float* param, float* v, float lr,
                                 float momentum) {
@@ -407,6 +448,45 @@ extern "C" int kfac_axpby(int64_t count, float a, const float* x, float b,
   axpby_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(count, a, x, b, y,
                                                          out);
   KFAC_LAUNCH_CHECK("axpby_kernel");
+  return KFAC_OK;
+}
+
+extern "C" int kfac_axpby_group(int n_arrays, const int64_t* counts, float a,
+                                const float* const* x, float b,
+                                const float* const* y, float* const* out,
+                                void* stream) {
+  if (n_arrays <= 0) return KFAC_OK;
+  KFAC_REQUIRE(counts && x && out && (b == 0.f || y),
+               "axpby_group: null argument");
+  KFAC_REQUIRE(n_arrays <= kAxpbyArrMax,
+               "axpby_group: %d arrays in one call, at most %d", n_arrays,
+               kAxpbyArrMax);
+  std::vector<AxpbyArr> tab(n_arrays);
+  long long items = 0;
+  for (int i = 0; i < n_arrays; ++i) {
+    KFAC_REQUIRE(counts[i] >= 0, "axpby_group: negative count at %d", i);
+    KFAC_REQUIRE(counts[i] == 0 || (x[i] && out[i] && (b == 0.f || y[i])),
+                 "axpby_group: null pointer at %d", i);
+    tab[i].x = x[i];
+    tab[i].y = b == 0.f ? nullptr : y[i];
+    tab[i].out = out[i];
+    tab[i].n = counts[i];
+    tab[i].item_begin = (int)items;
+    items += (counts[i] + kAxpbyChunk - 1) / kAxpbyChunk;
+    KFAC_REQUIRE(items < (1ll << 31), "axpby_group: too many elements");
+  }
+  if (items == 0) return KFAC_OK;
+  void* dev = nullptr;
+  int rc = ring_alloc(tab.size() * sizeof(AxpbyArr), &dev);
+  if (rc != KFAC_OK) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  KFAC_CUDA(cudaMemcpyAsync(dev, tab.data(), tab.size() * sizeof(AxpbyArr),
+                            cudaMemcpyHostToDevice, st));
+  const long long cap = (long long)sm_count() * 8;
+  const int grid = (int)(items < cap ? items : cap);
+  axpby_group_kernel<<<grid, 256, 0, st>>>(static_cast<const AxpbyArr*>(dev),
+                                           n_arrays, (int)items, a, b);
+  KFAC_LAUNCH_CHECK("axpby_group_kernel");
   return KFAC_OK;
 }
 

@@ -221,6 +221,22 @@ def axpby(a, x, b, y, out):
     return out
 
 
+def axpby_group(a, xs, b, ys, outs):
+    """outs[i] = a*xs[i] + b*ys[i] for lists of tensors, in one launch."""
+    if not xs:
+        return
+    lib = _lib.load()
+    for lst in (xs, ys, outs):
+        for t in lst:
+            _chk(t, 'axpby_group argument')
+    counts = (ctypes.c_int64 * len(xs))(*[int(t.numel()) for t in xs])
+    _lib.check(lib.kfac_axpby_group(
+        len(xs), counts, a, _lib.ptr_array([t.data_ptr() for t in xs]), b,
+        _lib.ptr_array([t.data_ptr() for t in ys]),
+        _lib.ptr_array([t.data_ptr() for t in outs]), _stream()),
+        'kfac_axpby_group')
+
+
 class InversePlan(object):
     """Batched damped inverse of a fixed set of factor buffers."""
 

@@ -171,6 +171,24 @@ class KFACUpdateRule(_base.UpdateRule):
     update_core_gpu = update_core
 
 
+def update_cov_emas_grouped(blocks):
+    """``FisherBlock.update_cov_emas`` for a list of blocks with the running
+    averages of all their factors in one launch.  Blocks without a running
+    average yet, or with decay 1 (plain copy), take the per-block path."""
+    xs, outs, r = [], [], None
+    for fb in blocks:
+        fb.check_attr('covs')
+        decay = fb.cov_ema_decay
+        if fb.cov_emas is None or decay == 1.0 or (r is not None and decay != r):
+            fb.update_cov_emas()
+            continue
+        r = decay
+        xs += list(fb.covs)
+        outs += list(fb.cov_emas)
+    if xs:
+        ops.axpby_group(r, xs, 1.0 - r, outs, outs)
+
+
 class KFAC(_base.GradientMethod):
     """K-FAC optimizer (``kfac.py:119-310``); same arguments and defaults."""
 
@@ -413,8 +431,7 @@ class KFAC(_base.GradientMethod):
                     items += fb.flush_items()
             if items:
                 ops.factor_group(items, dev)
-            for fb in blocks:
-                fb.update_cov_emas()
+            update_cov_emas_grouped(blocks)
             if c + 1 < len(classes):
                 plan.start_class(c, first.damping,
                                  first._pi_type == PI_TYPE_TRACENORM)
@@ -432,8 +449,7 @@ class KFAC(_base.GradientMethod):
         elif self._emas_done:
             self._emas_done = False      # a pipelined exchange already did it
         else:
-            for fblock in fblocks:
-                fblock.update_cov_emas()
+            update_cov_emas_grouped(fblocks)
         # one batched damped inverse per (damping, pi rule) group
         groups = {}
         for fb in fblocks:
@@ -634,9 +650,8 @@ class DistributedKFAC(KFAC):
                     [[i for i in ix if i in member_set] for ix in self.indices],
                     lambda block: block.extract_for_reduce_scatter_v())
                 self.comm.reduce_scatter_v_arrays(arrays)
-                for i in members:
-                    if i in local:
-                        self.fblocks[i].update_cov_emas()
+                update_cov_emas_grouped(
+                    [self.fblocks[i] for i in members if i in local])
                 if n + 1 < len(order) and key in plan.class_keys:
                     plan.start_class(plan.class_keys.index(key), first.damping,
                                      first._pi_type == PI_TYPE_TRACENORM)

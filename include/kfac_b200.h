@@ -157,6 +157,16 @@ int kfac_bn_sample_grads(const float* x, const float* gy, int n, int c, int hw,
 int kfac_axpby(int64_t count, float a, const float* x, float b, const float* y,
                float* out, void* stream);
 
+/* kfac_axpby over `n_arrays` (<= 1024) arrays in one launch: out[i] = a * x[i]
+ * + b * y[i] over counts[i] floats each (out[i] may alias y[i]); y may be NULL
+ * when b == 0.  The running averages of all factors of a step
+ * (FisherBlock.update_cov_emas called block by block in
+ * optimizers/kfac.py:306-311).  Pointer/size arrays are host arrays read
+ * during the call. */
+int kfac_axpby_group(int n_arrays, const int64_t* counts, float a,
+                     const float* const* x, float b, const float* const* y,
+                     float* const* out, void* stream);
+
 /* ------------------------------------------------------------------ inverse
  * Batched damped inverse of `count` symmetric positive definite factors:
  * inverses[i] = (factors[i] + add_i * I)^-1, dense symmetric, by blocked

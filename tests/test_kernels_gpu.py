@@ -416,6 +416,23 @@ def test_factor_conv_channels_last(ops, n, c, h, k, s, p, bias):
     assert rel(host(outg), wantg) < FACTOR_TOL
 
 
+def test_axpby_group_matches_single_calls(ops):
+    rng = np.random.default_rng(77)
+    shapes = [(3, 3), (8192,), (100, 130), (1,), (8193, 2)]
+    xs = [dev(rng.standard_normal(s).astype(np.float32)) for s in shapes]
+    ys = [dev(rng.standard_normal(s).astype(np.float32)) for s in shapes]
+    want = [ops.axpby(0.9, x, 0.1, y, torch.empty_like(y))
+            for x, y in zip(xs, ys)]
+    outs = [y.clone() for y in ys]
+    ops.axpby_group(0.9, xs, 0.1, outs, outs)        # in place on y
+    for o, w in zip(outs, want):
+        assert torch.equal(o, w)
+    outs = [torch.full_like(y, 7.0) for y in ys]
+    ops.axpby_group(1.0, xs, 0.0, ys, outs)          # plain copy
+    for o, x in zip(outs, xs):
+        assert torch.equal(o, x)
+
+
 def test_wire_pack_unpack_bit_exact(ops):
     rng = np.random.default_rng(14)
     shapes = [((37, 37), True), ((11,), False), ((1, 1), True),
