@@ -30,7 +30,7 @@ class FactorItem(ctypes.Structure):
                 ('w', ctypes.c_int), ('ksize', ctypes.c_int),
                 ('stride', ctypes.c_int), ('pad', ctypes.c_int),
                 ('alpha', ctypes.c_float), ('beta', ctypes.c_float),
-                ('out', ctypes.c_void_p)]
+                ('out', ctypes.c_void_p), ('layout', ctypes.c_int)]
 
 
 # name -> (restype, argtypes); mirrors include/kfac_b200.h one to one.

@@ -538,6 +538,11 @@ static int job_from_item(const kfac_factor_item& it, FactorJob& job) {
   job.beta = it.beta;
   job.out = it.out;
   job.n = it.n;
+  job.nhwc = 0;
+  KFAC_REQUIRE(it.layout == 0 ||
+                   (it.layout == 1 && it.kind == KFAC_FACTOR_CONV_INPUT),
+               "factor_group: layout %d of item kind %d unsupported", it.layout,
+               it.kind);
   if (it.kind == KFAC_FACTOR_DENSE) {
     KFAC_REQUIRE(it.ld >= it.d_in && it.rows > 0 && it.d_in > 0,
                  "factor_group: bad dense item");
@@ -559,6 +564,10 @@ static int job_from_item(const kfac_factor_item& it, FactorJob& job) {
                                it.pad, it.add_ones_col);
     job.rows = (long long)it.n * ho * wo;
     job.d = it.c * it.ksize * it.ksize + (it.add_ones_col ? 1 : 0);
+    job.nhwc = it.layout;
+    KFAC_REQUIRE(!job.nhwc || engine() == 1,
+                 "factor_group: channels-last inputs need the tensor-core "
+                 "engine");
   } else if (it.kind == KFAC_FACTOR_CONV_GRAD) {
     KFAC_REQUIRE(it.n > 0 && it.c > 0 && it.h > 0 && it.w > 0,
                  "factor_group: bad conv grad item");

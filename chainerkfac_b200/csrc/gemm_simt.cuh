@@ -270,7 +270,7 @@ int launch_tc_grouped(const GemmDesc* descs_dev, int ndesc, int total_tiles,
                       cudaStream_t stream);
 bool tc_desc_has_tails(const GemmDesc& g);
 size_t tc_factor_workspace_bytes(long long rows, int d);
-size_t tc_pad_bytes(const Operand& X, int n);
+size_t tc_pad_bytes(const Operand& X, int n, int nhwc = 0);
 int run_factor_tc(const Operand& X, long long rows, int d, float alpha,
                   float beta, float* out, void* workspace,
                   size_t workspace_bytes, cudaStream_t stream);
@@ -279,6 +279,7 @@ struct FactorJob {      // one factor of a grouped build
   long long rows;
   int d;
   int n;                // batch size (im2col operands)
+  int nhwc;             // im2col operand: the tensor is stored channels-last
   float alpha, beta;
   float* out;
 };

@@ -1349,8 +1349,10 @@ struct PadJob {
   float* dst;
   long long planes;
   int h, w, pad;
-  int group;        // planes per work item
+  int group;        // planes per work item (NCHW source)
   int item_begin;   // first work item of this job
+  int nhwc;         // source is channels-last: items are 32 x 32 transposes
+  int C;            // channels (channels-last source)
 };
 
 constexpr int kPadJobsMax = 256;
@@ -1359,6 +1361,7 @@ __global__ void __launch_bounds__(256)
 pad_copy_group_kernel(const PadJob* __restrict__ jobs, int njobs,
                       int total_items) {
   __shared__ int s_begin[kPadJobsMax];
+  __shared__ float tile[32][33];
   for (int i = threadIdx.x; i < njobs; i += blockDim.x)
     s_begin[i] = jobs[i].item_begin;
   __syncthreads();
@@ -1370,6 +1373,36 @@ pad_copy_group_kernel(const PadJob* __restrict__ jobs, int njobs,
     }
     const PadJob j = jobs[lo];
     const int wp = j.w + 2 * j.pad, per = (j.h + 2 * j.pad) * wp;
+    if (j.nhwc) {
+      // (n, h, w, c) -> zero-bordered (n, c, h + 2p, w + 2p): a 32-pixel x
+      // 32-channel tile is read along c and written along the pixels; the
+      // border was cleared before the launch
+      const int hw = j.h * j.w;
+      const int ct = (j.C + 31) >> 5, qt = (hw + 31) >> 5;
+      int t = item - j.item_begin;
+      const int n = t / (ct * qt);
+      t -= n * ct * qt;
+      const int c0 = (t / qt) << 5, q0 = (t % qt) << 5;
+      const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int q = q0 + ty + 8 * i, c = c0 + tx;
+        if (q < hw && c < j.C)
+          tile[ty + 8 * i][tx] = j.src[((long long)n * hw + q) * j.C + c];
+      }
+      __syncthreads();
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int c = c0 + ty + 8 * i, q = q0 + tx;
+        if (c < j.C && q < hw) {
+          const int y = q / j.w, x = q - y * j.w;
+          j.dst[((long long)n * j.C + c) * per + (y + j.pad) * wp + x + j.pad] =
+              tile[tx][ty + 8 * i];
+        }
+      }
+      __syncthreads();
+      continue;
+    }
     const long long p0 = (long long)(item - j.item_begin) * j.group;
     const long long p1 = min(j.planes, p0 + j.group);
     for (long long plane = p0; plane < p1; ++plane) {
@@ -1589,8 +1622,10 @@ size_t tc_factor_workspace_bytes(long long rows, int d) {
   return (size_t)s.splits * s.tiles * TC_BM * TC_BN * sizeof(float);
 }
 
-size_t tc_pad_bytes(const Operand& X, int n) {
-  if (X.mode != 1 || X.pd == 0) return 0;
+size_t tc_pad_bytes(const Operand& X, int n, int nhwc) {
+  // a staging copy is made for a zero border and / or to turn a channels-last
+  // tensor into the NCHW planes the gather walks
+  if (X.mode != 1 || (X.pd == 0 && !nhwc)) return 0;
   size_t e = (size_t)n * X.C * (X.H + 2 * X.pd) * (X.W + 2 * X.pd);
   return (e * sizeof(float) + 255) & ~(size_t)255;
 }
@@ -1613,7 +1648,7 @@ size_t tc_factor_group_workspace_bytes(int count, const FactorJob* jobs) {
   const long long chunk = tc_group_chunk(count, jobs);
   size_t total = 0;
   for (int i = 0; i < count; ++i) {
-    total += tc_pad_bytes(jobs[i].X, jobs[i].n);
+    total += tc_pad_bytes(jobs[i].X, jobs[i].n, jobs[i].nhwc);
     TcFactorSplit s = count == 1 ? tc_factor_split(jobs[i].rows, jobs[i].d)
                                  : tc_split_for(jobs[i].rows, jobs[i].d, chunk);
     if (s.splits > 1)
@@ -1672,9 +1707,9 @@ int run_factor_group_tc(int count, const FactorJob* jobs, void* workspace,
     KFAC_REQUIRE(job.rows > 0 && job.d > 0 && job.rows < (1LL << 31),
                  "factor: rows=%lld d=%d out of range", job.rows, job.d);
     Operand X = job.X;
-    if (X.mode == 1 && X.pd > 0) {
-      // zero-bordered copy first; the gather then needs no bounds checks
-      const size_t pad_bytes = tc_pad_bytes(X, job.n);
+    if (X.mode == 1 && (X.pd > 0 || job.nhwc)) {
+      // zero-bordered NCHW copy first; the gather then needs no bounds checks
+      const size_t pad_bytes = tc_pad_bytes(X, job.n, job.nhwc);
       float* padded = reinterpret_cast<float*>(ws);
       ws += pad_bytes;
       const long long planes = (long long)job.n * X.C;
@@ -1690,7 +1725,15 @@ int run_factor_group_tc(int count, const FactorJob* jobs, void* workspace,
       pj.pad = X.pd;
       pj.group = per >= 4096 ? 1 : 4096 / per;
       pj.item_begin = pad_items;
-      pad_items += (int)((planes + pj.group - 1) / pj.group);
+      pj.nhwc = job.nhwc;
+      pj.C = X.C;
+      if (job.nhwc) {
+        if (X.pd > 0)
+          KFAC_CUDA(cudaMemsetAsync(padded, 0, pad_bytes, stream));
+        pad_items += job.n * ((X.C + 31) / 32) * ((X.H * X.W + 31) / 32);
+      } else {
+        pad_items += (int)((planes + pj.group - 1) / pj.group);
+      }
       pads.push_back(pj);
       X.base = padded;
       X.H += 2 * X.pd;
@@ -1738,9 +1781,8 @@ int run_factor_group_tc(int count, const FactorJob* jobs, void* workspace,
     std::vector<PadJob> part(pads.begin() + b, pads.begin() + b + nj);
     const int first = part[0].item_begin;
     for (PadJob& pj : part) pj.item_begin -= first;
-    const PadJob& lastj = part[nj - 1];
-    const int items = lastj.item_begin +
-                      (int)((lastj.planes + lastj.group - 1) / lastj.group);
+    const int items =
+        (b + nj < pads.size() ? pads[b + nj].item_begin : pad_items) - first;
     void* dev = nullptr;
     rc = ring_alloc(part.size() * sizeof(PadJob), &dev);
     if (rc != KFAC_OK) return rc;
@@ -1854,6 +1896,7 @@ int run_factor_tc(const Operand& X, long long rows, int d, float alpha,
   job.rows = rows;
   job.d = d;
   job.n = X.mode == 1 ? (int)(rows / ((long long)X.Ho * X.Wo)) : 0;
+  job.nhwc = 0;
   job.alpha = alpha;
   job.beta = beta;
   job.out = out;

@@ -153,11 +153,19 @@ def dense_item(x, add_ones_col, alpha, beta, out):
 def conv_input_item(x, ksize, stride, pad, add_ones_col, alpha, beta, out):
     if _conv_input_as_dense(x, ksize, stride, pad):
         return dense_item(_nhwc_rows(x), add_ones_col, alpha, beta, out)
+    layout = 0
     if _is_nhwc(x):
-        x = x.contiguous()
-    _chk(x, 'x')
+        if _lib.load().kfac_get_engine() == 1:
+            layout = 1       # the staging copy reads channels-last directly
+        else:
+            x = x.contiguous()
+    if layout == 0:
+        _chk(x, 'x')
+    elif not x.is_cuda or x.dtype != torch.float32:
+        raise TypeError('x must be a float32 CUDA tensor')
     _chk(out, 'out')
     it = _lib.FactorItem()
+    it.layout = layout
     it.kind, it.add_ones_col = 1, int(bool(add_ones_col))
     it.x = x.data_ptr()
     it.n, it.c, it.h, it.w = x.shape

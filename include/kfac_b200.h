@@ -118,6 +118,9 @@ int kfac_factor_dense_noalloc(const float* x, int64_t rows, int d_in,
  * layers fill the GPU together (the reference builds one factor per hook
  * call; results are identical).  Each item is one of the three builds above
  * with the same meaning of its fields; conv gradients pass ho, wo in h, w.
+ * `layout` (conv inputs only, tensor-core engine only): 0 = NCHW as in the
+ * reference; 1 = the same logical (n, c, h, w) tensor stored channels-last
+ * (n, h, w, c), which the zero-bordered staging copy then reads directly.
  * `items` is a host array read during the call; outputs must not alias. */
 #define KFAC_FACTOR_DENSE 0
 #define KFAC_FACTOR_CONV_INPUT 1
@@ -132,6 +135,7 @@ typedef struct kfac_factor_item {
   int n, c, h, w, ksize, stride, pad; /* conv */
   float alpha, beta;
   float* out;
+  int layout;     /* conv input: 0 NCHW, 1 channels-last */
 } kfac_factor_item;
 
 size_t kfac_factor_group_workspace_bytes(int count,

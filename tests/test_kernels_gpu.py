@@ -390,8 +390,10 @@ def test_bn_kfgrad(ops, golden):
 # -------------------------------------------------------------- wire format
 @pytest.mark.parametrize('n,c,h,k,s,p,bias', [
     (2, 40, 9, 1, 1, 0, True),      # its own patch matrix: read in place
-    (2, 64, 14, 3, 1, 1, False),    # copied to NCHW for the gather
-    (2, 24, 10, 1, 2, 0, False)])
+    (2, 64, 14, 3, 1, 1, False),    # staged as zero-bordered NCHW planes
+    (2, 24, 10, 1, 2, 0, False),    # staged without a border
+    (2, 3, 32, 7, 2, 3, True),      # few channels, bias column
+    (3, 40, 9, 3, 1, 1, True)])     # sizes that are no multiples of 32
 def test_factor_conv_channels_last(ops, n, c, h, k, s, p, bias):
     """Channels-last activations and gradients give the factors of the same
     logical NCHW tensors."""
