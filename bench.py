@@ -405,12 +405,11 @@ class DistributedWorkload(DeviceWorkload):
                 side.wait_event(built)
             with torch.cuda.stream(side):
                 self.comm.reduce_scatter_v_arrays(self.class_rs[c])
-                for i in layers:
-                    if i in mine:
-                        for j in (0, 1):
-                            self.ops.axpby(r, self.cov[2 * i + j], rest,
-                                           self.ema[2 * i + j],
-                                           self.ema[2 * i + j])
+                own = [2 * i + j for i in layers if i in mine for j in (0, 1)]
+                if own:
+                    emas = [self.ema[k] for k in own]
+                    self.ops.axpby_group(r, [self.cov[k] for k in own], rest,
+                                         emas, emas)
                 if c < last and self.class_plan[c] is not None:
                     self.plan.start_class(self.class_plan[c], DAMPING, True)
             if side is not main:
