@@ -49,9 +49,9 @@ OWNERSHIP = 'balanced'   # layer ownership at N > 1 ('reference': by count)
 
 
 def layer_table():
-    from oracle import kfac_oracle as orc
-    layers = orc.resnet50_layers(batch=BATCH)
-    return layers, [orc.layer_dims(l) for l in layers]
+    import bench_workloads as bw
+    layers = bw.resnet50_layers(batch=BATCH)
+    return layers, [bw.layer_dims(l) for l in layers]
 
 
 def algorithmic_flops(dims):
@@ -321,7 +321,6 @@ class DistributedWorkload(DeviceWorkload):
     def __init__(self, device, seed, comm):
         super(DistributedWorkload, self).__init__(device, seed)
         import torch
-        from oracle import kfac_oracle as orc
         self.comm = comm
         from chainerkfac_b200.optimizers.kfac import balanced_split
         cnt = len(self.layers)
@@ -330,7 +329,9 @@ class DistributedWorkload(DeviceWorkload):
                 [float(dA) ** 3 + float(dG) ** 3
                  for dA, dG, _, _ in self.dims], comm.size)
         else:
-            self.indices = orc.split_indices(cnt, comm.size)
+            # the reference's contiguous split of the layer list by count
+            self.indices = [ix.tolist() for ix in
+                            np.array_split(np.arange(cnt), comm.size)]
         self.mine = self.indices[comm.rank]
         self.cov = [torch.zeros_like(e) for e in self.ema]
         bounds = self.plan.bounds
@@ -626,7 +627,7 @@ def run_e2e(args, device, world, rank):
     """images/sec of KFAC.update(lossfun, x, t) on a torch ResNet-50 with the
     batch copied from pinned host memory and the loss read back every step."""
     import torch
-    from chainerkfac_b200.bench_model import build_training_step
+    from bench_model import build_training_step
     step, h2d, d2h = build_training_step(device, BATCH, world, rank,
                                          cov_ema_decay=DECAY, damping=DAMPING,
                                          lr=LR, momentum=MOMENTUM,

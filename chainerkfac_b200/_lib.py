@@ -60,6 +60,9 @@ SIGNATURES = {
                                      c_int_p, c_int_p, c_float_p, c_float_p,
                                      VP, SZ, c_void_pp]),
     'kfac_inverse_plan_run': (I, [VP, F, I, VP, VP, VP]),
+    'kfac_inverse_plan_set_refine': (I, [VP, I, F]),
+    'kfac_inverse_plan_refined': (I, [VP, c_int_p]),
+    'kfac_inverse_plan_set_second_floor': (I, [VP, c_float_p]),
     'kfac_inverse_plan_destroy': (I, [VP]),
     'kfac_precond_workspace_bytes': (SZ, [I, c_int_p, c_int_p, c_int_p]),
     'kfac_precondition': (I, [I, c_int_p, c_int_p] + [c_void_pp] * 10 +

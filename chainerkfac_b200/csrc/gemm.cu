@@ -48,6 +48,7 @@ gemm_grouped_kernel(const GemmDesc* __restrict__ descs, int ndesc, float lr,
       dst[i] = src[i];
   }
   __syncthreads();
+  if (sd.gate != nullptr && *sd.gate == 0) return;   // uniform per CTA
 
   const int lt = tile - sd.tile_begin;
   int bi, bj;
@@ -118,6 +119,7 @@ gemm_grouped_kernel(const GemmDesc* __restrict__ descs, int ndesc, float lr,
       if (beta != 0.f) v += beta * (*p);
       *p = v;
       if (mirror) sd.C[(long long)c * sd.ldc + r] = v;
+      if (sd.C2 != nullptr) sd.C2[(long long)r * sd.ldc + c] = v;
     }
   }
 }
@@ -133,7 +135,7 @@ int launch_grouped_gemm(const GemmDesc* descs_dev, int ndesc, int total_tiles,
 
 }  // namespace kfac
 
-extern "C" int kfac_abi_version(void) { return 1; }
+extern "C" int kfac_abi_version(void) { return 2; }
 extern "C" const char* kfac_last_error(void) { return kfac::error_buffer(); }
 extern "C" int64_t kfac_launch_count(void) {
   return kfac::g_launches.load(std::memory_order_relaxed);

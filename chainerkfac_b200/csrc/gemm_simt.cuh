@@ -257,6 +257,9 @@ struct GemmDesc {
   int ntiles;              // tiles of one split (virtual tile = split * ntiles + tile)
   long long k_per_split;
   float* partial;          // partial tiles when splits > 1
+  const int* gate;         // if set and *gate == 0 the problem is skipped
+  float* C2;               // if set, C's new values are stored here as well
+                           // (same row pitch; plain epilogue only)
 };
 
 int launch_grouped_gemm(const GemmDesc* descs_dev, int ndesc, int total_tiles,

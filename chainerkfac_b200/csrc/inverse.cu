@@ -30,7 +30,7 @@ struct MatInfo {
   int role;
   float l2;
   float scale;
-  int pad_;
+  float l2b;      // role 2: floor of the second half of the diagonal
 };
 
 __global__ void trace_kernel(const MatInfo* __restrict__ mats,
@@ -56,14 +56,18 @@ __global__ void trace_kernel(const MatInfo* __restrict__ mats,
 __global__ void damping_kernel(const MatInfo* __restrict__ mats, int count,
                                const float* __restrict__ trace, float damping,
                                int use_pi, float* __restrict__ add,
+                               float* __restrict__ add2,
                                float* __restrict__ add_out) {
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= count) return;
   const MatInfo mi = mats[i];
   float g = fmaxf(mi.l2, damping);
-  float v;
+  float v, v2;
   if (mi.role == 2) {
+    // first half of the diagonal (scale parameters) and second half (shift
+    // parameters) have their own floors
     v = g * mi.scale;
+    v2 = fmaxf(mi.l2b, damping) * mi.scale;
   } else {
     float r = sqrtf(g);
     float pi = 1.f;
@@ -77,8 +81,10 @@ __global__ void damping_kernel(const MatInfo* __restrict__ mats, int count,
       pi = sqrtf((tA * dG) / (tG * dA));
     }
     v = mi.role == 0 ? pi * r : (1.f / pi) * r;
+    v2 = v;
   }
   add[i] = v;
+  add2[i] = v2;
   if (add_out) add_out[i] = v;
 }
 
@@ -86,14 +92,16 @@ __global__ void damping_kernel(const MatInfo* __restrict__ mats, int count,
 // the lower triangle and the rest of each diagonal 128-block (which the
 // trailing updates read-modify-write) is ever used, so only that is copied.
 __global__ void damp_copy_kernel(const MatInfo* __restrict__ mats,
-                                 const float* __restrict__ add) {
+                                 const float* __restrict__ add,
+                                 const float* __restrict__ add2) {
   const MatInfo mi = mats[blockIdx.y];
-  const float a = add[blockIdx.y];
+  const float a_first = add[blockIdx.y], a_second = add2[blockIdx.y];
   const int d = mi.d;
   const bool vec = (d & 3) == 0 &&
                    ((reinterpret_cast<uintptr_t>(mi.F) |
                      reinterpret_cast<uintptr_t>(mi.W)) & 15) == 0;
   for (int r = blockIdx.x; r < d; r += gridDim.x) {
+    const float a = (mi.role == 2 && 2 * r >= d) ? a_second : a_first;
     const int cend = min(d, (r | (DB - 1)) + 1);
     const float* src = mi.F + (long long)r * d;
     float* dst = mi.W + (long long)r * d;
@@ -376,6 +384,194 @@ chol_diag_kernel(const MatInfo* __restrict__ mats, const int* __restrict__ ids,
   }
 }
 
+
+// ---------------------------------------------------------------- refinement
+// One step of iterative refinement for factors whose fp32 inverse is visibly
+// off (ill-conditioned factors: the error of any fp32 inverse grows with the
+// condition number).  With R = I - (F + add I) X accumulated in fp64 from the
+// fp32 data, X <- X + X R has the error of X squared (times the condition
+// number), so one step is enough.  Whether a factor needs the step is decided
+// on the device from a probe: for a fixed +-1 vector v,
+//   t = X v,  r = v - (F + add I) t,  e = X r   (fp64 accumulation)
+// e estimates (X - A^-1) v, so |e| / |t| estimates the relative error of X;
+// the step runs when that exceeds `threshold` and d <= `max_dim`.
+constexpr int kRefineDimCap = 1024;   // workspace is reserved up to this size
+
+struct RefineItem {
+  int mat;          // index into the plan's matrices
+  int d;
+  int tile_begin;   // first 64 x 64 tile of this matrix in the residual grid
+  int pad_;
+  float* Y;         // d x d scratch for X R
+  double* vec;      // 2 d doubles: t, r
+};
+
+__device__ __forceinline__ float probe_sign(int i) {
+  unsigned h = (unsigned)i * 2654435761u;
+  h ^= h >> 15; h *= 2246822519u; h ^= h >> 13;
+  return (h & 1u) ? 1.f : -1.f;
+}
+
+__device__ __forceinline__ float damp_of_row(const MatInfo& mi, float add,
+                                             float add2, int row) {
+  return (mi.role == 2 && 2 * row >= mi.d) ? add2 : add;
+}
+
+// stage 0: t = X v; stage 1: r = v - (F + add I) t; stage 2: e = X r and
+// sums[item] += (|e|^2, |t|^2).  One warp per row, blockIdx.y = item.
+__global__ void __launch_bounds__(256)
+refine_probe_kernel(const MatInfo* __restrict__ mats,
+                    const RefineItem* __restrict__ items,
+                    const float* __restrict__ add,
+                    const float* __restrict__ add2, double* __restrict__ sums,
+                    int stage) {
+  const RefineItem it = items[blockIdx.y];
+  const MatInfo mi = mats[it.mat];
+  const int d = it.d;
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (stage == 1 && blockIdx.x == 0 && threadIdx.x == 0) {
+    sums[2 * blockIdx.y] = 0.0;
+    sums[2 * blockIdx.y + 1] = 0.0;
+  }
+  if (row >= d) return;
+  double* t = it.vec;
+  double* r = it.vec + d;
+  const float* mrow = (stage == 1 ? mi.F : mi.inv) + (long long)row * d;
+  double s = 0.0;
+  if (stage == 0) {
+    for (int c = lane; c < d; c += 32) s += (double)mrow[c] * probe_sign(c);
+  } else {
+    const double* x = stage == 1 ? t : r;
+    for (int c = lane; c < d; c += 32) s += (double)mrow[c] * x[c];
+  }
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_down_sync(0xffffffffu, s, o);
+  if (lane != 0) return;
+  if (stage == 0) {
+    t[row] = s;
+  } else if (stage == 1) {
+    const float a = damp_of_row(mi, add[it.mat], add2[it.mat], row);
+    r[row] = (double)probe_sign(row) - (s + (double)a * t[row]);
+  } else {
+    atomicAdd(&sums[2 * blockIdx.y], s * s);
+    atomicAdd(&sums[2 * blockIdx.y + 1], t[row] * t[row]);
+  }
+}
+
+__global__ void refine_gate_kernel(const RefineItem* __restrict__ items, int n,
+                                   const double* __restrict__ sums,
+                                   int max_dim, float threshold,
+                                   int* __restrict__ gate,
+                                   int* __restrict__ refined_count) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i == 0) *refined_count = 0;
+  __syncthreads();
+  if (i >= n) return;
+  const double e2 = sums[2 * i], t2 = sums[2 * i + 1];
+  const double thr = (double)threshold;
+  // a NaN estimate (broken factorisation) is left alone: info reports it
+  const int on = items[i].d <= max_dim && e2 > thr * thr * t2;
+  gate[i] = on;
+  if (on) atomicAdd(refined_count, 1);
+}
+
+// R = I - (F + add I) X for a 64 x 64 tile, fp64 accumulation, R stored as
+// fp32 into the matrix's W scratch.  256 threads, 4 x 4 outputs each.
+__global__ void __launch_bounds__(256)
+refine_residual_kernel(const MatInfo* __restrict__ mats,
+                       const RefineItem* __restrict__ items, int nitems,
+                       const float* __restrict__ add,
+                       const float* __restrict__ add2,
+                       const int* __restrict__ gate) {
+  __shared__ double As[16][64 + 2];   // As[k][i] = A[i0 + i][k0 + k]
+  __shared__ double Bs[16][64 + 2];   // Bs[k][j] = X[k0 + k][j0 + j]
+  __shared__ int s_item;
+  const int tid = threadIdx.x;
+  if (tid == 0) {
+    int lo = 0, hi = nitems - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (items[mid].tile_begin <= (int)blockIdx.x) lo = mid; else hi = mid - 1;
+    }
+    s_item = lo;
+  }
+  __syncthreads();
+  const int item = s_item;
+  if (gate[item] == 0) return;
+  const RefineItem it = items[item];
+  const MatInfo mi = mats[it.mat];
+  const int d = it.d;
+  const int nt = (d + 63) >> 6;
+  const int lt = blockIdx.x - it.tile_begin;
+  const int i0 = (lt / nt) * 64, j0 = (lt % nt) * 64;
+  const float a1 = add[it.mat], a2 = add2[it.mat];
+  const int ty = tid >> 4, tx = tid & 15;
+  double acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.0;
+  // loaders: A tile 64 rows x 16 k (thread: row tid / 4, k 4 (tid % 4) ..+3);
+  // X tile 16 k x 64 cols (thread: k tid / 16, cols 4 (tid % 16) ..+3)
+  const int ar = tid >> 2, ak = (tid & 3) * 4;
+  const int bk = tid >> 4, bc = (tid & 15) * 4;
+  for (int k0 = 0; k0 < d; k0 += 16) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int gi = i0 + ar, gk = k0 + ak + q;
+      double v = 0.0;
+      if (gi < d && gk < d) {
+        v = (double)mi.F[(long long)gi * d + gk];
+        if (gi == gk) v += (double)damp_of_row(mi, a1, a2, gi);
+      }
+      As[ak + q][ar] = v;
+      const int gk2 = k0 + bk, gj = j0 + bc + q;
+      Bs[bk][bc + q] =
+          (gk2 < d && gj < d) ? (double)mi.inv[(long long)gk2 * d + gj] : 0.0;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      double a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = As[k][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b[j] = Bs[k][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fma(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int gi = i0 + ty * 4 + i;
+    if (gi >= d) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int gj = j0 + tx * 4 + j;
+      if (gj < d)
+        mi.W[(long long)gi * d + gj] =
+            (float)((gi == gj ? 1.0 : 0.0) - acc[i][j]);
+    }
+  }
+}
+
+// inv += Y for the refined matrices; blockIdx.y = item.
+__global__ void __launch_bounds__(256)
+refine_apply_kernel(const MatInfo* __restrict__ mats,
+                    const RefineItem* __restrict__ items,
+                    const int* __restrict__ gate) {
+  if (gate[blockIdx.y] == 0) return;
+  const RefineItem it = items[blockIdx.y];
+  float* inv = mats[it.mat].inv;
+  const long long n = (long long)it.d * it.d;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x)
+    inv[i] += it.Y[i];
+}
+
 constexpr size_t kDiagSmemBytes =
     (DB * (DB + 4) + 24 * DB + 16 * 64) * sizeof(float);   // Lt, Pt, Xr, Tk
 
@@ -404,6 +600,19 @@ struct kfac_inverse_plan {
   std::vector<Launch> launches;
   long long total_elems;
   bool use_tc;
+  // refinement (see refine_* kernels)
+  float* add2_dev;
+  int n_refine;
+  int refine_dmax;
+  int refine_tiles;
+  Launch refine_prod;
+  RefineItem* refine_items_dev;
+  double* refine_sums_dev;
+  double* refine_vec_dev;
+  int* refine_gate_dev;
+  int* refine_count_dev;
+  int refine_max_dim;
+  float refine_threshold;
 };
 
 static size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
@@ -412,7 +621,9 @@ extern "C" size_t kfac_inverse_workspace_bytes(int count, const int* dims) {
   size_t total = 0;
   for (int i = 0; i < count; ++i) {
     if (dims[i] <= 0) return 0;
-    total += 2 * align256((size_t)dims[i] * dims[i] * sizeof(float));
+    const size_t bytes = align256((size_t)dims[i] * dims[i] * sizeof(float));
+    total += 2 * bytes;                              // W, X
+    if (dims[i] <= kRefineDimCap) total += bytes;    // Y of the refinement
   }
   return total;
 }
@@ -448,6 +659,7 @@ extern "C" int kfac_inverse_plan_create(
   // zeros by the wide tiles of the triangular-inverse products.
   KFAC_CUDA(cudaMemset(workspace, 0, need));
   std::vector<MatInfo> mats(count);
+  std::vector<float*> ybuf(count, nullptr);
   char* ws = static_cast<char*>(workspace);
   int dmax = 0;
   long long total_elems = 0;
@@ -458,12 +670,15 @@ extern "C" int kfac_inverse_plan_create(
     m.inv = inverses[i];
     m.W = reinterpret_cast<float*>(ws); ws += bytes;
     m.X = reinterpret_cast<float*>(ws); ws += bytes;
+    if (dims[i] <= kRefineDimCap) {
+      ybuf[i] = reinterpret_cast<float*>(ws); ws += bytes;
+    }
     m.d = dims[i];
     m.partner = partner ? partner[i] : -1;
     m.role = role[i];
     m.l2 = l2_coef ? l2_coef[i] : 0.f;
     m.scale = scale ? scale[i] : 1.f;
-    m.pad_ = 0;
+    m.l2b = m.l2;
     dmax = std::max(dmax, dims[i]);
     total_elems += (long long)dims[i] * dims[i];
   }
@@ -615,6 +830,28 @@ extern "C" int kfac_inverse_plan_create(
     end_gemm(prod);
   }
 
+  // refinement of the matrices of up to kRefineDimCap rows: Y = X R on the
+  // tile engine (Y is symmetric: lower tiles, mirrored), gated per matrix
+  std::vector<RefineItem> ritems;
+  int refine_tiles = 0, refine_dmax = 0;
+  long long vec_elems = 0;
+  for (int i : order) {
+    if (dims[i] > kRefineDimCap) continue;
+    RefineItem it;
+    it.mat = i;
+    it.d = dims[i];
+    it.tile_begin = refine_tiles;
+    it.pad_ = 0;
+    it.Y = ybuf[i];
+    it.vec = reinterpret_cast<double*>(vec_elems);   // offset, fixed up below
+    const int nt = (dims[i] + 63) / 64;
+    refine_tiles += nt * nt;
+    refine_dmax = std::max(refine_dmax, dims[i]);
+    vec_elems += 2LL * dims[i];
+    ritems.push_back(it);
+  }
+  Launch refine_prod = begin_gemm();
+
   kfac_inverse_plan* p = new kfac_inverse_plan();
   p->count = count;
   p->total_elems = total_elems;
@@ -622,7 +859,43 @@ extern "C" int kfac_inverse_plan_create(
   p->use_tc = use_tc;
   p->mats_dev = nullptr; p->trace_dev = nullptr; p->add_dev = nullptr;
   p->info_dev = nullptr; p->ids_dev = nullptr; p->descs_dev = nullptr;
+  p->add2_dev = nullptr; p->refine_items_dev = nullptr;
+  p->refine_sums_dev = nullptr; p->refine_vec_dev = nullptr;
+  p->refine_gate_dev = nullptr; p->refine_count_dev = nullptr;
+  p->n_refine = (int)ritems.size();
+  p->refine_dmax = refine_dmax;
+  p->refine_tiles = refine_tiles;
+  p->refine_max_dim = kRefineDimCap;
+  p->refine_threshold = 3e-5f;
   cudaError_t e = cudaGetDevice(&p->device);
+  if (e == cudaSuccess) e = cudaMalloc(&p->add2_dev, sizeof(float) * count);
+  if (e == cudaSuccess) e = cudaMalloc(&p->refine_count_dev, sizeof(int));
+  if (e == cudaSuccess) e = cudaMemset(p->refine_count_dev, 0, sizeof(int));
+  if (e == cudaSuccess && !ritems.empty()) {
+    const size_t nr = ritems.size();
+    e = cudaMalloc(&p->refine_items_dev, sizeof(RefineItem) * nr);
+    if (e == cudaSuccess) e = cudaMalloc(&p->refine_sums_dev, sizeof(double) * 2 * nr);
+    if (e == cudaSuccess) e = cudaMalloc(&p->refine_vec_dev, sizeof(double) * vec_elems);
+    if (e == cudaSuccess) e = cudaMalloc(&p->refine_gate_dev, sizeof(int) * nr);
+    if (e == cudaSuccess) {
+      for (size_t r = 0; r < nr; ++r) {
+        RefineItem& it = ritems[r];
+        it.vec = p->refine_vec_dev + reinterpret_cast<long long>(it.vec);
+        const int d = it.d;
+        const MatInfo& m = mats[it.mat];
+        GemmDesc g = {};
+        g.A = strided_operand(m.inv, 1, d, d);     // A(k, m) = X[m][k]
+        g.B = strided_operand(m.W, d, 1, d);       // B(k, n) = R[k][n]
+        g.C = it.Y; g.ldc = d; g.M = d; g.N = d; g.K = d;
+        g.alpha = 1.f; g.beta = 0.f; g.flags = G_LOWER | G_MIRROR;
+        g.gate = p->refine_gate_dev + r;
+        push_desc(refine_prod, g);
+      }
+      e = cudaMemcpy(p->refine_items_dev, ritems.data(),
+                     sizeof(RefineItem) * nr, cudaMemcpyHostToDevice);
+    }
+  }
+  p->refine_prod = refine_prod;
   if (e == cudaSuccess) e = cudaMalloc(&p->mats_dev, sizeof(MatInfo) * count);
   if (e == cudaSuccess) e = cudaMalloc(&p->trace_dev, sizeof(float) * count);
   if (e == cudaSuccess) e = cudaMalloc(&p->add_dev, sizeof(float) * count);
@@ -654,11 +927,12 @@ extern "C" int kfac_inverse_plan_run(kfac_inverse_plan* p, float damping,
   KFAC_LAUNCH_CHECK("trace_kernel");
   damping_kernel<<<ceil_div(p->count, 128), 128, 0, st>>>(
       p->mats_dev, p->count, p->trace_dev, damping, use_pi, p->add_dev,
-      diag_dev);
+      p->add2_dev, diag_dev);
   KFAC_LAUNCH_CHECK("damping_kernel");
   {
     dim3 grid(512, p->count);
-    damp_copy_kernel<<<grid, 256, 0, st>>>(p->mats_dev, p->add_dev);
+    damp_copy_kernel<<<grid, 256, 0, st>>>(p->mats_dev, p->add_dev,
+                                           p->add2_dev);
     KFAC_LAUNCH_CHECK("damp_copy_kernel");
   }
   for (const Launch& l : p->launches) {
@@ -675,11 +949,81 @@ extern "C" int kfac_inverse_plan_run(kfac_inverse_plan* p, float damping,
       if (rc != KFAC_OK) return rc;
     }
   }
+  if (p->n_refine > 0 && p->refine_max_dim > 0) {
+    const dim3 pgrid(ceil_div(p->refine_dmax, 8), p->n_refine);
+    for (int stage = 0; stage < 3; ++stage) {
+      refine_probe_kernel<<<pgrid, 256, 0, st>>>(
+          p->mats_dev, p->refine_items_dev, p->add_dev, p->add2_dev,
+          p->refine_sums_dev, stage);
+      KFAC_LAUNCH_CHECK("refine_probe_kernel");
+    }
+    refine_gate_kernel<<<ceil_div(p->n_refine, 256), 256, 0, st>>>(
+        p->refine_items_dev, p->n_refine, p->refine_sums_dev,
+        p->refine_max_dim, p->refine_threshold, p->refine_gate_dev,
+        p->refine_count_dev);
+    KFAC_LAUNCH_CHECK("refine_gate_kernel");
+    refine_residual_kernel<<<p->refine_tiles, 256, 0, st>>>(
+        p->mats_dev, p->refine_items_dev, p->n_refine, p->add_dev,
+        p->add2_dev, p->refine_gate_dev);
+    KFAC_LAUNCH_CHECK("refine_residual_kernel");
+    const Launch& l = p->refine_prod;
+    int rc = p->use_tc
+                 ? launch_tc_grouped(p->descs_dev + l.off, l.n, l.tiles, 0.f,
+                                     0.f, l.tails != 0, st)
+                 : launch_grouped_gemm(p->descs_dev + l.off, l.n, l.tiles, 0.f,
+                                       0.f, st);
+    if (rc != KFAC_OK) return rc;
+    const dim3 agrid(64, p->n_refine);
+    refine_apply_kernel<<<agrid, 256, 0, st>>>(p->mats_dev, p->refine_items_dev,
+                                               p->refine_gate_dev);
+    KFAC_LAUNCH_CHECK("refine_apply_kernel");
+  }
+  return KFAC_OK;
+}
+
+extern "C" int kfac_inverse_plan_set_refine(kfac_inverse_plan* p, int max_dim,
+                                            float threshold) {
+  KFAC_REQUIRE(p != nullptr, "inverse_plan_set_refine: null plan");
+  KFAC_REQUIRE(max_dim >= 0 && threshold >= 0.f,
+               "inverse_plan_set_refine: max_dim=%d threshold=%g", max_dim,
+               (double)threshold);
+  p->refine_max_dim = max_dim < kRefineDimCap ? max_dim : kRefineDimCap;
+  p->refine_threshold = threshold;
+  return KFAC_OK;
+}
+
+extern "C" int kfac_inverse_plan_refined(kfac_inverse_plan* p,
+                                         int* refined_out) {
+  KFAC_REQUIRE(p != nullptr && refined_out != nullptr,
+               "inverse_plan_refined: null argument");
+  KFAC_CUDA(cudaDeviceSynchronize());
+  KFAC_CUDA(cudaMemcpy(refined_out, p->refine_count_dev, sizeof(int),
+                       cudaMemcpyDeviceToHost));
+  return KFAC_OK;
+}
+
+extern "C" int kfac_inverse_plan_set_second_floor(kfac_inverse_plan* p,
+                                                  const float* l2_coef_second) {
+  KFAC_REQUIRE(p != nullptr && l2_coef_second != nullptr,
+               "inverse_plan_set_second_floor: null argument");
+  std::vector<MatInfo> mats(p->count);
+  KFAC_CUDA(cudaDeviceSynchronize());
+  KFAC_CUDA(cudaMemcpy(mats.data(), p->mats_dev, sizeof(MatInfo) * p->count,
+                       cudaMemcpyDeviceToHost));
+  for (int i = 0; i < p->count; ++i) mats[i].l2b = l2_coef_second[i];
+  KFAC_CUDA(cudaMemcpy(p->mats_dev, mats.data(), sizeof(MatInfo) * p->count,
+                       cudaMemcpyHostToDevice));
   return KFAC_OK;
 }
 
 extern "C" int kfac_inverse_plan_destroy(kfac_inverse_plan* p) {
   if (p == nullptr) return KFAC_OK;
+  cudaFree(p->add2_dev);
+  cudaFree(p->refine_items_dev);
+  cudaFree(p->refine_sums_dev);
+  cudaFree(p->refine_vec_dev);
+  cudaFree(p->refine_gate_dev);
+  cudaFree(p->refine_count_dev);
   cudaFree(p->mats_dev);
   cudaFree(p->trace_dev);
   cudaFree(p->add_dev);

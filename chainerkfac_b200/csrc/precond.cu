@@ -136,6 +136,26 @@ __global__ void symv_split_kernel(const float* __restrict__ m, int d, int d0,
   }
 }
 
+// The reference's fallback for a block whose preconditioned gradient contains
+// NaN (batch_normalization.py:159-173 with _check_nan): use the raw gradient.
+// flag[0] is this call's NaN marker (cleared here), flag[1] counts fallbacks.
+__global__ void __launch_bounds__(256)
+symv_nan_fallback_kernel(int* __restrict__ flag, int d, int d0,
+                         const float* __restrict__ x0,
+                         const float* __restrict__ x1, float* y0, float* y1) {
+  __shared__ int f;
+  if (threadIdx.x == 0) f = flag[0];
+  __syncthreads();
+  if (f == 0) return;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    if (i < d0) y0[i] = x0[i]; else y1[i - d0] = x1[i - d0];
+  }
+  if (threadIdx.x == 0) {
+    flag[0] = 0;
+    flag[1] += 1;
+  }
+}
+
 extern "C" int kfac_symv_split(const float* m, int d, int d0, const float* x0,
                                const float* x1, float* y0, float* y1,
                                int* nan_flag_dev, void* stream) {
@@ -146,5 +166,10 @@ extern "C" int kfac_symv_split(const float* m, int d, int d0, const float* x0,
   symv_split_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(
       m, d, d0, x0, x1, y0, y1, nan_flag_dev);
   KFAC_LAUNCH_CHECK("symv_split_kernel");
+  if (nan_flag_dev != nullptr) {
+    symv_nan_fallback_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(
+        nan_flag_dev, d, d0, x0, x1, y0, y1);
+    KFAC_LAUNCH_CHECK("symv_nan_fallback_kernel");
+  }
   return KFAC_OK;
 }

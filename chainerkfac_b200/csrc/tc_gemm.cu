@@ -578,7 +578,10 @@ tc_gemm_kernel(const GemmDesc* __restrict__ descs, int ndesc,
   if (g.flags & G_KBEG_N0) kbeg = max(kbeg, (long long)n0);
   if (g.flags & G_KBEG_M0) kbeg = max(kbeg, (long long)m0);
   if (g.flags & G_KEND_M0) kend = min(kend, (long long)(m0 + TC_BM));
-  const int nkb = kend > kbeg ? (int)((kend - kbeg + TC_BK - 1) / TC_BK) : 0;
+  // a gated-off problem runs no k-blocks and stores nothing
+  const bool gated_off = g.gate != nullptr && *g.gate == 0;
+  const int nkb = (kend > kbeg && !gated_off)
+                      ? (int)((kend - kbeg + TC_BK - 1) / TC_BK) : 0;
   // X^T X on a diagonal tile: the tile's A rows are rows [m0 - n0, m0 - n0 +
   // 128) of its B rows (m0 - n0 is 0 or 128), so only B is staged and the A
   // descriptors point into the B tiles.
@@ -721,7 +724,7 @@ tc_gemm_kernel(const GemmDesc* __restrict__ descs, int ndesc,
                  ::"r"(tmem), "r"(TC_TMEM_COLS)
                  : "memory");
   }
-  if (warp >= TC_PRODUCERS / 32 || ctl->abort_flag) return;
+  if (warp >= TC_PRODUCERS / 32 || ctl->abort_flag || gated_off) return;
 
   if (g.splits > 1) {
     float* p = g.partial + ((long long)split * g.ntiles + lt) * (TC_BM * TC_BN);
@@ -801,6 +804,7 @@ tc_gemm_kernel(const GemmDesc* __restrict__ descs, int ndesc,
         float v = alpha * stage[r * TC_EPI_PITCH + c];
         if (beta != 0.f) v += beta * old[i];
         crow[c] = v;
+        if (g.C2 != nullptr) g.C2[(long long)gr * g.ldc + n0 + c] = v;
         if (mirror) stage[r * TC_EPI_PITCH + c] = v;
       }
     }
@@ -1428,12 +1432,20 @@ struct ReduceItem {     // one output tile whose split partials are summed
   float alpha, beta;
 };
 
+// `items` == nullptr: every block works on `single`, the item of tile 0 of one
+// factor, and takes tile blockIdx.x of it (a lone factor needs no table in
+// device memory, so the call neither allocates nor copies one).
 __global__ void __launch_bounds__(256)
-tc_reduce_kernel(const ReduceItem* __restrict__ items) {
+tc_reduce_kernel(const ReduceItem* __restrict__ items,
+                 const __grid_constant__ ReduceItem single) {
   // Four lanes share one output element: lane q sums the splits
   // q, q+4, q+8, ... (always in that order), then the four sums are added in
   // a fixed tree, so the result does not depend on scheduling.
-  const ReduceItem it = items[blockIdx.x];
+  ReduceItem it = items != nullptr ? items[blockIdx.x] : single;
+  if (items == nullptr) {
+    it.tile = (int)blockIdx.x;
+    it.partial += (long long)blockIdx.x * (TC_BM * TC_BN);
+  }
   int bi, bj;
   tc_tri_tile(it.tile, bi, bj);
   const int d = it.d;
@@ -1871,18 +1883,22 @@ int run_factor_group_tc(int count, const FactorJob* jobs, void* workspace,
   }
   if (!reduces.empty()) {
     void* dev = nullptr;
-    rc = ring_alloc(reduces.size() * sizeof(ReduceItem), &dev);
-    if (rc != KFAC_OK) return rc;
-    KFAC_CUDA(cudaMemcpyAsync(dev, reduces.data(),
-                              reduces.size() * sizeof(ReduceItem),
-                              cudaMemcpyHostToDevice, stream));
+    if (count > 1) {
+      rc = ring_alloc(reduces.size() * sizeof(ReduceItem), &dev);
+      if (rc != KFAC_OK) return rc;
+      KFAC_CUDA(cudaMemcpyAsync(dev, reduces.data(),
+                                reduces.size() * sizeof(ReduceItem),
+                                cudaMemcpyHostToDevice, stream));
+    }
     int dmax = 0;
     for (const ReduceItem& it : reduces) dmax = it.d > dmax ? it.d : dmax;
     const int rmax = dmax < TC_BM ? dmax : TC_BM;
     const int cmax = dmax < TC_BN ? dmax : TC_BN;
     dim3 rgrid((unsigned)reduces.size(), (rmax * cmax + 1023) / 1024);
+    // a lone factor: its items are consecutive tiles of one output, passed
+    // by value (reduces[0] is tile 0)
     tc_reduce_kernel<<<rgrid, 256, 0, stream>>>(
-        static_cast<const ReduceItem*>(dev));
+        static_cast<const ReduceItem*>(dev), reduces[0]);
     KFAC_LAUNCH_CHECK("tc_reduce_kernel");
   }
   return KFAC_OK;

@@ -249,7 +249,7 @@ class InversePlan(object):
     """Batched damped inverse of a fixed set of factor buffers."""
 
     def __init__(self, factors, inverses, partner, role, l2_coef=None,
-                 scale=None):
+                 scale=None, l2_coef_second=None):
         lib = _lib.load()
         self._lib = lib
         self.count = len(factors)
@@ -278,6 +278,27 @@ class InversePlan(object):
             _p(self.workspace), self.workspace.numel(),
             ctypes.byref(handle)), 'kfac_inverse_plan_create')
         self._handle = handle
+        if l2_coef_second is not None and any(r == 2 for r in role):
+            _lib.check(lib.kfac_inverse_plan_set_second_floor(
+                handle, _lib.float_array(l2_coef_second)),
+                'kfac_inverse_plan_set_second_floor')
+        refine = os.environ.get('KFAC_REFINE_MAX_DIM')
+        if refine is not None:
+            self.set_refine(int(refine))
+
+    def set_refine(self, max_dim, threshold=3e-5):
+        """Refinement of ill-conditioned factors of up to ``max_dim`` rows
+        (0: off); see kfac_inverse_plan_set_refine."""
+        _lib.check(self._lib.kfac_inverse_plan_set_refine(
+            self._handle, int(max_dim), float(threshold)),
+            'kfac_inverse_plan_set_refine')
+
+    def refined(self):
+        """Number of factors the last run refined (synchronises)."""
+        n = ctypes.c_int(0)
+        _lib.check(self._lib.kfac_inverse_plan_refined(
+            self._handle, ctypes.byref(n)), 'kfac_inverse_plan_refined')
+        return n.value
 
     def run(self, damping, use_pi=True):
         _lib.check(self._lib.kfac_inverse_plan_run(
@@ -306,13 +327,14 @@ class InversePlanSet(object):
     layer) stay in one plan so that pi sees both traces."""
 
     def __init__(self, factors, inverses, partner, role, l2_coef=None,
-                 scale=None, bounds=None):
+                 scale=None, bounds=None, l2_coef_second=None):
         n = len(factors)
         if bounds is None:
             bounds = tuple(int(b) for b in os.environ.get(
                 'KFAC_CLASS_BOUNDS', '1024,3000').split(','))
         l2_coef = l2_coef if l2_coef is not None else [0.0] * n
         scale = scale if scale is not None else [1.0] * n
+        second = l2_coef_second if l2_coef_second is not None else l2_coef
 
         def size_class(i):
             d = max(factors[i].shape[0],
@@ -330,7 +352,7 @@ class InversePlanSet(object):
                 [factors[i] for i in idx], [inverses[i] for i in idx],
                 [pos[partner[i]] if partner[i] >= 0 else -1 for i in idx],
                 [role[i] for i in idx], [l2_coef[i] for i in idx],
-                [scale[i] for i in idx]))
+                [scale[i] for i in idx], [second[i] for i in idx]))
             self.index.append(idx)
         self.streams = [torch.cuda.Stream() for _ in self.plans[1:]]
         # optional early start of a class (see start_class)
@@ -380,6 +402,10 @@ class InversePlanSet(object):
                     after_class(c)
         if after_class is not None:
             for c in self._early:
+                # what the caller queued on the current stream since the
+                # class was started (optimizer pre-hooks on the gradients,
+                # for instance) comes before the class's follow-up work
+                self.early_streams[c].wait_event(start)
                 with torch.cuda.stream(self.early_streams[c]):
                     after_class(c)
                     ev = torch.cuda.Event()
@@ -396,6 +422,13 @@ class InversePlanSet(object):
         for ev in self._early.values():
             cur.wait_event(ev)
         self._early = {}
+
+    def set_refine(self, max_dim, threshold=3e-5):
+        for p in self.plans:
+            p.set_refine(max_dim, threshold)
+
+    def refined(self):
+        return sum(p.refined() for p in self.plans)
 
     def gather(self, attr):
         """Per-factor values (info / diag) in the caller's original order."""

@@ -71,6 +71,11 @@ class UpdateRule(object):
         if self._state is None:
             self._state = {}
             self.init_state(param)
+        # gradients of a scaled loss are un-scaled here, as in Chainer's
+        # UpdateRule.update
+        if getattr(param, '_loss_scale', None) is not None and \
+                param.grad is not None:
+            param.grad /= param._loss_scale
         for hook in self._pre_update_hooks.values():
             hook(self, param)
         self.update_core(param)

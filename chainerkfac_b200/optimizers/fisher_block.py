@@ -91,7 +91,8 @@ class FisherBlock(object):
 
     # -- damped inverse (fisher_block.py:165-179) -------------------------
     def plan_entries(self):
-        """(role, l2_coef, scale) for each factor, see kfac_inverse_plan."""
+        """(role, l2_coef, scale[, l2_coef_second]) for each factor, see
+        kfac_inverse_plan_create / kfac_inverse_plan_set_second_floor."""
         raise NotImplementedError
 
     def ensure_invs(self):
@@ -109,7 +110,8 @@ class FisherBlock(object):
             self._plan = ops.InversePlan(
                 self.cov_emas, self.invs, partner,
                 [e[0] for e in entries], [e[1] for e in entries],
-                [e[2] for e in entries])
+                [e[2] for e in entries],
+                [e[3] if len(e) > 3 else e[1] for e in entries])
         self._plan.run(self.damping, self._pi_type == PI_TYPE_TRACENORM)
         self.set_diag_vals(self._plan.diag)
 

@@ -64,10 +64,12 @@ class FisherBlockBatchNormalization(FisherBlock):
         return ops.factor_dense(grads, False, alpha=1.0 / n, out=out)
 
     def plan_entries(self):
-        # batch_normalization.py:133-157: max(l2_coef, damping) * stab_coeff
-        l2 = max(getattr(self.link.gamma, 'l2_coef', 0.0) or 0.0,
-                 getattr(self.link.beta, 'l2_coef', 0.0) or 0.0)
-        return [(2, l2, float(self.stab_coeff))]
+        # batch_normalization.py:133-157: max(l2_coef, damping) * stab_coeff,
+        # with gamma's l2_coef for the first half of the diagonal and beta's
+        # for the second
+        l2_gamma = getattr(self.link.gamma, 'l2_coef', 0.0) or 0.0
+        l2_beta = getattr(self.link.beta, 'l2_coef', 0.0) or 0.0
+        return [(2, l2_gamma, float(self.stab_coeff), l2_beta)]
 
     def set_diag_vals(self, diag):
         self.diag_val_backward = diag[0]
@@ -79,30 +81,34 @@ class FisherBlockBatchNormalization(FisherBlock):
 
     def update_kfgrads(self):
         # batch_normalization.py:159-191: F_inv [grad_gamma; grad_beta]; on
-        # NaN the raw gradients are used instead (checked on the host, as the
-        # reference does with xp.any(xp.isnan(..)))
+        # NaN the raw gradients are used instead (the reference checks on the
+        # host with xp.any(xp.isnan(..)); here the library substitutes them
+        # on the device, without a synchronisation)
         self.check_attr('invs')
         gamma, beta = self.link.gamma, self.link.beta
         for p in (gamma, beta):
             if getattr(p, 'kfgrad', None) is None or p.kfgrad is p.grad:
                 p.kfgrad = torch.empty_like(p.data)
         if self._nan_flag is None:
-            self._nan_flag = torch.zeros(1, dtype=torch.int32,
+            self._nan_flag = torch.zeros(2, dtype=torch.int32,
                                          device=gamma.data.device)
+            self._nan_seen = 0
         ops.symv_split(self.invs[0], gamma.grad.contiguous(),
                        beta.grad.contiguous(), gamma.kfgrad, beta.kfgrad,
                        self._nan_flag)
 
     def check_nan(self):
-        """Host check of the NaN flag (synchronises); substitutes the raw
-        gradients like ``_check_nan`` of the reference."""
-        if self._nan_flag is not None and int(self._nan_flag.item()) != 0:
+        """True (with the reference's warning) when a step since the last
+        check fell back to the raw gradients because its preconditioned
+        gradients contained NaN.  Reads a device counter: synchronises."""
+        if self._nan_flag is None:
+            return False
+        count = int(self._nan_flag[1].item())
+        if count != self._nan_seen:
+            self._nan_seen = count
             warnings.warn(
                 'Detected NaN in the kfgrads of the batch normalization layer'
                 'Substitue ``grad`` as ``kfgrad`` to avoid crashing')
-            self.link.gamma.kfgrad = self.link.gamma.grad
-            self.link.beta.kfgrad = self.link.beta.grad
-            self._nan_flag.zero_()
             return True
         return False
 

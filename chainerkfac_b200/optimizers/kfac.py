@@ -293,6 +293,10 @@ class KFAC(_base.GradientMethod):
                 loss.backward(torch.full_like(loss, self._loss_scale))
             else:
                 loss.backward()
+        # what Chainer's backward(loss_scale=) leaves on every parameter: the
+        # update rules divide the (scaled) gradients by it
+        for param in self.target.params():
+            param._loss_scale = self._loss_scale
         # with a valid inverse plan the factor build is pipelined with the
         # inverses inside update_kfgrads; otherwise build everything now
         self._factors_pending = self._pipeline_ready()
@@ -345,29 +349,50 @@ class KFAC(_base.GradientMethod):
             'acc_count {} should not be larger than acc_iters {}'.format(
                 self.acc_count, self.acc_iters))
 
-    def accumulate_grads(self):
+    def _accumulate_group(self, pairs):
+        """acc += x / acc_iters for (x, acc) pairs, acc = x / acc_iters for
+        (x, None); one grouped launch each for the new and for the existing
+        accumulators.  Returns the accumulators in order."""
         s = 1.0 / self.acc_iters
-        for param in self.target.params():
-            if param.grad is None:
-                continue
-            g = param.grad.contiguous()
-            if getattr(param, 'acc_grad', None) is None:
-                param.acc_grad = torch.empty_like(g)
-                ops.axpby(s, g, 0.0, param.acc_grad, param.acc_grad)
+        accs, first, rest = [], [], []
+        for x, acc in pairs:
+            if acc is None:
+                acc = torch.empty_like(x)
+                first.append((x, acc))
             else:
-                ops.axpby(s, g, 1.0, param.acc_grad, param.acc_grad)
+                rest.append((x, acc))
+            accs.append(acc)
+        for group, b in ((first, 0.0), (rest, 1.0)):
+            for k in range(0, len(group), 1024):
+                part = group[k:k + 1024]
+                xs = [x for x, _ in part]
+                outs = [a for _, a in part]
+                ops.axpby_group(s, xs, b, outs, outs)
+        return accs
+
+    def accumulate_grads(self):
+        """``kfac.py:286-293``."""
+        params = [p for p in self.target.params() if p.grad is not None]
+        accs = self._accumulate_group(
+            [(p.grad.contiguous(), getattr(p, 'acc_grad', None))
+             for p in params])
+        for p, a in zip(params, accs):
+            p.acc_grad = a
 
     def accumulate_covs(self):
-        s = 1.0 / self.acc_iters
+        """``kfac.py:295-304``."""
+        pairs = []
         for fblock in self.fblocks:
             fblock.check_attr('covs')
-            if getattr(fblock, 'acc_covs', None) is None:
-                fblock.acc_covs = [torch.empty_like(c) for c in fblock.covs]
-                for c, a in zip(fblock.covs, fblock.acc_covs):
-                    ops.axpby(s, c, 0.0, a, a)
-            else:
-                for c, a in zip(fblock.covs, fblock.acc_covs):
-                    ops.axpby(s, c, 1.0, a, a)
+            old = getattr(fblock, 'acc_covs', None)
+            for j, c in enumerate(fblock.covs):
+                pairs.append((c, None if old is None else old[j]))
+        accs = self._accumulate_group(pairs)
+        k = 0
+        for fblock in self.fblocks:
+            n = len(fblock.covs)
+            fblock.acc_covs = accs[k:k + n]
+            k += n
 
     # -- curvature stages (kfac.py:306-310), batched over blocks ------------
     def _plan_for(self, fblocks):
@@ -379,18 +404,22 @@ class KFAC(_base.GradientMethod):
         if entry is not None:
             entry[0].close()
         factors, inverses, partner, role, l2, scale = [], [], [], [], [], []
+        l2_second = []
         for fb in fblocks:
             ents = fb.plan_entries()
             base = len(factors)
             fb.ensure_invs()
-            for j, (rl, l2c, sc) in enumerate(ents):
+            for j, ent in enumerate(ents):
+                rl, l2c, sc = ent[:3]
+                l2_second.append(ent[3] if len(ent) > 3 else l2c)
                 factors.append(fb.cov_emas[j])
                 inverses.append(fb.invs[j])
                 partner.append(base + 1 - j if len(ents) == 2 else -1)
                 role.append(rl)
                 l2.append(l2c)
                 scale.append(sc)
-        plan = ops.InversePlanSet(factors, inverses, partner, role, l2, scale)
+        plan = ops.InversePlanSet(factors, inverses, partner, role, l2, scale,
+                                  l2_coef_second=l2_second)
         self._plans[key] = (plan, bufs)
         return plan
 
@@ -497,6 +526,7 @@ class KFAC(_base.GradientMethod):
         rule = param.update_rule
         return (self.fuse_update and isinstance(rule, KFACUpdateRule) and
                 rule.enabled and param._loss_scale is None and
+                rule.hyperparam.lr == self.hyperparam.lr and
                 not rule._pre_update_hooks and not rule._post_update_hooks)
 
     def _precondition(self, conn, ws_key=None):

@@ -215,6 +215,30 @@ int kfac_inverse_plan_create(int count, const int* dims,
 int kfac_inverse_plan_run(kfac_inverse_plan* plan, float damping, int use_pi,
                           int* info_dev, float* diag_dev, void* stream);
 
+/* Iterative refinement of ill-conditioned factors (not in the reference,
+ * whose NumPy path reaches the same accuracy through LAPACK): after the
+ * inverse X of a factor of at most `max_dim` rows (capped at 1024, the size
+ * the workspace reserves room for) a probe estimates its relative error; where
+ * that exceeds `threshold`, one step X <- X + X (I - (F + add I) X) runs with
+ * the residual accumulated in fp64.  Defaults of a new plan: max_dim = 1024,
+ * threshold = 3e-5; max_dim = 0 switches the step off.  Takes effect at the
+ * next run. */
+int kfac_inverse_plan_set_refine(kfac_inverse_plan* plan, int max_dim,
+                                 float threshold);
+/* Synchronises the device; *refined_out = number of factors the last run
+ * refined. */
+int kfac_inverse_plan_refined(kfac_inverse_plan* plan, int* refined_out);
+
+/* Role-2 blocks only (others ignore it): the rows of the second half of the
+ * diagonal (the shift parameters of a BatchNormalization block) are damped
+ * with max(l2_coef_second[i], damping) * scale[i] instead of the first half's
+ * floor; FisherBlockBatchNormalization.get_diagvals
+ * (normalizations/batch_normalization.py:133-157) floors gamma and beta
+ * separately.  `l2_coef_second` is a host array of `count` floats.
+ * Synchronises the device. */
+int kfac_inverse_plan_set_second_floor(kfac_inverse_plan* plan,
+                                       const float* l2_coef_second);
+
 int kfac_inverse_plan_destroy(kfac_inverse_plan* plan);
 
 /* ------------------------------------------------------------ precondition
@@ -247,9 +271,12 @@ int kfac_precondition(int count, const int* dG, const int* dW,
  * preconditioning F_inv * [grad_gamma; grad_beta]
  * (normalizations/batch_normalization.py:175-191). x is given in two pieces
  * (x0 of length d0, then x1 of length d - d0; x1 may be NULL when d0 == d);
- * y likewise.  nan_flag_dev (device int, may be NULL) is set to 1 when any
- * output is NaN, which is the condition of the reference's raw-gradient
- * fallback. */
+ * y likewise.  nan_flag_dev (two device ints, zero-initialised by the caller;
+ * may be NULL): when any output is NaN the whole of y is replaced by x, which
+ * is the reference's raw-gradient fallback (_check_nan,
+ * normalizations/batch_normalization.py:14-31,165-166), done on the device by
+ * a second small launch; nan_flag_dev[0] is scratch (0 again afterwards),
+ * nan_flag_dev[1] counts the fallbacks taken so far. */
 int kfac_symv_split(const float* m, int d, int d0, const float* x0,
                     const float* x1, float* y0, float* y1, int* nan_flag_dev,
                     void* stream);

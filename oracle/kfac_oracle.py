@@ -250,6 +250,21 @@ def connection_step(A, G, grad_W, grad_b, damping, ema_A=None, ema_G=None,
 # Wire format and collectives (communicators/pure_nccl_communicator.py).
 # --------------------------------------------------------------------------
 
+def accumulate(samples, acc_iters):
+    """``KFAC.accumulate_grads`` / ``accumulate_covs``
+    (``optimizers/kfac.py:286-304``): the running sum of ``x * (1 /
+    acc_iters)`` over the micro-steps, in the arrays' own precision and in
+    arrival order."""
+    acc = None
+    for x in samples:
+        new = x * (1 / acc_iters)
+        if acc is None:
+            acc = new
+        else:
+            acc += new
+    return acc
+
+
 def pack_lower(a):
     """Packed row-major lower triangle incl. diagonal:
     dst[r(r+1)/2 + c] = a[r, c], c <= r (``pure_nccl_communicator.py:343-349``).
@@ -335,51 +350,3 @@ def all_gather_v_sim(per_rank_arrays):
 def split_indices(n_blocks, size):
     """Ownership of ``kfac.py:344-348``: contiguous ``np.array_split``."""
     return [idx.tolist() for idx in np.array_split(np.arange(n_blocks), size)]
-
-
-# --------------------------------------------------------------------------
-# Layer tables of the benchmark configurations.
-# --------------------------------------------------------------------------
-
-def resnet50_layers(batch=32, image=224, classes=1000):
-    """Conv/fc layers of a vanilla ResNet-50 (v1.5: stride on the 3x3) as
-    dicts with the geometry the factor kernels need.  Returned in network
-    order; 53 convolutions + 1 fully connected layer."""
-    layers = []
-
-    def conv(name, cin, cout, k, s, p, hin, bias=False):
-        ho = conv_out_size(hin, k, s, p)
-        layers.append(dict(name=name, kind='conv', cin=cin, cout=cout, k=k,
-                           stride=s, pad=p, hin=hin, hout=ho, bias=bias,
-                           n=batch))
-        return ho
-
-    h = conv('conv1', 3, 64, 7, 2, 3, image, bias=True)
-    h = conv_out_size(h, 3, 2, 1)  # 3x3/2 max pool
-    cin = 64
-    for stage, (blocks, mid) in enumerate(
-            [(3, 64), (4, 128), (6, 256), (3, 512)], start=1):
-        for b in range(blocks):
-            s = 2 if (b == 0 and stage > 1) else 1
-            pre = 'res%d.%d.' % (stage, b)
-            hin = h
-            conv(pre + 'conv1', cin, mid, 1, 1, 0, hin)
-            h2 = conv(pre + 'conv2', mid, mid, 3, s, 1, hin)
-            conv(pre + 'conv3', mid, mid * 4, 1, 1, 0, h2)
-            if b == 0:
-                conv(pre + 'short', cin, mid * 4, 1, s, 0, hin)
-            cin = mid * 4
-            h = h2
-    layers.append(dict(name='fc', kind='linear', cin=cin, cout=classes,
-                       bias=True, n=batch))
-    return layers
-
-
-def layer_dims(layer):
-    """(dA, dG, rows_A, rows_G) of a layer dict."""
-    if layer['kind'] == 'linear':
-        return (layer['cin'] + int(layer['bias']), layer['cout'],
-                layer['n'], layer['n'])
-    dA = layer['cin'] * layer['k'] ** 2 + int(layer['bias'])
-    rows = layer['n'] * layer['hout'] ** 2
-    return dA, layer['cout'], rows, rows

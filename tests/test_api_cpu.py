@@ -13,6 +13,7 @@ import torch.multiprocessing as mp
 from torch import nn
 
 from oracle import kfac_oracle as orc
+import bench_workloads as bw
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
@@ -54,7 +55,7 @@ def test_public_interface_and_defaults():
 
 def test_balanced_ownership_is_deterministic_and_even():
     from chainerkfac_b200.optimizers.kfac import balanced_split
-    dims = [orc.layer_dims(l) for l in orc.resnet50_layers()]
+    dims = [bw.layer_dims(l) for l in bw.resnet50_layers()]
     costs = [float(a) ** 3 + float(g) ** 3 for a, g, _, _ in dims]
     for size in (2, 4, 8):
         owned = balanced_split(costs, size)

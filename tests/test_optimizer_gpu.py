@@ -185,28 +185,96 @@ def test_running_average_over_steps_stays_undamped():
     assert rel(host(fb.cov_emas[0]), want) < FACTOR_TOL
 
 
-def test_accumulation_matches_one_big_step():
+def _capture_mlp(model, x, t):
+    """Per-layer inputs, output gradients and parameter gradients of one
+    micro-batch by plain autograd (no optimizer involved)."""
+    rec, handles = {}, []
+    for name in ('l1', 'l2', 'l3'):
+        def fwd(mod, inp, out, name=name):
+            rec[name + '.x'] = host(inp[0])
+            out.register_hook(lambda gr, name=name: rec.__setitem__(
+                name + '.gy', host(gr)))
+        handles.append(getattr(model, name).register_forward_hook(fwd))
+    model.zero_grad(set_to_none=True)
+    F.cross_entropy(model(x), t).backward()
+    for h in handles:
+        h.remove()
+    for name in ('l1', 'l2', 'l3'):
+        m = getattr(model, name)
+        rec[name + '.gW'] = host(m.weight.grad)
+        rec[name + '.gb'] = host(m.bias.grad)
+        rec[name + '.W'] = host(m.weight).copy()
+    model.zero_grad(set_to_none=True)
+    return rec
+
+
+def test_accumulation_matches_oracle():
+    """acc_iters micro-steps on different micro-batches against the
+    reference's accumulation rule (kfac.py:259-304) restated in the oracle:
+    accumulated factors and gradients, then one K-FAC step on them."""
     import chainerkfac_b200 as ck
     torch.manual_seed(2)
-    m1 = MLP((6, 5, 5, 3)).cuda()
-    m2 = MLP((6, 5, 5, 3)).cuda()
-    m2.load_state_dict(m1.state_dict())
-    x = torch.rand(8, 6, device='cuda')
-    t = torch.randint(0, 3, (8,), device='cuda')
-    o1 = ck.KFAC(lr=0.1, cov_ema_decay=1.0, damping=1e-2, acc_iters=2)
-    o1.setup(m1)
-    for _ in range(2):       # same micro-batch twice == one step on it
-        o1.update(lambda a, b: F.cross_entropy(m1(a), b), x, t)
-    assert o1.t == 1 and o1.acc_count == 0
-    o2 = ck.KFAC(lr=0.1, cov_ema_decay=1.0, damping=1e-2)
-    o2.setup(m2)
-    o2.update(lambda a, b: F.cross_entropy(m2(a), b), x, t)
-    for p1, p2 in zip(m1.parameters(), m2.parameters()):
-        assert rel(host(p1), host(p2)) < 1e-5
+    acc_iters, damping, lr = 3, 1e-2, 0.1
+    model = MLP((6, 5, 5, 3)).cuda()
+    xs = [torch.rand(8, 6, device='cuda') for _ in range(acc_iters)]
+    ts = [torch.randint(0, 3, (8,), device='cuda') for _ in range(acc_iters)]
+    recs = [_capture_mlp(model, x, t) for x, t in zip(xs, ts)]
+    opt = ck.KFAC(lr=lr, momentum=0.0, cov_ema_decay=1.0, damping=damping,
+                  acc_iters=acc_iters)
+    opt.setup(model)
+    for i, (x, t) in enumerate(zip(xs, ts)):
+        opt.update(lambda a, b: F.cross_entropy(model(a), b), x, t)
+        assert opt.acc_count == (i + 1) % acc_iters
+        assert opt.t == (1 if i + 1 == acc_iters else 0)
+    blocks = {fb.linkname: fb for fb in opt.fblocks}
+    for name in ('l1', 'l2', 'l3'):
+        A = orc.accumulate([orc.linear_A(r[name + '.x'], True) for r in recs],
+                           acc_iters)
+        G = orc.accumulate([orc.linear_G(r[name + '.gy']) for r in recs],
+                           acc_iters)
+        gW = orc.accumulate([r[name + '.gW'] for r in recs], acc_iters)
+        gb = orc.accumulate([r[name + '.gb'] for r in recs], acc_iters)
+        fb = blocks['/' + name]
+        assert rel(host(fb.cov_forward), A) < FACTOR_TOL
+        assert rel(host(fb.cov_backward), G) < FACTOR_TOL
+        assert rel(host(fb.link.W.grad), gW) < 1e-5
+        want = orc.connection_step(A, G, gW, gb, damping)
+        assert rel(host(fb.link.W.kfgrad), want['kfgrad_W']) < KFGRAD_TOL
+        assert rel(host(fb.link.b.kfgrad), want['kfgrad_b']) < KFGRAD_TOL
+        W = recs[0][name + '.W'].copy()
+        orc.momentum_update(W, np.zeros_like(W), want['kfgrad_W'], lr, 0.0)
+        assert rel(host(fb.link.W.data), W) < 1e-5
+
+
+@pytest.mark.parametrize('fuse', [True, False])
+def test_loss_scale_gives_the_unscaled_trajectory(fuse):
+    """``KFAC(loss_scale=s)`` scales the backward seed, un-scales the output
+    gradients inside the factors (linear.py:34-36) and divides the
+    preconditioned gradients by s before the update (kfac.py:72-78): the
+    weights must follow the trajectory of the run without a scale."""
+    import chainerkfac_b200 as ck
+    x = torch.rand(16, 12, device='cuda',
+                   generator=torch.Generator(device='cuda').manual_seed(3))
+    t = torch.randint(0, 5, (16,), device='cuda',
+                      generator=torch.Generator(device='cuda').manual_seed(4))
+    finals = []
+    for scale in (None, 128.0):
+        torch.manual_seed(7)
+        model = MLP((12, 9, 9, 5)).cuda()
+        opt = ck.KFAC(lr=0.05, momentum=0.9, cov_ema_decay=0.9, damping=1e-2,
+                      loss_scale=scale)
+        opt.setup(model)
+        opt.fuse_update = fuse
+        init = [host(p).copy() for p in model.parameters()]
+        for _ in range(3):
+            opt.update(lambda a, b: F.cross_entropy(model(a), b), x, t)
+        finals.append([host(p) - w for p, w in zip(model.parameters(), init)])
+    for a, b in zip(*finals):
+        assert rel(b, a) < KFGRAD_TOL
 
 
 def test_bench_resnet50_step_runs():
-    from chainerkfac_b200.bench_model import build_training_step
+    from bench_model import build_training_step
     step, h2d, d2h = build_training_step(
         torch.device('cuda', 0), 2, 1, 0, cov_ema_decay=0.9, damping=2.5e-4,
         lr=0.01, momentum=0.9, image=64, classes=10)

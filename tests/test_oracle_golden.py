@@ -5,6 +5,7 @@ import numpy as np
 import pytest
 
 from oracle import kfac_oracle as orc
+import bench_workloads as bw
 
 TOL = 2e-6
 
@@ -168,9 +169,9 @@ def test_collective_semantics():
 
 
 def test_resnet50_table():
-    layers = orc.resnet50_layers()
+    layers = bw.resnet50_layers()
     assert len(layers) == 54
-    dims = [orc.layer_dims(l) for l in layers]
+    dims = [bw.layer_dims(l) for l in layers]
     assert dims[0] == (148, 64, 401408, 401408)
     assert dims[-1] == (2049, 1000, 32, 32)
     assert max(d[0] for d in dims) == 4608

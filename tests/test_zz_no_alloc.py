@@ -87,3 +87,58 @@ def test_noalloc_rejects_shapes_beyond_the_built_in_scratch():
     assert rc == 3
     msg = lib.kfac_last_error().decode()
     assert 'scratch' in msg and str(32 << 20) in msg
+
+
+_FIRST_CALL_SCRIPT = r'''
+import ctypes, sys
+import torch
+from chainerkfac_b200 import _lib
+
+lib = _lib.load()
+vp = lambda t: ctypes.c_void_p(t.data_ptr())
+g = torch.Generator(device='cuda'); g.manual_seed(5)
+x = torch.rand((60000, 200), device='cuda', generator=g)
+out = torch.zeros((201, 201), device='cuda')
+ref = torch.zeros((201, 201), device='cuda')
+need = lib.kfac_factor_workspace_bytes(60000, 201)
+ws = torch.empty(max(need, 256), dtype=torch.uint8, device='cuda')
+status = ctypes.c_int(-1)
+# loads the library's device code (and with it the built-in scratch array)
+# without touching any of its allocating paths
+_lib.check(lib.kfac_tc_status(ctypes.byref(status)), 'kfac_tc_status')
+torch.cuda.synchronize()
+free0, _ = torch.cuda.mem_get_info()
+_lib.check(lib.kfac_factor_dense_noalloc(vp(x), 60000, 200, 200, 1,
+                                         1.0 / 60000, 0.0, vp(out), None),
+           'kfac_factor_dense_noalloc')
+torch.cuda.synchronize()
+free1, _ = torch.cuda.mem_get_info()
+_lib.check(lib.kfac_factor_dense(vp(x), 60000, 200, 200, 1, 1.0 / 60000, 0.0,
+                                 vp(ref), vp(ws), ws.numel(), None),
+           'kfac_factor_dense')
+torch.cuda.synchronize()
+err = float((out.double() - ref.double()).norm() / ref.double().norm())
+print('RESULT', need, free0 - free1, err)
+'''
+
+
+def test_noalloc_as_first_call_of_a_process_leaves_free_memory_unchanged():
+    """The entry point must not allocate even when nothing has warmed the
+    library up: in a fresh process, with the library's device code loaded
+    eagerly so that code loading cannot be mistaken for an allocation, the
+    device's free memory is the same before and after the first call."""
+    import os
+    import subprocess
+    import sys
+    env = dict(os.environ)
+    env['CUDA_MODULE_LOADING'] = 'EAGER'
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env['PYTHONPATH'] = root + os.pathsep + env.get('PYTHONPATH', '')
+    r = subprocess.run([sys.executable, '-c', _FIRST_CALL_SCRIPT], env=env,
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout + r.stderr
+    line = [l for l in r.stdout.splitlines() if l.startswith('RESULT')][-1]
+    need, drop, err = line.split()[1:]
+    assert int(need) > 0                 # the shape does use the scratch
+    assert int(drop) < (1 << 20), 'free memory fell by %s bytes' % drop
+    assert float(err) < FACTOR_TOL
