@@ -62,6 +62,7 @@ SIGNATURES = {
     'kfac_inverse_plan_run': (I, [VP, F, I, VP, VP, VP]),
     'kfac_inverse_plan_set_refine': (I, [VP, I, F]),
     'kfac_inverse_plan_refined': (I, [VP, c_int_p]),
+    'kfac_inverse_plan_error_estimates': (I, [VP, c_float_p]),
     'kfac_inverse_plan_set_second_floor': (I, [VP, c_float_p]),
     'kfac_inverse_plan_destroy': (I, [VP]),
     'kfac_precond_workspace_bytes': (SZ, [I, c_int_p, c_int_p, c_int_p]),

@@ -47,6 +47,9 @@ inline int ceil_div(int64_t a, int64_t b) { return (int)((a + b - 1) / b); }
 
 // Counter behind kfac_launch_count().
 void count_launch();
+// Add n (replayed graph nodes; negative: launches that were only captured).
+void count_launches(long long n);
+long long launch_count_now();
 
 // Slice of a small per-device ring of device memory for descriptor tables
 // built per call (see pack.cu).

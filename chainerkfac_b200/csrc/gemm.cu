@@ -12,6 +12,12 @@ char* error_buffer() { return g_err; }
 
 static std::atomic<long long> g_launches(0);
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+void count_launches(long long n) {
+  g_launches.fetch_add(n, std::memory_order_relaxed);
+}
+long long launch_count_now() {
+  return g_launches.load(std::memory_order_relaxed);
+}
 
 int sm_count() {
   static int cached[64] = {0};

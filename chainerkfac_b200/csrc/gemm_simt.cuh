@@ -268,6 +268,9 @@ int launch_grouped_gemm(const GemmDesc* descs_dev, int ndesc, int total_tiles,
 // Tensor-core engine (tc_gemm.cu): 128 x 256 tiles, tcgen05 split-TF32.
 int engine();   // 1: tensor cores (default), 0: fp32 FFMA tiles
 int tc_tiles(GemmDesc& g);
+// Opt the tile kernels into their shared-memory sizes on the current device
+// (once per device; the launch helpers call it, plans call it before capture).
+int tc_prepare();
 int launch_tc_grouped(const GemmDesc* descs_dev, int ndesc, int total_tiles,
                       float lr, float momentum, bool tails,
                       cudaStream_t stream);

@@ -33,6 +33,33 @@ struct MatInfo {
   float l2b;      // role 2: floor of the second half of the diagonal
 };
 
+// Per-run arguments, kept in device memory so that a captured CUDA graph of
+// the plan's launches can be replayed with new values: a one-thread kernel
+// ahead of the graph writes them.
+struct RunParams {
+  float damping;
+  int use_pi;
+  int refine_max_dim;
+  float refine_threshold;
+  // CUDA graph of one run (captured on first use)
+  RunParams* params_dev;
+  cudaStream_t cap_stream;
+  cudaGraphExec_t graph_exec;
+  int* graph_info;
+  float* graph_diag;
+  long long graph_launches;
+  bool graph_ok;
+};
+
+__global__ void set_run_params_kernel(RunParams* prm, float damping,
+                                      int use_pi, int refine_max_dim,
+                                      float refine_threshold) {
+  prm->damping = damping;
+  prm->use_pi = use_pi;
+  prm->refine_max_dim = refine_max_dim;
+  prm->refine_threshold = refine_threshold;
+}
+
 __global__ void trace_kernel(const MatInfo* __restrict__ mats,
                              float* __restrict__ trace, int* __restrict__ info) {
   const MatInfo mi = mats[blockIdx.x];
@@ -54,12 +81,15 @@ __global__ void trace_kernel(const MatInfo* __restrict__ mats,
 }
 
 __global__ void damping_kernel(const MatInfo* __restrict__ mats, int count,
-                               const float* __restrict__ trace, float damping,
-                               int use_pi, float* __restrict__ add,
+                               const float* __restrict__ trace,
+                               const RunParams* __restrict__ prm,
+                               float* __restrict__ add,
                                float* __restrict__ add2,
                                float* __restrict__ add_out) {
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= count) return;
+  const float damping = prm->damping;
+  const int use_pi = prm->use_pi;
   const MatInfo mi = mats[i];
   float g = fmaxf(mi.l2, damping);
   float v, v2;
@@ -424,7 +454,8 @@ refine_probe_kernel(const MatInfo* __restrict__ mats,
                     const RefineItem* __restrict__ items,
                     const float* __restrict__ add,
                     const float* __restrict__ add2, double* __restrict__ sums,
-                    int stage) {
+                    const RunParams* __restrict__ prm, int stage) {
+  if (prm->refine_max_dim <= 0) return;
   const RefineItem it = items[blockIdx.y];
   const MatInfo mi = mats[it.mat];
   const int d = it.d;
@@ -460,9 +491,11 @@ refine_probe_kernel(const MatInfo* __restrict__ mats,
 
 __global__ void refine_gate_kernel(const RefineItem* __restrict__ items, int n,
                                    const double* __restrict__ sums,
-                                   int max_dim, float threshold,
+                                   const RunParams* __restrict__ prm,
                                    int* __restrict__ gate,
                                    int* __restrict__ refined_count) {
+  const int max_dim = prm->refine_max_dim;
+  const float threshold = prm->refine_threshold;
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i == 0) *refined_count = 0;
   __syncthreads();
@@ -613,6 +646,14 @@ struct kfac_inverse_plan {
   int* refine_count_dev;
   int refine_max_dim;
   float refine_threshold;
+  // CUDA graph of one run (captured on first use)
+  RunParams* params_dev;
+  cudaStream_t cap_stream;
+  cudaGraphExec_t graph_exec;
+  int* graph_info;
+  float* graph_diag;
+  long long graph_launches;
+  bool graph_ok;
 };
 
 static size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
@@ -867,7 +908,20 @@ extern "C" int kfac_inverse_plan_create(
   p->refine_tiles = refine_tiles;
   p->refine_max_dim = kRefineDimCap;
   p->refine_threshold = 3e-5f;
+  p->params_dev = nullptr;
+  p->cap_stream = nullptr;
+  p->graph_exec = nullptr;
+  p->graph_info = nullptr;
+  p->graph_diag = nullptr;
+  p->graph_launches = 0;
+  {
+    const char* env = getenv("KFAC_INVERSE_GRAPH");
+    p->graph_ok = !(env && env[0] == '0');
+  }
   cudaError_t e = cudaGetDevice(&p->device);
+  if (e == cudaSuccess) e = cudaMalloc(&p->params_dev, sizeof(RunParams));
+  if (e == cudaSuccess)
+    e = cudaStreamCreateWithFlags(&p->cap_stream, cudaStreamNonBlocking);
   if (e == cudaSuccess) e = cudaMalloc(&p->add2_dev, sizeof(float) * count);
   if (e == cudaSuccess) e = cudaMalloc(&p->refine_count_dev, sizeof(int));
   if (e == cudaSuccess) e = cudaMemset(p->refine_count_dev, 0, sizeof(int));
@@ -913,20 +967,25 @@ extern "C" int kfac_inverse_plan_create(
     kfac_inverse_plan_destroy(p);
     return fail(KFAC_ERR_CUDA, "inverse_plan_create: %s", cudaGetErrorString(e));
   }
+  if (use_tc) {
+    const int rc = tc_prepare();
+    if (rc != KFAC_OK) {
+      kfac_inverse_plan_destroy(p);
+      return rc;
+    }
+  }
   *out = p;
   return KFAC_OK;
 }
 
-extern "C" int kfac_inverse_plan_run(kfac_inverse_plan* p, float damping,
-                                     int use_pi, int* info_dev,
-                                     float* diag_dev, void* stream) {
-  KFAC_REQUIRE(p != nullptr, "inverse_plan_run: null plan");
-  cudaStream_t st = (cudaStream_t)stream;
-  int* info = info_dev ? info_dev : p->info_dev;
+// Issue every launch of one run into `st` (a real stream, or one that is
+// being captured into a graph).
+static int plan_enqueue(kfac_inverse_plan* p, int* info, float* diag_dev,
+                        cudaStream_t st) {
   trace_kernel<<<p->count, 256, 0, st>>>(p->mats_dev, p->trace_dev, info);
   KFAC_LAUNCH_CHECK("trace_kernel");
   damping_kernel<<<ceil_div(p->count, 128), 128, 0, st>>>(
-      p->mats_dev, p->count, p->trace_dev, damping, use_pi, p->add_dev,
+      p->mats_dev, p->count, p->trace_dev, p->params_dev, p->add_dev,
       p->add2_dev, diag_dev);
   KFAC_LAUNCH_CHECK("damping_kernel");
   {
@@ -949,18 +1008,17 @@ extern "C" int kfac_inverse_plan_run(kfac_inverse_plan* p, float damping,
       if (rc != KFAC_OK) return rc;
     }
   }
-  if (p->n_refine > 0 && p->refine_max_dim > 0) {
+  if (p->n_refine > 0) {
     const dim3 pgrid(ceil_div(p->refine_dmax, 8), p->n_refine);
     for (int stage = 0; stage < 3; ++stage) {
       refine_probe_kernel<<<pgrid, 256, 0, st>>>(
           p->mats_dev, p->refine_items_dev, p->add_dev, p->add2_dev,
-          p->refine_sums_dev, stage);
+          p->refine_sums_dev, p->params_dev, stage);
       KFAC_LAUNCH_CHECK("refine_probe_kernel");
     }
     refine_gate_kernel<<<ceil_div(p->n_refine, 256), 256, 0, st>>>(
-        p->refine_items_dev, p->n_refine, p->refine_sums_dev,
-        p->refine_max_dim, p->refine_threshold, p->refine_gate_dev,
-        p->refine_count_dev);
+        p->refine_items_dev, p->n_refine, p->refine_sums_dev, p->params_dev,
+        p->refine_gate_dev, p->refine_count_dev);
     KFAC_LAUNCH_CHECK("refine_gate_kernel");
     refine_residual_kernel<<<p->refine_tiles, 256, 0, st>>>(
         p->mats_dev, p->refine_items_dev, p->n_refine, p->add_dev,
@@ -979,6 +1037,72 @@ extern "C" int kfac_inverse_plan_run(kfac_inverse_plan* p, float damping,
     KFAC_LAUNCH_CHECK("refine_apply_kernel");
   }
   return KFAC_OK;
+}
+
+static void plan_drop_graph(kfac_inverse_plan* p) {
+  if (p->graph_exec != nullptr) cudaGraphExecDestroy(p->graph_exec);
+  p->graph_exec = nullptr;
+}
+
+// Capture one run into a graph (on the plan's own stream: nothing executes
+// during capture).  On any failure the plan falls back to plain launches.
+static void plan_capture(kfac_inverse_plan* p, int* info, float* diag_dev) {
+  plan_drop_graph(p);
+  const long long before = launch_count_now();
+  if (cudaStreamBeginCapture(p->cap_stream, cudaStreamCaptureModeRelaxed) !=
+      cudaSuccess) {
+    cudaGetLastError();
+    p->graph_ok = false;
+    return;
+  }
+  const int rc = plan_enqueue(p, info, diag_dev, p->cap_stream);
+  cudaGraph_t graph = nullptr;
+  cudaError_t e = cudaStreamEndCapture(p->cap_stream, &graph);
+  const long long captured = launch_count_now() - before;
+  count_launches(-captured);          // nothing ran yet
+  if (rc == KFAC_OK && e == cudaSuccess && graph != nullptr)
+    e = cudaGraphInstantiate(&p->graph_exec, graph, 0);
+  if (graph != nullptr) cudaGraphDestroy(graph);
+  if (rc != KFAC_OK || e != cudaSuccess || p->graph_exec == nullptr) {
+    cudaGetLastError();
+    plan_drop_graph(p);
+    p->graph_ok = false;
+    return;
+  }
+  p->graph_info = info;
+  p->graph_diag = diag_dev;
+  p->graph_launches = captured;
+}
+
+extern "C" int kfac_inverse_plan_run(kfac_inverse_plan* p, float damping,
+                                     int use_pi, int* info_dev,
+                                     float* diag_dev, void* stream) {
+  KFAC_REQUIRE(p != nullptr, "inverse_plan_run: null plan");
+  cudaStream_t st = (cudaStream_t)stream;
+  int* info = info_dev ? info_dev : p->info_dev;
+  set_run_params_kernel<<<1, 1, 0, st>>>(p->params_dev, damping, use_pi,
+                                         p->refine_max_dim,
+                                         p->refine_threshold);
+  KFAC_LAUNCH_CHECK("set_run_params_kernel");
+  if (p->graph_ok) {
+    // a caller that is itself capturing gets plain launches in its capture
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cs) != cudaSuccess) {
+      cudaGetLastError();
+      cs = cudaStreamCaptureStatusNone;
+    }
+    if (cs == cudaStreamCaptureStatusNone) {
+      if (p->graph_exec == nullptr || p->graph_info != info ||
+          p->graph_diag != diag_dev)
+        plan_capture(p, info, diag_dev);
+      if (p->graph_exec != nullptr) {
+        KFAC_CUDA(cudaGraphLaunch(p->graph_exec, st));
+        count_launches(p->graph_launches);
+        return KFAC_OK;
+      }
+    }
+  }
+  return plan_enqueue(p, info, diag_dev, st);
 }
 
 extern "C" int kfac_inverse_plan_set_refine(kfac_inverse_plan* p, int max_dim,
@@ -1002,6 +1126,28 @@ extern "C" int kfac_inverse_plan_refined(kfac_inverse_plan* p,
   return KFAC_OK;
 }
 
+extern "C" int kfac_inverse_plan_error_estimates(kfac_inverse_plan* p,
+                                                 float* estimates_out) {
+  KFAC_REQUIRE(p != nullptr && estimates_out != nullptr,
+               "inverse_plan_error_estimates: null argument");
+  for (int i = 0; i < p->count; ++i) estimates_out[i] = -1.f;
+  if (p->n_refine == 0) return KFAC_OK;
+  std::vector<RefineItem> items(p->n_refine);
+  std::vector<double> sums(2 * (size_t)p->n_refine);
+  KFAC_CUDA(cudaDeviceSynchronize());
+  KFAC_CUDA(cudaMemcpy(items.data(), p->refine_items_dev,
+                       sizeof(RefineItem) * p->n_refine,
+                       cudaMemcpyDeviceToHost));
+  KFAC_CUDA(cudaMemcpy(sums.data(), p->refine_sums_dev,
+                       sizeof(double) * 2 * p->n_refine,
+                       cudaMemcpyDeviceToHost));
+  for (int r = 0; r < p->n_refine; ++r)
+    estimates_out[items[r].mat] =
+        sums[2 * r + 1] > 0.0 ? (float)sqrt(sums[2 * r] / sums[2 * r + 1])
+                              : -1.f;
+  return KFAC_OK;
+}
+
 extern "C" int kfac_inverse_plan_set_second_floor(kfac_inverse_plan* p,
                                                   const float* l2_coef_second) {
   KFAC_REQUIRE(p != nullptr && l2_coef_second != nullptr,
@@ -1018,6 +1164,9 @@ extern "C" int kfac_inverse_plan_set_second_floor(kfac_inverse_plan* p,
 
 extern "C" int kfac_inverse_plan_destroy(kfac_inverse_plan* p) {
   if (p == nullptr) return KFAC_OK;
+  plan_drop_graph(p);
+  if (p->cap_stream != nullptr) cudaStreamDestroy(p->cap_stream);
+  cudaFree(p->params_dev);
   cudaFree(p->add2_dev);
   cudaFree(p->refine_items_dev);
   cudaFree(p->refine_sums_dev);

@@ -1491,7 +1491,7 @@ int tc_tiles(GemmDesc& g) {
   return g.tiles_m * g.tiles_n;
 }
 
-static int tc_prepare() {
+int tc_prepare() {
   static std::mutex mu;
   static bool done[64] = {false};
   int dev = 0;

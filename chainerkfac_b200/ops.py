@@ -293,6 +293,14 @@ class InversePlan(object):
             self._handle, int(max_dim), float(threshold)),
             'kfac_inverse_plan_set_refine')
 
+    def error_estimates(self):
+        """Probe estimate of each inverse's relative error before refinement
+        in the last run (-1: not probed).  Synchronises."""
+        out = (ctypes.c_float * self.count)()
+        _lib.check(self._lib.kfac_inverse_plan_error_estimates(
+            self._handle, out), 'kfac_inverse_plan_error_estimates')
+        return list(out)
+
     def refined(self):
         """Number of factors the last run refined (synchronises)."""
         n = ctypes.c_int(0)

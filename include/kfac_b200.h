@@ -229,6 +229,12 @@ int kfac_inverse_plan_set_refine(kfac_inverse_plan* plan, int max_dim,
  * refined. */
 int kfac_inverse_plan_refined(kfac_inverse_plan* plan, int* refined_out);
 
+/* Synchronises the device; estimates_out (host, `count` floats) receives the
+ * probe's estimate of the relative error each inverse had before refinement
+ * in the last run (-1 for factors above the size cap or before any run). */
+int kfac_inverse_plan_error_estimates(kfac_inverse_plan* plan,
+                                      float* estimates_out);
+
 /* Role-2 blocks only (others ignore it): the rows of the second half of the
  * diagonal (the shift parameters of a BatchNormalization block) are damped
  * with max(l2_coef_second[i], damping) * scale[i] instead of the first half's

@@ -620,10 +620,23 @@ def test_config1_mlp_shapes_step(ops):
                                    orc.linear_G(gys[i]), gWs[i], gbs[i], 1e-3)
         assert rel(host(F[2 * i]), want['ema_A']) < FACTOR_TOL
         # These factors are ill-conditioned (uniform[0,1) inputs: cond ~ 6e3
-        # to 1.2e4 with damping 1e-3); the plan's probe sees that and runs
-        # the fp64-residual refinement step on them.
-        assert rel(host(inv[2 * i]), want['A_inv']) < INVERSE_TOL, i
-        assert rel(host(inv[2 * i + 1]), want['G_inv']) < INVERSE_TOL, i
+        # to 1.4e4 with damping 1e-3); the plan's probe sees that and runs
+        # the fp64-residual refinement step on them.  The inverse stage is
+        # judged on identical inputs: the oracle inverts the factor this
+        # stage was given (a factor that differs by 2e-6 moves the inverse
+        # by up to cond * 2e-6, whoever computes it), with the damping the
+        # oracle derives from it.
+        for j, key in ((0, 'A_inv'), (1, 'G_inv')):
+            f = host(F[2 * i + j])
+            _, dA, dG = orc.connection_damping(host(F[2 * i]),
+                                               host(F[2 * i + 1]), 1e-3)
+            add = np.float32(dA if j == 0 else dG)
+            oracle_inv = orc.damped_inverse(f, add)
+            truth = np.linalg.inv(f.astype(np.float64) +
+                                  float(add) * np.eye(len(f)))
+            got = host(inv[2 * i + j])
+            assert rel(got, oracle_inv) < INVERSE_TOL, (i, key)
+            assert rel(got, truth) < INVERSE_TOL, (i, key)
         assert rel(host(kW[i]), want['kfgrad_W']) < KFGRAD_TOL
         assert rel(host(kb[i]), want['kfgrad_b']) < KFGRAD_TOL
     plan.close()
