@@ -2,22 +2,27 @@
 """Benchmark of the K-FAC curvature hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload resnet50|config1|config2|config4|config5]
 
-Workload (``config.workload``): one K-FAC step of a vanilla ResNet-50 at batch
-32 per GPU, 224x224 inputs -- for each of its 54 convolution / fully-connected
-layers the two Kronecker factors are built from the layer's input activations
-and output gradients with the running average fused in (decay 0.9), all 108
-factors are inverted with pi-split damping 2.5e-4, and the gradients are
-preconditioned and applied with momentum.  Activations and gradients are
-synthetic (seeded) tensors of the real shapes; ImageNet is not used.
+Default workload (``config.workload`` = resnet50_kfac_step_b32_224): one K-FAC
+step of a vanilla ResNet-50 at batch 32 per GPU, 224x224 inputs -- for each of
+its 54 convolution / fully-connected layers the two Kronecker factors are built
+from the layer's input activations and output gradients with the running
+average fused in (decay 0.9), all 108 factors are inverted with pi-split
+damping 2.5e-4, and the gradients are preconditioned and applied with
+momentum.  Activations and gradients are synthetic (seeded) tensors of the
+real shapes; ImageNet is not used.  The other workloads are the remaining
+benchmark configurations with the same stages: the MNIST-shaped MLP (config1),
+the CIFAR ResNet-18 at batch 128 (config2), the isolated curvature microbench
+of 54 prebuilt factor pairs (config4: inverse + precondition only) and
+ResNet-50 with 16 accumulation micro-steps per update (config5).
 
 ``value`` is images/sec with activations/gradients resident in HBM; ``e2e`` is
 images/sec of the optimizer's public ``update(lossfun, x, t)`` call with the
 image batch coming from pinned host memory and the loss read back.  Rank 0
 prints one JSON line.  ``--impl reference`` times the reference's CPU (NumPy)
 arithmetic for the same stages through the oracle restatement on the host
-cores, on one layer per distinct layer shape (times multiplied by the number of
-layers of that shape).
+cores, whole passes over all layers until a time budget is used.
 """
 
 import argparse
@@ -34,35 +39,73 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-BATCH = 32
-DECAY = 0.9
-DAMPING = 2.5e-4
+import bench_workloads as bw  # noqa: E402
+
 LR = 0.01
 MOMENTUM = 0.9
-WORKLOAD = 'resnet50_kfac_step_b32_224'
-# DRAM traffic of one factor measured with ncu (profiles/), bytes: measured,
-# algorithmic (padded input once + factor written once)
-TRAFFIC_CASE = (33.9e6, 8.2e6 + 21.2e6)
 COMMUNICATOR = 'peer_memory'   # or 'pure_nccl' (NCCL reduce / broadcast)
 OVERLAP = True           # start the largest factors' inverse during the factor build
 OWNERSHIP = 'balanced'   # layer ownership at N > 1 ('reference': by count)
 
+# name -> layer table, per-GPU batch, running-average decay (r on the new
+# sample), damping, accumulation micro-steps per update
+WORKLOADS = {
+    'resnet50': dict(name='resnet50_kfac_step_b32_224',
+                     layers=lambda: bw.resnet50_layers(batch=32), batch=32,
+                     decay=0.9, damping=2.5e-4, acc=1),
+    'config1': dict(name='mlp_784_1000_1000_10_kfac_step_b128',
+                    layers=lambda: bw.mlp_layers(batch=128), batch=128,
+                    decay=0.99, damping=1e-3, acc=1),
+    'config2': dict(name='cifar_resnet18_kfac_step_b128_32',
+                    layers=lambda: bw.resnet18_cifar_layers(batch=128),
+                    batch=128, decay=0.99, damping=1e-3, acc=1),
+    'config4': dict(name='curvature_microbench_54_pairs_m8192',
+                    layers=lambda: bw.resnet50_layers(batch=32), batch=32,
+                    decay=1.0, damping=0.0, acc=1, prebuilt=8192),
+    'config5': dict(name='resnet50_kfac_acc16_b32_224',
+                    layers=lambda: bw.resnet50_layers(batch=32), batch=32,
+                    decay=0.9, damping=2.5e-4, acc=16),
+}
 
-def layer_table():
-    import bench_workloads as bw
-    layers = bw.resnet50_layers(batch=BATCH)
-    return layers, [bw.layer_dims(l) for l in layers]
+# DRAM bytes of single launches measured with ncu on small cases (the
+# full-size grouped launches are too large for a multi-pass capture); the
+# bench scales them by the algorithmic work of its own launches.
+# stage: (case, measured bytes, algorithmic bytes, algorithmic flops)
+TRAFFIC_CASES = {
+    'factor': ('conv3x3_c256_hw14 (tc_pair_kernel)', 33.9e6, 29.4e6,
+               32 * 14 * 14 * 2304 * 2305.0),
+    'inverse': None,
+    'precondition': None,
+}
 
 
-def algorithmic_flops(dims):
+def algorithmic_flops(dims, prebuilt=False):
     """Flops per step per GPU: one triangle of each factor, d^3 per inverse,
     two products per preconditioned gradient."""
-    factor = sum(rA * dA * (dA + 1) + rG * dG * (dG + 1)
-                 for dA, dG, rA, rG in dims)
+    factor = 0 if prebuilt else sum(
+        rA * dA * (dA + 1) + rG * dG * (dG + 1) for dA, dG, rA, rG in dims)
     inverse = sum(dA ** 3 + dG ** 3 for dA, dG, _, _ in dims)
     precond = sum(2 * dG * dG * dA + 2 * dG * dA * dA for dA, dG, _, _ in dims)
     return dict(factor=float(factor), inverse=float(inverse),
                 precondition=float(precond))
+
+
+def algorithmic_bytes(layers, dims, prebuilt=False):
+    """Minimum DRAM bytes per step per GPU: each un-expanded input once and
+    each factor written once (plus read for the running average); factor read
+    + inverse written; both inverses, gradient, result."""
+    factor = 0.0
+    if not prebuilt:
+        for l, (dA, dG, rA, rG) in zip(layers, dims):
+            if l['kind'] == 'conv':
+                src = l['n'] * l['cin'] * l['hin'] ** 2 + rG * dG
+            else:
+                src = rA * l['cin'] + rG * dG
+            factor += 4.0 * (src + 2 * (dA * dA + dG * dG))
+    inverse = sum(4.0 * 2 * (dA * dA + dG * dG) for dA, dG, _, _ in dims)
+    precond = sum(4.0 * (dG * dG + dA * dA + 3 * dG * dA)
+                  for dA, dG, _, _ in dims)
+    return dict(factor=factor, inverse=inverse, precondition=precond)
 
 
 def measure_tf32_peak(device):
@@ -133,11 +176,8 @@ class ClockSampler(object):
         for line in self.proc.stdout:
             self.lines.append((time.perf_counter(), line.strip()))
 
-    def stop(self, t0=None, t1=None):
-        """Summary of the samples read between host times t0 and t1 (the
-        timed region); the sampler is started before the warm-up steps, which
-        run the same work, and their samples are used (and said so) when the
-        timed region was too short to catch one."""
+    def stop(self, t0, t1, label):
+        """Summary of the samples read between host times t0 and t1."""
         if self.proc is None:
             return dict(sm_mhz=None, sm_max_mhz=None, reasons=['unsampled'])
         self.proc.terminate()
@@ -145,22 +185,19 @@ class ClockSampler(object):
             self.proc.wait(timeout=5)
         except Exception:
             pass
-        sm, smax, reasons = [], [], set()
+        sm, smax, power, reasons = [], [], [], set()
         names = ['hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown',
                  'sw_power_cap']
-        window = 'timed region'
-        lines = [l for ts, l in self.lines
-                 if t0 is None or (t0 <= ts <= t1)]
-        if not lines:
-            window = 'warm-up and timed region'
-            lines = [l for ts, l in self.lines if t1 is None or ts <= t1]
-        for line in lines:
+        for ts, line in self.lines:
+            if not (t0 <= ts <= t1):
+                continue
             parts = [p.strip() for p in line.split(',')]
             if len(parts) < 7:
                 continue
             try:
                 sm.append(float(parts[0]))
                 smax.append(float(parts[1]))
+                power.append(float(parts[2]))
             except ValueError:
                 continue
             for nm, val in zip(names, parts[3:7]):
@@ -169,19 +206,24 @@ class ClockSampler(object):
         if not sm:
             return dict(sm_mhz=None, sm_max_mhz=None, reasons=['unsampled'])
         return dict(sm_mhz=float(np.median(sm)), sm_max_mhz=float(max(smax)),
-                    samples=len(sm), window=window, reasons=sorted(reasons))
+                    power_w_max=float(max(power)), samples=len(sm),
+                    window=label, reasons=sorted(reasons))
 
 
 # ------------------------------------------------------------- GPU workload
 class DeviceWorkload(object):
     """Synthetic per-layer activations, output gradients, weights and K-FAC
-    state of ResNet-50 at batch 32, resident on one GPU."""
+    state of one benchmark configuration, resident on one GPU."""
 
-    def __init__(self, device, seed):
+    def __init__(self, device, seed, spec):
         import torch
         from chainerkfac_b200 import ops
-        self.torch, self.ops = torch, ops
-        self.layers, self.dims = layer_table()
+        self.torch, self.ops, self.spec = torch, ops, spec
+        self.layers = spec['layers']()
+        self.dims = [bw.layer_dims(l) for l in self.layers]
+        self.decay, self.damping = spec['decay'], spec['damping']
+        self.acc = spec['acc']
+        self.prebuilt = spec.get('prebuilt')
         g = torch.Generator(device=device)
         g.manual_seed(seed)
         self.x, self.gy, self.W, self.b = [], [], [], []
@@ -195,11 +237,12 @@ class DeviceWorkload(object):
                 ws = (l['cout'], l['cin'], l['k'], l['k'])
             else:
                 xs, gs, ws = (n, l['cin']), (n, l['cout']), (l['cout'], l['cin'])
-            x = torch.randn(xs, device=device, generator=g)
-            if i > 0:
-                x.clamp_(min=0)          # post-ReLU activations
-            self.x.append(x)
-            self.gy.append(torch.randn(gs, device=device, generator=g) / n)
+            if not self.prebuilt:
+                x = torch.randn(xs, device=device, generator=g)
+                if i > 0:
+                    x.clamp_(min=0)          # post-ReLU activations
+                self.x.append(x)
+                self.gy.append(torch.randn(gs, device=device, generator=g) / n)
             fan = ws[1] * (ws[2] * ws[3] if len(ws) == 4 else 1)
             self.W.append(torch.randn(ws, device=device, generator=g) / fan ** 0.5)
             self.gW.append(torch.randn(ws, device=device, generator=g) * 1e-2)
@@ -216,92 +259,171 @@ class DeviceWorkload(object):
                          torch.zeros((dG, dG), device=device)]
             self.inv += [torch.empty((dA, dA), device=device),
                          torch.empty((dG, dG), device=device)]
-        cnt = len(self.layers)
-        partner = [j ^ 1 for j in range(2 * cnt)]
-        role = [j & 1 for j in range(2 * cnt)]
-        self.plan = ops.InversePlanSet(self.ema, self.inv, partner, role)
-        self.class_layers = [sorted({i // 2 for i in idx})
-                             for idx in self.plan.classes()]
+        if self.prebuilt:
+            # factors X^T X / m + 1e-3 I from X ~ N(0,1) with m rows, built
+            # once; the timed step only inverts and preconditions
+            m = self.prebuilt
+            for f in self.ema:
+                d = f.shape[0]
+                X = torch.randn((m, d), device=device, generator=g)
+                ops.factor_dense(X, False, alpha=1.0 / m, out=f)
+                f.diagonal().add_(1e-3)
+        if self.acc > 1:
+            self.cov = [torch.zeros_like(e) for e in self.ema]
+            self.acc_cov = [torch.zeros_like(e) for e in self.ema]
+            self.acc_gW = [torch.zeros_like(w) for w in self.gW]
+            self.micro = 0
+        self.make_plan(list(range(len(self.layers))))
         self.first = True
         self.input_bytes = sum(t.numel() * 4 for t in self.x + self.gy)
 
+    def make_plan(self, own, bounds=None):
+        cnt = len(own)
+        if self.prebuilt:
+            # the 1e-3 I inside the factors is the damping: nothing is added
+            partner, role, scale = [-1] * (2 * cnt), [2] * (2 * cnt), \
+                [0.0] * (2 * cnt)
+        else:
+            partner = [k ^ 1 for k in range(2 * cnt)]
+            role = [k & 1 for k in range(2 * cnt)]
+            scale = None
+        self.plan = self.ops.InversePlanSet(
+            [self.ema[2 * i + j] for i in own for j in (0, 1)],
+            [self.inv[2 * i + j] for i in own for j in (0, 1)],
+            partner, role, scale=scale, bounds=bounds)
+        self.plan_layers = own
+        self.class_layers = [sorted({own[i // 2] for i in idx})
+                             for idx in self.plan.classes()]
+
+    def layer_items(self, i, A, G, r, rest):
+        ops, l = self.ops, self.layers[i]
+        n = l['n']
+        if l['kind'] == 'conv':
+            return [ops.conv_input_item(self.x[i], l['k'], l['stride'],
+                                        l['pad'], l['bias'], r / n, rest, A),
+                    ops.conv_grad_item(self.gy[i],
+                                       r * n / float(l['hout'] ** 2), rest, G)]
+        return [ops.dense_item(self.x[i], l['bias'], r / n, rest, A),
+                ops.dense_item(self.gy[i], False, r * n, rest, G)]
+
     def factor_items(self, outs, r, rest):
-        ops, items = self.ops, []
-        for i, l in enumerate(self.layers):
-            n = l['n']
-            A, G = outs[2 * i], outs[2 * i + 1]
-            if l['kind'] == 'conv':
-                items.append(ops.conv_input_item(
-                    self.x[i], l['k'], l['stride'], l['pad'], l['bias'],
-                    r / n, rest, A))
-                items.append(ops.conv_grad_item(
-                    self.gy[i], r * n / float(l['hout'] ** 2), rest, G))
-            else:
-                items.append(ops.dense_item(self.x[i], l['bias'], r / n, rest,
-                                            A))
-                items.append(ops.dense_item(self.gy[i], False, r * n, rest, G))
+        items = []
+        for i in range(len(self.layers)):
+            items += self.layer_items(i, outs[2 * i], outs[2 * i + 1], r, rest)
         return items
 
+    # -- stages timed alone (nothing else on the device) --------------------
     def factors_alone(self):
-        """The factor stage with nothing else on the device: every factor in
-        one grouped call, no inverse started beside it."""
-        items = self.factor_items(self.ema, DECAY, 1.0 - DECAY)
+        """Every factor in one grouped call, no inverse started beside it."""
+        items = self.factor_items(self.ema, self.decay, 1.0 - self.decay)
         self.ops.factor_group(items, self.ema[0].device)
 
+    def inverses_alone(self):
+        self.plan.run(self.damping, not self.prebuilt)
+
+    def precondition_alone(self):
+        own = self.plan_layers
+        self.ops.precondition(
+            [self.inv[2 * i + 1] for i in own], [self.inv[2 * i] for i in own],
+            [self.gW[i] for i in own], [self.gb[i] for i in own], None, None,
+            [self.W[i] for i in own], [self.b[i] for i in own],
+            [self.vW[i] for i in own], [self.vb[i] for i in own], lr=0.0,
+            momentum=1.0)
+
+    # -- the step ------------------------------------------------------------
+    def accumulate(self):
+        """Micro-step of an accumulated update: build this micro-batch's
+        factors and add 1/acc of them (and of the gradients) to the
+        accumulators in one launch."""
+        dev = self.ema[0].device
+        self.ops.factor_group(self.factor_items(self.cov, 1.0, 0.0), dev)
+        s, keep = 1.0 / self.acc, (0.0 if self.micro == 0 else 1.0)
+        self.ops.axpby_group(s, self.cov + self.gW, keep,
+                             self.acc_cov + self.acc_gW,
+                             self.acc_cov + self.acc_gW)
+        self.micro += 1
+
+    def ema_weights(self):
+        w = (1.0, 0.0) if self.first else (self.decay, 1.0 - self.decay)
+        self.first = False
+        return w
+
     def factors(self):
-        # all 108 factors in one grouped call per size class, running average
+        # all factors in one grouped call per size class, running average
         # fused in, largest class first: its inverse (a long serial chain that
         # uses few SMs) starts on a side stream while the other layers'
         # factors are still being built
-        r, rest = (1.0, 0.0) if self.first else (DECAY, 1.0 - DECAY)
-        items = self.factor_items(self.ema, r, rest)
+        if self.prebuilt:
+            return
         dev = self.ema[0].device
+        if self.acc > 1:
+            self.accumulate()
+            if self.micro == self.acc:
+                r, rest = self.ema_weights()
+                self.ops.axpby_group(r, self.acc_cov, rest, self.ema, self.ema)
+            return
+        r, rest = self.ema_weights()
+        items = self.factor_items(self.ema, r, rest)
         classes = self.plan.classes() if OVERLAP else []
         done = set()
         for c, idx in enumerate(classes[:-1]):
             self.ops.factor_group([items[i] for i in idx], dev)
-            self.plan.start_class(c, DAMPING, True)
+            self.plan.start_class(c, self.damping, True)
             done.update(idx)
         self.ops.factor_group([it for i, it in enumerate(items)
                                if i not in done], dev)
-        self.first = False
+
+    def update_due(self):
+        if self.acc > 1:
+            if self.micro < self.acc:
+                return False
+            self.micro = 0
+        return True
 
     def inverses(self):
         # the layers of a size class are preconditioned (and updated) on that
         # class's stream as soon as its inverses are done, next to the
         # remaining classes' inverses
-        self.plan.run(DAMPING, True,
+        self.plan.run(self.damping, not self.prebuilt,
                       after_class=self.precondition_class if OVERLAP else None)
 
-    def precondition_class(self, c):
-        layers = self.class_layers[c]
+    def grads(self):
+        return self.acc_gW if self.acc > 1 else self.gW
+
+    def precondition_layers(self, layers, ws_key=None):
+        gW = self.grads()
         self.ops.precondition(
             [self.inv[2 * i + 1] for i in layers],
             [self.inv[2 * i] for i in layers],
-            [self.gW[i] for i in layers], [self.gb[i] for i in layers],
+            [gW[i] for i in layers], [self.gb[i] for i in layers],
             None, None,
             [self.W[i] for i in layers], [self.b[i] for i in layers],
             [self.vW[i] for i in layers], [self.vb[i] for i in layers],
-            lr=LR, momentum=MOMENTUM, ws_key=c)
+            lr=LR, momentum=MOMENTUM, ws_key=ws_key)
+
+    def precondition_class(self, c):
+        self.precondition_layers(self.class_layers[c], ws_key=c)
 
     def precondition(self):
-        if OVERLAP:
-            return               # done per class inside inverses()
-        cnt = len(self.layers)
-        self.ops.precondition(
-            [self.inv[2 * i + 1] for i in range(cnt)],
-            [self.inv[2 * i] for i in range(cnt)], self.gW, self.gb,
-            None, None, self.W, self.b, self.vW, self.vb, lr=LR,
-            momentum=MOMENTUM)
+        if not OVERLAP:          # else done per class inside inverses()
+            self.precondition_layers(self.plan_layers)
 
-    def step(self, events=None):
+    def micro_step(self, events=None):
         self.factors()
         if events is not None:
             events[1].record()
-        self.inverses()
-        if events is not None:
+        if self.update_due():
+            self.inverses()
+            if events is not None:
+                events[2].record()
+            self.precondition()
+        elif events is not None:
             events[2].record()
-        self.precondition()
+
+    def step(self, events=None):
+        """One update: `acc` micro-steps (1 without accumulation)."""
+        for m in range(self.acc):
+            self.micro_step(events if m == self.acc - 1 else None)
 
 
 class DistributedWorkload(DeviceWorkload):
@@ -312,14 +434,15 @@ class DistributedWorkload(DeviceWorkload):
     and preconditions/updates only its own layers, and the updated weights
     are all-gathered.  Ownership is cost-balanced by default (OWNERSHIP);
     'reference' is the reference's contiguous split of the layer list by
-    count.
+    count.  With accumulation the factors and gradients are accumulated
+    locally and exchanged once per update (the reduction is linear).
 
     The first exchange runs size class by size class, largest first: as soon
     as a class is reduced its owners start its inverses on a side stream, next
     to the factor build and exchange of the remaining classes."""
 
-    def __init__(self, device, seed, comm):
-        super(DistributedWorkload, self).__init__(device, seed)
+    def __init__(self, device, seed, spec, comm):
+        super(DistributedWorkload, self).__init__(device, seed, spec)
         import torch
         self.comm = comm
         from chainerkfac_b200.optimizers.kfac import balanced_split
@@ -333,22 +456,20 @@ class DistributedWorkload(DeviceWorkload):
             self.indices = [ix.tolist() for ix in
                             np.array_split(np.arange(cnt), comm.size)]
         self.mine = self.indices[comm.rank]
-        self.cov = [torch.zeros_like(e) for e in self.ema]
+        if self.acc == 1 and not self.prebuilt:
+            self.cov = [torch.zeros_like(e) for e in self.ema]
         bounds = self.plan.bounds
         self.plan.close()
-        own = self.mine
-        self.plan = self.ops.InversePlanSet(
-            [self.ema[2 * i + j] for i in own for j in (0, 1)],
-            [self.inv[2 * i + j] for i in own for j in (0, 1)],
-            [k ^ 1 for k in range(2 * len(own))],
-            [k & 1 for k in range(2 * len(own))], bounds=bounds)
-        self.own_class_layers = [sorted({own[i // 2] for i in idx})
-                                 for idx in self.plan.classes()]
+        self.make_plan(self.mine, bounds)
         # size classes over all layers, largest first, as the plan forms them
         key_of = [sum(max(dA, dG) > b for b in bounds)
                   for dA, dG, _, _ in self.dims]
-        keys = sorted(set(key_of), reverse=True) if OVERLAP else [None]
-        self.class_layers, self.class_rs, self.class_plan = [], [], []
+        pipelined = OVERLAP and self.acc == 1 and not self.prebuilt
+        keys = sorted(set(key_of), reverse=True) if pipelined else [None]
+        src = None if self.prebuilt else (
+            self.acc_cov if self.acc > 1 else self.cov)
+        gsrc = self.grads()
+        self.xclass_layers, self.class_rs, self.class_plan = [], [], []
         for key in keys:
             layers = [i for i in range(cnt) if key is None or key_of[i] == key]
             rs = []
@@ -358,13 +479,14 @@ class DistributedWorkload(DeviceWorkload):
                     if i not in layers:
                         continue
                     # sorted parameter names: W before b
-                    loc.append((self.gW[i], False))
+                    loc.append((gsrc[i], False))
                     if self.gb[i] is not None:
                         loc.append((self.gb[i], False))
-                    loc.append((self.cov[2 * i], True))
-                    loc.append((self.cov[2 * i + 1], True))
+                    if src is not None:
+                        loc.append((src[2 * i], True))
+                        loc.append((src[2 * i + 1], True))
                 rs.append(loc)
-            self.class_layers.append(layers)
+            self.xclass_layers.append(layers)
             self.class_rs.append(rs)
             self.class_plan.append(
                 self.plan.class_keys.index(key)
@@ -385,13 +507,28 @@ class DistributedWorkload(DeviceWorkload):
 
     def factors(self):
         torch = self.torch
-        r, rest = (1.0, 0.0) if self.first else (DECAY, 1.0 - DECAY)
-        items = self.factor_items(self.cov, 1.0, 0.0)
-        dev = self.cov[0].device
+        dev = self.ema[0].device
         mine = set(self.mine)
-        last = len(self.class_layers) - 1
+        if self.prebuilt:
+            # only the gradients travel to the owners
+            self.comm.reduce_scatter_v_arrays(self.class_rs[0])
+            return
+        if self.acc > 1:
+            self.accumulate()
+            if self.micro == self.acc:
+                # one exchange per update: accumulated factors and gradients
+                self.comm.reduce_scatter_v_arrays(self.class_rs[0])
+                r, rest = self.ema_weights()
+                own = [2 * i + j for i in self.mine for j in (0, 1)]
+                emas = [self.ema[k] for k in own]
+                self.ops.axpby_group(r, [self.acc_cov[k] for k in own], rest,
+                                     emas, emas)
+            return
+        r, rest = self.ema_weights()
+        items = self.factor_items(self.cov, 1.0, 0.0)
+        last = len(self.xclass_layers) - 1
         main = torch.cuda.current_stream()
-        for c, layers in enumerate(self.class_layers):
+        for c, layers in enumerate(self.xclass_layers):
             self.ops.factor_group(
                 [items[2 * i + j] for i in layers for j in (0, 1)], dev)
             # exchange 1 for this class and the owner's running average run
@@ -412,7 +549,8 @@ class DistributedWorkload(DeviceWorkload):
                     self.ops.axpby_group(r, [self.cov[k] for k in own], rest,
                                          emas, emas)
                 if c < last and self.class_plan[c] is not None:
-                    self.plan.start_class(self.class_plan[c], DAMPING, True)
+                    self.plan.start_class(self.class_plan[c], self.damping,
+                                          True)
             if side is not main:
                 done = torch.cuda.Event()
                 done.record(side)
@@ -421,35 +559,91 @@ class DistributedWorkload(DeviceWorkload):
             # later work on the main stream (and the next step's factor build,
             # which overwrites cov) comes after the exchanges
             main.wait_event(self._exchanged)
-        self.first = False
-
-    def inverses(self):
-        self.plan.run(DAMPING, True,
-                      after_class=self.precondition_class if OVERLAP else None)
-
-    def precondition_class(self, c):
-        own = self.own_class_layers[c]
-        self.ops.precondition(
-            [self.inv[2 * i + 1] for i in own], [self.inv[2 * i] for i in own],
-            [self.gW[i] for i in own], [self.gb[i] for i in own], None, None,
-            [self.W[i] for i in own], [self.b[i] for i in own],
-            [self.vW[i] for i in own], [self.vb[i] for i in own], lr=LR,
-            momentum=MOMENTUM, ws_key=c)
 
     def precondition(self):
-        if OVERLAP:
-            # owned layers were updated per size class inside inverses()
-            self.comm.all_gather_v_arrays(self.ag_arrays)
-            return
-        own = self.mine
-        self.ops.precondition(
-            [self.inv[2 * i + 1] for i in own], [self.inv[2 * i] for i in own],
-            [self.gW[i] for i in own], [self.gb[i] for i in own], None, None,
-            [self.W[i] for i in own], [self.b[i] for i in own],
-            [self.vW[i] for i in own], [self.vb[i] for i in own], lr=LR,
-            momentum=MOMENTUM)
+        super(DistributedWorkload, self).precondition()
         # exchange 2: updated weights to everyone
         self.comm.all_gather_v_arrays(self.ag_arrays)
+
+    def check(self):
+        """One extra update from a clean state (running average = this
+        update's mean factor) whose results are checked across ranks: the
+        owner's averaged factors of one small layer against the mean of the
+        factors every rank built, the owner's inverses of them against fp64
+        inverses of that mean with the reference's damping rule, and the
+        gathered weights of all layers for equality on every rank."""
+        import torch.distributed as dist
+        torch = self.torch
+        if self.prebuilt:
+            return None
+        world = self.comm.size
+        small = [i for i, (dA, dG, _, _) in enumerate(self.dims)
+                 if max(dA, dG) <= 600]
+        i = small[len(small) // 2] if small else 0
+        owner = [r for r, ix in enumerate(self.indices) if i in ix][0]
+        self.first = True
+        self.step()
+        torch.cuda.synchronize()
+        # the factors this rank contributed (every micro-step of an
+        # accumulated update saw the same synthetic batch)
+        mine = [torch.empty_like(self.ema[2 * i + j]) for j in (0, 1)]
+        self.ops.factor_group(self.layer_items(i, mine[0], mine[1], 1.0, 0.0),
+                              mine[0].device)
+        worst_f = worst_i = 0.0
+        means = []
+        for j in (0, 1):
+            parts = [torch.empty_like(mine[j]) for _ in range(world)]
+            dist.all_gather(parts, mine[j])
+            mean = sum(p.double() for p in parts) / world
+            got = self.ema[2 * i + j].clone()
+            dist.broadcast(got, src=owner)
+            worst_f = max(worst_f, float((got.double() - mean).norm() /
+                                         mean.norm()))
+            means.append(mean)
+        A, G = means
+        pi = float(((A.trace() * G.shape[0]) /
+                    (G.trace() * A.shape[0])).sqrt())
+        adds = (pi * self.damping ** 0.5, self.damping ** 0.5 / pi)
+        for j, (m, add) in enumerate(zip((A, G), adds)):
+            want = torch.linalg.inv(
+                m + add * torch.eye(m.shape[0], device=m.device,
+                                    dtype=torch.float64))
+            got = self.inv[2 * i + j].clone()
+            dist.broadcast(got, src=owner)
+            worst_i = max(worst_i, float((got.double() - want).norm() /
+                                         want.norm()))
+        diff = torch.zeros(1, device=mine[0].device, dtype=torch.float64)
+        for w in self.W + [b for b in self.b if b is not None]:
+            ref = w.clone()
+            dist.broadcast(ref, src=0)
+            diff = torch.maximum(diff, (w - ref).abs().max().double())
+        dist.all_reduce(diff, op=dist.ReduceOp.MAX)
+        return dict(layer=self.layers[i]['name'], owner=owner,
+                    factor_rel=worst_f, inverse_rel=worst_i,
+                    weights_equal=bool(float(diff.item()) == 0.0))
+
+
+def time_alone(torch, fn, reps):
+    fn()
+    torch.cuda.synchronize()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps
+
+
+STAGE_KERNELS = {
+    'factor': 'tc_pair_kernel (grouped strided and im2col launches over all '
+              'factors, plus staging copies and the split reduce)',
+    'inverse': 'tc_gemm_kernel + chol_diag_kernel (batched blocked Cholesky, '
+               'triangular inverse and symmetric product of every factor, '
+               'three size classes on three streams)',
+    'precondition': 'tc_gemm_kernel (two grouped launches over all layers, '
+                    'update fused)'}
 
 
 def run_ours(args):
@@ -457,6 +651,7 @@ def run_ours(args):
     import torch.distributed as dist
     from chainerkfac_b200 import _lib
 
+    spec = WORKLOADS[args.workload]
     world = int(os.environ.get('WORLD_SIZE', '1'))
     rank = int(os.environ.get('RANK', '0'))
     local_rank = int(os.environ.get('LOCAL_RANK', '0'))
@@ -467,14 +662,17 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group('nccl', device_id=device)
     lib = _lib.load()
+    batch, acc = spec['batch'], spec['acc']
+    prebuilt = bool(spec.get('prebuilt'))
 
     if world > 1:
         from chainerkfac_b200.communicators import create_communicator
-        wl = DistributedWorkload(device, 1234 + rank,
+        wl = DistributedWorkload(device, 1234 + rank, spec,
                                  create_communicator(COMMUNICATOR))
     else:
-        wl = DeviceWorkload(device, seed=1234 + rank)
-    flops = algorithmic_flops(wl.dims)
+        wl = DeviceWorkload(device, 1234 + rank, spec)
+    flops = algorithmic_flops(wl.dims, prebuilt)
+    abytes = algorithmic_bytes(wl.layers, wl.dims, prebuilt)
 
     def barrier():
         if world > 1:
@@ -484,7 +682,8 @@ def run_ours(args):
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    for _ in range(max(args.warmup, 3)):
+    warmup = max(args.warmup, 3)
+    for _ in range(warmup):
         wl.step()
     barrier()
 
@@ -500,8 +699,6 @@ def run_ours(args):
     barrier()
     t_end = time.perf_counter()
     launches = lib.kfac_launch_count() - launches0
-    clocks = sampler.stop(t_begin, t_end) if rank == 0 else None
-
     total_ms = ev[0][0].elapsed_time(ev[-1][3])
     phase = np.zeros(3)
     for s in range(args.steps):
@@ -513,126 +710,176 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     total_ms = float(t.item())
     ms_per_step = total_ms / args.steps
-    value = BATCH * world / (ms_per_step * 1e-3)
+    # the same steps go on, untimed, until two seconds of load have been
+    # sampled: a 0.2 s timed region sees only a few clock samples (the count
+    # comes from the reduced time, so every rank runs the same number)
+    soak = int(max(0.0, 2000.0 - total_ms) / max(ms_per_step, 0.05))
+    for _ in range(min(soak, 4000)):
+        wl.step()
+    barrier()
+    clocks = sampler.stop(
+        t_begin, time.perf_counter(),
+        'timed region and the same steps repeated, untimed, until 2 s of '
+        'load were sampled') if rank == 0 else None
+    if prebuilt:
+        # strong scaling: the set of pairs is fixed
+        value, unit = len(wl.layers) / (ms_per_step * 1e-3), 'factor pairs/sec'
+    else:
+        value, unit = batch * acc * world / (ms_per_step * 1e-3), 'images/sec'
 
     info_bad = int((wl.plan.info != 0).sum().item())
+    refined = wl.plan.refined()
 
-    # The step overlaps the factor build with the first inverses, so the
-    # stage events above do not isolate the dominant kernel.  Time the factor
-    # stage alone for the roofline: the same grouped launches, nothing beside
-    # them, inputs larger than L2, CUDA events on the launching stream.
-    factor_alone_ms = None
-    if rank == 0 and world == 1:
-        reps = max(3, min(args.steps, 10))
-        wl.factors_alone()
-        torch.cuda.synchronize()
-        e0 = torch.cuda.Event(enable_timing=True)
-        e1 = torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(reps):
-            wl.factors_alone()
-        e1.record()
-        torch.cuda.synchronize()
-        factor_alone_ms = e0.elapsed_time(e1) / reps
+    # The step overlaps its stages, so the stage events above do not isolate
+    # them.  Each stage is therefore also timed alone: the same launches,
+    # nothing beside them, CUDA events on the launching stream.  At N > 1 a
+    # rank times the stages of the layers it owns (the factor build is the
+    # same on every rank) and the slowest rank counts.
+    reps = max(3, min(args.steps, 10))
+    alone = {}
+    if not prebuilt:
+        alone['factor'] = time_alone(torch, wl.factors_alone, reps)
+    alone['inverse'] = time_alone(torch, wl.inverses_alone, reps)
+    alone['precondition'] = time_alone(torch, wl.precondition_alone, reps)
+    if world > 1:
+        names = sorted(alone)
+        tt = torch.tensor([alone[k] for k in names], device=device,
+                          dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        alone = {k: float(v) for k, v in zip(names, tt.tolist())}
+    all_layers = None
+    if world > 1 and rank == 0:
+        # the owner-partitioned stages over ALL layers on one GPU, for their
+        # parallel efficiency: alone(all layers) / (N * slowest owner alone)
+        own, cls, plan = wl.plan_layers, wl.class_layers, wl.plan
+        wl.make_plan(list(range(len(wl.layers))), plan.bounds)
+        all_layers = {
+            'inverse': time_alone(torch, wl.inverses_alone, reps),
+            'precondition': time_alone(torch, wl.precondition_alone, reps)}
+        wl.plan.close()
+        wl.plan, wl.plan_layers, wl.class_layers = plan, own, cls
+    barrier()
+
+    dist_check = wl.check() if world > 1 else None
 
     e2e = None
-    if not args.no_e2e:
-        try:
-            e2e = run_e2e(args, device, world, rank)
-        except ImportError as exc:     # API layer not built yet
-            e2e = dict(value=None, unit='images/sec', error=str(exc))
+    if not args.no_e2e and args.workload in ('resnet50', 'config5'):
+        e2e = run_e2e(args, device, world, rank, spec)
 
     if rank == 0:
         peaks = measured_peaks()
         tf32 = measure_tf32_peak(device)
         names = ['factor', 'inverse', 'precondition']
-        # the factor stage is the grouped launches of tc_gemm_kernel, the
-        # kernel that also carries the inverse and precondition products
-        dom = 0
-        dom_ms = factor_alone_ms if factor_alone_ms else phase[dom]
-        achieved = flops[names[dom]] / (dom_ms * 1e-3) / 1e12
-        stage = {nm: dict(ms=float(ms), tflops=float(flops[nm] / (ms * 1e-3) / 1e12))
-                 for nm, ms in zip(names, phase)}
-        if OVERLAP and world == 1:
-            # each size class is preconditioned on its own stream right after
-            # its inverses: that work is inside the 'inverse' interval
-            stage['inverse']['tflops'] = float(
-                (flops['inverse'] + flops['precondition']) /
-                (phase[1] * 1e-3) / 1e12)
+        stage = {nm: dict(ms=float(ms)) for nm, ms in zip(names, phase)}
+        if OVERLAP:
             stage['inverse']['includes'] = 'precondition'
-            stage['precondition'] = dict(ms=float(phase[2]), tflops=None)
-        cpu = None if args.no_cpu_baseline else cpu_baseline_sample(steps=1, warmup=0)
+        for nm in alone:
+            stage[nm]['alone_ms'] = float(alone[nm])
+            stage[nm]['algorithmic_gflop'] = flops[nm] / 1e9
+            stage[nm]['algorithmic_mbytes'] = abytes[nm] / 1e6
+            if world == 1 or nm == 'factor':
+                stage[nm]['alone_tflops'] = float(
+                    flops[nm] / (alone[nm] * 1e-3) / 1e12)
+        if all_layers:
+            for nm, ms in all_layers.items():
+                stage[nm]['alone_all_layers_one_gpu_ms'] = float(ms)
+                stage[nm]['parallel_efficiency'] = float(
+                    ms / (world * alone[nm]))
+        # the roofline entry is the stage that takes longest alone
+        dom = max(alone, key=lambda k: alone[k])
+        if world == 1 or dom == 'factor':
+            dom_flops = flops[dom]
+            dom_ms = alone[dom]
+        else:
+            # an owner-partitioned stage: all layers on one GPU
+            dom_flops = flops[dom]
+            dom_ms = all_layers[dom]
+        achieved = dom_flops / (dom_ms * 1e-3) / 1e12
+        traffic = None
+        tcase = TRAFFIC_CASES.get(dom)
+        if tcase is not None:
+            # measured bytes of the small case, scaled by algorithmic flops
+            traffic = tcase[1] * dom_flops / tcase[3]
+        cpu = None
+        if not args.no_cpu_baseline and world == 1:
+            cpu = cpu_baseline(spec, budget_s=25.0, min_passes=1)
         line = {
-            'metric': 'ResNet-50 K-FAC images/sec (factor+inverse+precondition step)',
-            'value': value, 'unit': 'images/sec', 'n_gpus': world,
-            'steps': args.steps, 'warmup': max(args.warmup, 3),
+            'metric': 'ResNet-50 K-FAC images/sec (factor+inverse+'
+                      'precondition step)' if not prebuilt else
+                      'curvature microbench factor pairs/sec (inverse+'
+                      'precondition)',
+            'value': value, 'unit': unit, 'n_gpus': world,
+            'steps': args.steps, 'warmup': warmup,
             'ms_per_step': ms_per_step, 'higher_is_better': True,
-            'scaling': 'weak', 'vs_baseline': None, 'dtype': 'f32',
-            'data': 'synthetic',
-            'config': {'workload': WORKLOAD, 'batch_per_gpu': BATCH,
-                       'layers': len(wl.layers), 'cov_ema_decay': DECAY,
-                       'damping': DAMPING,
-                       'l2_flush': 'inputs larger than L2 (%.1f GB of '
-                                   'activations and gradients per step)'
-                                   % (wl.input_bytes / 1e9),
+            'scaling': 'strong' if prebuilt else 'weak', 'vs_baseline': None,
+            'dtype': 'f32', 'data': 'synthetic',
+            'config': {'workload': spec['name'], 'batch_per_gpu': batch,
+                       'layers': len(wl.layers),
+                       'cov_ema_decay': spec['decay'],
+                       'damping': spec['damping'], 'acc_iters': acc,
+                       'l2_flush': ('inputs larger than L2 (%.2f GB of '
+                                    'activations and gradients per step)'
+                                    % (wl.input_bytes / 1e9))
+                       if wl.input_bytes > 126e6 else
+                       ('factor and inverse buffers of %.2f GB per step'
+                        % (sum(e.numel() for e in wl.ema) * 8 / 1e9)),
                        'parallelism': 'dp%d' % world,
                        'ownership': OWNERSHIP if world > 1 else None,
                        'communicator': COMMUNICATOR if world > 1 else None},
-            # stage boundaries on the main stream; at one GPU the inverses of
-            # the larger size classes run on side streams during 'factor', so
-            # the per-stage rates there are not isolated kernel rates
+            # 'ms': stage boundaries on the main stream of the overlapped
+            # step (the inverses of the larger size classes run on side
+            # streams during 'factor'); 'alone_ms': the stage by itself
             'stages': stage,
-            'stages_overlap': bool(OVERLAP and world == 1),
-            'factor_alone_ms': factor_alone_ms,
+            'stages_overlap': bool(OVERLAP),
             'factor_inverse_ms': float(phase[0] + phase[1]),
+            'ms_per_micro_step': ms_per_step / acc,
             'roofline': {
                 'bound': 'tensor',
-                'kernel': 'tc_pair_kernel (factor stage: grouped strided and '
-                          'im2col launches over all 108 factors, plus pad '
-                          'copies and split reduce)',
-                # the factor stage is timed alone (a few launches, tens of
-                # ms): the burst figure is its denominator
+                'stage': dom,
+                'kernel': STAGE_KERNELS[dom],
                 'achieved': achieved, 'peak': peaks['tflops_burst'],
                 'unit': 'TFLOP/s', 'frac': achieved / peaks['tflops_burst'],
                 'peak_source': 'of %s: dense bf16 burst from '
-                               'MEASURED_PEAKS.json (kernel timed alone)'
+                               'MEASURED_PEAKS.json (stage timed alone)'
                                % peaks['source'],
-                # fp32 operands are split into two bf16 terms: three MMAs per
-                # algorithmic product, so a third of the bf16 rate is the
-                # ceiling of this scheme
-                'frac_of_split_bf16_ceiling':
-                    achieved / (peaks['tflops_burst'] / 3.0),
-                # the inverse and precondition products run as split TF32
+                # fp32 operands are split into two terms and every product
+                # costs three MMAs: bf16 terms for the factors, TF32 terms
+                # for the inverse and precondition products
+                'frac_of_split_ceiling': achieved / (
+                    (peaks['tflops_burst'] if dom == 'factor' else tf32) / 3.0),
                 'tf32_tflops_measured_here': tf32,
-                'step_tflops': float(sum(flops.values()) /
-                                     (ms_per_step * 1e-3) / 1e12),
-                # full-size launches are too large for a multi-pass capture;
-                # profiles/ holds DRAM traffic of single factors
-                'traffic': None,
-                'traffic_case': {'case': 'conv3x3_c256_hw14 (tc_pair_kernel)',
-                                 'dram_bytes': TRAFFIC_CASE[0],
-                                 'algorithmic_bytes': TRAFFIC_CASE[1]}},
+                'step_tflops': (float(sum(flops.values()) * acc /
+                                      (ms_per_step * 1e-3) / 1e12)
+                                if world == 1 and acc == 1 else None),
+                'traffic': traffic,
+                'traffic_case': None if tcase is None else {
+                    'case': tcase[0], 'dram_bytes': tcase[1],
+                    'algorithmic_bytes': tcase[2]}},
             'cpu_baseline': cpu,
             'gpu_launches': int(launches),
             'clocks': clocks,
             'e2e': e2e,
+            'dist_check': dist_check,
             'nonpositive_pivots': info_bad,
+            'inverses_refined_last_step': refined,
         }
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
 
 
-def run_e2e(args, device, world, rank):
+def run_e2e(args, device, world, rank, spec):
     """images/sec of KFAC.update(lossfun, x, t) on a torch ResNet-50 with the
     batch copied from pinned host memory and the loss read back every step."""
     import torch
     from bench_model import build_training_step
-    step, h2d, d2h = build_training_step(device, BATCH, world, rank,
-                                         cov_ema_decay=DECAY, damping=DAMPING,
-                                         lr=LR, momentum=MOMENTUM,
-                                         communicator=COMMUNICATOR)
-    for _ in range(max(args.warmup, 3)):
+    acc = spec['acc']
+    step, h2d, d2h = build_training_step(
+        device, spec['batch'], world, rank, cov_ema_decay=spec['decay'],
+        damping=spec['damping'], lr=LR, momentum=MOMENTUM,
+        communicator=COMMUNICATOR, acc_iters=acc, bn_blocks=args.bn_blocks)
+    steps = args.steps * acc
+    for _ in range(max(args.warmup, 3) * acc):
         step()
     torch.cuda.synchronize()
     if world > 1:
@@ -640,20 +887,36 @@ def run_e2e(args, device, world, rank):
     t0 = torch.cuda.Event(enable_timing=True)
     t1 = torch.cuda.Event(enable_timing=True)
     t0.record()
-    for _ in range(args.steps):
+    for _ in range(steps):
         step()
     t1.record()
     torch.cuda.synchronize()
     ms = torch.tensor([t0.elapsed_time(t1)], device=device, dtype=torch.float64)
     if world > 1:
         torch.distributed.all_reduce(ms, op=torch.distributed.ReduceOp.MAX)
-    per = float(ms.item()) / args.steps
-    return dict(value=BATCH * world / (per * 1e-3), unit='images/sec',
-                ms_per_step=per, h2d_bytes_per_step=h2d,
-                d2h_bytes_per_step=d2h)
+    per = float(ms.item()) / steps
+    return dict(value=spec['batch'] * world / (per * 1e-3), unit='images/sec',
+                ms_per_step=per * acc, ms_per_micro_step=per,
+                h2d_bytes_per_step=h2d * acc, d2h_bytes_per_step=d2h * acc,
+                bn_blocks=bool(args.bn_blocks))
 
 
 # ------------------------------------------------------------- CPU baseline
+def use_all_host_threads():
+    """The BLAS behind NumPy follows OMP_NUM_THREADS, which torchrun sets to 1
+    for its workers: raise the limit of the loaded BLAS to every host core.
+    Returns the thread count in force."""
+    n = os.cpu_count() or 1
+    try:
+        import threadpoolctl
+        threadpoolctl.threadpool_limits(limits=n)
+        got = max([p.get('num_threads', 1)
+                   for p in threadpoolctl.threadpool_info()] or [1])
+        return int(got)
+    except Exception:
+        return 1
+
+
 def cpu_layer_inputs(l, rng):
     n = l['n']
     if l['kind'] == 'conv':
@@ -668,59 +931,85 @@ def cpu_layer_inputs(l, rng):
     return x, gy, gW, gb
 
 
-def cpu_layer_pass(orc, l, inputs):
+def cpu_layer_pass(orc, l, inputs, spec, prebuilt_AG=None):
     """The reference's --no_cuda stages for one layer, via the oracle."""
     x, gy, gW, gb = inputs
     W, v = np.zeros_like(gW), np.zeros_like(gW)
     t0 = time.perf_counter()
-    if l['kind'] == 'conv':
+    if prebuilt_AG is not None:
+        A, G = prebuilt_AG
+    elif l['kind'] == 'conv':
         A = orc.conv_A(x, l['k'], l['stride'], l['pad'], l['bias'])
         G = orc.conv_G(gy)
     else:
         A = orc.linear_A(x, l['bias'])
         G = orc.linear_G(gy)
     t1 = time.perf_counter()
-    out = orc.connection_step(A, G, gW, gb, DAMPING, None, None, DECAY)
-    orc.momentum_update(W, v, out['kfgrad_W'], LR, MOMENTUM)
+    if prebuilt_AG is not None:
+        kW, _ = orc.connection_kfgrads(orc.inverse(A), orc.inverse(G), gW, gb)
+    else:
+        out = orc.connection_step(A, G, gW, gb, spec['damping'], None, None,
+                                  spec['decay'])
+        kW = out['kfgrad_W']
+    orc.momentum_update(W, v, kW, LR, MOMENTUM)
     t2 = time.perf_counter()
     return t1 - t0, t2 - t1
 
 
-def cpu_baseline_sample(steps=1, warmup=0, budget_s=150.0):
-    """Time the oracle on one layer per distinct shape; scale by multiplicity.
-    Stops early (and says so) once `budget_s` seconds of passes have run."""
+def cpu_baseline(spec, budget_s, min_passes=1, max_passes=None):
+    """Whole passes of the oracle (the reference's --no_cuda arithmetic) over
+    the workload: one layer of each distinct shape is timed and counted once
+    per layer of that shape.  Passes repeat until `budget_s` seconds are used
+    (at least `min_passes`, at most `max_passes`)."""
     from oracle import kfac_oracle as orc
-    layers, dims = layer_table()
-    groups = {}
-    for l, d in zip(layers, dims):
-        key = (l['kind'], l.get('k'), l.get('stride'), l['cin'], l['cout'],
-               l.get('hin'), l['bias'])
-        groups.setdefault(key, [l, 0])[1] += 1
+    threads = use_all_host_threads()
+    layers = spec['layers']()
+    groups = bw.distinct_shapes(layers)
     rng = np.random.default_rng(7)
-    inputs = [cpu_layer_inputs(l, rng) for l, _ in groups.values()]
-    times, t_start, done = [], time.perf_counter(), 0
-    for it in range(warmup + steps):
+    inputs = [cpu_layer_inputs(l, rng) for l, _ in groups]
+    prebuilt = None
+    if spec.get('prebuilt'):
+        prebuilt = []
+        for l, _ in groups:
+            dA, dG, _, _ = bw.layer_dims(l)
+            pair = []
+            for d in (dA, dG):
+                X = rng.standard_normal((2048, d), dtype=np.float32)
+                pair.append((X.T @ X / 2048 + 1e-3 * np.eye(d)).astype(np.float32))
+            prebuilt.append(pair)
+    acc = spec['acc']
+    times, t_start = [], time.perf_counter()
+    while True:
         tf = ti = 0.0
-        for (l, mult), inp in zip(groups.values(), inputs):
-            a, b = cpu_layer_pass(orc, l, inp)
-            tf += a * mult
+        for k, ((l, mult), inp) in enumerate(zip(groups, inputs)):
+            a, b = cpu_layer_pass(orc, l, inp, spec,
+                                  None if prebuilt is None else prebuilt[k])
+            # with accumulation the factors are built in every micro-step,
+            # the inverse and preconditioning once per update
+            tf += a * mult * acc
             ti += b * mult
-        done += 1
-        if it >= warmup:
-            times.append((tf, ti))
-        if time.perf_counter() - t_start > budget_s and times:
+        times.append((tf, ti))
+        used = time.perf_counter() - t_start
+        if len(times) >= min_passes and (
+                used + used / len(times) > budget_s or
+                (max_passes and len(times) >= max_passes)):
             break
     tf = float(np.mean([t[0] for t in times]))
     ti = float(np.mean([t[1] for t in times]))
-    return dict(value=BATCH / (tf + ti), unit='images/sec',
-                cores=os.cpu_count(), kind='port',
+    if spec.get('prebuilt'):
+        value, unit = len(layers) / (tf + ti), 'factor pairs/sec'
+    else:
+        value, unit = spec['batch'] * acc / (tf + ti), 'images/sec'
+    return dict(value=value, unit=unit, cores=threads,
+                host_cpus=os.cpu_count(), kind='port',
                 factor_s=tf, inverse_precondition_s=ti,
-                passes_timed=len(times), passes_run=done,
-                sample='NumPy oracle (reference --no_cuda arithmetic, all '
-                       'host cores through the BLAS threads) on one layer of '
-                       'each of the %d distinct ResNet-50 layer shapes, batch '
-                       '32; each time multiplied by the number of layers of '
-                       'that shape (54 layers in total)' % len(groups))
+                passes_timed=len(times), wall_s=time.perf_counter() - t_start,
+                sample='NumPy oracle (the reference --no_cuda arithmetic '
+                       'restated; %d BLAS threads) on one layer of each of '
+                       'the %d distinct layer shapes of %s, each time counted '
+                       'once per layer of that shape (%d layers): %d whole '
+                       'pass(es)' % (threads, len(groups), spec['name'],
+                                     len(layers), len(times)))
 
 
 def run_reference(args):
@@ -728,25 +1017,36 @@ def run_reference(args):
     world = int(os.environ.get('WORLD_SIZE', '1'))
     if rank != 0:
         return
-    t0 = time.perf_counter()
-    cpu = cpu_baseline_sample(steps=max(args.steps, 1), warmup=args.warmup)
-    wall = time.perf_counter() - t0
+    spec = WORKLOADS[args.workload]
+    # one warm-up pass, then whole passes for about a minute and a half;
+    # `steps` is the number of passes really timed
+    warm = cpu_baseline(spec, budget_s=0.0, min_passes=1, max_passes=1)
+    want = max(1, min(args.steps, int(90.0 / max(warm['wall_s'], 1e-3))))
+    cpu = cpu_baseline(spec, budget_s=1e9, min_passes=want, max_passes=want)
     value = cpu['value']
     line = {
         'impl': 'reference',
-        'metric': 'ResNet-50 K-FAC images/sec (factor+inverse+precondition step)',
-        'value': value, 'unit': 'images/sec', 'n_gpus': world,
-        'steps': args.steps, 'warmup': args.warmup,
-        'ms_per_step': 1e3 * BATCH / value, 'higher_is_better': True,
-        'scaling': 'weak', 'vs_baseline': None, 'dtype': 'f32',
-        'data': 'synthetic',
-        'config': {'workload': WORKLOAD, 'batch_per_gpu': BATCH,
-                   'layers': 54, 'cov_ema_decay': DECAY, 'damping': DAMPING,
-                   'parallelism': 'cpu (rank 0 only)'},
+        'metric': 'ResNet-50 K-FAC images/sec (factor+inverse+'
+                  'precondition step)' if not spec.get('prebuilt') else
+                  'curvature microbench factor pairs/sec (inverse+'
+                  'precondition)',
+        'value': value, 'unit': cpu['unit'], 'n_gpus': world,
+        'steps': cpu['passes_timed'], 'warmup': 1,
+        'steps_requested': args.steps,
+        'ms_per_step': 1e3 * (cpu['factor_s'] + cpu['inverse_precondition_s']),
+        'higher_is_better': True,
+        'scaling': 'strong' if spec.get('prebuilt') else 'weak',
+        'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
+        'config': {'workload': spec['name'], 'batch_per_gpu': spec['batch'],
+                   'layers': len(spec['layers']()),
+                   'cov_ema_decay': spec['decay'], 'damping': spec['damping'],
+                   'acc_iters': spec['acc'],
+                   'parallelism': 'cpu (rank 0 only, %d BLAS threads)'
+                                  % cpu['cores']},
         'cpu_baseline': cpu,
-        'e2e': {'value': value, 'unit': 'images/sec',
+        'e2e': {'value': value, 'unit': cpu['unit'],
                 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
-        'gpu_launches': 0, 'wall_s': wall,
+        'gpu_launches': 0,
     }
     print(json.dumps(line))
 
@@ -761,8 +1061,11 @@ MICRO_CASES = {
     'conv3x3_c512_hw7': ('conv_input', dict(n=32, c=512, hw=7, k=3, s=1, p=1)),
     'conv7x7_c3_hw224': ('conv_input', dict(n=32, c=3, hw=224, k=7, s=2, p=3)),
     'dense_rows8192_d4608': ('dense', dict(rows=8192, d=4608)),
+    'inverse_d1024': ('inverse', dict(dims=[1024])),
     'inverse_d2304': ('inverse', dict(dims=[2304])),
     'inverse_d4608': ('inverse', dict(dims=[4608])),
+    'inverse_d4608x3': ('inverse', dict(dims=[4608, 4608, 4608])),
+    'precondition_dG512_dA4608': ('precondition', dict(dG=512, dA=4608)),
     # wire format of the exchange: every factor of ResNet-50 (308 MB packed,
     # 615 MB dense); the sum reads 4 rank buffers, all on this GPU here
     'wire_pack_resnet50': ('wire_pack', dict()),
@@ -771,8 +1074,8 @@ MICRO_CASES = {
 
 
 def run_micro(args):
-    """Time one small case (CUDA events); the command line used for the ncu
-    captures summarised under profiles/."""
+    """Time one small case with CUDA events (the cases the ncu captures
+    use)."""
     import torch
     from chainerkfac_b200 import ops
     kind, p = MICRO_CASES[args.micro]
@@ -795,8 +1098,16 @@ def run_micro(args):
         out = torch.empty(p['d'], p['d'], device='cuda')
         fn = lambda: ops.factor_dense(x, False, alpha=1.0, out=out)
         flops = p['rows'] * p['d'] * (p['d'] + 1)
+    elif kind == 'precondition':
+        dG, dA = p['dG'], p['dA']
+        Gi = torch.randn(dG, dG, device='cuda')
+        Ai = torch.randn(dA, dA, device='cuda')
+        gW = torch.randn(dG, dA, device='cuda')
+        kW = torch.empty_like(gW)
+        fn = lambda: ops.precondition([Gi], [Ai], [gW], [None], [kW], [None])
+        flops = 2 * dG * dG * dA + 2 * dG * dA * dA
     elif kind in ('wire_pack', 'wire_unpack'):
-        _, dims = layer_table()
+        dims = [bw.layer_dims(l) for l in bw.resnet50_layers(batch=32)]
         sides = [d for dA, dG, _, _ in dims for d in (dA, dG)]
         arrs = [torch.randn(d, d, device='cuda') for d in sides]
         tri = [True] * len(arrs)
@@ -848,8 +1159,11 @@ def main():
     ap.add_argument('--steps', type=int, default=20)
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
+    ap.add_argument('--workload', default='resnet50', choices=sorted(WORKLOADS))
     ap.add_argument('--no-e2e', action='store_true')
     ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--bn-blocks', action='store_true',
+                    help='end-to-end model with BatchNormalization blocks too')
     ap.add_argument('--no-overlap', action='store_true',
                     help='do not start the largest inverses during the '
                          'factor build')

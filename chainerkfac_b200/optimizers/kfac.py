@@ -232,6 +232,7 @@ class KFAC(_base.GradientMethod):
         self.group_factors = True
         self._factors_pending = False
         self._emas_done = False
+        self._accumulated = False    # accumulate() already ran for this call
         self._plans = {}
         self.observation = {}
 
@@ -308,9 +309,10 @@ class KFAC(_base.GradientMethod):
         if lossfun is not None:
             self._forward_backward(lossfun, args, kwargs)
 
-        if self.acc_iters > 1:
+        if self.acc_iters > 1 and not self._accumulated:
             if self.accumulate():
                 return
+        self._accumulated = False
 
         self.reallocate_cleared_grads()
         self.call_hooks('pre')
@@ -576,8 +578,16 @@ class DistributedKFAC(KFAC):
 
     def __init__(self, comm, *args, communicate_after_forward=False,
                  only_pic_update_weight=True, ownership='reference',
-                 **kwargs):
+                 exchange_every_micro_step=False, **kwargs):
         super(DistributedKFAC, self).__init__(*args, **kwargs)
+        # With acc_iters > 1 the reference reduce-scatters gradients and
+        # factors in every micro-step and accumulates the reduced values
+        # (kfac.py:356-382 with :259-304).  The reduction is linear, so
+        # accumulating locally and exchanging the accumulated arrays once per
+        # update gives the owners the same values with 1/acc_iters of the
+        # traffic; that is the default here.  True restores the reference's
+        # schedule (also used when the forward factors travel early).
+        self.exchange_every_micro_step = exchange_every_micro_step
         if ownership not in ('reference', 'balanced'):
             raise ValueError("ownership must be 'reference' or 'balanced'")
         # 'reference': contiguous split of the name-sorted block list by count
@@ -622,6 +632,16 @@ class DistributedKFAC(KFAC):
                 after_forward=self.reduce_scatter_v_after_forward)
         if self.is_changed(self.target):
             self.comm.bcast_data(self.target)
+        elif self.acc_iters > 1 and not self.exchange_every_micro_step and \
+                not self.communicate_after_forward:
+            # accumulate this rank's own gradients and factors; on the last
+            # micro-step exchange the accumulated arrays once
+            if self.accumulate():
+                return
+            self._accumulated = True
+            self.reduce_scatter_v_after_backward()
+            super(DistributedKFAC, self).update()
+            self._real_updates += 1
         else:
             if self._factors_pending:
                 self._factors_pending = False

@@ -147,6 +147,81 @@ def make_arrays(rng, size):
     return out
 
 
+def check_single_exchange_accumulation(ck, comm, rank, size):
+    """acc_iters micro-steps of DistributedKFAC: every rank accumulates its
+    own gradients and factors (kfac.py:286-304) and the owners receive, in
+    ONE reduce-scatter per update, the mean over ranks of the accumulated
+    arrays -- what the reference obtains by exchanging in every micro-step.
+    The device arithmetic is replaced by torch on the CPU; the sequencing,
+    the arrays handed to the communicator and the values the curvature
+    stages then see are what is checked."""
+    from chainerkfac_b200 import ops
+    from chainerkfac_b200.optimizers import kfac as kfac_mod
+
+    def axpby_group(a, xs, b, ys, outs):
+        for x, y, o in zip(xs, ys, outs):
+            o.copy_(a * x + (b * y if b != 0.0 else 0.0))
+    old = ops.axpby_group
+    ops.axpby_group = axpby_group
+    try:
+        acc = 3
+        torch.manual_seed(0)
+        model = nn.Sequential(nn.Linear(6, 5), nn.ReLU(), nn.Linear(5, 4),
+                              nn.ReLU(), nn.Linear(4, 3))
+        opt = ck.DistributedKFAC(comm, lr=0.1, acc_iters=acc)
+        opt.setup(model)
+        opt.update()                   # first call only broadcasts
+        calls, seen = [], {}
+        orig_rs = comm.reduce_scatter_v_arrays
+        comm.reduce_scatter_v_arrays = lambda arrays, stream=None: (
+            calls.append(1), orig_rs(arrays, stream))[1]
+
+        def fake_update_kfgrads(fblocks):
+            for i in opt.local_indices:
+                fb = opt.fblocks[i]
+                seen[i] = ([c.clone() for c in fb.covs],
+                           fb.link.W.grad.clone())
+        opt.update_kfgrads = fake_update_kfgrads
+        opt.comm.all_gather_v_arrays = lambda arrays, stream=None: None
+        for p in opt.target.params():
+            p.update = lambda: None
+        rngs = [np.random.default_rng(500 + q) for q in range(size)]
+        per_rank = []                  # [rank][micro][block] -> (A, G, gW)
+        for q in range(size):
+            micro = []
+            for m in range(acc):
+                blocks = []
+                for fb in opt.fblocks:
+                    dG = fb.link.W.shape[0]
+                    dA = fb.link.W.size // dG + 1
+                    A = rngs[q].standard_normal((dA, dA)).astype(np.float32)
+                    G = rngs[q].standard_normal((dG, dG)).astype(np.float32)
+                    gW = rngs[q].standard_normal(
+                        tuple(fb.link.W.shape)).astype(np.float32)
+                    blocks.append(((A + A.T) / 2, (G + G.T) / 2, gW))
+                micro.append(blocks)
+            per_rank.append(micro)
+        for m in range(acc):
+            for fb, (A, G, gW) in zip(opt.fblocks, per_rank[rank][m]):
+                fb.covs = [torch.from_numpy(A.copy()),
+                           torch.from_numpy(G.copy())]
+                fb.link.W.grad = torch.from_numpy(gW.copy())
+                fb.link.b.grad = torch.zeros(tuple(fb.link.b.shape))
+            opt.update()
+            assert len(calls) == (1 if m == acc - 1 else 0)
+        assert opt.t == 1 and opt.acc_count == 0
+        for i in opt.local_indices:
+            for j in (0, 1, 2):
+                want = np.mean(
+                    [orc.accumulate([per_rank[q][m][i][j]
+                                     for m in range(acc)], acc)
+                     for q in range(size)], axis=0)
+                got = (seen[i][0][j] if j < 2 else seen[i][1]).numpy()
+                assert np.allclose(got, want, rtol=1e-5, atol=1e-6), (i, j)
+    finally:
+        ops.axpby_group = old
+
+
 def _worker(rank, size, port, tmp):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR='127.0.0.1', MASTER_PORT=str(port),
@@ -220,6 +295,7 @@ def _worker(rank, size, port, tmp):
     assert all(torch.equal(gathered[0], g) for g in gathered)
     with pytest.warns(UserWarning):
         comm.allreduce_grad()
+    check_single_exchange_accumulation(ck, comm, rank, size)
     open(os.path.join(tmp, 'ok%d' % rank), 'w').close()
     dist.destroy_process_group()
 

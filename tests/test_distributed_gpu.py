@@ -64,30 +64,44 @@ for rep in range(3):
         for (x, _), (y, _) in zip(a_nccl[o], a_peer[o]):
             assert torch.equal(x, y), (rep, o)
 
-for pic, early, own, cname in (
-        (True, False, 'reference', 'pure_nccl'),
-        (False, False, 'reference', 'pure_nccl'),
-        (True, True, 'balanced', 'pure_nccl'),
-        (True, False, 'balanced', 'peer_memory'),
-        (False, True, 'reference', 'peer_memory')):
+for pic, early, own, cname, decay, acc in (
+        (True, False, 'reference', 'pure_nccl', 1.0, 1),
+        (False, False, 'reference', 'pure_nccl', 1.0, 1),
+        (True, True, 'balanced', 'pure_nccl', 1.0, 1),
+        (True, False, 'balanced', 'peer_memory', 1.0, 1),
+        (False, True, 'reference', 'peer_memory', 1.0, 1),
+        # running averages blended on the exchange stream of the pipelined
+        # exchange, several steps
+        (True, False, 'balanced', 'peer_memory', 0.9, 1),
+        (True, False, 'reference', 'pure_nccl', 0.9, 1),
+        # accumulation over micro-steps with a single exchange per update
+        (True, False, 'balanced', 'peer_memory', 0.9, 2)):
     model = make()
     comm = comms[cname]
-    opt = ck.DistributedKFAC(comm, lr=0.05, momentum=0.9, cov_ema_decay=1.0,
+    opt = ck.DistributedKFAC(comm, lr=0.05, momentum=0.9, cov_ema_decay=decay,
                              damping=1e-2, only_pic_update_weight=pic,
-                             communicate_after_forward=early, ownership=own)
+                             communicate_after_forward=early, ownership=own,
+                             acc_iters=acc)
     opt.setup(model)
     lossfun = lambda a, b: F.cross_entropy(model(a), b)
     opt.update(lossfun, xs, ts)          # first call: broadcast only
     assert opt.t == 0
     opt.update(lossfun, xs, ts)
-    assert opt.t == 1
     # further steps take the pipelined exchange (size class by size class)
     # when the configuration allows it
-    steps = 3 if not early else 1
-    for _ in range(steps - 1):
-        opt.update(lossfun, xs, ts)
+    steps = (4 if decay < 1.0 else 3) if not early else 1
+    if acc > 1:
+        # the call above was the first micro-step of the first update
+        assert opt.t == 0 and opt.acc_count == 1
+        for _ in range(acc * steps - 1):
+            opt.update(lossfun, xs, ts)
+        assert opt.t == steps
+    else:
+        assert opt.t == 1
+        for _ in range(steps - 1):
+            opt.update(lossfun, xs, ts)
     assert opt._real_updates == steps
-    if not early:
+    if not early and acc == 1:
         assert opt._pipeline_ready()
     # every rank holds the same weights afterwards
     flat = torch.cat([p.detach().reshape(-1) for p in model.parameters()])
@@ -99,14 +113,15 @@ for pic, early, own, cname in (
         # average exactly; factors of the halves average to the whole-batch
         # factor for A (scaled 1/n_local) and G (per-rank n_local * gy^T gy).
         ref = make()
-        o1 = ck.KFAC(lr=0.05, momentum=0.9, cov_ema_decay=1.0, damping=1e-2)
+        o1 = ck.KFAC(lr=0.05, momentum=0.9, cov_ema_decay=decay, damping=1e-2,
+                     acc_iters=acc)
         o1.setup(ref)
-        for _ in range(steps):
+        for _ in range(steps * acc):
             o1.update(lambda a, b: F.cross_entropy(ref(a), b), X, T)
         for (n1, p1), (n2, p2) in zip(ref.named_parameters(),
                                       model.named_parameters()):
             err = float((p1 - p2).norm() / p1.norm())
-            assert err < 2e-3, (pic, early, own, cname, n1, err)
+            assert err < 2e-3, (pic, early, own, cname, decay, acc, n1, err)
 dist.barrier()
 if rank == 0:
     print('DISTRIBUTED_OK')
