@@ -55,6 +55,9 @@ long long launch_count_now();
 // built per call (see pack.cu).
 int ring_alloc(size_t bytes, void** out);
 
+// Status word of the inverse's diagonal kernel (inverse.cu).
+int diag_status_read(int* out);
+
 // Number of streaming multiprocessors of the current device (cached).
 int sm_count();
 

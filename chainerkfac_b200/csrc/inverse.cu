@@ -14,11 +14,14 @@
 #include <algorithm>
 
 #include "gemm_simt.cuh"
+#include "tc_common.cuh"
 
 namespace kfac {
 
 constexpr int DB = 128;        // diagonal block
 constexpr int PW = 512;        // Cholesky panel width (outer blocking)
+// floats of the diagonal kernel's shared memory: Lt, Pt, Xr, Tk
+constexpr int kDiagBaseFloats = DB * (DB + 4) + 24 * DB + 16 * 64;
 
 struct MatInfo {
   const float* F;
@@ -43,6 +46,11 @@ struct RunParams {
   float refine_threshold;
   // CUDA graph of one run (captured on first use)
   RunParams* params_dev;
+  std::vector<cudaEvent_t> events;   // edges between the two streams
+  cudaEvent_t fork_ev, join_ev[2];
+  cudaStream_t side_stream[2];       // bulk / far stream of plain runs
+  cudaStream_t cap_side[2];          // the same during capture
+  bool look;
   cudaStream_t cap_stream;
   cudaGraphExec_t graph_exec;
   int* graph_info;
@@ -121,15 +129,18 @@ __global__ void damping_kernel(const MatInfo* __restrict__ mats, int count,
 // W = F + add * I, blockIdx.y = matrix, blockIdx.x strides over rows.  Only
 // the lower triangle and the rest of each diagonal 128-block (which the
 // trailing updates read-modify-write) is ever used, so only that is copied.
+// With `dual` the first block column below the first diagonal block is also
+// stored in the inverse's output buffer (see the look-ahead of the Cholesky).
 __global__ void damp_copy_kernel(const MatInfo* __restrict__ mats,
                                  const float* __restrict__ add,
-                                 const float* __restrict__ add2) {
+                                 const float* __restrict__ add2, int dual) {
   const MatInfo mi = mats[blockIdx.y];
   const float a_first = add[blockIdx.y], a_second = add2[blockIdx.y];
   const int d = mi.d;
   const bool vec = (d & 3) == 0 &&
                    ((reinterpret_cast<uintptr_t>(mi.F) |
-                     reinterpret_cast<uintptr_t>(mi.W)) & 15) == 0;
+                     reinterpret_cast<uintptr_t>(mi.W) |
+                     reinterpret_cast<uintptr_t>(mi.inv)) & 15) == 0;
   for (int r = blockIdx.x; r < d; r += gridDim.x) {
     const float a = (mi.role == 2 && 2 * r >= d) ? a_second : a_first;
     const int cend = min(d, (r | (DB - 1)) + 1);
@@ -149,15 +160,226 @@ __global__ void damp_copy_kernel(const MatInfo* __restrict__ mats,
           else v.w += a;
         }
         d4[c4] = v;
+        if (dual && r >= DB && c4 < DB / 4)
+          reinterpret_cast<float4*>(mi.inv + (long long)r * d)[c4] = v;
       }
     } else {
       for (int c = threadIdx.x; c < cend; c += blockDim.x) {
         float v = src[c];
         if (r == c) v += a;
         dst[c] = v;
+        if (dual && r >= DB && c < DB) mi.inv[(long long)r * d + c] = v;
       }
     }
   }
+}
+
+
+// ------------------------------------------------ look-ahead of the Cholesky
+constexpr int DLD = DB + 4;   // shared-memory row pitch of a 128 x 128 block
+constexpr int kLookTile = DB * 32 * 4;          // one 128 x 32 fp32 operand tile
+constexpr int kLookStage = 4 * kLookTile;       // [A hi][A lo][B hi][B lo]
+constexpr int kLookCols = 2 * DB;               // tensor-memory columns
+
+static __device__ int g_diag_status = 0;
+
+struct LookControl {
+  unsigned long long bar[2];   // a stage's MMAs have finished reading it
+  unsigned long long done;     // all MMAs of the second product have finished
+  unsigned tmem_base;
+  volatile int abort_flag;
+};
+
+// Issue the three split-TF32 MMAs of one 32-k operand block: D(128 x 128) +=
+// A B^T with A, B given as hi / lo tile addresses (K-major, 128-byte
+// swizzle).  hi*hi goes to columns [0, 128) of the tensor memory, the cross
+// terms to [128, 256).
+__device__ __forceinline__ void look_mma_block(unsigned tmem, unsigned a_hi,
+                                               unsigned a_lo, unsigned b_hi,
+                                               unsigned b_lo, bool first) {
+  const unsigned idesc = tc_instr_desc(DB);
+  const unsigned long long dah = tc_smem_desc(a_hi), dal = tc_smem_desc(a_lo);
+  const unsigned long long dbh = tc_smem_desc(b_hi), dbl = tc_smem_desc(b_lo);
+#pragma unroll
+  for (int kk = 0; kk < 4; ++kk) {
+    const unsigned long long adv = (unsigned long long)(kk * 32 >> 4);
+    const unsigned acc = (first && kk == 0) ? 0u : 1u;
+    tc_mma(tmem + DB, dal + adv, dbh + adv, idesc, acc);
+    tc_mma(tmem + DB, dah + adv, dbl + adv, idesc, 1u);
+    tc_mma(tmem, dah + adv, dbh + adv, idesc, acc);
+  }
+}
+
+// The diagonal block of step k has received the updates of all steps before
+// k - 1; the update of step k - 1,
+//   D = W_kk - L' L'^T,  L' = A' X_pp^T,
+// is computed here from A' (block (k, k-1) as it was before step k-1's panel
+// solve overwrote it; the updates keep a second copy of it in the inverse's
+// output buffer) and X_pp (inverse of the previous diagonal block's factor),
+// so that this kernel does not have to wait for the panel solve and panel
+// update of step k - 1.  Both products run on the tensor cores (tcgen05,
+// split TF32, accumulators in tensor memory).  Result: D in Sa (rows and
+// columns below `bs` are meaningful).  256 threads.  Returns false if a
+// bounded wait ran out (the status word is set; the caller stores nothing).
+__device__ __forceinline__ bool diag_lookahead(const MatInfo& mi, int o, int bs,
+                                               float* Sa, unsigned char* stage,
+                                               LookControl* ctl) {
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const long long ld = mi.d;
+  const float* Ap = mi.inv + (long long)o * ld + (o - DB);
+  const float* Xp = mi.X + (long long)(o - DB) * ld + (o - DB);
+  const float* Wd = mi.W + (long long)o * ld + o;
+  const bool vec = (ld & 3) == 0 && (o & 3) == 0 &&
+                   ((reinterpret_cast<uintptr_t>(mi.inv) |
+                     reinterpret_cast<uintptr_t>(mi.X) |
+                     reinterpret_cast<uintptr_t>(mi.W)) & 15) == 0;
+  if (tid == 0) {
+    mbar_init(&ctl->bar[0], 1);
+    mbar_init(&ctl->bar[1], 1);
+    mbar_init(&ctl->done, 1);
+    ctl->abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile(
+        "tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+        ::"r"(smem_u32(&ctl->tmem_base)), "r"(kLookCols)
+        : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;"
+                 ::: "memory");
+  }
+  // W_kk into Sa (the update is subtracted from it at the end)
+  for (int idx = tid; idx < DB * (DB / 4); idx += 256) {
+    const int r = idx >> 5, c = (idx & 31) * 4;
+    float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (r < bs) {
+      if (vec && c + 3 < bs) {
+        w = *reinterpret_cast<const float4*>(&Wd[r * ld + c]);
+      } else {
+        if (c < bs) w.x = Wd[r * ld + c];
+        if (c + 1 < bs) w.y = Wd[r * ld + c + 1];
+        if (c + 2 < bs) w.z = Wd[r * ld + c + 2];
+        if (c + 3 < bs) w.w = Wd[r * ld + c + 3];
+      }
+    }
+    *reinterpret_cast<float4*>(&Sa[r * DLD + c]) = w;
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const unsigned tmem = ctl->tmem_base;
+  const unsigned sbase = smem_u32(stage);
+  bool ok = true;
+
+  // ---- L' = A' X_pp^T: four operand blocks of 32 k through two stages; the
+  // global loads of block kb + 1 are in flight while block kb is split,
+  // stored and multiplied
+  float4 va[4], vx[4];
+  auto load_block = [&](int kb) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int c = tid + 256 * j, row = c >> 3, col = 32 * kb + 4 * (c & 7);
+      va[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (vec) {
+        if (row < bs) va[j] = *reinterpret_cast<const float4*>(&Ap[row * ld + col]);
+        vx[j] = *reinterpret_cast<const float4*>(&Xp[row * ld + col]);
+      } else {
+        if (row < bs) {
+          va[j].x = Ap[row * ld + col]; va[j].y = Ap[row * ld + col + 1];
+          va[j].z = Ap[row * ld + col + 2]; va[j].w = Ap[row * ld + col + 3];
+        }
+        vx[j].x = Xp[row * ld + col]; vx[j].y = Xp[row * ld + col + 1];
+        vx[j].z = Xp[row * ld + col + 2]; vx[j].w = Xp[row * ld + col + 3];
+      }
+    }
+  };
+  load_block(0);
+#pragma unroll
+  for (int kb = 0; kb < 4; ++kb) {
+    const int s = kb & 1;
+    if (kb >= 2) ok = mbar_wait_status(&ctl->bar[s], 0, &ctl->abort_flag,
+                                       &g_diag_status) && ok;
+    const unsigned st = sbase + s * kLookStage;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int c = tid + 256 * j;
+      const unsigned off = (unsigned)sw128_chunk_off(c >> 3, c & 7);
+      store_split(st + off, st + kLookTile + off, va[j]);
+      store_split(st + 2 * kLookTile + off, st + 3 * kLookTile + off, vx[j]);
+    }
+    if (kb + 1 < 4) load_block(kb + 1);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncthreads();
+    if (tid == 0 && !ctl->abort_flag) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      look_mma_block(tmem, st, st + kLookTile, st + 2 * kLookTile,
+                     st + 3 * kLookTile, kb == 0);
+      tc_commit(&ctl->bar[s]);
+    }
+  }
+  ok = mbar_wait_status(&ctl->bar[0], 1, &ctl->abort_flag, &g_diag_status) && ok;
+  ok = mbar_wait_status(&ctl->bar[1], 1, &ctl->abort_flag, &g_diag_status) && ok;
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+
+  // ---- L' out of tensor memory, split, into the operand blocks of the second
+  // product (A and B are the same matrix: [hi][lo] per 32 k, four blocks)
+  const int q = warp & 3, h = warp >> 2;
+  const int row = 32 * q + lane;
+  ok = __all_sync(0xffffffffu, ok);     // the loads below are warp-wide
+  if (ok) {
+#pragma unroll
+    for (int cc = 0; cc < 4; ++cc) {
+      const int c0 = 64 * h + 16 * cc;
+      float v[16], w[16];
+      tc_ld16(tmem + ((unsigned)(32 * q) << 16) + (unsigned)c0, v);
+      tc_ld16(tmem + ((unsigned)(32 * q) << 16) + (unsigned)(DB + c0), w);
+      const unsigned blk = sbase + (unsigned)(c0 >> 5) * (2 * kLookTile);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float4 x = make_float4(v[4 * i] + w[4 * i], v[4 * i + 1] + w[4 * i + 1],
+                                     v[4 * i + 2] + w[4 * i + 2],
+                                     v[4 * i + 3] + w[4 * i + 3]);
+        const unsigned off =
+            (unsigned)sw128_chunk_off(row, ((c0 & 31) >> 2) + i);
+        store_split(blk + off, blk + kLookTile + off, x);
+      }
+    }
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  // ---- L' L'^T
+  if (tid == 0 && !ctl->abort_flag) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+    for (int kb = 0; kb < 4; ++kb) {
+      const unsigned blk = sbase + (unsigned)kb * (2 * kLookTile);
+      look_mma_block(tmem, blk, blk + kLookTile, blk, blk + kLookTile, kb == 0);
+    }
+    tc_commit(&ctl->done);
+  }
+  ok = mbar_wait_status(&ctl->done, 0, &ctl->abort_flag, &g_diag_status) && ok;
+  ok = __all_sync(0xffffffffu, ok);
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  if (ok) {
+#pragma unroll
+    for (int cc = 0; cc < 4; ++cc) {
+      const int c0 = 64 * h + 16 * cc;
+      float v[16], w[16];
+      tc_ld16(tmem + ((unsigned)(32 * q) << 16) + (unsigned)c0, v);
+      tc_ld16(tmem + ((unsigned)(32 * q) << 16) + (unsigned)(DB + c0), w);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) Sa[row * DLD + c0 + i] -= v[i] + w[i];
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
+                 ::"r"(tmem), "r"(kLookCols)
+                 : "memory");
+  }
+  return ctl->abort_flag == 0;
 }
 
 // Factor one diagonal block (<= 128 x 128) of W and invert the resulting
@@ -175,6 +397,7 @@ __global__ void damp_copy_kernel(const MatInfo* __restrict__ mats,
 //   Inverse, block row kb: the threads of block row kb apply the stored 8 x 8
 //   inverse to their blocks of the running right-hand side (rows kb of X are
 //   then final); the rows below take a rank-8 update.
+template <bool LOOK>
 __global__ void __launch_bounds__(256)
 chol_diag_kernel(const MatInfo* __restrict__ mats, const int* __restrict__ ids,
                  int step, int* __restrict__ info) {
@@ -200,6 +423,29 @@ chol_diag_kernel(const MatInfo* __restrict__ mats, const int* __restrict__ ids,
                    ((reinterpret_cast<uintptr_t>(mi.W) |
                      reinterpret_cast<uintptr_t>(mi.X)) & 15) == 0;
   float a[8][8];
+  if (LOOK) {
+    // the block with step - 1's update applied comes out of the look-ahead
+    // in shared memory (aliasing Lt, which is written only after the
+    // Cholesky sweep's barriers)
+    float* Sa = dsm;
+    unsigned char* stage = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(dsm + kDiagBaseFloats) + 1023) &
+        ~(uintptr_t)1023);
+    LookControl* ctl = reinterpret_cast<LookControl*>(stage + 2 * kLookStage);
+    if (!diag_lookahead(mi, o, bs, Sa, stage, ctl)) return;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int gi = 8 * br + i;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int gj = 8 * bc + j;
+        float v = (gi == gj) ? 1.f : 0.f;
+        if (gi < bs && gj <= gi) v = Sa[gi * DLD + gj];
+        a[i][j] = v;
+      }
+    }
+    __syncthreads();
+  } else
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const int gi = 8 * br + i;
@@ -606,16 +852,33 @@ refine_apply_kernel(const MatInfo* __restrict__ mats,
 }
 
 constexpr size_t kDiagSmemBytes =
-    (DB * (DB + 4) + 24 * DB + 16 * 64) * sizeof(float);   // Lt, Pt, Xr, Tk
+    kDiagBaseFloats * sizeof(float);                        // Lt, Pt, Xr, Tk
+constexpr size_t kDiagLookSmemBytes =
+    kDiagBaseFloats * sizeof(float) + 1024 + 2 * kLookStage + 256;
+static_assert(kDiagLookSmemBytes <= 227 * 1024, "diagonal kernel shared memory");
 
 struct Launch {
   int tails;     // grouped gemm: some contraction is not a multiple of 32
-  int kind;      // 0 diag kernel, 1 grouped gemm
+  int kind;      // 0 diag kernel, 1 grouped gemm, 2 join of the side stream
   int off;       // offset into ids / descs
   int n;         // number of ids / descs
   int tiles;     // grouped gemm: total tiles
   int step;      // diag kernel: panel index
+  // A run uses two streams: the chain (0) and a side stream (1) for work
+  // that is off the critical path.  A launch may wait for an event first and
+  // record one afterwards (indices into the plan's events, -1: none).
+  int stream;
+  int wait_ev;
+  int rec_ev;
+  int wait_ev2;
+  bool look;     // diag kernel: with the look-ahead prologue
 };
+
+// Status word of the diagonal kernel's bounded waits (read by kfac_tc_status).
+int diag_status_read(int* out) {
+  KFAC_CUDA(cudaMemcpyFromSymbol(out, g_diag_status, sizeof(int)));
+  return KFAC_OK;
+}
 
 }  // namespace kfac
 
@@ -648,6 +911,11 @@ struct kfac_inverse_plan {
   float refine_threshold;
   // CUDA graph of one run (captured on first use)
   RunParams* params_dev;
+  std::vector<cudaEvent_t> events;   // edges between the two streams
+  cudaEvent_t fork_ev, join_ev[2];
+  cudaStream_t side_stream[2];       // bulk / far stream of plain runs
+  cudaStream_t cap_side[2];          // the same during capture
+  bool look;
   cudaStream_t cap_stream;
   cudaGraphExec_t graph_exec;
   int* graph_info;
@@ -734,8 +1002,15 @@ extern "C" int kfac_inverse_plan_create(
   std::vector<Launch> launches;
   const bool use_tc = engine() == 1;
 
+  int n_events = 0;
+  const bool look = use_tc && [] {
+    const char* env = getenv("KFAC_INVERSE_LOOKAHEAD");
+    return !(env && env[0] == '0');
+  }();
+  std::vector<int> diag_ev((dmax + DB - 1) / DB + 1, -1);
+  std::vector<int> upd_ev((dmax + DB - 1) / DB + 1, -1);
   auto begin_gemm = [&]() {
-    Launch l = {0, 1, (int)descs.size(), 0, 0, 0};
+    Launch l = {0, 1, (int)descs.size(), 0, 0, 0, 0, -1, -1, -1, false};
     return l;
   };
   auto push_desc = [&](Launch& l, GemmDesc g) {
@@ -755,16 +1030,33 @@ extern "C" int kfac_inverse_plan_create(
     if (l.n > 0) launches.push_back(l);
   };
 
+  int prev_far_ev = -1;
   // Two-level right-looking Cholesky: panels of PW columns are factored by
   // 128-wide inner steps whose updates stay inside the panel (short
   // contractions, little work); the bulk of the flops is the update of the
   // trailing matrix with the whole panel (contraction length PW).
+  //
+  // With look-ahead (default) a run uses three streams.  The chain (0)
+  // carries the diagonal kernels; inside a panel the diagonal kernel of step
+  // k applies step k-1's update to its own block itself (diag_lookahead), so
+  // it only waits for the panel update of step k-2.  The panel solves and
+  // panel updates of the steps run on the bulk stream (1) behind the chain,
+  // and the part of a panel's trailing update that the next panel does not
+  // need runs on the far stream (2).  Panel updates (and the near part of a
+  // trailing update, and the damped copy for the first block column) store
+  // their results a second time in the inverse's output buffer: that copy of
+  // block (k, k-1) is what diag_lookahead reads while the panel solve of
+  // step k-1 overwrites the original.
   for (int po = 0; po < dmax; po += PW) {
     const int inner = std::min(PW, dmax - po);
+    int last_solve_ev = -1;
     for (int o = po; o < po + inner; o += DB) {
-      Launch dl = {0, 0, (int)ids.size(), 0, 0, o / DB};
+      const bool lk = look && o > po;
+      Launch dl = {0, 0, (int)ids.size(), 0, 0, o / DB, 0, -1, -1, -1, lk};
       for (int i : order)
         if (dims[i] > o) { ids.push_back(i); dl.n += 1; }
+      if (lk && o - 2 * DB >= po) dl.wait_ev = upd_ev[(o - 2 * DB) / DB];
+      if (look) dl.rec_ev = diag_ev[o / DB] = n_events++;
       launches.push_back(dl);
 
       Launch trsm = begin_gemm();
@@ -781,45 +1073,115 @@ extern "C" int kfac_inverse_plan_create(
         g.alpha = 1.f; g.beta = 0.f; g.flags = 0;
         push_desc(trsm, g);
       }
+      if (look && trsm.n > 0) {
+        trsm.stream = 1;
+        trsm.wait_ev = diag_ev[o / DB];
+        trsm.rec_ev = last_solve_ev = n_events++;
+      }
       end_gemm(trsm);
 
       // update the rest of this panel's columns (full rectangle; entries
-      // above the diagonal are written but never read)
+      // above the diagonal are written but never read).  With look-ahead the
+      // next diagonal block is left to the next diagonal kernel.
+      const int skip = (look && o + DB < po + inner) ? DB : 0;
       Launch upd = begin_gemm();
       for (int i : order) {
         const int d = dims[i];
-        const int M = d - o - DB;
+        const int M = d - o - DB - skip;
         const int N = std::min(po + PW, d) - (o + DB);
         if (M <= 0 || N <= 0) continue;
         const MatInfo& m = mats[i];
         GemmDesc g = {};
-        float* panel = m.W + (long long)(o + DB) * d + o;
+        float* panel = m.W + (long long)(o + DB + skip) * d + o;
+        const long long coff = (long long)(o + DB + skip) * d + (o + DB);
         g.A = strided_operand(panel, 1, d, M);
-        g.B = strided_operand(panel, 1, d, N);
-        g.C = m.W + (long long)(o + DB) * d + (o + DB);
+        g.B = strided_operand(m.W + (long long)(o + DB) * d + o, 1, d, N);
+        g.C = m.W + coff;
         g.ldc = d; g.M = M; g.N = N; g.K = DB;
         g.alpha = -1.f; g.beta = 1.f; g.flags = 0;
+        if (look) g.C2 = m.inv + coff;
         push_desc(upd, g);
+      }
+      if (look) {
+        upd.stream = 1;
+        if (upd.n > 0) upd.rec_ev = upd_ev[o / DB] = n_events++;
       }
       end_gemm(upd);
     }
 
-    Launch trail = begin_gemm();
+    // Update of the trailing matrix with the finished panel, in two parts:
+    // the columns of the next panel (needed before the chain can go on) on
+    // the chain's stream, the columns beyond them on the far stream, next to
+    // the next panel's chain.  Both parts of one panel touch disjoint tiles;
+    // parts of successive panels that touch the same tiles are ordered by
+    // events (next-panel part p+1 after far part p) or by stream order.
+    Launch near = begin_gemm(), far = begin_gemm();
+    std::vector<GemmDesc> far_descs;
     for (int i : order) {
       const int d = dims[i];
       const int M = d - po - PW;
       if (M <= 0) continue;
+      const int N1 = std::min(PW, M);
       const MatInfo& m = mats[i];
-      GemmDesc g = {};
-      float* panel = m.W + (long long)(po + PW) * d + po;
-      g.A = strided_operand(panel, 1, d, M);
-      g.B = g.A;
-      g.C = m.W + (long long)(po + PW) * d + (po + PW);
-      g.ldc = d; g.M = M; g.N = M; g.K = PW;
-      g.alpha = -1.f; g.beta = 1.f; g.flags = G_LOWER | G_SAME_AB;
-      push_desc(trail, g);
+      const float* panel = m.W + (long long)(po + PW) * d + po;
+      {
+        GemmDesc g = {};     // square block on the diagonal: lower tiles
+        const long long coff = (long long)(po + PW) * d + (po + PW);
+        g.A = strided_operand(panel, 1, d, N1);
+        g.B = g.A;
+        g.C = m.W + coff;
+        g.ldc = d; g.M = N1; g.N = N1; g.K = PW;
+        g.alpha = -1.f; g.beta = 1.f; g.flags = G_LOWER | G_SAME_AB;
+        if (look) g.C2 = m.inv + coff;
+        push_desc(near, g);
+      }
+      if (M > N1) {
+        const float* below = panel + (long long)N1 * d;
+        GemmDesc g = {};     // rectangle below it
+        const long long coff = (long long)(po + PW + N1) * d + (po + PW);
+        g.A = strided_operand(below, 1, d, M - N1);
+        g.B = strided_operand(panel, 1, d, N1);
+        g.C = m.W + coff;
+        g.ldc = d; g.M = M - N1; g.N = N1; g.K = PW;
+        g.alpha = -1.f; g.beta = 1.f; g.flags = 0;
+        if (look) g.C2 = m.inv + coff;
+        push_desc(near, g);
+        GemmDesc h = {};     // everything beyond the next panel's columns
+        h.A = strided_operand(below, 1, d, M - N1);
+        h.B = h.A;
+        h.C = m.W + (long long)(po + PW + N1) * d + (po + PW + N1);
+        h.ldc = d; h.M = M - N1; h.N = M - N1; h.K = PW;
+        h.alpha = -1.f; h.beta = 1.f; h.flags = G_LOWER | G_SAME_AB;
+        far_descs.push_back(h);
+      }
     }
-    end_gemm(trail);
+    far.off = (int)descs.size();
+    for (auto& h : far_descs) push_desc(far, h);
+    int panel_ev = look ? last_solve_ev : -1;
+    if (!look && far.n > 0) {
+      // the far part needs the finished panel: an event recorded on the
+      // chain right before the near part
+      panel_ev = n_events++;
+      launches.back().rec_ev = panel_ev;   // last launch of the panel's chain
+    }
+    if (near.n > 0) {
+      near.wait_ev = prev_far_ev;          // far part of the previous panel
+      near.wait_ev2 = look ? panel_ev : -1;  // the bulk stream's last solve
+      prev_far_ev = -1;
+    }
+    if (far.n > 0) {
+      far.stream = 2;
+      far.wait_ev = panel_ev;
+      far.rec_ev = n_events++;
+      prev_far_ev = far.rec_ev;
+    }
+    end_gemm(near);
+    end_gemm(far);
+  }
+  {
+    // the triangular inverse reads all of L: join the side stream
+    Launch join = {0, 2, 0, 0, 0, 0, 0, -1, -1, -1, false};
+    launches.push_back(join);
   }
 
   for (long long b = DB; b < dmax; b *= 2) {
@@ -909,6 +1271,10 @@ extern "C" int kfac_inverse_plan_create(
   p->refine_max_dim = kRefineDimCap;
   p->refine_threshold = 3e-5f;
   p->params_dev = nullptr;
+  p->fork_ev = p->join_ev[0] = p->join_ev[1] = nullptr;
+  p->side_stream[0] = p->side_stream[1] = nullptr;
+  p->cap_side[0] = p->cap_side[1] = nullptr;
+  p->look = look;
   p->cap_stream = nullptr;
   p->graph_exec = nullptr;
   p->graph_info = nullptr;
@@ -920,8 +1286,29 @@ extern "C" int kfac_inverse_plan_create(
   }
   cudaError_t e = cudaGetDevice(&p->device);
   if (e == cudaSuccess) e = cudaMalloc(&p->params_dev, sizeof(RunParams));
+  // the chain is latency-bound and uses few SMs: it gets the higher
+  // priority, the side stream's tiles fill the rest
+  int prio_lo = 0, prio_hi = 0;
+  if (e == cudaSuccess) e = cudaDeviceGetStreamPriorityRange(&prio_lo, &prio_hi);
   if (e == cudaSuccess)
-    e = cudaStreamCreateWithFlags(&p->cap_stream, cudaStreamNonBlocking);
+    e = cudaStreamCreateWithPriority(&p->cap_stream, cudaStreamNonBlocking,
+                                     prio_hi);
+  for (int k = 0; k < 2 && e == cudaSuccess; ++k) {
+    e = cudaStreamCreateWithPriority(&p->cap_side[k], cudaStreamNonBlocking,
+                                     prio_lo);
+    if (e == cudaSuccess)
+      e = cudaStreamCreateWithPriority(&p->side_stream[k],
+                                       cudaStreamNonBlocking, prio_lo);
+  }
+  if (e == cudaSuccess)
+    e = cudaEventCreateWithFlags(&p->fork_ev, cudaEventDisableTiming);
+  for (int k = 0; k < 2 && e == cudaSuccess; ++k)
+    e = cudaEventCreateWithFlags(&p->join_ev[k], cudaEventDisableTiming);
+  for (int k = 0; k < n_events + 1 && e == cudaSuccess; ++k) {
+    cudaEvent_t ev = nullptr;
+    e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
+    if (e == cudaSuccess) p->events.push_back(ev);
+  }
   if (e == cudaSuccess) e = cudaMalloc(&p->add2_dev, sizeof(float) * count);
   if (e == cudaSuccess) e = cudaMalloc(&p->refine_count_dev, sizeof(int));
   if (e == cudaSuccess) e = cudaMemset(p->refine_count_dev, 0, sizeof(int));
@@ -960,9 +1347,13 @@ extern "C" int kfac_inverse_plan_create(
   if (e == cudaSuccess && !ids.empty()) e = cudaMemcpy(p->ids_dev, ids.data(), sizeof(int) * ids.size(), cudaMemcpyHostToDevice);
   if (e == cudaSuccess && !descs.empty()) e = cudaMemcpy(p->descs_dev, descs.data(), sizeof(GemmDesc) * descs.size(), cudaMemcpyHostToDevice);
   if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(chol_diag_kernel,
+    e = cudaFuncSetAttribute(chol_diag_kernel<false>,
                              cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)kDiagSmemBytes);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(chol_diag_kernel<true>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)kDiagLookSmemBytes);
   if (e != cudaSuccess) {
     kfac_inverse_plan_destroy(p);
     return fail(KFAC_ERR_CUDA, "inverse_plan_create: %s", cudaGetErrorString(e));
@@ -981,7 +1372,13 @@ extern "C" int kfac_inverse_plan_create(
 // Issue every launch of one run into `st` (a real stream, or one that is
 // being captured into a graph).
 static int plan_enqueue(kfac_inverse_plan* p, int* info, float* diag_dev,
-                        cudaStream_t st) {
+                        cudaStream_t main_st, cudaStream_t* side_st) {
+  cudaStream_t st = main_st;
+  cudaStream_t sts[3] = {main_st, side_st[0], side_st[1]};
+  // fork: the side streams start after what precedes this run
+  KFAC_CUDA(cudaEventRecord(p->fork_ev, main_st));
+  KFAC_CUDA(cudaStreamWaitEvent(side_st[0], p->fork_ev, 0));
+  KFAC_CUDA(cudaStreamWaitEvent(side_st[1], p->fork_ev, 0));
   trace_kernel<<<p->count, 256, 0, st>>>(p->mats_dev, p->trace_dev, info);
   KFAC_LAUNCH_CHECK("trace_kernel");
   damping_kernel<<<ceil_div(p->count, 128), 128, 0, st>>>(
@@ -991,13 +1388,29 @@ static int plan_enqueue(kfac_inverse_plan* p, int* info, float* diag_dev,
   {
     dim3 grid(512, p->count);
     damp_copy_kernel<<<grid, 256, 0, st>>>(p->mats_dev, p->add_dev,
-                                           p->add2_dev);
+                                           p->add2_dev, p->look ? 1 : 0);
     KFAC_LAUNCH_CHECK("damp_copy_kernel");
   }
   for (const Launch& l : p->launches) {
+    if (l.kind == 2) {
+      for (int k = 0; k < 2; ++k) {
+        KFAC_CUDA(cudaEventRecord(p->join_ev[k], side_st[k]));
+        KFAC_CUDA(cudaStreamWaitEvent(main_st, p->join_ev[k], 0));
+      }
+      continue;
+    }
+    st = sts[l.stream];
+    if (l.wait_ev >= 0)
+      KFAC_CUDA(cudaStreamWaitEvent(st, p->events[l.wait_ev], 0));
+    if (l.wait_ev2 >= 0)
+      KFAC_CUDA(cudaStreamWaitEvent(st, p->events[l.wait_ev2], 0));
     if (l.kind == 0) {
-      chol_diag_kernel<<<l.n, 256, kDiagSmemBytes, st>>>(p->mats_dev, p->ids_dev + l.off,
-                                              l.step, info);
+      if (l.look)
+        chol_diag_kernel<true><<<l.n, 256, kDiagLookSmemBytes, st>>>(
+            p->mats_dev, p->ids_dev + l.off, l.step, info);
+      else
+        chol_diag_kernel<false><<<l.n, 256, kDiagSmemBytes, st>>>(
+            p->mats_dev, p->ids_dev + l.off, l.step, info);
       KFAC_LAUNCH_CHECK("chol_diag_kernel");
     } else {
       int rc = p->use_tc
@@ -1007,7 +1420,9 @@ static int plan_enqueue(kfac_inverse_plan* p, int* info, float* diag_dev,
                                          0.f, 0.f, st);
       if (rc != KFAC_OK) return rc;
     }
+    if (l.rec_ev >= 0) KFAC_CUDA(cudaEventRecord(p->events[l.rec_ev], st));
   }
+  st = main_st;
   if (p->n_refine > 0) {
     const dim3 pgrid(ceil_div(p->refine_dmax, 8), p->n_refine);
     for (int stage = 0; stage < 3; ++stage) {
@@ -1055,7 +1470,7 @@ static void plan_capture(kfac_inverse_plan* p, int* info, float* diag_dev) {
     p->graph_ok = false;
     return;
   }
-  const int rc = plan_enqueue(p, info, diag_dev, p->cap_stream);
+  const int rc = plan_enqueue(p, info, diag_dev, p->cap_stream, p->cap_side);
   cudaGraph_t graph = nullptr;
   cudaError_t e = cudaStreamEndCapture(p->cap_stream, &graph);
   const long long captured = launch_count_now() - before;
@@ -1102,7 +1517,7 @@ extern "C" int kfac_inverse_plan_run(kfac_inverse_plan* p, float damping,
       }
     }
   }
-  return plan_enqueue(p, info, diag_dev, st);
+  return plan_enqueue(p, info, diag_dev, st, p->side_stream);
 }
 
 extern "C" int kfac_inverse_plan_set_refine(kfac_inverse_plan* p, int max_dim,
@@ -1166,6 +1581,13 @@ extern "C" int kfac_inverse_plan_destroy(kfac_inverse_plan* p) {
   if (p == nullptr) return KFAC_OK;
   plan_drop_graph(p);
   if (p->cap_stream != nullptr) cudaStreamDestroy(p->cap_stream);
+  for (int k = 0; k < 2; ++k) {
+    if (p->cap_side[k] != nullptr) cudaStreamDestroy(p->cap_side[k]);
+    if (p->side_stream[k] != nullptr) cudaStreamDestroy(p->side_stream[k]);
+    if (p->join_ev[k] != nullptr) cudaEventDestroy(p->join_ev[k]);
+  }
+  if (p->fork_ev != nullptr) cudaEventDestroy(p->fork_ev);
+  for (cudaEvent_t ev : p->events) cudaEventDestroy(ev);
   cudaFree(p->params_dev);
   cudaFree(p->add2_dev);
   cudaFree(p->refine_items_dev);
