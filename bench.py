@@ -52,19 +52,19 @@ OWNERSHIP = 'balanced'   # layer ownership at N > 1 ('reference': by count)
 WORKLOADS = {
     'resnet50': dict(name='resnet50_kfac_step_b32_224',
                      layers=lambda: bw.resnet50_layers(batch=32), batch=32,
-                     decay=0.9, damping=2.5e-4, acc=1),
+                     decay=0.9, damping=2.5e-4, acc=1, bn=True),
     'config1': dict(name='mlp_784_1000_1000_10_kfac_step_b128',
                     layers=lambda: bw.mlp_layers(batch=128), batch=128,
                     decay=0.99, damping=1e-3, acc=1),
     'config2': dict(name='cifar_resnet18_kfac_step_b128_32',
                     layers=lambda: bw.resnet18_cifar_layers(batch=128),
-                    batch=128, decay=0.99, damping=1e-3, acc=1),
+                    batch=128, decay=0.99, damping=1e-3, acc=1, bn=True),
     'config4': dict(name='curvature_microbench_54_pairs_m8192',
                     layers=lambda: bw.resnet50_layers(batch=32), batch=32,
                     decay=1.0, damping=0.0, acc=1, prebuilt=8192),
     'config5': dict(name='resnet50_kfac_acc16_b32_224',
                     layers=lambda: bw.resnet50_layers(batch=32), batch=32,
-                    decay=0.9, damping=2.5e-4, acc=16),
+                    decay=0.9, damping=2.5e-4, acc=16, bn=True),
 }
 
 # DRAM bytes of single launches measured with ncu on small cases (the
@@ -79,32 +79,47 @@ TRAFFIC_CASES = {
 }
 
 
-def algorithmic_flops(dims, prebuilt=False):
+def algorithmic_flops(layers, prebuilt=False):
     """Flops per step per GPU: one triangle of each factor, d^3 per inverse,
-    two products per preconditioned gradient."""
-    factor = 0 if prebuilt else sum(
-        rA * dA * (dA + 1) + rG * dG * (dG + 1) for dA, dG, rA, rG in dims)
-    inverse = sum(dA ** 3 + dG ** 3 for dA, dG, _, _ in dims)
-    precond = sum(2 * dG * dG * dA + 2 * dG * dA * dA for dA, dG, _, _ in dims)
-    return dict(factor=float(factor), inverse=float(inverse),
-                precondition=float(precond))
+    two products per preconditioned gradient (one matrix-vector product for a
+    BatchNormalization block)."""
+    factor = inverse = precond = 0.0
+    for l in layers:
+        for d, rows in bw.block_factors(l):
+            if not prebuilt:
+                factor += float(rows) * d * (d + 1)
+            inverse += float(d) ** 3
+        if l['kind'] == 'bn':
+            precond += 2.0 * (2 * l['c']) ** 2
+        else:
+            dA, dG, _, _ = bw.layer_dims(l)
+            precond += 2.0 * dG * dG * dA + 2.0 * dG * dA * dA
+    return dict(factor=factor, inverse=inverse, precondition=precond)
 
 
-def algorithmic_bytes(layers, dims, prebuilt=False):
+def algorithmic_bytes(layers, prebuilt=False):
     """Minimum DRAM bytes per step per GPU: each un-expanded input once and
     each factor written once (plus read for the running average); factor read
-    + inverse written; both inverses, gradient, result."""
-    factor = 0.0
-    if not prebuilt:
-        for l, (dA, dG, rA, rG) in zip(layers, dims):
-            if l['kind'] == 'conv':
-                src = l['n'] * l['cin'] * l['hin'] ** 2 + rG * dG
+    + inverse written; inverses, gradient, result."""
+    factor = inverse = precond = 0.0
+    for l in layers:
+        sides = [d for d, _ in bw.block_factors(l)]
+        sq = sum(d * d for d in sides)
+        if not prebuilt:
+            if l['kind'] == 'bn':
+                src = 2 * l['n'] * l['c'] * l['h'] ** 2
+            elif l['kind'] == 'conv':
+                src = l['n'] * (l['cin'] * l['hin'] ** 2 +
+                                l['cout'] * l['hout'] ** 2)
             else:
-                src = rA * l['cin'] + rG * dG
-            factor += 4.0 * (src + 2 * (dA * dA + dG * dG))
-    inverse = sum(4.0 * 2 * (dA * dA + dG * dG) for dA, dG, _, _ in dims)
-    precond = sum(4.0 * (dG * dG + dA * dA + 3 * dG * dA)
-                  for dA, dG, _, _ in dims)
+                src = l['n'] * (l['cin'] + l['cout'])
+            factor += 4.0 * (src + 2 * sq)
+        inverse += 4.0 * 2 * sq
+        if l['kind'] == 'bn':
+            precond += 4.0 * (sq + 4 * l['c'])
+        else:
+            dA, dG, _, _ = bw.layer_dims(l)
+            precond += 4.0 * (sq + 3 * dG * dA)
     return dict(factor=factor, inverse=inverse, precondition=precond)
 
 
@@ -211,54 +226,82 @@ class ClockSampler(object):
 
 
 # ------------------------------------------------------------- GPU workload
+STAB_COEFF = 16.0      # BatchNormalization blocks: damping * stab_coeff
+
+
 class DeviceWorkload(object):
     """Synthetic per-layer activations, output gradients, weights and K-FAC
-    state of one benchmark configuration, resident on one GPU."""
+    state of one benchmark configuration, resident on one GPU.
 
-    def __init__(self, device, seed, spec):
+    A *block* is a layer with curvature: a convolution / fully-connected layer
+    (two factors A, G; parameters W [, b]) or a BatchNormalization layer (one
+    factor F of side 2c; parameters gamma, beta).  Factors live in flat lists
+    (`ema`, `inv`, ...); `fidx[i]` lists the factor indices of block i."""
+
+    def __init__(self, device, seed, spec, bn_blocks=True):
         import torch
         from chainerkfac_b200 import ops
         self.torch, self.ops, self.spec = torch, ops, spec
         self.layers = spec['layers']()
-        self.dims = [bw.layer_dims(l) for l in self.layers]
         self.decay, self.damping = spec['decay'], spec['damping']
         self.acc = spec['acc']
         self.prebuilt = spec.get('prebuilt')
+        if bn_blocks and spec.get('bn') and not self.prebuilt:
+            self.layers = self.layers + bw.bn_layers_of(self.layers)
+        self.dims = [bw.layer_dims(l) for l in self.layers]
         g = torch.Generator(device=device)
         g.manual_seed(seed)
-        self.x, self.gy, self.W, self.b = [], [], [], []
-        self.gW, self.gb, self.vW, self.vb = [], [], [], []
-        self.ema, self.inv = [], []
-        for i, (l, (dA, dG, _, _)) in enumerate(zip(self.layers, self.dims)):
+        nl = len(self.layers)
+        self.x, self.gy = [None] * nl, [None] * nl
+        # parameters, gradients, velocities per block: [W, b] or [gamma, beta]
+        self.P, self.gP, self.vP = [], [], []
+        self.ema, self.inv, self.fidx = [], [], []
+        self.bn_grads, self.bn_kf = [None] * nl, [None] * nl
+        for i, l in enumerate(self.layers):
             n = l['n']
-            if l['kind'] == 'conv':
+            if l['kind'] == 'bn':
+                xs = gs = (n, l['c'], l['h'], l['h'])
+                shapes = [(l['c'],), (l['c'],)]
+                sides = [2 * l['c']]
+            elif l['kind'] == 'conv':
                 xs = (n, l['cin'], l['hin'], l['hin'])
                 gs = (n, l['cout'], l['hout'], l['hout'])
-                ws = (l['cout'], l['cin'], l['k'], l['k'])
+                shapes = [(l['cout'], l['cin'], l['k'], l['k'])]
+                sides = list(self.dims[i][:2])
             else:
-                xs, gs, ws = (n, l['cin']), (n, l['cout']), (l['cout'], l['cin'])
+                xs, gs = (n, l['cin']), (n, l['cout'])
+                shapes = [(l['cout'], l['cin'])]
+                sides = list(self.dims[i][:2])
+            if l['kind'] != 'bn':
+                shapes.append((shapes[0][0],) if l['bias'] else None)
             if not self.prebuilt:
                 x = torch.randn(xs, device=device, generator=g)
-                if i > 0:
+                if i > 0 and l['kind'] != 'bn':
                     x.clamp_(min=0)          # post-ReLU activations
-                self.x.append(x)
-                self.gy.append(torch.randn(gs, device=device, generator=g) / n)
-            fan = ws[1] * (ws[2] * ws[3] if len(ws) == 4 else 1)
-            self.W.append(torch.randn(ws, device=device, generator=g) / fan ** 0.5)
-            self.gW.append(torch.randn(ws, device=device, generator=g) * 1e-2)
-            self.vW.append(torch.zeros(ws, device=device))
-            if l['bias']:
-                self.b.append(torch.zeros(ws[0], device=device))
-                self.gb.append(torch.randn(ws[0], device=device, generator=g) * 1e-2)
-                self.vb.append(torch.zeros(ws[0], device=device))
-            else:
-                self.b.append(None)
-                self.gb.append(None)
-                self.vb.append(None)
-            self.ema += [torch.zeros((dA, dA), device=device),
-                         torch.zeros((dG, dG), device=device)]
-            self.inv += [torch.empty((dA, dA), device=device),
-                         torch.empty((dG, dG), device=device)]
+                self.x[i] = x
+                self.gy[i] = torch.randn(gs, device=device, generator=g) / n
+            P, gP, vP = [], [], []
+            for shp in shapes:
+                if shp is None:
+                    P.append(None); gP.append(None); vP.append(None)
+                    continue
+                fan = 1
+                for v in shp[1:]:
+                    fan *= v
+                P.append(torch.randn(shp, device=device, generator=g) /
+                         fan ** 0.5)
+                gP.append(torch.randn(shp, device=device, generator=g) * 1e-2)
+                vP.append(torch.zeros(shp, device=device))
+            self.P.append(P); self.gP.append(gP); self.vP.append(vP)
+            self.fidx.append(list(range(len(self.ema),
+                                        len(self.ema) + len(sides))))
+            for d in sides:
+                self.ema.append(torch.zeros((d, d), device=device))
+                self.inv.append(torch.empty((d, d), device=device))
+            if l['kind'] == 'bn':
+                self.bn_grads[i] = torch.empty((n, 2 * l['c']), device=device)
+                self.bn_kf[i] = [torch.empty_like(t) for t in P]
+        self.bn_flags = torch.zeros((nl, 2), dtype=torch.int32, device=device)
         if self.prebuilt:
             # factors X^T X / m + 1e-3 I from X ~ N(0,1) with m rows, built
             # once; the timed step only inverts and preconditions
@@ -271,76 +314,105 @@ class DeviceWorkload(object):
         if self.acc > 1:
             self.cov = [torch.zeros_like(e) for e in self.ema]
             self.acc_cov = [torch.zeros_like(e) for e in self.ema]
-            self.acc_gW = [torch.zeros_like(w) for w in self.gW]
+            self.acc_g = [[None if t is None else torch.zeros_like(t)
+                           for t in gp] for gp in self.gP]
             self.micro = 0
-        self.make_plan(list(range(len(self.layers))))
+        self.make_plan(list(range(nl)))
         self.first = True
-        self.input_bytes = sum(t.numel() * 4 for t in self.x + self.gy)
+        self.input_bytes = sum(t.numel() * 4 for t in self.x + self.gy
+                               if t is not None)
+
+    def is_bn(self, i):
+        return self.layers[i]['kind'] == 'bn'
 
     def make_plan(self, own, bounds=None):
-        cnt = len(own)
-        if self.prebuilt:
-            # the 1e-3 I inside the factors is the damping: nothing is added
-            partner, role, scale = [-1] * (2 * cnt), [2] * (2 * cnt), \
-                [0.0] * (2 * cnt)
-        else:
-            partner = [k ^ 1 for k in range(2 * cnt)]
-            role = [k & 1 for k in range(2 * cnt)]
-            scale = None
-        self.plan = self.ops.InversePlanSet(
-            [self.ema[2 * i + j] for i in own for j in (0, 1)],
-            [self.inv[2 * i + j] for i in own for j in (0, 1)],
-            partner, role, scale=scale, bounds=bounds)
+        factors, inverses, partner, role, scale = [], [], [], [], []
+        for i in own:
+            base = len(factors)
+            ks = self.fidx[i]
+            for j, k in enumerate(ks):
+                factors.append(self.ema[k])
+                inverses.append(self.inv[k])
+                if self.prebuilt:
+                    # the 1e-3 I inside the factors is the damping
+                    partner.append(-1); role.append(2); scale.append(0.0)
+                elif len(ks) == 2:
+                    partner.append(base + 1 - j); role.append(j)
+                    scale.append(1.0)
+                else:
+                    partner.append(-1); role.append(2)
+                    scale.append(STAB_COEFF)
+        self.plan = self.ops.InversePlanSet(factors, inverses, partner, role,
+                                            scale=scale, bounds=bounds)
         self.plan_layers = own
-        self.class_layers = [sorted({own[i // 2] for i in idx})
+        owner_of = [i for i in own for _ in self.fidx[i]]
+        self.class_layers = [sorted({owner_of[q] for q in idx})
                              for idx in self.plan.classes()]
 
-    def layer_items(self, i, A, G, r, rest):
+    def layer_items(self, i, outs, r, rest):
+        """Grouped-build items of block i's factors into `outs` (one tensor
+        per factor).  BatchNormalization blocks need their per-sample
+        gradients first (bn_prepare)."""
         ops, l = self.ops, self.layers[i]
         n = l['n']
+        if l['kind'] == 'bn':
+            return [ops.dense_item(self.bn_grads[i], False, r / n, rest,
+                                   outs[0])]
         if l['kind'] == 'conv':
             return [ops.conv_input_item(self.x[i], l['k'], l['stride'],
-                                        l['pad'], l['bias'], r / n, rest, A),
+                                        l['pad'], l['bias'], r / n, rest,
+                                        outs[0]),
                     ops.conv_grad_item(self.gy[i],
-                                       r * n / float(l['hout'] ** 2), rest, G)]
-        return [ops.dense_item(self.x[i], l['bias'], r / n, rest, A),
-                ops.dense_item(self.gy[i], False, r * n, rest, G)]
+                                       r * n / float(l['hout'] ** 2), rest,
+                                       outs[1])]
+        return [ops.dense_item(self.x[i], l['bias'], r / n, rest, outs[0]),
+                ops.dense_item(self.gy[i], False, r * n, rest, outs[1])]
 
-    def factor_items(self, outs, r, rest):
+    def bn_prepare(self, layers):
+        """Per-sample gradients of the BatchNormalization blocks among
+        `layers`, one grouped call."""
+        items = [self.ops.bn_item(self.x[i], self.gy[i], 2e-5,
+                                  float(self.layers[i]['n']), self.bn_grads[i])
+                 for i in layers if self.is_bn(i)]
+        self.ops.bn_sample_grads_group(items)
+
+    def build(self, layers, outs, r, rest):
+        """Factors of `layers` into the flat list `outs`, one grouped call
+        (plus the grouped per-sample gradients of BatchNormalization)."""
+        if not layers:
+            return
+        self.bn_prepare(layers)
         items = []
-        for i in range(len(self.layers)):
-            items += self.layer_items(i, outs[2 * i], outs[2 * i + 1], r, rest)
-        return items
+        for i in layers:
+            items += self.layer_items(i, [outs[k] for k in self.fidx[i]], r,
+                                      rest)
+        self.ops.factor_group(items, self.ema[0].device)
 
     # -- stages timed alone (nothing else on the device) --------------------
     def factors_alone(self):
         """Every factor in one grouped call, no inverse started beside it."""
-        items = self.factor_items(self.ema, self.decay, 1.0 - self.decay)
-        self.ops.factor_group(items, self.ema[0].device)
+        self.build(list(range(len(self.layers))), self.ema, self.decay,
+                   1.0 - self.decay)
 
     def inverses_alone(self):
         self.plan.run(self.damping, not self.prebuilt)
 
     def precondition_alone(self):
-        own = self.plan_layers
-        self.ops.precondition(
-            [self.inv[2 * i + 1] for i in own], [self.inv[2 * i] for i in own],
-            [self.gW[i] for i in own], [self.gb[i] for i in own], None, None,
-            [self.W[i] for i in own], [self.b[i] for i in own],
-            [self.vW[i] for i in own], [self.vb[i] for i in own], lr=0.0,
-            momentum=1.0)
+        self.precondition_layers(self.plan_layers, lr=0.0, momentum=1.0,
+                                 grads=self.gP)
 
     # -- the step ------------------------------------------------------------
+    def flat(self, per_block):
+        return [t for blk in per_block for t in blk if t is not None]
+
     def accumulate(self):
         """Micro-step of an accumulated update: build this micro-batch's
         factors and add 1/acc of them (and of the gradients) to the
         accumulators in one launch."""
-        dev = self.ema[0].device
-        self.ops.factor_group(self.factor_items(self.cov, 1.0, 0.0), dev)
+        self.build(list(range(len(self.layers))), self.cov, 1.0, 0.0)
         s, keep = 1.0 / self.acc, (0.0 if self.micro == 0 else 1.0)
-        self.ops.axpby_group(s, self.cov + self.gW, keep,
-                             self.acc_cov + self.acc_gW,
-                             self.acc_cov + self.acc_gW)
+        acc = self.acc_cov + self.flat(self.acc_g)
+        self.ops.axpby_group(s, self.cov + self.flat(self.gP), keep, acc, acc)
         self.micro += 1
 
     def ema_weights(self):
@@ -355,7 +427,6 @@ class DeviceWorkload(object):
         # factors are still being built
         if self.prebuilt:
             return
-        dev = self.ema[0].device
         if self.acc > 1:
             self.accumulate()
             if self.micro == self.acc:
@@ -363,15 +434,14 @@ class DeviceWorkload(object):
                 self.ops.axpby_group(r, self.acc_cov, rest, self.ema, self.ema)
             return
         r, rest = self.ema_weights()
-        items = self.factor_items(self.ema, r, rest)
-        classes = self.plan.classes() if OVERLAP else []
+        classes = self.class_layers if OVERLAP else []
         done = set()
-        for c, idx in enumerate(classes[:-1]):
-            self.ops.factor_group([items[i] for i in idx], dev)
+        for c, layers in enumerate(classes[:-1]):
+            self.build(layers, self.ema, r, rest)
             self.plan.start_class(c, self.damping, True)
-            done.update(idx)
-        self.ops.factor_group([it for i, it in enumerate(items)
-                               if i not in done], dev)
+            done.update(layers)
+        self.build([i for i in range(len(self.layers)) if i not in done],
+                   self.ema, r, rest)
 
     def update_due(self):
         if self.acc > 1:
@@ -388,18 +458,33 @@ class DeviceWorkload(object):
                       after_class=self.precondition_class if OVERLAP else None)
 
     def grads(self):
-        return self.acc_gW if self.acc > 1 else self.gW
+        return self.acc_g if self.acc > 1 else self.gP
 
-    def precondition_layers(self, layers, ws_key=None):
-        gW = self.grads()
-        self.ops.precondition(
-            [self.inv[2 * i + 1] for i in layers],
-            [self.inv[2 * i] for i in layers],
-            [gW[i] for i in layers], [self.gb[i] for i in layers],
-            None, None,
-            [self.W[i] for i in layers], [self.b[i] for i in layers],
-            [self.vW[i] for i in layers], [self.vb[i] for i in layers],
-            lr=LR, momentum=MOMENTUM, ws_key=ws_key)
+    def precondition_layers(self, layers, ws_key=None, lr=LR,
+                            momentum=MOMENTUM, grads=None):
+        g = grads if grads is not None else self.grads()
+        conn = [i for i in layers if not self.is_bn(i)]
+        bn = [i for i in layers if self.is_bn(i)]
+        if conn:
+            self.ops.precondition(
+                [self.inv[self.fidx[i][1]] for i in conn],
+                [self.inv[self.fidx[i][0]] for i in conn],
+                [g[i][0] for i in conn], [g[i][1] for i in conn], None, None,
+                [self.P[i][0] for i in conn], [self.P[i][1] for i in conn],
+                [self.vP[i][0] for i in conn], [self.vP[i][1] for i in conn],
+                lr=lr, momentum=momentum, ws_key=ws_key)
+        if bn:
+            self.ops.bn_precondition_group(
+                [self.inv[self.fidx[i][0]] for i in bn],
+                [g[i][0] for i in bn], [g[i][1] for i in bn],
+                [self.bn_kf[i][0] for i in bn],
+                [self.bn_kf[i][1] for i in bn],
+                [self.bn_flags[i] for i in bn],
+                param_gamma=[self.P[i][0] for i in bn],
+                param_beta=[self.P[i][1] for i in bn],
+                mom_gamma=[self.vP[i][0] for i in bn],
+                mom_beta=[self.vP[i][1] for i in bn], lr=lr,
+                momentum=momentum)
 
     def precondition_class(self, c):
         self.precondition_layers(self.class_layers[c], ws_key=c)
@@ -441,16 +526,17 @@ class DistributedWorkload(DeviceWorkload):
     as a class is reduced its owners start its inverses on a side stream, next
     to the factor build and exchange of the remaining classes."""
 
-    def __init__(self, device, seed, spec, comm):
-        super(DistributedWorkload, self).__init__(device, seed, spec)
+    def __init__(self, device, seed, spec, comm, bn_blocks=True):
+        super(DistributedWorkload, self).__init__(device, seed, spec,
+                                                  bn_blocks)
         import torch
         self.comm = comm
         from chainerkfac_b200.optimizers.kfac import balanced_split
         cnt = len(self.layers)
+        sides = [[self.ema[k].shape[0] for k in ks] for ks in self.fidx]
         if OWNERSHIP == 'balanced':
             self.indices = balanced_split(
-                [float(dA) ** 3 + float(dG) ** 3
-                 for dA, dG, _, _ in self.dims], comm.size)
+                [sum(float(d) ** 3 for d in sd) for sd in sides], comm.size)
         else:
             # the reference's contiguous split of the layer list by count
             self.indices = [ix.tolist() for ix in
@@ -462,8 +548,7 @@ class DistributedWorkload(DeviceWorkload):
         self.plan.close()
         self.make_plan(self.mine, bounds)
         # size classes over all layers, largest first, as the plan forms them
-        key_of = [sum(max(dA, dG) > b for b in bounds)
-                  for dA, dG, _, _ in self.dims]
+        key_of = [sum(max(sd) > b for b in bounds) for sd in sides]
         pipelined = OVERLAP and self.acc == 1 and not self.prebuilt
         keys = sorted(set(key_of), reverse=True) if pipelined else [None]
         src = None if self.prebuilt else (
@@ -478,37 +563,31 @@ class DistributedWorkload(DeviceWorkload):
                 for i in idx:
                     if i not in layers:
                         continue
-                    # sorted parameter names: W before b
-                    loc.append((gsrc[i], False))
-                    if self.gb[i] is not None:
-                        loc.append((self.gb[i], False))
+                    # gradients (sorted parameter names), then the factors
+                    loc += [(t, False) for t in gsrc[i] if t is not None]
                     if src is not None:
-                        loc.append((src[2 * i], True))
-                        loc.append((src[2 * i + 1], True))
+                        loc += [(src[k], True) for k in self.fidx[i]]
                 rs.append(loc)
             self.xclass_layers.append(layers)
             self.class_rs.append(rs)
             self.class_plan.append(
                 self.plan.class_keys.index(key)
                 if key in self.plan.class_keys else None)
-        self.ag_arrays = []
-        for idx in self.indices:
-            ag = []
-            for i in idx:
-                ag.append((self.W[i], False))
-                if self.b[i] is not None:
-                    ag.append((self.b[i], False))
-            self.ag_arrays.append(ag)
+        self.ag_arrays = [[(t, False) for i in idx for t in self.P[i]
+                           if t is not None] for idx in self.indices]
         self.comm_stream = torch.cuda.Stream(priority=-1)
         if hasattr(comm, 'reserve'):
             from chainerkfac_b200.communicators import _utility
             comm.reserve(max([_utility.get_nelems(rs) for rs in self.class_rs]
                              + [_utility.get_nelems(self.ag_arrays)]), device)
 
+    def own_factors(self, layers=None):
+        mine = set(self.mine)
+        return [k for i in (layers if layers is not None else self.mine)
+                if i in mine for k in self.fidx[i]]
+
     def factors(self):
         torch = self.torch
-        dev = self.ema[0].device
-        mine = set(self.mine)
         if self.prebuilt:
             # only the gradients travel to the owners
             self.comm.reduce_scatter_v_arrays(self.class_rs[0])
@@ -519,18 +598,16 @@ class DistributedWorkload(DeviceWorkload):
                 # one exchange per update: accumulated factors and gradients
                 self.comm.reduce_scatter_v_arrays(self.class_rs[0])
                 r, rest = self.ema_weights()
-                own = [2 * i + j for i in self.mine for j in (0, 1)]
+                own = self.own_factors()
                 emas = [self.ema[k] for k in own]
                 self.ops.axpby_group(r, [self.acc_cov[k] for k in own], rest,
                                      emas, emas)
             return
         r, rest = self.ema_weights()
-        items = self.factor_items(self.cov, 1.0, 0.0)
         last = len(self.xclass_layers) - 1
         main = torch.cuda.current_stream()
         for c, layers in enumerate(self.xclass_layers):
-            self.ops.factor_group(
-                [items[2 * i + j] for i in layers for j in (0, 1)], dev)
+            self.build(layers, self.cov, 1.0, 0.0)
             # exchange 1 for this class and the owner's running average run
             # on the exchange stream: the factor build of the next class does
             # not wait for the other ranks
@@ -543,7 +620,7 @@ class DistributedWorkload(DeviceWorkload):
                 side.wait_event(built)
             with torch.cuda.stream(side):
                 self.comm.reduce_scatter_v_arrays(self.class_rs[c])
-                own = [2 * i + j for i in layers if i in mine for j in (0, 1)]
+                own = self.own_factors(layers)
                 if own:
                     emas = [self.ema[k] for k in own]
                     self.ops.axpby_group(r, [self.cov[k] for k in own], rest,
@@ -577,8 +654,8 @@ class DistributedWorkload(DeviceWorkload):
         if self.prebuilt:
             return None
         world = self.comm.size
-        small = [i for i, (dA, dG, _, _) in enumerate(self.dims)
-                 if max(dA, dG) <= 600]
+        small = [i for i, l in enumerate(self.layers)
+                 if l['kind'] != 'bn' and max(self.dims[i][:2]) <= 600]
         i = small[len(small) // 2] if small else 0
         owner = [r for r, ix in enumerate(self.indices) if i in ix][0]
         self.first = True
@@ -586,16 +663,16 @@ class DistributedWorkload(DeviceWorkload):
         torch.cuda.synchronize()
         # the factors this rank contributed (every micro-step of an
         # accumulated update saw the same synthetic batch)
-        mine = [torch.empty_like(self.ema[2 * i + j]) for j in (0, 1)]
-        self.ops.factor_group(self.layer_items(i, mine[0], mine[1], 1.0, 0.0),
+        mine = [torch.empty_like(self.ema[k]) for k in self.fidx[i]]
+        self.ops.factor_group(self.layer_items(i, mine, 1.0, 0.0),
                               mine[0].device)
         worst_f = worst_i = 0.0
         means = []
-        for j in (0, 1):
+        for j, k in enumerate(self.fidx[i]):
             parts = [torch.empty_like(mine[j]) for _ in range(world)]
             dist.all_gather(parts, mine[j])
             mean = sum(p.double() for p in parts) / world
-            got = self.ema[2 * i + j].clone()
+            got = self.ema[k].clone()
             dist.broadcast(got, src=owner)
             worst_f = max(worst_f, float((got.double() - mean).norm() /
                                          mean.norm()))
@@ -604,16 +681,16 @@ class DistributedWorkload(DeviceWorkload):
         pi = float(((A.trace() * G.shape[0]) /
                     (G.trace() * A.shape[0])).sqrt())
         adds = (pi * self.damping ** 0.5, self.damping ** 0.5 / pi)
-        for j, (m, add) in enumerate(zip((A, G), adds)):
+        for k, m, add in zip(self.fidx[i], (A, G), adds):
             want = torch.linalg.inv(
                 m + add * torch.eye(m.shape[0], device=m.device,
                                     dtype=torch.float64))
-            got = self.inv[2 * i + j].clone()
+            got = self.inv[k].clone()
             dist.broadcast(got, src=owner)
             worst_i = max(worst_i, float((got.double() - want).norm() /
                                          want.norm()))
         diff = torch.zeros(1, device=mine[0].device, dtype=torch.float64)
-        for w in self.W + [b for b in self.b if b is not None]:
+        for w in self.flat(self.P):
             ref = w.clone()
             dist.broadcast(ref, src=0)
             diff = torch.maximum(diff, (w - ref).abs().max().double())
@@ -668,11 +745,13 @@ def run_ours(args):
     if world > 1:
         from chainerkfac_b200.communicators import create_communicator
         wl = DistributedWorkload(device, 1234 + rank, spec,
-                                 create_communicator(COMMUNICATOR))
+                                 create_communicator(COMMUNICATOR),
+                                 bn_blocks=not args.no_bn_blocks)
     else:
-        wl = DeviceWorkload(device, 1234 + rank, spec)
-    flops = algorithmic_flops(wl.dims, prebuilt)
-    abytes = algorithmic_bytes(wl.layers, wl.dims, prebuilt)
+        wl = DeviceWorkload(device, 1234 + rank, spec,
+                            bn_blocks=not args.no_bn_blocks)
+    flops = algorithmic_flops(wl.layers, prebuilt)
+    abytes = algorithmic_bytes(wl.layers, prebuilt)
 
     def barrier():
         if world > 1:
@@ -802,7 +881,8 @@ def run_ours(args):
             traffic = tcase[1] * dom_flops / tcase[3]
         cpu = None
         if not args.no_cpu_baseline and world == 1:
-            cpu = cpu_baseline(spec, budget_s=25.0, min_passes=1)
+            cpu = cpu_baseline(spec, budget_s=25.0, min_passes=1,
+                               bn_blocks=not args.no_bn_blocks)
         line = {
             'metric': 'ResNet-50 K-FAC images/sec (factor+inverse+'
                       'precondition step)' if not prebuilt else
@@ -815,6 +895,8 @@ def run_ours(args):
             'dtype': 'f32', 'data': 'synthetic',
             'config': {'workload': spec['name'], 'batch_per_gpu': batch,
                        'layers': len(wl.layers),
+                       'bn_blocks': sum(1 for l in wl.layers
+                                        if l['kind'] == 'bn'),
                        'cov_ema_decay': spec['decay'],
                        'damping': spec['damping'], 'acc_iters': acc,
                        'l2_flush': ('inputs larger than L2 (%.2f GB of '
@@ -877,7 +959,8 @@ def run_e2e(args, device, world, rank, spec):
     step, h2d, d2h = build_training_step(
         device, spec['batch'], world, rank, cov_ema_decay=spec['decay'],
         damping=spec['damping'], lr=LR, momentum=MOMENTUM,
-        communicator=COMMUNICATOR, acc_iters=acc, bn_blocks=args.bn_blocks)
+        communicator=COMMUNICATOR, acc_iters=acc,
+        bn_blocks=not args.no_bn_blocks)
     steps = args.steps * acc
     for _ in range(max(args.warmup, 3) * acc):
         step()
@@ -898,7 +981,7 @@ def run_e2e(args, device, world, rank, spec):
     return dict(value=spec['batch'] * world / (per * 1e-3), unit='images/sec',
                 ms_per_step=per * acc, ms_per_micro_step=per,
                 h2d_bytes_per_step=h2d * acc, d2h_bytes_per_step=d2h * acc,
-                bn_blocks=bool(args.bn_blocks))
+                bn_blocks=not args.no_bn_blocks)
 
 
 # ------------------------------------------------------------- CPU baseline
@@ -919,6 +1002,12 @@ def use_all_host_threads():
 
 def cpu_layer_inputs(l, rng):
     n = l['n']
+    if l['kind'] == 'bn':
+        shp = (n, l['c'], l['h'], l['h'])
+        return (rng.standard_normal(shp, dtype=np.float32),
+                rng.standard_normal(shp, dtype=np.float32) / np.float32(n),
+                rng.standard_normal(l['c'], dtype=np.float32),
+                rng.standard_normal(l['c'], dtype=np.float32))
     if l['kind'] == 'conv':
         x = rng.standard_normal((n, l['cin'], l['hin'], l['hin']), dtype=np.float32)
         gy = rng.standard_normal((n, l['cout'], l['hout'], l['hout']), dtype=np.float32) / np.float32(n)
@@ -936,6 +1025,18 @@ def cpu_layer_pass(orc, l, inputs, spec, prebuilt_AG=None):
     x, gy, gW, gb = inputs
     W, v = np.zeros_like(gW), np.zeros_like(gW)
     t0 = time.perf_counter()
+    if l['kind'] == 'bn':
+        # batch_normalization.py:78-191 (gW, gb hold the gradients of gamma
+        # and beta)
+        F = orc.bn_F(x, gy, 2e-5)
+        t1 = time.perf_counter()
+        Finv = orc.damped_inverse(
+            F, np.float32(orc.bn_damping(spec['damping'], STAB_COEFF)))
+        kg, kb = orc.bn_kfgrads(Finv, gW, gb)
+        orc.momentum_update(W, v, kg, LR, MOMENTUM)
+        orc.momentum_update(np.zeros_like(gb), np.zeros_like(gb), kb, LR,
+                            MOMENTUM)
+        return t1 - t0, time.perf_counter() - t1
     if prebuilt_AG is not None:
         A, G = prebuilt_AG
     elif l['kind'] == 'conv':
@@ -956,7 +1057,8 @@ def cpu_layer_pass(orc, l, inputs, spec, prebuilt_AG=None):
     return t1 - t0, t2 - t1
 
 
-def cpu_baseline(spec, budget_s, min_passes=1, max_passes=None):
+def cpu_baseline(spec, budget_s, min_passes=1, max_passes=None,
+                 bn_blocks=True):
     """Whole passes of the oracle (the reference's --no_cuda arithmetic) over
     the workload: one layer of each distinct shape is timed and counted once
     per layer of that shape.  Passes repeat until `budget_s` seconds are used
@@ -964,6 +1066,8 @@ def cpu_baseline(spec, budget_s, min_passes=1, max_passes=None):
     from oracle import kfac_oracle as orc
     threads = use_all_host_threads()
     layers = spec['layers']()
+    if bn_blocks and spec.get('bn') and not spec.get('prebuilt'):
+        layers = layers + bw.bn_layers_of(layers)
     groups = bw.distinct_shapes(layers)
     rng = np.random.default_rng(7)
     inputs = [cpu_layer_inputs(l, rng) for l, _ in groups]
@@ -1001,7 +1105,8 @@ def cpu_baseline(spec, budget_s, min_passes=1, max_passes=None):
     else:
         value, unit = spec['batch'] * acc / (tf + ti), 'images/sec'
     return dict(value=value, unit=unit, cores=threads,
-                host_cpus=os.cpu_count(), kind='port',
+                host_cpus=os.cpu_count(), kind='port', layers=len(layers),
+                bn_blocks=sum(1 for l in layers if l['kind'] == 'bn'),
                 factor_s=tf, inverse_precondition_s=ti,
                 passes_timed=len(times), wall_s=time.perf_counter() - t_start,
                 sample='NumPy oracle (the reference --no_cuda arithmetic '
@@ -1020,9 +1125,12 @@ def run_reference(args):
     spec = WORKLOADS[args.workload]
     # one warm-up pass, then whole passes for about a minute and a half;
     # `steps` is the number of passes really timed
-    warm = cpu_baseline(spec, budget_s=0.0, min_passes=1, max_passes=1)
+    bn = not args.no_bn_blocks
+    warm = cpu_baseline(spec, budget_s=0.0, min_passes=1, max_passes=1,
+                        bn_blocks=bn)
     want = max(1, min(args.steps, int(90.0 / max(warm['wall_s'], 1e-3))))
-    cpu = cpu_baseline(spec, budget_s=1e9, min_passes=want, max_passes=want)
+    cpu = cpu_baseline(spec, budget_s=1e9, min_passes=want, max_passes=want,
+                       bn_blocks=bn)
     value = cpu['value']
     line = {
         'impl': 'reference',
@@ -1038,7 +1146,7 @@ def run_reference(args):
         'scaling': 'strong' if spec.get('prebuilt') else 'weak',
         'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
         'config': {'workload': spec['name'], 'batch_per_gpu': spec['batch'],
-                   'layers': len(spec['layers']()),
+                   'layers': cpu['layers'], 'bn_blocks': cpu['bn_blocks'],
                    'cov_ema_decay': spec['decay'], 'damping': spec['damping'],
                    'acc_iters': spec['acc'],
                    'parallelism': 'cpu (rank 0 only, %d BLAS threads)'
@@ -1162,8 +1270,10 @@ def main():
     ap.add_argument('--workload', default='resnet50', choices=sorted(WORKLOADS))
     ap.add_argument('--no-e2e', action='store_true')
     ap.add_argument('--no-cpu-baseline', action='store_true')
-    ap.add_argument('--bn-blocks', action='store_true',
-                    help='end-to-end model with BatchNormalization blocks too')
+    ap.add_argument('--no-bn-blocks', action='store_true',
+                    help='leave the BatchNormalization layers to the plain '
+                         'momentum rule (convolution / fully-connected '
+                         'blocks only)')
     ap.add_argument('--no-overlap', action='store_true',
                     help='do not start the largest inverses during the '
                          'factor build')

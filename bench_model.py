@@ -56,7 +56,7 @@ class ResNet50(nn.Module):
 
 def build_training_step(device, batch, world, rank, cov_ema_decay, damping,
                         lr, momentum, image=224, classes=1000,
-                        bn_blocks=False, communicator='peer_memory',
+                        bn_blocks=True, communicator='peer_memory',
                         channels_last=True, acc_iters=1):
     """Returns (step, h2d_bytes, d2h_bytes).  ``step()`` copies one pinned
     host batch to the device, runs ``optimizer.update(lossfun, x, t)``

@@ -43,15 +43,12 @@ def resnet50_layers(batch=32, image=224, classes=1000):
     return layers
 
 
-def resnet50_bn_layers(batch=32, image=224):
-    """The 53 BatchNormalization layers of the same network: (channels,
-    spatial size) after each convolution."""
-    out = []
-    for l in resnet50_layers(batch, image):
-        if l['kind'] == 'conv':
-            out.append(dict(name=l['name'] + '.bn', kind='bn', c=l['cout'],
-                            h=l['hout'], n=batch))
-    return out
+def bn_layers_of(layers):
+    """The BatchNormalization layers of a network whose every convolution is
+    followed by one (ResNet-50: 53, CIFAR ResNet-18: 20): channels and
+    spatial size of the convolution's output."""
+    return [dict(name=l['name'] + '.bn', kind='bn', c=l['cout'], h=l['hout'],
+                 n=l['n'], bias=True) for l in layers if l['kind'] == 'conv']
 
 
 def resnet18_cifar_layers(batch=128, image=32, classes=10):
@@ -82,8 +79,21 @@ def mlp_layers(batch=128, sizes=(784, 1000, 1000, 10)):
                  n=batch) for i, (a, b) in enumerate(zip(sizes, sizes[1:]))]
 
 
+def block_factors(layer):
+    """[(side, rows of the matrix it is built from), ...] for the factors of a
+    layer's curvature block: (A, G) of a connection, F of side 2c built from
+    the n per-sample gradients for BatchNormalization."""
+    if layer['kind'] == 'bn':
+        return [(2 * layer['c'], layer['n'])]
+    dA, dG, rA, rG = layer_dims(layer)
+    return [(dA, rA), (dG, rG)]
+
+
 def layer_dims(layer):
-    """(dA, dG, rows_A, rows_G) of a layer dict."""
+    """(dA, dG, rows_A, rows_G) of a connection layer dict; for a
+    BatchNormalization layer (2c, 0, n, 0)."""
+    if layer['kind'] == 'bn':
+        return 2 * layer['c'], 0, layer['n'], 0
     if layer['kind'] == 'linear':
         return (layer['cin'] + int(layer['bias']), layer['cout'],
                 layer['n'], layer['n'])
@@ -96,7 +106,8 @@ def distinct_shapes(layers):
     """One layer per distinct geometry, with its multiplicity."""
     groups = {}
     for l in layers:
-        key = (l['kind'], l.get('k'), l.get('stride'), l.get('pad'), l['cin'],
-               l['cout'], l.get('hin'), l['bias'], l['n'])
+        key = (l['kind'], l.get('k'), l.get('stride'), l.get('pad'),
+               l.get('cin'), l.get('cout'), l.get('hin'), l.get('c'),
+               l.get('h'), l['bias'], l['n'])
         groups.setdefault(key, [l, 0])[1] += 1
     return [(l, m) for l, m in groups.values()]

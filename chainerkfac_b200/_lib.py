@@ -33,6 +33,15 @@ class FactorItem(ctypes.Structure):
                 ('out', ctypes.c_void_p), ('layout', ctypes.c_int)]
 
 
+class BnItem(ctypes.Structure):
+    """struct kfac_bn_item of include/kfac_b200.h."""
+    _fields_ = [('x', ctypes.c_void_p), ('gy', ctypes.c_void_p),
+                ('out', ctypes.c_void_p), ('stats', ctypes.c_void_p),
+                ('n', ctypes.c_int), ('c', ctypes.c_int), ('hw', ctypes.c_int),
+                ('layout', ctypes.c_int), ('eps', ctypes.c_float),
+                ('scale', ctypes.c_float)]
+
+
 # name -> (restype, argtypes); mirrors include/kfac_b200.h one to one.
 SIGNATURES = {
     'kfac_abi_version': (I, []),
@@ -52,6 +61,9 @@ SIGNATURES = {
     'kfac_factor_group_workspace_bytes': (SZ, [I, ctypes.POINTER(FactorItem)]),
     'kfac_factor_group': (I, [I, ctypes.POINTER(FactorItem), VP, SZ, VP]),
     'kfac_bn_sample_grads': (I, [VP, VP, I, I, I, F, F, VP, VP, VP]),
+    'kfac_bn_sample_grads_group': (I, [I, ctypes.POINTER(BnItem), VP]),
+    'kfac_bn_precondition_group': (I, [I, c_int_p] + [c_void_pp] * 10 +
+                                   [F, F, VP]),
     'kfac_axpby': (I, [I64, F, VP, F, VP, VP, VP]),
     'kfac_axpby_group': (I, [I, c_i64_p, F, c_void_pp, F, c_void_pp,
                              c_void_pp, VP]),

@@ -182,71 +182,225 @@ static int run_factor(const Operand& X, long long rows, int d, float alpha,
 }
 
 // ------------------------------------------------------------ BN sample grads
-// Pass 1: per-channel batch mean and 1/sqrt(var + eps) over (n, hw).
-__global__ void bn_stats_kernel(const float* __restrict__ x, int n, int c,
-                                int hw, float eps, float* __restrict__ stats) {
-  const int ch = blockIdx.x;
-  double s = 0.0, ss = 0.0;
-  const long long per = (long long)n * hw;
-  for (long long i = threadIdx.x; i < per; i += blockDim.x) {
-    long long smp = i / hw;
-    long long off = (smp * c + ch) * hw + (i - smp * hw);
-    double v = x[off];
-    s += v;
-    ss += v * v;
+// ---- grouped BatchNormalization work: all layers of a step in two launches
+struct BnItem {
+  const float* x;
+  const float* gy;
+  float* out;        // (n, 2c) per-sample gradients
+  float* stats;      // 2c floats: mean, 1 / sqrt(var + eps)
+  int n, c, hw;
+  int nhwc;          // 0: (n, c, hw) planes, 1: (n, hw, c) channels-last
+  float eps, scale;
+  int stat_begin;    // first block of this layer in the statistics launch
+  int grad_begin;    // first block of this layer in the gradient launch
+};
+
+constexpr int kBnItemsMax = 256;
+
+__device__ __forceinline__ int bn_find_item(const int* begins, int n, int b) {
+  int lo = 0, hi = n - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (begins[mid] <= b) lo = mid; else hi = mid - 1;
   }
-  __shared__ double sh[2][32];
-  for (int o = 16; o > 0; o >>= 1) {
-    s += __shfl_down_sync(0xffffffffu, s, o);
-    ss += __shfl_down_sync(0xffffffffu, ss, o);
-  }
-  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
-  if (l == 0) { sh[0][w] = s; sh[1][w] = ss; }
+  return lo;
+}
+
+// Batch mean and 1/sqrt(var + eps) per channel.  Planes: one block per
+// channel, threads along the pixels of each sample.  Channels-last: one block
+// per 32 channels, 32 x 8 threads, lanes along channels.
+__global__ void __launch_bounds__(256)
+bn_stats_group_kernel(const BnItem* __restrict__ items, int nitems) {
+  __shared__ int s_begin[kBnItemsMax];
+  __shared__ double sh[2][8][33];
+  for (int i = threadIdx.x; i < nitems; i += blockDim.x)
+    s_begin[i] = items[i].stat_begin;
   __syncthreads();
-  if (w == 0) {
-    const int nw = blockDim.x >> 5;
-    s = l < nw ? sh[0][l] : 0.0;
-    ss = l < nw ? sh[1][l] : 0.0;
+  const BnItem it = items[bn_find_item(s_begin, nitems, blockIdx.x)];
+  const int b = blockIdx.x - it.stat_begin;
+  const long long per = (long long)it.n * it.hw;
+  if (!it.nhwc) {
+    const int ch = b;
+    double s = 0.0, ss = 0.0;
+    for (long long i = threadIdx.x; i < per; i += blockDim.x) {
+      const long long smp = i / it.hw;
+      const double v = it.x[(smp * it.c + ch) * it.hw + (i - smp * it.hw)];
+      s += v;
+      ss += v * v;
+    }
     for (int o = 16; o > 0; o >>= 1) {
       s += __shfl_down_sync(0xffffffffu, s, o);
       ss += __shfl_down_sync(0xffffffffu, ss, o);
     }
-    if (l == 0) {
-      double mean = s / (double)per;
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+    if (l == 0) { sh[0][w][0] = s; sh[1][w][0] = ss; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      s = ss = 0.0;
+      for (int k = 0; k < 8; ++k) { s += sh[0][k][0]; ss += sh[1][k][0]; }
+      const double mean = s / (double)per;
       double var = ss / (double)per - mean * mean;
       if (var < 0.0) var = 0.0;
-      stats[ch] = (float)mean;
-      stats[c + ch] = (float)(1.0 / sqrt(var + (double)eps));
+      it.stats[ch] = (float)mean;
+      it.stats[it.c + ch] = (float)(1.0 / sqrt(var + (double)it.eps));
     }
+    return;
+  }
+  const int cx = threadIdx.x & 31, py = threadIdx.x >> 5;
+  const int ch = 32 * b + cx;
+  double s = 0.0, ss = 0.0;
+  if (ch < it.c) {
+    for (long long p = py; p < per; p += 8) {
+      const double v = it.x[p * it.c + ch];
+      s += v;
+      ss += v * v;
+    }
+  }
+  sh[0][py][cx] = s;
+  sh[1][py][cx] = ss;
+  __syncthreads();
+  if (py == 0 && ch < it.c) {
+    s = ss = 0.0;
+    for (int k = 0; k < 8; ++k) { s += sh[0][k][cx]; ss += sh[1][k][cx]; }
+    const double mean = s / (double)per;
+    double var = ss / (double)per - mean * mean;
+    if (var < 0.0) var = 0.0;
+    it.stats[ch] = (float)mean;
+    it.stats[it.c + ch] = (float)(1.0 / sqrt(var + (double)it.eps));
   }
 }
 
-// Pass 2: one warp per (sample, channel): sum_hw gy*xhat and sum_hw gy.
-__global__ void bn_sample_grads_kernel(const float* __restrict__ x,
-                                       const float* __restrict__ gy, int n,
-                                       int c, int hw, float scale,
-                                       const float* __restrict__ stats,
-                                       float* __restrict__ out) {
-  const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+// out[s, j] = scale * sum_p gy xhat, out[s, c + j] = scale * sum_p gy.
+// Planes: a warp per (sample, channel).  Channels-last: a block per (sample,
+// 32 channels), lanes along channels.
+__global__ void __launch_bounds__(256)
+bn_grads_group_kernel(const BnItem* __restrict__ items, int nitems) {
+  __shared__ int s_begin[kBnItemsMax];
+  __shared__ float sh[2][8][33];
+  for (int i = threadIdx.x; i < nitems; i += blockDim.x)
+    s_begin[i] = items[i].grad_begin;
+  __syncthreads();
+  const BnItem it = items[bn_find_item(s_begin, nitems, blockIdx.x)];
+  const int b = blockIdx.x - it.grad_begin;
+  if (!it.nhwc) {
+    const long long warp = (long long)b * 8 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (warp >= (long long)it.n * it.c) return;
+    const int smp = (int)(warp / it.c), ch = (int)(warp - (long long)smp * it.c);
+    const float mean = it.stats[ch], istd = it.stats[it.c + ch];
+    const float* px = it.x + warp * it.hw;
+    const float* pg = it.gy + warp * it.hw;
+    float a = 0.f, g0 = 0.f;
+    for (int i = lane; i < it.hw; i += 32) {
+      const float g = pg[i] * it.scale;
+      a += g * ((px[i] - mean) * istd);
+      g0 += g;
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+      a += __shfl_down_sync(0xffffffffu, a, o);
+      g0 += __shfl_down_sync(0xffffffffu, g0, o);
+    }
+    if (lane == 0) {
+      it.out[(long long)smp * 2 * it.c + ch] = a;
+      it.out[(long long)smp * 2 * it.c + it.c + ch] = g0;
+    }
+    return;
+  }
+  const int cblocks = (it.c + 31) >> 5;
+  const int smp = b / cblocks, cb = b - smp * cblocks;
+  const int cx = threadIdx.x & 31, py = threadIdx.x >> 5;
+  const int ch = 32 * cb + cx;
+  float a = 0.f, g0 = 0.f;
+  if (ch < it.c) {
+    const float mean = it.stats[ch], istd = it.stats[it.c + ch];
+    const float* px = it.x + (long long)smp * it.hw * it.c + ch;
+    const float* pg = it.gy + (long long)smp * it.hw * it.c + ch;
+    for (int p = py; p < it.hw; p += 8) {
+      const float g = pg[(long long)p * it.c] * it.scale;
+      a += g * ((px[(long long)p * it.c] - mean) * istd);
+      g0 += g;
+    }
+  }
+  sh[0][py][cx] = a;
+  sh[1][py][cx] = g0;
+  __syncthreads();
+  if (py == 0 && ch < it.c) {
+    a = g0 = 0.f;
+    for (int k = 0; k < 8; ++k) { a += sh[0][k][cx]; g0 += sh[1][k][cx]; }
+    it.out[(long long)smp * 2 * it.c + ch] = a;
+    it.out[(long long)smp * 2 * it.c + it.c + ch] = g0;
+  }
+}
+
+// Preconditioning of all BatchNormalization blocks: y = F_inv [g_gamma;
+// g_beta], a warp per row.
+struct BnPrecondItem {
+  const float* Finv;
+  const float* g0;     // gradient of gamma (c floats)
+  const float* g1;     // gradient of beta
+  float* y0;           // preconditioned gradients
+  float* y1;
+  float* p0;           // parameters and velocities for the fused update
+  float* p1;
+  float* v0;
+  float* v1;
+  int* flag;           // [0] NaN marker of this call, [1] fallback counter
+  int c;
+  int row_begin;       // first block (8 rows) of this layer in launch 1
+};
+
+__global__ void __launch_bounds__(256)
+bn_precond_group_kernel(const BnPrecondItem* __restrict__ items, int nitems) {
+  __shared__ int s_begin[kBnItemsMax];
+  for (int i = threadIdx.x; i < nitems; i += blockDim.x)
+    s_begin[i] = items[i].row_begin;
+  __syncthreads();
+  const BnPrecondItem it = items[bn_find_item(s_begin, nitems, blockIdx.x)];
+  const int d = 2 * it.c;
+  const int row = (blockIdx.x - it.row_begin) * 8 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
-  if (warp >= (long long)n * c) return;
-  const int smp = (int)(warp / c), ch = (int)(warp - (long long)smp * c);
-  const float mean = stats[ch], istd = stats[c + ch];
-  const float* px = x + warp * hw;
-  const float* pg = gy + warp * hw;
-  float a = 0.f, b = 0.f;
-  for (int i = lane; i < hw; i += 32) {
-    float g = pg[i] * scale;
-    a += g * ((px[i] - mean) * istd);
-    b += g;
-  }
-  for (int o = 16; o > 0; o >>= 1) {
-    a += __shfl_down_sync(0xffffffffu, a, o);
-    b += __shfl_down_sync(0xffffffffu, b, o);
-  }
+  if (row >= d) return;
+  const float* mr = it.Finv + (long long)row * d;
+  float s = 0.f;
+  for (int k = lane; k < d; k += 32)
+    s += mr[k] * (k < it.c ? it.g0[k] : it.g1[k - it.c]);
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_down_sync(0xffffffffu, s, o);
   if (lane == 0) {
-    out[(long long)smp * 2 * c + ch] = a;
-    out[(long long)smp * 2 * c + c + ch] = b;
+    if (row < it.c) it.y0[row] = s; else it.y1[row - it.c] = s;
+    if (isnan(s)) atomicExch(&it.flag[0], 1);
+  }
+}
+
+// Second launch, a block per layer: where the product contained a NaN the raw
+// gradients take its place (the reference's _check_nan fallback); then,
+// if parameters are given, v = momentum v - lr kf; p += v.
+__global__ void __launch_bounds__(256)
+bn_finish_group_kernel(const BnPrecondItem* __restrict__ items, float lr,
+                       float momentum) {
+  const BnPrecondItem it = items[blockIdx.x];
+  __shared__ int f;
+  if (threadIdx.x == 0) f = it.flag[0];
+  __syncthreads();
+  for (int i = threadIdx.x; i < 2 * it.c; i += blockDim.x) {
+    const bool first = i < it.c;
+    const int k = first ? i : i - it.c;
+    float* y = first ? it.y0 : it.y1;
+    float kf = y[k];
+    if (f != 0) {
+      kf = (first ? it.g0 : it.g1)[k];
+      y[k] = kf;
+    }
+    float* p = first ? it.p0 : it.p1;
+    if (p != nullptr) {
+      float* v = first ? it.v0 : it.v1;
+      const float nv = momentum * v[k] - lr * kf;
+      v[k] = nv;
+      p[k] += nv;
+    }
+  }
+  if (threadIdx.x == 0 && f != 0) {
+    it.flag[0] = 0;
+    it.flag[1] += 1;
   }
 }
 
@@ -422,19 +576,110 @@ extern "C" int kfac_factor_conv_grad(const float* gy, int n, int c, int ho,
                     workspace_bytes, (cudaStream_t)stream);
 }
 
+extern "C" int kfac_bn_sample_grads_group(int count,
+                                          const kfac_bn_item* items,
+                                          void* stream) {
+  KFAC_REQUIRE(count > 0 && items != nullptr, "bn_sample_grads_group: no items");
+  KFAC_REQUIRE(count <= kBnItemsMax,
+               "bn_sample_grads_group: %d layers in one call, at most %d",
+               count, kBnItemsMax);
+  std::vector<BnItem> tab(count);
+  long long sb = 0, gb = 0;
+  for (int i = 0; i < count; ++i) {
+    const kfac_bn_item& k = items[i];
+    KFAC_REQUIRE(k.x && k.gy && k.out && k.stats,
+                 "bn_sample_grads_group: null pointer at %d", i);
+    KFAC_REQUIRE(k.n > 0 && k.c > 0 && k.hw > 0 &&
+                     (k.layout == 0 || k.layout == 1),
+                 "bn_sample_grads_group: bad shape or layout at %d", i);
+    BnItem& t = tab[i];
+    t.x = k.x; t.gy = k.gy; t.out = k.out; t.stats = k.stats;
+    t.n = k.n; t.c = k.c; t.hw = k.hw;
+    t.nhwc = (k.layout == 1 && k.hw > 1) ? 1 : 0;
+    t.eps = k.eps; t.scale = k.scale;
+    t.stat_begin = (int)sb;
+    t.grad_begin = (int)gb;
+    const long long cb = (k.c + 31) / 32;
+    sb += t.nhwc ? cb : k.c;
+    gb += t.nhwc ? (long long)k.n * cb : ((long long)k.n * k.c + 7) / 8;
+    KFAC_REQUIRE(sb < (1ll << 31) && gb < (1ll << 31),
+                 "bn_sample_grads_group: too many blocks");
+  }
+  void* dev = nullptr;
+  int rc = ring_alloc(tab.size() * sizeof(BnItem), &dev);
+  if (rc != KFAC_OK) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  KFAC_CUDA(cudaMemcpyAsync(dev, tab.data(), tab.size() * sizeof(BnItem),
+                            cudaMemcpyHostToDevice, st));
+  bn_stats_group_kernel<<<(int)sb, 256, 0, st>>>(static_cast<BnItem*>(dev),
+                                                 count);
+  KFAC_LAUNCH_CHECK("bn_stats_group_kernel");
+  bn_grads_group_kernel<<<(int)gb, 256, 0, st>>>(static_cast<BnItem*>(dev),
+                                                 count);
+  KFAC_LAUNCH_CHECK("bn_grads_group_kernel");
+  return KFAC_OK;
+}
+
 extern "C" int kfac_bn_sample_grads(const float* x, const float* gy, int n,
                                     int c, int hw, float eps, float scale,
                                     float* out, float* stats, void* stream) {
-  KFAC_REQUIRE(x && gy && out && stats, "bn_sample_grads: null pointer");
-  KFAC_REQUIRE(n > 0 && c > 0 && hw > 0, "bn_sample_grads: bad shape");
+  kfac_bn_item it;
+  it.x = x; it.gy = gy; it.out = out; it.stats = stats;
+  it.n = n; it.c = c; it.hw = hw; it.layout = 0; it.eps = eps;
+  it.scale = scale;
+  return kfac_bn_sample_grads_group(1, &it, stream);
+}
+
+extern "C" int kfac_bn_precondition_group(
+    int count, const int* channels, const float* const* F_inv,
+    const float* const* grad_gamma, const float* const* grad_beta,
+    float* const* kf_gamma, float* const* kf_beta, float* const* param_gamma,
+    float* const* param_beta, float* const* mom_gamma, float* const* mom_beta,
+    int* const* nan_flags, float lr, float momentum, void* stream) {
+  KFAC_REQUIRE(count > 0 && channels && F_inv && grad_gamma && grad_beta &&
+                   kf_gamma && kf_beta && nan_flags,
+               "bn_precondition_group: null argument or count=%d", count);
+  KFAC_REQUIRE(count <= kBnItemsMax,
+               "bn_precondition_group: %d layers in one call, at most %d",
+               count, kBnItemsMax);
+  std::vector<BnPrecondItem> tab(count);
+  long long rb = 0;
+  for (int i = 0; i < count; ++i) {
+    KFAC_REQUIRE(channels[i] > 0 && F_inv[i] && grad_gamma[i] && grad_beta[i] &&
+                     kf_gamma[i] && kf_beta[i] && nan_flags[i],
+                 "bn_precondition_group: bad layer %d", i);
+    BnPrecondItem& t = tab[i];
+    t.Finv = F_inv[i];
+    t.g0 = grad_gamma[i]; t.g1 = grad_beta[i];
+    t.y0 = kf_gamma[i]; t.y1 = kf_beta[i];
+    const bool fused = param_gamma && param_gamma[i];
+    if (fused)
+      KFAC_REQUIRE(param_beta && param_beta[i] && mom_gamma && mom_gamma[i] &&
+                       mom_beta && mom_beta[i],
+                   "bn_precondition_group: fused update of layer %d lacks a "
+                   "parameter or velocity pointer", i);
+    t.p0 = fused ? param_gamma[i] : nullptr;
+    t.p1 = fused ? param_beta[i] : nullptr;
+    t.v0 = fused ? mom_gamma[i] : nullptr;
+    t.v1 = fused ? mom_beta[i] : nullptr;
+    t.flag = nan_flags[i];
+    t.c = channels[i];
+    t.row_begin = (int)rb;
+    rb += (2LL * channels[i] + 7) / 8;
+    KFAC_REQUIRE(rb < (1ll << 31), "bn_precondition_group: too many rows");
+  }
+  void* dev = nullptr;
+  int rc = ring_alloc(tab.size() * sizeof(BnPrecondItem), &dev);
+  if (rc != KFAC_OK) return rc;
   cudaStream_t st = (cudaStream_t)stream;
-  bn_stats_kernel<<<c, 256, 0, st>>>(x, n, c, hw, eps, stats);
-  KFAC_LAUNCH_CHECK("bn_stats_kernel");
-  long long warps = (long long)n * c;
-  int blocks = ceil_div(warps * 32, 256);
-  bn_sample_grads_kernel<<<blocks, 256, 0, st>>>(x, gy, n, c, hw, scale, stats,
-                                                 out);
-  KFAC_LAUNCH_CHECK("bn_sample_grads_kernel");
+  KFAC_CUDA(cudaMemcpyAsync(dev, tab.data(), tab.size() * sizeof(BnPrecondItem),
+                            cudaMemcpyHostToDevice, st));
+  bn_precond_group_kernel<<<(int)rb, 256, 0, st>>>(
+      static_cast<BnPrecondItem*>(dev), count);
+  KFAC_LAUNCH_CHECK("bn_precond_group_kernel");
+  bn_finish_group_kernel<<<count, 256, 0, st>>>(
+      static_cast<BnPrecondItem*>(dev), lr, momentum);
+  KFAC_LAUNCH_CHECK("bn_finish_group_kernel");
   return KFAC_OK;
 }
 

@@ -202,21 +202,85 @@ def factor_group(items, device):
                                      _stream()), 'kfac_factor_group')
 
 
-def bn_sample_grads(x, gy, eps, scale):
-    """(n, 2c) per-sample gradients of the BatchNormalization scale/shift."""
-    lib = _lib.load()
-    _chk(x, 'x')
-    _chk(gy, 'gy')
+def bn_item(x, gy, eps, scale, out=None):
+    """Item of ``bn_sample_grads_group`` for one BatchNormalization layer:
+    ``x`` / ``gy`` are (n, c) or (n, c, h, w) tensors, NCHW-contiguous or
+    channels-last (both must have the same layout)."""
+    if not (x.is_cuda and x.dtype == torch.float32 and
+            gy.dtype == torch.float32):
+        raise TypeError('x and gy must be float32 CUDA tensors')
     n, c = x.shape[0], x.shape[1]
     hw = 1
     for s in x.shape[2:]:
         hw *= s
-    out = torch.empty((n, 2 * c), dtype=torch.float32, device=x.device)
+    layout = 0
+    if _is_nhwc(x) or _is_nhwc(gy):
+        # one common layout: channels-last if either is
+        x = x.contiguous(memory_format=torch.channels_last)
+        gy = gy.contiguous(memory_format=torch.channels_last)
+        layout = 1
+    else:
+        _chk(x, 'x')
+        _chk(gy, 'gy')
+    if out is None or tuple(out.shape) != (n, 2 * c) or out.device != x.device:
+        out = torch.empty((n, 2 * c), dtype=torch.float32, device=x.device)
+    it = _lib.BnItem()
+    it.x, it.gy, it.out = x.data_ptr(), gy.data_ptr(), out.data_ptr()
     stats = torch.empty(2 * c, dtype=torch.float32, device=x.device)
-    _lib.check(lib.kfac_bn_sample_grads(
-        _p(x), _p(gy), n, c, hw, eps, scale, _p(out), _p(stats), _stream()),
-        'kfac_bn_sample_grads')
-    return out
+    it.stats = stats.data_ptr()
+    it.n, it.c, it.hw, it.layout = n, c, hw, layout
+    it.eps, it.scale = eps, scale
+    it._keep = (x, gy, out, stats)
+    it.result = out
+    return it
+
+
+def bn_sample_grads_group(items):
+    """Per-sample gradients of all given layers (see bn_item), two launches."""
+    if not items:
+        return
+    lib = _lib.load()
+    for k in range(0, len(items), 256):
+        part = items[k:k + 256]
+        arr = (_lib.BnItem * len(part))(*part)
+        _lib.check(lib.kfac_bn_sample_grads_group(len(part), arr, _stream()),
+                   'kfac_bn_sample_grads_group')
+
+
+def bn_sample_grads(x, gy, eps, scale):
+    """(n, 2c) per-sample gradients of the BatchNormalization scale/shift."""
+    it = bn_item(x, gy, eps, scale)
+    bn_sample_grads_group([it])
+    return it.result
+
+
+def bn_precondition_group(F_inv, grad_gamma, grad_beta, kf_gamma, kf_beta,
+                          nan_flags, param_gamma=None, param_beta=None,
+                          mom_gamma=None, mom_beta=None, lr=0.0, momentum=0.0):
+    """kf = F_inv [grad_gamma; grad_beta] for lists of blocks, with the NaN
+    fallback and the optional fused momentum update (kfac_b200.h)."""
+    if not F_inv:
+        return
+    lib = _lib.load()
+
+    def ptrs(lst, lo, hi):
+        if lst is None:
+            return None
+        return _lib.ptr_array([None if t is None else t.data_ptr()
+                               for t in lst[lo:hi]])
+    for lst in (F_inv, grad_gamma, grad_beta, kf_gamma, kf_beta):
+        for t in lst:
+            _chk(t, 'bn_precondition_group argument')
+    for lo in range(0, len(F_inv), 256):
+        hi = min(lo + 256, len(F_inv))
+        _lib.check(lib.kfac_bn_precondition_group(
+            hi - lo, _lib.int_array([g.numel() for g in grad_gamma[lo:hi]]),
+            ptrs(F_inv, lo, hi), ptrs(grad_gamma, lo, hi),
+            ptrs(grad_beta, lo, hi), ptrs(kf_gamma, lo, hi),
+            ptrs(kf_beta, lo, hi), ptrs(param_gamma, lo, hi),
+            ptrs(param_beta, lo, hi), ptrs(mom_gamma, lo, hi),
+            ptrs(mom_beta, lo, hi), ptrs(nan_flags, lo, hi), lr, momentum,
+            _stream()), 'kfac_bn_precondition_group')
 
 
 def axpby(a, x, b, y, out):

@@ -39,29 +39,68 @@ class FisherBlockBatchNormalization(FisherBlock):
         return in_data[1] is self.link.gamma.data or \
             in_data[2] is self.link.beta.data
 
+    # With ``deferred`` set (by the optimizer) the hook only remembers its
+    # arguments; the optimizer then computes the per-sample gradients of all
+    # BatchNormalization layers in one grouped call and builds their factors
+    # together with the other layers' (``pending_item`` / ``factor_item``).
+    deferred = False
+
     def forward_postprocess(self, func, in_data):
         pass  # F needs the output gradient
 
     def backward_preprocess(self, func, in_data, out_grad_data):
+        if self.deferred:
+            self._pending = (in_data, out_grad_data)
+            return
         self._F = self.compute_F(in_data, out_grad_data)
         self.covs = [self._F]
+
+    def _check_dims(self, x):
+        if x.dim() not in (2, 4):
+            raise RuntimeError(
+                'len(x.shape) must be 2 or 4, not {}.'.format(x.dim()))
+
+    def factor_buffer(self, c, device):
+        out = self._F
+        if out is None or out.shape[0] != 2 * c or out.device != device:
+            out = torch.empty((2 * c, 2 * c), dtype=torch.float32,
+                              device=device)
+        return out
+
+    def pending_item(self):
+        """Item of ``ops.bn_sample_grads_group`` for the pending hook
+        arguments (None if there are none)."""
+        pend = getattr(self, '_pending', None)
+        if pend is None:
+            return None
+        self._pending = None
+        x, gy = pend[0][0], pend[1][0]
+        self._check_dims(x)
+        self._grads_item = ops.bn_item(
+            x, gy, float(self.link.eps), self.gy_scale(x.shape[0]),
+            getattr(self, '_grads', None))
+        self._grads = self._grads_item.result
+        return self._grads_item
+
+    def factor_item(self):
+        """Grouped-build item F = grads^T grads / n for the gradients of the
+        last ``pending_item``; sets ``covs``."""
+        grads = self._grads
+        n, c2 = grads.shape
+        self._F = self.factor_buffer(c2 // 2, grads.device)
+        self.covs = [self._F]
+        return ops.dense_item(grads, False, 1.0 / n, 0.0, self._F)
 
     def compute_F(self, in_data, out_grad_data):
         # batch_normalization.py:78-131: per-sample gradients of (gamma, beta)
         # with xhat from batch statistics, F = grad^T grad / n
-        x = in_data[0].contiguous()
-        gy = out_grad_data[0].contiguous()
-        if x.dim() not in (2, 4):
-            raise RuntimeError(
-                'len(x.shape) must be 2 or 4, not {}.'.format(x.dim()))
+        x, gy = in_data[0], out_grad_data[0]
+        self._check_dims(x)
         n, c = x.shape[0], x.shape[1]
         grads = ops.bn_sample_grads(x, gy, float(self.link.eps),
                                     self.gy_scale(n))
-        out = self._F
-        if out is None or out.shape[0] != 2 * c or out.device != x.device:
-            out = torch.empty((2 * c, 2 * c), dtype=torch.float32,
-                              device=x.device)
-        return ops.factor_dense(grads, False, alpha=1.0 / n, out=out)
+        return ops.factor_dense(grads, False, alpha=1.0 / n,
+                                out=self.factor_buffer(c, x.device))
 
     def plan_entries(self):
         # batch_normalization.py:133-157: max(l2_coef, damping) * stab_coeff,
@@ -79,11 +118,9 @@ class FisherBlockBatchNormalization(FisherBlock):
             self.update_invs()
         return [self.diag_val_backward.expand(self.cov_emas[0].shape[0])]
 
-    def update_kfgrads(self):
-        # batch_normalization.py:159-191: F_inv [grad_gamma; grad_beta]; on
-        # NaN the raw gradients are used instead (the reference checks on the
-        # host with xp.any(xp.isnan(..)); here the library substitutes them
-        # on the device, without a synchronisation)
+    def kfgrad_args(self):
+        """(F_inv, grad_gamma, grad_beta, kf_gamma, kf_beta, nan_flag) for
+        ``ops.bn_precondition_group``."""
         self.check_attr('invs')
         gamma, beta = self.link.gamma, self.link.beta
         for p in (gamma, beta):
@@ -93,9 +130,17 @@ class FisherBlockBatchNormalization(FisherBlock):
             self._nan_flag = torch.zeros(2, dtype=torch.int32,
                                          device=gamma.data.device)
             self._nan_seen = 0
-        ops.symv_split(self.invs[0], gamma.grad.contiguous(),
-                       beta.grad.contiguous(), gamma.kfgrad, beta.kfgrad,
-                       self._nan_flag)
+        return (self.invs[0], gamma.grad.contiguous(), beta.grad.contiguous(),
+                gamma.kfgrad, beta.kfgrad, self._nan_flag)
+
+    def update_kfgrads(self):
+        # batch_normalization.py:159-191: F_inv [grad_gamma; grad_beta]; on
+        # NaN the raw gradients are used instead (the reference checks on the
+        # host with xp.any(xp.isnan(..)); here the library substitutes them
+        # on the device, without a synchronisation)
+        a = self.kfgrad_args()
+        ops.bn_precondition_group([a[0]], [a[1]], [a[2]], [a[3]], [a[4]],
+                                  [a[5]])
 
     def check_nan(self):
         """True (with the reference's warning) when a step since the last

@@ -189,6 +189,26 @@ def update_cov_emas_grouped(blocks):
         ops.axpby_group(r, xs, 1.0 - r, outs, outs)
 
 
+def pending_factor_items(blocks, forward_only=False):
+    """Grouped-build items for every factor of ``blocks`` whose hook arguments
+    are pending.  The per-sample gradients of all BatchNormalization blocks
+    among them are computed here, in one grouped call, because their factors
+    are built from those."""
+    items, bn = [], []
+    for fb in blocks:
+        if isinstance(fb, FB.FisherBlockConnection):
+            items += fb.flush_items(forward_only)
+        elif isinstance(fb, FB.FisherBlockBatchNormalization) and \
+                not forward_only:
+            it = fb.pending_item()
+            if it is not None:
+                bn.append((fb, it))
+    if bn:
+        ops.bn_sample_grads_group([it for _, it in bn])
+        items += [fb.factor_item() for fb, _ in bn]
+    return items
+
+
 class KFAC(_base.GradientMethod):
     """K-FAC optimizer (``kfac.py:119-310``); same arguments and defaults."""
 
@@ -267,10 +287,7 @@ class KFAC(_base.GradientMethod):
 
     def flush_factors(self, forward_only=False):
         """Grouped build of every factor whose hook arguments are pending."""
-        items = []
-        for fb in self.fblocks:
-            if isinstance(fb, FB.FisherBlockConnection):
-                items += fb.flush_items(forward_only)
+        items = pending_factor_items(self.fblocks, forward_only)
         if items:
             dev = next(self.target.params()).data.device
             ops.factor_group(items, dev)
@@ -280,8 +297,7 @@ class KFAC(_base.GradientMethod):
 
     def _forward_backward(self, lossfun, args, kwargs, after_forward=None):
         for fb in self.fblocks:
-            if isinstance(fb, FB.FisherBlockConnection):
-                fb.deferred = self.group_factors
+            fb.deferred = self.group_factors
         with self.kfhook:
             loss = lossfun(*args, **kwargs)
             if after_forward is not None:
@@ -456,10 +472,7 @@ class KFAC(_base.GradientMethod):
                 if id(owner[i]) not in seen:
                     seen.add(id(owner[i]))
                     blocks.append(owner[i])
-            items = []
-            for fb in blocks:
-                if isinstance(fb, FB.FisherBlockConnection):
-                    items += fb.flush_items()
+            items = pending_factor_items(blocks)
             if items:
                 ops.factor_group(items, dev)
             update_cov_emas_grouped(blocks)
@@ -520,9 +533,43 @@ class KFAC(_base.GradientMethod):
                 id(fb) not in done]
         if conn:
             self._precondition(conn)
-        for fb in fblocks:
-            if isinstance(fb, FB.FisherBlockBatchNormalization):
-                fb.update_kfgrads()
+        bn = [fb for fb in fblocks
+              if isinstance(fb, FB.FisherBlockBatchNormalization)]
+        if bn:
+            self._precondition_bn(bn)
+
+    def _precondition_bn(self, blocks):
+        """All BatchNormalization blocks in one grouped call, with the
+        momentum update fused in where the update rule allows it."""
+        cols = [[] for _ in range(6)]
+        pg, pb, vg, vb, fused_params = [], [], [], [], []
+        mom, any_fused = None, False
+        for fb in blocks:
+            for col, a in zip(cols, fb.kfgrad_args()):
+                col.append(a)
+            gamma, beta = fb.link.gamma, fb.link.beta
+            fuse = self._can_fuse(gamma) and self._can_fuse(beta)
+            if fuse:
+                m = gamma.update_rule.effective_momentum()
+                mom = m if mom is None else mom
+                fuse = (m == mom)
+            if fuse:
+                any_fused = True
+                pg.append(gamma.data)
+                pb.append(beta.data)
+                vg.append(gamma.update_rule.velocity(gamma))
+                vb.append(beta.update_rule.velocity(beta))
+                fused_params += [gamma, beta]
+            else:
+                pg.append(None)
+                pb.append(None)
+                vg.append(None)
+                vb.append(None)
+        extra = dict(param_gamma=pg, param_beta=pb, mom_gamma=vg, mom_beta=vb,
+                     lr=self.hyperparam.lr, momentum=mom) if any_fused else {}
+        ops.bn_precondition_group(*cols, **extra)
+        for p in fused_params:
+            p._kfac_applied = True
 
     def _can_fuse(self, param):
         rule = param.update_rule
@@ -683,11 +730,7 @@ class DistributedKFAC(KFAC):
         order = sorted(set(keys), reverse=True)
         for n, key in enumerate(order):
             members = [i for i, k in enumerate(keys) if k == key]
-            items = []
-            for i in members:
-                fb = self.fblocks[i]
-                if isinstance(fb, FB.FisherBlockConnection):
-                    items += fb.flush_items()
+            items = pending_factor_items([self.fblocks[i] for i in members])
             if items:
                 ops.factor_group(items, dev)
             built = torch.cuda.Event()

@@ -154,6 +154,23 @@ int kfac_bn_sample_grads(const float* x, const float* gy, int n, int c, int hw,
                          float eps, float scale, float* out, float* stats,
                          void* stream);
 
+/* kfac_bn_sample_grads for all BatchNormalization layers of a step in two
+ * launches (the reference computes them layer by layer inside its backward
+ * hook, normalizations/batch_normalization.py:78-124).  `layout` 1: x and gy
+ * are stored channels-last, (n, hw, c); 0: (n, c, hw) as in the reference.
+ * `items` is a host array (<= 256 entries) read during the call. */
+typedef struct kfac_bn_item {
+  const float* x;
+  const float* gy;
+  float* out;      /* (n, 2c) */
+  float* stats;    /* scratch, 2c floats */
+  int n, c, hw;
+  int layout;
+  float eps, scale;
+} kfac_bn_item;
+int kfac_bn_sample_grads_group(int count, const kfac_bn_item* items,
+                               void* stream);
+
 /* out = a * x + b * y elementwise over `count` floats (out may alias y).
  * Replaces the running-average expression of FisherBlock.update_cov_emas,
  * optimizers/fisher_block.py:155-163, and KFAC.accumulate_grads /
@@ -286,6 +303,21 @@ int kfac_precondition(int count, const int* dG, const int* dW,
 int kfac_symv_split(const float* m, int d, int d0, const float* x0,
                     const float* x1, float* y0, float* y1, int* nan_flag_dev,
                     void* stream);
+
+/* kfac_symv_split for `count` (<= 256) BatchNormalization blocks in two
+ * launches: kf = F_inv [grad_gamma; grad_beta] per block (F_inv is 2c x 2c),
+ * the NaN fallback to the raw gradients (nan_flags[i]: two device ints per
+ * block as in kfac_symv_split), and, for blocks whose param_gamma[i] is not
+ * NULL, the fused update v = momentum * v - lr * kf; param += v
+ * (normalizations/batch_normalization.py:159-191 and optimizers/kfac.py:
+ * 87-116).  param_* / mom_* may be NULL when no block is fused.  All pointer
+ * arrays are host arrays of device pointers, read during the call. */
+int kfac_bn_precondition_group(
+    int count, const int* channels, const float* const* F_inv,
+    const float* const* grad_gamma, const float* const* grad_beta,
+    float* const* kf_gamma, float* const* kf_beta, float* const* param_gamma,
+    float* const* param_beta, float* const* mom_gamma, float* const* mom_beta,
+    int* const* nan_flags, float lr, float momentum, void* stream);
 
 /* v = momentum * v - lr * grad; param += v over `count` floats.
  * Replaces KFACUpdateRule.update_core_gpu, optimizers/kfac.py:101-116. */

@@ -116,3 +116,60 @@ def test_factors_at_full_size(layer):
         assert rel(A, A64) < FACTOR_TOL, (fmt, rel(A, A64))
         assert rel(G, G64) < FACTOR_TOL, (fmt, rel(G, G64))
         assert torch.equal(A, A.T) and torch.equal(G, G.T)
+
+
+@pytest.mark.parametrize('c,h', [(256, 14), (1024, 14), (2048, 7)])
+def test_batch_normalization_block_at_resnet50_sizes(c, h):
+    """The BatchNormalization block (batch_normalization.py:78-191) at the
+    channel counts of ResNet-50's later stages, batch 32, 4-D inputs in both
+    layouts: per-sample gradients and factor against the oracle, the damped
+    inverse and the preconditioned gradients against the oracle applied to
+    the same factor."""
+    from chainerkfac_b200 import ops
+    n, eps, damping, stab = 32, 2e-5, 2.5e-4, 16.0
+    rng = np.random.default_rng(c + h)
+    x = rng.standard_normal((n, c, h, h)).astype(np.float32)
+    # gradients of a mean-reduced loss shrink with batch and feature-map size
+    gy = (rng.standard_normal((n, c, h, h)) * (4.0 / (n * h * h))).astype(
+        np.float32)
+    gg = rng.standard_normal(c).astype(np.float32)
+    gb = rng.standard_normal(c).astype(np.float32)
+    want_grads = orc.bn_sample_grads(x, gy, eps)
+    want_F = orc.bn_F(x, gy, eps)
+
+    def rel_np(a, b):
+        a = np.asarray(a, np.float64)
+        b = np.asarray(b, np.float64)
+        return np.linalg.norm(a - b) / np.linalg.norm(b)
+    xd, gd = torch.from_numpy(x).cuda(), torch.from_numpy(gy).cuda()
+    Fs = []
+    for fmt in (torch.contiguous_format, torch.channels_last):
+        it = ops.bn_item(xd.contiguous(memory_format=fmt),
+                         gd.contiguous(memory_format=fmt), eps, float(n))
+        ops.bn_sample_grads_group([it])
+        assert rel_np(it.result.cpu().numpy(), want_grads) < FACTOR_TOL
+        F = torch.empty((2 * c, 2 * c), device='cuda')
+        ops.factor_group([ops.dense_item(it.result, False, 1.0 / n, 0.0, F)],
+                         F.device)
+        assert rel_np(F.cpu().numpy(), want_F) < FACTOR_TOL
+        assert torch.equal(F, F.T)
+        Fs.append(F)
+    F = Fs[0]
+    inv = torch.empty_like(F)
+    plan = ops.InversePlan([F], [inv], [-1], [2], l2_coef=[0.0], scale=[stab])
+    plan.run(damping)
+    add = np.float32(orc.bn_damping(damping, stab))
+    want_inv = orc.damped_inverse(F.cpu().numpy(), add)
+    assert rel_np(inv.cpu().numpy(), want_inv) < 1e-4
+    assert int(plan.info.cpu()[0]) == 0
+    kg = torch.empty(c, device='cuda')
+    kb = torch.empty(c, device='cuda')
+    flag = torch.zeros(2, dtype=torch.int32, device='cuda')
+    ops.bn_precondition_group([inv], [torch.from_numpy(gg).cuda()],
+                              [torch.from_numpy(gb).cuda()], [kg], [kb],
+                              [flag])
+    wg, wb = orc.bn_kfgrads(want_inv, gg, gb)
+    assert rel_np(kg.cpu().numpy(), wg) < 1e-3
+    assert rel_np(kb.cpu().numpy(), wb) < 1e-3
+    assert flag.tolist() == [0, 0]
+    plan.close()
