@@ -50,6 +50,7 @@ SIGNATURES = {
     'kfac_set_engine': (I, [I]),
     'kfac_get_engine': (I, []),
     'kfac_tc_status': (I, [c_int_p]),
+    'kfac_selftest_wait_expiry': (I, [c_int_p, c_int_p]),
     'kfac_factor_workspace_bytes': (SZ, [I64, I]),
     'kfac_factor_dense': (I, [VP, I64, I, I64, I, F, F, VP, VP, SZ, VP]),
     'kfac_factor_noalloc_max_bytes': (SZ, []),
@@ -82,6 +83,7 @@ SIGNATURES = {
                           [F, F, VP, SZ, VP]),
     'kfac_symv_split': (I, [VP, I, I, VP, VP, VP, VP, VP, VP]),
     'kfac_momentum_update': (I, [I64, VP, VP, VP, F, F, VP]),
+    'kfac_normalize_weight': (I, [I64, VP, F, F, VP, VP]),
     'kfac_wire_nelems': (I64, [I, c_i64_p, c_int_p]),
     'kfac_wire_pack': (I, [I, c_void_pp, c_i64_p, c_int_p, c_int_p, I, VP,
                            VP]),
@@ -89,6 +91,10 @@ SIGNATURES = {
                              VP, VP]),
     'kfac_wire_unpack_sum': (I, [I, c_void_pp, c_i64_p, c_int_p, c_int_p, F,
                                  F, c_void_pp, I, VP]),
+    'kfac_wire_pack_as': (I, [I, I, c_void_pp, c_i64_p, c_int_p, c_int_p, I,
+                              VP, VP]),
+    'kfac_wire_unpack_sum_as': (I, [I, I, c_void_pp, c_i64_p, c_int_p,
+                                    c_int_p, F, F, c_void_pp, I, VP]),
 }
 
 _lib = None

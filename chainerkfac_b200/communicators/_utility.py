@@ -20,3 +20,16 @@ def get_local_nelems(local_arrays):
         else:
             nelems += array.numel() if hasattr(array, 'numel') else array.size
     return nelems
+
+
+def wire_torch_dtype(name):
+    """torch dtype of a wire element type given by name (or dtype)."""
+    import torch
+    table = {'float32': torch.float32, 'float16': torch.float16,
+             'bfloat16': torch.bfloat16}
+    if isinstance(name, torch.dtype):
+        name = str(name).replace('torch.', '')
+    if name not in table:
+        raise ValueError('wire_dtype must be one of {}, not {}'.format(
+            sorted(table), name))
+    return table[name]

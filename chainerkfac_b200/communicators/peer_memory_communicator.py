@@ -34,8 +34,8 @@ from chainerkfac_b200.communicators.pure_nccl_communicator import \
 
 class PeerMemoryCommunicator(PureNcclCommunicator):
 
-    def __init__(self, group=None):
-        super(PeerMemoryCommunicator, self).__init__(group)
+    def __init__(self, group=None, wire_dtype='float32'):
+        super(PeerMemoryCommunicator, self).__init__(group, wire_dtype)
         self._wires = [None, None]    # (tensor, device addresses by rank)
         self._turn = 0
         self._flag = None
@@ -46,7 +46,7 @@ class PeerMemoryCommunicator(PureNcclCommunicator):
         group; returns (local tensor, device addresses of all ranks' buffers
         in rank order).  Collective."""
         import torch.distributed._symmetric_memory as symm
-        t = symm.empty(nelems, dtype=torch.float32, device=device)
+        t = symm.empty(nelems, dtype=self.wire_dtype, device=device)
         group = self.group if self.group is not None else dist.group.WORLD
         handle = symm.rendezvous(t, group)
         ptrs = [int(p) for p in handle.buffer_ptrs]
@@ -63,7 +63,8 @@ class PeerMemoryCommunicator(PureNcclCommunicator):
 
     def _unpack_sum(self, flat, tri, ptrs, select, scale):
         from chainerkfac_b200 import ops
-        ops.wire_unpack_sum(flat, tri, ptrs, select=select, scale=scale)
+        ops.wire_unpack_sum(flat, tri, ptrs, select=select, scale=scale,
+                            wire_dtype=self.wire_dtype)
 
     # -------------------------------------------------------------------------
     def reserve(self, nelems, device):

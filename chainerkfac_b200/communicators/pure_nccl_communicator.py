@@ -20,15 +20,21 @@ from chainerkfac_b200.communicators import base
 
 class PureNcclCommunicator(base.KfacCommunicatorBase):
 
-    def __init__(self, group=None):
+    def __init__(self, group=None, wire_dtype='float32'):
         super(PureNcclCommunicator, self).__init__(group)
         self.gpu_buf_a = None   # grow-only wire buffer
+        # element type of the wire buffer.  The reference's pack kernels can
+        # cast to fp16 (:354-375,438-461) but its communicator fixes fp32
+        # (:32-33); 'float16' / 'bfloat16' halve the bytes on the wire at
+        # 16-bit accuracy of what arrives (the arrays themselves stay fp32).
+        self.wire_dtype = _utility.wire_torch_dtype(wire_dtype)
 
     # -- pieces a test can replace (pack/unpack need the CUDA library) ------
     def _wire_buffer(self, nelems, like):
         if self.gpu_buf_a is None or self.gpu_buf_a.numel() < nelems or \
-                self.gpu_buf_a.device != like.device:
-            self.gpu_buf_a = torch.empty(max(nelems, 1), dtype=torch.float32,
+                self.gpu_buf_a.device != like.device or \
+                self.gpu_buf_a.dtype != self.wire_dtype:
+            self.gpu_buf_a = torch.empty(max(nelems, 1), dtype=self.wire_dtype,
                                          device=like.device)
         return self.gpu_buf_a[:nelems]
 

@@ -457,6 +457,40 @@ axpby_group_kernel(const AxpbyArr* __restrict__ arrs, int narr, int total_items,
   }
 }
 
+// Weight rescaling of the ImageNet recipe: w *= target / (|w| + eps) when that
+// factor is below 1.  Pass 1 adds block sums of squares into *sumsq (cleared
+// by the caller), pass 2 scales.
+__global__ void __launch_bounds__(256)
+sumsq_kernel(long long count, const float* __restrict__ w,
+             float* __restrict__ sumsq) {
+  float s = 0.f;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+       i < count; i += (long long)gridDim.x * blockDim.x)
+    s += w[i] * w[i];
+  __shared__ float sh[8];
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_down_sync(0xffffffffu, s, o);
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    s = 0.f;
+    for (int k = 0; k < 8; ++k) s += sh[k];
+    atomicAdd(sumsq, s);
+  }
+}
+
+__global__ void __launch_bounds__(256)
+norm_clip_kernel(long long count, float* __restrict__ w,
+                 const float* __restrict__ sumsq, float target, float eps,
+                 float* __restrict__ scale_out) {
+  const float scale = target / (sqrtf(*sumsq) + eps);
+  if (scale_out != nullptr && blockIdx.x == 0 && threadIdx.x == 0)
+    *scale_out = scale;
+  if (!(scale < 1.f)) return;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+       i < count; i += (long long)gridDim.x * blockDim.x)
+    w[i] *= scale;
+}
+
 __global__ void momentum_kernel(long long count, const float* __restrict__ grad,
                                 float* param, float* v, float lr,
                                 float momentum) {
@@ -746,6 +780,24 @@ extern "C" int kfac_momentum_update(int64_t count, const float* grad,
   momentum_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(count, grad, param,
                                                             v, lr, momentum);
   KFAC_LAUNCH_CHECK("momentum_kernel");
+  return KFAC_OK;
+}
+
+extern "C" int kfac_normalize_weight(int64_t count, float* w,
+                                     float target_norm, float eps,
+                                     float* scratch, void* stream) {
+  if (count <= 0) return KFAC_OK;
+  KFAC_REQUIRE(w && scratch, "normalize_weight: null pointer");
+  cudaStream_t st = (cudaStream_t)stream;
+  KFAC_CUDA(cudaMemsetAsync(scratch, 0, sizeof(float), st));
+  int blocks = ceil_div(count, 256 * 8);
+  const int cap = sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  sumsq_kernel<<<blocks, 256, 0, st>>>(count, w, scratch);
+  KFAC_LAUNCH_CHECK("sumsq_kernel");
+  norm_clip_kernel<<<blocks, 256, 0, st>>>(count, w, scratch, target_norm, eps,
+                                           scratch + 1);
+  KFAC_LAUNCH_CHECK("norm_clip_kernel");
   return KFAC_OK;
 }
 

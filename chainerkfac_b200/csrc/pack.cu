@@ -6,9 +6,30 @@
 #include <mutex>
 #include <vector>
 
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
 #include "common.cuh"
 
 namespace kfac {
+
+// Element types of the wire buffer (KFAC_WIRE_*): values are rounded to the
+// wire type when packed and widened to fp32 when unpacked; sums over wire
+// buffers are formed in fp32.
+template <typename W> __device__ __forceinline__ W to_wire(float v);
+template <> __device__ __forceinline__ float to_wire<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half to_wire<__half>(float v) {
+  return __float2half_rn(v);
+}
+template <> __device__ __forceinline__ __nv_bfloat16 to_wire<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+__device__ __forceinline__ float from_wire(float v) { return v; }
+__device__ __forceinline__ float from_wire(__half v) { return __half2float(v); }
+__device__ __forceinline__ float from_wire(__nv_bfloat16 v) {
+  return __bfloat162float(v);
+}
+
 
 struct WireArray {
   float* ptr;
@@ -59,7 +80,7 @@ static const int kChunk = 8192;
 static const int kMaxWires = 16;
 
 struct WireSources {
-  const float* p[kMaxWires];
+  const void* p[kMaxWires];
   int n;
 };
 
@@ -97,16 +118,17 @@ __device__ __forceinline__ int find_array(const int* s_begin, int n_arrays,
   return lo;
 }
 
+template <typename W>
 __global__ void __launch_bounds__(256, kBlocksPerSm)
 wire_pack_kernel(const WireArray* __restrict__ arrs, int n_arrays,
-                 int total_items, float* __restrict__ wire) {
+                 int total_items, W* __restrict__ wire) {
   __shared__ int s_begin[kTabCap];
   load_item_table(arrs, n_arrays, s_begin);
   const int tx = threadIdx.x & (kTile - 1), ty = threadIdx.x >> 6;
   for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
     const WireArray a = arrs[find_array(s_begin, n_arrays, item)];
     const int t = item - (int)a.item_begin;
-    float* __restrict__ dst = wire + a.wire_off;
+    W* __restrict__ dst = wire + a.wire_off;
     if (a.tri > 0 && a.select) {
       int tr, tc;
       tri_index(t, tr, tc);
@@ -125,7 +147,8 @@ wire_pack_kernel(const WireArray* __restrict__ arrs, int n_arrays,
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const int r = rb + 4 * i;
-          if (r < d && c <= r) dst[(long long)r * (r + 1) / 2 + c] = v[i];
+          if (r < d && c <= r)
+            dst[(long long)r * (r + 1) / 2 + c] = to_wire<W>(v[i]);
         }
       }
     } else {
@@ -135,7 +158,7 @@ wire_pack_kernel(const WireArray* __restrict__ arrs, int n_arrays,
 #pragma unroll 8
       for (int k = threadIdx.x; k < kChunk; k += 256) {
         const long long w = base + k;
-        if (w < a.wire_n) dst[w] = a.select ? src[w] : 0.f;
+        if (w < a.wire_n) dst[w] = to_wire<W>(a.select ? src[w] : 0.f);
       }
     }
   }
@@ -147,6 +170,7 @@ wire_pack_kernel(const WireArray* __restrict__ arrs, int n_arrays,
 // tile and its mirror image, both as coalesced rows.  A tile is handled in
 // four passes of 16 rows (4 elements per thread and source in flight, few
 // registers, 8 blocks per SM).
+template <typename W>
 __global__ void __launch_bounds__(256, kBlocksPerSm)
 wire_unpack_kernel(const WireArray* __restrict__ arrs, int n_arrays,
                    int total_items, float scale, float ema_r,
@@ -170,12 +194,13 @@ wire_unpack_kernel(const WireArray* __restrict__ arrs, int n_arrays,
         const int rb = tr * kTile + pass * 16 + ty;   // rows rb, rb+4, ...
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
         for (int s = 0; s < srcs.n; ++s) {
-          const float* __restrict__ src = srcs.p[s] + off;
+          const W* __restrict__ src = static_cast<const W*>(srcs.p[s]) + off;
           float x[4];
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const int r = rb + 4 * i;
-            x[i] = (r < d && c <= r) ? src[(long long)r * (r + 1) / 2] : 0.f;
+            x[i] = (r < d && c <= r)
+                       ? from_wire(src[(long long)r * (r + 1) / 2]) : 0.f;
           }
 #pragma unroll
           for (int i = 0; i < 4; ++i) acc[i] += x[i];
@@ -207,12 +232,13 @@ wire_unpack_kernel(const WireArray* __restrict__ arrs, int n_arrays,
       for (int k0 = 0; k0 < kChunk; k0 += 256 * 4) {
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
         for (int s = 0; s < srcs.n; ++s) {
-          const float* __restrict__ src = srcs.p[s] + a.wire_off;
+          const W* __restrict__ src =
+              static_cast<const W*>(srcs.p[s]) + a.wire_off;
           float x[4];
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const long long w = base + k0 + i * 256 + threadIdx.x;
-            x[i] = w < a.wire_n ? src[w] : 0.f;
+            x[i] = w < a.wire_n ? from_wire(src[w]) : 0.f;
           }
 #pragma unroll
           for (int i = 0; i < 4; ++i) acc[i] += x[i];
@@ -298,10 +324,13 @@ extern "C" int64_t kfac_wire_nelems(int n_arrays, const int64_t* nelems,
   return total;
 }
 
-extern "C" int kfac_wire_pack(int n_arrays, const float* const* arrays,
-                              const int64_t* nelems, const int* tri_dim,
-                              const int* select, int zero_skipped, float* wire,
-                              void* stream) {
+extern "C" int kfac_wire_pack_as(int wire_dtype, int n_arrays,
+                                 const float* const* arrays,
+                                 const int64_t* nelems, const int* tri_dim,
+                                 const int* select, int zero_skipped,
+                                 void* wire, void* stream) {
+  KFAC_REQUIRE(wire_dtype >= 0 && wire_dtype <= 2,
+               "wire_pack: unknown wire dtype %d", wire_dtype);
   std::vector<WireArray> tab;
   long long total = 0, items = 0;
   int rc = build_table(n_arrays, const_cast<float* const*>(arrays), nelems,
@@ -313,18 +342,38 @@ extern "C" int kfac_wire_pack(int n_arrays, const float* const* arrays,
   const WireArray* tab_dev = nullptr;
   rc = upload_table(tab, st, &tab_dev);
   if (rc != KFAC_OK) return rc;
-  const long long grid = std::min<long long>(items, (long long)sm_count() * kBlocksPerSm);
-  wire_pack_kernel<<<(unsigned)grid, 256, 0, st>>>(tab_dev, n_arrays,
-                                                   (int)items, wire);
+  const unsigned grid = (unsigned)std::min<long long>(
+      items, (long long)sm_count() * kBlocksPerSm);
+  if (wire_dtype == KFAC_WIRE_F16)
+    wire_pack_kernel<__half><<<grid, 256, 0, st>>>(
+        tab_dev, n_arrays, (int)items, static_cast<__half*>(wire));
+  else if (wire_dtype == KFAC_WIRE_BF16)
+    wire_pack_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
+        tab_dev, n_arrays, (int)items, static_cast<__nv_bfloat16*>(wire));
+  else
+    wire_pack_kernel<float><<<grid, 256, 0, st>>>(
+        tab_dev, n_arrays, (int)items, static_cast<float*>(wire));
   KFAC_LAUNCH_CHECK("wire_pack_kernel");
   return KFAC_OK;
 }
 
-extern "C" int kfac_wire_unpack_sum(int n_arrays, float* const* arrays,
-                                    const int64_t* nelems, const int* tri_dim,
-                                    const int* select, float scale,
-                                    float ema_r, const float* const* wires,
-                                    int n_wires, void* stream) {
+extern "C" int kfac_wire_pack(int n_arrays, const float* const* arrays,
+                              const int64_t* nelems, const int* tri_dim,
+                              const int* select, int zero_skipped, float* wire,
+                              void* stream) {
+  return kfac_wire_pack_as(KFAC_WIRE_F32, n_arrays, arrays, nelems, tri_dim,
+                           select, zero_skipped, wire, stream);
+}
+
+extern "C" int kfac_wire_unpack_sum_as(int wire_dtype, int n_arrays,
+                                       float* const* arrays,
+                                       const int64_t* nelems,
+                                       const int* tri_dim, const int* select,
+                                       float scale, float ema_r,
+                                       const void* const* wires, int n_wires,
+                                       void* stream) {
+  KFAC_REQUIRE(wire_dtype >= 0 && wire_dtype <= 2,
+               "wire_unpack: unknown wire dtype %d", wire_dtype);
   KFAC_REQUIRE(wires != nullptr && n_wires >= 1 && n_wires <= kMaxWires,
                "wire_unpack: %d wire buffers given, 1..%d supported", n_wires,
                kMaxWires);
@@ -344,11 +393,29 @@ extern "C" int kfac_wire_unpack_sum(int n_arrays, float* const* arrays,
   const WireArray* tab_dev = nullptr;
   rc = upload_table(tab, st, &tab_dev);
   if (rc != KFAC_OK) return rc;
-  const long long grid = std::min<long long>(items, (long long)sm_count() * kBlocksPerSm);
-  wire_unpack_kernel<<<(unsigned)grid, 256, 0, st>>>(
-      tab_dev, n_arrays, (int)items, scale, ema_r, srcs);
+  const unsigned grid = (unsigned)std::min<long long>(
+      items, (long long)sm_count() * kBlocksPerSm);
+  if (wire_dtype == KFAC_WIRE_F16)
+    wire_unpack_kernel<__half><<<grid, 256, 0, st>>>(
+        tab_dev, n_arrays, (int)items, scale, ema_r, srcs);
+  else if (wire_dtype == KFAC_WIRE_BF16)
+    wire_unpack_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
+        tab_dev, n_arrays, (int)items, scale, ema_r, srcs);
+  else
+    wire_unpack_kernel<float><<<grid, 256, 0, st>>>(
+        tab_dev, n_arrays, (int)items, scale, ema_r, srcs);
   KFAC_LAUNCH_CHECK("wire_unpack_kernel");
   return KFAC_OK;
+}
+
+extern "C" int kfac_wire_unpack_sum(int n_arrays, float* const* arrays,
+                                    const int64_t* nelems, const int* tri_dim,
+                                    const int* select, float scale,
+                                    float ema_r, const float* const* wires,
+                                    int n_wires, void* stream) {
+  return kfac_wire_unpack_sum_as(
+      KFAC_WIRE_F32, n_arrays, arrays, nelems, tri_dim, select, scale, ema_r,
+      reinterpret_cast<const void* const*>(wires), n_wires, stream);
 }
 
 extern "C" int kfac_wire_unpack(int n_arrays, float* const* arrays,

@@ -31,7 +31,8 @@ __device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
 __device__ __forceinline__ bool mbar_wait_status(unsigned long long* bar,
                                                  unsigned parity,
                                                  volatile int* abort_flag,
-                                                 int* status_word) {
+                                                 int* status_word,
+                                                 unsigned limit = TC_SPIN_LIMIT) {
   const unsigned addr = smem_u32(bar);
   {
     // fast path: the phase is usually complete already; test_wait answers
@@ -46,7 +47,7 @@ __device__ __forceinline__ bool mbar_wait_status(unsigned long long* bar,
         : "memory");
     if (done) return true;
   }
-  for (unsigned i = 0; i < TC_SPIN_LIMIT; ++i) {
+  for (unsigned i = 0; i < limit; ++i) {
     unsigned done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"

@@ -1817,6 +1817,49 @@ extern "C" int kfac_tc_trace(long long* buf_dev, int capacity) {
 }
 #endif
 
+namespace kfac {
+// Self-test of the bounded barrier wait every tile kernel relies on: one warp
+// waits on a barrier that nothing will ever arrive at, with a short limit.
+// The wait must give up, raise the status word it was given and let the
+// kernel return.
+__global__ void wait_expiry_selftest_kernel(int* status, int* returned) {
+  __shared__ unsigned long long bar;
+  __shared__ volatile int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+  const bool ok = mbar_wait_status(&bar, 0, &abort_flag, status, 1u << 10);
+  if (threadIdx.x == 0) *returned = ok ? 1 : 2;
+}
+}  // namespace kfac
+
+extern "C" int kfac_selftest_wait_expiry(int* status_out, int* returned_out) {
+  KFAC_REQUIRE(status_out != nullptr && returned_out != nullptr,
+               "selftest_wait_expiry: null pointer");
+  int* dev = nullptr;
+  KFAC_CUDA(cudaMalloc(&dev, 2 * sizeof(int)));
+  cudaError_t e = cudaMemset(dev, 0, 2 * sizeof(int));
+  if (e == cudaSuccess) {
+    kfac::wait_expiry_selftest_kernel<<<1, 32>>>(dev, dev + 1);
+    kfac::count_launch();
+    e = cudaGetLastError();
+  }
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  int host[2] = {-1, -1};
+  if (e == cudaSuccess)
+    e = cudaMemcpy(host, dev, sizeof(host), cudaMemcpyDeviceToHost);
+  cudaFree(dev);
+  if (e != cudaSuccess)
+    return kfac::fail(KFAC_ERR_CUDA, "selftest_wait_expiry: %s",
+                      cudaGetErrorString(e));
+  *status_out = host[0];
+  *returned_out = host[1];
+  return KFAC_OK;
+}
+
 extern "C" int kfac_tc_status(int* status_out) {
   KFAC_REQUIRE(status_out != nullptr, "tc_status: null pointer");
   KFAC_CUDA(cudaDeviceSynchronize());

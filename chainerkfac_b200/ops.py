@@ -574,6 +574,19 @@ def momentum_update(grad, param, v, lr, momentum):
                'kfac_momentum_update')
 
 
+def normalize_weight(w, target_norm, eps=1e-9, scratch=None):
+    """In-place w *= target_norm / (|w| + eps) if that is below 1; returns the
+    two-float device scratch (|w|^2 before, factor)."""
+    lib = _lib.load()
+    _chk(w, 'w')
+    if scratch is None:
+        scratch = torch.empty(2, dtype=torch.float32, device=w.device)
+    _lib.check(lib.kfac_normalize_weight(w.numel(), _p(w), target_norm, eps,
+                                         _p(scratch), _stream()),
+               'kfac_normalize_weight')
+    return scratch
+
+
 def _wire_args(arrays, tri, select):
     nelems = [int(a.numel()) for a in arrays]
     tri_dim = [int(a.shape[0]) if t else 0 for a, t in zip(arrays, tri)]
@@ -588,29 +601,32 @@ def wire_nelems(arrays, tri):
     return int(lib.kfac_wire_nelems(n, nelems, tri_dim))
 
 
+WIRE_DTYPES = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
+
+
 def wire_pack(arrays, tri, wire, select=None, zero_skipped=False):
+    """Pack into ``wire`` (fp32, or fp16 / bf16 for a reduced-precision
+    wire)."""
     lib = _lib.load()
     n, ptrs, nelems, tri_dim, sel = _wire_args(arrays, tri, select)
-    _lib.check(lib.kfac_wire_pack(n, ptrs, nelems, tri_dim, sel,
-                                  int(bool(zero_skipped)), _p(wire),
-                                  _stream()), 'kfac_wire_pack')
+    _lib.check(lib.kfac_wire_pack_as(
+        WIRE_DTYPES[wire.dtype], n, ptrs, nelems, tri_dim, sel,
+        int(bool(zero_skipped)), ctypes.c_void_p(wire.data_ptr()), _stream()),
+        'kfac_wire_pack_as')
 
 
 def wire_unpack_sum(arrays, tri, wire_ptrs, select=None, scale=1.0,
-                    ema_r=-1.0):
+                    ema_r=-1.0, wire_dtype=torch.float32):
     """Unpack the sum of several wire buffers given as raw device addresses
     (this GPU's buffer and peer mappings of the other ranks' buffers)."""
     lib = _lib.load()
     n, ptrs, nelems, tri_dim, sel = _wire_args(arrays, tri, select)
-    _lib.check(lib.kfac_wire_unpack_sum(
-        n, ptrs, nelems, tri_dim, sel, scale, ema_r,
+    _lib.check(lib.kfac_wire_unpack_sum_as(
+        WIRE_DTYPES[wire_dtype], n, ptrs, nelems, tri_dim, sel, scale, ema_r,
         _lib.ptr_array([int(q) for q in wire_ptrs]), len(wire_ptrs),
-        _stream()), 'kfac_wire_unpack_sum')
+        _stream()), 'kfac_wire_unpack_sum_as')
 
 
 def wire_unpack(arrays, tri, wire, select=None, scale=1.0, ema_r=-1.0):
-    lib = _lib.load()
-    n, ptrs, nelems, tri_dim, sel = _wire_args(arrays, tri, select)
-    _lib.check(lib.kfac_wire_unpack(n, ptrs, nelems, tri_dim, sel, scale,
-                                    ema_r, _p(wire), _stream()),
-               'kfac_wire_unpack')
+    wire_unpack_sum(arrays, tri, [wire.data_ptr()], select, scale, ema_r,
+                    wire_dtype=wire.dtype)

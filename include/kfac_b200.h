@@ -49,6 +49,14 @@ int kfac_get_engine(void);
  * results of that launch are then invalid). */
 int kfac_tc_status(int* status_out);
 
+/* Self-test of that mechanism (failure detection without a fault): launches
+ * one warp that waits, with a limit of about a thousand polls, on a barrier
+ * nothing arrives at.  On return *status_out is the status word the wait
+ * raised (1) and *returned_out is 2 when the wait reported its expiry to the
+ * kernel, which then returned normally.  Uses its own status word: the one
+ * behind kfac_tc_status is not touched.  Synchronises the device. */
+int kfac_selftest_wait_expiry(int* status_out, int* returned_out);
+
 /* ------------------------------------------------------------------ factors
  * out(d x d) = alpha * X^T X + beta * out, X a (rows x d) matrix that is never
  * materialised.  Only one triangle of tiles is computed; both triangles of
@@ -324,6 +332,15 @@ int kfac_bn_precondition_group(
 int kfac_momentum_update(int64_t count, const float* grad, float* param,
                          float* v, float lr, float momentum, void* stream);
 
+/* w *= target_norm / (|w|_2 + eps) when that factor is below 1 (`count`
+ * floats), without a host synchronisation: the post-update weight rescaling
+ * NormalizeWeightUR._normalize_weight of the reference's ImageNet recipe
+ * (examples/imagenet/train.py:56-115) with skip_scale_comp off.  `scratch`:
+ * two device floats; on return scratch[0] = |w|^2 before scaling,
+ * scratch[1] = the factor. */
+int kfac_normalize_weight(int64_t count, float* w, float target_norm,
+                          float eps, float* scratch, void* stream);
+
 /* ------------------------------------------------------- wire pack / unpack
  * Wire format of the reference's collectives: the arrays concatenated in the
  * given order, a square factor (tri_dim[i] > 0) as its packed row-major lower
@@ -363,6 +380,27 @@ int kfac_wire_unpack_sum(int n_arrays, float* const* arrays,
                          const int64_t* nelems, const int* tri_dim,
                          const int* select, float scale, float ema_r,
                          const float* const* wires, int n_wires, void* stream);
+
+/* The same two calls with a reduced-precision wire buffer, halving the bytes
+ * that cross NVLink: values are rounded to `wire_dtype` when packed and
+ * widened to fp32 when unpacked (sums over wire buffers are formed in fp32).
+ * The arrays stay fp32.  The reference's pack / unpack kernels carry the same
+ * casts (communicators/pure_nccl_communicator.py:354-375,438-461) but its
+ * communicator fixes the wire type to fp32 (:32-33); here the type is the
+ * caller's choice, fp32 by default.  A 16-bit wire cannot hold a factor to
+ * the 1e-4 bound (bf16: 4e-3, fp16: 5e-4 relative per element). */
+#define KFAC_WIRE_F32 0
+#define KFAC_WIRE_F16 1
+#define KFAC_WIRE_BF16 2
+int kfac_wire_pack_as(int wire_dtype, int n_arrays, const float* const* arrays,
+                      const int64_t* nelems, const int* tri_dim,
+                      const int* select, int zero_skipped, void* wire,
+                      void* stream);
+int kfac_wire_unpack_sum_as(int wire_dtype, int n_arrays, float* const* arrays,
+                            const int64_t* nelems, const int* tri_dim,
+                            const int* select, float scale, float ema_r,
+                            const void* const* wires, int n_wires,
+                            void* stream);
 
 #ifdef __cplusplus
 }

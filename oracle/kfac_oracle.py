@@ -350,3 +350,49 @@ def all_gather_v_sim(per_rank_arrays):
 def split_indices(n_blocks, size):
     """Ownership of ``kfac.py:344-348``: contiguous ``np.array_split``."""
     return [idx.tolist() for idx in np.array_split(np.arange(n_blocks), size)]
+
+
+# --------------------------------------------------------------------------
+# Training-recipe pieces of the ImageNet example.
+# --------------------------------------------------------------------------
+
+def lr_polynomial_decay(epoch, ref_lr, epoch_start, epoch_end, p=2):
+    """``LrPolynomialDecay.lr`` (``examples/imagenet/train.py:37-45``)."""
+    if epoch < epoch_start:
+        rate = 1.0
+    elif epoch < epoch_end:
+        rate = (1.0 - (epoch - epoch_start) / (epoch_end - epoch_start)) ** p
+    else:
+        rate = 0.0
+    return ref_lr * rate
+
+
+def normalize_weight(w, eps=1e-9):
+    """``NormalizeWeightUR`` with ``skip_scale_comp`` off
+    (``examples/imagenet/train.py:68-115``): scale down to the norm
+    sqrt(2 * w.shape[0]) if larger.  Returns the new array."""
+    target = np.sqrt(2.0 * w.shape[0])
+    scale = target / (np.linalg.norm(w) + eps)
+    return w * np.float32(scale) if scale < 1 else w.copy()
+
+
+def soft_target_cross_entropy(x, t, tt=None, ignore_label=-1):
+    """Loss and gradient of ``examples/imagenet/softmax_cross_entropy.py``
+    (forward ``:76-118`` with normalize=True, reduce='mean'; backward
+    ``:235-291``): the loss uses the hard labels, the gradient the soft
+    targets when given."""
+    x64 = x.astype(np.float64)
+    m = x64.max(axis=1, keepdims=True)
+    log_y = x64 - m - np.log(np.exp(x64 - m).sum(axis=1, keepdims=True))
+    valid = t != ignore_label
+    count = max(int(valid.sum()), 1)
+    picked = log_y[np.arange(len(t)), np.maximum(t, 0)]
+    loss = -(picked * valid).sum() / count
+    y = np.exp(log_y)
+    if tt is not None:
+        gx = (y - tt) / count
+    else:
+        onehot = np.zeros_like(y)
+        onehot[np.arange(len(t)), np.maximum(t, 0)] = 1.0
+        gx = (y - onehot) * valid[:, None] / count
+    return loss, gx

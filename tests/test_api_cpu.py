@@ -77,6 +77,36 @@ def test_adjust_momentum_rule():
     assert KFACUpdateRule(hp).effective_momentum() == 0.9
 
 
+def test_recipe_schedule_and_soft_target_loss():
+    """LrPolynomialDecay and the soft-target cross entropy of the ImageNet
+    recipe against their restatements (host-side glue: runs on the CPU)."""
+    from chainerkfac_b200 import recipe
+    sched = recipe.LrPolynomialDecay(0.8, 2, 10, p=2)
+    for e in (0.0, 1.99, 2.0, 5.5, 9.99, 10.0, 12.0):
+        assert sched.lr(e) == pytest.approx(
+            orc.lr_polynomial_decay(e, 0.8, 2, 10, 2))
+
+    class Opt(object):
+        lr, lr_pre = 0.8, 0.8
+    opt = Opt()
+    sched(opt, 6.0)
+    assert opt.lr_pre == 0.8 and opt.lr == pytest.approx(0.8 * 0.25)
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((7, 5)).astype(np.float32)
+    t = np.array([0, 4, -1, 2, 2, 1, 3])
+    tt = rng.random((7, 5)).astype(np.float32)
+    tt /= tt.sum(axis=1, keepdims=True)
+    for soft in (None, tt):
+        xt = torch.from_numpy(x).requires_grad_(True)
+        loss = recipe.softmax_cross_entropy(
+            xt, torch.from_numpy(t), None if soft is None
+            else torch.from_numpy(soft))
+        loss.backward()
+        want_loss, want_gx = orc.soft_target_cross_entropy(x, t, soft)
+        assert float(loss) == pytest.approx(want_loss, rel=1e-5)
+        assert np.allclose(xt.grad.numpy(), want_gx, rtol=1e-4, atol=1e-6)
+
+
 class NumpyWire(object):
     """Pack/unpack of the wire format with the oracle (CPU stand-in for the
     library kernels, injected by these tests only)."""

@@ -64,6 +64,16 @@ for rep in range(3):
         for (x, _), (y, _) in zip(a_nccl[o], a_peer[o]):
             assert torch.equal(x, y), (rep, o)
 
+# a bf16 wire: the exchanged arrays arrive rounded to bf16 (2^-9 relative)
+half = ck.create_communicator('peer_memory', wire_dtype='bfloat16')
+a_half = [[(t.clone(), tri) for t, tri in loc] for loc in a_nccl]
+a_full = [[(t.clone(), tri) for t, tri in loc] for loc in a_nccl]
+half.reduce_scatter_v_arrays(a_half)
+comms['peer_memory'].reduce_scatter_v_arrays(a_full)
+for (x, _), (y, _) in zip(a_full[rank], a_half[rank]):
+    err = float((x - y).norm() / x.norm())
+    assert 0 < err < 4e-3, err
+
 for pic, early, own, cname, decay, acc in (
         (True, False, 'reference', 'pure_nccl', 1.0, 1),
         (False, False, 'reference', 'pure_nccl', 1.0, 1),

@@ -215,6 +215,22 @@ def test_bn_factor_golden(ops, golden, name):
     assert rel(F, g['F']) < FACTOR_TOL
 
 
+def test_bounded_wait_expires_and_reports(ops):
+    """A barrier wait that can never be satisfied gives up after its poll
+    limit, raises its status word and lets the kernel return (the mechanism
+    every tile kernel's waits use); the context stays usable."""
+    import ctypes
+    from chainerkfac_b200 import _lib
+    lib = _lib.load()
+    status, returned = ctypes.c_int(-1), ctypes.c_int(-1)
+    _lib.check(lib.kfac_selftest_wait_expiry(ctypes.byref(status),
+                                             ctypes.byref(returned)),
+               'kfac_selftest_wait_expiry')
+    assert status.value == 1 and returned.value == 2
+    x = torch.ones(4, 3, device='cuda')
+    assert float(ops.factor_dense(x, False, alpha=1.0).sum()) == 36.0
+
+
 # ------------------------------------------------------------------ inverse
 def spd(rng, d, m=None):
     m = m or max(2 * d, 64)
@@ -506,6 +522,43 @@ def test_wire_pack_unpack_bit_exact(ops):
     ops.wire_unpack(prev, tri, wire, scale=1.0, ema_r=0.5)
     for a, o in zip(arrs, prev):
         assert rel(host(o), 0.5 * a + 0.5) < 1e-6
+
+
+@pytest.mark.parametrize('wdt', [torch.float16, torch.bfloat16])
+def test_wire_reduced_precision(ops, wdt):
+    """A 16-bit wire buffer holds each value rounded to the wire type (the
+    cast of pure_nccl_communicator.py:354-375); the sum over several wire
+    buffers is formed in fp32 from the widened values (:438-461)."""
+    rng = np.random.default_rng(15)
+    shapes = [((70, 70), True), ((1000,), False), ((129, 129), True)]
+    arrs = []
+    for shp, tri in shapes:
+        a = rng.standard_normal(shp).astype(np.float32)
+        arrs.append((a + a.T).astype(np.float32) if tri else a)
+    tri = [t for _, t in shapes]
+    nested = [[(a, t) for a, t in zip(arrs, tri)]]
+    n = orc.wire_nelems(nested)
+    ranks = 3
+    wires, want = [], np.zeros(n, np.float32)
+    for r in range(ranks):
+        scaled = [dev(a * np.float32(r + 1)) for a in arrs]
+        w = torch.zeros(n, dtype=wdt, device='cuda')
+        ops.wire_pack(scaled, tri, w)
+        exp = torch.from_numpy(orc.pack_arrays(
+            [[(a * np.float32(r + 1), t) for a, t in zip(arrs, tri)]])).to(wdt)
+        assert torch.equal(w.cpu(), exp)          # rounded to nearest
+        want += exp.float().numpy()
+        wires.append(w)
+    outs = [torch.zeros_like(dev(a)) for a in arrs]
+    ops.wire_unpack_sum(outs, tri, [w.data_ptr() for w in wires],
+                        scale=1.0 / ranks, wire_dtype=wdt)
+    ref = [np.zeros_like(a) for a in arrs]
+    orc.unpack_arrays([[(a, t) for a, t in zip(ref, tri)]], want,
+                      divisor=float(ranks))
+    for o, a in zip(outs, ref):
+        assert rel(host(o), a) < 1e-6
+        if a.ndim == 2:
+            assert np.array_equal(host(o), host(o).T)
 
 
 def test_wire_unpack_sum_of_rank_buffers(ops):

@@ -273,6 +273,48 @@ def test_loss_scale_gives_the_unscaled_trajectory(fuse):
         assert rel(b, a) < KFGRAD_TOL
 
 
+def test_normalize_weight_hook_matches_restatement():
+    """NormalizeWeightUR as a post-update hook (train.py:56-115): weights
+    whose norm exceeds sqrt(2 * out) are scaled down to it on the device,
+    others are left alone; the skip_scale_comp schedule gives the same
+    weights while it recomputes the norm every step (warm-up)."""
+    import chainerkfac_b200 as ck
+    from chainerkfac_b200 import recipe
+    torch.manual_seed(4)
+    model = MLP((12, 9, 9, 5)).cuda()
+    with torch.no_grad():
+        model.l1.weight.mul_(20.0)          # far above its target norm
+    opt = ck.KFAC(lr=0.05, momentum=0.0, cov_ema_decay=1.0, damping=1e-2)
+    opt.setup(model)
+    opt.fuse_update = False                 # hooks run in the plain rule
+    hooked = [opt.target.l1.W, opt.target.l2.W]
+    for p in hooked:
+        p.update_rule.add_hook(recipe.NormalizeWeightUR(), timing='post')
+    x = torch.rand(16, 12, device='cuda')
+    t = torch.randint(0, 5, (16,), device='cuda')
+    ref = MLP((12, 9, 9, 5)).cuda()
+    ref.load_state_dict(model.state_dict())
+    o2 = ck.KFAC(lr=0.05, momentum=0.0, cov_ema_decay=1.0, damping=1e-2)
+    o2.setup(ref)
+    o2.fuse_update = False
+    opt.update(lambda a, b: F.cross_entropy(model(a), b), x, t)
+    o2.update(lambda a, b: F.cross_entropy(ref(a), b), x, t)
+    for name in ('l1', 'l2'):
+        got = host(getattr(model, name).weight)
+        want = orc.normalize_weight(host(getattr(ref, name).weight))
+        assert rel(got, want) < 1e-6
+    n1 = float(np.linalg.norm(host(model.l1.weight)))
+    assert abs(n1 - np.sqrt(2.0 * 9)) < 1e-4      # clipped
+    assert rel(host(model.l3.weight), host(ref.l3.weight)) < 1e-7
+    # the interval schedule, during its warm-up, computes the same scale
+    w = torch.randn(9, 30, device='cuda') * 3
+    p = type('P', (), {})()
+    p.data = w.clone()
+    rule = type('R', (), {'t': 0})()
+    recipe.NormalizeWeightUR(skip_scale_comp=True)(rule, p)
+    assert rel(host(p.data), orc.normalize_weight(host(w))) < 1e-6
+
+
 def test_bench_resnet50_step_runs():
     from bench_model import build_training_step
     step, h2d, d2h = build_training_step(
