@@ -34,7 +34,6 @@ constexpr int TC_BK = 32;
 // pixel rows of ResNet-50, where the per-thread offset bookkeeping that more
 // threads replicate costs as much as the extra warps hide; strided operands
 // need the 96 registers that only the 16-warp CTA leaves per thread.
-constexpr int TC_PW_IM2COL = 16;
 constexpr int TC_PW_STRIDED = 16;
 constexpr int TC_A_BYTES = TC_BM * TC_BK * 4;   // 16 KB
 constexpr int TC_B_BYTES = TC_BN * TC_BK * 4;   // 32 KB
@@ -1382,12 +1381,6 @@ int tc_prepare() {
     KFAC_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<false, true, TC_PW_STRIDED>,
                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    TC_SMEM_BYTES));
-    KFAC_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<true, false, TC_PW_IM2COL>,
-                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   TC_SMEM_BYTES));
-    KFAC_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<true, true, TC_PW_IM2COL>,
-                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   TC_SMEM_BYTES));
     KFAC_CUDA(cudaFuncSetAttribute(tc_pair_kernel<false, false>,
                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    PK_SMEM_BYTES));
@@ -1438,24 +1431,8 @@ struct TcFactorSplit {
   long long k_per_split;
 };
 
-// Factor builds run on the 256 x 256 kernel unless KFAC_TC_PAIR=0 is set in
-// the environment (kept for comparison runs).
-static bool tc_use_pair() {
-  static const bool on = [] {
-    const char* e = getenv("KFAC_TC_PAIR");
-    return !(e && e[0] == '0');
-  }();
-  return on;
-}
-
 // CTAs that cover the lower tiles of a d x d output once.
 static int tc_factor_ctas(int d) {
-  if (!tc_use_pair()) {
-    GemmDesc g = {};
-    g.M = g.N = d;
-    g.flags = G_LOWER;
-    return tc_tiles(g);
-  }
   const int nblk = (d + PK_ROWS - 1) / PK_ROWS;
   return nblk * (nblk + 1) / 2;
 }
@@ -1701,12 +1678,10 @@ int run_factor_group_tc(int count, const FactorJob* jobs, void* workspace,
       long long kb = (b.splits > 1 ? b.k_per_split : b.K) * tc_block_cost(b.M);
       return ka > kb;
     });
-    const bool pair = tc_use_pair();
     int total = 0;
     for (GemmDesc& g : v) {
       g.tile_begin = total;
-      total += (pair ? tc_factor_ctas(g.M) : g.ntiles) *
-               (g.splits > 1 ? g.splits : 1);
+      total += tc_factor_ctas(g.M) * (g.splits > 1 ? g.splits : 1);
     }
     bool tails = false;
     for (const GemmDesc& g : v) tails = tails || tc_desc_has_tails(g);
@@ -1723,35 +1698,19 @@ int run_factor_group_tc(int count, const FactorJob* jobs, void* workspace,
       dev_descs = static_cast<const GemmDesc*>(dev);
     }
     const int nd = (int)v.size();
-    if (pair) {
-      if (m == 1 && tails)
-        tc_pair_kernel<true, true><<<total, PK_THREADS, PK_SMEM_BYTES, stream>>>(
-            dev_descs, nd, inl);
-      else if (m == 1)
-        tc_pair_kernel<true, false><<<total, PK_THREADS, PK_SMEM_BYTES, stream>>>(
-            dev_descs, nd, inl);
-      else if (tails)
-        tc_pair_kernel<false, true><<<total, PK_THREADS, PK_SMEM_BYTES, stream>>>(
-            dev_descs, nd, inl);
-      else
-        tc_pair_kernel<false, false><<<total, PK_THREADS, PK_SMEM_BYTES, stream>>>(
-            dev_descs, nd, inl);
-      KFAC_LAUNCH_CHECK("tc_pair_kernel");
-      continue;
-    }
     if (m == 1 && tails)
-      tc_gemm_kernel<true, true, TC_PW_IM2COL><<<total, TcMap<TC_PW_IM2COL>::kThreads, TC_SMEM_BYTES, stream>>>(
-          dev_descs, nd, inl, 0.f, 0.f);
+      tc_pair_kernel<true, true><<<total, PK_THREADS, PK_SMEM_BYTES, stream>>>(
+          dev_descs, nd, inl);
     else if (m == 1)
-      tc_gemm_kernel<true, false, TC_PW_IM2COL><<<total, TcMap<TC_PW_IM2COL>::kThreads, TC_SMEM_BYTES, stream>>>(
-          dev_descs, nd, inl, 0.f, 0.f);
+      tc_pair_kernel<true, false><<<total, PK_THREADS, PK_SMEM_BYTES, stream>>>(
+          dev_descs, nd, inl);
     else if (tails)
-      tc_gemm_kernel<false, true, TC_PW_STRIDED><<<total, TcMap<TC_PW_STRIDED>::kThreads, TC_SMEM_BYTES, stream>>>(
-          dev_descs, nd, inl, 0.f, 0.f);
+      tc_pair_kernel<false, true><<<total, PK_THREADS, PK_SMEM_BYTES, stream>>>(
+          dev_descs, nd, inl);
     else
-      tc_gemm_kernel<false, false, TC_PW_STRIDED><<<total, TcMap<TC_PW_STRIDED>::kThreads, TC_SMEM_BYTES,
-                                     stream>>>(dev_descs, nd, inl, 0.f, 0.f);
-    KFAC_LAUNCH_CHECK("tc_gemm_kernel");
+      tc_pair_kernel<false, false><<<total, PK_THREADS, PK_SMEM_BYTES, stream>>>(
+          dev_descs, nd, inl);
+    KFAC_LAUNCH_CHECK("tc_pair_kernel");
   }
   stream = main_stream;
   if (side != nullptr) {

@@ -36,12 +36,15 @@ const char* kfac_last_error(void);
 int64_t kfac_launch_count(void);
 
 /* Arithmetic engine of the factor / inverse / precondition products.
- * 1 (default): tcgen05 tensor cores with fp32 operands split into two terms,
- * three MMAs per product, fp32 accumulation: two bf16 terms (16 significant
- * bits) for the factor builds, two TF32 terms (22 bits) for the inverse and
- * precondition products.  Relative Frobenius error of a factor stays below
- * 1e-5 (bound of the reference comparison: 1e-4).  0: fp32 FFMA tiles.  The
- * choice is read when a call is made or a plan is created. */
+ * 1 (default, the product): tcgen05 tensor cores with fp32 operands split into
+ * two terms, three MMAs per product, fp32 accumulation: two bf16 terms (16
+ * significant bits) for the factor builds, two TF32 terms (22 bits) for the
+ * inverse and precondition products.  Relative Frobenius error of a factor
+ * stays below 1e-5 (bound of the reference comparison: 1e-4).
+ * 0: fp32 FFMA tiles on the CUDA cores.  Not a supported product path: it is
+ * the accuracy yardstick the parity tests run beside the tensor-core engine
+ * (several times slower, no look-ahead, NCHW inputs only) and may go away.
+ * The choice is read when a call is made or a plan is created. */
 int kfac_set_engine(int engine);
 int kfac_get_engine(void);
 /* Synchronises the device and returns in *status_out the tensor-core engine's

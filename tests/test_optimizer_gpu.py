@@ -287,8 +287,8 @@ def test_normalize_weight_hook_matches_restatement():
     opt = ck.KFAC(lr=0.05, momentum=0.0, cov_ema_decay=1.0, damping=1e-2)
     opt.setup(model)
     opt.fuse_update = False                 # hooks run in the plain rule
-    hooked = [opt.target.l1.W, opt.target.l2.W]
-    for p in hooked:
+    links = dict(opt.target.namedlinks())
+    for p in (links['/l1'].W, links['/l2'].W):
         p.update_rule.add_hook(recipe.NormalizeWeightUR(), timing='post')
     x = torch.rand(16, 12, device='cuda')
     t = torch.randint(0, 5, (16,), device='cuda')
