@@ -1457,11 +1457,31 @@ static long long tc_block_cost(int d) {
 // prologue and epilogue stay amortised, and a contraction is only cut when
 // that brings its CTAs closer to the target than leaving it whole (partial
 // tiles cost a write, a read and the reduce kernel).
+// The tensor core adds each MMA's products into the fp32 accumulator with
+// truncation, so a sum of N MMAs drifts by up to about N * 2^-25 of its
+// magnitude, all in one direction when the addends share a sign (activation
+// factors: products of non-negative values; three MMAs per 16 rows here).
+// Measured relative error of 100 352-row factors: 2e-4 when one CTA
+// accumulates 1500 k-blocks, 4.7e-5 at 256, 2e-5 at 128.  A CTA therefore
+// never accumulates more than this many k-blocks (of 32 rows); the partial
+// tiles of longer contractions are summed in fp32 by the reduce kernel, with
+// rounding to nearest.  256 keeps the drift at half the 1e-4 bound and costs
+// nothing measurable; 128 costs 15 % of the factor stage.
+static long long tc_max_kblocks() {
+  static const long long v = [] {
+    const char* e = getenv("KFAC_TC_MAX_KBLOCKS");
+    const long long k = e ? atoll(e) : 256;
+    return k >= 16 ? k : 256;
+  }();
+  return v;
+}
+
 static TcFactorSplit tc_split_for(long long rows, int d, long long chunk) {
   TcFactorSplit s;
   s.tiles = tc_lower_tiles(d);
   chunk /= tc_block_cost(d);
   if (chunk < 16) chunk = 16;
+  if (chunk > tc_max_kblocks()) chunk = tc_max_kblocks();
   const long long kblocks = (rows + TC_BK - 1) / TC_BK;
   long long sp = (kblocks + chunk / 2) / chunk;
   if (sp < 1) sp = 1;

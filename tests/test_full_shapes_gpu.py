@@ -178,3 +178,40 @@ def test_batch_normalization_block_at_resnet50_sizes(c, h):
     assert rel_np(kb.cpu().numpy(), wb) < 1e-3
     assert flag.tolist() == [0, 0]
     plan.close()
+
+
+def test_grouped_build_of_all_resnet50_factors():
+    """All 108 factors of ResNet-50 at batch 32 in ONE grouped call, as the
+    optimizer and the benchmark issue them.  A grouped call gives each CTA a
+    longer stretch of the contraction than a call for one layer does, and the
+    tensor core's truncating accumulation drifts with that length, so the
+    single-layer cases above do not cover it."""
+    import bench
+    dev = torch.device('cuda', 0)
+    wl = bench.DeviceWorkload(dev, 1234, bench.WORKLOADS['resnet50'],
+                              bn_blocks=False)
+    outs = [torch.empty_like(e) for e in wl.ema]
+    wl.build(list(range(len(wl.layers))), outs, 1.0, 0.0)
+    torch.cuda.synchronize()
+    worst = 0.0
+    for i, l in enumerate(wl.layers):
+        if l['name'] not in ('conv1', 'res1.0.conv2', 'res1.1.conv1',
+                             'res2.2.conv3', 'res3.5.conv1', 'res4.1.conv2',
+                             'fc'):
+            continue
+        if l['kind'] == 'conv':
+            A64 = factor_A_fp64(wl.x[i], l['k'], l['stride'], l['pad'],
+                                l['bias'])
+            G64 = factor_G_fp64(wl.gy[i])
+        else:
+            x = wl.x[i].double()
+            x = torch.cat([x, torch.ones_like(x[:, :1])], 1)
+            A64 = x.T @ x / l['n']
+            g = wl.gy[i].double()
+            G64 = g.T @ g * l['n']
+        eA = rel(outs[wl.fidx[i][0]], A64)
+        eG = rel(outs[wl.fidx[i][1]], G64)
+        assert eA < FACTOR_TOL and eG < FACTOR_TOL, (l['name'], eA, eG)
+        worst = max(worst, eA, eG)
+    assert worst < 7e-5, worst      # drift stays well inside the bound
+    wl.plan.close()
