@@ -79,12 +79,21 @@ TRAFFIC_CASES = {
 }
 
 
-def algorithmic_flops(layers, prebuilt=False):
+def algorithmic_flops(layers, prebuilt=False, lowrank=None):
     """Flops per step per GPU: one triangle of each factor, d^3 per inverse,
     two products per preconditioned gradient (one matrix-vector product for a
-    BatchNormalization block)."""
+    BatchNormalization block).  `lowrank` maps the index of a
+    BatchNormalization block held in low-rank form to its history rows m:
+    the triangle of the m x m matrix Hs Hs^T over 2c columns, m^3 for its
+    inverse, two m x 2c matrix-vector products to apply it."""
     factor = inverse = precond = 0.0
-    for l in layers:
+    for i, l in enumerate(layers):
+        if lowrank and i in lowrank:
+            m, d = lowrank[i], 2 * l['c']
+            factor += float(d) * m * (m + 1)
+            inverse += float(m) ** 3
+            precond += 4.0 * m * d + 2.0 * m * m
+            continue
         for d, rows in bw.block_factors(l):
             if not prebuilt:
                 factor += float(rows) * d * (d + 1)
@@ -97,12 +106,23 @@ def algorithmic_flops(layers, prebuilt=False):
     return dict(factor=factor, inverse=inverse, precondition=precond)
 
 
-def algorithmic_bytes(layers, prebuilt=False):
+def algorithmic_bytes(layers, prebuilt=False, lowrank=None):
     """Minimum DRAM bytes per step per GPU: each un-expanded input once and
     each factor written once (plus read for the running average); factor read
-    + inverse written; inverses, gradient, result."""
+    + inverse written; inverses, gradient, result.  A low-rank
+    BatchNormalization block (`lowrank`: index -> history rows m) reads its
+    input, writes n new history rows, writes and reads the scaled history and
+    writes the m x m matrix; its inverse reads and writes m x m; applying it
+    reads the inverse and the scaled history twice."""
     factor = inverse = precond = 0.0
-    for l in layers:
+    for i, l in enumerate(layers):
+        if lowrank and i in lowrank:
+            m, d = lowrank[i], 2 * l['c']
+            factor += 4.0 * (2 * l['n'] * l['c'] * l['h'] ** 2 + l['n'] * d +
+                             3 * m * d + m * m)
+            inverse += 4.0 * 2 * m * m
+            precond += 4.0 * (m * m + 2 * m * d + 4 * l['c'])
+            continue
         sides = [d for d, _ in bw.block_factors(l)]
         sq = sum(d * d for d in sides)
         if not prebuilt:
@@ -238,10 +258,14 @@ class DeviceWorkload(object):
     factor F of side 2c; parameters gamma, beta).  Factors live in flat lists
     (`ema`, `inv`, ...); `fidx[i]` lists the factor indices of block i."""
 
-    def __init__(self, device, seed, spec, bn_blocks=True):
+    def __init__(self, device, seed, spec, bn_blocks=True, bn_lowrank=True,
+                 world=1, rank=0):
         import torch
         from chainerkfac_b200 import ops
+        from chainerkfac_b200.optimizers.fisher_blocks.normalizations \
+            .batch_normalization import lowrank_window
         self.torch, self.ops, self.spec = torch, ops, spec
+        self.world, self.rank = world, rank
         self.layers = spec['layers']()
         self.decay, self.damping = spec['decay'], spec['damping']
         self.acc = spec['acc']
@@ -257,12 +281,23 @@ class DeviceWorkload(object):
         self.P, self.gP, self.vP = [], [], []
         self.ema, self.inv, self.fidx = [], [], []
         self.bn_grads, self.bn_kf = [None] * nl, [None] * nl
+        # low-rank form of a BatchNormalization block (kfac_bn_lowrank_*):
+        # when the per-sample gradients of the steps the running average
+        # still remembers number fewer than half the factor's side
+        self.lr_slots = lowrank_window(self.decay) if (
+            bn_lowrank and self.acc == 1) else 0
+        self.lowrank = [False] * nl
+        self.lr = {}
         for i, l in enumerate(self.layers):
             n = l['n']
             if l['kind'] == 'bn':
                 xs = gs = (n, l['c'], l['h'], l['h'])
                 shapes = [(l['c'],), (l['c'],)]
                 sides = [2 * l['c']]
+                m = self.lr_slots * n * world
+                if self.lr_slots and m <= l['c']:
+                    self.lowrank[i] = True
+                    sides = []
             elif l['kind'] == 'conv':
                 xs = (n, l['cin'], l['hin'], l['hin'])
                 gs = (n, l['cout'], l['hout'], l['hout'])
@@ -299,8 +334,18 @@ class DeviceWorkload(object):
                 self.ema.append(torch.zeros((d, d), device=device))
                 self.inv.append(torch.empty((d, d), device=device))
             if l['kind'] == 'bn':
-                self.bn_grads[i] = torch.empty((n, 2 * l['c']), device=device)
                 self.bn_kf[i] = [torch.empty_like(t) for t in P]
+                if self.lowrank[i]:
+                    m, d = self.lr_slots * n * world, 2 * l['c']
+                    self.lr[i] = dict(
+                        hist=torch.zeros((m, d), device=device),
+                        Hs=torch.empty((m, d), device=device),
+                        M=torch.empty((m, m), device=device),
+                        Minv=torch.empty((m, m), device=device),
+                        w=[0.0] * self.lr_slots, pos=-1, rows=n * world)
+                else:
+                    self.bn_grads[i] = torch.empty((n, 2 * l['c']),
+                                                   device=device)
         self.bn_flags = torch.zeros((nl, 2), dtype=torch.int32, device=device)
         if self.prebuilt:
             # factors X^T X / m + 1e-3 I from X ~ N(0,1) with m rows, built
@@ -318,6 +363,7 @@ class DeviceWorkload(object):
                            for t in gp] for gp in self.gP]
             self.micro = 0
         self.make_plan(list(range(nl)))
+        self.make_lr_plan(list(range(nl)))
         self.first = True
         self.input_bytes = sum(t.numel() * 4 for t in self.x + self.gy
                                if t is not None)
@@ -349,6 +395,56 @@ class DeviceWorkload(object):
         self.class_layers = [sorted({owner_of[q] for q in idx})
                              for idx in self.plan.classes()]
 
+    def make_lr_plan(self, own):
+        """Inverse plan of the m x m matrices I + Hs Hs^T of the owned
+        low-rank BatchNormalization blocks (damping 1 adds the identity)."""
+        self.lr_layers = [i for i in own if self.lowrank[i]]
+        self.lr_plan = None
+        if self.lr_layers:
+            k = len(self.lr_layers)
+            self.lr_plan = self.ops.InversePlanSet(
+                [self.lr[i]['M'] for i in self.lr_layers],
+                [self.lr[i]['Minv'] for i in self.lr_layers],
+                [-1] * k, [2] * k, scale=[1.0] * k)
+
+    def lr_slot(self, i):
+        """View of block i's current history slot (rows of all ranks)."""
+        st = self.lr[i]
+        return st['hist'][st['pos'] * st['rows']:(st['pos'] + 1) * st['rows']]
+
+    def lr_advance(self, i, r, rest):
+        """Start a step for low-rank block i: older slots fade by `rest`, the
+        next slot of the ring takes weight r."""
+        st = self.lr[i]
+        st['pos'] = (st['pos'] + 1) % self.lr_slots
+        st['w'] = [w * rest for w in st['w']]
+        st['w'][st['pos']] = r
+
+    def lr_item(self, i, grads=None):
+        st, l = self.lr[i], self.layers[i]
+        # F = sum_s w_s * (sum over ranks of U^T U) / (n * world); after the
+        # mean-reduce of the exchange a slot holds every rank's rows / world
+        fac = float(self.world) / l['n']
+        g = grads if grads is not None else self.grads()
+        d = max(self.damping, 0.0) * STAB_COEFF
+        return self.ops.bn_lowrank_item(
+            st['hist'], st['Hs'], l['c'], st['rows'],
+            [w * fac for w in st['w']], d, d, st['Minv'], g[i][0], g[i][1],
+            self.bn_kf[i][0], self.bn_kf[i][1], self.bn_flags[i],
+            self.P[i][0], self.P[i][1], self.vP[i][0], self.vP[i][1])
+
+    def lr_build(self, layers):
+        """Hs and Hs Hs^T of the low-rank blocks among `layers` (their
+        history slots must hold this step's rows)."""
+        lr = [i for i in layers if self.lowrank[i]]
+        if not lr:
+            return
+        self.ops.bn_lowrank_scale([self.lr_item(i) for i in lr])
+        self.ops.factor_group(
+            [self.ops.dense_t_item(self.lr[i]['Hs'], 1.0, 0.0,
+                                   self.lr[i]['M']) for i in lr],
+            self.ema[0].device)
+
     def layer_items(self, i, outs, r, rest):
         """Grouped-build items of block i's factors into `outs` (one tensor
         per factor).  BatchNormalization blocks need their per-sample
@@ -371,9 +467,19 @@ class DeviceWorkload(object):
     def bn_prepare(self, layers):
         """Per-sample gradients of the BatchNormalization blocks among
         `layers`, one grouped call."""
-        items = [self.ops.bn_item(self.x[i], self.gy[i], 2e-5,
-                                  float(self.layers[i]['n']), self.bn_grads[i])
-                 for i in layers if self.is_bn(i)]
+        items = []
+        for i in layers:
+            if not self.is_bn(i):
+                continue
+            n = self.layers[i]['n']
+            out = self.bn_grads[i]
+            if self.lowrank[i]:
+                slot = self.lr_slot(i)
+                if self.world > 1:
+                    slot.zero_()         # the other ranks' rows arrive by sum
+                out = slot[self.rank * n:(self.rank + 1) * n]
+            items.append(self.ops.bn_item(self.x[i], self.gy[i], 2e-5,
+                                          float(n), out))
         self.ops.bn_sample_grads_group(items)
 
     def build(self, layers, outs, r, rest):
@@ -381,12 +487,19 @@ class DeviceWorkload(object):
         (plus the grouped per-sample gradients of BatchNormalization)."""
         if not layers:
             return
+        for i in layers:
+            if self.lowrank[i]:
+                self.lr_advance(i, r, rest)
         self.bn_prepare(layers)
         items = []
         for i in layers:
-            items += self.layer_items(i, [outs[k] for k in self.fidx[i]], r,
-                                      rest)
-        self.ops.factor_group(items, self.ema[0].device)
+            if not self.lowrank[i]:
+                items += self.layer_items(
+                    i, [outs[k] for k in self.fidx[i]], r, rest)
+        if items:
+            self.ops.factor_group(items, self.ema[0].device)
+        if self.world == 1:
+            self.lr_build(layers)       # else after the exchange
 
     # -- stages timed alone (nothing else on the device) --------------------
     def factors_alone(self):
@@ -395,6 +508,8 @@ class DeviceWorkload(object):
                    1.0 - self.decay)
 
     def inverses_alone(self):
+        if self.lr_plan is not None:
+            self.lr_plan.run(1.0, False)
         self.plan.run(self.damping, not self.prebuilt)
 
     def precondition_alone(self):
@@ -436,6 +551,12 @@ class DeviceWorkload(object):
         r, rest = self.ema_weights()
         classes = self.class_layers if OVERLAP else []
         done = set()
+        if OVERLAP and self.lr_plan is not None:
+            # the low-rank BatchNormalization blocks first: their small
+            # inverses run beside everything else
+            self.build(self.lr_layers, self.ema, r, rest)
+            self.lr_plan.start_class(0, 1.0, False)
+            done.update(self.lr_layers)
         for c, layers in enumerate(classes[:-1]):
             self.build(layers, self.ema, r, rest)
             self.plan.start_class(c, self.damping, True)
@@ -454,6 +575,10 @@ class DeviceWorkload(object):
         # the layers of a size class are preconditioned (and updated) on that
         # class's stream as soon as its inverses are done, next to the
         # remaining classes' inverses
+        if self.lr_plan is not None:
+            self.lr_plan.run(
+                1.0, False, after_class=(lambda c: self.precondition_layers(
+                    self.lr_layers)) if OVERLAP else None)
         self.plan.run(self.damping, not self.prebuilt,
                       after_class=self.precondition_class if OVERLAP else None)
 
@@ -464,7 +589,11 @@ class DeviceWorkload(object):
                             momentum=MOMENTUM, grads=None):
         g = grads if grads is not None else self.grads()
         conn = [i for i in layers if not self.is_bn(i)]
-        bn = [i for i in layers if self.is_bn(i)]
+        bn = [i for i in layers if self.is_bn(i) and not self.lowrank[i]]
+        low = [i for i in layers if self.lowrank[i]]
+        if low:
+            self.ops.bn_lowrank_apply([self.lr_item(i, g) for i in low], lr,
+                                      momentum)
         if conn:
             self.ops.precondition(
                 [self.inv[self.fidx[i][1]] for i in conn],
@@ -526,14 +655,19 @@ class DistributedWorkload(DeviceWorkload):
     as a class is reduced its owners start its inverses on a side stream, next
     to the factor build and exchange of the remaining classes."""
 
-    def __init__(self, device, seed, spec, comm, bn_blocks=True):
-        super(DistributedWorkload, self).__init__(device, seed, spec,
-                                                  bn_blocks)
+    def __init__(self, device, seed, spec, comm, bn_blocks=True,
+                 bn_lowrank=True):
+        super(DistributedWorkload, self).__init__(
+            device, seed, spec, bn_blocks, bn_lowrank, world=comm.size,
+            rank=comm.rank)
         import torch
         self.comm = comm
         from chainerkfac_b200.optimizers.kfac import balanced_split
         cnt = len(self.layers)
-        sides = [[self.ema[k].shape[0] for k in ks] for ks in self.fidx]
+        # a low-rank block costs its m x m inverse
+        sides = [[self.ema[k].shape[0] for k in ks] if ks else
+                 ([self.lr[i]['M'].shape[0]] if self.lowrank[i] else [1])
+                 for i, ks in enumerate(self.fidx)]
         if OWNERSHIP == 'balanced':
             self.indices = balanced_split(
                 [sum(float(d) ** 3 for d in sd) for sd in sides], comm.size)
@@ -547,29 +681,20 @@ class DistributedWorkload(DeviceWorkload):
         bounds = self.plan.bounds
         self.plan.close()
         self.make_plan(self.mine, bounds)
+        if self.lr_plan is not None:
+            self.lr_plan.close()
+        self.make_lr_plan(self.mine)
         # size classes over all layers, largest first, as the plan forms them
         key_of = [sum(max(sd) > b for b in bounds) for sd in sides]
         pipelined = OVERLAP and self.acc == 1 and not self.prebuilt
         keys = sorted(set(key_of), reverse=True) if pipelined else [None]
         src = None if self.prebuilt else (
             self.acc_cov if self.acc > 1 else self.cov)
-        gsrc = self.grads()
-        self.xclass_layers, self.class_rs, self.class_plan = [], [], []
+        self.xsrc = src
+        self.xclass_layers, self.class_plan = [], []
         for key in keys:
             layers = [i for i in range(cnt) if key is None or key_of[i] == key]
-            rs = []
-            for idx in self.indices:
-                loc = []
-                for i in idx:
-                    if i not in layers:
-                        continue
-                    # gradients (sorted parameter names), then the factors
-                    loc += [(t, False) for t in gsrc[i] if t is not None]
-                    if src is not None:
-                        loc += [(src[k], True) for k in self.fidx[i]]
-                rs.append(loc)
             self.xclass_layers.append(layers)
-            self.class_rs.append(rs)
             self.class_plan.append(
                 self.plan.class_keys.index(key)
                 if key in self.plan.class_keys else None)
@@ -578,8 +703,35 @@ class DistributedWorkload(DeviceWorkload):
         self.comm_stream = torch.cuda.Stream(priority=-1)
         if hasattr(comm, 'reserve'):
             from chainerkfac_b200.communicators import _utility
-            comm.reserve(max([_utility.get_nelems(rs) for rs in self.class_rs]
+            for st in self.lr.values():
+                st['pos'] = 0
+            comm.reserve(max([_utility.get_nelems(self.class_rs(c))
+                              for c in range(len(self.xclass_layers))]
                              + [_utility.get_nelems(self.ag_arrays)]), device)
+            for st in self.lr.values():
+                st['pos'] = -1
+
+    def class_rs(self, c):
+        """Arrays of exchange 1 for size class c, by owner: gradients (sorted
+        parameter names), then the factors -- or, for a low-rank
+        BatchNormalization block, the current history slot with this rank's
+        rows in place and zeros elsewhere, whose mean over ranks is the stack
+        of all ranks' rows divided by the number of ranks."""
+        layers = set(self.xclass_layers[c])
+        gsrc = self.grads()
+        rs = []
+        for idx in self.indices:
+            loc = []
+            for i in idx:
+                if i not in layers:
+                    continue
+                loc += [(t, False) for t in gsrc[i] if t is not None]
+                if self.lowrank[i]:
+                    loc.append((self.lr_slot(i), False))
+                elif self.xsrc is not None:
+                    loc += [(self.xsrc[k], True) for k in self.fidx[i]]
+            rs.append(loc)
+        return rs
 
     def own_factors(self, layers=None):
         mine = set(self.mine)
@@ -590,13 +742,13 @@ class DistributedWorkload(DeviceWorkload):
         torch = self.torch
         if self.prebuilt:
             # only the gradients travel to the owners
-            self.comm.reduce_scatter_v_arrays(self.class_rs[0])
+            self.comm.reduce_scatter_v_arrays(self.class_rs(0))
             return
         if self.acc > 1:
             self.accumulate()
             if self.micro == self.acc:
                 # one exchange per update: accumulated factors and gradients
-                self.comm.reduce_scatter_v_arrays(self.class_rs[0])
+                self.comm.reduce_scatter_v_arrays(self.class_rs(0))
                 r, rest = self.ema_weights()
                 own = self.own_factors()
                 emas = [self.ema[k] for k in own]
@@ -619,12 +771,19 @@ class DistributedWorkload(DeviceWorkload):
                 built.record(main)
                 side.wait_event(built)
             with torch.cuda.stream(side):
-                self.comm.reduce_scatter_v_arrays(self.class_rs[c])
+                self.comm.reduce_scatter_v_arrays(self.class_rs(c))
                 own = self.own_factors(layers)
                 if own:
                     emas = [self.ema[k] for k in own]
                     self.ops.axpby_group(r, [self.cov[k] for k in own], rest,
                                          emas, emas)
+                mine = set(self.mine)
+                low = [i for i in layers if self.lowrank[i] and i in mine]
+                if low:
+                    # every rank's rows have arrived in the owner's slot
+                    self.lr_build(low)
+                    if OVERLAP:
+                        self.lr_plan.start_class(0, 1.0, False)
                 if c < last and self.class_plan[c] is not None:
                     self.plan.start_class(self.class_plan[c], self.damping,
                                           True)
@@ -746,12 +905,15 @@ def run_ours(args):
         from chainerkfac_b200.communicators import create_communicator
         wl = DistributedWorkload(device, 1234 + rank, spec,
                                  create_communicator(COMMUNICATOR),
-                                 bn_blocks=not args.no_bn_blocks)
+                                 bn_blocks=not args.no_bn_blocks,
+                                 bn_lowrank=not args.bn_dense)
     else:
         wl = DeviceWorkload(device, 1234 + rank, spec,
-                            bn_blocks=not args.no_bn_blocks)
-    flops = algorithmic_flops(wl.layers, prebuilt)
-    abytes = algorithmic_bytes(wl.layers, prebuilt)
+                            bn_blocks=not args.no_bn_blocks,
+                            bn_lowrank=not args.bn_dense)
+    low = {i: wl.lr[i]['M'].shape[0] for i in wl.lr}
+    flops = algorithmic_flops(wl.layers, prebuilt, low)
+    abytes = algorithmic_bytes(wl.layers, prebuilt, low)
 
     def barrier():
         if world > 1:
@@ -895,9 +1057,7 @@ def run_ours(args):
             'dtype': 'f32', 'data': 'synthetic',
             'config': {'workload': spec['name'], 'batch_per_gpu': batch,
                        'layers': len(wl.layers),
-                       'bn_blocks': sum(1 for l in wl.layers
-                                        if l['kind'] == 'bn'),
-                       'cov_ema_decay': spec['decay'],
+X: spec['decay'],
                        'damping': spec['damping'], 'acc_iters': acc,
                        'l2_flush': ('inputs larger than L2 (%.2f GB of '
                                     'activations and gradients per step)'
@@ -1274,6 +1434,9 @@ def main():
                     help='leave the BatchNormalization layers to the plain '
                          'momentum rule (convolution / fully-connected '
                          'blocks only)')
+    ap.add_argument('--bn-dense', action='store_true',
+                    help='keep every BatchNormalization block as a dense '
+                         '2c x 2c factor (no low-rank form)')
     ap.add_argument('--no-overlap', action='store_true',
                     help='do not start the largest inverses during the '
                          'factor build')

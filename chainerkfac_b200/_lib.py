@@ -42,6 +42,17 @@ class BnItem(ctypes.Structure):
                 ('scale', ctypes.c_float)]
 
 
+class BnLowRankItem(ctypes.Structure):
+    """struct kfac_bn_lowrank_item of include/kfac_b200.h."""
+    _fields_ = [(nm, ctypes.c_void_p) for nm in (
+        'hist', 'scaled', 'm_inv', 'grad_gamma', 'grad_beta', 'kf_gamma',
+        'kf_beta', 'param_gamma', 'param_beta', 'mom_gamma', 'mom_beta',
+        'nan_flag')] + [
+        ('c', ctypes.c_int), ('rows_per_slot', ctypes.c_int),
+        ('slots', ctypes.c_int), ('damp_gamma', ctypes.c_float),
+        ('damp_beta', ctypes.c_float), ('slot_weight', ctypes.c_float * 32)]
+
+
 # name -> (restype, argtypes); mirrors include/kfac_b200.h one to one.
 SIGNATURES = {
     'kfac_abi_version': (I, []),
@@ -65,6 +76,9 @@ SIGNATURES = {
     'kfac_bn_sample_grads_group': (I, [I, ctypes.POINTER(BnItem), VP]),
     'kfac_bn_precondition_group': (I, [I, c_int_p] + [c_void_pp] * 10 +
                                    [F, F, VP]),
+    'kfac_bn_lowrank_scale': (I, [I, ctypes.POINTER(BnLowRankItem), VP]),
+    'kfac_bn_lowrank_apply': (I, [I, ctypes.POINTER(BnLowRankItem), F, F,
+                                  VP]),
     'kfac_axpby': (I, [I64, F, VP, F, VP, VP, VP]),
     'kfac_axpby_group': (I, [I, c_i64_p, F, c_void_pp, F, c_void_pp,
                              c_void_pp, VP]),

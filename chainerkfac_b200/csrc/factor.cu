@@ -404,6 +404,115 @@ bn_finish_group_kernel(const BnPrecondItem* __restrict__ items, float lr,
   }
 }
 
+// ---- low-rank form of the BatchNormalization blocks ------------------------
+// The factor of a BatchNormalization block is F = sum_s w_s U_s^T U_s over the
+// per-sample gradient matrices U_s (n x 2c) of the last few steps (running
+// average weights w_s), so its rank is at most m = steps * n, far below 2c
+// for the wide layers.  With D = diag(d_gamma ... d_beta ...) the damped
+// inverse applied to a gradient g is
+//   (D + H^T H)^-1 g = D^-1/2 ( g' - Hs^T (I + Hs Hs^T)^-1 Hs g' ),
+//   H = rows sqrt(w_s) u,  Hs = H D^-1/2,  g' = D^-1/2 g,
+// which needs the m x m matrix I + Hs Hs^T instead of the 2c x 2c factor.
+// Kernel 1 scales the stored rows into Hs; the factor engine forms Hs Hs^T;
+// the inverse plan inverts I + Hs Hs^T; kernel 2 applies the formula.
+constexpr int kLowRankSlots = 32;
+
+struct BnLowRankItem {
+  const float* hist;   // (m x 2c) stored per-sample gradients, slot after slot
+  float* Hs;           // (m x 2c) scaled copy
+  const float* Minv;   // (m x m) inverse of I + Hs Hs^T (kernel 2)
+  const float* g0;     // gradient of gamma, of beta
+  const float* g1;
+  float* y0;           // preconditioned gradients
+  float* y1;
+  float* p0;           // parameters / velocities of the fused update (or null)
+  float* p1;
+  float* v0;
+  float* v1;
+  int* flag;           // [0] scratch, [1] fallback counter
+  int c, m, rows_per_slot;
+  float dinv0, dinv1;  // d_gamma^-1/2, d_beta^-1/2
+  int blk_begin;       // first block of this layer in the scale launch
+  float slot_scale[kLowRankSlots];   // sqrt(weight) of every slot (0: unused)
+};
+
+__global__ void __launch_bounds__(256)
+bn_lowrank_scale_kernel(const BnLowRankItem* __restrict__ items, int nitems) {
+  __shared__ int s_begin[kBnItemsMax];
+  for (int i = threadIdx.x; i < nitems; i += blockDim.x)
+    s_begin[i] = items[i].blk_begin;
+  __syncthreads();
+  const int idx = bn_find_item(s_begin, nitems, blockIdx.x);
+  const BnLowRankItem* it = items + idx;
+  const int row = blockIdx.x - it->blk_begin;       // one block per stored row
+  const int c = it->c, d = 2 * c;
+  const float s = it->slot_scale[row / it->rows_per_slot];
+  const float a0 = s * it->dinv0, a1 = s * it->dinv1;
+  const float* src = it->hist + (long long)row * d;
+  float* dst = it->Hs + (long long)row * d;
+  for (int k = threadIdx.x; k < d; k += blockDim.x)
+    dst[k] = s == 0.f ? 0.f : src[k] * (k < c ? a0 : a1);
+}
+
+// One CTA per block.  Shared memory: g' and the result (2c floats each), v and
+// y (m floats each).
+__global__ void __launch_bounds__(256)
+bn_lowrank_apply_kernel(const BnLowRankItem* __restrict__ items, float lr,
+                        float momentum) {
+  extern __shared__ float lsm[];
+  const BnLowRankItem* it = items + blockIdx.x;
+  const int c = it->c, d = 2 * c, m = it->m;
+  float* gp = lsm;            // d
+  float* kf = lsm + d;        // d
+  float* v = lsm + 2 * d;     // m
+  float* y = v + m;           // m
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const float dinv0 = it->dinv0, dinv1 = it->dinv1;
+  for (int k = tid; k < d; k += 256)
+    gp[k] = k < c ? it->g0[k] * dinv0 : it->g1[k - c] * dinv1;
+  __syncthreads();
+  for (int a = warp; a < m; a += 8) {
+    const float* hr = it->Hs + (long long)a * d;
+    float s = 0.f;
+    for (int k = lane; k < d; k += 32) s += hr[k] * gp[k];
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_down_sync(0xffffffffu, s, o);
+    if (lane == 0) v[a] = s;
+  }
+  __syncthreads();
+  for (int a = warp; a < m; a += 8) {
+    const float* mr = it->Minv + (long long)a * m;
+    float s = 0.f;
+    for (int b = lane; b < m; b += 32) s += mr[b] * v[b];
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_down_sync(0xffffffffu, s, o);
+    if (lane == 0) y[a] = s;
+  }
+  __syncthreads();
+  int bad = 0;
+  for (int k = tid; k < d; k += 256) {
+    float s = 0.f;
+    for (int a = 0; a < m; ++a) s += it->Hs[(long long)a * d + k] * y[a];
+    const float r = (gp[k] - s) * (k < c ? dinv0 : dinv1);
+    kf[k] = r;
+    bad |= isnan(r) ? 1 : 0;
+  }
+  bad = __syncthreads_or(bad);
+  for (int k = tid; k < d; k += 256) {
+    const bool first = k < c;
+    const int j = first ? k : k - c;
+    // NaN anywhere: the raw gradients take the result's place
+    const float r = bad ? (first ? it->g0 : it->g1)[j] : kf[k];
+    (first ? it->y0 : it->y1)[j] = r;
+    float* p = first ? it->p0 : it->p1;
+    if (p != nullptr) {
+      float* vel = first ? it->v0 : it->v1;
+      const float nv = momentum * vel[j] - lr * r;
+      vel[j] = nv;
+      p[j] += nv;
+    }
+  }
+  if (tid == 0 && bad) it->flag[1] += 1;
+}
+
 __global__ void axpby_kernel(long long count, float a,
                              const float* __restrict__ x, float b,
                              const float* y, float* out) {
@@ -717,6 +826,105 @@ extern "C" int kfac_bn_precondition_group(
   return KFAC_OK;
 }
 
+static int lowrank_table(int count, const kfac_bn_lowrank_item* items,
+                         std::vector<BnLowRankItem>& tab, long long& blocks,
+                         size_t& smem_max) {
+  KFAC_REQUIRE(count > 0 && items != nullptr, "bn_lowrank: no items");
+  KFAC_REQUIRE(count <= kBnItemsMax, "bn_lowrank: %d layers, at most %d",
+               count, kBnItemsMax);
+  tab.resize(count);
+  blocks = 0;
+  smem_max = 0;
+  for (int i = 0; i < count; ++i) {
+    const kfac_bn_lowrank_item& k = items[i];
+    KFAC_REQUIRE(k.hist && k.scaled && k.c > 0 && k.rows_per_slot > 0 &&
+                     k.slots > 0 && k.slots <= kLowRankSlots,
+                 "bn_lowrank: bad item %d", i);
+    BnLowRankItem& t = tab[i];
+    t.hist = k.hist; t.Hs = k.scaled; t.Minv = k.m_inv;
+    t.g0 = k.grad_gamma; t.g1 = k.grad_beta;
+    t.y0 = k.kf_gamma; t.y1 = k.kf_beta;
+    t.p0 = k.param_gamma; t.p1 = k.param_beta;
+    t.v0 = k.mom_gamma; t.v1 = k.mom_beta;
+    t.flag = k.nan_flag;
+    t.c = k.c; t.rows_per_slot = k.rows_per_slot;
+    t.m = k.slots * k.rows_per_slot;
+    KFAC_REQUIRE(k.damp_gamma > 0.f && k.damp_beta > 0.f,
+                 "bn_lowrank: damping must be positive (item %d)", i);
+    t.dinv0 = 1.f / sqrtf(k.damp_gamma);
+    t.dinv1 = 1.f / sqrtf(k.damp_beta);
+    for (int s = 0; s < kLowRankSlots; ++s)
+      t.slot_scale[s] = s < k.slots && k.slot_weight[s] > 0.f
+                            ? sqrtf(k.slot_weight[s]) : 0.f;
+    t.blk_begin = (int)blocks;
+    blocks += t.m;
+    const size_t sm = (size_t)(4 * k.c + 2 * t.m) * sizeof(float);
+    smem_max = sm > smem_max ? sm : smem_max;
+  }
+  KFAC_REQUIRE(blocks < (1ll << 31), "bn_lowrank: too many rows");
+  return KFAC_OK;
+}
+
+extern "C" int kfac_bn_lowrank_scale(int count,
+                                     const kfac_bn_lowrank_item* items,
+                                     void* stream) {
+  std::vector<BnLowRankItem> tab;
+  long long blocks = 0;
+  size_t smem = 0;
+  int rc = lowrank_table(count, items, tab, blocks, smem);
+  if (rc != KFAC_OK) return rc;
+  void* dev = nullptr;
+  rc = ring_alloc(tab.size() * sizeof(BnLowRankItem), &dev);
+  if (rc != KFAC_OK) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  KFAC_CUDA(cudaMemcpyAsync(dev, tab.data(), tab.size() * sizeof(BnLowRankItem),
+                            cudaMemcpyHostToDevice, st));
+  bn_lowrank_scale_kernel<<<(int)blocks, 256, 0, st>>>(
+      static_cast<const BnLowRankItem*>(dev), count);
+  KFAC_LAUNCH_CHECK("bn_lowrank_scale_kernel");
+  return KFAC_OK;
+}
+
+extern "C" int kfac_bn_lowrank_apply(int count,
+                                     const kfac_bn_lowrank_item* items,
+                                     float lr, float momentum, void* stream) {
+  std::vector<BnLowRankItem> tab;
+  long long blocks = 0;
+  size_t smem = 0;
+  int rc = lowrank_table(count, items, tab, blocks, smem);
+  if (rc != KFAC_OK) return rc;
+  for (int i = 0; i < count; ++i) {
+    const kfac_bn_lowrank_item& k = items[i];
+    KFAC_REQUIRE(k.m_inv && k.grad_gamma && k.grad_beta && k.kf_gamma &&
+                     k.kf_beta && k.nan_flag,
+                 "bn_lowrank_apply: null pointer in item %d", i);
+    KFAC_REQUIRE(!k.param_gamma ||
+                     (k.param_beta && k.mom_gamma && k.mom_beta),
+                 "bn_lowrank_apply: fused update of item %d lacks a pointer",
+                 i);
+  }
+  KFAC_REQUIRE(smem <= 200 * 1024, "bn_lowrank_apply: block too large");
+  static bool attr_done[64] = {false};
+  int devi = 0;
+  KFAC_CUDA(cudaGetDevice(&devi));
+  if (devi >= 0 && devi < 64 && !attr_done[devi]) {
+    KFAC_CUDA(cudaFuncSetAttribute(bn_lowrank_apply_kernel,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   200 * 1024));
+    attr_done[devi] = true;
+  }
+  void* dev = nullptr;
+  rc = ring_alloc(tab.size() * sizeof(BnLowRankItem), &dev);
+  if (rc != KFAC_OK) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  KFAC_CUDA(cudaMemcpyAsync(dev, tab.data(), tab.size() * sizeof(BnLowRankItem),
+                            cudaMemcpyHostToDevice, st));
+  bn_lowrank_apply_kernel<<<count, 256, smem, st>>>(
+      static_cast<const BnLowRankItem*>(dev), lr, momentum);
+  KFAC_LAUNCH_CHECK("bn_lowrank_apply_kernel");
+  return KFAC_OK;
+}
+
 extern "C" int kfac_axpby(int64_t count, float a, const float* x, float b,
                           const float* y, float* out, void* stream) {
   if (count <= 0) return KFAC_OK;
@@ -847,6 +1055,16 @@ static int job_from_item(const kfac_factor_item& it, FactorJob& job) {
     if (it.add_ones_col) job.X.extra_idx = it.d_in;
     job.rows = it.rows;
     job.d = it.d_in + (it.add_ones_col ? 1 : 0);
+    job.n = 0;
+  } else if (it.kind == KFAC_FACTOR_DENSE_T) {
+    // X given transposed: x is (d_in x rows) row-major with pitch ld, i.e.
+    // out = alpha * x x^T + beta * out, contraction along x's rows
+    KFAC_REQUIRE(it.ld >= it.rows && it.rows > 0 && it.d_in > 0 &&
+                     !it.add_ones_col,
+                 "factor_group: bad transposed dense item");
+    job.X = strided_operand(it.x, 1, it.ld, it.d_in);
+    job.rows = it.rows;
+    job.d = it.d_in;
     job.n = 0;
   } else if (it.kind == KFAC_FACTOR_CONV_INPUT) {
     KFAC_REQUIRE(it.n > 0 && it.c > 0 && it.h > 0 && it.w > 0 && it.ksize > 0 &&

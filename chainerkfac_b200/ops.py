@@ -150,6 +150,20 @@ def dense_item(x, add_ones_col, alpha, beta, out):
     return it
 
 
+def dense_t_item(x, alpha, beta, out):
+    """Item for out = alpha * x x^T + beta * out with ``x`` (d, rows)
+    row-major: the contraction runs along x's rows."""
+    _chk(x, 'x')
+    _chk(out, 'out')
+    it = _lib.FactorItem()
+    it.kind, it.add_ones_col = 3, 0
+    it.x, it.d_in, it.rows, it.ld = x.data_ptr(), x.shape[0], x.shape[1], \
+        x.stride(0)
+    it.alpha, it.beta, it.out = alpha, beta, out.data_ptr()
+    it._keep = (x, out)
+    return it
+
+
 def conv_input_item(x, ksize, stride, pad, add_ones_col, alpha, beta, out):
     if _conv_input_as_dense(x, ksize, stride, pad):
         return dense_item(_nhwc_rows(x), add_ones_col, alpha, beta, out)
@@ -281,6 +295,52 @@ def bn_precondition_group(F_inv, grad_gamma, grad_beta, kf_gamma, kf_beta,
             ptrs(param_beta, lo, hi), ptrs(mom_gamma, lo, hi),
             ptrs(mom_beta, lo, hi), ptrs(nan_flags, lo, hi), lr, momentum,
             _stream()), 'kfac_bn_precondition_group')
+
+
+def bn_lowrank_item(hist, scaled, c, rows_per_slot, slot_weights, damp_gamma,
+                    damp_beta, m_inv=None, grad_gamma=None, grad_beta=None,
+                    kf_gamma=None, kf_beta=None, nan_flag=None,
+                    param_gamma=None, param_beta=None, mom_gamma=None,
+                    mom_beta=None):
+    """struct kfac_bn_lowrank_item for one BatchNormalization block (see
+    include/kfac_b200.h)."""
+    it = _lib.BnLowRankItem()
+    keep = []
+    for name, t in (('hist', hist), ('scaled', scaled), ('m_inv', m_inv),
+                    ('grad_gamma', grad_gamma), ('grad_beta', grad_beta),
+                    ('kf_gamma', kf_gamma), ('kf_beta', kf_beta),
+                    ('param_gamma', param_gamma), ('param_beta', param_beta),
+                    ('mom_gamma', mom_gamma), ('mom_beta', mom_beta),
+                    ('nan_flag', nan_flag)):
+        if t is not None:
+            if name != 'nan_flag':
+                _chk(t, name)
+            setattr(it, name, t.data_ptr())
+            keep.append(t)
+    it.c, it.rows_per_slot, it.slots = c, rows_per_slot, len(slot_weights)
+    it.damp_gamma, it.damp_beta = damp_gamma, damp_beta
+    for k, w in enumerate(slot_weights):
+        it.slot_weight[k] = w
+    it._keep = keep
+    return it
+
+
+def bn_lowrank_scale(items):
+    if not items:
+        return
+    lib = _lib.load()
+    arr = (_lib.BnLowRankItem * len(items))(*items)
+    _lib.check(lib.kfac_bn_lowrank_scale(len(items), arr, _stream()),
+               'kfac_bn_lowrank_scale')
+
+
+def bn_lowrank_apply(items, lr=0.0, momentum=0.0):
+    if not items:
+        return
+    lib = _lib.load()
+    arr = (_lib.BnLowRankItem * len(items))(*items)
+    _lib.check(lib.kfac_bn_lowrank_apply(len(items), arr, lr, momentum,
+                                         _stream()), 'kfac_bn_lowrank_apply')
 
 
 def axpby(a, x, b, y, out):

@@ -2,12 +2,35 @@
 mirrors ``chainerkfac/optimizers/fisher_blocks/normalizations/
 batch_normalization.py``."""
 
+import math
 import warnings
 
 import torch
 
 from chainerkfac_b200 import ops
 from chainerkfac_b200.optimizers.fisher_block import FisherBlock
+
+
+LOWRANK_MAX_SLOTS = 32      # slots of kfac_bn_lowrank_item
+LOWRANK_FORGET = 1e-8       # weight below which a past step is forgotten
+
+
+def lowrank_window(cov_ema_decay):
+    """Number of past steps whose per-sample gradients the running average
+    F <- decay * F_new + (1 - decay) * F still holds with a relative weight
+    above LOWRANK_FORGET (below fp32 resolution of the sum): 1 when the
+    running average is switched off (decay 1.0), 0 when the window would
+    not fit the history slots of the low-rank form, which then is not used.
+    A factor that is the weighted sum of w steps of n per-sample gradient
+    rows has rank <= w * n, and (F + D)^-1 g needs only the inverse of a
+    (w n) x (w n) matrix (Woodbury)."""
+    rest = 1.0 - float(cov_ema_decay)
+    if rest <= 0.0:
+        return 1
+    if rest >= 1.0:
+        return 0
+    w = int(math.ceil(math.log(LOWRANK_FORGET) / math.log(rest) - 1e-9))
+    return w if w <= LOWRANK_MAX_SLOTS else 0
 
 
 class BatchNormalizationFunction(object):

@@ -136,6 +136,8 @@ int kfac_factor_dense_noalloc(const float* x, int64_t rows, int d_in,
 #define KFAC_FACTOR_DENSE 0
 #define KFAC_FACTOR_CONV_INPUT 1
 #define KFAC_FACTOR_CONV_GRAD 2
+#define KFAC_FACTOR_DENSE_T 3   /* x is (d_in x rows) row-major, pitch ld:
+                                   out = alpha x x^T + beta out */
 typedef struct kfac_factor_item {
   int kind;
   int add_ones_col;
@@ -329,6 +331,45 @@ int kfac_bn_precondition_group(
     float* const* kf_gamma, float* const* kf_beta, float* const* param_gamma,
     float* const* param_beta, float* const* mom_gamma, float* const* mom_beta,
     int* const* nan_flags, float lr, float momentum, void* stream);
+
+/* Low-rank form of the BatchNormalization blocks (an addition: the reference
+ * always forms and inverts the dense 2c x 2c factor,
+ * normalizations/batch_normalization.py:126-191).  The factor of such a block
+ * is F = sum_s w_s U_s^T U_s over the per-sample gradient matrices U_s
+ * (rows_per_slot x 2c, as kfac_bn_sample_grads writes them) of the last
+ * `slots` steps, so its rank is at most m = slots * rows_per_slot.  With the
+ * damping D = diag(damp_gamma ... damp_beta ...)
+ *   (F + D)^-1 g = D^-1/2 (g' - Hs^T (I + Hs Hs^T)^-1 Hs g'),
+ *   Hs = rows sqrt(w_s) u D^-1/2,  g' = D^-1/2 g.
+ * kfac_bn_lowrank_scale writes Hs (`scaled`, m x 2c) from the stored rows
+ * (`hist`, m x 2c, slot after slot; slot_weight[s] <= 0: slot unused, rows
+ * become zero).  The caller then forms Hs Hs^T with kfac_factor_group
+ * (KFAC_FACTOR_DENSE_T) and inverts I + Hs Hs^T with an inverse plan (role 2,
+ * damping 1, scale 1).  kfac_bn_lowrank_apply evaluates the formula with that
+ * inverse (`m_inv`, m x m) for every block (one CTA each; 2c <= 12000), with
+ * the NaN fallback and the optional fused momentum update of
+ * kfac_bn_precondition_group.  `items` is a host array (<= 256 entries). */
+typedef struct kfac_bn_lowrank_item {
+  const float* hist;
+  float* scaled;
+  const float* m_inv;                 /* apply only */
+  const float* grad_gamma;            /* apply only, as are the next ten */
+  const float* grad_beta;
+  float* kf_gamma;
+  float* kf_beta;
+  float* param_gamma;                 /* NULL: no fused update */
+  float* param_beta;
+  float* mom_gamma;
+  float* mom_beta;
+  int* nan_flag;                      /* two device ints */
+  int c, rows_per_slot, slots;        /* slots <= 32 */
+  float damp_gamma, damp_beta;
+  float slot_weight[32];
+} kfac_bn_lowrank_item;
+int kfac_bn_lowrank_scale(int count, const kfac_bn_lowrank_item* items,
+                          void* stream);
+int kfac_bn_lowrank_apply(int count, const kfac_bn_lowrank_item* items,
+                          float lr, float momentum, void* stream);
 
 /* v = momentum * v - lr * grad; param += v over `count` floats.
  * Replaces KFACUpdateRule.update_core_gpu, optimizers/kfac.py:101-116. */

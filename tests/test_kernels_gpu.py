@@ -434,6 +434,52 @@ def test_bn_kfgrad(ops, golden):
     assert rel(host(y0), g['kf_gamma']) < KFGRAD_TOL
 
 
+def test_bn_lowrank_form_matches_dense_oracle(ops):
+    """The low-rank form of a BatchNormalization block -- (D + sum_s w_s
+    U_s^T U_s)^-1 g through the m x m matrix I + Hs Hs^T -- against the dense
+    path of the oracle: running average of three steps' factors (decay 0.9),
+    separate damping of the gamma and beta halves, damped inverse, product
+    with the gradient."""
+    rng = np.random.default_rng(31)
+    n, c, steps, r = 8, 20, 3, 0.9
+    d_gamma, d_beta = 16.0 * 1e-3, 16.0 * 5e-3
+    Us = [(rng.standard_normal((n, 2 * c)) * 0.3).astype(np.float32)
+          for _ in range(steps)]
+    # oracle: F_t = r U^T U / n + (1 - r) F_{t-1}, first step plain
+    F = None
+    for U in Us:
+        cov = (U.T @ U / n).astype(np.float32)
+        F = cov if F is None else orc.update_cov_ema(cov, F, r)
+    add = np.concatenate([np.full(c, d_gamma), np.full(c, d_beta)])
+    Finv = np.linalg.inv(F.astype(np.float64) + np.diag(add))
+    gg = rng.standard_normal(c).astype(np.float32)
+    gb = rng.standard_normal(c).astype(np.float32)
+    want = Finv @ np.concatenate([gg, gb])
+    # weights of the slots, oldest first: (1-r)^2, r(1-r), r; each over n
+    w = [(1 - r) ** 2 / n, r * (1 - r) / n, r / n, 0.0]    # one unused slot
+    hist = dev(np.concatenate(Us + [np.full((n, 2 * c), 7.0, np.float32)]))
+    m = 4 * n
+    Hs = torch.empty_like(hist)
+    M0 = torch.empty((m, m), device='cuda')
+    Minv = torch.empty_like(M0)
+    kg, kb = torch.empty(c, device='cuda'), torch.empty(c, device='cuda')
+    flag = torch.zeros(2, dtype=torch.int32, device='cuda')
+    item = ops.bn_lowrank_item(hist, Hs, c, n, w, d_gamma, d_beta, Minv,
+                               dev(gg), dev(gb), kg, kb, flag)
+    ops.bn_lowrank_scale([item])
+    ops.factor_group([ops.dense_t_item(Hs, 1.0, 0.0, M0)], M0.device)
+    plan = ops.InversePlan([M0], [Minv], [-1], [2], scale=[1.0])
+    plan.run(1.0, use_pi=False)
+    ops.bn_lowrank_apply([item])
+    got = np.concatenate([host(kg), host(kb)])
+    assert rel(got, want) < KFGRAD_TOL
+    assert rel(got, want) < 1e-4        # and in fact far inside it
+    assert flag.tolist() == [0, 0]
+    # the unused slot contributes nothing: its rows are zero in Hs
+    assert float(Hs[3 * n:].abs().max()) == 0.0
+    plan.close()
+
+
 # -------------------------------------------------------------- wire format
 @pytest.mark.parametrize('n,c,h,k,s,p,bias', [
     (2, 40, 9, 1, 1, 0, True),      # its own patch matrix: read in place
