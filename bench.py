@@ -314,7 +314,12 @@ class DeviceWorkload(object):
                 if i > 0 and l['kind'] != 'bn':
                     x.clamp_(min=0)          # post-ReLU activations
                 self.x[i] = x
-                self.gy[i] = torch.randn(gs, device=device, generator=g) / n
+                # output gradients of a mean loss; a BatchNormalization layer
+                # sums them over h x h positions per sample, so they are
+                # drawn smaller there by h (keeps F + damping well inside
+                # fp32 range of a Cholesky factorisation)
+                self.gy[i] = torch.randn(gs, device=device, generator=g) / (
+                    n * l['h'] if l['kind'] == 'bn' else n)
             P, gP, vP = [], [], []
             for shp in shapes:
                 if shp is None:
@@ -1057,7 +1062,10 @@ def run_ours(args):
             'dtype': 'f32', 'data': 'synthetic',
             'config': {'workload': spec['name'], 'batch_per_gpu': batch,
                        'layers': len(wl.layers),
-X: spec['decay'],
+                       'bn_blocks': sum(1 for l in wl.layers
+                                        if l['kind'] == 'bn'),
+                       'bn_blocks_low_rank': len(wl.lr),
+                       'cov_ema_decay': spec['decay'],
                        'damping': spec['damping'], 'acc_iters': acc,
                        'l2_flush': ('inputs larger than L2 (%.2f GB of '
                                     'activations and gradients per step)'
@@ -1120,7 +1128,7 @@ def run_e2e(args, device, world, rank, spec):
         device, spec['batch'], world, rank, cov_ema_decay=spec['decay'],
         damping=spec['damping'], lr=LR, momentum=MOMENTUM,
         communicator=COMMUNICATOR, acc_iters=acc,
-        bn_blocks=not args.no_bn_blocks)
+        bn_blocks=not args.no_bn_blocks, bn_low_rank=not args.bn_dense)
     steps = args.steps * acc
     for _ in range(max(args.warmup, 3) * acc):
         step()
@@ -1165,7 +1173,8 @@ def cpu_layer_inputs(l, rng):
     if l['kind'] == 'bn':
         shp = (n, l['c'], l['h'], l['h'])
         return (rng.standard_normal(shp, dtype=np.float32),
-                rng.standard_normal(shp, dtype=np.float32) / np.float32(n),
+                rng.standard_normal(shp, dtype=np.float32) /
+                np.float32(n * l['h']),
                 rng.standard_normal(l['c'], dtype=np.float32),
                 rng.standard_normal(l['c'], dtype=np.float32))
     if l['kind'] == 'conv':

@@ -57,7 +57,7 @@ class ResNet50(nn.Module):
 def build_training_step(device, batch, world, rank, cov_ema_decay, damping,
                         lr, momentum, image=224, classes=1000,
                         bn_blocks=True, communicator='peer_memory',
-                        channels_last=True, acc_iters=1):
+                        channels_last=True, acc_iters=1, bn_low_rank=True):
     """Returns (step, h2d_bytes, d2h_bytes).  ``step()`` copies one pinned
     host batch to the device, runs ``optimizer.update(lossfun, x, t)``
     (forward, backward, K-FAC factors / inverses / preconditioned update) and
@@ -71,7 +71,8 @@ def build_training_step(device, batch, world, rank, cov_ema_decay, damping,
     model.train()
     ctor = fblock_constructor if bn_blocks else connection_only_constructor
     kwargs = dict(lr=lr, momentum=momentum, cov_ema_decay=cov_ema_decay,
-                  damping=damping, constructor=ctor, acc_iters=acc_iters)
+                  damping=damping, constructor=ctor, acc_iters=acc_iters,
+                  bn_low_rank=bn_low_rank)
     if world > 1:
         comm = ck.create_communicator(communicator)
         opt = ck.DistributedKFAC(comm, ownership='balanced', **kwargs)

@@ -451,6 +451,13 @@ class InversePlan(object):
             pass
 
 
+def class_bounds():
+    """Sides that separate the size classes of an InversePlanSet (environment
+    variable KFAC_CLASS_BOUNDS, default 1024,3000)."""
+    return tuple(int(b) for b in os.environ.get(
+        'KFAC_CLASS_BOUNDS', '1024,3000').split(','))
+
+
 class InversePlanSet(object):
     """Several InversePlans over disjoint subsets of (factor, inverse) pairs,
     run on separate CUDA streams.  The long serial chain of diagonal-block
@@ -462,8 +469,7 @@ class InversePlanSet(object):
                  scale=None, bounds=None, l2_coef_second=None):
         n = len(factors)
         if bounds is None:
-            bounds = tuple(int(b) for b in os.environ.get(
-                'KFAC_CLASS_BOUNDS', '1024,3000').split(','))
+            bounds = class_bounds()
         l2_coef = l2_coef if l2_coef is not None else [0.0] * n
         scale = scale if scale is not None else [1.0] * n
         second = l2_coef_second if l2_coef_second is not None else l2_coef

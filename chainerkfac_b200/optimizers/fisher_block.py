@@ -70,6 +70,19 @@ class FisherBlock(object):
     def get_diagval(self, attr):
         return get_diagval(self._link, attr, self.damping)
 
+    low_rank_active = False
+
+    def has_state(self):
+        """A running average exists."""
+        return self.cov_emas is not None
+
+    def plan_factors(self):
+        """The factors the optimizer's batched inverse plan covers."""
+        return self.cov_emas
+
+    def max_side(self):
+        return max(int(c.shape[0]) for c in self.covs)
+
     def gy_scale(self, n):
         s = float(n)
         if self._loss_scale is not None:

@@ -38,14 +38,159 @@ class BatchNormalizationFunction(object):
 
 
 class FisherBlockBatchNormalization(FisherBlock):
+    """Besides the reference's dense 2C x 2C factor this block has a
+    low-rank form (no counterpart in the reference; same results up to the
+    forgotten tail of the running average, see ``lowrank_window``): while
+    the running average remembers w steps of n per-sample gradient rows on
+    each of ``world`` ranks and w * n * world <= C, the block stores those
+    rows instead of F, and applies (F + D)^-1 through the inverse of a
+    (w n world)-sided matrix.  The optimizer switches it on by setting
+    ``low_rank_world`` (the number of ranks; None: dense only); the block
+    falls back to the dense factor for good when the batch size or the decay
+    changes.  ``cov_emas`` then is the dense running average formed from the
+    stored rows on request; ``invs`` stays None."""
+
+    low_rank_world = None     # set by the optimizer: ranks whose rows arrive
+    low_rank_rank = 0         # this rank's position among them
+    keeps_history = True      # False on ranks that do not own the block
 
     def __init__(self, *args, **kwargs):
         self._F = None
         self._nan_flag = None
+        self._lr = None
+        self._cov_emas = None
         super(FisherBlockBatchNormalization, self).__init__(*args, **kwargs)
         if self.link.gamma is None or self.link.beta is None:
             raise NotImplementedError(
                 'BatchNormalization blocks need both gamma and beta')
+
+    # -- low-rank form -------------------------------------------------------
+    @property
+    def low_rank_active(self):
+        return self._lr is not None
+
+    @property
+    def cov_emas(self):
+        if self._lr is not None:
+            if not self.keeps_history or not any(self._lr['w']):
+                return None
+            return [self._dense_from_history()]
+        return self._cov_emas
+
+    @cov_emas.setter
+    def cov_emas(self, value):
+        self._cov_emas = value
+
+    def has_state(self):
+        """A running average exists (dense, or as stored rows)."""
+        if self._lr is not None:
+            return any(self._lr['w'])
+        return self._cov_emas is not None
+
+    def plan_factors(self):
+        """The factors the optimizer's batched inverse plan covers."""
+        return [] if self._lr is not None else self._cov_emas
+
+    def max_side(self):
+        if self._lr is not None:
+            return self._lr['slots'] * self._lr['rows']
+        return 2 * self.link.gamma.data.numel()
+
+    def _low_rank_wanted(self, n, c):
+        world = self.low_rank_world
+        if world is None or not self.deferred:
+            return None
+        slots = lowrank_window(self.cov_ema_decay)
+        if slots == 0 or slots * n * world > c:
+            return None
+        return (n, slots, world, float(self.cov_ema_decay))
+
+    def _low_rank_setup(self, key, c, device):
+        n, slots, world, _ = key
+        rows, d = n * world, 2 * c
+        own = self.keeps_history
+        m = slots * rows
+        z = dict(dtype=torch.float32, device=device)
+        self._lr = dict(
+            key=key, rows=rows, slots=slots, c=c,
+            hist=torch.zeros(((m if own else rows), d), **z),
+            Hs=torch.empty((m, d), **z) if own else None,
+            M=torch.empty((m, m), **z) if own else None,
+            Minv=torch.empty((m, m), **z) if own else None,
+            w=[0.0] * slots, pos=-1, plan=None)
+
+    def _next_slot(self):
+        st = self._lr
+        k = (st['pos'] + 1) % st['slots'] if self.keeps_history else 0
+        return st['hist'][k * st['rows']:(k + 1) * st['rows']]
+
+    def _row_factor(self):
+        # F = sum_s w_s (sum over ranks of U^T U) / (n world); after the mean
+        # over ranks of the exchange a slot holds every rank's rows / world
+        n, _, world, _ = self._lr['key']
+        return float(world) / n
+
+    def _dense_from_history(self, out=None):
+        st = self._lr
+        d = st['hist'].shape[1]
+        if out is None:
+            out = torch.empty((d, d), dtype=torch.float32,
+                              device=st['hist'].device)
+        beta, fac = 0.0, self._row_factor()
+        for k, w in enumerate(st['w']):
+            if w > 0.0:
+                rows = st['hist'][k * st['rows']:(k + 1) * st['rows']]
+                ops.factor_group([ops.dense_item(rows, False, w * fac, beta,
+                                                 out)], out.device)
+                beta = 1.0
+        if beta == 0.0:
+            out.zero_()
+        return out
+
+    def _to_dense(self):
+        """Leave the low-rank form for good: the running average becomes the
+        dense factor formed from the stored rows."""
+        st = self._lr
+        dense = None
+        if self.keeps_history and any(st['w']):
+            dense = [self._dense_from_history()]
+        self._lr = None
+        self._cov_emas = dense
+        self._grads = None
+
+    def commit_rows(self):
+        """The running-average step of the low-rank form: the rows written
+        by the last backward pass become the newest slot with the decay's
+        weight, older slots fade (first step: weight 1, as the reference's
+        first running average is a copy)."""
+        st = self._lr
+        r = self._lr['key'][3]
+        first = not any(st['w'])
+        st['pos'] = (st['pos'] + 1) % st['slots']
+        rest = 0.0 if (first or r == 1.0) else 1.0 - r
+        st['w'] = [w * rest for w in st['w']]
+        st['w'][st['pos']] = 1.0 if (first or r == 1.0) else r
+
+    def low_rank_item(self, with_grads=False):
+        """struct kfac_bn_lowrank_item of this block (``with_grads``: the
+        fields kfac_bn_lowrank_apply needs as well)."""
+        st = self._lr
+        fac = self._row_factor()
+        l2g = getattr(self.link.gamma, 'l2_coef', 0.0) or 0.0
+        l2b = getattr(self.link.beta, 'l2_coef', 0.0) or 0.0
+        dg = max(l2g, self.damping) * float(self.stab_coeff)
+        db = max(l2b, self.damping) * float(self.stab_coeff)
+        extra = ()
+        if with_grads:
+            a = self.kfgrad_args(low_rank=True)
+            extra = (st['Minv'], a[1], a[2], a[3], a[4], a[5])
+        return ops.bn_lowrank_item(st['hist'], st['Hs'], st['c'], st['rows'],
+                                   [w * fac for w in st['w']], dg, db, *extra)
+
+    def low_rank_matrix_item(self):
+        """Grouped-build item M = Hs Hs^T."""
+        st = self._lr
+        return ops.dense_t_item(st['Hs'], 1.0, 0.0, st['M'])
 
     @property
     def funcclass(self):
@@ -75,6 +220,8 @@ class FisherBlockBatchNormalization(FisherBlock):
         if self.deferred:
             self._pending = (in_data, out_grad_data)
             return
+        if self._lr is not None:
+            self._to_dense()
         self._F = self.compute_F(in_data, out_grad_data)
         self.covs = [self._F]
 
@@ -90,24 +237,52 @@ class FisherBlockBatchNormalization(FisherBlock):
                               device=device)
         return out
 
+    def resolve_form(self):
+        """Decide between the dense and the low-rank form for the pending
+        hook arguments: low-rank from a block's first step while the stored
+        rows stay fewer than C; dense for good once the batch size, the
+        decay or the number of ranks changes."""
+        pend = getattr(self, '_pending', None)
+        if pend is None:
+            return
+        x = pend[0][0]
+        self._check_dims(x)
+        n, c = x.shape[0], x.shape[1]
+        want = self._low_rank_wanted(n, c)
+        if self._lr is not None and self._lr['key'] != want:
+            self._to_dense()
+        elif self._lr is None and want is not None and \
+                self._cov_emas is None:
+            self._low_rank_setup(want, c, x.device)
+
     def pending_item(self):
         """Item of ``ops.bn_sample_grads_group`` for the pending hook
         arguments (None if there are none)."""
         pend = getattr(self, '_pending', None)
         if pend is None:
             return None
+        self.resolve_form()
         self._pending = None
         x, gy = pend[0][0], pend[1][0]
-        self._check_dims(x)
+        n = x.shape[0]
+        out = getattr(self, '_grads', None)
+        if self._lr is not None:
+            slot = self._next_slot()
+            if self._lr['key'][2] > 1:
+                slot.zero_()      # the other ranks' rows arrive by the sum
+            out = slot[self.low_rank_rank * n:(self.low_rank_rank + 1) * n]
+            self.covs = None
         self._grads_item = ops.bn_item(
-            x, gy, float(self.link.eps), self.gy_scale(x.shape[0]),
-            getattr(self, '_grads', None))
+            x, gy, float(self.link.eps), self.gy_scale(n), out)
         self._grads = self._grads_item.result
         return self._grads_item
 
     def factor_item(self):
         """Grouped-build item F = grads^T grads / n for the gradients of the
-        last ``pending_item``; sets ``covs``."""
+        last ``pending_item``; sets ``covs``.  None in the low-rank form (the
+        rows themselves are the state)."""
+        if self._lr is not None:
+            return None
         grads = self._grads
         n, c2 = grads.shape
         self._F = self.factor_buffer(c2 // 2, grads.device)
@@ -129,6 +304,8 @@ class FisherBlockBatchNormalization(FisherBlock):
         # batch_normalization.py:133-157: max(l2_coef, damping) * stab_coeff,
         # with gamma's l2_coef for the first half of the diagonal and beta's
         # for the second
+        if self._lr is not None:
+            return []           # no dense factor to invert
         l2_gamma = getattr(self.link.gamma, 'l2_coef', 0.0) or 0.0
         l2_beta = getattr(self.link.beta, 'l2_coef', 0.0) or 0.0
         return [(2, l2_gamma, float(self.stab_coeff), l2_beta)]
@@ -137,14 +314,38 @@ class FisherBlockBatchNormalization(FisherBlock):
         self.diag_val_backward = diag[0]
 
     def get_diagvals(self):
+        if self._lr is not None:
+            it = self.low_rank_item()
+            c = self._lr['c']
+            dev = self._lr['hist'].device
+            return [torch.cat([torch.full((c,), it.damp_gamma, device=dev),
+                               torch.full((c,), it.damp_beta, device=dev)])]
         if self._plan is None:
             self.update_invs()
         return [self.diag_val_backward.expand(self.cov_emas[0].shape[0])]
 
-    def kfgrad_args(self):
+    def update_cov_emas(self):
+        if self._lr is not None:
+            self.commit_rows()
+            return
+        super(FisherBlockBatchNormalization, self).update_cov_emas()
+
+    def update_invs(self):
+        if self._lr is None:
+            return super(FisherBlockBatchNormalization, self).update_invs()
+        st = self._lr
+        ops.bn_lowrank_scale([self.low_rank_item()])
+        ops.factor_group([self.low_rank_matrix_item()], st['M'].device)
+        if st['plan'] is None:
+            st['plan'] = ops.InversePlan([st['M']], [st['Minv']], [-1], [2],
+                                         scale=[1.0])
+        st['plan'].run(1.0, False)
+
+    def kfgrad_args(self, low_rank=False):
         """(F_inv, grad_gamma, grad_beta, kf_gamma, kf_beta, nan_flag) for
         ``ops.bn_precondition_group``."""
-        self.check_attr('invs')
+        if not low_rank:
+            self.check_attr('invs')
         gamma, beta = self.link.gamma, self.link.beta
         for p in (gamma, beta):
             if getattr(p, 'kfgrad', None) is None or p.kfgrad is p.grad:
@@ -153,14 +354,18 @@ class FisherBlockBatchNormalization(FisherBlock):
             self._nan_flag = torch.zeros(2, dtype=torch.int32,
                                          device=gamma.data.device)
             self._nan_seen = 0
-        return (self.invs[0], gamma.grad.contiguous(), beta.grad.contiguous(),
-                gamma.kfgrad, beta.kfgrad, self._nan_flag)
+        return (None if low_rank else self.invs[0], gamma.grad.contiguous(),
+                beta.grad.contiguous(), gamma.kfgrad, beta.kfgrad,
+                self._nan_flag)
 
     def update_kfgrads(self):
         # batch_normalization.py:159-191: F_inv [grad_gamma; grad_beta]; on
         # NaN the raw gradients are used instead (the reference checks on the
         # host with xp.any(xp.isnan(..)); here the library substitutes them
         # on the device, without a synchronisation)
+        if self._lr is not None:
+            ops.bn_lowrank_apply([self.low_rank_item(with_grads=True)])
+            return
         a = self.kfgrad_args()
         ops.bn_precondition_group([a[0]], [a[1]], [a[2]], [a[3]], [a[4]],
                                   [a[5]])
@@ -182,5 +387,10 @@ class FisherBlockBatchNormalization(FisherBlock):
 
     def extract_for_reduce_scatter_v(self):
         arrays = self.extract_attr_from_params('grad')
-        arrays.append((self.cov_backward, True))
+        if self._lr is not None:
+            # the slot with this rank's rows in place and zeros elsewhere:
+            # the mean over ranks is the stack of all ranks' rows / world
+            arrays.append((self._next_slot(), False))
+        else:
+            arrays.append((self.cov_backward, True))
         return arrays

@@ -177,6 +177,9 @@ def update_cov_emas_grouped(blocks):
     average yet, or with decay 1 (plain copy), take the per-block path."""
     xs, outs, r = [], [], None
     for fb in blocks:
+        if fb.low_rank_active:
+            fb.update_cov_emas()     # stored rows: a host-side step
+            continue
         fb.check_attr('covs')
         decay = fb.cov_ema_decay
         if fb.cov_emas is None or decay == 1.0 or (r is not None and decay != r):
@@ -205,8 +208,18 @@ def pending_factor_items(blocks, forward_only=False):
                 bn.append((fb, it))
     if bn:
         ops.bn_sample_grads_group([it for _, it in bn])
-        items += [fb.factor_item() for fb, _ in bn]
+        items += [it for it in (fb.factor_item() for fb, _ in bn)
+                  if it is not None]
     return items
+
+
+def lowrank_build(blocks, device):
+    """Scaled history Hs and M = Hs Hs^T of BatchNormalization blocks in
+    their low-rank form (after the running-average step of this update)."""
+    if blocks:
+        ops.bn_lowrank_scale([fb.low_rank_item() for fb in blocks])
+        ops.factor_group([fb.low_rank_matrix_item() for fb in blocks],
+                         device)
 
 
 class KFAC(_base.GradientMethod):
@@ -218,8 +231,13 @@ class KFAC(_base.GradientMethod):
                  damping=_default_hyperparam.damping, stab_coeff=16.0,
                  constructor=fblock_constructor, pi_type='tracenorm',
                  use_cholesky=True, loss_scale=None, adjust_momentum=False,
-                 acc_iters=1):
+                 acc_iters=1, bn_low_rank=True):
         super(KFAC, self).__init__()
+        # BatchNormalization blocks may keep their running average as the
+        # per-sample gradient rows it is made of (see
+        # FisherBlockBatchNormalization); False keeps the dense 2C x 2C
+        # factor everywhere
+        self.bn_low_rank = bn_low_rank
         self.hyperparam.lr = lr
         self.hyperparam.lr_pre = lr
         self.hyperparam.momentum = momentum
@@ -254,6 +272,8 @@ class KFAC(_base.GradientMethod):
         self._emas_done = False
         self._accumulated = False    # accumulate() already ran for this call
         self._plans = {}
+        self._lr_plans = {}
+        self._lr_built = False       # a pipelined path already built M
         self.observation = {}
 
     lr = _base.HyperparameterProxy('lr')
@@ -272,8 +292,17 @@ class KFAC(_base.GradientMethod):
             if fblock is None:
                 continue
             self.fblocks.append(fblock)
+        self._set_low_rank(1, 0, None)
         self.kfhook = KFACHook(self.fblocks)
         return self
+
+    def _set_low_rank(self, world, rank, owned):
+        on = self.bn_low_rank and self.acc_iters == 1
+        for i, fb in enumerate(self.fblocks):
+            if isinstance(fb, FB.FisherBlockBatchNormalization):
+                fb.low_rank_world = world if on else None
+                fb.low_rank_rank = rank
+                fb.keeps_history = owned is None or i in owned
 
     def reallocate_cleared_grads(self):
         for name, param in self.target.namedparams(include_uninit=False):
@@ -314,6 +343,9 @@ class KFAC(_base.GradientMethod):
         # update rules divide the (scaled) gradients by it
         for param in self.target.params():
             param._loss_scale = self._loss_scale
+        for fb in self.fblocks:
+            if isinstance(fb, FB.FisherBlockBatchNormalization):
+                fb.resolve_form()
         # with a valid inverse plan the factor build is pipelined with the
         # inverses inside update_kfgrads; otherwise build everything now
         self._factors_pending = self._pipeline_ready()
@@ -416,21 +448,26 @@ class KFAC(_base.GradientMethod):
     def _plan_for(self, fblocks):
         key = tuple(id(fb) for fb in fblocks)
         entry = self._plans.get(key)
-        bufs = tuple(e.data_ptr() for fb in fblocks for e in fb.cov_emas)
+        bufs = tuple(e.data_ptr() for fb in fblocks
+                     for e in fb.plan_factors())
         if entry is not None and entry[1] == bufs:
             return entry[0]
-        if entry is not None:
+        if entry is not None and entry[0] is not None:
             entry[0].close()
+        if not bufs:
+            self._plans[key] = (None, bufs)
+            return None
         factors, inverses, partner, role, l2, scale = [], [], [], [], [], []
         l2_second = []
         for fb in fblocks:
             ents = fb.plan_entries()
             base = len(factors)
-            fb.ensure_invs()
+            if ents:
+                fb.ensure_invs()
             for j, ent in enumerate(ents):
                 rl, l2c, sc = ent[:3]
                 l2_second.append(ent[3] if len(ent) > 3 else l2c)
-                factors.append(fb.cov_emas[j])
+                factors.append(fb.plan_factors()[j])
                 inverses.append(fb.invs[j])
                 partner.append(base + 1 - j if len(ents) == 2 else -1)
                 role.append(rl)
@@ -441,6 +478,23 @@ class KFAC(_base.GradientMethod):
         self._plans[key] = (plan, bufs)
         return plan
 
+    def _lr_plan_for(self, blocks):
+        """Batched inverse of the matrices I + Hs Hs^T of low-rank blocks
+        (role 2, damping 1, scale 1: the added diagonal is the identity)."""
+        key = tuple(id(fb) for fb in blocks)
+        entry = self._lr_plans.get(key)
+        bufs = tuple(fb._lr['M'].data_ptr() for fb in blocks)
+        if entry is not None and entry[1] == bufs:
+            return entry[0]
+        if entry is not None:
+            entry[0].close()
+        k = len(blocks)
+        plan = ops.InversePlanSet([fb._lr['M'] for fb in blocks],
+                                  [fb._lr['Minv'] for fb in blocks],
+                                  [-1] * k, [2] * k, scale=[1.0] * k)
+        self._lr_plans[key] = (plan, bufs)
+        return plan
+
     def _pipeline_ready(self):
         """True when the factor build may be pipelined with the inverses: a
         single process, no accumulation, grouped factors, one (damping, pi)
@@ -449,11 +503,12 @@ class KFAC(_base.GradientMethod):
                 not self.group_factors or not self.fblocks:
             return False
         first = self.fblocks[0]
-        if any(fb.cov_emas is None or
+        if any(not fb.has_state() or
                (fb.damping, fb._pi_type) != (first.damping, first._pi_type)
                for fb in self.fblocks):
             return False
-        return tuple(id(fb) for fb in self.fblocks) in self._plans
+        entry = self._plans.get(tuple(id(fb) for fb in self.fblocks))
+        return entry is not None and entry[0] is not None
 
     def _pipelined_factors_and_emas(self, fblocks, plan):
         """Build factors and running averages size class by size class,
@@ -462,10 +517,19 @@ class KFAC(_base.GradientMethod):
         factors then run next to the factor build of the other layers."""
         owner = []
         for fb in fblocks:
-            owner += [fb] * len(fb.cov_emas)
+            owner += [fb] * len(fb.plan_factors())
         classes = plan.classes()
         dev = next(self.target.params()).data.device
         first = fblocks[0]
+        low = [fb for fb in fblocks if fb.low_rank_active]
+        if low:
+            # the low-rank blocks first: their small inverses run beside
+            # everything else
+            pending_factor_items(low)
+            update_cov_emas_grouped(low)
+            lowrank_build(low, dev)
+            self._lr_plan_for(low).start_class(0, 1.0, False)
+            self._lr_built = True
         for c, idx in enumerate(classes):
             blocks, seen = [], set()
             for i in idx:
@@ -494,6 +558,12 @@ class KFAC(_base.GradientMethod):
             self._emas_done = False      # a pipelined exchange already did it
         else:
             update_cov_emas_grouped(fblocks)
+        low = [fb for fb in fblocks if fb.low_rank_active]
+        if low:
+            if not self._lr_built:
+                lowrank_build(low, next(self.target.params()).data.device)
+            self._lr_built = False
+            self._lr_plan_for(low).run(1.0, False)
         # one batched damped inverse per (damping, pi rule) group
         groups = {}
         for fb in fblocks:
@@ -501,13 +571,15 @@ class KFAC(_base.GradientMethod):
         done = set()
         for (damping, pi_type), group in groups.items():
             plan = self._plan_for(group)
+            if plan is None:
+                continue                 # low-rank blocks only
             after = None
             if len(groups) == 1:
                 # precondition the layers of a size class on that class's
                 # stream as soon as its inverses are done
                 owner = []
                 for fb in group:
-                    owner += [fb] * len(fb.cov_emas)
+                    owner += [fb] * len(fb.plan_factors())
                 classes = plan.classes()
 
                 def after(c, owner=owner, classes=classes):
@@ -525,7 +597,7 @@ class KFAC(_base.GradientMethod):
             diag = plan.diag
             k = 0
             for fb in group:
-                n = len(fb.cov_emas)
+                n = len(fb.plan_factors())
                 fb.set_diag_vals(diag[k:k + n])
                 k += n
         conn = [fb for fb in fblocks
@@ -544,9 +616,17 @@ class KFAC(_base.GradientMethod):
         cols = [[] for _ in range(6)]
         pg, pb, vg, vb, fused_params = [], [], [], [], []
         mom, any_fused = None, False
+        low_items = []
+        # dense blocks first, then the low-rank ones (same per-block logic)
+        blocks = [fb for fb in blocks if not fb.low_rank_active] + \
+            [fb for fb in blocks if fb.low_rank_active]
+        n_dense = sum(1 for fb in blocks if not fb.low_rank_active)
         for fb in blocks:
-            for col, a in zip(cols, fb.kfgrad_args()):
-                col.append(a)
+            if fb.low_rank_active:
+                low_items.append(fb.low_rank_item(with_grads=True))
+            else:
+                for col, a in zip(cols, fb.kfgrad_args()):
+                    col.append(a)
             gamma, beta = fb.link.gamma, fb.link.beta
             fuse = self._can_fuse(gamma) and self._can_fuse(beta)
             if fuse:
@@ -565,9 +645,21 @@ class KFAC(_base.GradientMethod):
                 pb.append(None)
                 vg.append(None)
                 vb.append(None)
-        extra = dict(param_gamma=pg, param_beta=pb, mom_gamma=vg, mom_beta=vb,
-                     lr=self.hyperparam.lr, momentum=mom) if any_fused else {}
-        ops.bn_precondition_group(*cols, **extra)
+        k = n_dense
+        extra = dict(param_gamma=pg[:k], param_beta=pb[:k], mom_gamma=vg[:k],
+                     mom_beta=vb[:k], lr=self.hyperparam.lr,
+                     momentum=mom) if any_fused else {}
+        if k:
+            ops.bn_precondition_group(*cols, **extra)
+        for j, it in enumerate(low_items):
+            if pg[k + j] is not None:
+                it.param_gamma = pg[k + j].data_ptr()
+                it.param_beta = pb[k + j].data_ptr()
+                it.mom_gamma = vg[k + j].data_ptr()
+                it.mom_beta = vb[k + j].data_ptr()
+        if low_items:
+            ops.bn_lowrank_apply(low_items, self.hyperparam.lr,
+                                 mom if mom is not None else 0.0)
         for p in fused_params:
             p._kfac_applied = True
 
@@ -670,6 +762,7 @@ class DistributedKFAC(KFAC):
         self.local_indices = local_indices
         self.local_fblocks = [self.fblocks[i] for i in local_indices]
         setattr(self.comm, 'indices', indices)
+        self._set_low_rank(local_size, local_rank, set(local_indices))
         return self
 
     def update(self, lossfun=None, *args, **kwargs):
@@ -712,13 +805,13 @@ class DistributedKFAC(KFAC):
                 len({(fb.damping, fb._pi_type) for fb in self.fblocks}) == 1)
 
     def _pipelined_exchange(self):
-        plan = self._plan_for(self.local_fblocks)
-        bounds = plan.bounds
+        plan = self._plan_for(self.local_fblocks)   # None: low-rank only
+        bounds = ops.class_bounds()
+        class_keys = plan.class_keys if plan is not None else []
 
         def key_of(fb):
             # covs exist on every rank from the first full update on
-            d = max(int(c.shape[0]) for c in fb.covs)
-            return sum(d > b for b in bounds)
+            return sum(fb.max_side() > b for b in bounds)
         keys = [key_of(fb) for fb in self.fblocks]
         dev = next(self.target.params()).data.device
         main = torch.cuda.current_stream()
@@ -743,14 +836,17 @@ class DistributedKFAC(KFAC):
                     [[i for i in ix if i in member_set] for ix in self.indices],
                     lambda block: block.extract_for_reduce_scatter_v())
                 self.comm.reduce_scatter_v_arrays(arrays)
-                update_cov_emas_grouped(
-                    [self.fblocks[i] for i in members if i in local])
-                if n + 1 < len(order) and key in plan.class_keys:
-                    plan.start_class(plan.class_keys.index(key), first.damping,
+                mine = [self.fblocks[i] for i in members if i in local]
+                update_cov_emas_grouped(mine)
+                # every rank's rows have arrived in the owner's slot
+                lowrank_build([fb for fb in mine if fb.low_rank_active], dev)
+                if n + 1 < len(order) and key in class_keys:
+                    plan.start_class(class_keys.index(key), first.damping,
                                      first._pi_type == PI_TYPE_TRACENORM)
         done = torch.cuda.Event()
         done.record(side)
         main.wait_event(done)
+        self._lr_built = True
         for fb in self.fblocks:
             fb._keep_x = fb._keep_gy = None
 

@@ -132,6 +132,43 @@ for pic, early, own, cname, decay, acc in (
                                       model.named_parameters()):
             err = float((p1 - p2).norm() / p1.norm())
             assert err < 2e-3, (pic, early, own, cname, decay, acc, n1, err)
+# BatchNormalization blocks in their low-rank form (every rank's per-sample
+# gradient rows travel to the owner instead of a dense factor) against the
+# dense form on the same ranks.  (A single-process run is no reference here:
+# batch statistics are per rank.)
+def make_bn():
+    torch.manual_seed(9)
+    return nn.Sequential(nn.Conv2d(3, 64, 3, 1, 1, bias=False),
+                         nn.BatchNorm2d(64), nn.ReLU(),
+                         nn.Conv2d(64, 64, 3, 2, 1, bias=False),
+                         nn.BatchNorm2d(64), nn.ReLU(),
+                         nn.AdaptiveAvgPool2d(1), nn.Flatten(),
+                         nn.Linear(64, 5)).cuda()
+
+for own, cname, decay in (('balanced', 'peer_memory', 0.9),
+                          ('reference', 'pure_nccl', 1.0)):
+    finals = []
+    for low in (True, False):
+        model = make_bn()
+        opt = ck.DistributedKFAC(comms[cname], lr=0.02, momentum=0.9,
+                                 cov_ema_decay=decay, damping=1e-2,
+                                 ownership=own, bn_low_rank=low)
+        opt.setup(model)
+        lossfun = lambda a, b: F.cross_entropy(model(a), b)
+        gb = torch.Generator().manual_seed(50 + rank)
+        for step in range(11):
+            xb = torch.randn(4, 3, 8, 8, generator=gb).cuda()
+            tb = torch.randint(0, 5, (4,), generator=gb).cuda()
+            opt.update(lossfun, xb, tb)
+        bn = [fb for fb in opt.fblocks if hasattr(fb.link, 'gamma')]
+        assert len(bn) == 2 and all(fb.low_rank_active == low for fb in bn)
+        flat = torch.cat([p.detach().reshape(-1) for p in model.parameters()])
+        other = [torch.empty_like(flat) for _ in range(world)]
+        dist.all_gather(other, flat)
+        assert all(torch.equal(other[0], o) for o in other), 'ranks diverged'
+        finals.append(flat)
+    err = float((finals[0] - finals[1]).norm() / finals[1].norm())
+    assert err < 1e-3, (own, cname, decay, err)
 dist.barrier()
 if rank == 0:
     print('DISTRIBUTED_OK')

@@ -168,6 +168,65 @@ def test_kfac_convnet_with_bn_blocks_matches_oracle():
         assert fb.check_nan() is False
 
 
+class WideBNNet(nn.Module):
+    def __init__(self, c=64):
+        super(WideBNNet, self).__init__()
+        self.conv1 = nn.Conv2d(3, c, 3, 1, 1, bias=False)
+        self.bn1 = nn.BatchNorm2d(c)
+        self.conv2 = nn.Conv2d(c, c, 3, 2, 1, bias=False)
+        self.bn2 = nn.BatchNorm2d(c)
+        self.fc = nn.Linear(c, 5)
+
+    def forward(self, x):
+        h = F.relu(self.bn1(self.conv1(x)))
+        h = F.relu(self.bn2(self.conv2(h)))
+        return self.fc(F.adaptive_avg_pool2d(h, 1).flatten(1))
+
+
+@pytest.mark.parametrize('decay', [0.9, 1.0])
+def test_bn_low_rank_form_gives_the_dense_trajectory(decay):
+    """BatchNormalization blocks kept as stored per-sample gradient rows
+    (8 steps x 4 samples <= 64 channels at decay 0.9) against the dense
+    2C x 2C factor of the reference, over more steps than the history ring
+    has slots; then a batch-size change, after which the block must carry on
+    with the dense factor formed from its rows."""
+    import chainerkfac_b200 as ck
+    from chainerkfac_b200.optimizers.fisher_blocks.normalizations \
+        .batch_normalization import FisherBlockBatchNormalization as BNB
+    runs = {}
+    for low in (True, False):
+        torch.manual_seed(5)
+        model = WideBNNet().cuda()
+        opt = ck.KFAC(lr=0.02, momentum=0.9, cov_ema_decay=decay,
+                      damping=1e-2, bn_low_rank=low)
+        opt.setup(model)
+        bn = [fb for fb in opt.fblocks if isinstance(fb, BNB)]
+        assert len(bn) == 2
+        g = torch.Generator(device='cuda').manual_seed(11)
+        lossfun = lambda a, b: F.cross_entropy(model(a), b)
+        snaps = []
+        for step in range(14):
+            n = 4 if step < 11 else 6
+            x = torch.randn(n, 3, 8, 8, device='cuda', generator=g)
+            t = torch.randint(0, 5, (n,), device='cuda', generator=g)
+            opt.update(lossfun, x, t)
+            if step == 10:
+                assert all(fb.low_rank_active == low for fb in bn)
+                if low:
+                    assert all(fb.invs is None for fb in bn)
+                snaps.append([host(fb.cov_emas[0]) for fb in bn])
+                snaps.append([host(p.data) for p in model.parameters()])
+        # after the batch-size change every block is dense
+        assert not any(fb.low_rank_active for fb in bn)
+        assert all(fb.check_nan() is False for fb in bn)
+        snaps.append([host(fb.cov_emas[0]) for fb in bn])
+        snaps.append([host(p.data) for p in model.parameters()])
+        runs[low] = snaps
+    for k, tol in ((0, 1e-5), (1, 1e-3), (2, 1e-5), (3, 1e-3)):
+        for a, b in zip(runs[True][k], runs[False][k]):
+            assert rel(a, b) < tol, (k, rel(a, b))
+
+
 def test_running_average_over_steps_stays_undamped():
     import chainerkfac_b200 as ck
     torch.manual_seed(1)
