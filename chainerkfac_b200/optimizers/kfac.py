@@ -64,6 +64,9 @@ class KFACHook(object):
         self.fblocks = fblocks
         self._handles = []
         self._by_array = None
+        # optional observers fb -> None, called after the block's own hook
+        self.on_forward = None
+        self.on_backward = None
 
     def _lookup(self, func, in_data, out_grad_data=None):
         if self._by_array is None or len(self._by_array) != len(self.fblocks):
@@ -83,11 +86,15 @@ class KFACHook(object):
         fblock = self._lookup(func, in_data)
         if fblock is not None:
             fblock.forward_postprocess(func, in_data)
+            if self.on_forward is not None:
+                self.on_forward(fblock)
 
     def backward_preprocess(self, func, in_data, out_grad_data):
         fblock = self._lookup(func, in_data, out_grad_data)
         if fblock is not None:
             fblock.backward_preprocess(func, in_data, out_grad_data)
+            if self.on_backward is not None:
+                self.on_backward(fblock)
 
     def _make_forward_hook(self, fblock):
         link = fblock.link
@@ -274,6 +281,13 @@ class KFAC(_base.GradientMethod):
         self._plans = {}
         self._lr_plans = {}
         self._lr_built = False       # a pipelined path already built M
+        # start the inverses of a size class during the backward pass, as
+        # soon as the output gradients of all its layers exist (the large
+        # classes sit in the last layers, whose gradients come first): their
+        # long serial chains then run beside the rest of the backward pass
+        self.eager_inverses = True
+        self._eager = None
+        self._eager_stream = None
         self.observation = {}
 
     lr = _base.HyperparameterProxy('lr')
@@ -327,6 +341,7 @@ class KFAC(_base.GradientMethod):
     def _forward_backward(self, lossfun, args, kwargs, after_forward=None):
         for fb in self.fblocks:
             fb.deferred = self.group_factors
+        self._eager_begin()
         with self.kfhook:
             loss = lossfun(*args, **kwargs)
             if after_forward is not None:
@@ -339,6 +354,7 @@ class KFAC(_base.GradientMethod):
                 loss.backward(torch.full_like(loss, self._loss_scale))
             else:
                 loss.backward()
+        self.kfhook.on_forward = self.kfhook.on_backward = None
         # what Chainer's backward(loss_scale=) leaves on every parameter: the
         # update rules divide the (scaled) gradients by it
         for param in self.target.params():
@@ -348,10 +364,89 @@ class KFAC(_base.GradientMethod):
                 fb.resolve_form()
         # with a valid inverse plan the factor build is pipelined with the
         # inverses inside update_kfgrads; otherwise build everything now
-        self._factors_pending = self._pipeline_ready()
+        # (a class already started during the backward pass keeps the step
+        # on that path)
+        self._factors_pending = self._pipeline_ready() or bool(
+            self._eager is not None and self._eager['started'])
         if not self._factors_pending:
+            self._eager = None
             self.flush_factors()
         self.loss = loss.detach()
+
+    # -- size classes started during the backward pass -----------------------
+    def _eager_begin(self):
+        self._eager = None
+        if type(self) is not KFAC or not self.eager_inverses or \
+                not torch.cuda.is_available() or not self._pipeline_ready():
+            return
+        plan = self._plans[tuple(id(fb) for fb in self.fblocks)][0]
+        owner = [fb for fb in self.fblocks for _ in fb.plan_factors()]
+        blocks_of, cls = [], {}
+        # the last class is built and started after the backward pass
+        for c, idx in enumerate(plan.classes()[:-1]):
+            blocks = []
+            for i in idx:
+                if id(owner[i]) not in cls:
+                    cls[id(owner[i])] = c
+                    blocks.append(owner[i])
+            blocks_of.append(blocks)
+        if not blocks_of:
+            return
+        if self._eager_stream is None:
+            self._eager_stream = torch.cuda.Stream(priority=-1)
+        self._eager = dict(
+            plan=plan, blocks=blocks_of, cls=cls, calls={},
+            waiting=[{id(fb) for fb in b} for b in blocks_of],
+            started={}, ema_done=set(), keep=[])
+        self.kfhook.on_forward = self._eager_forward
+        self.kfhook.on_backward = self._eager_backward
+
+    def _eager_forward(self, fb):
+        calls = self._eager['calls']
+        calls[id(fb)] = calls.get(id(fb), 0) + 1
+
+    def _eager_backward(self, fb):
+        e = self._eager
+        c = e['cls'].get(id(fb))
+        if c is None or c in e['started']:
+            return
+        if e['calls'].get(id(fb), 0) != 1:
+            return      # a layer called twice: its class waits for the end
+        if isinstance(fb, FB.FisherBlockBatchNormalization):
+            dense = not fb.low_rank_active
+            fb.resolve_form()
+            if dense == fb.low_rank_active:
+                return  # the block changed form: no early start
+        e['waiting'][c].discard(id(fb))
+        if e['waiting'][c]:
+            return
+        # every layer of class c has its output gradient: build its factors
+        # and running averages on a side stream and start its inverses
+        blocks = e['blocks'][c]
+        first = blocks[0]
+        cur = torch.cuda.current_stream()
+        ready = torch.cuda.Event()
+        ready.record(cur)
+        side = self._eager_stream
+        side.wait_event(ready)
+        with torch.cuda.stream(side):
+            items = pending_factor_items(blocks)
+            # the activations and gradients behind the items stay referenced
+            # until the main stream has waited for this build
+            e['keep'].append(items)
+            if items:
+                ops.factor_group(items, first.link.W.data.device
+                                 if hasattr(first.link, 'W')
+                                 else first.link.gamma.data.device)
+            update_cov_emas_grouped(blocks)
+            e['plan'].start_class(c, first.damping,
+                                  first._pi_type == PI_TYPE_TRACENORM)
+            built = torch.cuda.Event()
+            built.record(side)
+        e['started'][c] = built
+        e['ema_done'].update(id(fb) for fb in blocks)
+        self.observation['classes_started_in_backward'] = \
+            self.observation.get('classes_started_in_backward', 0) + 1
 
     def update(self, lossfun=None, *args, **kwargs):
         if lossfun is not None:
@@ -521,6 +616,18 @@ class KFAC(_base.GradientMethod):
         classes = plan.classes()
         dev = next(self.target.params()).data.device
         first = fblocks[0]
+        eager, self._eager = self._eager, None
+        started, ema_done = {}, set()
+        if eager is not None:
+            # classes started during the backward pass: the builds on the
+            # side stream come before anything queued here (shared build
+            # workspaces; the hook arguments are released below)
+            main = torch.cuda.current_stream()
+            for ev in eager['started'].values():
+                main.wait_event(ev)
+            ema_done = eager['ema_done']
+            if eager['plan'] is plan:
+                started = eager['started']
         low = [fb for fb in fblocks if fb.low_rank_active]
         if low:
             # the low-rank blocks first: their small inverses run beside
@@ -531,11 +638,14 @@ class KFAC(_base.GradientMethod):
             self._lr_plan_for(low).start_class(0, 1.0, False)
             self._lr_built = True
         for c, idx in enumerate(classes):
+            if c in started:
+                continue
             blocks, seen = [], set()
             for i in idx:
                 if id(owner[i]) not in seen:
                     seen.add(id(owner[i]))
-                    blocks.append(owner[i])
+                    if id(owner[i]) not in ema_done:
+                        blocks.append(owner[i])
             items = pending_factor_items(blocks)
             if items:
                 ops.factor_group(items, dev)
@@ -598,7 +708,8 @@ class KFAC(_base.GradientMethod):
             k = 0
             for fb in group:
                 n = len(fb.plan_factors())
-                fb.set_diag_vals(diag[k:k + n])
+                if n:
+                    fb.set_diag_vals(diag[k:k + n])
                 k += n
         conn = [fb for fb in fblocks
                 if isinstance(fb, FB.FisherBlockConnection) and

@@ -222,9 +222,34 @@ def test_bn_low_rank_form_gives_the_dense_trajectory(decay):
         snaps.append([host(fb.cov_emas[0]) for fb in bn])
         snaps.append([host(p.data) for p in model.parameters()])
         runs[low] = snaps
-    for k, tol in ((0, 1e-5), (1, 1e-3), (2, 1e-5), (3, 1e-3)):
+    for k, tol in ((0, 1e-4), (1, 1e-3), (2, 1e-4), (3, 1e-3)):
         for a, b in zip(runs[True][k], runs[False][k]):
             assert rel(a, b) < tol, (k, rel(a, b))
+
+
+def test_classes_started_during_backward_give_the_same_steps(monkeypatch):
+    """With several size classes the optimizer starts the inverses of the
+    large classes from the backward hooks; the result must not depend on
+    that schedule."""
+    import chainerkfac_b200 as ck
+    monkeypatch.setenv('KFAC_CLASS_BOUNDS', '20,60')
+    finals = {}
+    for eager in (True, False):
+        torch.manual_seed(3)
+        model = SmallNet().cuda()       # sides 28/8, 72/12, 16, 24, 13/7
+        opt = ck.KFAC(lr=0.05, momentum=0.9, cov_ema_decay=0.9, damping=1e-2)
+        opt.eager_inverses = eager
+        opt.setup(model)
+        g = torch.Generator(device='cuda').manual_seed(4)
+        for _ in range(5):
+            x = torch.randn(6, 3, 10, 10, device='cuda', generator=g)
+            t = torch.randint(0, 7, (6,), device='cuda', generator=g)
+            opt.update(lambda a, b: F.cross_entropy(model(a), b), x, t)
+        started = opt.observation.get('classes_started_in_backward', 0)
+        assert (started > 0) == eager
+        finals[eager] = [host(p.data) for p in model.parameters()]
+    for a, b in zip(finals[True], finals[False]):
+        assert rel(a, b) < 1e-6
 
 
 def test_running_average_over_steps_stays_undamped():
