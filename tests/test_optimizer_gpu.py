@@ -184,47 +184,52 @@ class WideBNNet(nn.Module):
 
 
 @pytest.mark.parametrize('decay', [0.9, 1.0])
-def test_bn_low_rank_form_gives_the_dense_trajectory(decay):
+def test_bn_low_rank_form_gives_the_dense_steps(decay):
     """BatchNormalization blocks kept as stored per-sample gradient rows
     (8 steps x 4 samples <= 64 channels at decay 0.9) against the dense
-    2C x 2C factor of the reference, over more steps than the history ring
-    has slots; then a batch-size change, after which the block must carry on
-    with the dense factor formed from its rows."""
+    2C x 2C factor of the reference, step by step from the same weights, over
+    more steps than the history ring has slots; then a batch-size change,
+    after which the block must carry on with the dense factor formed from
+    its rows."""
     import chainerkfac_b200 as ck
     from chainerkfac_b200.optimizers.fisher_blocks.normalizations \
         .batch_normalization import FisherBlockBatchNormalization as BNB
-    runs = {}
+    models, opts, bns = [], [], []
     for low in (True, False):
         torch.manual_seed(5)
         model = WideBNNet().cuda()
         opt = ck.KFAC(lr=0.02, momentum=0.9, cov_ema_decay=decay,
                       damping=1e-2, bn_low_rank=low)
         opt.setup(model)
-        bn = [fb for fb in opt.fblocks if isinstance(fb, BNB)]
-        assert len(bn) == 2
-        g = torch.Generator(device='cuda').manual_seed(11)
-        lossfun = lambda a, b: F.cross_entropy(model(a), b)
-        snaps = []
-        for step in range(14):
-            n = 4 if step < 11 else 6
-            x = torch.randn(n, 3, 8, 8, device='cuda', generator=g)
-            t = torch.randint(0, 5, (n,), device='cuda', generator=g)
-            opt.update(lossfun, x, t)
-            if step == 10:
-                assert all(fb.low_rank_active == low for fb in bn)
-                if low:
-                    assert all(fb.invs is None for fb in bn)
-                snaps.append([host(fb.cov_emas[0]) for fb in bn])
-                snaps.append([host(p.data) for p in model.parameters()])
-        # after the batch-size change every block is dense
-        assert not any(fb.low_rank_active for fb in bn)
-        assert all(fb.check_nan() is False for fb in bn)
-        snaps.append([host(fb.cov_emas[0]) for fb in bn])
-        snaps.append([host(p.data) for p in model.parameters()])
-        runs[low] = snaps
-    for k, tol in ((0, 1e-4), (1, 1e-3), (2, 1e-4), (3, 1e-3)):
-        for a, b in zip(runs[True][k], runs[False][k]):
-            assert rel(a, b) < tol, (k, rel(a, b))
+        models.append(model)
+        opts.append(opt)
+        bns.append([fb for fb in opt.fblocks if isinstance(fb, BNB)])
+        assert len(bns[-1]) == 2
+    g = torch.Generator(device='cuda').manual_seed(11)
+    for step in range(14):
+        n = 4 if step < 11 else 6
+        x = torch.randn(n, 3, 8, 8, device='cuda', generator=g)
+        t = torch.randint(0, 5, (n,), device='cuda', generator=g)
+        # the dense run restarts every step from the low-rank run's weights,
+        # batch statistics and velocities: differences do not compound
+        models[1].load_state_dict(models[0].state_dict())
+        for p0, p1 in zip(opts[0].target.params(), opts[1].target.params()):
+            p1.update_rule.velocity(p1).copy_(p0.update_rule.velocity(p0))
+        for model, opt in zip(models, opts):
+            opt.update(lambda a, b, m=model: F.cross_entropy(m(a), b), x, t)
+        assert all(fb.low_rank_active == (step < 11) for fb in bns[0])
+        assert not any(fb.low_rank_active for fb in bns[1])
+        if step < 11:
+            assert all(fb.invs is None for fb in bns[0])
+        for f0, f1 in zip(bns[0], bns[1]):
+            assert rel(host(f0.cov_emas[0]), host(f1.cov_emas[0])) < 1e-4, step
+            for nm in ('gamma', 'beta'):
+                a = host(getattr(f0.link, nm).kfgrad)
+                b = host(getattr(f1.link, nm).kfgrad)
+                assert rel(a, b) < KFGRAD_TOL, (step, nm, rel(a, b))
+        for p0, p1 in zip(models[0].parameters(), models[1].parameters()):
+            assert rel(host(p0.data), host(p1.data)) < 1e-5, step
+    assert all(fb.check_nan() is False for fb in bns[0] + bns[1])
 
 
 def test_classes_started_during_backward_give_the_same_steps(monkeypatch):
