@@ -73,6 +73,7 @@ class Link(object):
         self.module = module
         self._params = []
         self._children = []
+        self._flat_params = None     # params() of the finished tree
         for cname, tname in self.param_names:
             tp = getattr(module, tname, None)
             p = None if tp is None else Parameter(tp, cname)
@@ -90,6 +91,7 @@ class Link(object):
 
     def add_child(self, name, link):
         self._children.append((name, link))
+        self._flat_params = None
 
     def namedlinks(self, skipself=False, _prefix=''):
         if not skipself:
@@ -108,8 +110,10 @@ class Link(object):
                 yield item
 
     def params(self, include_uninit=True):
-        for _, p in self.namedparams(include_uninit):
-            yield p
+        # the tree is built once (wrap), bottom-up: the flat list is kept
+        if self._flat_params is None:
+            self._flat_params = [p for _, p in self.namedparams()]
+        return iter(self._flat_params)
 
     def links(self, skipself=False):
         for _, l in self.namedlinks(skipself):

@@ -216,7 +216,7 @@ def factor_group(items, device):
                                      _stream()), 'kfac_factor_group')
 
 
-def bn_item(x, gy, eps, scale, out=None):
+def bn_item(x, gy, eps, scale, out=None, stats=None):
     """Item of ``bn_sample_grads_group`` for one BatchNormalization layer:
     ``x`` / ``gy`` are (n, c) or (n, c, h, w) tensors, NCHW-contiguous or
     channels-last (both must have the same layout)."""
@@ -240,7 +240,8 @@ def bn_item(x, gy, eps, scale, out=None):
         out = torch.empty((n, 2 * c), dtype=torch.float32, device=x.device)
     it = _lib.BnItem()
     it.x, it.gy, it.out = x.data_ptr(), gy.data_ptr(), out.data_ptr()
-    stats = torch.empty(2 * c, dtype=torch.float32, device=x.device)
+    if stats is None or stats.numel() != 2 * c or stats.device != x.device:
+        stats = torch.empty(2 * c, dtype=torch.float32, device=x.device)
     it.stats = stats.data_ptr()
     it.n, it.c, it.hw, it.layout = n, c, hw, layout
     it.eps, it.scale = eps, scale

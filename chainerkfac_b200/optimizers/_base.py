@@ -122,6 +122,6 @@ class GradientMethod(object):
         self._use_cleargrads = use
 
     def reallocate_cleared_grads(self):
-        for _, param in self.target.namedparams(False):
+        for param in self.target.params(False):
             if param.grad is None:
                 param.grad = torch.zeros_like(param.data)

@@ -173,19 +173,31 @@ class FisherBlockBatchNormalization(FisherBlock):
 
     def low_rank_item(self, with_grads=False):
         """struct kfac_bn_lowrank_item of this block (``with_grads``: the
-        fields kfac_bn_lowrank_apply needs as well)."""
+        fields kfac_bn_lowrank_apply needs as well).  One struct per block,
+        refreshed in place: the history, its scaled copy and the inverse keep
+        their addresses."""
         st = self._lr
+        it = st.get('item')
+        if it is None:
+            it = st['item'] = ops.bn_lowrank_item(
+                st['hist'], st['Hs'], st['c'], st['rows'],
+                [0.0] * st['slots'], 0.0, 0.0, st['Minv'])
         fac = self._row_factor()
+        for k, w in enumerate(st['w']):
+            it.slot_weight[k] = w * fac
         l2g = getattr(self.link.gamma, 'l2_coef', 0.0) or 0.0
         l2b = getattr(self.link.beta, 'l2_coef', 0.0) or 0.0
-        dg = max(l2g, self.damping) * float(self.stab_coeff)
-        db = max(l2b, self.damping) * float(self.stab_coeff)
-        extra = ()
+        it.damp_gamma = max(l2g, self.damping) * float(self.stab_coeff)
+        it.damp_beta = max(l2b, self.damping) * float(self.stab_coeff)
         if with_grads:
             a = self.kfgrad_args(low_rank=True)
-            extra = (st['Minv'], a[1], a[2], a[3], a[4], a[5])
-        return ops.bn_lowrank_item(st['hist'], st['Hs'], st['c'], st['rows'],
-                                   [w * fac for w in st['w']], dg, db, *extra)
+            it.grad_gamma, it.grad_beta = a[1].data_ptr(), a[2].data_ptr()
+            it.kf_gamma, it.kf_beta = a[3].data_ptr(), a[4].data_ptr()
+            it.nan_flag = a[5].data_ptr()
+            it.param_gamma = it.param_beta = None     # no fused update
+            it.mom_gamma = it.mom_beta = None
+            it._grads_keep = a
+        return it
 
     def low_rank_matrix_item(self):
         """Grouped-build item M = Hs Hs^T."""
@@ -257,7 +269,9 @@ class FisherBlockBatchNormalization(FisherBlock):
 
     def pending_item(self):
         """Item of ``ops.bn_sample_grads_group`` for the pending hook
-        arguments (None if there are none)."""
+        arguments (None if there are none).  The item of the last step is
+        used again when the arrays have the same addresses and geometry (see
+        ``FisherBlockConnection._memo_item``)."""
         pend = getattr(self, '_pending', None)
         if pend is None:
             return None
@@ -272,10 +286,25 @@ class FisherBlockBatchNormalization(FisherBlock):
                 slot.zero_()      # the other ranks' rows arrive by the sum
             out = slot[self.low_rank_rank * n:(self.low_rank_rank + 1) * n]
             self.covs = None
-        self._grads_item = ops.bn_item(
-            x, gy, float(self.link.eps), self.gy_scale(n), out)
-        self._grads = self._grads_item.result
-        return self._grads_item
+        key = (x.data_ptr(), gy.data_ptr(), x.shape, x.stride(), gy.stride(),
+               None if out is None else out.data_ptr(), self._loss_scale)
+        memo = getattr(self, '_item_memo', None)
+        self._keep_x, self._keep_gy = x, gy
+        if memo is not None and memo[0] == key:
+            it = memo[1]
+        else:
+            it = ops.bn_item(x, gy, float(self.link.eps), self.gy_scale(n),
+                             out, getattr(self, '_stats', None))
+            self._stats = it._keep[3]
+            self._item_memo = None
+            if it.x == x.data_ptr() and it.gy == gy.data_ptr():
+                it._keep = it._keep[2:]   # output and statistics only
+                self._item_memo = (
+                    (x.data_ptr(), gy.data_ptr(), x.shape, x.stride(),
+                     gy.stride(), it.result.data_ptr(), self._loss_scale), it)
+        self._grads_item = it
+        self._grads = it.result
+        return it
 
     def factor_item(self):
         """Grouped-build item F = grads^T grads / n for the gradients of the

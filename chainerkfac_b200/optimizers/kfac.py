@@ -319,7 +319,7 @@ class KFAC(_base.GradientMethod):
                 fb.keeps_history = owned is None or i in owned
 
     def reallocate_cleared_grads(self):
-        for name, param in self.target.namedparams(include_uninit=False):
+        for param in self.target.params(include_uninit=False):
             if hasattr(param, 'kfgrad') and param.kfgrad is None:
                 param.kfgrad = torch.zeros_like(param.data)
         super(KFAC, self).reallocate_cleared_grads()
