@@ -150,13 +150,14 @@ static int noalloc_scratch_address(float** out) {
 
 static int run_factor(const Operand& X, long long rows, int d, float alpha,
                       float beta, float* out, void* workspace,
-                      size_t workspace_bytes, cudaStream_t stream) {
+                      size_t workspace_bytes, cudaStream_t stream,
+                      bool staged = true) {
   KFAC_REQUIRE(out != nullptr && X.base != nullptr, "factor: null pointer");
   KFAC_REQUIRE(rows > 0 && d > 0, "factor: rows=%lld d=%d must be positive",
                rows, d);
   if (engine() == 1)
     return run_factor_tc(X, rows, d, alpha, beta, out, workspace,
-                         workspace_bytes, stream);
+                         workspace_bytes, stream, staged);
   FactorSplit s = factor_split(rows, d);
   float* partial = nullptr;
   if (s.splits > 1) {
@@ -1019,7 +1020,10 @@ extern "C" int kfac_factor_dense_noalloc(const float* x, int64_t rows,
   KFAC_REQUIRE(ld >= d_in, "factor_dense_noalloc: ld=%lld < d_in=%d",
                (long long)ld, d_in);
   const int d = d_in + (add_ones_col ? 1 : 0);
-  size_t need = kfac_factor_workspace_bytes(rows, d);
+  // (no staging pass here: its planes would not fit the built-in scratch and
+  // its tensor maps travel through an allocated table)
+  size_t need = engine() == 1 ? tc_factor_workspace_bytes(rows, d, false)
+                              : kfac_factor_workspace_bytes(rows, d);
   if (need > kNoAllocBytes)
     return fail(KFAC_ERR_WORKSPACE,
                 "factor_dense_noalloc: rows=%lld d=%d needs %zu bytes of "
@@ -1034,7 +1038,7 @@ extern "C" int kfac_factor_dense_noalloc(const float* x, int64_t rows,
   // Every partial tile is written in full before it is read, so nothing in
   // the shared scratch has to be cleared between calls.
   return run_factor(X, rows, d, alpha, beta, out, scratch, kNoAllocBytes,
-                    (cudaStream_t)stream);
+                    (cudaStream_t)stream, false);
 }
 
 // ------------------------------------------------------------ grouped build

@@ -260,6 +260,10 @@ struct GemmDesc {
   const int* gate;         // if set and *gate == 0 the problem is skipped
   float* C2;               // if set, C's new values are stored here as well
                            // (same row pitch; plain epilogue only)
+  // factor builds from staged operands: tensor maps (device memory) of the
+  // hi and lo bf16 planes of X^T, see stage.cu
+  const void* tmap_hi;
+  const void* tmap_lo;
 };
 
 int launch_grouped_gemm(const GemmDesc* descs_dev, int ndesc, int total_tiles,
@@ -275,11 +279,12 @@ int launch_tc_grouped(const GemmDesc* descs_dev, int ndesc, int total_tiles,
                       float lr, float momentum, bool tails,
                       cudaStream_t stream);
 bool tc_desc_has_tails(const GemmDesc& g);
-size_t tc_factor_workspace_bytes(long long rows, int d);
+size_t tc_factor_workspace_bytes(long long rows, int d, bool staged = true);
 size_t tc_pad_bytes(const Operand& X, int n, int nhwc = 0);
 int run_factor_tc(const Operand& X, long long rows, int d, float alpha,
                   float beta, float* out, void* workspace,
-                  size_t workspace_bytes, cudaStream_t stream);
+                  size_t workspace_bytes, cudaStream_t stream,
+                  bool staged = true);
 struct FactorJob {      // one factor of a grouped build
   Operand X;
   long long rows;
@@ -289,9 +294,16 @@ struct FactorJob {      // one factor of a grouped build
   float alpha, beta;
   float* out;
 };
-size_t tc_factor_group_workspace_bytes(int count, const FactorJob* jobs);
+size_t tc_factor_group_workspace_bytes(int count, const FactorJob* jobs,
+                                       bool staged = true);
+// Staging pass (stage.cu): bytes of both bf16 planes of one operand; staging
+// of a group into `ws` with two tensor maps per job written to `tmaps`.
+size_t tc_stage_bytes(long long rows, int d);
+int tc_stage_group(int count, const FactorJob* jobs, char* ws, void* tmaps,
+                   cudaStream_t stream);
 int run_factor_group_tc(int count, const FactorJob* jobs, void* workspace,
-                        size_t workspace_bytes, cudaStream_t stream);
+                        size_t workspace_bytes, cudaStream_t stream,
+                        bool staged = true);
 
 // Host helper: fill tile counts of a descriptor and return its tile count.
 inline int gemm_desc_tiles(GemmDesc& g) {

@@ -812,7 +812,21 @@ __device__ __forceinline__ void pk_pair(int t, int& Bi, int& Bj) {
   Bj = t - a * (a + 1) / 2;
 }
 
-template <bool IM2COL, bool TAILS>
+// STAGED: the operand comes from the bf16 planes of the staging pass through
+// TMA: one thread issues, per k-block, a 32 k x 256 row box of each plane for
+// the B rows (and the A rows off the diagonal) straight into the stage, in
+// the 64-byte-swizzled K-major layout; rows past d and k past K arrive as
+// zeros.  The other producer warps wait for the epilogue.
+__device__ __forceinline__ void tma_load_2d(unsigned dst, const void* tmap,
+                                            int x, int y, unsigned bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::"
+      "complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+
+template <bool IM2COL, bool TAILS, bool STAGED = false>
 __global__ void __launch_bounds__(PK_THREADS, 1)
 tc_pair_kernel(const GemmDesc* __restrict__ descs, int ndesc,
                const __grid_constant__ GemmDesc inline_desc) {
@@ -842,7 +856,7 @@ tc_pair_kernel(const GemmDesc* __restrict__ descs, int ndesc,
   }
   if (tid == 0) {
     for (int s = 0; s < PK_STAGES; ++s) {
-      mbar_init(&ctl->full[s], PK_PWARPS);
+      mbar_init(&ctl->full[s], STAGED ? 1 : PK_PWARPS);
       mbar_init(&ctl->empty[s], 1);
     }
     mbar_init(&ctl->accum, 1);
@@ -863,7 +877,7 @@ tc_pair_kernel(const GemmDesc* __restrict__ descs, int ndesc,
 
   const GemmDesc& g = ctl->desc;
   const unsigned tmem = ctl->tmem_base;
-  const int nblk = (g.tiles_m + 1) >> 1;            // 256-row blocks
+  const int nblk = (g.M + PK_ROWS - 1) / PK_ROWS;   // 256-row blocks
   const int npairs = nblk * (nblk + 1) / 2;
   int lt = tile - g.tile_begin, split = 0;
   if (g.splits > 1) {
@@ -885,7 +899,38 @@ tc_pair_kernel(const GemmDesc* __restrict__ descs, int ndesc,
   }
   const int nkb = kend > kbeg ? (int)((kend - kbeg + PK_BK - 1) / PK_BK) : 0;
 
-  if (warp < PK_PWARPS) {
+  if (STAGED && warp < PK_PWARPS) {
+    // ===================== TMA producer =====================
+    if (tid == 0) {
+      // the tensor maps were written to device memory by a copy that
+      // precedes this launch in the stream
+      asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;"
+                   ::"l"(g.tmap_hi) : "memory");
+      asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;"
+                   ::"l"(g.tmap_lo) : "memory");
+      const unsigned bytes = (share ? 2u : 4u) * PK_TILE_BYTES;
+      for (int kb = 0; kb < nkb; ++kb) {
+        const int s = kb % PK_STAGES;
+        if (kb >= PK_STAGES) {
+          if (!mbar_wait(&ctl->empty[s], ((kb / PK_STAGES) - 1) & 1,
+                         &ctl->abort_flag))
+            break;
+        }
+        const unsigned bar = smem_u32(&ctl->full[s]);
+        asm volatile(
+            "mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;"
+            ::"r"(bar), "r"(bytes) : "memory");
+        const unsigned st = smem_u32(smem + s * PK_STAGE_BYTES);
+        const int k0 = (int)kbeg + kb * PK_BK;
+        tma_load_2d(st + PK_TILE_BYTES, g.tmap_hi, k0, n0, bar);
+        tma_load_2d(st + PK_LO_OFF + PK_TILE_BYTES, g.tmap_lo, k0, n0, bar);
+        if (!share) {
+          tma_load_2d(st, g.tmap_hi, k0, m0, bar);
+          tma_load_2d(st + PK_LO_OFF, g.tmap_lo, k0, m0, bar);
+        }
+      }
+    }
+  } else if (warp < PK_PWARPS) {
     // ===================== producers =====================
     const Operand X = g.A;                          // A and B are the same
     if (IM2COL) {
@@ -1209,6 +1254,11 @@ tc_pair_kernel(const GemmDesc* __restrict__ descs, int ndesc,
       asm volatile("bar.sync 1, %0;" ::"r"(PK_PRODUCERS) : "memory");
     }
   }
+  if (STAGED && tid == 0 && ctl->abort_flag != 0) {
+    // a wait ran out: give the copies already issued time to land before
+    // the shared memory is handed back (bounded: 64 us)
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == PK_PWARPS) {
@@ -1381,6 +1431,9 @@ int tc_prepare() {
     KFAC_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<false, true, TC_PW_STRIDED>,
                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    TC_SMEM_BYTES));
+    KFAC_CUDA(cudaFuncSetAttribute(tc_pair_kernel<false, false, true>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   PK_SMEM_BYTES));
     KFAC_CUDA(cudaFuncSetAttribute(tc_pair_kernel<false, false>,
                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    PK_SMEM_BYTES));
@@ -1502,10 +1555,23 @@ static TcFactorSplit tc_factor_split(long long rows, int d) {
   return tc_split_for(rows, d, chunk * tc_block_cost(d));
 }
 
-size_t tc_factor_workspace_bytes(long long rows, int d) {
+// Factor builds read their operands from the staged bf16 planes through TMA
+// (stage.cu) unless KFAC_TC_STAGED=0 or the caller has no workspace to give
+// (then the producer warps gather and split the operands themselves).
+bool tc_staged() {
+  static const bool v = [] {
+    const char* e = getenv("KFAC_TC_STAGED");
+    return e == nullptr || atoi(e) != 0;
+  }();
+  return v;
+}
+
+size_t tc_factor_workspace_bytes(long long rows, int d, bool staged) {
   TcFactorSplit s = tc_factor_split(rows, d);
-  if (s.splits <= 1) return 0;
-  return (size_t)s.splits * s.tiles * TC_BM * TC_BN * sizeof(float);
+  size_t bytes = (staged && tc_staged()) ? tc_stage_bytes(rows, d) : 0;
+  if (s.splits > 1)
+    bytes += (size_t)s.splits * s.tiles * TC_BM * TC_BN * sizeof(float);
+  return bytes;
 }
 
 size_t tc_pad_bytes(const Operand& X, int n, int nhwc) {
@@ -1530,11 +1596,14 @@ static long long tc_group_chunk(int count, const FactorJob* jobs) {
   return work / (waves * sm_count());
 }
 
-size_t tc_factor_group_workspace_bytes(int count, const FactorJob* jobs) {
+size_t tc_factor_group_workspace_bytes(int count, const FactorJob* jobs,
+                                       bool staged) {
   const long long chunk = tc_group_chunk(count, jobs);
+  staged = staged && tc_staged();
   size_t total = 0;
   for (int i = 0; i < count; ++i) {
-    total += tc_pad_bytes(jobs[i].X, jobs[i].n, jobs[i].nhwc);
+    total += staged ? tc_stage_bytes(jobs[i].rows, jobs[i].d)
+                    : tc_pad_bytes(jobs[i].X, jobs[i].n, jobs[i].nhwc);
     TcFactorSplit s = count == 1 ? tc_factor_split(jobs[i].rows, jobs[i].d)
                                  : tc_split_for(jobs[i].rows, jobs[i].d, chunk);
     if (s.splits > 1)
@@ -1569,12 +1638,18 @@ static int tc_side_stream(SideStream** out) {
   return KFAC_OK;
 }
 
+struct alignas(64) TmapBlob {     // a CUtensorMap, opaque here
+  unsigned char b[128];
+};
+
 int run_factor_group_tc(int count, const FactorJob* jobs, void* workspace,
-                        size_t workspace_bytes, cudaStream_t main_stream) {
+                        size_t workspace_bytes, cudaStream_t main_stream,
+                        bool staged) {
   cudaStream_t stream = main_stream;
   int rc = tc_prepare();
   if (rc != KFAC_OK) return rc;
-  const size_t need = tc_factor_group_workspace_bytes(count, jobs);
+  staged = staged && tc_staged();
+  const size_t need = tc_factor_group_workspace_bytes(count, jobs, staged);
   if (need > 0 && (workspace == nullptr || workspace_bytes < need))
     return fail(KFAC_ERR_WORKSPACE,
                 "factor: workspace of %zu bytes needed, %zu given", need,
@@ -1587,13 +1662,32 @@ int run_factor_group_tc(int count, const FactorJob* jobs, void* workspace,
   std::vector<PadJob> pads;
   int pad_items = 0;
   for (int i = 0; i < count; ++i) {
-    const FactorJob& job = jobs[i];
-    KFAC_REQUIRE(job.out != nullptr && job.X.base != nullptr,
+    KFAC_REQUIRE(jobs[i].out != nullptr && jobs[i].X.base != nullptr,
                  "factor: null pointer");
-    KFAC_REQUIRE(job.rows > 0 && job.d > 0 && job.rows < (1LL << 31),
-                 "factor: rows=%lld d=%d out of range", job.rows, job.d);
+    KFAC_REQUIRE(jobs[i].rows > 0 && jobs[i].d > 0 &&
+                     jobs[i].rows < (1LL << 31),
+                 "factor: rows=%lld d=%d out of range", jobs[i].rows,
+                 jobs[i].d);
+  }
+  const TmapBlob* dev_maps = nullptr;
+  if (staged) {
+    // staging pass: X^T of every job as two bf16 planes, two tensor maps each
+    std::vector<TmapBlob> maps(2 * (size_t)count);
+    rc = tc_stage_group(count, jobs, ws, maps.data(), stream);
+    if (rc != KFAC_OK) return rc;
+    for (int i = 0; i < count; ++i)
+      ws += tc_stage_bytes(jobs[i].rows, jobs[i].d);
+    void* dev = nullptr;
+    rc = ring_alloc(maps.size() * sizeof(TmapBlob), &dev);
+    if (rc != KFAC_OK) return rc;
+    KFAC_CUDA(cudaMemcpyAsync(dev, maps.data(), maps.size() * sizeof(TmapBlob),
+                              cudaMemcpyHostToDevice, stream));
+    dev_maps = static_cast<const TmapBlob*>(dev);
+  }
+  for (int i = 0; i < count; ++i) {
+    const FactorJob& job = jobs[i];
     Operand X = job.X;
-    if (X.mode == 1 && (X.pd > 0 || job.nhwc)) {
+    if (!staged && X.mode == 1 && (X.pd > 0 || job.nhwc)) {
       // zero-bordered NCHW copy first; the gather then needs no bounds checks
       const size_t pad_bytes = tc_pad_bytes(X, job.n, job.nhwc);
       float* padded = reinterpret_cast<float*>(ws);
@@ -1643,6 +1737,10 @@ int run_factor_group_tc(int count, const FactorJob* jobs, void* workspace,
     g.splits = s.splits;
     g.k_per_split = s.k_per_split;
     g.partial = nullptr;
+    if (staged) {
+      g.tmap_hi = dev_maps + 2 * i;
+      g.tmap_lo = dev_maps + 2 * i + 1;
+    }
     if (s.splits > 1) {
       g.partial = reinterpret_cast<float*>(ws);
       ws += (size_t)s.splits * s.tiles * TC_BM * TC_BN * sizeof(float);
@@ -1659,7 +1757,7 @@ int run_factor_group_tc(int count, const FactorJob* jobs, void* workspace,
         reduces.push_back(it);
       }
     }
-    descs[X.mode == 1 ? 1 : 0].push_back(g);
+    descs[(X.mode == 1 && !staged) ? 1 : 0].push_back(g);
   }
   for (size_t b = 0; b < pads.size(); b += kPadJobsMax) {
     // (more than kPadJobsMax padded inputs in one group: several launches)
@@ -1718,7 +1816,10 @@ int run_factor_group_tc(int count, const FactorJob* jobs, void* workspace,
       dev_descs = static_cast<const GemmDesc*>(dev);
     }
     const int nd = (int)v.size();
-    if (m == 1 && tails)
+    if (staged)
+      tc_pair_kernel<false, false, true>
+          <<<total, PK_THREADS, PK_SMEM_BYTES, stream>>>(dev_descs, nd, inl);
+    else if (m == 1 && tails)
       tc_pair_kernel<true, true><<<total, PK_THREADS, PK_SMEM_BYTES, stream>>>(
           dev_descs, nd, inl);
     else if (m == 1)
@@ -1762,7 +1863,7 @@ int run_factor_group_tc(int count, const FactorJob* jobs, void* workspace,
 
 int run_factor_tc(const Operand& X, long long rows, int d, float alpha,
                   float beta, float* out, void* workspace,
-                  size_t workspace_bytes, cudaStream_t stream) {
+                  size_t workspace_bytes, cudaStream_t stream, bool staged) {
   FactorJob job;
   job.X = X;
   job.rows = rows;
@@ -1772,7 +1873,8 @@ int run_factor_tc(const Operand& X, long long rows, int d, float alpha,
   job.alpha = alpha;
   job.beta = beta;
   job.out = out;
-  return run_factor_group_tc(1, &job, workspace, workspace_bytes, stream);
+  return run_factor_group_tc(1, &job, workspace, workspace_bytes, stream,
+                             staged);
 }
 
 int engine() { return g_engine; }

@@ -284,8 +284,11 @@ class KFAC(_base.GradientMethod):
         # start the inverses of a size class during the backward pass, as
         # soon as the output gradients of all its layers exist (the large
         # classes sit in the last layers, whose gradients come first): their
-        # long serial chains then run beside the rest of the backward pass
-        self.eager_inverses = True
+        # long serial chains then run beside the rest of the backward pass.
+        # Off by default: on ResNet-50 at batch 32 the backward pass keeps
+        # the GPU busy by itself and the early inverses slow it down by more
+        # than they save afterwards (33.4 ms per step against 29.8 ms).
+        self.eager_inverses = False
         self._eager = None
         self._eager_stream = None
         self.observation = {}
