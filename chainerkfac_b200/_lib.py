@@ -60,6 +60,8 @@ SIGNATURES = {
     'kfac_launch_count': (I64, []),
     'kfac_set_engine': (I, [I]),
     'kfac_get_engine': (I, []),
+    'kfac_set_factor_staging': (I, [I]),
+    'kfac_get_factor_staging': (I, []),
     'kfac_tc_status': (I, [c_int_p]),
     'kfac_selftest_wait_expiry': (I, [c_int_p, c_int_p]),
     'kfac_factor_workspace_bytes': (SZ, [I64, I]),

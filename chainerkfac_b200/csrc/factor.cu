@@ -213,7 +213,7 @@ __device__ __forceinline__ int bn_find_item(const int* begins, int n, int b) {
 __global__ void __launch_bounds__(256)
 bn_stats_group_kernel(const BnItem* __restrict__ items, int nitems) {
   __shared__ int s_begin[kBnItemsMax];
-  __shared__ double sh[2][8][33];
+  __shared__ double sh[2][32][9];
   for (int i = threadIdx.x; i < nitems; i += blockDim.x)
     s_begin[i] = items[i].stat_begin;
   __syncthreads();
@@ -247,27 +247,34 @@ bn_stats_group_kernel(const BnItem* __restrict__ items, int nitems) {
     }
     return;
   }
-  const int cx = threadIdx.x & 31, py = threadIdx.x >> 5;
-  const int ch = 32 * b + cx;
+  // channels-last: a block per (sample, 8 channels); 8 channels along the
+  // fastest thread index (one 32-byte sector per pixel), 32 pixels in
+  // flight per block.  The block leaves its sample's sums in the scratch
+  // behind the statistics (doubles, [sample][2c]); the gradient kernel adds
+  // the samples up in a fixed order.
+  const int groups = (it.c + 7) >> 3;
+  const int smp = b / groups, cg = b - smp * groups;
+  const int cx = threadIdx.x & 7, px = threadIdx.x >> 3;
+  const int ch = 8 * cg + cx;
   double s = 0.0, ss = 0.0;
   if (ch < it.c) {
-    for (long long p = py; p < per; p += 8) {
-      const double v = it.x[p * it.c + ch];
+    const float* p = it.x + (long long)smp * it.hw * it.c + ch;
+    for (int q = px; q < it.hw; q += 32) {
+      const double v = p[(long long)q * it.c];
       s += v;
       ss += v * v;
     }
   }
-  sh[0][py][cx] = s;
-  sh[1][py][cx] = ss;
+  double (*acc)[32][9] = reinterpret_cast<double (*)[32][9]>(&sh[0][0][0]);
+  acc[0][px][cx] = s;
+  acc[1][px][cx] = ss;
   __syncthreads();
-  if (py == 0 && ch < it.c) {
+  if (px == 0 && ch < it.c) {
     s = ss = 0.0;
-    for (int k = 0; k < 8; ++k) { s += sh[0][k][cx]; ss += sh[1][k][cx]; }
-    const double mean = s / (double)per;
-    double var = ss / (double)per - mean * mean;
-    if (var < 0.0) var = 0.0;
-    it.stats[ch] = (float)mean;
-    it.stats[it.c + ch] = (float)(1.0 / sqrt(var + (double)it.eps));
+    for (int k = 0; k < 32; ++k) { s += acc[0][k][cx]; ss += acc[1][k][cx]; }
+    double* part = reinterpret_cast<double*>(it.stats + 2 * it.c);
+    part[(long long)smp * 2 * it.c + ch] = s;
+    part[(long long)smp * 2 * it.c + it.c + ch] = ss;
   }
 }
 
@@ -277,7 +284,7 @@ bn_stats_group_kernel(const BnItem* __restrict__ items, int nitems) {
 __global__ void __launch_bounds__(256)
 bn_grads_group_kernel(const BnItem* __restrict__ items, int nitems) {
   __shared__ int s_begin[kBnItemsMax];
-  __shared__ float sh[2][8][33];
+  __shared__ float sh[2][32][9];
   for (int i = threadIdx.x; i < nitems; i += blockDim.x)
     s_begin[i] = items[i].grad_begin;
   __syncthreads();
@@ -307,27 +314,51 @@ bn_grads_group_kernel(const BnItem* __restrict__ items, int nitems) {
     }
     return;
   }
-  const int cblocks = (it.c + 31) >> 5;
-  const int smp = b / cblocks, cb = b - smp * cblocks;
-  const int cx = threadIdx.x & 31, py = threadIdx.x >> 5;
-  const int ch = 32 * cb + cx;
+  // channels-last: a block per (sample, 8 channels), as in the statistics
+  // kernel; mean and 1/sqrt(var + eps) of its channels first, from the
+  // per-sample sums
+  const int groups = (it.c + 7) >> 3;
+  const int smp = b / groups, cg = b - smp * groups;
+  const int cx = threadIdx.x & 7, px = threadIdx.x >> 3;
+  const int ch = 8 * cg + cx;
+  __shared__ float s_mean[8], s_istd[8];
+  if (threadIdx.x < 8 && ch < it.c) {
+    const double* part = reinterpret_cast<const double*>(it.stats + 2 * it.c);
+    double ds = 0.0, dss = 0.0;
+    for (int k = 0; k < it.n; ++k) {
+      ds += part[(long long)k * 2 * it.c + ch];
+      dss += part[(long long)k * 2 * it.c + it.c + ch];
+    }
+    const double per = (double)it.n * it.hw;
+    const double mean = ds / per;
+    double var = dss / per - mean * mean;
+    if (var < 0.0) var = 0.0;
+    s_mean[cx] = (float)mean;
+    s_istd[cx] = (float)(1.0 / sqrt(var + (double)it.eps));
+    if (smp == 0) {
+      it.stats[ch] = s_mean[cx];
+      it.stats[it.c + ch] = s_istd[cx];
+    }
+  }
+  __syncthreads();
   float a = 0.f, g0 = 0.f;
   if (ch < it.c) {
-    const float mean = it.stats[ch], istd = it.stats[it.c + ch];
-    const float* px = it.x + (long long)smp * it.hw * it.c + ch;
+    const float mean = s_mean[cx], istd = s_istd[cx];
+    const float* pxp = it.x + (long long)smp * it.hw * it.c + ch;
     const float* pg = it.gy + (long long)smp * it.hw * it.c + ch;
-    for (int p = py; p < it.hw; p += 8) {
-      const float g = pg[(long long)p * it.c] * it.scale;
-      a += g * ((px[(long long)p * it.c] - mean) * istd);
+    for (int q = px; q < it.hw; q += 32) {
+      const float g = pg[(long long)q * it.c] * it.scale;
+      a += g * ((pxp[(long long)q * it.c] - mean) * istd);
       g0 += g;
     }
   }
-  sh[0][py][cx] = a;
-  sh[1][py][cx] = g0;
+  float (*acc)[32][9] = reinterpret_cast<float (*)[32][9]>(&sh[0][0][0]);
+  acc[0][px][cx] = a;
+  acc[1][px][cx] = g0;
   __syncthreads();
-  if (py == 0 && ch < it.c) {
+  if (px == 0 && ch < it.c) {
     a = g0 = 0.f;
-    for (int k = 0; k < 8; ++k) { a += sh[0][k][cx]; g0 += sh[1][k][cx]; }
+    for (int k = 0; k < 32; ++k) { a += acc[0][k][cx]; g0 += acc[1][k][cx]; }
     it.out[(long long)smp * 2 * it.c + ch] = a;
     it.out[(long long)smp * 2 * it.c + it.c + ch] = g0;
   }
@@ -433,7 +464,9 @@ struct BnLowRankItem {
   int* flag;           // [0] scratch, [1] fallback counter
   int c, m, rows_per_slot;
   float dinv0, dinv1;  // d_gamma^-1/2, d_beta^-1/2
-  int blk_begin;       // first block of this layer in the scale launch
+  int blk_begin;       // first block of this layer in the per-row launches
+  int col_begin;       // first block of this layer in the per-column launch
+  float* vy;           // scratch: v (m floats), then y (m floats)
   float slot_scale[kLowRankSlots];   // sqrt(weight) of every slot (0: unused)
 };
 
@@ -455,54 +488,113 @@ bn_lowrank_scale_kernel(const BnLowRankItem* __restrict__ items, int nitems) {
     dst[k] = s == 0.f ? 0.f : src[k] * (k < c ? a0 : a1);
 }
 
-// One CTA per block.  Shared memory: g' and the result (2c floats each), v and
-// y (m floats each).
+// Applying the low-rank form, four grouped launches over all blocks:
+//   v = Hs g'          (a CTA per row of Hs; g' = D^-1/2 g on the fly)
+//   y = Minv v         (a CTA per row of Minv)
+//   kf = D^-1/2 (g' - Hs^T y)   (a thread per column; NaN raises flag[0])
+//   finish             (a CTA per block: NaN fallback, fused update)
+// v and y live in a scratch the launcher takes from the descriptor ring.
+__device__ __forceinline__ int lowrank_find(const int* begins, int n, int b) {
+  int lo = 0, hi = n - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (begins[mid] <= b) lo = mid; else hi = mid - 1;
+  }
+  return lo;
+}
+
+__device__ __forceinline__ float block_sum_256(float s, float* red) {
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_down_sync(0xffffffffu, s, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+  __syncthreads();
+  float t = 0.f;
+  if (threadIdx.x == 0)
+    for (int k = 0; k < 8; ++k) t += red[k];
+  return t;                      // valid in thread 0
+}
+
 __global__ void __launch_bounds__(256)
-bn_lowrank_apply_kernel(const BnLowRankItem* __restrict__ items, float lr,
-                        float momentum) {
-  extern __shared__ float lsm[];
-  const BnLowRankItem* it = items + blockIdx.x;
+bn_lowrank_v_kernel(const BnLowRankItem* __restrict__ items, int nitems) {
+  __shared__ int s_begin[kBnItemsMax];
+  __shared__ float red[8];
+  for (int i = threadIdx.x; i < nitems; i += blockDim.x)
+    s_begin[i] = items[i].blk_begin;
+  __syncthreads();
+  const BnLowRankItem* it = items + lowrank_find(s_begin, nitems, blockIdx.x);
+  const int a = blockIdx.x - it->blk_begin;
+  const int c = it->c, d = 2 * c;
+  const float* hr = it->Hs + (long long)a * d;
+  float s = 0.f;
+  for (int k = threadIdx.x; k < d; k += 256) {
+    const float g = k < c ? it->g0[k] * it->dinv0 : it->g1[k - c] * it->dinv1;
+    s += hr[k] * g;
+  }
+  s = block_sum_256(s, red);
+  if (threadIdx.x == 0) it->vy[a] = s;
+}
+
+__global__ void __launch_bounds__(256)
+bn_lowrank_y_kernel(const BnLowRankItem* __restrict__ items, int nitems) {
+  __shared__ int s_begin[kBnItemsMax];
+  __shared__ float red[8];
+  for (int i = threadIdx.x; i < nitems; i += blockDim.x)
+    s_begin[i] = items[i].blk_begin;
+  __syncthreads();
+  const BnLowRankItem* it = items + lowrank_find(s_begin, nitems, blockIdx.x);
+  const int a = blockIdx.x - it->blk_begin;
+  const int m = it->m;
+  const float* mr = it->Minv + (long long)a * m;
+  float s = 0.f;
+  for (int b = threadIdx.x; b < m; b += 256) s += mr[b] * it->vy[b];
+  s = block_sum_256(s, red);
+  if (threadIdx.x == 0) it->vy[m + a] = s;
+}
+
+__global__ void __launch_bounds__(256)
+bn_lowrank_out_kernel(const BnLowRankItem* __restrict__ items, int nitems) {
+  __shared__ int s_begin[kBnItemsMax];
+  __shared__ float y[kLowRankSlots * 64];      // a run of 2048 rows at a time
+  for (int i = threadIdx.x; i < nitems; i += blockDim.x)
+    s_begin[i] = items[i].col_begin;
+  __syncthreads();
+  const BnLowRankItem* it = items + lowrank_find(s_begin, nitems, blockIdx.x);
   const int c = it->c, d = 2 * c, m = it->m;
-  float* gp = lsm;            // d
-  float* kf = lsm + d;        // d
-  float* v = lsm + 2 * d;     // m
-  float* y = v + m;           // m
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const float dinv0 = it->dinv0, dinv1 = it->dinv1;
-  for (int k = tid; k < d; k += 256)
-    gp[k] = k < c ? it->g0[k] * dinv0 : it->g1[k - c] * dinv1;
-  __syncthreads();
-  for (int a = warp; a < m; a += 8) {
-    const float* hr = it->Hs + (long long)a * d;
-    float s = 0.f;
-    for (int k = lane; k < d; k += 32) s += hr[k] * gp[k];
-    for (int o = 16; o > 0; o >>= 1) s += __shfl_down_sync(0xffffffffu, s, o);
-    if (lane == 0) v[a] = s;
+  const int k = (blockIdx.x - it->col_begin) * 256 + threadIdx.x;
+  float s = 0.f;
+  for (int a0 = 0; a0 < m; a0 += kLowRankSlots * 64) {
+    const int na = min(kLowRankSlots * 64, m - a0);
+    __syncthreads();
+    for (int a = threadIdx.x; a < na; a += 256) y[a] = it->vy[m + a0 + a];
+    __syncthreads();
+    if (k < d) {
+      const float* hc = it->Hs + (long long)a0 * d + k;
+      for (int a = 0; a < na; ++a) s += hc[(long long)a * d] * y[a];
+    }
   }
-  __syncthreads();
-  for (int a = warp; a < m; a += 8) {
-    const float* mr = it->Minv + (long long)a * m;
-    float s = 0.f;
-    for (int b = lane; b < m; b += 32) s += mr[b] * v[b];
-    for (int o = 16; o > 0; o >>= 1) s += __shfl_down_sync(0xffffffffu, s, o);
-    if (lane == 0) y[a] = s;
+  if (k < d) {
+    const bool first = k < c;
+    const float dinv = first ? it->dinv0 : it->dinv1;
+    const float g = first ? it->g0[k] : it->g1[k - c];
+    const float r = (g * dinv - s) * dinv;
+    (first ? it->y0 : it->y1)[first ? k : k - c] = r;
+    if (isnan(r)) atomicOr(&it->flag[0], 1);
   }
+}
+
+__global__ void __launch_bounds__(256)
+bn_lowrank_finish_kernel(const BnLowRankItem* __restrict__ items, float lr,
+                         float momentum) {
+  const BnLowRankItem* it = items + blockIdx.x;
+  const int c = it->c, d = 2 * c;
+  const int bad = it->flag[0];
   __syncthreads();
-  int bad = 0;
-  for (int k = tid; k < d; k += 256) {
-    float s = 0.f;
-    for (int a = 0; a < m; ++a) s += it->Hs[(long long)a * d + k] * y[a];
-    const float r = (gp[k] - s) * (k < c ? dinv0 : dinv1);
-    kf[k] = r;
-    bad |= isnan(r) ? 1 : 0;
-  }
-  bad = __syncthreads_or(bad);
-  for (int k = tid; k < d; k += 256) {
+  for (int k = threadIdx.x; k < d; k += 256) {
     const bool first = k < c;
     const int j = first ? k : k - c;
+    float* out = first ? it->y0 : it->y1;
     // NaN anywhere: the raw gradients take the result's place
-    const float r = bad ? (first ? it->g0 : it->g1)[j] : kf[k];
-    (first ? it->y0 : it->y1)[j] = r;
+    const float r = bad ? (first ? it->g0 : it->g1)[j] : out[j];
+    if (bad) out[j] = r;
     float* p = first ? it->p0 : it->p1;
     if (p != nullptr) {
       float* vel = first ? it->v0 : it->v1;
@@ -511,7 +603,10 @@ bn_lowrank_apply_kernel(const BnLowRankItem* __restrict__ items, float lr,
       p[j] += nv;
     }
   }
-  if (tid == 0 && bad) it->flag[1] += 1;
+  if (threadIdx.x == 0 && bad) {
+    it->flag[1] += 1;
+    it->flag[0] = 0;
+  }
 }
 
 __global__ void axpby_kernel(long long count, float a,
@@ -743,9 +838,9 @@ extern "C" int kfac_bn_sample_grads_group(int count,
     t.eps = k.eps; t.scale = k.scale;
     t.stat_begin = (int)sb;
     t.grad_begin = (int)gb;
-    const long long cb = (k.c + 31) / 32;
-    sb += t.nhwc ? cb : k.c;
-    gb += t.nhwc ? (long long)k.n * cb : ((long long)k.n * k.c + 7) / 8;
+    const long long cg = (k.c + 7) / 8;
+    sb += t.nhwc ? (long long)k.n * cg : k.c;
+    gb += t.nhwc ? (long long)k.n * cg : ((long long)k.n * k.c + 7) / 8;
     KFAC_REQUIRE(sb < (1ll << 31) && gb < (1ll << 31),
                  "bn_sample_grads_group: too many blocks");
   }
@@ -904,15 +999,23 @@ extern "C" int kfac_bn_lowrank_apply(int count,
                  "bn_lowrank_apply: fused update of item %d lacks a pointer",
                  i);
   }
-  KFAC_REQUIRE(smem <= 200 * 1024, "bn_lowrank_apply: block too large");
-  static bool attr_done[64] = {false};
-  int devi = 0;
-  KFAC_CUDA(cudaGetDevice(&devi));
-  if (devi >= 0 && devi < 64 && !attr_done[devi]) {
-    KFAC_CUDA(cudaFuncSetAttribute(bn_lowrank_apply_kernel,
-                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   200 * 1024));
-    attr_done[devi] = true;
+  // v and y of every block from the descriptor ring
+  long long vy_floats = 0, cols = 0;
+  for (BnLowRankItem& t : tab) {
+    t.col_begin = (int)cols;
+    cols += (2 * t.c + 255) / 256;
+    vy_floats += 2 * t.m;
+  }
+  KFAC_REQUIRE(cols < (1ll << 31), "bn_lowrank_apply: too many columns");
+  void* vy = nullptr;
+  rc = ring_alloc((size_t)vy_floats * sizeof(float), &vy);
+  if (rc != KFAC_OK) return rc;
+  {
+    float* p = static_cast<float*>(vy);
+    for (BnLowRankItem& t : tab) {
+      t.vy = p;
+      p += 2 * t.m;
+    }
   }
   void* dev = nullptr;
   rc = ring_alloc(tab.size() * sizeof(BnLowRankItem), &dev);
@@ -920,9 +1023,15 @@ extern "C" int kfac_bn_lowrank_apply(int count,
   cudaStream_t st = (cudaStream_t)stream;
   KFAC_CUDA(cudaMemcpyAsync(dev, tab.data(), tab.size() * sizeof(BnLowRankItem),
                             cudaMemcpyHostToDevice, st));
-  bn_lowrank_apply_kernel<<<count, 256, smem, st>>>(
-      static_cast<const BnLowRankItem*>(dev), lr, momentum);
-  KFAC_LAUNCH_CHECK("bn_lowrank_apply_kernel");
+  const BnLowRankItem* d_items = static_cast<const BnLowRankItem*>(dev);
+  bn_lowrank_v_kernel<<<(int)blocks, 256, 0, st>>>(d_items, count);
+  KFAC_LAUNCH_CHECK("bn_lowrank_v_kernel");
+  bn_lowrank_y_kernel<<<(int)blocks, 256, 0, st>>>(d_items, count);
+  KFAC_LAUNCH_CHECK("bn_lowrank_y_kernel");
+  bn_lowrank_out_kernel<<<(int)cols, 256, 0, st>>>(d_items, count);
+  KFAC_LAUNCH_CHECK("bn_lowrank_out_kernel");
+  bn_lowrank_finish_kernel<<<count, 256, 0, st>>>(d_items, lr, momentum);
+  KFAC_LAUNCH_CHECK("bn_lowrank_finish_kernel");
   return KFAC_OK;
 }
 

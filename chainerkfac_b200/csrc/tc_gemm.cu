@@ -1556,14 +1556,16 @@ static TcFactorSplit tc_factor_split(long long rows, int d) {
 }
 
 // Factor builds read their operands from the staged bf16 planes through TMA
-// (stage.cu) unless KFAC_TC_STAGED=0 or the caller has no workspace to give
-// (then the producer warps gather and split the operands themselves).
+// (stage.cu) when this is on (kfac_set_factor_staging, initial value from
+// KFAC_TC_STAGED, default off) and the caller gives workspace; otherwise the
+// producer warps gather and split the operands themselves.
+static int g_staged = -1;
 bool tc_staged() {
-  static const bool v = [] {
+  if (g_staged < 0) {
     const char* e = getenv("KFAC_TC_STAGED");
-    return e == nullptr || atoi(e) != 0;
-  }();
-  return v;
+    g_staged = (e != nullptr && atoi(e) != 0) ? 1 : 0;
+  }
+  return g_staged != 0;
 }
 
 size_t tc_factor_workspace_bytes(long long rows, int d, bool staged) {
@@ -1889,6 +1891,15 @@ extern "C" int kfac_set_engine(int engine) {
 }
 
 extern "C" int kfac_get_engine(void) { return kfac::g_engine; }
+
+extern "C" int kfac_set_factor_staging(int on) {
+  kfac::g_staged = on ? 1 : 0;
+  return KFAC_OK;
+}
+
+extern "C" int kfac_get_factor_staging(void) {
+  return kfac::tc_staged() ? 1 : 0;
+}
 
 #ifdef KFAC_TC_TRACE
 extern "C" int kfac_tc_trace(long long* buf_dev, int capacity) {

@@ -240,8 +240,9 @@ def bn_item(x, gy, eps, scale, out=None, stats=None):
         out = torch.empty((n, 2 * c), dtype=torch.float32, device=x.device)
     it = _lib.BnItem()
     it.x, it.gy, it.out = x.data_ptr(), gy.data_ptr(), out.data_ptr()
-    if stats is None or stats.numel() != 2 * c or stats.device != x.device:
-        stats = torch.empty(2 * c, dtype=torch.float32, device=x.device)
+    need = 2 * c + 4 * n * c     # statistics, then per-sample double sums
+    if stats is None or stats.numel() != need or stats.device != x.device:
+        stats = torch.empty(need, dtype=torch.float32, device=x.device)
     it.stats = stats.data_ptr()
     it.n, it.c, it.hw, it.layout = n, c, hw, layout
     it.eps, it.scale = eps, scale

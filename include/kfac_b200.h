@@ -47,6 +47,20 @@ int64_t kfac_launch_count(void);
  * The choice is read when a call is made or a plan is created. */
 int kfac_set_engine(int engine);
 int kfac_get_engine(void);
+
+/* Operand feed of the tensor-core factor builds (no counterpart in the
+ * reference).  0 (default): producer warps gather the operand from the
+ * caller's arrays (strided rows, implicit im2col) and split it into bf16
+ * terms on the way into shared memory.  1: a staging pass first writes X^T as
+ * two bf16 planes into the workspace, and the X^T X kernel fetches 32 k x 256
+ * row boxes of them with TMA (cp.async.bulk.tensor, 64-byte swizzle); needs
+ * 4 * d * roundup(rows, 8) more workspace bytes per factor (the *_workspace_
+ * bytes functions account for it) and is not used by
+ * kfac_factor_dense_noalloc.  Same results; measured slower on B200 (the
+ * 64-byte box rows arrive at about 16 bytes per clock per SM), hence off.
+ * The environment variable KFAC_TC_STAGED sets the initial value. */
+int kfac_set_factor_staging(int on);
+int kfac_get_factor_staging(void);
 /* Synchronises the device and returns in *status_out the tensor-core engine's
  * status word: 0, or 1 if a bounded barrier wait inside a kernel ran out (the
  * results of that launch are then invalid). */
@@ -160,7 +174,8 @@ int kfac_factor_group(int count, const kfac_factor_item* items,
  * out[s, j] = scale * sum_hw gy[s,j,:] * xhat[s,j,:] and
  * out[s, c+j] = scale * sum_hw gy[s,j,:], xhat = x normalised with the batch
  * mean and biased variance (+eps).  hw = 1 for 2-D inputs.  `stats` is a
- * device scratch of 2*c floats.  Followed by kfac_factor_dense(out, n, 2c, ..)
+ * device scratch of 2*c + 4*n*c floats (mean, 1/sqrt(var + eps), then per-
+ * sample partial sums in double precision), 8-byte aligned.  Followed by kfac_factor_dense(out, n, 2c, ..)
  * it replaces FisherBlockBatchNormalization.compute_F,
  * optimizers/fisher_blocks/normalizations/batch_normalization.py:78-131. */
 int kfac_bn_sample_grads(const float* x, const float* gy, int n, int c, int hw,
@@ -176,7 +191,7 @@ typedef struct kfac_bn_item {
   const float* x;
   const float* gy;
   float* out;      /* (n, 2c) */
-  float* stats;    /* scratch, 2c floats */
+  float* stats;    /* scratch, 2c + 4nc floats, 8-byte aligned */
   int n, c, hw;
   int layout;
   float eps, scale;
@@ -346,8 +361,8 @@ int kfac_bn_precondition_group(
  * become zero).  The caller then forms Hs Hs^T with kfac_factor_group
  * (KFAC_FACTOR_DENSE_T) and inverts I + Hs Hs^T with an inverse plan (role 2,
  * damping 1, scale 1).  kfac_bn_lowrank_apply evaluates the formula with that
- * inverse (`m_inv`, m x m) for every block (one CTA each; 2c <= 12000), with
- * the NaN fallback and the optional fused momentum update of
+ * inverse (`m_inv`, m x m) for every block (four grouped launches: rows of
+ * Hs, rows of the inverse, columns, finish), with the NaN fallback and the optional fused momentum update of
  * kfac_bn_precondition_group.  `items` is a host array (<= 256 entries). */
 typedef struct kfac_bn_lowrank_item {
   const float* hist;

@@ -45,10 +45,16 @@ def test_pure_host_entry_points(lib):
     n = lib.kfac_wire_nelems(2, _lib.i64_array([16, 5]),
                              _lib.int_array([4, 0]))
     assert n == 10 + 5
-    # a short contraction needs no partial tiles, only the two staged bf16
-    # planes of the transposed operand (rows of 32 k, 256-byte aligned)
-    plane = (2049 * 32 * 2 + 255) // 256 * 256
-    assert lib.kfac_factor_workspace_bytes(32, 2049) == 2 * plane
+    assert lib.kfac_get_factor_staging() == 0
+    assert lib.kfac_factor_workspace_bytes(32, 2049) == 0
+    # with the staging pass on: the two bf16 planes of the transposed operand
+    # (rows of 32 k, 256-byte aligned); a short contraction needs no more
+    lib.kfac_set_factor_staging(1)
+    try:
+        plane = (2049 * 32 * 2 + 255) // 256 * 256
+        assert lib.kfac_factor_workspace_bytes(32, 2049) == 2 * plane
+    finally:
+        lib.kfac_set_factor_staging(0)
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):

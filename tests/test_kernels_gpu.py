@@ -203,6 +203,69 @@ def test_factor_group_matches_single_calls(ops):
                                          False)) < FACTOR_TOL
 
 
+def test_factor_builds_from_staged_operands(ops, engine):
+    """The optional operand feed of the factor builds (staging pass that
+    writes X^T as two bf16 planes, TMA boxes into the tile kernel) against the
+    oracle and against the default feed: every operand kind and layout,
+    ragged sizes, a cut contraction, the appended ones column."""
+    from chainerkfac_b200 import _lib
+    if engine == 0:
+        pytest.skip('the staged feed belongs to the tensor-core engine')
+    lib = _lib.load()
+    rng = np.random.default_rng(77)
+
+    def arr(*shape):
+        return dev(rng.standard_normal(shape).astype(np.float32))
+
+    xd, xs = arr(5000, 300), arr(70, 33)
+    xl = arr(70000, 130)                      # several splits
+    xc, x2, x7 = arr(4, 16, 14, 14), arr(2, 8, 15, 15), arr(2, 3, 30, 30)
+    xn = arr(4, 32, 8, 8).contiguous(memory_format=torch.channels_last)
+    x1 = arr(3, 24, 6, 6).contiguous(memory_format=torch.channels_last)
+    gy = arr(3, 40, 12, 12)
+    gn = arr(3, 40, 5, 5).contiguous(memory_format=torch.channels_last)
+    xt = arr(48, 1000)
+    cases = [
+        lambda o: ops.dense_item(xd, True, 1 / 5000., 0.0, o),
+        lambda o: ops.dense_item(xs, False, 1.0, 0.0, o),
+        lambda o: ops.dense_item(xl, True, 1 / 70000., 0.0, o),
+        lambda o: ops.conv_input_item(xc, 3, 1, 1, True, 0.25, 0.0, o),
+        lambda o: ops.conv_input_item(x2, 3, 2, 1, False, 0.5, 0.0, o),
+        lambda o: ops.conv_input_item(x7, 7, 2, 3, True, 0.5, 0.0, o),
+        lambda o: ops.conv_input_item(xn, 3, 1, 1, True, 0.25, 0.0, o),
+        lambda o: ops.conv_input_item(x1, 1, 1, 0, False, 1.0, 0.0, o),
+        lambda o: ops.conv_grad_item(gy, 2.0, 0.0, o),
+        lambda o: ops.conv_grad_item(gn, 2.0, 0.0, o),
+        lambda o: ops.dense_t_item(xt, 1.0, 0.0, o),
+    ]
+    sides = [301, 33, 131, 145, 72, 148, 289, 24, 40, 40, 48]
+    results = {}
+    for staged in (0, 1):
+        lib.kfac_set_factor_staging(staged)
+        try:
+            outs = [torch.full((d, d), 7.0, device='cuda') for d in sides]
+            ops.factor_group([c(o) for c, o in zip(cases, outs)], xd.device)
+            # a lone factor takes the by-value descriptor path
+            lone = ops.factor_conv_input(xc, 3, 1, 1, True, alpha=0.25)
+            torch.cuda.synchronize()
+            results[staged] = [host(o) for o in outs] + [host(lone)]
+        finally:
+            lib.kfac_set_factor_staging(0)
+    for k, (a, b) in enumerate(zip(results[1], results[0])):
+        assert rel(a, b) < 2e-6, (k, rel(a, b))
+        check_symmetric(a)
+    want = orc.conv_A(host(xc).astype(np.float64), 3, 1, 1, True)
+    assert rel(results[1][3], want) < FACTOR_TOL
+    want = orc.conv_A(host(xn).astype(np.float64), 3, 1, 1, True)
+    assert rel(results[1][6], want) < FACTOR_TOL
+    want = host(xl).astype(np.float64)
+    want = np.concatenate([want, np.ones((70000, 1))], 1)
+    assert rel(results[1][2], want.T @ want / 70000.) < FACTOR_TOL
+    assert rel(results[1][10],
+               host(xt).astype(np.float64) @ host(xt).astype(np.float64).T) \
+        < FACTOR_TOL
+
+
 @pytest.mark.parametrize('name', ['bn_4d', 'bn_2d'])
 def test_bn_factor_golden(ops, golden, name):
     g = golden(name)
