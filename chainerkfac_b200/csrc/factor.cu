@@ -207,9 +207,10 @@ __device__ __forceinline__ int bn_find_item(const int* begins, int n, int b) {
   return lo;
 }
 
-// Batch mean and 1/sqrt(var + eps) per channel.  Planes: one block per
-// channel, threads along the pixels of each sample.  Channels-last: one block
-// per 32 channels, 32 x 8 threads, lanes along channels.
+// Sums of x and x^2 per (sample, channel), in double precision, into the
+// scratch behind the statistics; the gradient kernel turns them into the
+// batch mean and 1/sqrt(var + eps).  Planes: a warp per (sample, channel).
+// Channels-last: a block per (sample, 8 channels).
 __global__ void __launch_bounds__(256)
 bn_stats_group_kernel(const BnItem* __restrict__ items, int nitems) {
   __shared__ int s_begin[kBnItemsMax];
@@ -221,11 +222,16 @@ bn_stats_group_kernel(const BnItem* __restrict__ items, int nitems) {
   const int b = blockIdx.x - it.stat_begin;
   const long long per = (long long)it.n * it.hw;
   if (!it.nhwc) {
-    const int ch = b;
+    // planes: a warp per (sample, channel) plane; its sums go to the
+    // per-sample scratch like the channels-last ones
+    const long long warp = (long long)b * 8 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (warp >= (long long)it.n * it.c) return;
+    const int smp = (int)(warp / it.c), ch = (int)(warp - (long long)smp * it.c);
+    const float* px = it.x + warp * it.hw;
     double s = 0.0, ss = 0.0;
-    for (long long i = threadIdx.x; i < per; i += blockDim.x) {
-      const long long smp = i / it.hw;
-      const double v = it.x[(smp * it.c + ch) * it.hw + (i - smp * it.hw)];
+    for (int i = lane; i < it.hw; i += 32) {
+      const double v = px[i];
       s += v;
       ss += v * v;
     }
@@ -233,17 +239,10 @@ bn_stats_group_kernel(const BnItem* __restrict__ items, int nitems) {
       s += __shfl_down_sync(0xffffffffu, s, o);
       ss += __shfl_down_sync(0xffffffffu, ss, o);
     }
-    const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
-    if (l == 0) { sh[0][w][0] = s; sh[1][w][0] = ss; }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      s = ss = 0.0;
-      for (int k = 0; k < 8; ++k) { s += sh[0][k][0]; ss += sh[1][k][0]; }
-      const double mean = s / (double)per;
-      double var = ss / (double)per - mean * mean;
-      if (var < 0.0) var = 0.0;
-      it.stats[ch] = (float)mean;
-      it.stats[it.c + ch] = (float)(1.0 / sqrt(var + (double)it.eps));
+    if (lane == 0) {
+      double* part = reinterpret_cast<double*>(it.stats + 2 * it.c);
+      part[(long long)smp * 2 * it.c + ch] = s;
+      part[(long long)smp * 2 * it.c + it.c + ch] = ss;
     }
     return;
   }
@@ -295,7 +294,28 @@ bn_grads_group_kernel(const BnItem* __restrict__ items, int nitems) {
     const int lane = threadIdx.x & 31;
     if (warp >= (long long)it.n * it.c) return;
     const int smp = (int)(warp / it.c), ch = (int)(warp - (long long)smp * it.c);
-    const float mean = it.stats[ch], istd = it.stats[it.c + ch];
+    // mean and 1/sqrt(var + eps) from the per-sample sums, added up in a
+    // fixed order (lanes take samples, then a butterfly)
+    const double* part = reinterpret_cast<const double*>(it.stats + 2 * it.c);
+    double ds = 0.0, dss = 0.0;
+    for (int k = lane; k < it.n; k += 32) {
+      ds += part[(long long)k * 2 * it.c + ch];
+      dss += part[(long long)k * 2 * it.c + it.c + ch];
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+      ds += __shfl_xor_sync(0xffffffffu, ds, o);
+      dss += __shfl_xor_sync(0xffffffffu, dss, o);
+    }
+    const double per = (double)it.n * it.hw;
+    const double dmean = ds / per;
+    double var = dss / per - dmean * dmean;
+    if (var < 0.0) var = 0.0;
+    const float mean = (float)dmean;
+    const float istd = (float)(1.0 / sqrt(var + (double)it.eps));
+    if (smp == 0 && lane == 0) {
+      it.stats[ch] = mean;
+      it.stats[it.c + ch] = istd;
+    }
     const float* px = it.x + warp * it.hw;
     const float* pg = it.gy + warp * it.hw;
     float a = 0.f, g0 = 0.f;
@@ -839,7 +859,7 @@ extern "C" int kfac_bn_sample_grads_group(int count,
     t.stat_begin = (int)sb;
     t.grad_begin = (int)gb;
     const long long cg = (k.c + 7) / 8;
-    sb += t.nhwc ? (long long)k.n * cg : k.c;
+    sb += t.nhwc ? (long long)k.n * cg : ((long long)k.n * k.c + 7) / 8;
     gb += t.nhwc ? (long long)k.n * cg : ((long long)k.n * k.c + 7) / 8;
     KFAC_REQUIRE(sb < (1ll << 31) && gb < (1ll << 31),
                  "bn_sample_grads_group: too many blocks");

@@ -132,7 +132,7 @@ def test_batch_normalization_block_at_resnet50_sizes(c, h):
     # gradients of a mean-reduced loss shrink with batch and feature-map
     # size; with this scale the damped factors have condition numbers of
     # 1e2..1e3 (refinement covers sides up to 1024; the 2048- and 4096-row
-    # factors here are judged as the blocked fp32 algorithm leaves them)
+    # factors here are taken as the blocked fp32 algorithm leaves them)
     gy = (rng.standard_normal((n, c, h, h)) * (1.0 / (n * h * h))).astype(
         np.float32)
     gg = rng.standard_normal(c).astype(np.float32)

@@ -784,7 +784,7 @@ def test_config1_mlp_shapes_step(ops):
         # These factors are ill-conditioned (uniform[0,1) inputs: cond ~ 6e3
         # to 1.4e4 with damping 1e-3); the plan's probe sees that and runs
         # the fp64-residual refinement step on them.  The inverse stage is
-        # judged on identical inputs: the oracle inverts the factor this
+        # compared on identical inputs: the oracle inverts the factor this
         # stage was given (a factor that differs by 2e-6 moves the inverse
         # by up to cond * 2e-6, whoever computes it), with the damping the
         # oracle derives from it.
