@@ -53,6 +53,56 @@ def test_public_interface_and_defaults():
         ck.KFAC(use_cholesky=False).setup(small_model())
 
 
+def test_bn_low_rank_history_weights_follow_the_running_average():
+    """Host logic of the low-rank form of a BatchNormalization block: which
+    blocks take it, how the history ring rotates, and that the slot weights
+    reproduce the reference's running average (fisher_block.py:155-163)
+    F <- decay * F_new + (1 - decay) * F up to the forgotten tail."""
+    import chainerkfac_b200 as ck
+    from chainerkfac_b200.optimizers.fisher_blocks.normalizations \
+        .batch_normalization import lowrank_window
+    assert [lowrank_window(d) for d in (1.0, 0.9, 0.99, 0.5)] == [1, 8, 4, 27]
+    assert lowrank_window(0.05) == 0          # window longer than the ring
+    model = nn.Sequential(nn.Conv2d(3, 64, 3), nn.BatchNorm2d(64))
+    opt = ck.KFAC(cov_ema_decay=0.9).setup(model)
+    fb = opt.fblocks[1]
+    assert fb.low_rank_world == 1 and not fb.low_rank_active
+    fb.deferred = True
+    # 8 slots x 8 samples = 64 rows <= 64 channels: low rank; 9 samples: dense
+    assert fb._low_rank_wanted(8, 64) == (8, 8, 1, 0.9)
+    assert fb._low_rank_wanted(9, 64) is None
+    assert ck.KFAC(acc_iters=2).setup(model).fblocks[1].low_rank_world is None
+    assert ck.KFAC(bn_low_rank=False).setup(model).fblocks[1] \
+        .low_rank_world is None
+    fb._low_rank_setup((8, 8, 1, 0.9), 64, torch.device('cpu'))
+    assert fb.low_rank_active and fb.plan_entries() == [] and \
+        fb.plan_factors() == [] and not fb.has_state()
+    assert fb._lr['hist'].shape == (64, 128) and fb.max_side() == 64
+    rng = np.random.default_rng(0)
+    dense = None
+    for step in range(12):                    # more steps than slots
+        rows = rng.standard_normal((8, 128)).astype(np.float32)
+        slot = fb._next_slot()
+        assert slot.data_ptr() == fb._lr['hist'][
+            ((step % 8) * 8):].data_ptr()
+        slot.copy_(torch.from_numpy(rows))
+        fb.commit_rows()
+        f_new = rows.astype(np.float64).T @ rows / 8
+        dense = f_new if dense is None else 0.9 * f_new + 0.1 * dense
+        hist = fb._lr['hist'].numpy().astype(np.float64)
+        got = sum(w * fb._row_factor() * hist[8 * k:8 * k + 8].T @
+                  hist[8 * k:8 * k + 8] for k, w in enumerate(fb._lr['w']))
+        assert np.linalg.norm(got - dense) <= 2e-8 * np.linalg.norm(dense)
+    assert fb.has_state()
+    # a rank that does not own the block keeps one slot only
+    other = ck.KFAC(cov_ema_decay=0.9).setup(model).fblocks[1]
+    other.keeps_history, other.low_rank_world, other.low_rank_rank = \
+        False, 2, 1
+    other._low_rank_setup((4, 8, 2, 0.9), 64, torch.device('cpu'))
+    assert other._lr['hist'].shape == (8, 128) and other._lr['M'] is None
+    assert other._next_slot().shape == (8, 128) and other.cov_emas is None
+
+
 def test_balanced_ownership_is_deterministic_and_even():
     from chainerkfac_b200.optimizers.kfac import balanced_split
     dims = [bw.layer_dims(l) for l in bw.resnet50_layers()]
