@@ -61,7 +61,8 @@ def build_training_step(device, batch, world, rank, cov_ema_decay, damping,
     """Returns (step, h2d_bytes, d2h_bytes).  ``step()`` copies one pinned
     host batch to the device, runs ``optimizer.update(lossfun, x, t)``
     (forward, backward, K-FAC factors / inverses / preconditioned update) and
-    reads the loss back to the host."""
+    returns the step's loss, read back to the host as soon as the forward
+    pass has produced it."""
     import chainerkfac_b200 as ck
     from chainerkfac_b200.optimizers.kfac import connection_only_constructor
     from chainerkfac_b200.optimizers.kfac import fblock_constructor
@@ -91,8 +92,15 @@ def build_training_step(device, batch, world, rank, cov_ema_decay, damping,
     ht = torch.randint(0, classes, (batch,), generator=g).pin_memory()
     hloss = torch.empty((), dtype=torch.float32).pin_memory()
 
+    have_loss = torch.cuda.Event()
+
     def lossfun(x, t):
-        return F.cross_entropy(model(x), t)
+        loss = F.cross_entropy(model(x), t)
+        # the loss goes to the host right behind the forward pass; the
+        # backward pass and the K-FAC stages are queued after this copy
+        hloss.copy_(loss.detach(), non_blocking=True)
+        have_loss.record()
+        return loss
 
     def step():
         x = hx.to(device, non_blocking=True)
@@ -100,8 +108,10 @@ def build_training_step(device, batch, world, rank, cov_ema_decay, damping,
             x = x.contiguous(memory_format=torch.channels_last)
         t = ht.to(device, non_blocking=True)
         opt.update(lossfun, x, t)
-        hloss.copy_(opt.loss, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        # wait for this step's loss only: the host then prepares the next
+        # batch while the device finishes this update (the caller's timed
+        # region ends with a full synchronisation)
+        have_loss.synchronize()
         return float(hloss)
 
     h2d = hx.numel() * hx.element_size() + ht.numel() * ht.element_size()

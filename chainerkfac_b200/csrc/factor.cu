@@ -943,14 +943,12 @@ extern "C" int kfac_bn_precondition_group(
 }
 
 static int lowrank_table(int count, const kfac_bn_lowrank_item* items,
-                         std::vector<BnLowRankItem>& tab, long long& blocks,
-                         size_t& smem_max) {
+                         std::vector<BnLowRankItem>& tab, long long& blocks) {
   KFAC_REQUIRE(count > 0 && items != nullptr, "bn_lowrank: no items");
   KFAC_REQUIRE(count <= kBnItemsMax, "bn_lowrank: %d layers, at most %d",
                count, kBnItemsMax);
   tab.resize(count);
   blocks = 0;
-  smem_max = 0;
   for (int i = 0; i < count; ++i) {
     const kfac_bn_lowrank_item& k = items[i];
     KFAC_REQUIRE(k.hist && k.scaled && k.c > 0 && k.rows_per_slot > 0 &&
@@ -974,8 +972,6 @@ static int lowrank_table(int count, const kfac_bn_lowrank_item* items,
                             ? sqrtf(k.slot_weight[s]) : 0.f;
     t.blk_begin = (int)blocks;
     blocks += t.m;
-    const size_t sm = (size_t)(4 * k.c + 2 * t.m) * sizeof(float);
-    smem_max = sm > smem_max ? sm : smem_max;
   }
   KFAC_REQUIRE(blocks < (1ll << 31), "bn_lowrank: too many rows");
   return KFAC_OK;
@@ -986,8 +982,7 @@ extern "C" int kfac_bn_lowrank_scale(int count,
                                      void* stream) {
   std::vector<BnLowRankItem> tab;
   long long blocks = 0;
-  size_t smem = 0;
-  int rc = lowrank_table(count, items, tab, blocks, smem);
+  int rc = lowrank_table(count, items, tab, blocks);
   if (rc != KFAC_OK) return rc;
   void* dev = nullptr;
   rc = ring_alloc(tab.size() * sizeof(BnLowRankItem), &dev);
@@ -1006,8 +1001,7 @@ extern "C" int kfac_bn_lowrank_apply(int count,
                                      float lr, float momentum, void* stream) {
   std::vector<BnLowRankItem> tab;
   long long blocks = 0;
-  size_t smem = 0;
-  int rc = lowrank_table(count, items, tab, blocks, smem);
+  int rc = lowrank_table(count, items, tab, blocks);
   if (rc != KFAC_OK) return rc;
   for (int i = 0; i < count; ++i) {
     const kfac_bn_lowrank_item& k = items[i];
