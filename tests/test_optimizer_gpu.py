@@ -404,6 +404,13 @@ def test_normalize_weight_hook_matches_restatement():
     assert rel(host(p.data), orc.normalize_weight(host(w))) < 1e-6
 
 
+def test_driver_smoke_entry_point():
+    """The driver's smoke() (one small pass of the hot path checked against
+    the oracle) stays green."""
+    import __graft_entry__
+    __graft_entry__.smoke()
+
+
 def test_bench_resnet50_step_runs():
     from bench_model import build_training_step
     step, h2d, d2h = build_training_step(
