@@ -525,11 +525,14 @@ class InversePlanSet(object):
             ev.record(st)
         self._early[c] = ev
 
-    def run(self, damping, use_pi=True, after_class=None):
+    def run(self, damping, use_pi=True, after_class=None, join=True):
         """Run every class not started yet and join all of them.
         ``after_class(c)``, if given, is called on class c's stream right
         after its plan (its kernels then overlap the other classes'
-        inverses); it must only touch data of that class."""
+        inverses); it must only touch data of that class.  With
+        ``join=False`` the current stream does not wait for the classes on
+        side streams: the call returns {class: event} for them and the
+        caller orders later work after those events itself."""
         cur = torch.cuda.current_stream()
         start = torch.cuda.Event()
         start.record(cur)
@@ -555,13 +558,18 @@ class InversePlanSet(object):
             self.plans[rest[0]].run(damping, use_pi)
             if after_class is not None:
                 after_class(rest[0])
+        pending = {}
         for c, st in zip(rest[1:], self.streams):
             done = torch.cuda.Event()
             done.record(st)
-            cur.wait_event(done)
-        for ev in self._early.values():
-            cur.wait_event(ev)
+            pending[c] = done
+        pending.update(self._early)
         self._early = {}
+        if not join:
+            return pending
+        for ev in pending.values():
+            cur.wait_event(ev)
+        return {}
 
     def set_refine(self, max_dim, threshold=3e-5):
         for p in self.plans:

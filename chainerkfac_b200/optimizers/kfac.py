@@ -291,6 +291,18 @@ class KFAC(_base.GradientMethod):
         self.eager_inverses = False
         self._eager = None
         self._eager_stream = None
+        # Let update() return while size classes still run on their side
+        # streams (the serial chains of the largest factors outlast
+        # everything else): the next forward pass then overlaps them, and
+        # every layer waits for its own class right before it is called
+        # (forward pre-hooks installed by setup()).  Off by default: code that
+        # reads weights other than by calling the layers (checkpoints,
+        # parameter statistics) must call join() first.  Single process, one
+        # damping group, every update fused into the preconditioning.
+        self.defer_join = False
+        self._pending_classes = {}      # class index -> event
+        self._block_class = {}          # id(fblock) -> class index
+        self._deferred_refs = None      # gradients the side streams still read
         self.observation = {}
 
     lr = _base.HyperparameterProxy('lr')
@@ -311,7 +323,31 @@ class KFAC(_base.GradientMethod):
             self.fblocks.append(fblock)
         self._set_low_rank(1, 0, None)
         self.kfhook = KFACHook(self.fblocks)
+        for fb in self.fblocks:
+            module = getattr(fb.link, 'module', None)
+            if module is not None:
+                module.register_forward_pre_hook(
+                    lambda m, inp, fb=fb: self._wait_for_block(fb))
         return self
+
+    def _wait_for_block(self, fb):
+        """Forward pre-hook of a layer: its weights may still be being
+        updated on a side stream (defer_join)."""
+        if not self._pending_classes:
+            return
+        ev = self._pending_classes.pop(self._block_class.get(id(fb)), None)
+        if ev is not None:
+            torch.cuda.current_stream().wait_event(ev)
+
+    def join(self):
+        """Order the current stream after every size class still running
+        on a side stream (see defer_join)."""
+        if self._pending_classes:
+            cur = torch.cuda.current_stream()
+            for ev in self._pending_classes.values():
+                cur.wait_event(ev)
+            self._pending_classes = {}
+        self._deferred_refs = None
 
     def _set_low_rank(self, world, rank, owned):
         on = self.bn_low_rank and self.acc_iters == 1
@@ -663,6 +699,7 @@ class KFAC(_base.GradientMethod):
         fblocks = list(fblocks)
         if not fblocks:
             return
+        self.join()        # classes left over from the previous update
         if self._factors_pending:
             self._factors_pending = False
             plan = self._plan_for(fblocks)
@@ -682,6 +719,8 @@ class KFAC(_base.GradientMethod):
         for fb in fblocks:
             groups.setdefault((fb.damping, fb._pi_type), []).append(fb)
         done = set()
+        defer = (self.defer_join and type(self) is KFAC and
+                 len(groups) == 1 and not self._post_update_hooks)
         for (damping, pi_type), group in groups.items():
             plan = self._plan_for(group)
             if plan is None:
@@ -696,17 +735,39 @@ class KFAC(_base.GradientMethod):
                 classes = plan.classes()
 
                 def after(c, owner=owner, classes=classes):
-                    part, seen = [], set()
+                    part, part_bn, seen = [], [], set()
                     for i in classes[c]:
                         fb = owner[i]
-                        if id(fb) not in seen and \
-                                isinstance(fb, FB.FisherBlockConnection):
-                            seen.add(id(fb))
+                        if id(fb) in seen:
+                            continue
+                        seen.add(id(fb))
+                        if isinstance(fb, FB.FisherBlockConnection):
                             part.append(fb)
+                        elif defer:
+                            part_bn.append(fb)
                     if part:
                         self._precondition(part, ws_key=c)
-                        done.update(id(fb) for fb in part)
-            plan.run(damping, pi_type == PI_TYPE_TRACENORM, after_class=after)
+                    if part_bn:
+                        self._precondition_bn(part_bn)
+                    done.update(id(fb) for fb in part + part_bn)
+            pending = plan.run(damping, pi_type == PI_TYPE_TRACENORM,
+                               after_class=after, join=not defer)
+            if defer:
+                # (the damping values stay on the device, unread: gathering
+                # them would wait for every class)
+                self._pending_classes = pending
+                self._block_class = {}
+                owner_cls = {}
+                for c, idx in enumerate(plan.classes()):
+                    for i in idx:
+                        owner_cls[i] = c
+                k = 0
+                for fb in group:
+                    n = len(fb.plan_factors())
+                    if n:
+                        self._block_class[id(fb)] = owner_cls[k]
+                    k += n
+                continue
             diag = plan.diag
             k = 0
             for fb in group:
@@ -720,9 +781,19 @@ class KFAC(_base.GradientMethod):
         if conn:
             self._precondition(conn)
         bn = [fb for fb in fblocks
-              if isinstance(fb, FB.FisherBlockBatchNormalization)]
+              if isinstance(fb, FB.FisherBlockBatchNormalization) and
+              id(fb) not in done]
         if bn:
             self._precondition_bn(bn)
+        if self._pending_classes:
+            # the side streams still read this step's gradients: keep them
+            # from being handed out again until the classes are joined; a
+            # parameter whose update was not fused needs its class now
+            params = [p for fb in fblocks for p in fb.link.params()]
+            if all(getattr(p, '_kfac_applied', False) for p in params):
+                self._deferred_refs = [p.grad for p in params]
+            else:
+                self.join()
 
     def _precondition_bn(self, blocks):
         """All BatchNormalization blocks in one grouped call, with the

@@ -215,3 +215,74 @@ def test_grouped_build_of_all_resnet50_factors():
         worst = max(worst, eA, eG)
     assert worst < 7e-5, worst      # drift stays well inside the bound
     wl.plan.close()
+
+
+@pytest.mark.parametrize('c,rows,slots', [(256, 32, 8), (1024, 64, 8),
+                                          (2048, 256, 8)])
+def test_bn_low_rank_form_at_full_size(c, rows, slots):
+    """The low-rank form of a BatchNormalization block at ResNet-50 sizes
+    (C up to 2048; 8 slots of 32 rows on one GPU, of 256 rows on eight)
+    against the same formula in fp64: two blocks in one grouped call, a ring
+    whose newest slot is in the middle, one slot still unused, the fused
+    momentum update."""
+    from chainerkfac_b200 import ops
+
+    def dev(a):
+        return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+    def host(t):
+        return t.detach().cpu().numpy()
+
+    def rel(a, b):
+        return float(np.linalg.norm(a.astype(np.float64) - b) /
+                     np.linalg.norm(b))
+
+    rng = np.random.default_rng(c + rows)
+    m, d = rows * slots, 2 * c
+    dg, db = 16.0 * 2.5e-4, 16.0 * 1e-3
+    lr, mom = 0.05, 0.9
+    items, wants, outs = [], [], []
+    plans = []
+    for blk in range(2):
+        hist = (rng.standard_normal((m, d)) * 0.5).astype(np.float32)
+        age = [(3 - s) % slots for s in range(slots)]      # newest: slot 3
+        w = [0.9 * 0.1 ** a * 8.0 / rows for a in age]
+        w[5] = 0.0                                           # unused slot
+        gg = rng.standard_normal(c).astype(np.float32)
+        gb = rng.standard_normal(c).astype(np.float32)
+        dinv = np.concatenate([np.full(c, dg ** -0.5), np.full(c, db ** -0.5)])
+        scale = np.repeat(np.sqrt(np.array(w, np.float64)), rows)
+        Hs64 = hist.astype(np.float64) * scale[:, None] * dinv[None, :]
+        gp = np.concatenate([gg, gb]).astype(np.float64) * dinv
+        y = np.linalg.solve(np.eye(m) + Hs64 @ Hs64.T, Hs64 @ gp)
+        want = (gp - Hs64.T @ y) * dinv
+        wants.append(want)
+        hist_d = dev(hist)
+        Hs = torch.empty_like(hist_d)
+        M0 = torch.empty((m, m), device='cuda')
+        Minv = torch.empty_like(M0)
+        kg, kb = torch.empty(c, device='cuda'), torch.empty(c, device='cuda')
+        pg, pb = torch.ones(c, device='cuda'), torch.ones(c, device='cuda')
+        vg, vb = torch.zeros(c, device='cuda'), torch.zeros(c, device='cuda')
+        flag = torch.zeros(2, dtype=torch.int32, device='cuda')
+        items.append(ops.bn_lowrank_item(hist_d, Hs, c, rows, w, dg, db, Minv,
+                                         dev(gg), dev(gb), kg, kb, flag,
+                                         pg, pb, vg, vb))
+        outs.append((Hs, M0, Minv, kg, kb, pg, flag))
+    ops.bn_lowrank_scale(items)
+    ops.factor_group([ops.dense_t_item(o[0], 1.0, 0.0, o[1]) for o in outs],
+                     outs[0][1].device)
+    plan = ops.InversePlanSet([o[1] for o in outs], [o[2] for o in outs],
+                              [-1, -1], [2, 2], scale=[1.0, 1.0])
+    plan.run(1.0, False)
+    ops.bn_lowrank_apply(items, lr, mom)
+    torch.cuda.synchronize()
+    assert plan.info.cpu().tolist() == [0, 0]
+    for (Hs, M0, Minv, kg, kb, pg, flag), want in zip(outs, wants):
+        got = np.concatenate([host(kg), host(kb)])
+        assert rel(got, want) < 1e-3, rel(got, want)
+        assert flag.cpu().tolist() == [0, 0]
+        # fused update: v = -lr * kf, gamma = 1 + v
+        assert rel(host(pg) - 1.0, -lr * want[:c]) < 1e-3
+        assert float(Hs[5 * rows:6 * rows].abs().max()) == 0.0
+    plan.close()

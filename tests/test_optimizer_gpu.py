@@ -270,6 +270,35 @@ def test_classes_started_during_backward_give_the_same_steps(monkeypatch):
         assert rel(a, b) < 1e-6
 
 
+def test_deferred_join_gives_the_same_steps(monkeypatch):
+    """With defer_join the update returns while size classes still run on
+    side streams; every layer waits for its class in a forward pre-hook.
+    The trajectory must not change, join() must make the weights readable,
+    and a layer that is never called again is joined by the next update."""
+    import chainerkfac_b200 as ck
+    monkeypatch.setenv('KFAC_CLASS_BOUNDS', '20,60')
+    finals = {}
+    for defer in (True, False):
+        torch.manual_seed(3)
+        model = SmallNet().cuda()
+        opt = ck.KFAC(lr=0.05, momentum=0.9, cov_ema_decay=0.9, damping=1e-2)
+        opt.defer_join = defer
+        opt.setup(model)
+        g = torch.Generator(device='cuda').manual_seed(4)
+        seen_pending = 0
+        for _ in range(6):
+            x = torch.randn(6, 3, 10, 10, device='cuda', generator=g)
+            t = torch.randint(0, 7, (6,), device='cuda', generator=g)
+            opt.update(lambda a, b: F.cross_entropy(model(a), b), x, t)
+            seen_pending += len(opt._pending_classes)
+        assert (seen_pending > 0) == defer
+        opt.join()
+        assert not opt._pending_classes
+        finals[defer] = [host(p.data) for p in model.parameters()]
+    for a, b in zip(finals[True], finals[False]):
+        assert rel(a, b) < 1e-6
+
+
 def test_running_average_over_steps_stays_undamped():
     import chainerkfac_b200 as ck
     torch.manual_seed(1)
