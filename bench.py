@@ -856,15 +856,31 @@ class DistributedWorkload(DeviceWorkload):
             dist.broadcast(got, src=owner)
             worst_i = max(worst_i, float((got.double() - want).norm() /
                                          want.norm()))
-        diff = torch.zeros(1, device=mine[0].device, dtype=torch.float64)
-        for w in self.flat(self.P):
-            ref = w.clone()
-            dist.broadcast(ref, src=0)
-            diff = torch.maximum(diff, (w - ref).abs().max().double())
-        dist.all_reduce(diff, op=dist.ReduceOp.MAX)
+        # every rank's weights against rank 0's, element by element (a NaN
+        # counts as a difference), the layers that differ, and what the
+        # owners' inverse plans reported
+        dev0 = mine[0].device
+        bad = torch.zeros(len(self.layers), device=dev0, dtype=torch.float64)
+        nonfinite = torch.zeros(1, device=dev0, dtype=torch.float64)
+        for li, blk in enumerate(self.P):
+            for w in blk:
+                if w is None:
+                    continue
+                ref = w.clone()
+                dist.broadcast(ref, src=0)
+                bad[li] += (w != ref).sum().double()
+                nonfinite += (~torch.isfinite(w)).sum().double()
+        pivots = (self.plan.info != 0).sum().double().reshape(1)
+        for t in (bad, nonfinite, pivots):
+            dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        differing = [self.layers[li]['name'] for li in
+                     torch.nonzero(bad).flatten().tolist()]
         return dict(layer=self.layers[i]['name'], owner=owner,
                     factor_rel=worst_f, inverse_rel=worst_i,
-                    weights_equal=bool(float(diff.item()) == 0.0))
+                    weights_equal=not differing,
+                    weights_differing_layers=differing[:8],
+                    weights_nonfinite=int(nonfinite.item()),
+                    nonpositive_pivots_all_ranks=int(pivots.item()))
 
 
 def time_alone(torch, fn, reps):

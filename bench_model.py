@@ -79,9 +79,6 @@ def build_training_step(device, batch, world, rank, cov_ema_decay, damping,
         opt = ck.DistributedKFAC(comm, ownership='balanced', **kwargs)
     else:
         opt = ck.KFAC(**kwargs)
-        # the training loop below touches the model only by calling it: the
-        # largest factors' inverses may still run when update() returns
-        opt.defer_join = True
     opt.setup(model)
 
     g = torch.Generator().manual_seed(99 + rank)
