@@ -35,17 +35,26 @@ def _chk(t, name):
 
 
 class Workspace(object):
-    """Grow-only device scratch buffer."""
+    """Grow-only device scratch buffers, one per (device, CUDA stream): two
+    calls that run on different streams at the same time (a factor build on
+    the exchange stream beside one on the main stream) must not share their
+    partial tiles."""
 
     def __init__(self):
-        self.buf = None
+        self.bufs = {}
 
     def get(self, nbytes, device):
         nbytes = max(int(nbytes), 256)
-        if self.buf is None or self.buf.numel() < nbytes or \
-                self.buf.device != torch.device(device):
-            self.buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
-        return self.buf
+        device = torch.device(device)
+        key = (device, torch.cuda.current_stream(device).cuda_stream
+               if device.type == 'cuda' else 0)
+        buf = self.bufs.get(key)
+        if buf is None or buf.numel() < nbytes:
+            # allocated under the calling stream: the caching allocator
+            # hands the old buffer on in that stream's order
+            buf = self.bufs[key] = torch.empty(nbytes, dtype=torch.uint8,
+                                               device=device)
+        return buf
 
 
 _factor_ws = Workspace()
