@@ -203,6 +203,40 @@ def test_factor_group_matches_single_calls(ops):
                                          False)) < FACTOR_TOL
 
 
+def test_scratch_buffers_are_per_stream(ops):
+    """Factor builds issued on different CUDA streams may run at the same
+    time (the exchange stream builds a low-rank block's matrix while the main
+    stream builds the next size class): their partial-tile scratch must not
+    be the same memory."""
+    ws = ops.Workspace()
+    dev0 = torch.device('cuda', torch.cuda.current_device())
+    a = ws.get(1 << 20, dev0)
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        b = ws.get(1 << 20, dev0)
+        assert ws.get(1 << 10, dev0) is b          # grow-only, reused
+    assert a.data_ptr() != b.data_ptr()
+    assert ws.get(1 << 20, dev0) is a
+    # and a grouped build on a side stream beside one on the main stream
+    rng = np.random.default_rng(5)
+    x1 = dev(rng.standard_normal((90000, 200)).astype(np.float32))
+    x2 = dev(rng.standard_normal((80000, 150)).astype(np.float32))
+    o1 = torch.empty((200, 200), device='cuda')
+    o2 = torch.empty((150, 150), device='cuda')
+    torch.cuda.synchronize()
+    for _ in range(3):
+        ops.factor_group([ops.dense_item(x1, False, 1.0 / 90000, 0.0, o1)],
+                         dev0)
+        with torch.cuda.stream(side):
+            ops.factor_group([ops.dense_item(x2, False, 1.0 / 80000, 0.0, o2)],
+                             dev0)
+    torch.cuda.synchronize()
+    w1 = host(x1).astype(np.float64)
+    w2 = host(x2).astype(np.float64)
+    assert rel(host(o1), w1.T @ w1 / 90000) < FACTOR_TOL
+    assert rel(host(o2), w2.T @ w2 / 80000) < FACTOR_TOL
+
+
 def test_factor_builds_from_staged_operands(ops, engine):
     """The optional operand feed of the factor builds (staging pass that
     writes X^T as two bf16 planes, TMA boxes into the tile kernel) against the
