@@ -923,6 +923,15 @@ def run_ours(args):
         dist.init_process_group('nccl', device_id=device)
     lib = _lib.load()
     batch, acc = spec['batch'], spec['acc']
+    if args.only_e2e:
+        # the end-to-end steps alone (what a profiler run wants to see)
+        e2e = run_e2e(args, device, world, rank, spec, profile=True)
+        if rank == 0:
+            print(json.dumps({'e2e': e2e, 'n_gpus': world,
+                              'workload': spec['name']}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
     prebuilt = bool(spec.get('prebuilt'))
 
     if world > 1:
@@ -1140,7 +1149,7 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-def run_e2e(args, device, world, rank, spec):
+def run_e2e(args, device, world, rank, spec, profile=False):
     """images/sec of KFAC.update(lossfun, x, t) on a torch ResNet-50 with the
     batch copied from pinned host memory and the loss read back every step."""
     import torch
@@ -1159,11 +1168,15 @@ def run_e2e(args, device, world, rank, spec):
         torch.distributed.barrier()
     t0 = torch.cuda.Event(enable_timing=True)
     t1 = torch.cuda.Event(enable_timing=True)
+    if profile:
+        torch.cuda.profiler.start()
     t0.record()
     for _ in range(steps):
         step()
     t1.record()
     torch.cuda.synchronize()
+    if profile:
+        torch.cuda.profiler.stop()
     ms = torch.tensor([t0.elapsed_time(t1)], device=device, dtype=torch.float64)
     if world > 1:
         torch.distributed.all_reduce(ms, op=torch.distributed.ReduceOp.MAX)
@@ -1460,6 +1473,9 @@ def main():
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--workload', default='resnet50', choices=sorted(WORKLOADS))
     ap.add_argument('--no-e2e', action='store_true')
+    ap.add_argument('--only-e2e', action='store_true',
+                    help='run only the end-to-end steps (KFAC.update on the '
+                         'torch model), bracketed by cudaProfilerStart/Stop')
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--no-bn-blocks', action='store_true',
                     help='leave the BatchNormalization layers to the plain '
