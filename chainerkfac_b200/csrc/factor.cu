@@ -230,7 +230,6 @@ bn_stats_group_kernel(const BnItem* __restrict__ items, int nitems) {
     const int smp = (int)(warp / it.c), ch = (int)(warp - (long long)smp * it.c);
     const float* px = it.x + warp * it.hw;
     double s = 0.0, ss = 0.0;
-#pragma unroll 4
     for (int i = lane; i < it.hw; i += 32) {
       const double v = px[i];
       s += v;
@@ -259,7 +258,6 @@ bn_stats_group_kernel(const BnItem* __restrict__ items, int nitems) {
   double s = 0.0, ss = 0.0;
   if (ch < it.c) {
     const float* p = it.x + (long long)smp * it.hw * it.c + ch;
-#pragma unroll 4
     for (int q = px; q < it.hw; q += 32) {
       const double v = p[(long long)q * it.c];
       s += v;
@@ -321,7 +319,6 @@ bn_grads_group_kernel(const BnItem* __restrict__ items, int nitems) {
     const float* px = it.x + warp * it.hw;
     const float* pg = it.gy + warp * it.hw;
     float a = 0.f, g0 = 0.f;
-#pragma unroll 4
     for (int i = lane; i < it.hw; i += 32) {
       const float g = pg[i] * it.scale;
       a += g * ((px[i] - mean) * istd);
@@ -369,7 +366,6 @@ bn_grads_group_kernel(const BnItem* __restrict__ items, int nitems) {
     const float mean = s_mean[cx], istd = s_istd[cx];
     const float* pxp = it.x + (long long)smp * it.hw * it.c + ch;
     const float* pg = it.gy + (long long)smp * it.hw * it.c + ch;
-#pragma unroll 4
     for (int q = px; q < it.hw; q += 32) {
       const float g = pg[(long long)q * it.c] * it.scale;
       a += g * ((pxp[(long long)q * it.c] - mean) * istd);
