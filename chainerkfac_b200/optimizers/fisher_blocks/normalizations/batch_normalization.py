@@ -286,12 +286,18 @@ class FisherBlockBatchNormalization(FisherBlock):
                 slot.zero_()      # the other ranks' rows arrive by the sum
             out = slot[self.low_rank_rank * n:(self.low_rank_rank + 1) * n]
             self.covs = None
+        # (the output moves from slot to slot of the history ring in the
+        # low-rank form: it is not part of the key but patched in)
         key = (x.data_ptr(), gy.data_ptr(), x.shape, x.stride(), gy.stride(),
-               None if out is None else out.data_ptr(), self._loss_scale)
+               self._loss_scale)
         memo = getattr(self, '_item_memo', None)
         self._keep_x, self._keep_gy = x, gy
-        if memo is not None and memo[0] == key:
+        if memo is not None and memo[0] == key and out is not None and \
+                out.shape == memo[1].result.shape:
             it = memo[1]
+            it.out = out.data_ptr()
+            it.result = out
+            it._keep = (out, it._keep[-1])
         else:
             it = ops.bn_item(x, gy, float(self.link.eps), self.gy_scale(n),
                              out, getattr(self, '_stats', None))
@@ -299,9 +305,7 @@ class FisherBlockBatchNormalization(FisherBlock):
             self._item_memo = None
             if it.x == x.data_ptr() and it.gy == gy.data_ptr():
                 it._keep = it._keep[2:]   # output and statistics only
-                self._item_memo = (
-                    (x.data_ptr(), gy.data_ptr(), x.shape, x.stride(),
-                     gy.stride(), it.result.data_ptr(), self._loss_scale), it)
+                self._item_memo = (key, it)
         self._grads_item = it
         self._grads = it.result
         return it
