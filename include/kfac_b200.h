@@ -9,6 +9,16 @@
  * function synchronises the device or the stream unless it says so.  There is
  * no CPU implementation behind this interface.
  *
+ * Grouped entry points (one call for many layers) copy their per-layer tables
+ * to the device through an 8 MiB ring per device, allocated on first use (the
+ * one exception is kfac_factor_dense_noalloc, which allocates nothing).  A
+ * table is read by the kernels of its own call, in stream order; the ring
+ * has no in-flight tracking, so a region is handed out again once 8 MiB of
+ * later tables have been requested: callers that let the host run more than
+ * a few thousand grouped calls ahead of the device must synchronise.  A
+ * workspace passed to a call is scratch of that call's kernels: calls that
+ * may run at the same time (different streams) need different workspaces.
+ *
  * The reference (chainerkfac) has no native boundary: each entry point names
  * the Python function(s) of the reference whose arithmetic it replaces, by
  * path inside the chainerkfac project.
