@@ -14,8 +14,9 @@
  * one exception is kfac_factor_dense_noalloc, which allocates nothing).  A
  * table is read by the kernels of its own call, in stream order; the ring
  * has no in-flight tracking, so a region is handed out again once 8 MiB of
- * later tables have been requested: callers that let the host run more than
- * a few thousand grouped calls ahead of the device must synchronise.  A
+ * later tables have been requested (a ResNet-50 step with 161 factors
+ * requests about 0.3 MiB): a caller whose host runs that far ahead of the
+ * device must synchronise.  A
  * workspace passed to a call is scratch of that call's kernels: calls that
  * may run at the same time (different streams) need different workspaces.
  *
