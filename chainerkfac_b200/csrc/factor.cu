@@ -194,6 +194,7 @@ struct BnItem {
   float eps, scale;
   int stat_begin;    // first block of this layer in the statistics launch
   int grad_begin;    // first block of this layer in the gradient launch
+  int chan_begin;    // first channel of this layer in the finishing launch
 };
 
 constexpr int kBnItemsMax = 256;
@@ -277,6 +278,33 @@ bn_stats_group_kernel(const BnItem* __restrict__ items, int nitems) {
   }
 }
 
+// Batch mean and 1/sqrt(var + eps) of every channel from the per-sample sums,
+// added up in a fixed order: a thread per channel over all layers.
+__global__ void __launch_bounds__(256)
+bn_finish_stats_kernel(const BnItem* __restrict__ items, int nitems,
+                       int channels) {
+  __shared__ int s_begin[kBnItemsMax];
+  for (int i = threadIdx.x; i < nitems; i += blockDim.x)
+    s_begin[i] = items[i].chan_begin;
+  __syncthreads();
+  const int g = blockIdx.x * blockDim.x + threadIdx.x;
+  if (g >= channels) return;
+  const BnItem& it = items[bn_find_item(s_begin, nitems, g)];
+  const int ch = g - it.chan_begin;
+  const double* part = reinterpret_cast<const double*>(it.stats + 2 * it.c);
+  double ds = 0.0, dss = 0.0;
+  for (int k = 0; k < it.n; ++k) {
+    ds += part[(long long)k * 2 * it.c + ch];
+    dss += part[(long long)k * 2 * it.c + it.c + ch];
+  }
+  const double per = (double)it.n * it.hw;
+  const double mean = ds / per;
+  double var = dss / per - mean * mean;
+  if (var < 0.0) var = 0.0;
+  it.stats[ch] = (float)mean;
+  it.stats[it.c + ch] = (float)(1.0 / sqrt(var + (double)it.eps));
+}
+
 // out[s, j] = scale * sum_p gy xhat, out[s, c + j] = scale * sum_p gy.
 // Planes: a warp per (sample, channel).  Channels-last: a block per (sample,
 // 32 channels), lanes along channels.
@@ -294,28 +322,7 @@ bn_grads_group_kernel(const BnItem* __restrict__ items, int nitems) {
     const int lane = threadIdx.x & 31;
     if (warp >= (long long)it.n * it.c) return;
     const int smp = (int)(warp / it.c), ch = (int)(warp - (long long)smp * it.c);
-    // mean and 1/sqrt(var + eps) from the per-sample sums, added up in a
-    // fixed order (lanes take samples, then a butterfly)
-    const double* part = reinterpret_cast<const double*>(it.stats + 2 * it.c);
-    double ds = 0.0, dss = 0.0;
-    for (int k = lane; k < it.n; k += 32) {
-      ds += part[(long long)k * 2 * it.c + ch];
-      dss += part[(long long)k * 2 * it.c + it.c + ch];
-    }
-    for (int o = 16; o > 0; o >>= 1) {
-      ds += __shfl_xor_sync(0xffffffffu, ds, o);
-      dss += __shfl_xor_sync(0xffffffffu, dss, o);
-    }
-    const double per = (double)it.n * it.hw;
-    const double dmean = ds / per;
-    double var = dss / per - dmean * dmean;
-    if (var < 0.0) var = 0.0;
-    const float mean = (float)dmean;
-    const float istd = (float)(1.0 / sqrt(var + (double)it.eps));
-    if (smp == 0 && lane == 0) {
-      it.stats[ch] = mean;
-      it.stats[it.c + ch] = istd;
-    }
+    const float mean = it.stats[ch], istd = it.stats[it.c + ch];
     const float* px = it.x + warp * it.hw;
     const float* pg = it.gy + warp * it.hw;
     float a = 0.f, g0 = 0.f;
@@ -335,35 +342,14 @@ bn_grads_group_kernel(const BnItem* __restrict__ items, int nitems) {
     return;
   }
   // channels-last: a block per (sample, 8 channels), as in the statistics
-  // kernel; mean and 1/sqrt(var + eps) of its channels first, from the
-  // per-sample sums
+  // kernel
   const int groups = (it.c + 7) >> 3;
   const int smp = b / groups, cg = b - smp * groups;
   const int cx = threadIdx.x & 7, px = threadIdx.x >> 3;
   const int ch = 8 * cg + cx;
-  __shared__ float s_mean[8], s_istd[8];
-  if (threadIdx.x < 8 && ch < it.c) {
-    const double* part = reinterpret_cast<const double*>(it.stats + 2 * it.c);
-    double ds = 0.0, dss = 0.0;
-    for (int k = 0; k < it.n; ++k) {
-      ds += part[(long long)k * 2 * it.c + ch];
-      dss += part[(long long)k * 2 * it.c + it.c + ch];
-    }
-    const double per = (double)it.n * it.hw;
-    const double mean = ds / per;
-    double var = dss / per - mean * mean;
-    if (var < 0.0) var = 0.0;
-    s_mean[cx] = (float)mean;
-    s_istd[cx] = (float)(1.0 / sqrt(var + (double)it.eps));
-    if (smp == 0) {
-      it.stats[ch] = s_mean[cx];
-      it.stats[it.c + ch] = s_istd[cx];
-    }
-  }
-  __syncthreads();
   float a = 0.f, g0 = 0.f;
   if (ch < it.c) {
-    const float mean = s_mean[cx], istd = s_istd[cx];
+    const float mean = it.stats[ch], istd = it.stats[it.c + ch];
     const float* pxp = it.x + (long long)smp * it.hw * it.c + ch;
     const float* pg = it.gy + (long long)smp * it.hw * it.c + ch;
     for (int q = px; q < it.hw; q += 32) {
@@ -843,7 +829,7 @@ extern "C" int kfac_bn_sample_grads_group(int count,
                "bn_sample_grads_group: %d layers in one call, at most %d",
                count, kBnItemsMax);
   std::vector<BnItem> tab(count);
-  long long sb = 0, gb = 0;
+  long long sb = 0, gb = 0, cbeg = 0;
   for (int i = 0; i < count; ++i) {
     const kfac_bn_item& k = items[i];
     KFAC_REQUIRE(k.x && k.gy && k.out && k.stats,
@@ -858,6 +844,8 @@ extern "C" int kfac_bn_sample_grads_group(int count,
     t.eps = k.eps; t.scale = k.scale;
     t.stat_begin = (int)sb;
     t.grad_begin = (int)gb;
+    t.chan_begin = (int)cbeg;
+    cbeg += k.c;
     const long long cg = (k.c + 7) / 8;
     sb += t.nhwc ? (long long)k.n * cg : ((long long)k.n * k.c + 7) / 8;
     gb += t.nhwc ? (long long)k.n * cg : ((long long)k.n * k.c + 7) / 8;
@@ -873,6 +861,10 @@ extern "C" int kfac_bn_sample_grads_group(int count,
   bn_stats_group_kernel<<<(int)sb, 256, 0, st>>>(static_cast<BnItem*>(dev),
                                                  count);
   KFAC_LAUNCH_CHECK("bn_stats_group_kernel");
+  KFAC_REQUIRE(cbeg < (1ll << 31), "bn_sample_grads_group: too many channels");
+  bn_finish_stats_kernel<<<(int)((cbeg + 255) / 256), 256, 0, st>>>(
+      static_cast<BnItem*>(dev), count, (int)cbeg);
+  KFAC_LAUNCH_CHECK("bn_finish_stats_kernel");
   bn_grads_group_kernel<<<(int)gb, 256, 0, st>>>(static_cast<BnItem*>(dev),
                                                  count);
   KFAC_LAUNCH_CHECK("bn_grads_group_kernel");
